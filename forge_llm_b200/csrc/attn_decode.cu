@@ -1,0 +1,182 @@
+// Single-query decode attention over the paged fp16 KV cache (replaces attention_flash,
+// crates/forgellm-codegen-cpu/src/emit.rs:657-715; GQA mapping kv_head = h / (nq/nkv), :660-666).
+// HBM-bound on K/V: the context is split over CTAs (split-KV), every K/V row is read once per
+// KV head with 128-bit loads and shared by the query heads of its group, the online-softmax
+// state (m, l, acc) is f32, exp is expf.  Split partials are merged by the last CTA to finish
+// a KV head (atomic ticket), so no second launch is needed.
+#include "common.cuh"
+
+namespace forge {
+
+namespace {
+
+constexpr int kThreads = 128;
+constexpr int kGC = 4;  // query heads processed per pass over the keys
+
+template <int HD> struct Seg { static constexpr int W = (HD == 64) ? 8 : 16, ACTIVE = HD / 8, RPW = 32 / W; };
+
+struct DecParams {
+    AttnDecodeArgs a;
+    float scale;
+};
+
+__device__ __forceinline__ void unpack8(const uint4& v, float* f) {
+    const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { float2 t = __half22float2(h[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
+}
+
+template <int HD>
+__global__ void __launch_bounds__(kThreads) attn_decode_kernel(DecParams p) {
+    constexpr int W = Seg<HD>::W, ACTIVE = Seg<HD>::ACTIVE, RPW = Seg<HD>::RPW;
+    constexpr int PARTS = (kThreads / 32) * RPW;
+    __shared__ float s_ml[PARTS][kGC][2];
+    __shared__ float s_acc[PARTS][kGC][HD];
+    __shared__ int s_last;
+    const AttnDecodeArgs& a = p.a;
+    const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int seg = lane / W, sl = lane % W;
+    const bool act = sl < ACTIVE;
+    const int G = a.nq / a.nkv, kvd = a.nkv * HD;
+    const int n_ctx = a.seq_len ? a.seq_len[b] + 1 : a.seq_len_host;
+    int chunk = (n_ctx + a.splits - 1) / a.splits;
+    chunk = (chunk + PARTS - 1) / PARTS * PARTS;
+    const int t_begin = split * chunk;
+    const int t_end = min(n_ctx, t_begin + chunk);
+    const int32_t* pt = a.page_table ? a.page_table + size_t(b) * a.pages_per_seq : nullptr;
+    const size_t seq_base = a.page_table ? 0 : size_t(b) * a.max_ctx;  // contiguous: [batch][max_ctx][kvd]
+    const int part = warp * RPW + seg;
+
+    for (int g0 = 0; g0 < G; g0 += kGC) {
+        const int gc = min(kGC, G - g0);
+        float q[kGC][8], acc[kGC][8], mi[kGC], li[kGC];
+#pragma unroll
+        for (int g = 0; g < kGC; ++g) {
+            mi[g] = -INFINITY; li[g] = 0.f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) { acc[g][i] = 0.f; q[g][i] = 0.f; }
+            if (g < gc && act) {
+                const float4* qp = reinterpret_cast<const float4*>(a.q + (size_t(b) * a.nq + kvh * G + g0 + g) * HD + sl * 8);
+                float4 x0 = qp[0], x1 = qp[1];
+                q[g][0] = x0.x; q[g][1] = x0.y; q[g][2] = x0.z; q[g][3] = x0.w;
+                q[g][4] = x1.x; q[g][5] = x1.y; q[g][6] = x1.z; q[g][7] = x1.w;
+            }
+        }
+        for (int base = t_begin + warp * RPW; base < t_end; base += PARTS) {
+            const int t = base + seg;
+            const bool valid = t < t_end;
+            float kf[8], vf[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) { kf[i] = 0.f; vf[i] = 0.f; }
+            if (valid && act) {
+                const int lp = t / FORGE_KV_PAGE;
+                const size_t row = seq_base + size_t(pt ? pt[lp] : lp) * FORGE_KV_PAGE + t % FORGE_KV_PAGE;
+                const size_t off = row * kvd + kvh * HD + sl * 8;
+                uint4 kr = *reinterpret_cast<const uint4*>(a.k_pool + off);
+                uint4 vr = *reinterpret_cast<const uint4*>(a.v_pool + off);
+                unpack8(kr, kf);
+                unpack8(vr, vf);
+            }
+#pragma unroll
+            for (int g = 0; g < kGC; ++g) {
+                float s = 0.f;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) s += q[g][i] * kf[i];
+#pragma unroll
+                for (int o = W / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+                s *= p.scale;
+                if (valid && g < gc) {
+                    float mn = fmaxf(mi[g], s);
+                    float es = expf(mi[g] - mn), pr = expf(s - mn);
+                    mi[g] = mn;
+                    li[g] = li[g] * es + pr;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) acc[g][i] = acc[g][i] * es + pr * vf[i];
+                }
+            }
+        }
+        // ---- merge the CTA's parts
+        __syncthreads();
+#pragma unroll
+        for (int g = 0; g < kGC; ++g) {
+            if (sl == 0) { s_ml[part][g][0] = mi[g]; s_ml[part][g][1] = li[g]; }
+            if (act) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) s_acc[part][g][sl * 8 + i] = acc[g][i];
+            }
+        }
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < gc * HD; idx += kThreads) {
+            const int g = idx / HD, dd = idx % HD;
+            float M = -INFINITY;
+#pragma unroll
+            for (int pp = 0; pp < PARTS; ++pp) M = fmaxf(M, s_ml[pp][g][0]);
+            float L = 0.f, A = 0.f;
+#pragma unroll
+            for (int pp = 0; pp < PARTS; ++pp) {
+                float m = s_ml[pp][g][0];
+                float w = (m == -INFINITY) ? 0.f : expf(m - M);
+                L += s_ml[pp][g][1] * w;
+                A += s_acc[pp][g][dd] * w;
+            }
+            const int head = kvh * G + g0 + g;
+            if (a.splits == 1) {
+                a.out[(size_t(b) * a.nq + head) * HD + dd] = A * (1.0f / L);
+            } else {
+                float* w = a.ws + ((size_t(b) * a.nq + head) * a.splits + split) * (HD + 2);
+                w[2 + dd] = A;
+                if (dd == 0) { w[0] = M; w[1] = L; }
+            }
+        }
+    }
+    if (a.splits == 1) return;
+
+    // ---- last CTA of this (batch, kv head) merges the splits
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int old = atomicAdd(a.counters + b * a.nkv + kvh, 1);
+        s_last = (old == a.splits - 1);
+        if (s_last) a.counters[b * a.nkv + kvh] = 0;  // ready for the next launch
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    for (int idx = threadIdx.x; idx < G * HD; idx += kThreads) {
+        const int g = idx / HD, dd = idx % HD, head = kvh * G + g;
+        const float* w0 = a.ws + (size_t(b) * a.nq + head) * a.splits * (HD + 2);
+        float M = -INFINITY;
+        for (int s = 0; s < a.splits; ++s) M = fmaxf(M, __ldcg(w0 + size_t(s) * (HD + 2)));
+        float L = 0.f, A = 0.f;
+        for (int s = 0; s < a.splits; ++s) {
+            const float* w = w0 + size_t(s) * (HD + 2);
+            float m = __ldcg(w);
+            float wt = (m == -INFINITY) ? 0.f : expf(m - M);
+            L += __ldcg(w + 1) * wt;
+            A += __ldcg(w + 2 + dd) * wt;
+        }
+        a.out[(size_t(b) * a.nq + head) * HD + dd] = A * (1.0f / L);
+    }
+}
+
+}  // namespace
+
+size_t attn_decode_ws_floats(int batch, int nq, int hd, int splits) { return size_t(batch) * nq * splits * (hd + 2); }
+
+int32_t attn_decode(const AttnDecodeArgs& a, cudaStream_t st) {
+    if (a.nq % a.nkv) { set_error("attention: num_heads %d not a multiple of num_kv_heads %d", a.nq, a.nkv); return FORGE_ERR_SHAPE; }
+    if (a.splits < 1 || (a.splits > 1 && (!a.ws || !a.counters))) { set_error("attention: split workspace missing"); return FORGE_ERR_INVALID_ARG; }
+    DecParams p{a, 1.0f / sqrtf(float(a.hd))};
+    dim3 grid(a.splits, a.nkv, a.batch);
+    switch (a.hd) {
+        case 64: attn_decode_kernel<64><<<grid, kThreads, 0, st>>>(p); break;
+        case 96: attn_decode_kernel<96><<<grid, kThreads, 0, st>>>(p); break;
+        case 128: attn_decode_kernel<128><<<grid, kThreads, 0, st>>>(p); break;
+        default: set_error("attention: head_dim %d unsupported (64, 96, 128)", a.hd); return FORGE_ERR_SHAPE;
+    }
+    FORGE_LAUNCH_CHECK();
+    return FORGE_OK;
+}
+
+}  // namespace forge

@@ -1,0 +1,130 @@
+// Shared declarations of the sm_100a backend: status plumbing, packed-weight descriptors,
+// the kernel launch prototypes each .cu file exports to the host-side model code.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "../../include/forge_b200.h"
+
+namespace forge {
+
+// ------------------------------------------------------------------ errors
+void set_error(const char* fmt, ...);
+extern thread_local long long g_launches;  // kernels of this library launched on this thread
+
+#define FORGE_CUDA(call)                                                                   \
+    do {                                                                                   \
+        cudaError_t e_ = (call);                                                           \
+        if (e_ != cudaSuccess) {                                                           \
+            forge::set_error("%s:%d %s: %s", __FILE__, __LINE__, #call, cudaGetErrorString(e_)); \
+            return FORGE_ERR_CUDA;                                                         \
+        }                                                                                  \
+    } while (0)
+
+#define FORGE_LAUNCH_CHECK()                                                               \
+    do {                                                                                   \
+        ++forge::g_launches;                                                               \
+        cudaError_t e_ = cudaGetLastError();                                               \
+        if (e_ != cudaSuccess) {                                                           \
+            forge::set_error("%s:%d kernel launch: %s", __FILE__, __LINE__, cudaGetErrorString(e_)); \
+            return FORGE_ERR_CUDA;                                                         \
+        }                                                                                  \
+    } while (0)
+
+#define FORGE_TRY(expr)                     \
+    do {                                    \
+        int32_t s_ = (expr);                \
+        if (s_ != FORGE_OK) return s_;      \
+    } while (0)
+
+// ------------------------------------------------------------------ packed weights
+// Load-time layout of one projection: the 32 (Q8_0) or 16 (Q4_0) quant bytes of every block,
+// verbatim and contiguous per row, and the f16 block scales in a second array.  Same bytes
+// per weight as the GGUF stream (34/32 and 18/32), but every row starts 16-byte aligned.
+struct QWeight {
+    uint8_t* qs = nullptr;  // [N][K] int8  or  [N][K/2] nibble pairs
+    __half* d = nullptr;    // [N][K/32]
+    int K = 0, N = 0, quant = 0;
+    size_t qs_row_bytes() const { return quant == FORGE_Q8_0 ? size_t(K) : size_t(K) / 2; }
+};
+
+// raw GGUF rows [row0, row0+rows) x blocks [blk0, blk0+blks) of a [N][K/32] block matrix ->
+// packed rows dst_row0.. with optional row interleave: dst row = dst_row0 + r*row_step.
+int32_t pack_rows(const uint8_t* raw_dev, int quant, int K_full, int row0, int rows, int blk0, int blks,
+                  QWeight& dst, int dst_row0, int row_step, cudaStream_t st);
+
+// ------------------------------------------------------------------ GEMV (decode)
+enum GemvEpilogue { EPI_STORE = 0, EPI_RESID = 1, EPI_QKV = 2, EPI_SILU = 3 };
+
+struct GemvArgs {
+    const float* x = nullptr;       // [batch][K] input rows
+    const float* norm_w = nullptr;  // if set: RMSNorm(x) * norm_w is applied before the product
+    float eps = 0.f;
+    float* out = nullptr;           // EPI_STORE / EPI_RESID / EPI_SILU target, [batch][N or N/2]
+    const float* resid = nullptr;   // EPI_RESID: out = resid + W x (may alias out)
+    int batch = 1;
+    // EPI_QKV
+    const float* bias = nullptr;    // [N] or null
+    const float* rope = nullptr;    // [pos][hd/2]{cos,sin}
+    float* q_out = nullptr;         // [batch][qk]
+    __half* k_pool = nullptr;       // this layer's page pool
+    __half* v_pool = nullptr;
+    const int32_t* page_table = nullptr;  // [batch][pages_per_seq]
+    const int32_t* seq_len = nullptr;     // [batch] device positions (the new row's position)
+    int pages_per_seq = 0;
+    int qk = 0, kv = 0, head_dim = 0;
+};
+int32_t gemv(const QWeight& w, GemvEpilogue epi, const GemvArgs& a, cudaStream_t st);
+
+// ------------------------------------------------------------------ elementwise
+int32_t rms_norm_f32(float* out, const float* in, const float* w, int rows, int n, float eps, cudaStream_t st);
+// fp16 outputs come as a hi/lo pair when `lo` is given: hi = fp16(x), lo = fp16(x - hi)
+int32_t rms_norm_f16(__half* out, __half* lo, const float* in, const float* w, int rows, int n, float eps, cudaStream_t st);
+int32_t rope_rows(float* data, int rows, int base_pos, int head_dim, int heads, const float* table, cudaStream_t st);
+int32_t silu_mul_f32(float* out, const float* g, const float* u, size_t n, cudaStream_t st);
+int32_t silu_mul_f16(__half* out, __half* lo, const float* gu, int rows, int ffn, cudaStream_t st);  // gu = interleaved [rows][2*ffn]
+int32_t residual_add_f32(float* a, const float* b, size_t n, cudaStream_t st);
+// hist/step (optional): also records tokens[r] at hist[*step * rows + r] (greedy loop bookkeeping)
+int32_t embedding_rows(float* out, const float* table, const uint32_t* tokens, int rows, int h, uint32_t* hist, const int32_t* step, cudaStream_t st);
+int32_t kv_append_contig(__half* kc, __half* vc, const float* k, const float* v, int rows, int base_pos, int kvd, cudaStream_t st);
+// prefill QKV epilogue: bias, RoPE, q -> fp16 [m][qk], k/v -> paged fp16 cache
+int32_t qkv_post(const float* qkv, int m, int base_pos, const float* bias, const float* rope, __half* q16,
+                 __half* k_pool, __half* v_pool, const int32_t* page_row, int qk, int kv, int hd, cudaStream_t st);
+int32_t argmax_last(uint32_t* result, const float* logits, int n, int batch, cudaStream_t st);
+int32_t f32_to_f16(__half* out, __half* lo, const float* in, size_t n, cudaStream_t st);
+int32_t step_advance(int32_t* seq_len, int batch, int32_t* step, cudaStream_t st);
+int32_t gather_rows_f16(float* out, const __half* pool, const int32_t* page_row, int len, int kvd, cudaStream_t st);
+
+// ------------------------------------------------------------------ attention
+struct AttnDecodeArgs {
+    float* out; const float* q;              // [batch][nq*hd]
+    const __half* k_pool; const __half* v_pool;
+    const int32_t* page_table; int pages_per_seq;  // null table = contiguous cache
+    const int32_t* seq_len;                  // device [batch]: attends to positions <= seq_len[b]
+    int seq_len_host;                        // used when seq_len == nullptr (op-level call): count of positions
+    int batch, nq, nkv, hd, max_ctx;
+    float* ws; int* counters;                // split workspace
+    int splits;
+};
+size_t attn_decode_ws_floats(int batch, int nq, int hd, int splits);
+int32_t attn_decode(const AttnDecodeArgs& a, cudaStream_t st);
+
+struct AttnPrefillArgs {
+    __half* out16; __half* out16_lo; float* out32;  // out16 (+ optional lo part) or out32: [m][nq*hd]
+    const __half* q16;                       // [m][nq*hd]
+    const __half* k_pool; const __half* v_pool;
+    const int32_t* page_row;                 // device [pages] physical page of logical page i (null = contiguous)
+    int m, base_pos, nq, nkv, hd;
+};
+int32_t attn_prefill(const AttnPrefillArgs& a, cudaStream_t st);
+int32_t attn_prefill_q32(const AttnPrefillArgs& a, const float* q32, cudaStream_t st);  // f32 queries, converted on load
+
+// ------------------------------------------------------------------ GEMM (prefill)
+// out f32 [m][N] = A f16 [m][K] x W^T; optional resid: out = resid + A W^T (may alias out)
+// Alo != null selects the split-precision form (A = A + Alo, weights split the same way)
+int32_t gemm_f16a(float* out, const __half* A, const __half* Alo, const QWeight& w, int m, const float* resid, cudaStream_t st);
+
+}  // namespace forge

@@ -1,0 +1,255 @@
+// Row-wise and elementwise operators of the forward path and the prefill glue kernels.
+// Reference statements (crates/forgellm-codegen-cpu/src/emit.rs): rms_norm :327-334,
+// rope :509-528, silu_mul :381-386, residual_add :455-459, embedding :586-589, bias adds
+// :4108-4118, cache write :4136-4153 (fp16 here instead of int8), argmax project.rs:501-503.
+#include "common.cuh"
+
+namespace forge {
+
+namespace {
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float s = 0.f;
+    for (int w = 0; w < nw; ++w) s += red[w];
+    return s;
+}
+
+// one CTA per row: out = x * (1/sqrt(mean(x^2)+eps)) * w
+__device__ __forceinline__ void store_split(__half* hi, __half* lo, size_t i, float v) {
+    __half h = __float2half_rn(v);
+    hi[i] = h;
+    if (lo) lo[i] = __float2half_rn(v - __half2float(h));
+}
+
+template <typename OutT>
+__global__ void rms_norm_kernel(OutT* __restrict__ out, __half* __restrict__ lo, const float* __restrict__ in, const float* __restrict__ w, int n, float eps) {
+    __shared__ float red[32];
+    const float* x = in + size_t(blockIdx.x) * n;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) { float v = x[i]; ss += v * v; }
+    ss = block_sum(ss, red);
+    float inv = 1.0f / sqrtf(ss / float(n) + eps);
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        float v = x[i] * inv * w[i];
+        if constexpr (sizeof(OutT) == 2) store_split(out, lo, size_t(blockIdx.x) * n + i, v);
+        else out[size_t(blockIdx.x) * n + i] = v;
+    }
+}
+
+// thread per (row, head, pair): adjacent-pair rotation, table = {cos, sin}[pos][hd/2]
+__global__ void rope_kernel(float* data, int rows, int base_pos, int hd, int heads, const float2* __restrict__ table) {
+    int half = hd / 2;
+    long total = long(rows) * heads * half;
+    for (long i = blockIdx.x * long(blockDim.x) + threadIdx.x; i < total; i += long(gridDim.x) * blockDim.x) {
+        int pr = int(i % half);
+        long rh = i / half;
+        int r = int(rh / heads);
+        float2 cs = table[size_t(base_pos + r) * half + pr];
+        float2* p = reinterpret_cast<float2*>(data) + rh * half + pr;
+        float2 v = *p;
+        *p = make_float2(v.x * cs.x - v.y * cs.y, v.x * cs.y + v.y * cs.x);
+    }
+}
+
+__global__ void silu_mul_kernel(float* out, const float* g, const float* u, size_t n) {
+    for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < n; i += size_t(gridDim.x) * blockDim.x) {
+        float x = g[i];
+        out[i] = (x / (1.0f + expf(-x))) * u[i];
+    }
+}
+
+// gu: [rows][2*ffn] with gate_j at column 2j and up_j at 2j+1  ->  out f16 [rows][ffn]
+__global__ void silu_mul_f16_kernel(__half* out, __half* lo, const float2* gu, size_t n) {
+    for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < n; i += size_t(gridDim.x) * blockDim.x) {
+        float2 v = gu[i];
+        store_split(out, lo, i, (v.x / (1.0f + expf(-v.x))) * v.y);
+    }
+}
+
+__global__ void residual_add_kernel(float* a, const float* b, size_t n) {
+    for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < n; i += size_t(gridDim.x) * blockDim.x) a[i] += b[i];
+}
+
+__global__ void embedding_kernel(float* out, const float* table, const uint32_t* tokens, int h, uint32_t* hist, const int32_t* step) {
+    if (hist && threadIdx.x == 0) hist[size_t(*step) * gridDim.x + blockIdx.x] = tokens[blockIdx.x];
+    const float4* src = reinterpret_cast<const float4*>(table + size_t(tokens[blockIdx.x]) * h);
+    float4* dst = reinterpret_cast<float4*>(out + size_t(blockIdx.x) * h);
+    for (int i = threadIdx.x; i < h / 4; i += blockDim.x) dst[i] = src[i];
+}
+
+__global__ void kv_append_contig_kernel(__half* kc, __half* vc, const float* k, const float* v, size_t n, size_t off) {
+    for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < n; i += size_t(gridDim.x) * blockDim.x) {
+        kc[off + i] = __float2half_rn(k[i]);
+        vc[off + i] = __float2half_rn(v[i]);
+    }
+}
+
+// prefill glue: fused [q;k;v] f32 rows -> (+bias) -> RoPE on q,k -> q fp16, k/v into the paged cache
+__global__ void qkv_post_kernel(const float* __restrict__ qkv, int m, int base_pos, const float* __restrict__ bias,
+                                const float2* __restrict__ rope, __half* __restrict__ q16, __half* __restrict__ k_pool,
+                                __half* __restrict__ v_pool, const int32_t* __restrict__ page_row, int qk, int kv, int hd) {
+    const int npairs = (qk + 2 * kv) / 2;
+    const int r = blockIdx.x;
+    const int pos = base_pos + r;
+    const float2* src = reinterpret_cast<const float2*>(qkv + size_t(r) * (qk + 2 * kv));
+    const int lp = pos / FORGE_KV_PAGE;
+    const size_t prow = (size_t(page_row ? page_row[lp] : lp) * FORGE_KV_PAGE + pos % FORGE_KV_PAGE) * kv;
+    for (int i = threadIdx.x; i < npairs; i += blockDim.x) {
+        float2 v = src[i];
+        int col = 2 * i;
+        if (bias) { v.x += bias[col]; v.y += bias[col + 1]; }
+        int region = 0;
+        if (col >= qk) { col -= qk; region = 1; }
+        if (region == 1 && col >= kv) { col -= kv; region = 2; }
+        if (region < 2) {
+            float2 cs = rope[size_t(pos) * (hd / 2) + (col % hd) / 2];
+            v = make_float2(v.x * cs.x - v.y * cs.y, v.x * cs.y + v.y * cs.x);
+        }
+        __half2 hv = __floats2half2_rn(v.x, v.y);
+        if (region == 0) *reinterpret_cast<__half2*>(q16 + size_t(r) * qk + col) = hv;
+        else *reinterpret_cast<__half2*>((region == 1 ? k_pool : v_pool) + prow + col) = hv;
+    }
+}
+
+// Greedy pick with the generated main's tie rule: the LAST index among equal maxima.
+__global__ void argmax_kernel(uint32_t* result, const float* logits, int n) {
+    __shared__ float bv[32];
+    __shared__ int bi[32];
+    const float* x = logits + size_t(blockIdx.x) * n;
+    float best = -INFINITY;
+    int idx = -1;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        float v = x[i];
+        if (idx < 0 || v > best || (v == best && i > idx)) { best = v; idx = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+        if (oi >= 0 && (idx < 0 || ov > best || (ov == best && oi > idx))) { best = ov; idx = oi; }
+    }
+    int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    if (lane == 0) { bv[warp] = best; bi[warp] = idx; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < nw; ++w)
+            if (bi[w] >= 0 && (idx < 0 || bv[w] > best || (bv[w] == best && bi[w] > idx))) { best = bv[w]; idx = bi[w]; }
+        result[blockIdx.x] = uint32_t(idx < 0 ? 0 : idx);
+    }
+}
+
+__global__ void f32_to_f16_kernel(__half* out, __half* lo, const float* in, size_t n) {
+    for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < n; i += size_t(gridDim.x) * blockDim.x) store_split(out, lo, i, in[i]);
+}
+
+__global__ void step_advance_kernel(int32_t* seq_len, int batch, int32_t* step) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < batch) seq_len[i] += 1;
+    if (i == 0 && step) *step += 1;
+}
+
+__global__ void gather_rows_kernel(float* out, const __half* pool, const int32_t* page_row, int len, int kvd) {
+    size_t n = size_t(len) * kvd;
+    for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < n; i += size_t(gridDim.x) * blockDim.x) {
+        int t = int(i / kvd), c = int(i % kvd);
+        int lp = t / FORGE_KV_PAGE;
+        out[i] = __half2float(pool[(size_t(page_row ? page_row[lp] : lp) * FORGE_KV_PAGE + t % FORGE_KV_PAGE) * kvd + c]);
+    }
+}
+
+inline int grid_for(size_t n, int threads = 256) {
+    size_t g = (n + threads - 1) / threads;
+    return int(g < 148 * 32 ? (g ? g : 1) : 148 * 32);
+}
+
+}  // namespace
+
+int32_t rms_norm_f32(float* out, const float* in, const float* w, int rows, int n, float eps, cudaStream_t st) {
+    if (rows <= 0) return FORGE_OK;
+    rms_norm_kernel<float><<<rows, 256, 0, st>>>(out, nullptr, in, w, n, eps);
+    FORGE_LAUNCH_CHECK();
+    return FORGE_OK;
+}
+int32_t rms_norm_f16(__half* out, __half* lo, const float* in, const float* w, int rows, int n, float eps, cudaStream_t st) {
+    if (rows <= 0) return FORGE_OK;
+    rms_norm_kernel<__half><<<rows, 256, 0, st>>>(out, lo, in, w, n, eps);
+    FORGE_LAUNCH_CHECK();
+    return FORGE_OK;
+}
+int32_t rope_rows(float* data, int rows, int base_pos, int head_dim, int heads, const float* table, cudaStream_t st) {
+    size_t n = size_t(rows) * heads * (head_dim / 2);
+    if (n == 0) return FORGE_OK;
+    rope_kernel<<<grid_for(n), 256, 0, st>>>(data, rows, base_pos, head_dim, heads, reinterpret_cast<const float2*>(table));
+    FORGE_LAUNCH_CHECK();
+    return FORGE_OK;
+}
+int32_t silu_mul_f32(float* out, const float* g, const float* u, size_t n, cudaStream_t st) {
+    if (n == 0) return FORGE_OK;
+    silu_mul_kernel<<<grid_for(n), 256, 0, st>>>(out, g, u, n);
+    FORGE_LAUNCH_CHECK();
+    return FORGE_OK;
+}
+int32_t silu_mul_f16(__half* out, __half* lo, const float* gu, int rows, int ffn, cudaStream_t st) {
+    size_t n = size_t(rows) * ffn;
+    if (n == 0) return FORGE_OK;
+    silu_mul_f16_kernel<<<grid_for(n), 256, 0, st>>>(out, lo, reinterpret_cast<const float2*>(gu), n);
+    FORGE_LAUNCH_CHECK();
+    return FORGE_OK;
+}
+int32_t residual_add_f32(float* a, const float* b, size_t n, cudaStream_t st) {
+    if (n == 0) return FORGE_OK;
+    residual_add_kernel<<<grid_for(n), 256, 0, st>>>(a, b, n);
+    FORGE_LAUNCH_CHECK();
+    return FORGE_OK;
+}
+int32_t embedding_rows(float* out, const float* table, const uint32_t* tokens, int rows, int h, uint32_t* hist, const int32_t* step, cudaStream_t st) {
+    if (rows <= 0) return FORGE_OK;
+    embedding_kernel<<<rows, 128, 0, st>>>(out, table, tokens, h, hist, step);
+    FORGE_LAUNCH_CHECK();
+    return FORGE_OK;
+}
+int32_t kv_append_contig(__half* kc, __half* vc, const float* k, const float* v, int rows, int base_pos, int kvd, cudaStream_t st) {
+    size_t n = size_t(rows) * kvd;
+    if (n == 0) return FORGE_OK;
+    kv_append_contig_kernel<<<grid_for(n), 256, 0, st>>>(kc, vc, k, v, n, size_t(base_pos) * kvd);
+    FORGE_LAUNCH_CHECK();
+    return FORGE_OK;
+}
+int32_t qkv_post(const float* qkv, int m, int base_pos, const float* bias, const float* rope, __half* q16,
+                 __half* k_pool, __half* v_pool, const int32_t* page_row, int qk, int kv, int hd, cudaStream_t st) {
+    if (m <= 0) return FORGE_OK;
+    qkv_post_kernel<<<m, 256, 0, st>>>(qkv, m, base_pos, bias, reinterpret_cast<const float2*>(rope), q16, k_pool, v_pool, page_row, qk, kv, hd);
+    FORGE_LAUNCH_CHECK();
+    return FORGE_OK;
+}
+int32_t argmax_last(uint32_t* result, const float* logits, int n, int batch, cudaStream_t st) {
+    argmax_kernel<<<batch, 1024, 0, st>>>(result, logits, n);
+    FORGE_LAUNCH_CHECK();
+    return FORGE_OK;
+}
+int32_t f32_to_f16(__half* out, __half* lo, const float* in, size_t n, cudaStream_t st) {
+    if (n == 0) return FORGE_OK;
+    f32_to_f16_kernel<<<grid_for(n), 256, 0, st>>>(out, lo, in, n);
+    FORGE_LAUNCH_CHECK();
+    return FORGE_OK;
+}
+int32_t step_advance(int32_t* seq_len, int batch, int32_t* step, cudaStream_t st) {
+    step_advance_kernel<<<(batch + 127) / 128, 128, 0, st>>>(seq_len, batch, step);
+    FORGE_LAUNCH_CHECK();
+    return FORGE_OK;
+}
+int32_t gather_rows_f16(float* out, const __half* pool, const int32_t* page_row, int len, int kvd, cudaStream_t st) {
+    size_t n = size_t(len) * kvd;
+    if (n == 0) return FORGE_OK;
+    gather_rows_kernel<<<grid_for(n), 256, 0, st>>>(out, pool, page_row, len, kvd);
+    FORGE_LAUNCH_CHECK();
+    return FORGE_OK;
+}
+
+}  // namespace forge

@@ -1,0 +1,677 @@
+// Host side of the backend: Weights / KVCache / forward / forward_prefill of the generated
+// module (crates/forgellm-codegen-cpu/src/emit.rs:3875-4015, :4029-4500, :4553-4587, :5118-5486)
+// and the greedy loop of the generated main (crates/forgellm-codegen-cpu/src/project.rs:714-751),
+// re-stated as kernel launches on one CUDA stream per model.  The decode step is captured once
+// into a CUDA graph (positions and the sampled token live in device memory, so the same graph
+// replays for every step).
+#include <algorithm>
+#include <cmath>
+#include <cstdarg>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "common.cuh"
+
+namespace forge {
+
+thread_local std::string g_error;
+thread_local long long g_launches = 0;
+
+void set_error(const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    g_error = buf;
+}
+
+}  // namespace forge
+
+using namespace forge;
+
+// ------------------------------------------------------------------------------ structures
+struct ForgeLayer {
+    float* attn_norm = nullptr;
+    QWeight qkv;           // rows: [q ; k ; v] of this rank
+    float* qkv_bias = nullptr;
+    QWeight o;
+    float* ffn_norm = nullptr;
+    QWeight gateup;        // rows interleaved: 2j = gate_j, 2j+1 = up_j
+    QWeight down;
+};
+
+struct ForgeModel {
+    ForgeModelConfig cfg;
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    // local (per tensor-parallel rank) sizes
+    int h = 0, qk = 0, kv = 0, ff = 0, V = 0, hd = 0, nq = 0, nkv = 0;
+    float* embed = nullptr;
+    std::vector<ForgeLayer> layers;
+    float* final_norm = nullptr;
+    QWeight lm_head;
+    float* rope = nullptr;  // [max_seq][hd/2]{cos,sin}
+    int max_seq = 0;
+    std::vector<void*> allocs;
+    // prefill scratch (grown on demand)
+    int scratch_rows = 0;
+    float* p_hidden = nullptr; __half* p_normed = nullptr; float* p_qkv = nullptr; __half* p_q16 = nullptr;
+    __half* p_attn16 = nullptr; float* p_gu = nullptr; __half* p_act16 = nullptr; uint32_t* p_tokens = nullptr;
+    __half* p_normed_lo = nullptr; __half* p_attn16_lo = nullptr; __half* p_act16_lo = nullptr;
+    int gemm_passes = 3;  // 3: split-precision prefill GEMMs (default); 1: single fp16 pass
+    // decode scratch (per batch row)
+    int dec_batch = 0;
+    float* d_hidden = nullptr; float* d_q = nullptr; float* d_attn = nullptr; float* d_act = nullptr; float* d_logits = nullptr;
+    uint32_t* d_tok = nullptr; uint32_t* d_hist = nullptr; int hist_cap = 0; int32_t* d_step = nullptr;
+    // parity trace
+    bool trace_on = false; float* trace = nullptr; size_t trace_cap = 0; int trace_rows = 0;
+    // timing of the last generate call
+    cudaEvent_t ev[3] = {nullptr, nullptr, nullptr};
+    float prefill_ms = 0.f, decode_ms = 0.f; long long last_launches = 0;
+};
+
+struct ForgeKV {
+    ForgeModel* model = nullptr;
+    int max_seq = 0, batch = 0, pages_per_seq = 0, num_pages = 0;
+    __half* k_pool = nullptr; __half* v_pool = nullptr;
+    size_t layer_stride = 0;  // halfs per layer pool
+    int32_t* d_page_table = nullptr; int32_t* d_seq_len = nullptr;
+    std::vector<int32_t> h_page_table; std::vector<int> free_pages; std::vector<int> pages_used; std::vector<int> len;
+    float* attn_ws = nullptr; int* attn_counters = nullptr; int splits = 1;
+    cudaGraphExec_t graph = nullptr; int graph_batch = 0; bool graph_greedy = false;
+};
+
+namespace {
+
+template <typename T>
+int32_t dev_alloc(ForgeModel* m, T** p, size_t count) {
+    void* q = nullptr;
+    FORGE_CUDA(cudaMalloc(&q, std::max<size_t>(count, 1) * sizeof(T)));
+    m->allocs.push_back(q);
+    *p = static_cast<T*>(q);
+    return FORGE_OK;
+}
+
+int32_t alloc_qweight(ForgeModel* m, QWeight& w, int quant, int K, int N) {
+    w.K = K; w.N = N; w.quant = quant;
+    FORGE_TRY(dev_alloc(m, &w.qs, size_t(N) * w.qs_row_bytes()));
+    FORGE_TRY(dev_alloc(m, &w.d, size_t(N) * (K / 32)));
+    return FORGE_OK;
+}
+
+size_t raw_bytes(int quant, size_t n, size_t k) { return n * (k / 32) * (quant == FORGE_Q8_0 ? 34 : 18); }
+
+int32_t check_cfg(const ForgeModelConfig* c) {
+    if (!c) { set_error("null config"); return FORGE_ERR_INVALID_ARG; }
+    if (c->quant != FORGE_Q8_0 && c->quant != FORGE_Q4_0) { set_error("quant must be FORGE_Q8_0 or FORGE_Q4_0"); return FORGE_ERR_INVALID_ARG; }
+    if (c->hidden_size <= 0 || c->intermediate_size <= 0 || c->num_layers <= 0 || c->num_heads <= 0 || c->num_kv_heads <= 0 ||
+        c->vocab_size <= 0 || c->max_seq_len <= 0) { set_error("non-positive dimension in config"); return FORGE_ERR_INVALID_ARG; }
+    if (c->head_dim != 64 && c->head_dim != 96 && c->head_dim != 128) { set_error("head_dim %d unsupported (64, 96, 128)", c->head_dim); return FORGE_ERR_SHAPE; }
+    if (c->hidden_size % 32 || c->intermediate_size % 32 || (c->num_heads * c->head_dim) % 32) { set_error("hidden, intermediate and heads*head_dim must be multiples of 32"); return FORGE_ERR_SHAPE; }
+    if (c->num_heads % c->num_kv_heads) { set_error("num_heads must be a multiple of num_kv_heads"); return FORGE_ERR_SHAPE; }
+    int tp = c->tp_world < 1 ? 1 : c->tp_world;
+    if (c->tp_rank < 0 || c->tp_rank >= tp) { set_error("tp_rank out of range"); return FORGE_ERR_INVALID_ARG; }
+    if (c->num_kv_heads % tp || (c->intermediate_size / tp) % 32 || c->intermediate_size % tp) { set_error("tensor-parallel world %d does not divide kv heads / intermediate blocks", tp); return FORGE_ERR_SHAPE; }
+    return FORGE_OK;
+}
+
+int32_t ensure_prefill_scratch(ForgeModel* m, int rows) {
+    if (rows <= m->scratch_rows) return FORGE_OK;
+    // scratch is only ever grown between calls; old buffers stay alive until model destroy
+    size_t r = size_t(rows);
+    FORGE_TRY(dev_alloc(m, &m->p_hidden, r * m->h));
+    FORGE_TRY(dev_alloc(m, &m->p_normed, r * m->h));
+    FORGE_TRY(dev_alloc(m, &m->p_qkv, r * (m->qk + 2 * m->kv)));
+    FORGE_TRY(dev_alloc(m, &m->p_q16, r * m->qk));
+    FORGE_TRY(dev_alloc(m, &m->p_attn16, r * m->qk));
+    FORGE_TRY(dev_alloc(m, &m->p_gu, r * 2 * m->ff));
+    FORGE_TRY(dev_alloc(m, &m->p_act16, r * m->ff));
+    FORGE_TRY(dev_alloc(m, &m->p_tokens, r));
+    FORGE_TRY(dev_alloc(m, &m->p_normed_lo, r * m->h));
+    FORGE_TRY(dev_alloc(m, &m->p_attn16_lo, r * m->qk));
+    FORGE_TRY(dev_alloc(m, &m->p_act16_lo, r * m->ff));
+    m->scratch_rows = rows;
+    return FORGE_OK;
+}
+
+int32_t ensure_decode_scratch(ForgeModel* m, int batch) {
+    if (batch <= m->dec_batch) return FORGE_OK;
+    size_t b = size_t(batch);
+    FORGE_TRY(dev_alloc(m, &m->d_hidden, b * m->h));
+    FORGE_TRY(dev_alloc(m, &m->d_q, b * m->qk));
+    FORGE_TRY(dev_alloc(m, &m->d_attn, b * m->qk));
+    FORGE_TRY(dev_alloc(m, &m->d_act, b * m->ff));
+    FORGE_TRY(dev_alloc(m, &m->d_logits, b * m->V));
+    FORGE_TRY(dev_alloc(m, &m->d_tok, b));
+    if (!m->d_step) { FORGE_TRY(dev_alloc(m, &m->d_step, 1)); }
+    m->dec_batch = batch;
+    return FORGE_OK;
+}
+
+int32_t ensure_trace(ForgeModel* m, int rows) {
+    size_t need = size_t(m->cfg.num_layers) * rows * m->h;
+    if (need > m->trace_cap) {
+        FORGE_TRY(dev_alloc(m, &m->trace, need));
+        m->trace_cap = need;
+    }
+    m->trace_rows = rows;
+    return FORGE_OK;
+}
+
+// hand out pages so that sequence `seq` can hold `new_len` positions; uploads the table row if it changed
+int32_t ensure_pages(ForgeKV* kv, int seq, int new_len) {
+    if (new_len > kv->max_seq) { set_error("KV cache full: position %d >= max_seq %d", new_len - 1, kv->max_seq); return FORGE_ERR_KV_FULL; }
+    int need = (new_len + FORGE_KV_PAGE - 1) / FORGE_KV_PAGE;
+    bool dirty = false;
+    while (kv->pages_used[seq] < need) {
+        if (kv->free_pages.empty()) { set_error("KV page pool exhausted"); return FORGE_ERR_KV_FULL; }
+        int pg = kv->free_pages.back();
+        kv->free_pages.pop_back();
+        kv->h_page_table[size_t(seq) * kv->pages_per_seq + kv->pages_used[seq]++] = pg;
+        dirty = true;
+    }
+    if (dirty) {
+        FORGE_CUDA(cudaMemcpyAsync(kv->d_page_table + size_t(seq) * kv->pages_per_seq, &kv->h_page_table[size_t(seq) * kv->pages_per_seq],
+                                   sizeof(int32_t) * kv->pages_per_seq, cudaMemcpyHostToDevice, kv->model->stream));
+        FORGE_CUDA(cudaStreamSynchronize(kv->model->stream));  // the host vector may change before an async copy runs
+    }
+    return FORGE_OK;
+}
+
+int32_t upload_len(ForgeKV* kv) {
+    std::vector<int32_t> l(kv->len.begin(), kv->len.end());
+    FORGE_CUDA(cudaMemcpyAsync(kv->d_seq_len, l.data(), sizeof(int32_t) * kv->batch, cudaMemcpyHostToDevice, kv->model->stream));
+    FORGE_CUDA(cudaStreamSynchronize(kv->model->stream));
+    return FORGE_OK;
+}
+
+// ------------------------------------------------------------------ prefill of one sequence
+// forward_prefill_batched, emit.rs:5118-5486.  Leaves the last row's logits in m->d_logits[0..V).
+int32_t prefill_seq(ForgeModel* m, ForgeKV* kv, int seq, const uint32_t* tokens_host, int n) {
+    const ForgeModelConfig& c = m->cfg;
+    cudaStream_t st = m->stream;
+    const int base = kv->len[seq];
+    FORGE_TRY(ensure_pages(kv, seq, base + n));
+    FORGE_TRY(ensure_prefill_scratch(m, n));
+    FORGE_TRY(ensure_decode_scratch(m, 1));
+    if (m->trace_on) FORGE_TRY(ensure_trace(m, n));
+    FORGE_CUDA(cudaMemcpyAsync(m->p_tokens, tokens_host, sizeof(uint32_t) * n, cudaMemcpyHostToDevice, st));
+    FORGE_TRY(embedding_rows(m->p_hidden, m->embed, m->p_tokens, n, m->h, nullptr, nullptr, st));
+    const int32_t* page_row = kv->d_page_table + size_t(seq) * kv->pages_per_seq;
+    const bool split = m->gemm_passes == 3;
+    __half* nlo = split ? m->p_normed_lo : nullptr;
+    __half* alo = split ? m->p_attn16_lo : nullptr;
+    __half* flo = split ? m->p_act16_lo : nullptr;
+    for (int l = 0; l < c.num_layers; ++l) {
+        ForgeLayer& L = m->layers[l];
+        __half* kp = kv->k_pool + size_t(l) * kv->layer_stride;
+        __half* vp = kv->v_pool + size_t(l) * kv->layer_stride;
+        FORGE_TRY(rms_norm_f16(m->p_normed, nlo, m->p_hidden, L.attn_norm, n, m->h, c.rms_norm_eps, st));
+        FORGE_TRY(gemm_f16a(m->p_qkv, m->p_normed, nlo, L.qkv, n, nullptr, st));
+        FORGE_TRY(qkv_post(m->p_qkv, n, base, L.qkv_bias, m->rope, m->p_q16, kp, vp, page_row, m->qk, m->kv, m->hd, st));
+        AttnPrefillArgs pa{m->p_attn16, alo, nullptr, m->p_q16, kp, vp, page_row, n, base, m->nq, m->nkv, m->hd};
+        FORGE_TRY(attn_prefill(pa, st));
+        FORGE_TRY(gemm_f16a(m->p_hidden, m->p_attn16, alo, L.o, n, m->p_hidden, st));
+        FORGE_TRY(rms_norm_f16(m->p_normed, nlo, m->p_hidden, L.ffn_norm, n, m->h, c.rms_norm_eps, st));
+        FORGE_TRY(gemm_f16a(m->p_gu, m->p_normed, nlo, L.gateup, n, nullptr, st));
+        FORGE_TRY(silu_mul_f16(m->p_act16, flo, m->p_gu, n, m->ff, st));
+        FORGE_TRY(gemm_f16a(m->p_hidden, m->p_act16, flo, L.down, n, m->p_hidden, st));
+        if (m->trace_on)
+            FORGE_CUDA(cudaMemcpyAsync(m->trace + size_t(l) * n * m->h, m->p_hidden, sizeof(float) * n * m->h, cudaMemcpyDeviceToDevice, st));
+    }
+    // final rms_norm + lm_head on the last row only (emit.rs:5439-5482): exact-f32 GEMV
+    GemvArgs ga;
+    ga.x = m->p_hidden + size_t(n - 1) * m->h; ga.norm_w = m->final_norm; ga.eps = c.rms_norm_eps; ga.out = m->d_logits; ga.batch = 1;
+    FORGE_TRY(gemv(m->lm_head, EPI_STORE, ga, st));
+    kv->len[seq] += n;
+    return FORGE_OK;
+}
+
+// ------------------------------------------------------------------ one decode step (launch sequence)
+// forward(), emit.rs:4029-4500, for `batch` sequences.  Tokens are read from m->d_tok, positions
+// from kv->d_seq_len; with `greedy` the next token is selected on the device into m->d_tok.
+int32_t decode_launches(ForgeModel* m, ForgeKV* kv, int batch, bool greedy, bool record) {
+    const ForgeModelConfig& c = m->cfg;
+    cudaStream_t st = m->stream;
+    FORGE_TRY(embedding_rows(m->d_hidden, m->embed, m->d_tok, batch, m->h, record ? m->d_hist : nullptr, m->d_step, st));
+    for (int l = 0; l < c.num_layers; ++l) {
+        ForgeLayer& L = m->layers[l];
+        __half* kp = kv->k_pool + size_t(l) * kv->layer_stride;
+        __half* vp = kv->v_pool + size_t(l) * kv->layer_stride;
+        GemvArgs a;
+        a.x = m->d_hidden; a.norm_w = L.attn_norm; a.eps = c.rms_norm_eps; a.batch = batch;
+        a.bias = L.qkv_bias; a.rope = m->rope; a.q_out = m->d_q; a.k_pool = kp; a.v_pool = vp;
+        a.page_table = kv->d_page_table; a.seq_len = kv->d_seq_len; a.pages_per_seq = kv->pages_per_seq;
+        a.qk = m->qk; a.kv = m->kv; a.head_dim = m->hd;
+        FORGE_TRY(gemv(L.qkv, EPI_QKV, a, st));
+        AttnDecodeArgs da{m->d_attn, m->d_q, kp, vp, kv->d_page_table, kv->pages_per_seq, kv->d_seq_len, 0,
+                          batch, m->nq, m->nkv, m->hd, kv->max_seq, kv->attn_ws, kv->attn_counters, kv->splits};
+        FORGE_TRY(attn_decode(da, st));
+        GemvArgs o;
+        o.x = m->d_attn; o.out = m->d_hidden; o.resid = m->d_hidden; o.batch = batch;
+        FORGE_TRY(gemv(L.o, EPI_RESID, o, st));
+        GemvArgs g;
+        g.x = m->d_hidden; g.norm_w = L.ffn_norm; g.eps = c.rms_norm_eps; g.out = m->d_act; g.batch = batch;
+        FORGE_TRY(gemv(L.gateup, EPI_SILU, g, st));
+        GemvArgs d;
+        d.x = m->d_act; d.out = m->d_hidden; d.resid = m->d_hidden; d.batch = batch;
+        FORGE_TRY(gemv(L.down, EPI_RESID, d, st));
+        if (m->trace_on)
+            FORGE_CUDA(cudaMemcpyAsync(m->trace + size_t(l) * batch * m->h, m->d_hidden, sizeof(float) * batch * m->h, cudaMemcpyDeviceToDevice, st));
+    }
+    GemvArgs lm;
+    lm.x = m->d_hidden; lm.norm_w = m->final_norm; lm.eps = c.rms_norm_eps; lm.out = m->d_logits; lm.batch = batch;
+    FORGE_TRY(gemv(m->lm_head, EPI_STORE, lm, st));
+    if (greedy) FORGE_TRY(argmax_last(m->d_tok, m->d_logits, m->V, batch, st));
+    FORGE_TRY(step_advance(kv->d_seq_len, batch, m->d_step, st));
+    return FORGE_OK;
+}
+
+// host bookkeeping before a decode step: pages for the new position of every sequence
+int32_t decode_prepare(ForgeKV* kv, int batch) {
+    for (int b = 0; b < batch; ++b) FORGE_TRY(ensure_pages(kv, b, kv->len[b] + 1));
+    return FORGE_OK;
+}
+
+int32_t decode_step_graph(ForgeModel* m, ForgeKV* kv, int batch, bool greedy) {
+    if (m->trace_on) return decode_launches(m, kv, batch, greedy, greedy);
+    if (!kv->graph || kv->graph_batch != batch || kv->graph_greedy != greedy) {
+        if (kv->graph) { cudaGraphExecDestroy(kv->graph); kv->graph = nullptr; }
+        cudaGraph_t g = nullptr;
+        FORGE_CUDA(cudaStreamBeginCapture(m->stream, cudaStreamCaptureModeThreadLocal));
+        long long before = g_launches;
+        int32_t rc = decode_launches(m, kv, batch, greedy, greedy);
+        cudaError_t ce = cudaStreamEndCapture(m->stream, &g);
+        if (rc != FORGE_OK) { if (g) cudaGraphDestroy(g); return rc; }
+        if (ce != cudaSuccess) { set_error("graph capture: %s", cudaGetErrorString(ce)); return FORGE_ERR_CUDA; }
+        g_launches = before;  // captured, not launched
+        cudaError_t ie = cudaGraphInstantiate(&kv->graph, g, 0);
+        cudaGraphDestroy(g);
+        if (ie != cudaSuccess) { set_error("graph instantiate: %s", cudaGetErrorString(ie)); return FORGE_ERR_CUDA; }
+        kv->graph_batch = batch; kv->graph_greedy = greedy;
+    }
+    FORGE_CUDA(cudaGraphLaunch(kv->graph, m->stream));
+    // kernels inside one replay: embedding + 5 per layer + lm_head + (argmax) + advance
+    g_launches += 1 + 5LL * m->cfg.num_layers + 1 + (greedy ? 1 : 0) + 1;
+    return FORGE_OK;
+}
+
+int32_t check_seq(const ForgeKV* kv, int seq) {
+    if (!kv || seq < 0 || seq >= kv->batch) { set_error("sequence index out of range"); return FORGE_ERR_INVALID_ARG; }
+    return FORGE_OK;
+}
+
+}  // namespace
+
+// ------------------------------------------------------------------------------ C API
+extern "C" {
+
+const char* forge_last_error(void) { return g_error.c_str(); }
+
+int32_t forge_device_count(void) {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess) { cudaGetLastError(); return 0; }
+    return n;
+}
+
+size_t forge_weights_bin_size(const ForgeModelConfig* c) {
+    if (!c) return 0;
+    size_t h = c->hidden_size, qk = size_t(c->num_heads) * c->head_dim, kv = size_t(c->num_kv_heads) * c->head_dim;
+    size_t ff = c->intermediate_size, V = c->vocab_size;
+    int q = c->quant;
+    size_t per = h * 4 + raw_bytes(q, qk, h) + 2 * raw_bytes(q, kv, h) + (c->qkv_bias ? (qk + 2 * kv) * 4 : 0) + raw_bytes(q, h, qk) +
+                 h * 4 + 2 * raw_bytes(q, ff, h) + raw_bytes(q, h, ff);
+    return V * h * 4 + per * c->num_layers + h * 4 + raw_bytes(q, V, h);
+}
+
+int32_t forge_model_create(const ForgeModelConfig* cfg, const void* weights_bin, size_t len, int32_t device, ForgeModel** out) {
+    if (!out) { set_error("null out pointer"); return FORGE_ERR_INVALID_ARG; }
+    *out = nullptr;
+    FORGE_TRY(check_cfg(cfg));
+    if (!weights_bin) { set_error("null weights"); return FORGE_ERR_INVALID_ARG; }
+    if (len != forge_weights_bin_size(cfg)) { set_error("weights.bin is %zu bytes, configuration needs %zu", len, forge_weights_bin_size(cfg)); return FORGE_ERR_SHAPE; }
+    int ndev = forge_device_count();
+    if (ndev == 0) { set_error("no CUDA device: this backend has no CPU fallback"); return FORGE_ERR_CUDA; }
+    if (device < 0 || device >= ndev) { set_error("device %d out of range (%d visible)", device, ndev); return FORGE_ERR_INVALID_ARG; }
+    FORGE_CUDA(cudaSetDevice(device));
+    ForgeModel* m = new ForgeModel();
+    m->cfg = *cfg;
+    if (m->cfg.tp_world < 1) { m->cfg.tp_world = 1; m->cfg.tp_rank = 0; }
+    m->device = device;
+    const int tp = m->cfg.tp_world, rk = m->cfg.tp_rank, quant = cfg->quant;
+    const int H = cfg->hidden_size, QK = cfg->num_heads * cfg->head_dim, KV = cfg->num_kv_heads * cfg->head_dim, FF = cfg->intermediate_size;
+    m->h = H; m->hd = cfg->head_dim; m->V = cfg->vocab_size;
+    m->nq = cfg->num_heads / tp; m->nkv = cfg->num_kv_heads / tp;
+    m->qk = QK / tp; m->kv = KV / tp; m->ff = FF / tp;
+    m->max_seq = std::min(cfg->max_seq_len, 4096);  // emit.rs:178
+    int32_t rc = FORGE_OK;
+    auto fail = [&](int32_t code) { forge_model_destroy(m); return code; };
+    if (cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking) != cudaSuccess) { set_error("cudaStreamCreate failed"); return fail(FORGE_ERR_CUDA); }
+    for (auto& e : m->ev) if (cudaEventCreate(&e) != cudaSuccess) { set_error("cudaEventCreate failed"); return fail(FORGE_ERR_CUDA); }
+    cudaStream_t st = m->stream;
+
+    // staging buffer for raw blocks of the largest tensor
+    size_t max_raw = std::max({raw_bytes(quant, size_t(cfg->vocab_size), H), raw_bytes(quant, FF, H), raw_bytes(quant, QK, H)});
+    uint8_t* stage = nullptr;
+    if (cudaMalloc(&stage, max_raw) != cudaSuccess) { set_error("cudaMalloc(%zu) failed", max_raw); return fail(FORGE_ERR_CUDA); }
+    const uint8_t* p = static_cast<const uint8_t*>(weights_bin);
+    auto upload_f32 = [&](float** dst, size_t n, const uint8_t* src) -> int32_t {
+        FORGE_TRY(dev_alloc(m, dst, n));
+        FORGE_CUDA(cudaMemcpyAsync(*dst, src, n * 4, cudaMemcpyHostToDevice, st));
+        return FORGE_OK;
+    };
+    // raw [N][K] blocks at src -> pack rows/blocks slice into dst
+    auto upload_pack = [&](const uint8_t* src, int N, int K, int row0, int rows, int blk0, int blks, QWeight& dst, int dst_row0, int step) -> int32_t {
+        FORGE_CUDA(cudaMemcpyAsync(stage, src, raw_bytes(quant, N, K), cudaMemcpyHostToDevice, st));
+        FORGE_TRY(pack_rows(stage, quant, K, row0, rows, blk0, blks, dst, dst_row0, step, st));
+        FORGE_CUDA(cudaStreamSynchronize(st));  // stage is reused by the next tensor
+        return FORGE_OK;
+    };
+#define MC(expr) do { rc = (expr); if (rc != FORGE_OK) { cudaFree(stage); return fail(rc); } } while (0)
+    MC(upload_f32(&m->embed, size_t(cfg->vocab_size) * H, p));
+    p += size_t(cfg->vocab_size) * H * 4;
+    m->layers.resize(cfg->num_layers);
+    for (int l = 0; l < cfg->num_layers; ++l) {
+        ForgeLayer& L = m->layers[l];
+        MC(upload_f32(&L.attn_norm, H, p)); p += size_t(H) * 4;
+        MC(alloc_qweight(m, L.qkv, quant, H, m->qk + 2 * m->kv));
+        MC(upload_pack(p, QK, H, rk * m->qk, m->qk, 0, H / 32, L.qkv, 0, 1)); p += raw_bytes(quant, QK, H);
+        MC(upload_pack(p, KV, H, rk * m->kv, m->kv, 0, H / 32, L.qkv, m->qk, 1)); p += raw_bytes(quant, KV, H);
+        MC(upload_pack(p, KV, H, rk * m->kv, m->kv, 0, H / 32, L.qkv, m->qk + m->kv, 1)); p += raw_bytes(quant, KV, H);
+        if (cfg->qkv_bias) {
+            MC(dev_alloc(m, &L.qkv_bias, size_t(m->qk + 2 * m->kv)));
+            const float* bq = reinterpret_cast<const float*>(p);
+            const float* bk = bq + QK; const float* bv = bk + KV;
+            if (cudaMemcpyAsync(L.qkv_bias, bq + rk * m->qk, size_t(m->qk) * 4, cudaMemcpyHostToDevice, st) != cudaSuccess ||
+                cudaMemcpyAsync(L.qkv_bias + m->qk, bk + rk * m->kv, size_t(m->kv) * 4, cudaMemcpyHostToDevice, st) != cudaSuccess ||
+                cudaMemcpyAsync(L.qkv_bias + m->qk + m->kv, bv + rk * m->kv, size_t(m->kv) * 4, cudaMemcpyHostToDevice, st) != cudaSuccess) {
+                set_error("bias upload failed"); cudaFree(stage); return fail(FORGE_ERR_CUDA);
+            }
+            p += size_t(QK + 2 * KV) * 4;
+        }
+        MC(alloc_qweight(m, L.o, quant, m->qk, H));
+        MC(upload_pack(p, H, QK, 0, H, rk * (m->qk / 32), m->qk / 32, L.o, 0, 1)); p += raw_bytes(quant, H, QK);
+        MC(upload_f32(&L.ffn_norm, H, p)); p += size_t(H) * 4;
+        MC(alloc_qweight(m, L.gateup, quant, H, 2 * m->ff));
+        MC(upload_pack(p, FF, H, rk * m->ff, m->ff, 0, H / 32, L.gateup, 0, 2)); p += raw_bytes(quant, FF, H);
+        MC(upload_pack(p, FF, H, rk * m->ff, m->ff, 0, H / 32, L.gateup, 1, 2)); p += raw_bytes(quant, FF, H);
+        MC(alloc_qweight(m, L.down, quant, m->ff, H));
+        MC(upload_pack(p, H, FF, 0, H, rk * (m->ff / 32), m->ff / 32, L.down, 0, 1)); p += raw_bytes(quant, H, FF);
+    }
+    MC(upload_f32(&m->final_norm, H, p)); p += size_t(H) * 4;
+    MC(alloc_qweight(m, m->lm_head, quant, H, cfg->vocab_size));
+    MC(upload_pack(p, cfg->vocab_size, H, 0, cfg->vocab_size, 0, H / 32, m->lm_head, 0, 1));
+    cudaFree(stage);
+    // RoPE table with the host libm, f32 (emit.rs:502-519)
+    {
+        std::vector<float> tab(size_t(m->max_seq) * m->hd);
+        forge_rope_table(tab.data(), m->max_seq, m->hd, cfg->rope_theta);
+        rc = dev_alloc(m, &m->rope, tab.size());
+        if (rc != FORGE_OK) return fail(rc);
+        if (cudaMemcpyAsync(m->rope, tab.data(), tab.size() * 4, cudaMemcpyHostToDevice, st) != cudaSuccess ||
+            cudaStreamSynchronize(st) != cudaSuccess) { set_error("rope table upload failed"); return fail(FORGE_ERR_CUDA); }
+    }
+#undef MC
+    if (cudaStreamSynchronize(st) != cudaSuccess) { set_error("weight upload failed: %s", cudaGetErrorString(cudaGetLastError())); return fail(FORGE_ERR_CUDA); }
+    *out = m;
+    return FORGE_OK;
+}
+
+void forge_model_destroy(ForgeModel* m) {
+    if (!m) return;
+    cudaSetDevice(m->device);
+    if (m->stream) cudaStreamSynchronize(m->stream);
+    for (void* q : m->allocs) cudaFree(q);
+    for (auto& e : m->ev) if (e) cudaEventDestroy(e);
+    if (m->stream) cudaStreamDestroy(m->stream);
+    delete m;
+}
+
+void* forge_model_stream(ForgeModel* m) { return m ? static_cast<void*>(m->stream) : nullptr; }
+
+int32_t forge_kv_create(ForgeModel* m, int32_t max_seq, int32_t batch, ForgeKV** out) {
+    if (!m || !out || max_seq <= 0 || batch <= 0) { set_error("bad argument to forge_kv_create"); return FORGE_ERR_INVALID_ARG; }
+    *out = nullptr;
+    FORGE_CUDA(cudaSetDevice(m->device));
+    ForgeKV* kv = new ForgeKV();
+    kv->model = m;
+    kv->max_seq = std::min(max_seq, m->max_seq);
+    kv->batch = batch;
+    kv->pages_per_seq = (kv->max_seq + FORGE_KV_PAGE - 1) / FORGE_KV_PAGE;
+    kv->num_pages = kv->pages_per_seq * batch;
+    kv->layer_stride = size_t(kv->num_pages) * FORGE_KV_PAGE * m->kv;
+    size_t pool = kv->layer_stride * m->cfg.num_layers;
+    auto fail = [&](int32_t code) { forge_kv_destroy(kv); return code; };
+    if (cudaMalloc(&kv->k_pool, pool * sizeof(__half)) != cudaSuccess || cudaMalloc(&kv->v_pool, pool * sizeof(__half)) != cudaSuccess) {
+        set_error("KV pool allocation of %zu bytes failed", 2 * pool * sizeof(__half)); cudaGetLastError(); return fail(FORGE_ERR_CUDA);
+    }
+    cudaMemsetAsync(kv->k_pool, 0, pool * sizeof(__half), m->stream);
+    cudaMemsetAsync(kv->v_pool, 0, pool * sizeof(__half), m->stream);
+    if (cudaMalloc(&kv->d_page_table, sizeof(int32_t) * kv->num_pages) != cudaSuccess || cudaMalloc(&kv->d_seq_len, sizeof(int32_t) * batch) != cudaSuccess)
+        { set_error("KV table allocation failed"); return fail(FORGE_ERR_CUDA); }
+    cudaMemsetAsync(kv->d_page_table, 0, sizeof(int32_t) * kv->num_pages, m->stream);
+    cudaMemsetAsync(kv->d_seq_len, 0, sizeof(int32_t) * batch, m->stream);
+    kv->h_page_table.assign(kv->num_pages, 0);
+    kv->pages_used.assign(batch, 0);
+    kv->len.assign(batch, 0);
+    for (int i = kv->num_pages - 1; i >= 0; --i) kv->free_pages.push_back(i);
+    // split-KV: enough CTAs to cover the SMs about twice
+    int sms = 148;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, m->device);
+    int want = (2 * sms + batch * m->nkv - 1) / (batch * m->nkv);
+    kv->splits = std::max(1, std::min({want, kv->pages_per_seq, 64}));
+    if (cudaMalloc(&kv->attn_ws, sizeof(float) * attn_decode_ws_floats(batch, m->nq, m->hd, kv->splits)) != cudaSuccess ||
+        cudaMalloc(&kv->attn_counters, sizeof(int) * batch * m->nkv) != cudaSuccess) { set_error("attention workspace allocation failed"); return fail(FORGE_ERR_CUDA); }
+    cudaMemsetAsync(kv->attn_counters, 0, sizeof(int) * batch * m->nkv, m->stream);
+    if (cudaStreamSynchronize(m->stream) != cudaSuccess) { set_error("KV init failed"); return fail(FORGE_ERR_CUDA); }
+    *out = kv;
+    return FORGE_OK;
+}
+
+int32_t forge_kv_reset(ForgeKV* kv) {
+    if (!kv) { set_error("null kv"); return FORGE_ERR_INVALID_ARG; }
+    FORGE_CUDA(cudaSetDevice(kv->model->device));
+    FORGE_CUDA(cudaStreamSynchronize(kv->model->stream));
+    std::fill(kv->len.begin(), kv->len.end(), 0);
+    std::fill(kv->pages_used.begin(), kv->pages_used.end(), 0);
+    kv->free_pages.clear();
+    for (int i = kv->num_pages - 1; i >= 0; --i) kv->free_pages.push_back(i);
+    return upload_len(kv);
+}
+
+int32_t forge_kv_len(const ForgeKV* kv, int32_t seq) { return (kv && seq >= 0 && seq < kv->batch) ? kv->len[seq] : -1; }
+
+void forge_kv_destroy(ForgeKV* kv) {
+    if (!kv) return;
+    cudaSetDevice(kv->model->device);
+    cudaStreamSynchronize(kv->model->stream);
+    if (kv->graph) cudaGraphExecDestroy(kv->graph);
+    cudaFree(kv->k_pool); cudaFree(kv->v_pool); cudaFree(kv->d_page_table); cudaFree(kv->d_seq_len);
+    cudaFree(kv->attn_ws); cudaFree(kv->attn_counters);
+    delete kv;
+}
+
+int32_t forge_kv_read(ForgeKV* kv, int32_t seq, int32_t layer, int32_t which, float* out_host) {
+    FORGE_TRY(check_seq(kv, seq));
+    ForgeModel* m = kv->model;
+    if (layer < 0 || layer >= m->cfg.num_layers || !out_host) { set_error("bad argument to forge_kv_read"); return FORGE_ERR_INVALID_ARG; }
+    FORGE_CUDA(cudaSetDevice(m->device));
+    int len = kv->len[seq];
+    if (len == 0) return FORGE_OK;
+    float* tmp = nullptr;
+    FORGE_CUDA(cudaMalloc(&tmp, sizeof(float) * len * m->kv));
+    const __half* pool = (which ? kv->v_pool : kv->k_pool) + size_t(layer) * kv->layer_stride;
+    int32_t rc = gather_rows_f16(tmp, pool, kv->d_page_table + size_t(seq) * kv->pages_per_seq, len, m->kv, m->stream);
+    if (rc == FORGE_OK && (cudaMemcpyAsync(out_host, tmp, sizeof(float) * len * m->kv, cudaMemcpyDeviceToHost, m->stream) != cudaSuccess ||
+                           cudaStreamSynchronize(m->stream) != cudaSuccess)) { set_error("kv read copy failed"); rc = FORGE_ERR_CUDA; }
+    cudaFree(tmp);
+    return rc;
+}
+
+int32_t forge_forward_prefill_seq(ForgeModel* m, ForgeKV* kv, int32_t seq, const uint32_t* tokens, size_t n, float* logits_host) {
+    if (!m || !tokens || n == 0 || n > (1u << 20)) { set_error("bad argument to forge_forward_prefill"); return FORGE_ERR_INVALID_ARG; }
+    FORGE_TRY(check_seq(kv, seq));
+    if (kv->model != m) { set_error("kv belongs to another model"); return FORGE_ERR_INVALID_ARG; }
+    FORGE_CUDA(cudaSetDevice(m->device));
+    for (size_t i = 0; i < n; ++i) if (tokens[i] >= uint32_t(m->V)) { set_error("token id %u out of vocabulary", tokens[i]); return FORGE_ERR_INVALID_ARG; }
+    if (kv->len[seq] + int(n) > kv->max_seq) { set_error("KV cache full: %d + %zu > max_seq %d", kv->len[seq], n, kv->max_seq); return FORGE_ERR_KV_FULL; }
+    if (n < FORGE_PREFILL_BATCH_THRESHOLD && !m->trace_on) {
+        // emit.rs:4581: short prompts take the per-token path
+        for (size_t i = 0; i < n; ++i) FORGE_TRY(forge_forward_seq(m, kv, seq, tokens[i], (i + 1 == n) ? logits_host : nullptr));
+        return FORGE_OK;
+    }
+    FORGE_TRY(prefill_seq(m, kv, seq, tokens, int(n)));
+    FORGE_TRY(upload_len(kv));
+    if (logits_host) FORGE_CUDA(cudaMemcpyAsync(logits_host, m->d_logits, sizeof(float) * m->V, cudaMemcpyDeviceToHost, m->stream));
+    FORGE_CUDA(cudaStreamSynchronize(m->stream));
+    return FORGE_OK;
+}
+
+int32_t forge_forward_prefill(ForgeModel* m, ForgeKV* kv, const uint32_t* tokens, size_t n, float* logits_host) {
+    return forge_forward_prefill_seq(m, kv, 0, tokens, n, logits_host);
+}
+
+// single sequence `seq` of a multi-sequence cache: runs the batch-1 launch sequence on views of that sequence
+int32_t forge_forward_seq(ForgeModel* m, ForgeKV* kv, int32_t seq, uint32_t token, float* logits_host) {
+    if (!m) { set_error("null model"); return FORGE_ERR_INVALID_ARG; }
+    FORGE_TRY(check_seq(kv, seq));
+    if (kv->model != m) { set_error("kv belongs to another model"); return FORGE_ERR_INVALID_ARG; }
+    if (token >= uint32_t(m->V)) { set_error("token id %u out of vocabulary", token); return FORGE_ERR_INVALID_ARG; }
+    FORGE_CUDA(cudaSetDevice(m->device));
+    FORGE_TRY(ensure_decode_scratch(m, 1));
+    FORGE_TRY(ensure_pages(kv, seq, kv->len[seq] + 1));
+    if (m->trace_on) FORGE_TRY(ensure_trace(m, 1));
+    FORGE_CUDA(cudaMemcpyAsync(m->d_tok, &token, sizeof(uint32_t), cudaMemcpyHostToDevice, m->stream));
+    // view of sequence `seq` as a batch of one
+    ForgeKV view = *kv;
+    view.d_page_table = kv->d_page_table + size_t(seq) * kv->pages_per_seq;
+    view.d_seq_len = kv->d_seq_len + seq;
+    view.graph = nullptr;
+    int32_t rc;
+    if (seq == 0 && kv->batch >= 1 && !m->trace_on) {
+        rc = decode_step_graph(m, kv, 1, false);
+    } else {
+        rc = decode_launches(m, &view, 1, false, false);
+    }
+    view.h_page_table.clear();
+    FORGE_TRY(rc);
+    kv->len[seq] += 1;
+    if (logits_host) FORGE_CUDA(cudaMemcpyAsync(logits_host, m->d_logits, sizeof(float) * m->V, cudaMemcpyDeviceToHost, m->stream));
+    FORGE_CUDA(cudaStreamSynchronize(m->stream));
+    return FORGE_OK;
+}
+
+int32_t forge_forward(ForgeModel* m, ForgeKV* kv, uint32_t token, float* logits_host) { return forge_forward_seq(m, kv, 0, token, logits_host); }
+
+int32_t forge_forward_batch(ForgeModel* m, ForgeKV* kv, int32_t batch, const uint32_t* tokens, float* logits_host) {
+    if (!m || !kv || !tokens || batch <= 0 || batch > kv->batch || kv->model != m) { set_error("bad argument to forge_forward_batch"); return FORGE_ERR_INVALID_ARG; }
+    for (int b = 0; b < batch; ++b) if (tokens[b] >= uint32_t(m->V)) { set_error("token id %u out of vocabulary", tokens[b]); return FORGE_ERR_INVALID_ARG; }
+    FORGE_CUDA(cudaSetDevice(m->device));
+    FORGE_TRY(ensure_decode_scratch(m, batch));
+    FORGE_TRY(decode_prepare(kv, batch));
+    if (m->trace_on) FORGE_TRY(ensure_trace(m, batch));
+    FORGE_CUDA(cudaMemcpyAsync(m->d_tok, tokens, sizeof(uint32_t) * batch, cudaMemcpyHostToDevice, m->stream));
+    FORGE_TRY(decode_step_graph(m, kv, batch, false));
+    for (int b = 0; b < batch; ++b) kv->len[b] += 1;
+    if (logits_host) FORGE_CUDA(cudaMemcpyAsync(logits_host, m->d_logits, sizeof(float) * size_t(batch) * m->V, cudaMemcpyDeviceToHost, m->stream));
+    FORGE_CUDA(cudaStreamSynchronize(m->stream));
+    return FORGE_OK;
+}
+
+static int32_t ensure_hist(ForgeModel* m, int n) {
+    if (n > m->hist_cap) { FORGE_TRY(dev_alloc(m, &m->d_hist, size_t(n))); m->hist_cap = n; }
+    return FORGE_OK;
+}
+
+int32_t forge_decode_greedy_batch(ForgeModel* m, ForgeKV* kv, int32_t batch, const uint32_t* first_tokens, int32_t n_new, uint32_t* out_tokens) {
+    if (!m || !kv || !first_tokens || !out_tokens || batch <= 0 || batch > kv->batch || n_new <= 0 || kv->model != m) { set_error("bad argument to forge_decode_greedy_batch"); return FORGE_ERR_INVALID_ARG; }
+    FORGE_CUDA(cudaSetDevice(m->device));
+    for (int b = 0; b < batch; ++b) {
+        if (first_tokens[b] >= uint32_t(m->V)) { set_error("token id out of vocabulary"); return FORGE_ERR_INVALID_ARG; }
+        if (kv->len[b] + n_new > kv->max_seq) { set_error("KV cache full: %d + %d > max_seq %d", kv->len[b], n_new, kv->max_seq); return FORGE_ERR_KV_FULL; }
+    }
+    FORGE_TRY(ensure_decode_scratch(m, batch));
+    FORGE_TRY(ensure_hist(m, n_new * batch));
+    long long l0 = g_launches;
+    FORGE_CUDA(cudaMemcpyAsync(m->d_tok, first_tokens, sizeof(uint32_t) * batch, cudaMemcpyHostToDevice, m->stream));
+    FORGE_CUDA(cudaMemsetAsync(m->d_step, 0, sizeof(int32_t), m->stream));
+    FORGE_CUDA(cudaEventRecord(m->ev[1], m->stream));
+    bool saved_trace = m->trace_on;
+    m->trace_on = false;
+    for (int i = 0; i < n_new; ++i) {
+        int32_t rc = decode_prepare(kv, batch);
+        if (rc == FORGE_OK) rc = decode_step_graph(m, kv, batch, true);
+        if (rc != FORGE_OK) { m->trace_on = saved_trace; return rc; }
+        for (int b = 0; b < batch; ++b) kv->len[b] += 1;
+    }
+    m->trace_on = saved_trace;
+    FORGE_CUDA(cudaEventRecord(m->ev[2], m->stream));
+    FORGE_CUDA(cudaMemcpyAsync(out_tokens, m->d_hist, sizeof(uint32_t) * size_t(n_new) * batch, cudaMemcpyDeviceToHost, m->stream));
+    FORGE_CUDA(cudaStreamSynchronize(m->stream));
+    FORGE_CUDA(cudaEventElapsedTime(&m->decode_ms, m->ev[1], m->ev[2]));
+    m->last_launches = g_launches - l0;
+    return FORGE_OK;
+}
+
+int32_t forge_generate_greedy(ForgeModel* m, ForgeKV* kv, const uint32_t* prompt, size_t n, int32_t n_new, uint32_t* out_tokens) {
+    if (!m || !kv || !prompt || !out_tokens || n == 0 || n_new <= 0 || kv->model != m) { set_error("bad argument to forge_generate_greedy"); return FORGE_ERR_INVALID_ARG; }
+    FORGE_CUDA(cudaSetDevice(m->device));
+    if (kv->len[0] + int(n) + n_new > kv->max_seq) { set_error("KV cache full: %d + %zu + %d > max_seq %d", kv->len[0], n, n_new, kv->max_seq); return FORGE_ERR_KV_FULL; }
+    for (size_t i = 0; i < n; ++i) if (prompt[i] >= uint32_t(m->V)) { set_error("token id %u out of vocabulary", prompt[i]); return FORGE_ERR_INVALID_ARG; }
+    FORGE_TRY(ensure_decode_scratch(m, 1));
+    long long l0 = g_launches;
+    FORGE_CUDA(cudaEventRecord(m->ev[0], m->stream));
+    if (n < FORGE_PREFILL_BATCH_THRESHOLD) {
+        for (size_t i = 0; i < n; ++i) FORGE_TRY(forge_forward_seq(m, kv, 0, prompt[i], nullptr));
+    } else {
+        FORGE_TRY(prefill_seq(m, kv, 0, prompt, int(n)));
+        FORGE_TRY(upload_len(kv));
+    }
+    // first token: sample() of the prefill logits (project.rs:722)
+    FORGE_TRY(argmax_last(m->d_tok, m->d_logits, m->V, 1, m->stream));
+    uint32_t first = 0;
+    FORGE_CUDA(cudaMemcpyAsync(&first, m->d_tok, sizeof(uint32_t), cudaMemcpyDeviceToHost, m->stream));
+    FORGE_CUDA(cudaStreamSynchronize(m->stream));
+    long long lp = g_launches - l0;
+    int32_t rc = forge_decode_greedy_batch(m, kv, 1, &first, n_new, out_tokens);
+    if (rc != FORGE_OK) return rc;
+    FORGE_CUDA(cudaEventElapsedTime(&m->prefill_ms, m->ev[0], m->ev[1]));
+    m->last_launches += lp;
+    return FORGE_OK;
+}
+
+int32_t forge_model_set_gemm_passes(ForgeModel* m, int32_t passes) {
+    if (!m || (passes != 1 && passes != 3)) { set_error("gemm passes must be 1 or 3"); return FORGE_ERR_INVALID_ARG; }
+    m->gemm_passes = passes;
+    return FORGE_OK;
+}
+
+int32_t forge_hidden_trace_enable(ForgeModel* m, int32_t enable) {
+    if (!m) { set_error("null model"); return FORGE_ERR_INVALID_ARG; }
+    m->trace_on = enable != 0;
+    return FORGE_OK;
+}
+
+int32_t forge_hidden_trace_read(ForgeModel* m, float* out_host, size_t capacity_floats, int32_t* rows) {
+    if (!m || !out_host || !rows) { set_error("bad argument to forge_hidden_trace_read"); return FORGE_ERR_INVALID_ARG; }
+    size_t n = size_t(m->cfg.num_layers) * m->trace_rows * m->h;
+    if (n == 0 || !m->trace) { set_error("no trace recorded"); return FORGE_ERR_INVALID_ARG; }
+    if (capacity_floats < n) { set_error("trace needs %zu floats", n); return FORGE_ERR_INVALID_ARG; }
+    FORGE_CUDA(cudaSetDevice(m->device));
+    FORGE_CUDA(cudaMemcpyAsync(out_host, m->trace, n * 4, cudaMemcpyDeviceToHost, m->stream));
+    FORGE_CUDA(cudaStreamSynchronize(m->stream));
+    *rows = m->trace_rows;
+    return FORGE_OK;
+}
+
+int32_t forge_last_timing(ForgeModel* m, float* prefill_ms, float* decode_ms, int64_t* launches) {
+    if (!m) { set_error("null model"); return FORGE_ERR_INVALID_ARG; }
+    if (prefill_ms) *prefill_ms = m->prefill_ms;
+    if (decode_ms) *decode_ms = m->decode_ms;
+    if (launches) *launches = m->last_launches;
+    return FORGE_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,165 @@
+"""Host-side mirror of the generated ``model::`` surface on top of the C ABI.
+
+Names and argument meaning follow the reference's generated module
+(crates/forgellm-codegen-cpu/src/emit.rs): ``Weights``/``KVCache`` become :class:`Model` and
+:class:`KVCache`; ``forward(token, &weights, &mut cache)`` (emit.rs:4029) and
+``forward_prefill(tokens, &weights, &mut cache)`` (emit.rs:4553) become methods of the model.
+Errors the reference raises as panics (cache overrun, bad slice lengths) surface as
+:class:`ForgeError`.  All buffers crossing this layer are numpy arrays in host memory; the
+library copies to and from the GPU itself.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from ._lib import ForgeError, ForgeModelConfig, check, lib
+
+
+def _cfg_struct(c: dict, tp_rank: int = 0, tp_world: int = 1) -> ForgeModelConfig:
+    return ForgeModelConfig(c["hidden_size"], c["intermediate_size"], c["num_layers"], c["num_heads"],
+                            c["num_kv_heads"], c["head_dim"], c["vocab_size"], c["max_seq_len"],
+                            c["rms_norm_eps"], c["rope_theta"], c["quant"], int(c.get("qkv_bias", 0)),
+                            tp_rank, tp_world)
+
+
+def _p(a: np.ndarray | None):
+    return None if a is None else a.ctypes.data_as(C.c_void_p)
+
+
+def weights_bin_size(c: dict) -> int:
+    s = _cfg_struct(c)
+    return int(lib.forge_weights_bin_size(C.byref(s)))
+
+
+def quantize_q8_0(x: np.ndarray) -> np.ndarray:
+    """Host quantiser of the exporter (weight_loader.rs:1454-1486)."""
+    x = np.ascontiguousarray(x, np.float32).ravel()
+    out = np.empty(x.size // 32 * 34, np.uint8)
+    check(lib.forge_quantize_q8_0_host(_p(x), x.size, _p(out)))
+    return out
+
+
+def quantize_q4_0(x: np.ndarray, signed_max: bool = True) -> np.ndarray:
+    x = np.ascontiguousarray(x, np.float32).ravel()
+    out = np.empty(x.size // 32 * 18, np.uint8)
+    check(lib.forge_quantize_q4_0_host(_p(x), x.size, _p(out), int(signed_max)))
+    return out
+
+
+class KVCache:
+    """``KVCache`` of the generated module (emit.rs:3954-4015): fp16, paged, ``batch`` sequences."""
+
+    def __init__(self, model: "Model", max_seq: int | None = None, batch: int = 1):
+        self.model = model
+        self.batch = batch
+        h = C.c_void_p()
+        check(lib.forge_kv_create(model._h, int(max_seq or model.cfg["max_seq_len"]), batch, C.byref(h)))
+        self._h = h
+
+    def reset(self) -> None:
+        check(lib.forge_kv_reset(self._h))
+
+    def len(self, seq: int = 0) -> int:
+        return int(lib.forge_kv_len(self._h, seq))
+
+    def read(self, layer: int, which: int, seq: int = 0) -> np.ndarray:
+        kvd = self.model.cfg["num_kv_heads"] * self.model.cfg["head_dim"] // self.model.tp_world
+        out = np.empty((self.len(seq), kvd), np.float32)
+        check(lib.forge_kv_read(self._h, seq, layer, which, _p(out)))
+        return out
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            lib.forge_kv_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class Model:
+    """``Weights`` + ``forward`` / ``forward_prefill`` of the generated module."""
+
+    def __init__(self, cfg: dict, weights_bin: np.ndarray, device: int = 0, tp_rank: int = 0, tp_world: int = 1):
+        self.cfg = dict(cfg)
+        self.tp_world = tp_world
+        blob = np.ascontiguousarray(weights_bin, np.uint8)
+        s = _cfg_struct(cfg, tp_rank, tp_world)
+        h = C.c_void_p()
+        check(lib.forge_model_create(C.byref(s), _p(blob), blob.size, device, C.byref(h)))
+        self._h = h
+        self.device = device
+
+    @property
+    def stream(self) -> int:
+        return int(lib.forge_model_stream(self._h) or 0)
+
+    def new_cache(self, max_seq: int | None = None, batch: int = 1) -> KVCache:
+        return KVCache(self, max_seq, batch)
+
+    def forward(self, token: int, cache: KVCache, seq: int = 0, want_logits: bool = True):
+        logits = np.empty(self.cfg["vocab_size"], np.float32) if want_logits else None
+        check(lib.forge_forward_seq(self._h, cache._h, seq, int(token), _p(logits)))
+        return logits
+
+    def forward_prefill(self, tokens, cache: KVCache, seq: int = 0, want_logits: bool = True):
+        t = np.ascontiguousarray(tokens, np.uint32)
+        logits = np.empty(self.cfg["vocab_size"], np.float32) if want_logits else None
+        check(lib.forge_forward_prefill_seq(self._h, cache._h, seq, _p(t), t.size, _p(logits)))
+        return logits
+
+    def forward_batch(self, tokens, cache: KVCache, want_logits: bool = True):
+        t = np.ascontiguousarray(tokens, np.uint32)
+        logits = np.empty((t.size, self.cfg["vocab_size"]), np.float32) if want_logits else None
+        check(lib.forge_forward_batch(self._h, cache._h, t.size, _p(t), _p(logits)))
+        return logits
+
+    def generate_greedy(self, prompt, n_new: int, cache: KVCache) -> np.ndarray:
+        """Prefill + ``n_new`` greedy steps with token selection on the device (project.rs:714-751
+        at temperature 0, repeat penalty 1.0).  Host prompt in, host token ids out."""
+        t = np.ascontiguousarray(prompt, np.uint32)
+        out = np.empty(n_new, np.uint32)
+        check(lib.forge_generate_greedy(self._h, cache._h, _p(t), t.size, n_new, _p(out)))
+        return out
+
+    def decode_greedy_batch(self, first_tokens, n_new: int, cache: KVCache) -> np.ndarray:
+        t = np.ascontiguousarray(first_tokens, np.uint32)
+        out = np.empty((n_new, t.size), np.uint32)
+        check(lib.forge_decode_greedy_batch(self._h, cache._h, t.size, _p(t), n_new, _p(out)))
+        return out
+
+    def set_gemm_passes(self, passes: int) -> None:
+        """3 = split-precision prefill GEMMs (default), 1 = a single fp16 tensor-core pass."""
+        check(lib.forge_model_set_gemm_passes(self._h, passes))
+
+    def trace(self, enable: bool) -> None:
+        check(lib.forge_hidden_trace_enable(self._h, int(enable)))
+
+    def read_trace(self, rows: int) -> np.ndarray:
+        out = np.empty((self.cfg["num_layers"], rows, self.cfg["hidden_size"]), np.float32)
+        got = C.c_int32()
+        check(lib.forge_hidden_trace_read(self._h, _p(out), out.size, C.byref(got)))
+        if got.value != rows:
+            raise ForgeError(1, f"trace holds {got.value} rows, asked for {rows}")
+        return out
+
+    def last_timing(self):
+        a, b, n = C.c_float(), C.c_float(), C.c_int64()
+        check(lib.forge_last_timing(self._h, C.byref(a), C.byref(b), C.byref(n)))
+        return a.value, b.value, n.value
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            lib.forge_model_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

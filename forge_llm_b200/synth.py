@@ -46,7 +46,7 @@ def quantize_q4_0(x: np.ndarray) -> np.ndarray:
     b = np.ascontiguousarray(x, np.float32).reshape(-1, 32)
     idx = np.abs(b).argmax(axis=1)
     vmax = b[np.arange(b.shape[0]), idx]
-    d = (vmax / np.float32(-8.0)).astype(np.float32)
+    d = np.where(vmax == 0, np.float32(0), vmax / np.float32(-8.0)).astype(np.float32)
     with np.errstate(divide="ignore"):
         inv = np.where(d != 0, np.float32(1.0) / d, np.float32(0)).astype(np.float32)
     q = np.clip(_round_half_away(b * inv[:, None]).astype(np.int32) + 8, 0, 15).astype(np.uint8)

@@ -1,0 +1,208 @@
+/* forge_b200.h — C ABI of the B200 (sm_100a) backend for ForgeLLM's quantized forward path.
+ *
+ * The reference has no FFI: its boundary is the function surface of the Rust module that
+ * its CPU code generator emits (`model::forward`, `model::forward_prefill`, the shape-
+ * specialised `matmul_vec_*` / `matmul_mat_*`, `attention_flash*`, `rms_norm`, `rope`,
+ * `silu_mul`, `residual_add`) plus the `weights.bin` file format.  Each entry point below
+ * names the generated function it replaces (file:line in the reference tree, where
+ * E = crates/forgellm-codegen-cpu/src/emit.rs, P = crates/forgellm-codegen-cpu/src/project.rs,
+ * WL = crates/forgellm-frontend/src/weight_loader.rs, CLI = crates/forgellm-cli/src/main.rs).
+ *
+ * Conventions
+ *  - Every function returns a ForgeStatus (0 = ok); nothing aborts the process.
+ *  - "device pointer" arguments are CUDA global-memory addresses on the current device;
+ *    "host pointer" arguments are ordinary process memory.  No torch types appear here.
+ *  - `stream` is a `cudaStream_t` passed as `void*` (NULL = the default stream).
+ *  - Shapes are run-time arguments (the reference bakes them into function names).
+ *  - Calls that touch one ForgeKV must be serialised by the caller (the reference enforces
+ *    the same with `&mut KVCache`).
+ *  - There is no CPU fallback: without a CUDA device every compute entry point returns
+ *    FORGE_ERR_CUDA.
+ */
+#ifndef FORGE_B200_H
+#define FORGE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum ForgeStatus {
+    FORGE_OK = 0,
+    FORGE_ERR_INVALID_ARG = 1, /* null pointer, negative size, unknown enum value */
+    FORGE_ERR_SHAPE = 2,       /* K not a multiple of 32, unsupported head_dim, blob length mismatch */
+    FORGE_ERR_KV_FULL = 3,     /* position would pass max_seq (the reference panics on the slice bound) */
+    FORGE_ERR_CUDA = 4,        /* a CUDA runtime call failed; forge_last_error() has the text */
+    FORGE_ERR_TIMEOUT = 5,     /* a bounded device-side wait gave up */
+    FORGE_ERR_UNSUPPORTED = 6,
+    FORGE_ERR_COMM = 7         /* tensor-parallel collective failed */
+} ForgeStatus;
+
+#define FORGE_Q8_0 8 /* GGUF Q8_0: 34-byte blocks {f16 d; int8 q[32]}        (E:1266-1268, WL:860-888) */
+#define FORGE_Q4_0 4 /* GGUF Q4_0: 18-byte blocks {f16 d; u8 qs[16]}, value = nibble-8,
+                        byte j = element j (low) and j+16 (high)          (E:2337-2359, WL:893-926) */
+
+#define FORGE_PREFILL_BATCH_THRESHOLD 8 /* E:203-206 */
+#define FORGE_KV_PAGE 64                /* positions per KV page (= FLASH_ATTN_BLOCK_SIZE, E:199-202) */
+
+/* Mirrors the reference's ModelConfig (crates/forgellm-frontend/src/ir.rs:484-519), reduced
+ * to the fields the emitted constants use (E:151-206). */
+typedef struct ForgeModelConfig {
+    int32_t hidden_size;
+    int32_t intermediate_size;
+    int32_t num_layers;
+    int32_t num_heads;
+    int32_t num_kv_heads;
+    int32_t head_dim; /* 64, 96 or 128 */
+    int32_t vocab_size;
+    int32_t max_seq_len; /* capped at 4096 like MAX_SEQ_LEN (E:178) */
+    float rms_norm_eps;
+    float rope_theta;
+    int32_t quant;    /* FORGE_Q8_0 or FORGE_Q4_0, for every projection and lm_head */
+    int32_t qkv_bias; /* 1: f32 q,k,v biases follow v_proj in weights.bin (Qwen2, E:4108-4118) */
+    int32_t tp_rank;  /* tensor-parallel rank / world size; 0 / 1 when not sharded */
+    int32_t tp_world;
+} ForgeModelConfig;
+
+typedef struct ForgeModel ForgeModel;
+typedef struct ForgeKV ForgeKV;
+
+/* Text of the last error on the calling thread ("" if none). */
+const char* forge_last_error(void);
+/* Number of CUDA devices visible; 0 when there is no driver or no device. */
+int32_t forge_device_count(void);
+
+/* ------------------------------------------------------------------------------------
+ * Operator surface (device pointers).  Weights are raw GGUF block bytes, row-major
+ * [N][K/32][block], exactly what the generated functions take.
+ * ------------------------------------------------------------------------------------ */
+
+/* matmul_vec_q8_0_{K}x{N}(output, input, weight)              E:2047-2087 (dot_q8_0 E:1359-1377)
+ * matmul_mat_q8_0_{K}x{N}(output, m, input, weight)           E:2278-2299
+ *   out f32 [m][N], in f32 [m][K], w u8 [N][K/32][34].  m == 1 is the decode GEMV. */
+int32_t forge_matmul_mat_q8_0(float* out, int32_t m, const float* in, const uint8_t* w,
+                              int32_t K, int32_t N, void* stream);
+/* matmul_vec_q4_0_{K}x{N} E:2910-2953 (dot_q4_0 E:2337-2359); matmul_mat_q4_0_{K}x{N} E:3792-3813 */
+int32_t forge_matmul_mat_q4_0(float* out, int32_t m, const float* in, const uint8_t* w,
+                              int32_t K, int32_t N, void* stream);
+
+/* rms_norm(output, input, weight, eps)  E:327-334, applied to `rows` rows of n values. */
+int32_t forge_rms_norm(float* out, const float* in, const float* weight, int32_t rows, int32_t n,
+                       float eps, void* stream);
+/* rope_freqs + the per-position sin/cos table of rope()  E:502-519.  Host function: fills
+ * table[pos][i] = {cos, sin}(pos * 1/theta^(2i/head_dim)) for pos < n_pos, i < head_dim/2,
+ * with the host libm in f32 (the arithmetic the reference's CPU path performs). */
+int32_t forge_rope_table(float* table_host, int32_t n_pos, int32_t head_dim, float theta);
+/* rope(data, pos, head_dim, num_heads, freqs)  E:509-528, for `rows` rows; row r uses
+ * position base_pos + r.  `table` is a device copy of forge_rope_table's output. */
+int32_t forge_rope(float* data, int32_t rows, int32_t base_pos, int32_t head_dim, int32_t num_heads,
+                   const float* table, void* stream);
+/* silu_mul(output, gate, up)  E:381-386 */
+int32_t forge_silu_mul(float* out, const float* gate, const float* up, size_t n, void* stream);
+/* residual_add(a, b)  E:455-459 */
+int32_t forge_residual_add(float* a, const float* b, size_t n, void* stream);
+
+/* Cache write that replaces quantize_kv + copy_from_slice (E:533-545, E:4136-4153): rounds
+ * `rows` K and V rows (f32 [rows][num_kv_heads*head_dim]) to fp16 and stores them at
+ * positions base_pos.. of a contiguous fp16 cache [pos][kv_head][d]. */
+int32_t forge_kv_append_f16(uint16_t* k_cache, uint16_t* v_cache, const float* k, const float* v,
+                            int32_t rows, int32_t base_pos, int32_t kv_dim, void* stream);
+/* attention_flash(output, q, k_cache, v_cache, .., seq_len, num_heads, num_kv_heads, head_dim)
+ * E:657-715, over a contiguous fp16 cache [pos][kv_head][d] (the reference CPU cache is int8
+ * with per-token scales; fp16 is the cache type of this backend). out, q: f32 [nh*hd]. */
+int32_t forge_attention_flash(float* out, const float* q, const uint16_t* k_cache,
+                              const uint16_t* v_cache, int32_t seq_len, int32_t num_heads,
+                              int32_t num_kv_heads, int32_t head_dim, void* stream);
+/* attention_flash_batch(output, q_batch, k_cache, v_cache, .., m, base_pos, ...)  E:755-883.
+ * Query row r sits at position base_pos + r and sees cache positions <= its own. */
+int32_t forge_attention_flash_batch(float* out, const float* q_batch, const uint16_t* k_cache,
+                                    const uint16_t* v_cache, int32_t m, int32_t base_pos,
+                                    int32_t num_heads, int32_t num_kv_heads, int32_t head_dim,
+                                    void* stream);
+/* argmax of the generated main (P:501-503): on ties the LAST maximal index wins.
+ * logits: device f32 [n]; result: device u32. */
+int32_t forge_argmax(uint32_t* result, const float* logits, int32_t n, void* stream);
+
+/* Host-side quantisers of the reference's exporter (quantize_f32_to_q8_0 WL:1454-1486;
+ * Q4_0 packing WL:1494-1544 with `signed_max` = 0, or the signed-max scale rule
+ * d = largest-magnitude value / -8 with `signed_max` = 1).  n must be a multiple of 32. */
+int32_t forge_quantize_q8_0_host(const float* x, size_t n, uint8_t* out);
+int32_t forge_quantize_q4_0_host(const float* x, size_t n, uint8_t* out, int32_t signed_max);
+
+/* ------------------------------------------------------------------------------------
+ * Session surface: Weights / KVCache / forward / forward_prefill of the generated module.
+ * ------------------------------------------------------------------------------------ */
+
+/* Byte length of weights.bin for a configuration (layout: CLI:2714-2757, P:341-407). */
+size_t forge_weights_bin_size(const ForgeModelConfig* cfg);
+
+/* Weights (E:3875-3939) from a host image of weights.bin; uploads to `device` and repacks
+ * the blocks into the kernels' aligned layout (same bytes per weight).  With tp_world > 1
+ * the rank keeps its column slice of q/k/v/gate/up and its row slice of o/down. */
+int32_t forge_model_create(const ForgeModelConfig* cfg, const void* weights_bin, size_t len,
+                           int32_t device, ForgeModel** out);
+void forge_model_destroy(ForgeModel* model);
+/* The CUDA stream (cudaStream_t) all work of this model is launched on. */
+void* forge_model_stream(ForgeModel* model);
+
+/* Numeric form of the prefill GEMMs (matmul_mat_*, E:2278-2299).  3 (default): both operands
+ * are carried as fp16 hi+lo pairs and three tensor-core passes are accumulated in f32 (~1e-6
+ * relative to the reference's all-f32 arithmetic); 1: one fp16 pass (~3e-4 relative per GEMM,
+ * which exceeds 1e-3 on the hidden state after ~20 layers). */
+int32_t forge_model_set_gemm_passes(ForgeModel* model, int32_t passes);
+
+/* KVCache::new (E:3978-4000) for `batch` independent sequences of up to max_seq positions,
+ * fp16, paged (FORGE_KV_PAGE positions per page, pages handed out on demand). */
+int32_t forge_kv_create(ForgeModel* model, int32_t max_seq, int32_t batch, ForgeKV** out);
+/* KVCache::reset (E:4002-4005): all sequences back to length 0, pages returned. */
+int32_t forge_kv_reset(ForgeKV* kv);
+/* cache.len of sequence `seq`; -1 on a bad argument. */
+int32_t forge_kv_len(const ForgeKV* kv, int32_t seq);
+void forge_kv_destroy(ForgeKV* kv);
+/* Copy K (which = 0) or V (1) rows [0, len) of `layer`, sequence `seq`, widened to f32, into
+ * a host buffer [len][num_kv_heads*head_dim] (used by parity tests). */
+int32_t forge_kv_read(ForgeKV* kv, int32_t seq, int32_t layer, int32_t which, float* out_host);
+
+/* forward(token_id, &weights, &mut cache) -> Vec<f32>  E:4029-4500, sequence 0.
+ * logits_host: V floats (may be NULL to skip the copy). */
+int32_t forge_forward(ForgeModel* model, ForgeKV* kv, uint32_t token, float* logits_host);
+/* forward_prefill(tokens, &weights, &mut cache) -> Vec<f32>  E:4553-4587 / E:5118-5486,
+ * sequence 0; returns the logits of the last prompt row only (E:5439-5443). */
+int32_t forge_forward_prefill(ForgeModel* model, ForgeKV* kv, const uint32_t* tokens, size_t m,
+                              float* logits_host);
+/* The same two calls for sequence `seq` of a multi-sequence cache. */
+int32_t forge_forward_seq(ForgeModel* model, ForgeKV* kv, int32_t seq, uint32_t token, float* logits_host);
+int32_t forge_forward_prefill_seq(ForgeModel* model, ForgeKV* kv, int32_t seq, const uint32_t* tokens,
+                                  size_t m, float* logits_host);
+/* One decode step for the first `batch` sequences of the cache at once (the reference has no
+ * batched decode: this equals `batch` independent forward() calls).  tokens: host u32 [batch];
+ * logits_host: [batch][V] or NULL. */
+int32_t forge_forward_batch(ForgeModel* model, ForgeKV* kv, int32_t batch, const uint32_t* tokens,
+                            float* logits_host);
+/* The generated main's greedy loop (P:714-751 with temperature 0 and repeat penalty 1.0):
+ * prefill the prompt, then n_new times {argmax, forward}, token selection on the device.
+ * out_tokens: host u32 [n_new]. */
+int32_t forge_generate_greedy(ForgeModel* model, ForgeKV* kv, const uint32_t* prompt, size_t m,
+                              int32_t n_new, uint32_t* out_tokens);
+/* Batched twin of the loop above for the first `batch` sequences after they were prefilled:
+ * first_tokens host u32 [batch]; out_tokens host u32 [n_new][batch]. */
+int32_t forge_decode_greedy_batch(ForgeModel* model, ForgeKV* kv, int32_t batch,
+                                  const uint32_t* first_tokens, int32_t n_new, uint32_t* out_tokens);
+
+/* Parity hook: when enabled, the next forward / forward_prefill call records the hidden
+ * state after every layer.  forge_hidden_trace_read copies [num_layers][rows][hidden] f32 of
+ * the last call to a host buffer and returns the row count through *rows. */
+int32_t forge_hidden_trace_enable(ForgeModel* model, int32_t enable);
+int32_t forge_hidden_trace_read(ForgeModel* model, float* out_host, size_t capacity_floats, int32_t* rows);
+
+/* Device time (CUDA events on the model's stream) of the prefill part and the decode part of
+ * the last forge_generate_greedy / forge_decode_greedy_batch call, in milliseconds, and the
+ * number of kernels of this library launched by that call. */
+int32_t forge_last_timing(ForgeModel* model, float* prefill_ms, float* decode_ms, int64_t* launches);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FORGE_B200_H */

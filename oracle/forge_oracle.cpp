@@ -537,7 +537,7 @@ void fo_quantize_q4_0_signed(const float* x, size_t n, uint8_t* out) {
         size_t base = size_t(b) * 32, end = std::min(base + 32, n);
         float amax = 0.0f, vmax = 0.0f;
         for (size_t i = base; i < end; ++i) { float a = std::fabs(x[i]); if (a > amax) { amax = a; vmax = x[i]; } }
-        float d = vmax / -8.0f;
+        float d = (vmax == 0.0f) ? 0.0f : vmax / -8.0f;
         float inv = (d != 0.0f) ? 1.0f / d : 0.0f;
         uint8_t* o = out + size_t(b) * 18;
         uint16_t hb = f32_to_f16_bits(d);
