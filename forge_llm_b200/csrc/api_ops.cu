@@ -29,6 +29,30 @@ int32_t matmul_mat(int quant, float* out, int32_t m, const float* in, const uint
     if (K % 32) { set_error("K=%d must be a multiple of 32", K); return FORGE_ERR_SHAPE; }
     if (m == 0) return FORGE_OK;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int BS = quant == FORGE_Q8_0 ? 34 : 18;
+    if (m < FORGE_PREFILL_BATCH_THRESHOLD) {  // per-token path: the streaming GEMV, f32-exact up to summation order
+        QTiled qt;
+        qt.K = K; qt.N = N; qt.quant = quant; qt.row_tiles = (N + 15) / 16;
+        AsyncBuf td(st), tab(st), err(st);
+        FORGE_CUDA(td.alloc(qtiled_bytes(quant, K, N)));
+        FORGE_CUDA(tab.alloc(size_t(qt.row_tiles) * 16 * sizeof(uint8_t*)));
+        FORGE_CUDA(err.alloc(sizeof(int)));
+        FORGE_CUDA(cudaMemsetAsync(err.p, 0, sizeof(int), st));
+        std::vector<const uint8_t*> rows(size_t(qt.row_tiles) * 16, nullptr);
+        for (int r = 0; r < N; ++r) rows[r] = w + size_t(r) * (K / 32) * BS;
+        FORGE_CUDA(cudaMemcpyAsync(tab.p, rows.data(), rows.size() * sizeof(uint8_t*), cudaMemcpyHostToDevice, st));
+        FORGE_CUDA(cudaStreamSynchronize(st));  // `rows` leaves scope
+        qt.data = static_cast<uint8_t*>(td.p);
+        FORGE_TRY(tile_pack(static_cast<const uint8_t* const*>(tab.p), qt, st));
+        GemvArgs ga;
+        ga.x = in; ga.out = out; ga.batch = m;
+        FORGE_TRY(gemv_tc(qt, EPI_STORE, ga, static_cast<int*>(err.p), st));
+        int herr = 0;
+        FORGE_CUDA(cudaMemcpyAsync(&herr, err.p, sizeof(int), cudaMemcpyDeviceToHost, st));
+        FORGE_CUDA(cudaStreamSynchronize(st));
+        if (herr) { set_error("gemv: a bounded device-side wait gave up"); return FORGE_ERR_TIMEOUT; }
+        return FORGE_OK;
+    }
     QWeight qw;
     qw.K = K; qw.N = N; qw.quant = quant;
     AsyncBuf qs(st), d(st), a16(st), a16lo(st);
@@ -36,11 +60,6 @@ int32_t matmul_mat(int quant, float* out, int32_t m, const float* in, const uint
     FORGE_CUDA(d.alloc(size_t(N) * (K / 32) * sizeof(__half)));
     qw.qs = static_cast<uint8_t*>(qs.p); qw.d = static_cast<__half*>(d.p);
     FORGE_TRY(pack_rows(w, quant, K, 0, N, 0, K / 32, qw, 0, 1, st));
-    if (m < FORGE_PREFILL_BATCH_THRESHOLD) {  // per-token path: the exact-f32 GEMV
-        GemvArgs ga;
-        ga.x = in; ga.out = out; ga.batch = m;
-        return gemv(qw, EPI_STORE, ga, st);
-    }
     FORGE_CUDA(a16.alloc(size_t(m) * K * sizeof(__half)));
     FORGE_CUDA(a16lo.alloc(size_t(m) * K * sizeof(__half)));
     FORGE_TRY(f32_to_f16(static_cast<__half*>(a16.p), static_cast<__half*>(a16lo.p), in, size_t(m) * K, st));

@@ -77,7 +77,18 @@ struct GemvArgs {
     int pages_per_seq = 0;
     int qk = 0, kv = 0, head_dim = 0;
 };
-int32_t gemv(const QWeight& w, GemvEpilogue epi, const GemvArgs& a, cudaStream_t st);
+// Streaming layout of one projection for the decode GEMV: 16-row x 32-column tiles, each
+// {8 x half2 block scales}{quant bytes in MMA-fragment order}, K-major inside a 16-row band.
+struct QTiled {
+    uint8_t* data = nullptr;
+    int K = 0, N = 0, quant = 0, row_tiles = 0;  // row_tiles = ceil(N/16); padding rows are zero
+};
+size_t qtiled_bytes(int quant, int K, int N);
+// row_src_dev[r] (device array of row_tiles*16 device pointers): first raw GGUF block of the K
+// slice of destination row r, or null for a padding row
+int32_t tile_pack(const uint8_t* const* row_src_dev, QTiled& dst, cudaStream_t st);
+// err: device int set to 1 if a bounded wait inside the kernel gave up (may be null)
+int32_t gemv_tc(const QTiled& w, GemvEpilogue epi, const GemvArgs& a, int* err, cudaStream_t st);
 
 // ------------------------------------------------------------------ elementwise
 int32_t rms_norm_f32(float* out, const float* in, const float* w, int rows, int n, float eps, cudaStream_t st);

@@ -34,12 +34,16 @@ using namespace forge;
 // ------------------------------------------------------------------------------ structures
 struct ForgeLayer {
     float* attn_norm = nullptr;
-    QWeight qkv;           // rows: [q ; k ; v] of this rank
+    QWeight qkv;           // rows: [q ; k ; v] of this rank (row-major split layout: prefill GEMM)
+    QTiled qkv_t;          // the same matrix in the tiled streaming layout (decode GEMV)
     float* qkv_bias = nullptr;
     QWeight o;
+    QTiled o_t;
     float* ffn_norm = nullptr;
     QWeight gateup;        // rows interleaved: 2j = gate_j, 2j+1 = up_j
+    QTiled gateup_t;
     QWeight down;
+    QTiled down_t;
 };
 
 struct ForgeModel {
@@ -52,6 +56,8 @@ struct ForgeModel {
     std::vector<ForgeLayer> layers;
     float* final_norm = nullptr;
     QWeight lm_head;
+    QTiled lm_head_t;
+    int* d_err = nullptr;  // set by a kernel whose bounded wait gave up
     float* rope = nullptr;  // [max_seq][hd/2]{cos,sin}
     int max_seq = 0;
     std::vector<void*> allocs;
@@ -224,7 +230,7 @@ int32_t prefill_seq(ForgeModel* m, ForgeKV* kv, int seq, const uint32_t* tokens_
     // final rms_norm + lm_head on the last row only (emit.rs:5439-5482): exact-f32 GEMV
     GemvArgs ga;
     ga.x = m->p_hidden + size_t(n - 1) * m->h; ga.norm_w = m->final_norm; ga.eps = c.rms_norm_eps; ga.out = m->d_logits; ga.batch = 1;
-    FORGE_TRY(gemv(m->lm_head, EPI_STORE, ga, st));
+    FORGE_TRY(gemv_tc(m->lm_head_t, EPI_STORE, ga, m->d_err, st));
     kv->len[seq] += n;
     return FORGE_OK;
 }
@@ -245,25 +251,25 @@ int32_t decode_launches(ForgeModel* m, ForgeKV* kv, int batch, bool greedy, bool
         a.bias = L.qkv_bias; a.rope = m->rope; a.q_out = m->d_q; a.k_pool = kp; a.v_pool = vp;
         a.page_table = kv->d_page_table; a.seq_len = kv->d_seq_len; a.pages_per_seq = kv->pages_per_seq;
         a.qk = m->qk; a.kv = m->kv; a.head_dim = m->hd;
-        FORGE_TRY(gemv(L.qkv, EPI_QKV, a, st));
+        FORGE_TRY(gemv_tc(L.qkv_t, EPI_QKV, a, m->d_err, st));
         AttnDecodeArgs da{m->d_attn, m->d_q, kp, vp, kv->d_page_table, kv->pages_per_seq, kv->d_seq_len, 0,
                           batch, m->nq, m->nkv, m->hd, kv->max_seq, kv->attn_ws, kv->attn_counters, kv->splits};
         FORGE_TRY(attn_decode(da, st));
         GemvArgs o;
         o.x = m->d_attn; o.out = m->d_hidden; o.resid = m->d_hidden; o.batch = batch;
-        FORGE_TRY(gemv(L.o, EPI_RESID, o, st));
+        FORGE_TRY(gemv_tc(L.o_t, EPI_RESID, o, m->d_err, st));
         GemvArgs g;
         g.x = m->d_hidden; g.norm_w = L.ffn_norm; g.eps = c.rms_norm_eps; g.out = m->d_act; g.batch = batch;
-        FORGE_TRY(gemv(L.gateup, EPI_SILU, g, st));
+        FORGE_TRY(gemv_tc(L.gateup_t, EPI_SILU, g, m->d_err, st));
         GemvArgs d;
         d.x = m->d_act; d.out = m->d_hidden; d.resid = m->d_hidden; d.batch = batch;
-        FORGE_TRY(gemv(L.down, EPI_RESID, d, st));
+        FORGE_TRY(gemv_tc(L.down_t, EPI_RESID, d, m->d_err, st));
         if (m->trace_on)
             FORGE_CUDA(cudaMemcpyAsync(m->trace + size_t(l) * batch * m->h, m->d_hidden, sizeof(float) * batch * m->h, cudaMemcpyDeviceToDevice, st));
     }
     GemvArgs lm;
     lm.x = m->d_hidden; lm.norm_w = m->final_norm; lm.eps = c.rms_norm_eps; lm.out = m->d_logits; lm.batch = batch;
-    FORGE_TRY(gemv(m->lm_head, EPI_STORE, lm, st));
+    FORGE_TRY(gemv_tc(m->lm_head_t, EPI_STORE, lm, m->d_err, st));
     if (greedy) FORGE_TRY(argmax_last(m->d_tok, m->d_logits, m->V, batch, st));
     FORGE_TRY(step_advance(kv->d_seq_len, batch, m->d_step, st));
     return FORGE_OK;
@@ -352,34 +358,59 @@ int32_t forge_model_create(const ForgeModelConfig* cfg, const void* weights_bin,
     for (auto& e : m->ev) if (cudaEventCreate(&e) != cudaSuccess) { set_error("cudaEventCreate failed"); return fail(FORGE_ERR_CUDA); }
     cudaStream_t st = m->stream;
 
-    // staging buffer for raw blocks of the largest tensor
-    size_t max_raw = std::max({raw_bytes(quant, size_t(cfg->vocab_size), H), raw_bytes(quant, FF, H), raw_bytes(quant, QK, H)});
+    // Staging buffer for the raw blocks of one group of tensors (q,k,v | o | gate,up | down | lm_head): the
+    // group is repacked on the device into (a) the row-major split layout the prefill GEMM reads and (b) the
+    // tiled layout the decode GEMV streams, then the stage is reused.
+    const int BS = quant == FORGE_Q8_0 ? 34 : 18;
+    size_t max_raw = std::max({raw_bytes(quant, size_t(cfg->vocab_size), H), 2 * raw_bytes(quant, FF, H) + 64,
+                               raw_bytes(quant, QK, H) + 2 * raw_bytes(quant, KV, H) + 64});
+    size_t max_rows = std::max({size_t(cfg->vocab_size), size_t(2 * FF), size_t(QK + 2 * KV), size_t(H)}) + 16;
     uint8_t* stage = nullptr;
-    if (cudaMalloc(&stage, max_raw) != cudaSuccess) { set_error("cudaMalloc(%zu) failed", max_raw); return fail(FORGE_ERR_CUDA); }
+    const uint8_t** d_rowsrc = nullptr;
+    if (cudaMalloc(&stage, max_raw) != cudaSuccess || cudaMalloc(&d_rowsrc, max_rows * sizeof(uint8_t*)) != cudaSuccess) {
+        set_error("staging allocation of %zu bytes failed", max_raw); cudaFree(stage); return fail(FORGE_ERR_CUDA);
+    }
     const uint8_t* p = static_cast<const uint8_t*>(weights_bin);
     auto upload_f32 = [&](float** dst, size_t n, const uint8_t* src) -> int32_t {
         FORGE_TRY(dev_alloc(m, dst, n));
         FORGE_CUDA(cudaMemcpyAsync(*dst, src, n * 4, cudaMemcpyHostToDevice, st));
         return FORGE_OK;
     };
-    // raw [N][K] blocks at src -> pack rows/blocks slice into dst
-    auto upload_pack = [&](const uint8_t* src, int N, int K, int row0, int rows, int blk0, int blks, QWeight& dst, int dst_row0, int step) -> int32_t {
-        FORGE_CUDA(cudaMemcpyAsync(stage, src, raw_bytes(quant, N, K), cudaMemcpyHostToDevice, st));
-        FORGE_TRY(pack_rows(stage, quant, K, row0, rows, blk0, blks, dst, dst_row0, step, st));
-        FORGE_CUDA(cudaStreamSynchronize(st));  // stage is reused by the next tensor
+    // one source tensor of a group: raw [N_full][K_full/32] blocks on the host; this rank keeps rows
+    // [row0, row0+rows) and blocks [blk0, blk0+blks), landing at destination rows dst_row0 + r*step
+    struct Part { const uint8_t* host; int N_full, K_full, row0, rows, blk0, blks, dst_row0, step; };
+    auto load_group = [&](const std::vector<Part>& parts, QWeight& soa, QTiled& tiled, int K_local, int N_local) -> int32_t {
+        FORGE_TRY(alloc_qweight(m, soa, quant, K_local, N_local));
+        tiled.K = K_local; tiled.N = N_local; tiled.quant = quant; tiled.row_tiles = (N_local + 15) / 16;
+        FORGE_TRY(dev_alloc(m, &tiled.data, qtiled_bytes(quant, K_local, N_local)));
+        std::vector<const uint8_t*> table(size_t(tiled.row_tiles) * 16, nullptr);
+        size_t off = 0;
+        for (const Part& pt : parts) {
+            const size_t bytes = raw_bytes(quant, pt.N_full, pt.K_full);
+            FORGE_CUDA(cudaMemcpyAsync(stage + off, pt.host, bytes, cudaMemcpyHostToDevice, st));
+            FORGE_TRY(pack_rows(stage + off, quant, pt.K_full, pt.row0, pt.rows, pt.blk0, pt.blks, soa, pt.dst_row0, pt.step, st));
+            for (int r = 0; r < pt.rows; ++r)
+                table[size_t(pt.dst_row0) + size_t(r) * pt.step] = stage + off + (size_t(pt.row0 + r) * (pt.K_full / 32) + pt.blk0) * BS;
+            off += (bytes + 15) & ~size_t(15);
+        }
+        FORGE_CUDA(cudaMemcpyAsync(d_rowsrc, table.data(), table.size() * sizeof(uint8_t*), cudaMemcpyHostToDevice, st));
+        FORGE_TRY(tile_pack(d_rowsrc, tiled, st));
+        FORGE_CUDA(cudaStreamSynchronize(st));  // stage, table and the host vector are reused by the next group
         return FORGE_OK;
     };
-#define MC(expr) do { rc = (expr); if (rc != FORGE_OK) { cudaFree(stage); return fail(rc); } } while (0)
+#define MC(expr) do { rc = (expr); if (rc != FORGE_OK) { cudaFree(stage); cudaFree(d_rowsrc); return fail(rc); } } while (0)
     MC(upload_f32(&m->embed, size_t(cfg->vocab_size) * H, p));
     p += size_t(cfg->vocab_size) * H * 4;
     m->layers.resize(cfg->num_layers);
     for (int l = 0; l < cfg->num_layers; ++l) {
         ForgeLayer& L = m->layers[l];
         MC(upload_f32(&L.attn_norm, H, p)); p += size_t(H) * 4;
-        MC(alloc_qweight(m, L.qkv, quant, H, m->qk + 2 * m->kv));
-        MC(upload_pack(p, QK, H, rk * m->qk, m->qk, 0, H / 32, L.qkv, 0, 1)); p += raw_bytes(quant, QK, H);
-        MC(upload_pack(p, KV, H, rk * m->kv, m->kv, 0, H / 32, L.qkv, m->qk, 1)); p += raw_bytes(quant, KV, H);
-        MC(upload_pack(p, KV, H, rk * m->kv, m->kv, 0, H / 32, L.qkv, m->qk + m->kv, 1)); p += raw_bytes(quant, KV, H);
+        const uint8_t* pq = p; p += raw_bytes(quant, QK, H);
+        const uint8_t* pk = p; p += raw_bytes(quant, KV, H);
+        const uint8_t* pv = p; p += raw_bytes(quant, KV, H);
+        MC(load_group({{pq, QK, H, rk * m->qk, m->qk, 0, H / 32, 0, 1},
+                       {pk, KV, H, rk * m->kv, m->kv, 0, H / 32, m->qk, 1},
+                       {pv, KV, H, rk * m->kv, m->kv, 0, H / 32, m->qk + m->kv, 1}}, L.qkv, L.qkv_t, H, m->qk + 2 * m->kv));
         if (cfg->qkv_bias) {
             MC(dev_alloc(m, &L.qkv_bias, size_t(m->qk + 2 * m->kv)));
             const float* bq = reinterpret_cast<const float*>(p);
@@ -387,22 +418,23 @@ int32_t forge_model_create(const ForgeModelConfig* cfg, const void* weights_bin,
             if (cudaMemcpyAsync(L.qkv_bias, bq + rk * m->qk, size_t(m->qk) * 4, cudaMemcpyHostToDevice, st) != cudaSuccess ||
                 cudaMemcpyAsync(L.qkv_bias + m->qk, bk + rk * m->kv, size_t(m->kv) * 4, cudaMemcpyHostToDevice, st) != cudaSuccess ||
                 cudaMemcpyAsync(L.qkv_bias + m->qk + m->kv, bv + rk * m->kv, size_t(m->kv) * 4, cudaMemcpyHostToDevice, st) != cudaSuccess) {
-                set_error("bias upload failed"); cudaFree(stage); return fail(FORGE_ERR_CUDA);
+                set_error("bias upload failed"); cudaFree(stage); cudaFree(d_rowsrc); return fail(FORGE_ERR_CUDA);
             }
             p += size_t(QK + 2 * KV) * 4;
         }
-        MC(alloc_qweight(m, L.o, quant, m->qk, H));
-        MC(upload_pack(p, H, QK, 0, H, rk * (m->qk / 32), m->qk / 32, L.o, 0, 1)); p += raw_bytes(quant, H, QK);
+        MC(load_group({{p, H, QK, 0, H, rk * (m->qk / 32), m->qk / 32, 0, 1}}, L.o, L.o_t, m->qk, H)); p += raw_bytes(quant, H, QK);
         MC(upload_f32(&L.ffn_norm, H, p)); p += size_t(H) * 4;
-        MC(alloc_qweight(m, L.gateup, quant, H, 2 * m->ff));
-        MC(upload_pack(p, FF, H, rk * m->ff, m->ff, 0, H / 32, L.gateup, 0, 2)); p += raw_bytes(quant, FF, H);
-        MC(upload_pack(p, FF, H, rk * m->ff, m->ff, 0, H / 32, L.gateup, 1, 2)); p += raw_bytes(quant, FF, H);
-        MC(alloc_qweight(m, L.down, quant, m->ff, H));
-        MC(upload_pack(p, H, FF, 0, H, rk * (m->ff / 32), m->ff / 32, L.down, 0, 1)); p += raw_bytes(quant, H, FF);
+        const uint8_t* pg = p; p += raw_bytes(quant, FF, H);
+        const uint8_t* pu = p; p += raw_bytes(quant, FF, H);
+        MC(load_group({{pg, FF, H, rk * m->ff, m->ff, 0, H / 32, 0, 2}, {pu, FF, H, rk * m->ff, m->ff, 0, H / 32, 1, 2}},
+                      L.gateup, L.gateup_t, H, 2 * m->ff));
+        MC(load_group({{p, H, FF, 0, H, rk * (m->ff / 32), m->ff / 32, 0, 1}}, L.down, L.down_t, m->ff, H)); p += raw_bytes(quant, H, FF);
     }
     MC(upload_f32(&m->final_norm, H, p)); p += size_t(H) * 4;
-    MC(alloc_qweight(m, m->lm_head, quant, H, cfg->vocab_size));
-    MC(upload_pack(p, cfg->vocab_size, H, 0, cfg->vocab_size, 0, H / 32, m->lm_head, 0, 1));
+    MC(load_group({{p, cfg->vocab_size, H, 0, cfg->vocab_size, 0, H / 32, 0, 1}}, m->lm_head, m->lm_head_t, H, cfg->vocab_size));
+    MC(dev_alloc(m, &m->d_err, 1));
+    if (cudaMemsetAsync(m->d_err, 0, sizeof(int), st) != cudaSuccess) { set_error("memset failed"); cudaFree(stage); cudaFree(d_rowsrc); return fail(FORGE_ERR_CUDA); }
+    cudaFree(d_rowsrc);
     cudaFree(stage);
     // RoPE table with the host libm, f32 (emit.rs:502-519)
     {

@@ -69,7 +69,21 @@ def dequantize(quant: int, raw: np.ndarray, n: int) -> np.ndarray:
     return (np.concatenate([lo, hi], axis=1).astype(np.float32) * d).reshape(-1)[:n]
 
 
+_native = None
+
+
 def quantize(quant: int, x: np.ndarray) -> np.ndarray:
+    """Quantise with the library's host quantisers (multithreaded C++) when the shared object is
+    built, else with the numpy statements above; the two are bit-identical (tests/)."""
+    global _native
+    if _native is None:
+        try:
+            from . import runtime
+            _native = runtime
+        except Exception:
+            _native = False
+    if _native:
+        return _native.quantize_q8_0(x) if quant == 8 else _native.quantize_q4_0(x, True)
     return quantize_q8_0(x) if quant == 8 else quantize_q4_0(x)
 
 
