@@ -23,47 +23,85 @@ int32_t need_device() {
     return FORGE_OK;
 }
 
+}  // namespace
+
+// A projection repacked once into both kernel layouts (see forge_packed_create).
+struct ForgePacked {
+    QWeight soa;
+    QTiled tiled;
+    int* err = nullptr;
+    GemvSplit split;
+};
+
+namespace {
+
+int32_t packed_build(int quant, const uint8_t* w, int K, int N, cudaStream_t st, ForgePacked* pk) {
+    const int BS = quant == FORGE_Q8_0 ? 34 : 18;
+    pk->soa.K = K; pk->soa.N = N; pk->soa.quant = quant;
+    pk->tiled.K = K; pk->tiled.N = N; pk->tiled.quant = quant; pk->tiled.bands = (N + 127) / 128;
+    FORGE_CUDA(cudaMalloc(&pk->soa.qs, size_t(N) * pk->soa.qs_row_bytes()));
+    FORGE_CUDA(cudaMalloc(&pk->soa.d, size_t(N) * (K / 32) * sizeof(__half)));
+    FORGE_CUDA(cudaMalloc(&pk->tiled.data, qtiled_bytes(quant, K, N)));
+    FORGE_CUDA(cudaMalloc(&pk->err, sizeof(int)));
+    FORGE_CUDA(cudaMemsetAsync(pk->err, 0, sizeof(int), st));
+    FORGE_TRY(pack_rows(w, quant, K, 0, N, 0, K / 32, pk->soa, 0, 1, st));
+    if (pk->tiled.bands * 128 < kGemvSplitRows) {
+        FORGE_CUDA(cudaMalloc(&pk->split.scratch, sizeof(float) * kGemvMaxSlices * size_t(pk->tiled.bands) * 128));
+        FORGE_CUDA(cudaMalloc(&pk->split.tickets, sizeof(int) * size_t(pk->tiled.bands) * 8));
+        FORGE_CUDA(cudaMemsetAsync(pk->split.tickets, 0, sizeof(int) * size_t(pk->tiled.bands) * 8, st));
+        pk->split.max_slices = kGemvMaxSlices;
+    }
+    std::vector<const uint8_t*> rows(size_t(pk->tiled.bands) * 128, nullptr);
+    for (int r = 0; r < N; ++r) rows[r] = w + size_t(r) * (K / 32) * BS;
+    const uint8_t** tab = nullptr;
+    FORGE_CUDA(cudaMalloc(&tab, rows.size() * sizeof(uint8_t*)));
+    cudaError_t e = cudaMemcpyAsync(tab, rows.data(), rows.size() * sizeof(uint8_t*), cudaMemcpyHostToDevice, st);
+    int32_t rc = e == cudaSuccess ? tile_pack(tab, pk->tiled, st) : FORGE_ERR_CUDA;
+    cudaStreamSynchronize(st);
+    cudaFree(tab);
+    if (e != cudaSuccess) set_error("row table upload failed: %s", cudaGetErrorString(e));
+    return rc;
+}
+
+void packed_free(ForgePacked* pk) {
+    if (!pk) return;
+    cudaFree(pk->soa.qs); cudaFree(pk->soa.d); cudaFree(pk->tiled.data); cudaFree(pk->err); cudaFree(pk->split.scratch); cudaFree(pk->split.tickets);
+    delete pk;
+}
+
+int32_t matmul_packed(float* out, int32_t m, const float* in, const ForgePacked* pk, cudaStream_t st, bool check_err) {
+    const int K = pk->soa.K;
+    if (m < FORGE_PREFILL_BATCH_THRESHOLD) {  // per-token path: the streaming GEMV, f32-exact up to summation order
+        GemvArgs ga;
+        ga.x = in; ga.out = out; ga.batch = m;
+        FORGE_TRY(gemv_tc(pk->tiled, EPI_STORE, ga, pk->split, pk->err, st));
+        if (check_err) {
+            int herr = 0;
+            FORGE_CUDA(cudaMemcpyAsync(&herr, pk->err, sizeof(int), cudaMemcpyDeviceToHost, st));
+            FORGE_CUDA(cudaStreamSynchronize(st));
+            if (herr) { set_error("gemv: a bounded device-side wait gave up"); return FORGE_ERR_TIMEOUT; }
+        }
+        return FORGE_OK;
+    }
+    AsyncBuf a16(st), a16lo(st);
+    FORGE_CUDA(a16.alloc(size_t(m) * K * sizeof(__half)));
+    FORGE_CUDA(a16lo.alloc(size_t(m) * K * sizeof(__half)));
+    FORGE_TRY(f32_to_f16(static_cast<__half*>(a16.p), static_cast<__half*>(a16lo.p), in, size_t(m) * K, st));
+    return gemm_f16a(out, static_cast<const __half*>(a16.p), static_cast<const __half*>(a16lo.p), pk->soa, m, nullptr, st);
+}
+
 int32_t matmul_mat(int quant, float* out, int32_t m, const float* in, const uint8_t* w, int32_t K, int32_t N, void* stream) {
     FORGE_TRY(need_device());
     if (!out || !in || !w || m < 0 || K <= 0 || N <= 0) { set_error("bad argument to forge_matmul_mat"); return FORGE_ERR_INVALID_ARG; }
     if (K % 32) { set_error("K=%d must be a multiple of 32", K); return FORGE_ERR_SHAPE; }
     if (m == 0) return FORGE_OK;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    const int BS = quant == FORGE_Q8_0 ? 34 : 18;
-    if (m < FORGE_PREFILL_BATCH_THRESHOLD) {  // per-token path: the streaming GEMV, f32-exact up to summation order
-        QTiled qt;
-        qt.K = K; qt.N = N; qt.quant = quant; qt.row_tiles = (N + 15) / 16;
-        AsyncBuf td(st), tab(st), err(st);
-        FORGE_CUDA(td.alloc(qtiled_bytes(quant, K, N)));
-        FORGE_CUDA(tab.alloc(size_t(qt.row_tiles) * 16 * sizeof(uint8_t*)));
-        FORGE_CUDA(err.alloc(sizeof(int)));
-        FORGE_CUDA(cudaMemsetAsync(err.p, 0, sizeof(int), st));
-        std::vector<const uint8_t*> rows(size_t(qt.row_tiles) * 16, nullptr);
-        for (int r = 0; r < N; ++r) rows[r] = w + size_t(r) * (K / 32) * BS;
-        FORGE_CUDA(cudaMemcpyAsync(tab.p, rows.data(), rows.size() * sizeof(uint8_t*), cudaMemcpyHostToDevice, st));
-        FORGE_CUDA(cudaStreamSynchronize(st));  // `rows` leaves scope
-        qt.data = static_cast<uint8_t*>(td.p);
-        FORGE_TRY(tile_pack(static_cast<const uint8_t* const*>(tab.p), qt, st));
-        GemvArgs ga;
-        ga.x = in; ga.out = out; ga.batch = m;
-        FORGE_TRY(gemv_tc(qt, EPI_STORE, ga, static_cast<int*>(err.p), st));
-        int herr = 0;
-        FORGE_CUDA(cudaMemcpyAsync(&herr, err.p, sizeof(int), cudaMemcpyDeviceToHost, st));
-        FORGE_CUDA(cudaStreamSynchronize(st));
-        if (herr) { set_error("gemv: a bounded device-side wait gave up"); return FORGE_ERR_TIMEOUT; }
-        return FORGE_OK;
-    }
-    QWeight qw;
-    qw.K = K; qw.N = N; qw.quant = quant;
-    AsyncBuf qs(st), d(st), a16(st), a16lo(st);
-    FORGE_CUDA(qs.alloc(size_t(N) * qw.qs_row_bytes()));
-    FORGE_CUDA(d.alloc(size_t(N) * (K / 32) * sizeof(__half)));
-    qw.qs = static_cast<uint8_t*>(qs.p); qw.d = static_cast<__half*>(d.p);
-    FORGE_TRY(pack_rows(w, quant, K, 0, N, 0, K / 32, qw, 0, 1, st));
-    FORGE_CUDA(a16.alloc(size_t(m) * K * sizeof(__half)));
-    FORGE_CUDA(a16lo.alloc(size_t(m) * K * sizeof(__half)));
-    FORGE_TRY(f32_to_f16(static_cast<__half*>(a16.p), static_cast<__half*>(a16lo.p), in, size_t(m) * K, st));
-    return gemm_f16a(out, static_cast<const __half*>(a16.p), static_cast<const __half*>(a16lo.p), qw, m, nullptr, st);
+    ForgePacked* pk = new ForgePacked();
+    int32_t rc = packed_build(quant, w, K, N, st, pk);
+    if (rc == FORGE_OK) rc = matmul_packed(out, m, in, pk, st, true);
+    cudaStreamSynchronize(st);
+    packed_free(pk);
+    return rc;
 }
 
 }  // namespace
@@ -75,6 +113,28 @@ int32_t forge_matmul_mat_q8_0(float* out, int32_t m, const float* in, const uint
 }
 int32_t forge_matmul_mat_q4_0(float* out, int32_t m, const float* in, const uint8_t* w, int32_t K, int32_t N, void* stream) {
     return matmul_mat(FORGE_Q4_0, out, m, in, w, K, N, stream);
+}
+
+int32_t forge_packed_create(int32_t quant, const uint8_t* w, int32_t K, int32_t N, void* stream, ForgePacked** out) {
+    FORGE_TRY(need_device());
+    if (!out) { set_error("null out pointer"); return FORGE_ERR_INVALID_ARG; }
+    *out = nullptr;
+    if (!w || K <= 0 || N <= 0 || (quant != FORGE_Q8_0 && quant != FORGE_Q4_0)) { set_error("bad argument to forge_packed_create"); return FORGE_ERR_INVALID_ARG; }
+    if (K % 32) { set_error("K=%d must be a multiple of 32", K); return FORGE_ERR_SHAPE; }
+    ForgePacked* pk = new ForgePacked();
+    int32_t rc = packed_build(quant, w, K, N, static_cast<cudaStream_t>(stream), pk);
+    if (rc != FORGE_OK) { packed_free(pk); return rc; }
+    *out = pk;
+    return FORGE_OK;
+}
+
+void forge_packed_destroy(ForgePacked* pk) { packed_free(pk); }
+
+int32_t forge_matmul_mat_packed(float* out, int32_t m, const float* in, const ForgePacked* w, void* stream) {
+    FORGE_TRY(need_device());
+    if (!out || !in || !w || m < 0) { set_error("bad argument to forge_matmul_mat_packed"); return FORGE_ERR_INVALID_ARG; }
+    if (m == 0) return FORGE_OK;
+    return matmul_packed(out, m, in, w, static_cast<cudaStream_t>(stream), false);
 }
 
 int32_t forge_rms_norm(float* out, const float* in, const float* weight, int32_t rows, int32_t n, float eps, void* stream) {

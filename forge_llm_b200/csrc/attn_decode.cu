@@ -63,36 +63,44 @@ __global__ void __launch_bounds__(kThreads) attn_decode_kernel(DecParams p) {
                 q[g][4] = x1.x; q[g][5] = x1.y; q[g][6] = x1.z; q[g][7] = x1.w;
             }
         }
-        for (int base = t_begin + warp * RPW; base < t_end; base += PARTS) {
-            const int t = base + seg;
-            const bool valid = t < t_end;
-            float kf[8], vf[8];
+        constexpr int UNR = 4;  // positions per segment whose K/V loads are issued before any use
+        for (int base = t_begin + warp * RPW; base < t_end; base += PARTS * UNR) {
+            uint4 kr[UNR], vr[UNR];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) { kf[i] = 0.f; vf[i] = 0.f; }
-            if (valid && act) {
-                const int lp = t / FORGE_KV_PAGE;
-                const size_t row = seq_base + size_t(pt ? pt[lp] : lp) * FORGE_KV_PAGE + t % FORGE_KV_PAGE;
-                const size_t off = row * kvd + kvh * HD + sl * 8;
-                uint4 kr = *reinterpret_cast<const uint4*>(a.k_pool + off);
-                uint4 vr = *reinterpret_cast<const uint4*>(a.v_pool + off);
-                unpack8(kr, kf);
-                unpack8(vr, vf);
+            for (int u = 0; u < UNR; ++u) {
+                const int t = base + u * PARTS + seg;
+                kr[u] = make_uint4(0, 0, 0, 0);
+                vr[u] = make_uint4(0, 0, 0, 0);
+                if (t < t_end && act) {
+                    const int lp = t / FORGE_KV_PAGE;
+                    const size_t row = seq_base + size_t(pt ? pt[lp] : lp) * FORGE_KV_PAGE + t % FORGE_KV_PAGE;
+                    const size_t off = row * kvd + kvh * HD + sl * 8;
+                    kr[u] = __ldg(reinterpret_cast<const uint4*>(a.k_pool + off));
+                    vr[u] = __ldg(reinterpret_cast<const uint4*>(a.v_pool + off));
+                }
             }
 #pragma unroll
-            for (int g = 0; g < kGC; ++g) {
-                float s = 0.f;
+            for (int u = 0; u < UNR; ++u) {
+                const bool valid = (base + u * PARTS + seg) < t_end;
+                float kf[8], vf[8];
+                unpack8(kr[u], kf);
+                unpack8(vr[u], vf);
 #pragma unroll
-                for (int i = 0; i < 8; ++i) s += q[g][i] * kf[i];
+                for (int g = 0; g < kGC; ++g) {
+                    float s = 0.f;
 #pragma unroll
-                for (int o = W / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-                s *= p.scale;
-                if (valid && g < gc) {
-                    float mn = fmaxf(mi[g], s);
-                    float es = expf(mi[g] - mn), pr = expf(s - mn);
-                    mi[g] = mn;
-                    li[g] = li[g] * es + pr;
+                    for (int i = 0; i < 8; ++i) s += q[g][i] * kf[i];
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) acc[g][i] = acc[g][i] * es + pr * vf[i];
+                    for (int o = W / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+                    s *= p.scale;
+                    if (valid && g < gc) {
+                        float mn = fmaxf(mi[g], s);
+                        float es = expf(mi[g] - mn), pr = expf(s - mn);
+                        mi[g] = mn;
+                        li[g] = li[g] * es + pr;
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) acc[g][i] = acc[g][i] * es + pr * vf[i];
+                    }
                 }
             }
         }

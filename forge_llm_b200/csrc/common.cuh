@@ -81,14 +81,24 @@ struct GemvArgs {
 // {8 x half2 block scales}{quant bytes in MMA-fragment order}, K-major inside a 16-row band.
 struct QTiled {
     uint8_t* data = nullptr;
-    int K = 0, N = 0, quant = 0, row_tiles = 0;  // row_tiles = ceil(N/16); padding rows are zero
+    int K = 0, N = 0, quant = 0, bands = 0;  // bands = ceil(N/128); padding rows are zero
 };
+// Scratch for the split-K form of the GEMV (used when a matrix has fewer 128-row bands than SMs):
+// partial sums [max_slices][bands*128] and one self-resetting ticket per 16-row tile.
+struct GemvSplit {
+    float* scratch = nullptr;
+    int* tickets = nullptr;
+    int max_slices = 0;
+};
+int gemv_slices(const QTiled& w, const GemvSplit& sp, int sms, int batch);
+constexpr int kGemvMaxSlices = 16;
+constexpr int kGemvSplitRows = 148 * 128;  // split only happens below this many (padded) rows
 size_t qtiled_bytes(int quant, int K, int N);
-// row_src_dev[r] (device array of row_tiles*16 device pointers): first raw GGUF block of the K
+// row_src_dev[r] (device array of bands*128 device pointers): first raw GGUF block of the K
 // slice of destination row r, or null for a padding row
 int32_t tile_pack(const uint8_t* const* row_src_dev, QTiled& dst, cudaStream_t st);
 // err: device int set to 1 if a bounded wait inside the kernel gave up (may be null)
-int32_t gemv_tc(const QTiled& w, GemvEpilogue epi, const GemvArgs& a, int* err, cudaStream_t st);
+int32_t gemv_tc(const QTiled& w, GemvEpilogue epi, const GemvArgs& a, const GemvSplit& sp, int* err, cudaStream_t st);
 
 // ------------------------------------------------------------------ elementwise
 int32_t rms_norm_f32(float* out, const float* in, const float* w, int rows, int n, float eps, cudaStream_t st);
@@ -105,6 +115,9 @@ int32_t kv_append_contig(__half* kc, __half* vc, const float* k, const float* v,
 int32_t qkv_post(const float* qkv, int m, int base_pos, const float* bias, const float* rope, __half* q16,
                  __half* k_pool, __half* v_pool, const int32_t* page_row, int qk, int kv, int hd, cudaStream_t st);
 int32_t argmax_last(uint32_t* result, const float* logits, int n, int batch, cudaStream_t st);
+// many-CTA form; sval/sidx: [batch][kArgmaxSlices] scratch, ticket: [batch] zero-initialised counters
+constexpr int kArgmaxSlices = 148;
+int32_t argmax_slices(uint32_t* result, const float* logits, int n, int batch, float* sval, int* sidx, int* ticket, cudaStream_t st);
 int32_t f32_to_f16(__half* out, __half* lo, const float* in, size_t n, cudaStream_t st);
 int32_t step_advance(int32_t* seq_len, int batch, int32_t* step, cudaStream_t st);
 int32_t gather_rows_f16(float* out, const __half* pool, const int32_t* page_row, int len, int kvd, cudaStream_t st);

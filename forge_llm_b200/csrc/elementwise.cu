@@ -144,6 +144,60 @@ __global__ void argmax_kernel(uint32_t* result, const float* logits, int n) {
     }
 }
 
+// Two-stage variant for large vocabularies: every CTA scans a slice, the last CTA to finish (atomic
+// ticket) reduces the per-CTA winners with the same tie rule.  scratch: [batch][gridDim.x] pairs.
+__global__ void argmax_slices_kernel(uint32_t* result, const float* logits, int n, float* sval, int* sidx, int* ticket) {
+    __shared__ float bv[32];
+    __shared__ int bi[32];
+    __shared__ int s_last;
+    const int b = blockIdx.y, nb = gridDim.x;
+    const float* x = logits + size_t(b) * n;
+    const int per = (n + nb - 1) / nb, lo = blockIdx.x * per, hi = min(n, lo + per);
+    float best = -INFINITY;
+    int idx = -1;
+    auto better = [](float v, int i, float bv_, int bi_) { return i >= 0 && (bi_ < 0 || v > bv_ || (v == bv_ && i > bi_)); };
+    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+        float v = x[i];
+        if (better(v, i, best, idx)) { best = v; idx = i; }
+    }
+    auto block_reduce = [&]() {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+            if (better(ov, oi, best, idx)) { best = ov; idx = oi; }
+        }
+        int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+        __syncthreads();
+        if (lane == 0) { bv[warp] = best; bi[warp] = idx; }
+        __syncthreads();
+        if (threadIdx.x == 0)
+            for (int w = 1; w < nw; ++w)
+                if (better(bv[w], bi[w], best, idx)) { best = bv[w]; idx = bi[w]; }
+    };
+    block_reduce();
+    if (threadIdx.x == 0) {
+        sval[b * nb + blockIdx.x] = best;
+        sidx[b * nb + blockIdx.x] = idx;
+        __threadfence();
+        int old = atomicAdd(ticket + b, 1);
+        s_last = (old == nb - 1);
+        if (s_last) ticket[b] = 0;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    best = -INFINITY;
+    idx = -1;
+    for (int i = threadIdx.x; i < nb; i += blockDim.x) {
+        float v = __ldcg(sval + b * nb + i);
+        int vi = __ldcg(sidx + b * nb + i);
+        if (better(v, vi, best, idx)) { best = v; idx = vi; }
+    }
+    block_reduce();
+    if (threadIdx.x == 0) result[b] = uint32_t(idx < 0 ? 0 : idx);
+}
+
 __global__ void f32_to_f16_kernel(__half* out, __half* lo, const float* in, size_t n) {
     for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < n; i += size_t(gridDim.x) * blockDim.x) store_split(out, lo, i, in[i]);
 }
@@ -230,6 +284,12 @@ int32_t qkv_post(const float* qkv, int m, int base_pos, const float* bias, const
 }
 int32_t argmax_last(uint32_t* result, const float* logits, int n, int batch, cudaStream_t st) {
     argmax_kernel<<<batch, 1024, 0, st>>>(result, logits, n);
+    FORGE_LAUNCH_CHECK();
+    return FORGE_OK;
+}
+int32_t argmax_slices(uint32_t* result, const float* logits, int n, int batch, float* sval, int* sidx, int* ticket, cudaStream_t st) {
+    dim3 grid(kArgmaxSlices, batch);
+    argmax_slices_kernel<<<grid, 256, 0, st>>>(result, logits, n, sval, sidx, ticket);
     FORGE_LAUNCH_CHECK();
     return FORGE_OK;
 }

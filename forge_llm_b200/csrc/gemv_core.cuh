@@ -1,0 +1,368 @@
+// Device-side core of the streaming decode GEMV, shared by the stand-alone kernel (gemv_tc.cu)
+// and the whole-step decode kernel (decode_mega.cu).
+//
+// One CTA = 16 consumer warps + 1 producer warp.  The producer lane issues 1-D bulk copies
+// (cp.async.bulk, mbarrier completion) of "chunks" - runs of k-blocks of one 128-row band of the
+// tiled weight layout - into a ring of shared-memory stages.  Two consumer warps share each of
+// the band's eight 16-row tiles (even / odd k-blocks) and turn every 16 x 32 tile into one
+// integer tensor-core product (mma.sync m16n8k32, s8/u8 x s8 -> s32) against the activation held
+// in shared memory as four balanced base-128 digits of a 28-bit fixed-point value; digit sums
+// are scaled by the f16 block scale and accumulated in f32.  See gemv_tc.cu for the layout.
+#pragma once
+
+#include "common.cuh"
+
+namespace forge {
+namespace core {
+
+constexpr int kBandTiles = 8;                        // 16-row tiles per 128-row band
+constexpr int kConsumerWarps = 16;                   // two warps per row tile (even / odd k-blocks of a chunk)
+constexpr int kCT = kConsumerWarps * 32;             // consumer threads
+constexpr int kThreads = (kConsumerWarps + 1) * 32;  // + one producer warp
+constexpr int kStages = 8;
+constexpr int kMaxKB = 352;                          // K <= 11264
+constexpr uint32_t kSpinLimit = 1u << 24;
+
+template <int QUANT> struct Tile {
+    static constexpr int BYTES = (QUANT == FORGE_Q4_0) ? 288 : 544;
+    static constexpr int CHUNK_KB = (QUANT == FORGE_Q4_0) ? 8 : 4;          // k-blocks per pipeline stage
+    static constexpr int STAGE_BYTES = BYTES * CHUNK_KB * kBandTiles;       // 18432 / 17408
+};
+
+// ------------------------------------------------------------------ PTX helpers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// bounded wait: returns false when the limit ran out (the caller records an error and goes on)
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t addr = smem_u32(bar);
+    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+        uint32_t done;
+        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+                     : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+// D(16x8, s32) = A(16x32, row) * B(32x8, s8, col) + C, A unsigned (Q4_0 nibbles) or signed (Q8_0).
+// Not volatile: independent tiles interleave.
+__device__ __forceinline__ void imma16832_u8(int (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void imma16832_s8(int (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void csync() { asm volatile("bar.sync 1, %0;" ::"n"(kCT) : "memory"); }
+
+// chunk range [c0, c1) of slice s when `chunks` chunks are cut into `slices` near-equal slices
+__device__ __forceinline__ void slice_range(int chunks, int slices, int s, int& c0, int& c1) {
+    c0 = int((long(chunks) * s) / slices);
+    c1 = int((long(chunks) * (s + 1)) / slices);
+}
+
+// One GEMV ("phase") as the kernels see it.
+struct Phase {
+    const uint8_t* w;      // tiled weights
+    int K, N, kb, bands;   // kb = K/32, bands = ceil(N/128)
+    int slices;            // K slices per band (1 = no split)
+    int units;             // bands * slices
+    int rot;               // unit u is served by CTA (u + rot) % gridDim.x
+    int epi;               // GemvEpilogue
+    float* scratch;        // [slices][bands*128] partial sums (slices > 1)
+    int* tickets;          // [bands*8] zero-initialised, self-resetting (slices > 1)
+    GemvArgs a;
+};
+
+// Shared-memory state of the pipeline; `cc` counts chunks and must advance identically in the
+// producer and in every consumer warp.
+struct Shared {
+    uint64_t full_bar[kStages], empty_bar[kStages];
+    float part[32];
+    float pair[kBandTiles][16];
+    int err;
+};
+
+// first unit of CTA `cta` and the stride between its units
+__device__ __forceinline__ int first_unit(const Phase& ph, int cta, int grid) {
+    int r = (cta - ph.rot) % grid;
+    return r < 0 ? r + grid : r;
+}
+
+// ---- producer side: issue all chunks of this CTA's units of one phase (one batch row)
+template <int QUANT>
+__device__ __forceinline__ bool produce_phase(const Phase& ph, Shared& sh, unsigned char* ring, int& cc) {
+    using T = Tile<QUANT>;
+    const int chunks_per_band = (ph.kb + T::CHUNK_KB - 1) / T::CHUNK_KB;
+    for (int u = first_unit(ph, blockIdx.x, gridDim.x); u < ph.units; u += gridDim.x) {
+        const int band = u / ph.slices;
+        int c0, c1;
+        slice_range(chunks_per_band, ph.slices, u % ph.slices, c0, c1);
+        for (int c = c0; c < c1; ++c, ++cc) {
+            const int st = cc % kStages, use = cc / kStages;
+            if (use > 0 && !mbar_wait(&sh.empty_bar[st], (use - 1) & 1)) { atomicExch(&sh.err, 1); return false; }
+            if (*reinterpret_cast<volatile int*>(&sh.err)) return false;
+            const int kb0 = c * T::CHUNK_KB;
+            const int nkb = min(T::CHUNK_KB, ph.kb - kb0);
+            const uint32_t bytes = uint32_t(nkb) * kBandTiles * T::BYTES;
+            mbar_expect_tx(&sh.full_bar[st], bytes);
+            bulk_g2s(ring + size_t(st) * T::STAGE_BYTES, ph.w + (size_t(band) * ph.kb + kb0) * kBandTiles * T::BYTES, bytes, &sh.full_bar[st]);
+        }
+    }
+    return true;
+}
+
+// ---- consumer side, step 1: stage one activation row as int8 digit fragments.
+// xf: for k-block kb, digit column c (0..3), quad lane t: uint2 {digits of k = 4t..4t+3, of k = 16+4t..+3}
+// (the B fragment of m16n8k32).  Pass 1 copies x (coalesced; through L2 when `cg`, for data written by
+// other CTAs of the same kernel) into the fragment area as plain floats and reduces sum(x^2) and max|x|;
+// pass 2 converts in place: the 32 floats of a k-block and its 4 x 4 x 8-byte fragments occupy the same
+// 128 bytes, and the four threads of a k-block sit in one warp.  Returns 1/scale.  All consumer warps call it.
+template <int QUANT, bool CG>
+__device__ __forceinline__ float stage_activation(uint2* xf, int4* xoff, Shared& sh, const float* x, int K,
+                                                  const float* norm_w, float eps) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int KB = K / 32;
+    float* xraw = reinterpret_cast<float*>(xf);
+    csync();  // the previous contents are no longer read
+    float ss = 0.f, mx = 0.f;
+    for (int e = tid * 4; e < K; e += kCT * 4) {
+        float4 v = CG ? __ldcg(reinterpret_cast<const float4*>(x + e)) : *reinterpret_cast<const float4*>(x + e);
+        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        if (norm_w) {
+            const float4 nw = *reinterpret_cast<const float4*>(norm_w + e);
+            mx = fmaxf(fmaxf(mx, fmaxf(fabsf(v.x * nw.x), fabsf(v.y * nw.y))), fmaxf(fabsf(v.z * nw.z), fabsf(v.w * nw.w)));
+        } else {
+            mx = fmaxf(fmaxf(mx, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
+        }
+        *reinterpret_cast<float4*>(xraw + e) = v;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) { ss += __shfl_xor_sync(0xffffffffu, ss, o); mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o)); }
+    if (lane == 0) { sh.part[warp] = ss; sh.part[16 + warp] = mx; }
+    csync();
+    float s2 = 0.f, m2 = 0.f;
+#pragma unroll
+    for (int w = 0; w < kConsumerWarps; ++w) { s2 += sh.part[w]; m2 = fmaxf(m2, sh.part[16 + w]); }
+    const float inv = norm_w ? 1.0f / sqrtf(s2 / float(K) + eps) : 1.0f;
+    m2 *= inv;
+    // exact power-of-two scale that puts max|x| * 2^s in [2^25, 2^26): 28-bit signed fixed point
+    float sc = 1.0f;
+    if (m2 > 0.f && m2 < 3.0e38f) { int ex = 0; frexpf(m2, &ex); sc = ldexpf(1.0f, 26 - ex); }
+    for (int i0 = 0; i0 < KB * 4; i0 += kCT) {
+        const int i = i0 + tid;
+        const bool on = i < KB * 4;
+        const int kbi = i >> 2, tt = i & 3;
+        int xi[8];
+        if (on) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int k = kbi * 32 + h * 16 + 4 * tt + j;
+                    float xv = xraw[k];
+                    if (norm_w) xv = xv * inv * norm_w[k];
+                    xi[h * 4 + j] = __float2int_rn(xv * sc);
+                }
+        }
+        __syncwarp();  // all four readers of a k-block are done before it is overwritten
+        int dsum[4] = {0, 0, 0, 0};
+        if (on) {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                uint32_t w2[2] = {0u, 0u};
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                    // balanced base-128 digit in [-64, 63]; the last column takes what is left
+                    const int dgt = (c < 3) ? (((xi[q] + 64) & 127) - 64) : xi[q];
+                    xi[q] = (xi[q] - dgt) >> 7;
+                    dsum[c] += dgt;
+                    w2[q >> 2] |= uint32_t(dgt & 0xFF) << (8 * (q & 3));
+                }
+                xf[(kbi * 4 + c) * 4 + tt] = make_uint2(w2[0], w2[1]);
+            }
+        }
+        if (QUANT == FORGE_Q4_0) {
+            // Nibbles enter the product unsigned: rows g as n = q + 8, rows g+8 as 16 n (high nibble in
+            // place).  The accumulators start at -8 * sum(digits) and -128 * sum(digits).
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                dsum[c] += __shfl_xor_sync(0xffffffffu, dsum[c], 1);
+                dsum[c] += __shfl_xor_sync(0xffffffffu, dsum[c], 2);
+            }
+            if (on && tt == 0) {
+                xoff[2 * kbi] = make_int4(-8 * dsum[0], -8 * dsum[1], -128 * dsum[0], -128 * dsum[1]);
+                xoff[2 * kbi + 1] = make_int4(-8 * dsum[2], -8 * dsum[3], -128 * dsum[2], -128 * dsum[3]);
+            }
+        }
+    }
+    csync();
+    return 1.0f / sc;
+}
+
+// ---- epilogue of one finished output row (runtime-selected fusion)
+__device__ __forceinline__ void epilogue_row(const Phase& ph, int b, int row, float v, float partner) {
+    if (row >= ph.N) return;
+    const GemvArgs& a = ph.a;
+    if (ph.epi == EPI_STORE) {
+        a.out[size_t(b) * ph.N + row] = v;
+    } else if (ph.epi == EPI_RESID) {
+        a.out[size_t(b) * ph.N + row] = __ldcg(a.resid + size_t(b) * ph.N + row) + v;
+    } else if (ph.epi == EPI_SILU) {
+        if ((row & 1) == 0)  // rows interleaved at pack time: 2j = gate_j, 2j+1 = up_j
+            a.out[size_t(b) * (ph.N / 2) + (row >> 1)] = (v / (1.0f + expf(-v))) * partner;
+    } else if ((row & 1) == 0) {  // EPI_QKV: the thread of the even row handles the (even, odd) pair
+        float q0 = v, q1 = partner;
+        if (a.bias) { q0 += a.bias[row]; q1 += a.bias[row + 1]; }
+        const int pos = a.seq_len[b];
+        const int qk = a.qk, kv = a.kv, hd = a.head_dim;
+        int col = row, region = 0;
+        if (col >= qk) { col -= qk; region = 1; }
+        if (region == 1 && col >= kv) { col -= kv; region = 2; }
+        if (region < 2) {
+            const float2 cs = reinterpret_cast<const float2*>(a.rope)[size_t(pos) * (hd / 2) + (col % hd) / 2];
+            const float r0 = q0 * cs.x - q1 * cs.y, r1 = q0 * cs.y + q1 * cs.x;
+            q0 = r0; q1 = r1;
+        }
+        if (region == 0) {
+            *reinterpret_cast<float2*>(a.q_out + size_t(b) * qk + col) = make_float2(q0, q1);
+        } else {
+            const int page = a.page_table[size_t(b) * a.pages_per_seq + pos / FORGE_KV_PAGE];
+            __half* pool = region == 1 ? a.k_pool : a.v_pool;
+            *reinterpret_cast<__half2*>(pool + (size_t(page) * FORGE_KV_PAGE + pos % FORGE_KV_PAGE) * kv + col) =
+                __floats2half2_rn(q0, q1);
+        }
+    }
+}
+
+// ---- consumer side, step 2: all units of this CTA for one phase and one batch row.
+// `on_row(row, value)` is called by the finishing thread after the epilogue (used by the whole-step
+// kernel to track the arg-max of the logits); pass a no-op otherwise.
+template <int QUANT, typename RowHook>
+__device__ __forceinline__ void consume_phase(const Phase& ph, Shared& sh, const unsigned char* ring, const uint2* xf,
+                                              const int4* xoff, float unscale, int b, int& cc, RowHook on_row) {
+    using T = Tile<QUANT>;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int r8 = warp & (kBandTiles - 1), khalf = (warp >> 3) & 1;
+    const int KB = ph.kb;
+    const int chunks_per_band = (KB + T::CHUNK_KB - 1) / T::CHUNK_KB;
+    for (int u = first_unit(ph, blockIdx.x, gridDim.x); u < ph.units; u += gridDim.x) {
+        const int band = u / ph.slices, slice = u % ph.slices;
+        int c0, c1;
+        slice_range(chunks_per_band, ph.slices, slice, c0, c1);
+        // per-lane accumulators: rows g / g+8 of this warp's row tile x digit columns 2t / 2t+1
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int c = c0; c < c1; ++c, ++cc) {
+            const int st = cc % kStages, use = cc / kStages;
+            if (!mbar_wait(&sh.full_bar[st], use & 1)) atomicExch(&sh.err, 1);
+            const int kb0 = c * T::CHUNK_KB;
+            const int nkb = min(T::CHUNK_KB, KB - kb0);
+            const unsigned char* base = ring + size_t(st) * T::STAGE_BYTES + size_t(r8) * T::BYTES;
+            auto tile = [&](int j) {  // k-block kb0 + j of this warp's row tile
+                const unsigned char* tp = base + size_t(j) * (kBandTiles * T::BYTES);
+                // B fragment: digit column (g & 3); lanes g >= 4 duplicate columns whose results are never read
+                const uint2 bx = xf[((kb0 + j) * 4 + (g & 3)) * 4 + t];
+                const float2 d = __half22float2(*reinterpret_cast<const __half2*>(tp + g * 4));
+                int cf[4];
+                uint32_t a[4];
+                if (QUANT == FORGE_Q4_0) {
+                    const uint2 wq = *reinterpret_cast<const uint2*>(tp + 32 + lane * 8);
+                    a[0] = wq.x & 0x0F0F0F0Fu; a[1] = wq.x & 0xF0F0F0F0u;
+                    a[2] = wq.y & 0x0F0F0F0Fu; a[3] = wq.y & 0xF0F0F0F0u;
+                    const int4 xo = xoff[2 * (kb0 + j) + (t & 1)];
+                    cf[0] = xo.x; cf[1] = xo.y; cf[2] = xo.z; cf[3] = xo.w;
+                    imma16832_u8(cf, a, bx.x, bx.y);
+                } else {
+                    const uint4 wq = *reinterpret_cast<const uint4*>(tp + 32 + lane * 16);
+                    a[0] = wq.x; a[1] = wq.y; a[2] = wq.z; a[3] = wq.w;
+                    cf[0] = cf[1] = cf[2] = cf[3] = 0;
+                    imma16832_s8(cf, a, bx.x, bx.y);
+                }
+                acc[0] += d.x * float(cf[0]); acc[1] += d.x * float(cf[1]);
+                acc[2] += d.y * float(cf[2]); acc[3] += d.y * float(cf[3]);
+            };
+            if (nkb == T::CHUNK_KB) {  // full chunk: straight-line code, the tiles' loads and MMAs interleave
+#pragma unroll
+                for (int j = 0; j < T::CHUNK_KB / 2; ++j) tile(2 * j + khalf);
+            } else {
+                for (int j = khalf; j < nkb; j += 2) tile(j);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sh.empty_bar[st]);
+        }
+        // ---- the warp's part of this unit is complete: combine digits (quad lanes 0 and 1)
+        const float wgt = (t == 0) ? 1.0f : 16384.0f;  // lane 0: digits 0,1; lane 1: digits 2,3
+        const float w1 = (QUANT == FORGE_Q4_0) ? wgt * 0.0625f : wgt;  // Q4_0 rows g+8 were carried as 16 n
+        float v0 = (acc[0] + 128.0f * acc[1]) * wgt, v1 = (acc[2] + 128.0f * acc[3]) * w1;
+        v0 += __shfl_xor_sync(0xffffffffu, v0, 1);
+        v1 += __shfl_xor_sync(0xffffffffu, v1, 1);
+        // the two warps of a row tile (even / odd k-blocks) meet here: the odd one hands over its sums
+        if (khalf == 1 && t == 0) { sh.pair[r8][g] = v0; sh.pair[r8][g + 8] = v1; }
+        asm volatile("bar.sync %0, 64;" ::"r"(2 + r8) : "memory");
+        if (khalf == 1) {
+            asm volatile("bar.sync %0, 64;" ::"r"(2 + r8) : "memory");  // pair[] consumed
+            continue;
+        }
+        v0 += sh.pair[r8][g];
+        v1 += sh.pair[r8][g + 8];
+        asm volatile("bar.sync %0, 64;" ::"r"(2 + r8) : "memory");
+        v0 *= unscale;
+        v1 *= unscale;
+        const int rt = band * kBandTiles + r8;
+        const int row0 = rt * 16 + g;  // and row0 + 8
+        bool finish = true;
+        if (ph.slices > 1) {
+            // split K: publish this slice's partial sums; the last slice to arrive adds all of them
+            const size_t npad = size_t(ph.bands) * 128;
+            if (t == 0) {
+                ph.scratch[size_t(slice) * npad + row0] = v0;
+                ph.scratch[size_t(slice) * npad + row0 + 8] = v1;
+            }
+            __threadfence();
+            __syncwarp();
+            int old = 0;
+            if (lane == 0) old = atomicAdd(ph.tickets + rt, 1);
+            old = __shfl_sync(0xffffffffu, old, 0);
+            finish = (old == ph.slices - 1);
+            if (finish) {
+                __threadfence();
+                if (lane == 0) ph.tickets[rt] = 0;  // ready for the next use
+                v0 = 0.f; v1 = 0.f;
+                for (int s = 0; s < ph.slices; ++s) {  // fixed order: independent of which slice came last
+                    v0 += __ldcg(ph.scratch + size_t(s) * npad + row0);
+                    v1 += __ldcg(ph.scratch + size_t(s) * npad + row0 + 8);
+                }
+            }
+        }
+        // pair partners (rows r^1) live in the neighbouring quad
+        const float o0 = __shfl_xor_sync(0xffffffffu, v0, 4), o1 = __shfl_xor_sync(0xffffffffu, v1, 4);
+        if (finish && t == 0) {
+            epilogue_row(ph, b, row0, v0, o0);
+            epilogue_row(ph, b, row0 + 8, v1, o1);
+            on_row(row0, v0);
+            on_row(row0 + 8, v1);
+        }
+    }
+}
+
+// shared-memory bytes of the ring plus the activation fragments for the largest K in use
+template <int QUANT>
+inline size_t dyn_smem_bytes(int max_kb) { return size_t(kStages) * Tile<QUANT>::STAGE_BYTES + size_t(max_kb) * 128; }
+
+}  // namespace core
+}  // namespace forge

@@ -58,6 +58,7 @@ struct ForgeModel {
     QWeight lm_head;
     QTiled lm_head_t;
     int* d_err = nullptr;  // set by a kernel whose bounded wait gave up
+    GemvSplit split;       // split-K scratch shared by the decode GEMVs (one launch at a time on the stream)
     float* rope = nullptr;  // [max_seq][hd/2]{cos,sin}
     int max_seq = 0;
     std::vector<void*> allocs;
@@ -71,6 +72,7 @@ struct ForgeModel {
     int dec_batch = 0;
     float* d_hidden = nullptr; float* d_q = nullptr; float* d_attn = nullptr; float* d_act = nullptr; float* d_logits = nullptr;
     uint32_t* d_tok = nullptr; uint32_t* d_hist = nullptr; int hist_cap = 0; int32_t* d_step = nullptr;
+    float* d_amax_val = nullptr; int* d_amax_idx = nullptr; int* d_amax_ticket = nullptr;
     // parity trace
     bool trace_on = false; float* trace = nullptr; size_t trace_cap = 0; int trace_rows = 0;
     // timing of the last generate call
@@ -151,6 +153,10 @@ int32_t ensure_decode_scratch(ForgeModel* m, int batch) {
     FORGE_TRY(dev_alloc(m, &m->d_act, b * m->ff));
     FORGE_TRY(dev_alloc(m, &m->d_logits, b * m->V));
     FORGE_TRY(dev_alloc(m, &m->d_tok, b));
+    FORGE_TRY(dev_alloc(m, &m->d_amax_val, b * kArgmaxSlices));
+    FORGE_TRY(dev_alloc(m, &m->d_amax_idx, b * kArgmaxSlices));
+    FORGE_TRY(dev_alloc(m, &m->d_amax_ticket, b));
+    FORGE_CUDA(cudaMemsetAsync(m->d_amax_ticket, 0, sizeof(int) * b, m->stream));
     if (!m->d_step) { FORGE_TRY(dev_alloc(m, &m->d_step, 1)); }
     m->dec_batch = batch;
     return FORGE_OK;
@@ -230,7 +236,7 @@ int32_t prefill_seq(ForgeModel* m, ForgeKV* kv, int seq, const uint32_t* tokens_
     // final rms_norm + lm_head on the last row only (emit.rs:5439-5482): exact-f32 GEMV
     GemvArgs ga;
     ga.x = m->p_hidden + size_t(n - 1) * m->h; ga.norm_w = m->final_norm; ga.eps = c.rms_norm_eps; ga.out = m->d_logits; ga.batch = 1;
-    FORGE_TRY(gemv_tc(m->lm_head_t, EPI_STORE, ga, m->d_err, st));
+    FORGE_TRY(gemv_tc(m->lm_head_t, EPI_STORE, ga, m->split, m->d_err, st));
     kv->len[seq] += n;
     return FORGE_OK;
 }
@@ -251,26 +257,26 @@ int32_t decode_launches(ForgeModel* m, ForgeKV* kv, int batch, bool greedy, bool
         a.bias = L.qkv_bias; a.rope = m->rope; a.q_out = m->d_q; a.k_pool = kp; a.v_pool = vp;
         a.page_table = kv->d_page_table; a.seq_len = kv->d_seq_len; a.pages_per_seq = kv->pages_per_seq;
         a.qk = m->qk; a.kv = m->kv; a.head_dim = m->hd;
-        FORGE_TRY(gemv_tc(L.qkv_t, EPI_QKV, a, m->d_err, st));
+        FORGE_TRY(gemv_tc(L.qkv_t, EPI_QKV, a, m->split, m->d_err, st));
         AttnDecodeArgs da{m->d_attn, m->d_q, kp, vp, kv->d_page_table, kv->pages_per_seq, kv->d_seq_len, 0,
                           batch, m->nq, m->nkv, m->hd, kv->max_seq, kv->attn_ws, kv->attn_counters, kv->splits};
         FORGE_TRY(attn_decode(da, st));
         GemvArgs o;
         o.x = m->d_attn; o.out = m->d_hidden; o.resid = m->d_hidden; o.batch = batch;
-        FORGE_TRY(gemv_tc(L.o_t, EPI_RESID, o, m->d_err, st));
+        FORGE_TRY(gemv_tc(L.o_t, EPI_RESID, o, m->split, m->d_err, st));
         GemvArgs g;
         g.x = m->d_hidden; g.norm_w = L.ffn_norm; g.eps = c.rms_norm_eps; g.out = m->d_act; g.batch = batch;
-        FORGE_TRY(gemv_tc(L.gateup_t, EPI_SILU, g, m->d_err, st));
+        FORGE_TRY(gemv_tc(L.gateup_t, EPI_SILU, g, m->split, m->d_err, st));
         GemvArgs d;
         d.x = m->d_act; d.out = m->d_hidden; d.resid = m->d_hidden; d.batch = batch;
-        FORGE_TRY(gemv_tc(L.down_t, EPI_RESID, d, m->d_err, st));
+        FORGE_TRY(gemv_tc(L.down_t, EPI_RESID, d, m->split, m->d_err, st));
         if (m->trace_on)
             FORGE_CUDA(cudaMemcpyAsync(m->trace + size_t(l) * batch * m->h, m->d_hidden, sizeof(float) * batch * m->h, cudaMemcpyDeviceToDevice, st));
     }
     GemvArgs lm;
     lm.x = m->d_hidden; lm.norm_w = m->final_norm; lm.eps = c.rms_norm_eps; lm.out = m->d_logits; lm.batch = batch;
-    FORGE_TRY(gemv_tc(m->lm_head_t, EPI_STORE, lm, m->d_err, st));
-    if (greedy) FORGE_TRY(argmax_last(m->d_tok, m->d_logits, m->V, batch, st));
+    FORGE_TRY(gemv_tc(m->lm_head_t, EPI_STORE, lm, m->split, m->d_err, st));
+    if (greedy) FORGE_TRY(argmax_slices(m->d_tok, m->d_logits, m->V, batch, m->d_amax_val, m->d_amax_idx, m->d_amax_ticket, st));
     FORGE_TRY(step_advance(kv->d_seq_len, batch, m->d_step, st));
     return FORGE_OK;
 }
@@ -364,7 +370,7 @@ int32_t forge_model_create(const ForgeModelConfig* cfg, const void* weights_bin,
     const int BS = quant == FORGE_Q8_0 ? 34 : 18;
     size_t max_raw = std::max({raw_bytes(quant, size_t(cfg->vocab_size), H), 2 * raw_bytes(quant, FF, H) + 64,
                                raw_bytes(quant, QK, H) + 2 * raw_bytes(quant, KV, H) + 64});
-    size_t max_rows = std::max({size_t(cfg->vocab_size), size_t(2 * FF), size_t(QK + 2 * KV), size_t(H)}) + 16;
+    size_t max_rows = std::max({size_t(cfg->vocab_size), size_t(2 * FF), size_t(QK + 2 * KV), size_t(H)}) + 128;
     uint8_t* stage = nullptr;
     const uint8_t** d_rowsrc = nullptr;
     if (cudaMalloc(&stage, max_raw) != cudaSuccess || cudaMalloc(&d_rowsrc, max_rows * sizeof(uint8_t*)) != cudaSuccess) {
@@ -381,9 +387,9 @@ int32_t forge_model_create(const ForgeModelConfig* cfg, const void* weights_bin,
     struct Part { const uint8_t* host; int N_full, K_full, row0, rows, blk0, blks, dst_row0, step; };
     auto load_group = [&](const std::vector<Part>& parts, QWeight& soa, QTiled& tiled, int K_local, int N_local) -> int32_t {
         FORGE_TRY(alloc_qweight(m, soa, quant, K_local, N_local));
-        tiled.K = K_local; tiled.N = N_local; tiled.quant = quant; tiled.row_tiles = (N_local + 15) / 16;
+        tiled.K = K_local; tiled.N = N_local; tiled.quant = quant; tiled.bands = (N_local + 127) / 128;
         FORGE_TRY(dev_alloc(m, &tiled.data, qtiled_bytes(quant, K_local, N_local)));
-        std::vector<const uint8_t*> table(size_t(tiled.row_tiles) * 16, nullptr);
+        std::vector<const uint8_t*> table(size_t(tiled.bands) * 128, nullptr);
         size_t off = 0;
         for (const Part& pt : parts) {
             const size_t bytes = raw_bytes(quant, pt.N_full, pt.K_full);
@@ -433,6 +439,10 @@ int32_t forge_model_create(const ForgeModelConfig* cfg, const void* weights_bin,
     MC(upload_f32(&m->final_norm, H, p)); p += size_t(H) * 4;
     MC(load_group({{p, cfg->vocab_size, H, 0, cfg->vocab_size, 0, H / 32, 0, 1}}, m->lm_head, m->lm_head_t, H, cfg->vocab_size));
     MC(dev_alloc(m, &m->d_err, 1));
+    MC(dev_alloc(m, &m->split.scratch, size_t(kGemvMaxSlices) * kGemvSplitRows));
+    MC(dev_alloc(m, &m->split.tickets, size_t(kGemvSplitRows) / 16));
+    m->split.max_slices = kGemvMaxSlices;
+    if (cudaMemsetAsync(m->split.tickets, 0, sizeof(int) * kGemvSplitRows / 16, st) != cudaSuccess) { set_error("memset failed"); cudaFree(stage); cudaFree(d_rowsrc); return fail(FORGE_ERR_CUDA); }
     if (cudaMemsetAsync(m->d_err, 0, sizeof(int), st) != cudaSuccess) { set_error("memset failed"); cudaFree(stage); cudaFree(d_rowsrc); return fail(FORGE_ERR_CUDA); }
     cudaFree(d_rowsrc);
     cudaFree(stage);
@@ -662,7 +672,7 @@ int32_t forge_generate_greedy(ForgeModel* m, ForgeKV* kv, const uint32_t* prompt
         FORGE_TRY(upload_len(kv));
     }
     // first token: sample() of the prefill logits (project.rs:722)
-    FORGE_TRY(argmax_last(m->d_tok, m->d_logits, m->V, 1, m->stream));
+    FORGE_TRY(argmax_slices(m->d_tok, m->d_logits, m->V, 1, m->d_amax_val, m->d_amax_idx, m->d_amax_ticket, m->stream));
     uint32_t first = 0;
     FORGE_CUDA(cudaMemcpyAsync(&first, m->d_tok, sizeof(uint32_t), cudaMemcpyDeviceToHost, m->stream));
     FORGE_CUDA(cudaStreamSynchronize(m->stream));

@@ -88,6 +88,15 @@ int32_t forge_matmul_mat_q8_0(float* out, int32_t m, const float* in, const uint
 int32_t forge_matmul_mat_q4_0(float* out, int32_t m, const float* in, const uint8_t* w,
                               int32_t K, int32_t N, void* stream);
 
+/* The same products on a weight repacked once: forge_packed_create converts raw GGUF blocks
+ * (device pointer, [N][K/32][block]) into the kernels' aligned layouts (same bytes per weight),
+ * forge_matmul_mat_packed then runs without any per-call repacking or allocation for m < 8
+ * (the `Weights` struct of the generated module, E:3875-3939, plays this role there). */
+typedef struct ForgePacked ForgePacked;
+int32_t forge_packed_create(int32_t quant, const uint8_t* w, int32_t K, int32_t N, void* stream, ForgePacked** out);
+void forge_packed_destroy(ForgePacked* w);
+int32_t forge_matmul_mat_packed(float* out, int32_t m, const float* in, const ForgePacked* w, void* stream);
+
 /* rms_norm(output, input, weight, eps)  E:327-334, applied to `rows` rows of n values. */
 int32_t forge_rms_norm(float* out, const float* in, const float* weight, int32_t rows, int32_t n,
                        float eps, void* stream);
