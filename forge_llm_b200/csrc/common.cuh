@@ -100,6 +100,27 @@ int32_t tile_pack(const uint8_t* const* row_src_dev, QTiled& dst, cudaStream_t s
 // err: device int set to 1 if a bounded wait inside the kernel gave up (may be null)
 int32_t gemv_tc(const QTiled& w, GemvEpilogue epi, const GemvArgs& a, const GemvSplit& sp, int* err, cudaStream_t st);
 
+// ------------------------------------------------------------------ whole-step decode kernel (batch 1)
+namespace core { struct Phase; }
+struct MegaParams {
+    const core::Phase* phases;   // device array: per layer {QKV, O, gate/up, down}, then lm_head
+    int num_layers, h;
+    // attention of sequence 0
+    float* q; float* attn_out;
+    const __half* k_pool; const __half* v_pool; size_t layer_stride;
+    const int32_t* page_table; const int32_t* seq_len;
+    int nq, nkv, hd, attn_splits;
+    float* attn_ws; int* attn_tickets;
+    // token in / out, bookkeeping updated by the last CTA
+    const float* embed; float* hidden;
+    uint32_t* tok; uint32_t* hist; int32_t* step; int32_t* seq_len_mut;
+    int greedy;
+    float* amax_val; int* amax_idx; int* amax_ticket;
+    unsigned* bar; int* err;
+};
+// launches the cooperative kernel on `grid` CTAs (one per SM); max_kb = largest K/32 of any phase
+int32_t decode_step_mega(const MegaParams& p, int quant, int hd, int max_kb, int grid, cudaStream_t st);
+
 // ------------------------------------------------------------------ elementwise
 int32_t rms_norm_f32(float* out, const float* in, const float* w, int rows, int n, float eps, cudaStream_t st);
 // fp16 outputs come as a hi/lo pair when `lo` is given: hi = fp16(x), lo = fp16(x - hi)

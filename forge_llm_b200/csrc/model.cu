@@ -11,7 +11,7 @@
 #include <string>
 #include <vector>
 
-#include "common.cuh"
+#include "gemv_core.cuh"
 
 namespace forge {
 
@@ -68,6 +68,7 @@ struct ForgeModel {
     __half* p_attn16 = nullptr; float* p_gu = nullptr; __half* p_act16 = nullptr; uint32_t* p_tokens = nullptr;
     __half* p_normed_lo = nullptr; __half* p_attn16_lo = nullptr; __half* p_act16_lo = nullptr;
     int gemm_passes = 3;  // 3: split-precision prefill GEMMs (default); 1: single fp16 pass
+    bool use_mega = true; // batch-1 decode through the whole-step kernel
     // decode scratch (per batch row)
     int dec_batch = 0;
     float* d_hidden = nullptr; float* d_q = nullptr; float* d_attn = nullptr; float* d_act = nullptr; float* d_logits = nullptr;
@@ -89,6 +90,9 @@ struct ForgeKV {
     std::vector<int32_t> h_page_table; std::vector<int> free_pages; std::vector<int> pages_used; std::vector<int> len;
     float* attn_ws = nullptr; int* attn_counters = nullptr; int splits = 1;
     cudaGraphExec_t graph = nullptr; int graph_batch = 0; bool graph_greedy = false;
+    // whole-step decode kernel (batch 1, sequence 0)
+    core::Phase* d_phases = nullptr; int mega_grid = 0, mega_max_kb = 0, mega_splits = 1;
+    float* mega_ws = nullptr; int* mega_tickets = nullptr; unsigned* d_bar = nullptr;
 };
 
 namespace {
@@ -287,8 +291,25 @@ int32_t decode_prepare(ForgeKV* kv, int batch) {
     return FORGE_OK;
 }
 
+// batch 1 on sequence 0: the whole step is one persistent kernel
+int32_t decode_step_one_kernel(ForgeModel* m, ForgeKV* kv, bool greedy) {
+    MegaParams p;
+    p.phases = kv->d_phases; p.num_layers = m->cfg.num_layers; p.h = m->h;
+    p.q = m->d_q; p.attn_out = m->d_attn; p.k_pool = kv->k_pool; p.v_pool = kv->v_pool; p.layer_stride = kv->layer_stride;
+    p.page_table = kv->d_page_table; p.seq_len = kv->d_seq_len;
+    p.nq = m->nq; p.nkv = m->nkv; p.hd = m->hd; p.attn_splits = kv->mega_splits;
+    p.attn_ws = kv->mega_ws; p.attn_tickets = kv->mega_tickets;
+    p.embed = m->embed; p.hidden = m->d_hidden;
+    p.tok = m->d_tok; p.hist = greedy ? m->d_hist : nullptr; p.step = m->d_step; p.seq_len_mut = kv->d_seq_len;
+    p.greedy = greedy ? 1 : 0;
+    p.amax_val = m->d_amax_val; p.amax_idx = m->d_amax_idx; p.amax_ticket = m->d_amax_ticket;
+    p.bar = kv->d_bar; p.err = m->d_err;
+    return decode_step_mega(p, m->cfg.quant, m->hd, kv->mega_max_kb, kv->mega_grid, m->stream);
+}
+
 int32_t decode_step_graph(ForgeModel* m, ForgeKV* kv, int batch, bool greedy) {
     if (m->trace_on) return decode_launches(m, kv, batch, greedy, greedy);
+    if (batch == 1 && m->use_mega && kv->d_phases && kv->mega_grid <= kArgmaxSlices) return decode_step_one_kernel(m, kv, greedy);
     if (!kv->graph || kv->graph_batch != batch || kv->graph_greedy != greedy) {
         if (kv->graph) { cudaGraphExecDestroy(kv->graph); kv->graph = nullptr; }
         cudaGraph_t g = nullptr;
@@ -507,6 +528,54 @@ int32_t forge_kv_create(ForgeModel* m, int32_t max_seq, int32_t batch, ForgeKV**
     if (cudaMalloc(&kv->attn_ws, sizeof(float) * attn_decode_ws_floats(batch, m->nq, m->hd, kv->splits)) != cudaSuccess ||
         cudaMalloc(&kv->attn_counters, sizeof(int) * batch * m->nkv) != cudaSuccess) { set_error("attention workspace allocation failed"); return fail(FORGE_ERR_CUDA); }
     cudaMemsetAsync(kv->attn_counters, 0, sizeof(int) * batch * m->nkv, m->stream);
+    {   // phase table of the whole-step decode kernel
+        std::vector<core::Phase> ph(size_t(4) * m->cfg.num_layers + 1);
+        int rot = 0, max_kb = 0;
+        auto fill = [&](core::Phase& P, const QTiled& w, int epi) {
+            P.w = w.data; P.K = w.K; P.N = w.N; P.kb = w.K / 32; P.bands = w.bands;
+            P.slices = gemv_slices(w, m->split, sms, 1);
+            P.units = w.bands * P.slices;
+            P.rot = rot;
+            rot = (rot + P.units) % sms;
+            P.epi = epi; P.scratch = m->split.scratch; P.tickets = m->split.tickets;
+            P.a = GemvArgs();
+            max_kb = std::max(max_kb, P.kb);
+        };
+        if (ensure_decode_scratch(m, 1) != FORGE_OK) return fail(FORGE_ERR_CUDA);
+        for (int l = 0; l < m->cfg.num_layers; ++l) {
+            ForgeLayer& L = m->layers[l];
+            core::Phase& q = ph[4 * l];
+            fill(q, L.qkv_t, EPI_QKV);
+            q.a.x = m->d_hidden; q.a.norm_w = L.attn_norm; q.a.eps = m->cfg.rms_norm_eps; q.a.bias = L.qkv_bias; q.a.rope = m->rope;
+            q.a.q_out = m->d_q; q.a.k_pool = kv->k_pool + size_t(l) * kv->layer_stride; q.a.v_pool = kv->v_pool + size_t(l) * kv->layer_stride;
+            q.a.page_table = kv->d_page_table; q.a.seq_len = kv->d_seq_len; q.a.pages_per_seq = kv->pages_per_seq;
+            q.a.qk = m->qk; q.a.kv = m->kv; q.a.head_dim = m->hd;
+            core::Phase& o = ph[4 * l + 1];
+            fill(o, L.o_t, EPI_RESID);
+            o.a.x = m->d_attn; o.a.out = m->d_hidden; o.a.resid = m->d_hidden;
+            core::Phase& g = ph[4 * l + 2];
+            fill(g, L.gateup_t, EPI_SILU);
+            g.a.x = m->d_hidden; g.a.norm_w = L.ffn_norm; g.a.eps = m->cfg.rms_norm_eps; g.a.out = m->d_act;
+            core::Phase& d = ph[4 * l + 3];
+            fill(d, L.down_t, EPI_RESID);
+            d.a.x = m->d_act; d.a.out = m->d_hidden; d.a.resid = m->d_hidden;
+        }
+        core::Phase& lm = ph.back();
+        fill(lm, m->lm_head_t, EPI_STORE);
+        lm.a.x = m->d_hidden; lm.a.norm_w = m->final_norm; lm.a.eps = m->cfg.rms_norm_eps; lm.a.out = m->d_logits;
+        kv->mega_grid = sms;
+        kv->mega_max_kb = max_kb;
+        kv->mega_splits = std::max(1, std::min({(sms + m->nkv - 1) / m->nkv, 64}));
+        if (cudaMalloc(&kv->d_phases, ph.size() * sizeof(core::Phase)) != cudaSuccess ||
+            cudaMalloc(&kv->mega_ws, sizeof(float) * size_t(m->nq) * kv->mega_splits * (m->hd + 2)) != cudaSuccess ||
+            cudaMalloc(&kv->mega_tickets, sizeof(int) * m->nkv) != cudaSuccess || cudaMalloc(&kv->d_bar, sizeof(unsigned)) != cudaSuccess) {
+            set_error("decode kernel tables allocation failed"); return fail(FORGE_ERR_CUDA);
+        }
+        cudaMemcpyAsync(kv->d_phases, ph.data(), ph.size() * sizeof(core::Phase), cudaMemcpyHostToDevice, m->stream);
+        cudaMemsetAsync(kv->mega_tickets, 0, sizeof(int) * m->nkv, m->stream);
+        cudaMemsetAsync(kv->d_bar, 0, sizeof(unsigned), m->stream);
+        if (cudaStreamSynchronize(m->stream) != cudaSuccess) { set_error("KV init failed"); return fail(FORGE_ERR_CUDA); }
+    }
     if (cudaStreamSynchronize(m->stream) != cudaSuccess) { set_error("KV init failed"); return fail(FORGE_ERR_CUDA); }
     *out = kv;
     return FORGE_OK;
@@ -532,6 +601,7 @@ void forge_kv_destroy(ForgeKV* kv) {
     if (kv->graph) cudaGraphExecDestroy(kv->graph);
     cudaFree(kv->k_pool); cudaFree(kv->v_pool); cudaFree(kv->d_page_table); cudaFree(kv->d_seq_len);
     cudaFree(kv->attn_ws); cudaFree(kv->attn_counters);
+    cudaFree(kv->d_phases); cudaFree(kv->mega_ws); cudaFree(kv->mega_tickets); cudaFree(kv->d_bar);
     delete kv;
 }
 
