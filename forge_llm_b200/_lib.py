@@ -59,6 +59,7 @@ SIGNATURES = {
     "forge_model_destroy": (None, [vp]),
     "forge_model_stream": (vp, [vp]),
     "forge_model_set_gemm_passes": (i32, [vp, i32]),
+    "forge_model_set_decode_mode": (i32, [vp, i32]),
     "forge_kv_create": (i32, [vp, i32, i32, C.POINTER(vp)]),
     "forge_kv_reset": (i32, [vp]),
     "forge_kv_len": (i32, [vp, i32]),

@@ -38,20 +38,21 @@ namespace {
 int32_t packed_build(int quant, const uint8_t* w, int K, int N, cudaStream_t st, ForgePacked* pk) {
     const int BS = quant == FORGE_Q8_0 ? 34 : 18;
     pk->soa.K = K; pk->soa.N = N; pk->soa.quant = quant;
-    pk->tiled.K = K; pk->tiled.N = N; pk->tiled.quant = quant; pk->tiled.bands = (N + 127) / 128;
+    pk->tiled.K = K; pk->tiled.N = N; pk->tiled.quant = quant; { int dev = 0, sms = 148; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+      pk->tiled.bt = gemv_band_tiles(N, sms); pk->tiled.bands = (N + 16 * pk->tiled.bt - 1) / (16 * pk->tiled.bt); }
     FORGE_CUDA(cudaMalloc(&pk->soa.qs, size_t(N) * pk->soa.qs_row_bytes()));
     FORGE_CUDA(cudaMalloc(&pk->soa.d, size_t(N) * (K / 32) * sizeof(__half)));
-    FORGE_CUDA(cudaMalloc(&pk->tiled.data, qtiled_bytes(quant, K, N)));
+    FORGE_CUDA(cudaMalloc(&pk->tiled.data, qtiled_bytes(quant, K, N, pk->tiled.bt)));
     FORGE_CUDA(cudaMalloc(&pk->err, sizeof(int)));
     FORGE_CUDA(cudaMemsetAsync(pk->err, 0, sizeof(int), st));
     FORGE_TRY(pack_rows(w, quant, K, 0, N, 0, K / 32, pk->soa, 0, 1, st));
-    if (pk->tiled.bands * 128 < kGemvSplitRows) {
-        FORGE_CUDA(cudaMalloc(&pk->split.scratch, sizeof(float) * kGemvMaxSlices * size_t(pk->tiled.bands) * 128));
-        FORGE_CUDA(cudaMalloc(&pk->split.tickets, sizeof(int) * size_t(pk->tiled.bands) * 8));
-        FORGE_CUDA(cudaMemsetAsync(pk->split.tickets, 0, sizeof(int) * size_t(pk->tiled.bands) * 8, st));
+    if (pk->tiled.bands * 16 * pk->tiled.bt <= kGemvSplitRows) {
+        FORGE_CUDA(cudaMalloc(&pk->split.scratch, sizeof(float) * kGemvMaxSlices * size_t(pk->tiled.bands) * 16 * pk->tiled.bt));
+        FORGE_CUDA(cudaMalloc(&pk->split.tickets, sizeof(int) * size_t(pk->tiled.bands) * pk->tiled.bt));
+        FORGE_CUDA(cudaMemsetAsync(pk->split.tickets, 0, sizeof(int) * size_t(pk->tiled.bands) * pk->tiled.bt, st));
         pk->split.max_slices = kGemvMaxSlices;
     }
-    std::vector<const uint8_t*> rows(size_t(pk->tiled.bands) * 128, nullptr);
+    std::vector<const uint8_t*> rows(size_t(pk->tiled.bands) * 16 * pk->tiled.bt, nullptr);
     for (int r = 0; r < N; ++r) rows[r] = w + size_t(r) * (K / 32) * BS;
     const uint8_t** tab = nullptr;
     FORGE_CUDA(cudaMalloc(&tab, rows.size() * sizeof(uint8_t*)));

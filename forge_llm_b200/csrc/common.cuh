@@ -57,7 +57,8 @@ int32_t pack_rows(const uint8_t* raw_dev, int quant, int K_full, int row0, int r
                   QWeight& dst, int dst_row0, int row_step, cudaStream_t st);
 
 // ------------------------------------------------------------------ GEMV (decode)
-enum GemvEpilogue { EPI_STORE = 0, EPI_RESID = 1, EPI_QKV = 2, EPI_SILU = 3 };
+// EPI_PARTIAL: every K slice stores its raw partial sums at scratch[slice][row]; the reader adds them
+enum GemvEpilogue { EPI_STORE = 0, EPI_RESID = 1, EPI_QKV = 2, EPI_SILU = 3, EPI_PARTIAL = 4 };
 
 struct GemvArgs {
     const float* x = nullptr;       // [batch][K] input rows
@@ -81,7 +82,7 @@ struct GemvArgs {
 // {8 x half2 block scales}{quant bytes in MMA-fragment order}, K-major inside a 16-row band.
 struct QTiled {
     uint8_t* data = nullptr;
-    int K = 0, N = 0, quant = 0, bands = 0;  // bands = ceil(N/128); padding rows are zero
+    int K = 0, N = 0, quant = 0, bands = 0, bt = 1;  // bt row tiles per band; bands = ceil(N/(16*bt)); padding rows are zero
 };
 // Scratch for the split-K form of the GEMV (used when a matrix has fewer 128-row bands than SMs):
 // partial sums [max_slices][bands*128] and one self-resetting ticket per 16-row tile.
@@ -92,9 +93,10 @@ struct GemvSplit {
 };
 int gemv_slices(const QTiled& w, const GemvSplit& sp, int sms, int batch);
 constexpr int kGemvMaxSlices = 16;
-constexpr int kGemvSplitRows = 148 * 128;  // split only happens below this many (padded) rows
-size_t qtiled_bytes(int quant, int K, int N);
-// row_src_dev[r] (device array of bands*128 device pointers): first raw GGUF block of the K
+constexpr int kGemvSplitRows = 256 * 128;  // split only happens up to this many (padded) rows
+size_t qtiled_bytes(int quant, int K, int N, int bt);
+int gemv_band_tiles(int N, int sms);
+// row_src_dev[r] (device array of bands*16*bt device pointers): first raw GGUF block of the K
 // slice of destination row r, or null for a padding row
 int32_t tile_pack(const uint8_t* const* row_src_dev, QTiled& dst, cudaStream_t st);
 // err: device int set to 1 if a bounded wait inside the kernel gave up (may be null)
@@ -106,13 +108,12 @@ struct MegaParams {
     const core::Phase* phases;   // device array: per layer {QKV, O, gate/up, down}, then lm_head
     int num_layers, h;
     // attention of sequence 0
-    float* q; float* attn_out;
-    const __half* k_pool; const __half* v_pool; size_t layer_stride;
+    __half* k_pool; __half* v_pool; size_t layer_stride;
     const int32_t* page_table; const int32_t* seq_len;
     int nq, nkv, hd, attn_splits;
-    float* attn_ws; int* attn_tickets;
+    float* attn_ws;              // [nq][attn_splits][hd + 2] partials (m, l, acc)
     // token in / out, bookkeeping updated by the last CTA
-    const float* embed; float* hidden;
+    const float* embed; float* hidden0; float* hidden1;  // residual stream, double-buffered
     uint32_t* tok; uint32_t* hist; int32_t* step; int32_t* seq_len_mut;
     int greedy;
     float* amax_val; int* amax_idx; int* amax_ticket;

@@ -15,7 +15,7 @@
 namespace forge {
 namespace core {
 
-constexpr int kBandTiles = 8;                        // 16-row tiles per 128-row band
+constexpr int kBandTiles = 8;                        // 16-row tiles per band in the wide layout (bt = 8); bt = 1: one tile
 constexpr int kConsumerWarps = 16;                   // two warps per row tile (even / odd k-blocks of a chunk)
 constexpr int kCT = kConsumerWarps * 32;             // consumer threads
 constexpr int kThreads = (kConsumerWarps + 1) * 32;  // + one producer warp
@@ -78,15 +78,18 @@ __device__ __forceinline__ void slice_range(int chunks, int slices, int s, int& 
 // One GEMV ("phase") as the kernels see it.
 struct Phase {
     const uint8_t* w;      // tiled weights
-    int K, N, kb, bands;   // kb = K/32, bands = ceil(N/128)
+    int K, N, kb, bands;   // kb = K/32, bands = ceil(N / (16 * bt))
+    int bt;                // row tiles per band: 8 (two warps per tile) or 1 (all sixteen warps share the tile)
     int slices;            // K slices per band (1 = no split)
     int units;             // bands * slices
     int rot;               // unit u is served by CTA (u + rot) % gridDim.x
     int epi;               // GemvEpilogue
-    float* scratch;        // [slices][bands*128] partial sums (slices > 1)
-    int* tickets;          // [bands*8] zero-initialised, self-resetting (slices > 1)
+    float* scratch;        // [slices][bands*16*bt] partial sums (slices > 1 or EPI_PARTIAL)
+    int* tickets;          // [bands*bt] zero-initialised, self-resetting (slices > 1)
     GemvArgs a;
 };
+
+__device__ __host__ inline size_t phase_npad(const Phase& ph) { return size_t(ph.bands) * 16 * ph.bt; }
 
 // Shared-memory state of the pipeline; `cc` counts chunks and must advance identically in the
 // producer and in every consumer warp.
@@ -94,6 +97,7 @@ struct Shared {
     uint64_t full_bar[kStages], empty_bar[kStages];
     float part[32];
     float pair[kBandTiles][16];
+    float red[2][kConsumerWarps][16];
     int err;
 };
 
@@ -107,7 +111,8 @@ __device__ __forceinline__ int first_unit(const Phase& ph, int cta, int grid) {
 template <int QUANT>
 __device__ __forceinline__ bool produce_phase(const Phase& ph, Shared& sh, unsigned char* ring, int& cc) {
     using T = Tile<QUANT>;
-    const int chunks_per_band = (ph.kb + T::CHUNK_KB - 1) / T::CHUNK_KB;
+    const int ckb = T::CHUNK_KB * (kBandTiles / ph.bt);  // k-blocks per chunk: a chunk is always CHUNK_KB * 8 tiles
+    const int chunks_per_band = (ph.kb + ckb - 1) / ckb;
     for (int u = first_unit(ph, blockIdx.x, gridDim.x); u < ph.units; u += gridDim.x) {
         const int band = u / ph.slices;
         int c0, c1;
@@ -116,11 +121,11 @@ __device__ __forceinline__ bool produce_phase(const Phase& ph, Shared& sh, unsig
             const int st = cc % kStages, use = cc / kStages;
             if (use > 0 && !mbar_wait(&sh.empty_bar[st], (use - 1) & 1)) { atomicExch(&sh.err, 1); return false; }
             if (*reinterpret_cast<volatile int*>(&sh.err)) return false;
-            const int kb0 = c * T::CHUNK_KB;
-            const int nkb = min(T::CHUNK_KB, ph.kb - kb0);
-            const uint32_t bytes = uint32_t(nkb) * kBandTiles * T::BYTES;
+            const int kb0 = c * ckb;
+            const int nkb = min(ckb, ph.kb - kb0);
+            const uint32_t bytes = uint32_t(nkb) * ph.bt * T::BYTES;
             mbar_expect_tx(&sh.full_bar[st], bytes);
-            bulk_g2s(ring + size_t(st) * T::STAGE_BYTES, ph.w + (size_t(band) * ph.kb + kb0) * kBandTiles * T::BYTES, bytes, &sh.full_bar[st]);
+            bulk_g2s(ring + size_t(st) * T::STAGE_BYTES, ph.w + (size_t(band) * ph.kb + kb0) * ph.bt * T::BYTES, bytes, &sh.full_bar[st]);
         }
     }
     return true;
@@ -128,29 +133,59 @@ __device__ __forceinline__ bool produce_phase(const Phase& ph, Shared& sh, unsig
 
 // ---- consumer side, step 1: stage one activation row as int8 digit fragments.
 // xf: for k-block kb, digit column c (0..3), quad lane t: uint2 {digits of k = 4t..4t+3, of k = 16+4t..+3}
-// (the B fragment of m16n8k32).  Pass 1 copies x (coalesced; through L2 when `cg`, for data written by
-// other CTAs of the same kernel) into the fragment area as plain floats and reduces sum(x^2) and max|x|;
-// pass 2 converts in place: the 32 floats of a k-block and its 4 x 4 x 8-byte fragments occupy the same
-// 128 bytes, and the four threads of a k-block sit in one warp.  Returns 1/scale.  All consumer warps call it.
-template <int QUANT, bool CG>
-__device__ __forceinline__ float stage_activation(uint2* xf, int4* xoff, Shared& sh, const float* x, int K,
-                                                  const float* norm_w, float eps) {
+// (the B fragment of m16n8k32).  The row is first written as plain floats into the fragment area
+// ("fill": stage_fill_global below, or a caller's own loop), then converted in place by stage_finish:
+// the 32 floats of a k-block and its 4 x 4 x 8-byte fragments occupy the same 128 bytes, and the four
+// threads that convert a k-block sit in one warp.  All consumer warps take part in both steps.
+
+// running sum(x^2) and max|x * norm_w| of the values a thread wrote during the fill
+struct FillStat { float ss = 0.f, mx = 0.f; };
+
+__device__ __forceinline__ void fill_note(FillStat& st, const float4& v, const float* norm_w, int e) {
+    st.ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    if (norm_w) {
+        const float4 nw = *reinterpret_cast<const float4*>(norm_w + e);
+        st.mx = fmaxf(fmaxf(st.mx, fmaxf(fabsf(v.x * nw.x), fabsf(v.y * nw.y))), fmaxf(fabsf(v.z * nw.z), fabsf(v.w * nw.w)));
+    } else {
+        st.mx = fmaxf(fmaxf(st.mx, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
+    }
+}
+
+// Fill from global memory: x = base (may be null) + the sum of `nparts` partial vectors
+// (parts + s * pstride), added in slice order.  With `writeback`, element group i (4 floats) is also
+// stored by CTA i % gridDim.x, so the summed vector exists once in global memory afterwards.
+// CG: read through L2 (data written by other CTAs of the same kernel).
+template <bool CG>
+__device__ __forceinline__ FillStat stage_fill_global(uint2* xf, const float* base, const float* parts, int nparts, size_t pstride,
+                                                     float* writeback, int K, const float* norm_w) {
+    float* xraw = reinterpret_cast<float*>(xf);
+    FillStat st;
+    csync();  // the previous contents of the fragment area are no longer read
+    for (int e = threadIdx.x * 4; e < K; e += kCT * 4) {
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (base) v = CG ? __ldcg(reinterpret_cast<const float4*>(base + e)) : *reinterpret_cast<const float4*>(base + e);
+        if (nparts > 0) {
+            float4 pv[kGemvMaxSlices];
+#pragma unroll
+            for (int s = 0; s < kGemvMaxSlices; ++s)
+                pv[s] = (s < nparts) ? __ldcg(reinterpret_cast<const float4*>(parts + size_t(s) * pstride + e)) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int s = 0; s < kGemvMaxSlices; ++s) { v.x += pv[s].x; v.y += pv[s].y; v.z += pv[s].z; v.w += pv[s].w; }
+            if (writeback && ((e >> 2) % int(gridDim.x)) == int(blockIdx.x)) *reinterpret_cast<float4*>(writeback + e) = v;
+        }
+        fill_note(st, v, norm_w, e);
+        *reinterpret_cast<float4*>(xraw + e) = v;
+    }
+    return st;
+}
+
+// Convert the filled row in place; returns 1/scale.
+template <int QUANT>
+__device__ __forceinline__ float stage_finish(uint2* xf, int4* xoff, Shared& sh, FillStat st, int K, const float* norm_w, float eps) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int KB = K / 32;
     float* xraw = reinterpret_cast<float*>(xf);
-    csync();  // the previous contents are no longer read
-    float ss = 0.f, mx = 0.f;
-    for (int e = tid * 4; e < K; e += kCT * 4) {
-        float4 v = CG ? __ldcg(reinterpret_cast<const float4*>(x + e)) : *reinterpret_cast<const float4*>(x + e);
-        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
-        if (norm_w) {
-            const float4 nw = *reinterpret_cast<const float4*>(norm_w + e);
-            mx = fmaxf(fmaxf(mx, fmaxf(fabsf(v.x * nw.x), fabsf(v.y * nw.y))), fmaxf(fabsf(v.z * nw.z), fabsf(v.w * nw.w)));
-        } else {
-            mx = fmaxf(fmaxf(mx, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
-        }
-        *reinterpret_cast<float4*>(xraw + e) = v;
-    }
+    float ss = st.ss, mx = st.mx;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) { ss += __shfl_xor_sync(0xffffffffu, ss, o); mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o)); }
     if (lane == 0) { sh.part[warp] = ss; sh.part[16 + warp] = mx; }
@@ -163,21 +198,27 @@ __device__ __forceinline__ float stage_activation(uint2* xf, int4* xoff, Shared&
     // exact power-of-two scale that puts max|x| * 2^s in [2^25, 2^26): 28-bit signed fixed point
     float sc = 1.0f;
     if (m2 > 0.f && m2 < 3.0e38f) { int ex = 0; frexpf(m2, &ex); sc = ldexpf(1.0f, 26 - ex); }
+    // balanced base-128 digits without carries: with y = x + 64 * (1 + 128 + 128^2 + 128^3), digit c of x
+    // is ((y >> 7c) & 127) - 64 for c < 3 and (y >> 21) - 64 for the last one
+    constexpr int kBias = 64 * (1 + 128 + 128 * 128 + 128 * 128 * 128);
     for (int i0 = 0; i0 < KB * 4; i0 += kCT) {
         const int i = i0 + tid;
         const bool on = i < KB * 4;
         const int kbi = i >> 2, tt = i & 3;
-        int xi[8];
+        int y[8];
         if (on) {
+            const float4 r0 = *reinterpret_cast<const float4*>(xraw + kbi * 32 + 4 * tt);
+            const float4 r1 = *reinterpret_cast<const float4*>(xraw + kbi * 32 + 16 + 4 * tt);
+            float xv[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+            if (norm_w) {
+                const float4 n0 = *reinterpret_cast<const float4*>(norm_w + kbi * 32 + 4 * tt);
+                const float4 n1 = *reinterpret_cast<const float4*>(norm_w + kbi * 32 + 16 + 4 * tt);
+                const float nw[8] = {n0.x, n0.y, n0.z, n0.w, n1.x, n1.y, n1.z, n1.w};
 #pragma unroll
-            for (int h = 0; h < 2; ++h)
+                for (int q = 0; q < 8; ++q) xv[q] = xv[q] * inv * nw[q];
+            }
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const int k = kbi * 32 + h * 16 + 4 * tt + j;
-                    float xv = xraw[k];
-                    if (norm_w) xv = xv * inv * norm_w[k];
-                    xi[h * 4 + j] = __float2int_rn(xv * sc);
-                }
+            for (int q = 0; q < 8; ++q) y[q] = __float2int_rn(xv[q] * sc) + kBias;
         }
         __syncwarp();  // all four readers of a k-block are done before it is overwritten
         int dsum[4] = {0, 0, 0, 0};
@@ -187,9 +228,7 @@ __device__ __forceinline__ float stage_activation(uint2* xf, int4* xoff, Shared&
                 uint32_t w2[2] = {0u, 0u};
 #pragma unroll
                 for (int q = 0; q < 8; ++q) {
-                    // balanced base-128 digit in [-64, 63]; the last column takes what is left
-                    const int dgt = (c < 3) ? (((xi[q] + 64) & 127) - 64) : xi[q];
-                    xi[q] = (xi[q] - dgt) >> 7;
+                    const int dgt = ((c < 3) ? ((y[q] >> (7 * c)) & 127) : (y[q] >> 21)) - 64;
                     dsum[c] += dgt;
                     w2[q >> 2] |= uint32_t(dgt & 0xFF) << (8 * (q & 3));
                 }
@@ -212,6 +251,14 @@ __device__ __forceinline__ float stage_activation(uint2* xf, int4* xoff, Shared&
     }
     csync();
     return 1.0f / sc;
+}
+
+// the common case: one plain row from global memory
+template <int QUANT, bool CG>
+__device__ __forceinline__ float stage_activation(uint2* xf, int4* xoff, Shared& sh, const float* x, int K,
+                                                  const float* norm_w, float eps) {
+    const FillStat st = stage_fill_global<CG>(xf, x, nullptr, 0, 0, nullptr, K, norm_w);
+    return stage_finish<QUANT>(xf, xoff, sh, st, K, norm_w, eps);
 }
 
 // ---- epilogue of one finished output row (runtime-selected fusion)
@@ -258,10 +305,13 @@ __device__ __forceinline__ void consume_phase(const Phase& ph, Shared& sh, const
     using T = Tile<QUANT>;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
-    const int r8 = warp & (kBandTiles - 1), khalf = (warp >> 3) & 1;
+    const int bt = ph.bt, kparts = kConsumerWarps / bt;            // warps sharing one row tile
+    const int r8 = warp % bt, khalf = warp / bt;                    // row tile within the band, k part of this warp
     const int KB = ph.kb;
-    const int chunks_per_band = (KB + T::CHUNK_KB - 1) / T::CHUNK_KB;
-    for (int u = first_unit(ph, blockIdx.x, gridDim.x); u < ph.units; u += gridDim.x) {
+    const int ckb = T::CHUNK_KB * (kBandTiles / bt);
+    const int chunks_per_band = (KB + ckb - 1) / ckb;
+    int ui = 0;
+    for (int u = first_unit(ph, blockIdx.x, gridDim.x); u < ph.units; u += gridDim.x, ++ui) {
         const int band = u / ph.slices, slice = u % ph.slices;
         int c0, c1;
         slice_range(chunks_per_band, ph.slices, slice, c0, c1);
@@ -270,11 +320,11 @@ __device__ __forceinline__ void consume_phase(const Phase& ph, Shared& sh, const
         for (int c = c0; c < c1; ++c, ++cc) {
             const int st = cc % kStages, use = cc / kStages;
             if (!mbar_wait(&sh.full_bar[st], use & 1)) atomicExch(&sh.err, 1);
-            const int kb0 = c * T::CHUNK_KB;
-            const int nkb = min(T::CHUNK_KB, KB - kb0);
+            const int kb0 = c * ckb;
+            const int nkb = min(ckb, KB - kb0);
             const unsigned char* base = ring + size_t(st) * T::STAGE_BYTES + size_t(r8) * T::BYTES;
             auto tile = [&](int j) {  // k-block kb0 + j of this warp's row tile
-                const unsigned char* tp = base + size_t(j) * (kBandTiles * T::BYTES);
+                const unsigned char* tp = base + size_t(j) * (bt * T::BYTES);
                 // B fragment: digit column (g & 3); lanes g >= 4 duplicate columns whose results are never read
                 const uint2 bx = xf[((kb0 + j) * 4 + (g & 3)) * 4 + t];
                 const float2 d = __half22float2(*reinterpret_cast<const __half2*>(tp + g * 4));
@@ -296,11 +346,11 @@ __device__ __forceinline__ void consume_phase(const Phase& ph, Shared& sh, const
                 acc[0] += d.x * float(cf[0]); acc[1] += d.x * float(cf[1]);
                 acc[2] += d.y * float(cf[2]); acc[3] += d.y * float(cf[3]);
             };
-            if (nkb == T::CHUNK_KB) {  // full chunk: straight-line code, the tiles' loads and MMAs interleave
+            if (nkb == ckb) {  // full chunk: straight-line code, the tiles' loads and MMAs interleave
 #pragma unroll
-                for (int j = 0; j < T::CHUNK_KB / 2; ++j) tile(2 * j + khalf);
+                for (int j = 0; j < T::CHUNK_KB / 2; ++j) tile(j * kparts + khalf);
             } else {
-                for (int j = khalf; j < nkb; j += 2) tile(j);
+                for (int j = khalf; j < nkb; j += kparts) tile(j);
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&sh.empty_bar[st]);
@@ -311,24 +361,45 @@ __device__ __forceinline__ void consume_phase(const Phase& ph, Shared& sh, const
         float v0 = (acc[0] + 128.0f * acc[1]) * wgt, v1 = (acc[2] + 128.0f * acc[3]) * w1;
         v0 += __shfl_xor_sync(0xffffffffu, v0, 1);
         v1 += __shfl_xor_sync(0xffffffffu, v1, 1);
-        // the two warps of a row tile (even / odd k-blocks) meet here: the odd one hands over its sums
-        if (khalf == 1 && t == 0) { sh.pair[r8][g] = v0; sh.pair[r8][g + 8] = v1; }
-        asm volatile("bar.sync %0, 64;" ::"r"(2 + r8) : "memory");
-        if (khalf == 1) {
-            asm volatile("bar.sync %0, 64;" ::"r"(2 + r8) : "memory");  // pair[] consumed
-            continue;
+        if (bt == kBandTiles) {
+            // the two warps of a row tile (even / odd k-blocks) meet here: the odd one hands over its sums
+            if (khalf == 1 && t == 0) { sh.pair[r8][g] = v0; sh.pair[r8][g + 8] = v1; }
+            asm volatile("bar.sync %0, 64;" ::"r"(2 + r8) : "memory");
+            if (khalf == 1) {
+                asm volatile("bar.sync %0, 64;" ::"r"(2 + r8) : "memory");  // pair[] consumed
+                continue;
+            }
+            v0 += sh.pair[r8][g];
+            v1 += sh.pair[r8][g + 8];
+            asm volatile("bar.sync %0, 64;" ::"r"(2 + r8) : "memory");
+        } else {
+            // all sixteen warps worked on the same row tile: warp 0 adds their sums (double-buffered by unit
+            // parity; the next unit's barrier orders the reuse)
+            const int par = ui & 1;
+            if (t == 0) { sh.red[par][warp][g] = v0; sh.red[par][warp][g + 8] = v1; }
+            csync();
+            if (warp != 0) continue;
+            v0 = 0.f; v1 = 0.f;
+#pragma unroll
+            for (int w = 0; w < kConsumerWarps; ++w) { v0 += sh.red[par][w][g]; v1 += sh.red[par][w][g + 8]; }
         }
-        v0 += sh.pair[r8][g];
-        v1 += sh.pair[r8][g + 8];
-        asm volatile("bar.sync %0, 64;" ::"r"(2 + r8) : "memory");
         v0 *= unscale;
         v1 *= unscale;
-        const int rt = band * kBandTiles + r8;
+        const int rt = band * bt + r8;
         const int row0 = rt * 16 + g;  // and row0 + 8
         bool finish = true;
+        if (ph.epi == EPI_PARTIAL) {
+            // raw partial sums of this K slice; whoever reads them adds the slices in order
+            if (t == 0) {
+                const size_t npad = size_t(ph.bands) * 16 * bt;
+                ph.scratch[size_t(slice) * npad + row0] = v0;
+                ph.scratch[size_t(slice) * npad + row0 + 8] = v1;
+            }
+            continue;
+        }
         if (ph.slices > 1) {
             // split K: publish this slice's partial sums; the last slice to arrive adds all of them
-            const size_t npad = size_t(ph.bands) * 128;
+            const size_t npad = size_t(ph.bands) * 16 * bt;
             if (t == 0) {
                 ph.scratch[size_t(slice) * npad + row0] = v0;
                 ph.scratch[size_t(slice) * npad + row0 + 8] = v1;
@@ -342,11 +413,18 @@ __device__ __forceinline__ void consume_phase(const Phase& ph, Shared& sh, const
             if (finish) {
                 __threadfence();
                 if (lane == 0) ph.tickets[rt] = 0;  // ready for the next use
-                v0 = 0.f; v1 = 0.f;
-                for (int s = 0; s < ph.slices; ++s) {  // fixed order: independent of which slice came last
-                    v0 += __ldcg(ph.scratch + size_t(s) * npad + row0);
-                    v1 += __ldcg(ph.scratch + size_t(s) * npad + row0 + 8);
+                // all loads are issued before the first add (one L2 round trip); the sum runs in slice
+                // order, independent of which slice came last
+                float p0[kGemvMaxSlices], p1[kGemvMaxSlices];
+#pragma unroll
+                for (int s = 0; s < kGemvMaxSlices; ++s) {
+                    const bool in = s < ph.slices;
+                    p0[s] = in ? __ldcg(ph.scratch + size_t(s) * npad + row0) : 0.f;
+                    p1[s] = in ? __ldcg(ph.scratch + size_t(s) * npad + row0 + 8) : 0.f;
                 }
+                v0 = 0.f; v1 = 0.f;
+#pragma unroll
+                for (int s = 0; s < kGemvMaxSlices; ++s) { v0 += p0[s]; v1 += p1[s]; }
             }
         }
         // pair partners (rows r^1) live in the neighbouring quad

@@ -27,6 +27,8 @@
 // exactly the 34 / 18 bytes per block of the GGUF stream.  Tiles are ordered
 // [128-row band][k-block][row tile within band], so a chunk (a run of k-blocks of one band) is
 // one contiguous, 16-byte aligned bulk copy.
+#include <algorithm>
+
 #include "gemv_core.cuh"
 
 namespace forge {
@@ -77,16 +79,16 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tc_kernel(TcParams p) {
 // thread per (tile, lane): gathers the lane's A-fragment bytes from the two raw GGUF rows it owns
 // (rows g and g+8 of the 16-row tile; k = 4t..4t+3 and 16+4t..16+4t+3 of the block)
 template <int QUANT>
-__global__ void tile_pack_kernel(const uint8_t* const* __restrict__ row_src, int KB, int bands, uint8_t* __restrict__ dst) {
+__global__ void tile_pack_kernel(const uint8_t* const* __restrict__ row_src, int KB, int bands, int bt, uint8_t* __restrict__ dst) {
     constexpr int BS = QUANT == FORGE_Q8_0 ? 34 : 18;
     using T = core::Tile<QUANT>;
-    const long total = long(bands) * KB * core::kBandTiles * 32;
+    const long total = long(bands) * KB * bt * 32;
     for (long i = blockIdx.x * long(blockDim.x) + threadIdx.x; i < total; i += long(gridDim.x) * blockDim.x) {
         const int lane = int(i & 31);
-        const long tile = i >> 5;                      // ((band * KB + kb) * 8 + r8)
-        const int r8 = int(tile % core::kBandTiles);
-        const int kb = int((tile / core::kBandTiles) % KB), band = int(tile / (long(core::kBandTiles) * KB));
-        const int rt = band * core::kBandTiles + r8;
+        const long tile = i >> 5;                      // ((band * KB + kb) * bt + r8)
+        const int r8 = int(tile % bt);
+        const int kb = int((tile / bt) % KB), band = int(tile / (long(bt) * KB));
+        const int rt = band * bt + r8;
         const int g = lane >> 2, t = lane & 3;
         const uint8_t* r0 = row_src[rt * 16 + g];
         const uint8_t* r1 = row_src[rt * 16 + g + 8];
@@ -130,7 +132,7 @@ int32_t launch(const QTiled& w, GemvEpilogue epi, const GemvArgs& a, const GemvS
     using T = Tile<QUANT>;
     TcParams p;
     Phase& ph = p.ph;
-    ph.w = w.data; ph.K = w.K; ph.N = w.N; ph.kb = w.K / 32; ph.bands = w.bands; ph.a = a; ph.epi = epi; ph.rot = 0;
+    ph.w = w.data; ph.K = w.K; ph.N = w.N; ph.kb = w.K / 32; ph.bands = w.bands; ph.bt = w.bt; ph.a = a; ph.epi = epi; ph.rot = 0;
     p.err = err;
     const size_t smem = dyn_smem_bytes<QUANT>(ph.kb);
     if (smem > 220 * 1024 || ph.kb > kMaxKB) { set_error("gemv: K=%d is beyond the supported %d", w.K, kMaxKB * 32); return FORGE_ERR_SHAPE; }
@@ -150,32 +152,33 @@ int32_t launch(const QTiled& w, GemvEpilogue epi, const GemvArgs& a, const GemvS
 
 }  // namespace
 
-// K slices per band: split when a matrix has fewer bands than SMs (one batch row only: the scratch
-// holds one row), never finer than one pipeline chunk
+// K slices per band: split (ticketed cross-CTA reduction) only when the matrix has so few bands that at
+// least half of the SMs would idle; one batch row only (the scratch holds one row), never finer than one
+// pipeline chunk.
 int gemv_slices(const QTiled& w, const GemvSplit& sp, int sms, int batch) {
-    const int ck = w.quant == FORGE_Q4_0 ? 8 : 4;
-    const int chunks = (w.K / 32 + ck - 1) / ck;
-    int slices = 1;
-    if (sp.scratch && sp.tickets && w.bands < sms && batch == 1) {
-        slices = (sms + w.bands - 1) / w.bands;
-        if (slices > chunks) slices = chunks;
-        if (slices > sp.max_slices) slices = sp.max_slices;
-        if (slices < 1) slices = 1;
-    }
-    return slices;
+    const int ckb = (w.quant == FORGE_Q4_0 ? 8 : 4) * (core::kBandTiles / w.bt);
+    const int chunks = (w.K / 32 + ckb - 1) / ckb;
+    if (!sp.scratch || !sp.tickets || batch != 1 || 2 * w.bands > sms) return 1;
+    int slices = (sms + w.bands - 1) / w.bands;
+    slices = std::min({slices, chunks, sp.max_slices, kGemvMaxSlices});
+    return slices < 1 ? 1 : slices;
 }
 
-size_t qtiled_bytes(int quant, int K, int N) {
-    const size_t bands = size_t((N + 127) / 128);
-    return bands * core::kBandTiles * size_t(K / 32) * (quant == FORGE_Q4_0 ? 288 : 544);
+// Row tiles per band for an N-row matrix: the wide form (8 tiles, two warps per tile, no CTA-level
+// reduction) when there are at least four bands per SM, else one tile per band (finer units for balance).
+int gemv_band_tiles(int N, int sms) { return ((N + 127) / 128 >= 4 * sms) ? core::kBandTiles : 1; }
+
+size_t qtiled_bytes(int quant, int K, int N, int bt) {
+    const size_t bands = size_t((N + 16 * bt - 1) / (16 * bt));
+    return bands * bt * size_t(K / 32) * (quant == FORGE_Q4_0 ? 288 : 544);
 }
 
 int32_t tile_pack(const uint8_t* const* row_src_dev, QTiled& dst, cudaStream_t st) {
-    const long total = long(dst.bands) * (dst.K / 32) * core::kBandTiles * 32;
+    const long total = long(dst.bands) * (dst.K / 32) * dst.bt * 32;
     if (total == 0) return FORGE_OK;
     const int grid = int((total + 255) / 256 < 148 * 32 ? (total + 255) / 256 : 148 * 32);
-    if (dst.quant == FORGE_Q8_0) tile_pack_kernel<FORGE_Q8_0><<<grid, 256, 0, st>>>(row_src_dev, dst.K / 32, dst.bands, dst.data);
-    else tile_pack_kernel<FORGE_Q4_0><<<grid, 256, 0, st>>>(row_src_dev, dst.K / 32, dst.bands, dst.data);
+    if (dst.quant == FORGE_Q8_0) tile_pack_kernel<FORGE_Q8_0><<<grid, 256, 0, st>>>(row_src_dev, dst.K / 32, dst.bands, dst.bt, dst.data);
+    else tile_pack_kernel<FORGE_Q4_0><<<grid, 256, 0, st>>>(row_src_dev, dst.K / 32, dst.bands, dst.bt, dst.data);
     FORGE_LAUNCH_CHECK();
     return FORGE_OK;
 }

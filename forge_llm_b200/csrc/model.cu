@@ -68,9 +68,10 @@ struct ForgeModel {
     __half* p_attn16 = nullptr; float* p_gu = nullptr; __half* p_act16 = nullptr; uint32_t* p_tokens = nullptr;
     __half* p_normed_lo = nullptr; __half* p_attn16_lo = nullptr; __half* p_act16_lo = nullptr;
     int gemm_passes = 3;  // 3: split-precision prefill GEMMs (default); 1: single fp16 pass
-    bool use_mega = true; // batch-1 decode through the whole-step kernel
+    bool use_mega = false; // batch-1 decode through the whole-step kernel (forge_model_set_decode_mode)
     // decode scratch (per batch row)
     int dec_batch = 0;
+    float* d_hidden2 = nullptr;
     float* d_hidden = nullptr; float* d_q = nullptr; float* d_attn = nullptr; float* d_act = nullptr; float* d_logits = nullptr;
     uint32_t* d_tok = nullptr; uint32_t* d_hist = nullptr; int hist_cap = 0; int32_t* d_step = nullptr;
     float* d_amax_val = nullptr; int* d_amax_idx = nullptr; int* d_amax_ticket = nullptr;
@@ -92,7 +93,7 @@ struct ForgeKV {
     cudaGraphExec_t graph = nullptr; int graph_batch = 0; bool graph_greedy = false;
     // whole-step decode kernel (batch 1, sequence 0)
     core::Phase* d_phases = nullptr; int mega_grid = 0, mega_max_kb = 0, mega_splits = 1;
-    float* mega_ws = nullptr; int* mega_tickets = nullptr; unsigned* d_bar = nullptr;
+    float* mega_ws = nullptr; float* mega_scr[3] = {nullptr, nullptr, nullptr}; unsigned* d_bar = nullptr;
 };
 
 namespace {
@@ -152,6 +153,7 @@ int32_t ensure_decode_scratch(ForgeModel* m, int batch) {
     if (batch <= m->dec_batch) return FORGE_OK;
     size_t b = size_t(batch);
     FORGE_TRY(dev_alloc(m, &m->d_hidden, b * m->h));
+    FORGE_TRY(dev_alloc(m, &m->d_hidden2, b * m->h));
     FORGE_TRY(dev_alloc(m, &m->d_q, b * m->qk));
     FORGE_TRY(dev_alloc(m, &m->d_attn, b * m->qk));
     FORGE_TRY(dev_alloc(m, &m->d_act, b * m->ff));
@@ -295,11 +297,11 @@ int32_t decode_prepare(ForgeKV* kv, int batch) {
 int32_t decode_step_one_kernel(ForgeModel* m, ForgeKV* kv, bool greedy) {
     MegaParams p;
     p.phases = kv->d_phases; p.num_layers = m->cfg.num_layers; p.h = m->h;
-    p.q = m->d_q; p.attn_out = m->d_attn; p.k_pool = kv->k_pool; p.v_pool = kv->v_pool; p.layer_stride = kv->layer_stride;
+    p.k_pool = kv->k_pool; p.v_pool = kv->v_pool; p.layer_stride = kv->layer_stride;
     p.page_table = kv->d_page_table; p.seq_len = kv->d_seq_len;
     p.nq = m->nq; p.nkv = m->nkv; p.hd = m->hd; p.attn_splits = kv->mega_splits;
-    p.attn_ws = kv->mega_ws; p.attn_tickets = kv->mega_tickets;
-    p.embed = m->embed; p.hidden = m->d_hidden;
+    p.attn_ws = kv->mega_ws;
+    p.embed = m->embed; p.hidden0 = m->d_hidden; p.hidden1 = m->d_hidden2;
     p.tok = m->d_tok; p.hist = greedy ? m->d_hist : nullptr; p.step = m->d_step; p.seq_len_mut = kv->d_seq_len;
     p.greedy = greedy ? 1 : 0;
     p.amax_val = m->d_amax_val; p.amax_idx = m->d_amax_idx; p.amax_ticket = m->d_amax_ticket;
@@ -309,7 +311,7 @@ int32_t decode_step_one_kernel(ForgeModel* m, ForgeKV* kv, bool greedy) {
 
 int32_t decode_step_graph(ForgeModel* m, ForgeKV* kv, int batch, bool greedy) {
     if (m->trace_on) return decode_launches(m, kv, batch, greedy, greedy);
-    if (batch == 1 && m->use_mega && kv->d_phases && kv->mega_grid <= kArgmaxSlices) return decode_step_one_kernel(m, kv, greedy);
+    if (batch == 1 && m->use_mega && kv->d_phases && kv->mega_grid <= kArgmaxSlices && (m->nq / m->nkv) * m->hd <= 512) return decode_step_one_kernel(m, kv, greedy);
     if (!kv->graph || kv->graph_batch != batch || kv->graph_greedy != greedy) {
         if (kv->graph) { cudaGraphExecDestroy(kv->graph); kv->graph = nullptr; }
         cudaGraph_t g = nullptr;
@@ -389,6 +391,8 @@ int32_t forge_model_create(const ForgeModelConfig* cfg, const void* weights_bin,
     // group is repacked on the device into (a) the row-major split layout the prefill GEMM reads and (b) the
     // tiled layout the decode GEMV streams, then the stage is reused.
     const int BS = quant == FORGE_Q8_0 ? 34 : 18;
+    int sm_count = 148;
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device);
     size_t max_raw = std::max({raw_bytes(quant, size_t(cfg->vocab_size), H), 2 * raw_bytes(quant, FF, H) + 64,
                                raw_bytes(quant, QK, H) + 2 * raw_bytes(quant, KV, H) + 64});
     size_t max_rows = std::max({size_t(cfg->vocab_size), size_t(2 * FF), size_t(QK + 2 * KV), size_t(H)}) + 128;
@@ -408,9 +412,9 @@ int32_t forge_model_create(const ForgeModelConfig* cfg, const void* weights_bin,
     struct Part { const uint8_t* host; int N_full, K_full, row0, rows, blk0, blks, dst_row0, step; };
     auto load_group = [&](const std::vector<Part>& parts, QWeight& soa, QTiled& tiled, int K_local, int N_local) -> int32_t {
         FORGE_TRY(alloc_qweight(m, soa, quant, K_local, N_local));
-        tiled.K = K_local; tiled.N = N_local; tiled.quant = quant; tiled.bands = (N_local + 127) / 128;
-        FORGE_TRY(dev_alloc(m, &tiled.data, qtiled_bytes(quant, K_local, N_local)));
-        std::vector<const uint8_t*> table(size_t(tiled.bands) * 128, nullptr);
+        tiled.K = K_local; tiled.N = N_local; tiled.quant = quant; tiled.bt = gemv_band_tiles(N_local, sm_count); tiled.bands = (N_local + 16 * tiled.bt - 1) / (16 * tiled.bt);
+        FORGE_TRY(dev_alloc(m, &tiled.data, qtiled_bytes(quant, K_local, N_local, tiled.bt)));
+        std::vector<const uint8_t*> table(size_t(tiled.bands) * 16 * tiled.bt, nullptr);
         size_t off = 0;
         for (const Part& pt : parts) {
             const size_t bytes = raw_bytes(quant, pt.N_full, pt.K_full);
@@ -532,7 +536,7 @@ int32_t forge_kv_create(ForgeModel* m, int32_t max_seq, int32_t batch, ForgeKV**
         std::vector<core::Phase> ph(size_t(4) * m->cfg.num_layers + 1);
         int rot = 0, max_kb = 0;
         auto fill = [&](core::Phase& P, const QTiled& w, int epi) {
-            P.w = w.data; P.K = w.K; P.N = w.N; P.kb = w.K / 32; P.bands = w.bands;
+            P.w = w.data; P.K = w.K; P.N = w.N; P.kb = w.K / 32; P.bands = w.bands; P.bt = w.bt;
             P.slices = gemv_slices(w, m->split, sms, 1);
             P.units = w.bands * P.slices;
             P.rot = rot;
@@ -542,22 +546,27 @@ int32_t forge_kv_create(ForgeModel* m, int32_t max_seq, int32_t batch, ForgeKV**
             max_kb = std::max(max_kb, P.kb);
         };
         if (ensure_decode_scratch(m, 1) != FORGE_OK) return fail(FORGE_ERR_CUDA);
+        {   // raw partial sums of the K-split projections: [slices][rows padded to 128]
+            const size_t rows[3] = {size_t((m->qk + 2 * m->kv + 127) / 128) * 128, size_t((m->h + 127) / 128) * 128, size_t((m->h + 127) / 128) * 128};
+            for (int i = 0; i < 3; ++i)
+                if (cudaMalloc(&kv->mega_scr[i], sizeof(float) * kGemvMaxSlices * rows[i]) != cudaSuccess) { set_error("decode scratch allocation failed"); return fail(FORGE_ERR_CUDA); }
+        }
         for (int l = 0; l < m->cfg.num_layers; ++l) {
             ForgeLayer& L = m->layers[l];
             core::Phase& q = ph[4 * l];
-            fill(q, L.qkv_t, EPI_QKV);
+            fill(q, L.qkv_t, EPI_PARTIAL); q.scratch = kv->mega_scr[0];
             q.a.x = m->d_hidden; q.a.norm_w = L.attn_norm; q.a.eps = m->cfg.rms_norm_eps; q.a.bias = L.qkv_bias; q.a.rope = m->rope;
             q.a.q_out = m->d_q; q.a.k_pool = kv->k_pool + size_t(l) * kv->layer_stride; q.a.v_pool = kv->v_pool + size_t(l) * kv->layer_stride;
             q.a.page_table = kv->d_page_table; q.a.seq_len = kv->d_seq_len; q.a.pages_per_seq = kv->pages_per_seq;
             q.a.qk = m->qk; q.a.kv = m->kv; q.a.head_dim = m->hd;
             core::Phase& o = ph[4 * l + 1];
-            fill(o, L.o_t, EPI_RESID);
+            fill(o, L.o_t, EPI_PARTIAL); o.scratch = kv->mega_scr[1];
             o.a.x = m->d_attn; o.a.out = m->d_hidden; o.a.resid = m->d_hidden;
             core::Phase& g = ph[4 * l + 2];
             fill(g, L.gateup_t, EPI_SILU);
             g.a.x = m->d_hidden; g.a.norm_w = L.ffn_norm; g.a.eps = m->cfg.rms_norm_eps; g.a.out = m->d_act;
             core::Phase& d = ph[4 * l + 3];
-            fill(d, L.down_t, EPI_RESID);
+            fill(d, L.down_t, EPI_PARTIAL); d.scratch = kv->mega_scr[2];
             d.a.x = m->d_act; d.a.out = m->d_hidden; d.a.resid = m->d_hidden;
         }
         core::Phase& lm = ph.back();
@@ -565,14 +574,14 @@ int32_t forge_kv_create(ForgeModel* m, int32_t max_seq, int32_t batch, ForgeKV**
         lm.a.x = m->d_hidden; lm.a.norm_w = m->final_norm; lm.a.eps = m->cfg.rms_norm_eps; lm.a.out = m->d_logits;
         kv->mega_grid = sms;
         kv->mega_max_kb = max_kb;
-        kv->mega_splits = std::max(1, std::min({(sms + m->nkv - 1) / m->nkv, 64}));
+        // context splits per KV head: cover the SMs, at most 16, and nq * splits <= 512 (limits of decode_mega.cu)
+        kv->mega_splits = std::max(1, std::min({(sms + m->nkv - 1) / m->nkv, 16, 512 / m->nq}));
         if (cudaMalloc(&kv->d_phases, ph.size() * sizeof(core::Phase)) != cudaSuccess ||
             cudaMalloc(&kv->mega_ws, sizeof(float) * size_t(m->nq) * kv->mega_splits * (m->hd + 2)) != cudaSuccess ||
-            cudaMalloc(&kv->mega_tickets, sizeof(int) * m->nkv) != cudaSuccess || cudaMalloc(&kv->d_bar, sizeof(unsigned)) != cudaSuccess) {
+            cudaMalloc(&kv->d_bar, sizeof(unsigned)) != cudaSuccess) {
             set_error("decode kernel tables allocation failed"); return fail(FORGE_ERR_CUDA);
         }
         cudaMemcpyAsync(kv->d_phases, ph.data(), ph.size() * sizeof(core::Phase), cudaMemcpyHostToDevice, m->stream);
-        cudaMemsetAsync(kv->mega_tickets, 0, sizeof(int) * m->nkv, m->stream);
         cudaMemsetAsync(kv->d_bar, 0, sizeof(unsigned), m->stream);
         if (cudaStreamSynchronize(m->stream) != cudaSuccess) { set_error("KV init failed"); return fail(FORGE_ERR_CUDA); }
     }
@@ -601,7 +610,8 @@ void forge_kv_destroy(ForgeKV* kv) {
     if (kv->graph) cudaGraphExecDestroy(kv->graph);
     cudaFree(kv->k_pool); cudaFree(kv->v_pool); cudaFree(kv->d_page_table); cudaFree(kv->d_seq_len);
     cudaFree(kv->attn_ws); cudaFree(kv->attn_counters);
-    cudaFree(kv->d_phases); cudaFree(kv->mega_ws); cudaFree(kv->mega_tickets); cudaFree(kv->d_bar);
+    cudaFree(kv->d_phases); cudaFree(kv->mega_ws); cudaFree(kv->d_bar);
+    for (float* q : kv->mega_scr) cudaFree(q);
     delete kv;
 }
 
@@ -757,6 +767,12 @@ int32_t forge_generate_greedy(ForgeModel* m, ForgeKV* kv, const uint32_t* prompt
 int32_t forge_model_set_gemm_passes(ForgeModel* m, int32_t passes) {
     if (!m || (passes != 1 && passes != 3)) { set_error("gemm passes must be 1 or 3"); return FORGE_ERR_INVALID_ARG; }
     m->gemm_passes = passes;
+    return FORGE_OK;
+}
+
+int32_t forge_model_set_decode_mode(ForgeModel* m, int32_t mode) {
+    if (!m || (mode != 0 && mode != 1)) { set_error("decode mode must be 0 or 1"); return FORGE_ERR_INVALID_ARG; }
+    m->use_mega = mode == 1;
     return FORGE_OK;
 }
 

@@ -137,6 +137,10 @@ class Model:
         """3 = split-precision prefill GEMMs (default), 1 = a single fp16 tensor-core pass."""
         check(lib.forge_model_set_gemm_passes(self._h, passes))
 
+    def set_decode_mode(self, mode: int) -> None:
+        """0 = CUDA-graph replay of the per-operator kernels (default), 1 = one persistent kernel per step."""
+        check(lib.forge_model_set_decode_mode(self._h, mode))
+
     def trace(self, enable: bool) -> None:
         check(lib.forge_hidden_trace_enable(self._h, int(enable)))
 

@@ -162,6 +162,11 @@ void* forge_model_stream(ForgeModel* model);
  * which exceeds 1e-3 on the hidden state after ~20 layers). */
 int32_t forge_model_set_gemm_passes(ForgeModel* model, int32_t passes);
 
+/* How batch-1 decode steps of sequence 0 are issued.  0 (default): one kernel per fused operator, the
+ * step replayed as a CUDA graph.  1: the whole step as one persistent cooperative kernel (a CTA per SM,
+ * weights streamed across grid barriers); needs the GPU to itself. */
+int32_t forge_model_set_decode_mode(ForgeModel* model, int32_t mode);
+
 /* KVCache::new (E:3978-4000) for `batch` independent sequences of up to max_seq positions,
  * fp16, paged (FORGE_KV_PAGE positions per page, pages handed out on demand). */
 int32_t forge_kv_create(ForgeModel* model, int32_t max_seq, int32_t batch, ForgeKV** out);

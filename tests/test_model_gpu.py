@@ -192,3 +192,30 @@ def test_reduced_configs(oracle, key, layers, vocab, n_prompt):
     # that the oracle finishes in seconds
     from forge_llm_b200 import configs
     _run_case(oracle, configs.reduced(key, layers, vocab), n_prompt=n_prompt, n_decode=2, n_greedy=32)
+
+
+@pytest.mark.parametrize("quant,hd,nq,nkv,bias", [(4, 64, 4, 2, 0), (8, 64, 7, 1, 1), (8, 96, 2, 2, 0), (4, 128, 2, 1, 1)])
+def test_whole_step_decode_kernel(oracle, quant, hd, nq, nkv, bias):
+    # decode mode 1: the step as one persistent cooperative kernel; same gates as the default mode
+    from forge_llm_b200 import configs, runtime, synth
+    c = configs.tiny(quant, hd=hd, nq=nq, nkv=nkv, bias=bias, hidden=nq * hd if (nq * hd) % 32 == 0 else 448)
+    blob = synth.make_weights_bin(c)
+    toks = synth.prompt_tokens(c, 150)
+    gm = runtime.Model(c, blob)
+    gm.set_decode_mode(1)
+    kv = gm.new_cache(max_seq=256)
+    om = oracle.OracleModel(c, blob, kv_mode=oracle.KV_F16)
+    lo = om.forward_prefill(toks)
+    gm.forward_prefill(toks, kv)
+    for _ in range(6):
+        t = oracle.argmax(lo)
+        lo = om.forward(t)
+        lg = gm.forward(t, kv)
+        assert np.abs(lg - lo).max() < LOGIT_TOL
+    kv.reset()
+    om.reset()
+    ref_ids, _ = om.generate_greedy(toks, 32)
+    assert np.array_equal(gm.generate_greedy(toks, 32, kv), ref_ids)
+    assert kv.len() == 182
+    kv.close()
+    gm.close()
