@@ -50,6 +50,7 @@ SIGNATURES = {
     "forge_residual_add": (i32, [vp, vp, sz, vp]),
     "forge_kv_append_f16": (i32, [vp, vp, vp, vp, i32, i32, i32, vp]),
     "forge_attention_flash": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, vp]),
+    "forge_attention_flash_static": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, vp]),
     "forge_attention_flash_batch": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, i32, vp]),
     "forge_argmax": (i32, [vp, vp, i32, vp]),
     "forge_quantize_q8_0_host": (i32, [vp, sz, vp]),

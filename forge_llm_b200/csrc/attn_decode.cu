@@ -4,6 +4,9 @@
 // KV head with 128-bit loads and shared by the query heads of its group, the online-softmax
 // state (m, l, acc) is f32, exp is expf.  Split partials are merged by the last CTA to finish
 // a KV head (atomic ticket), so no second launch is needed.
+#include <algorithm>
+#include <mutex>
+
 #include "common.cuh"
 
 namespace forge {
@@ -188,3 +191,80 @@ int32_t attn_decode(const AttnDecodeArgs& a, cudaStream_t st) {
 }
 
 }  // namespace forge
+
+// ------------------------------------------------------------------------------------------------
+// forge_attention_flash_static: the same single-query attention for callers that must not allocate.
+//
+// Some hosts cannot let a library call cudaMalloc: a serving process whose own pool has already claimed
+// the whole device (an allocation here would fail or fragment it), or a loop with a latency budget that
+// cannot absorb the device-wide synchronisation an allocation or a free may imply.  forge_attention_flash
+// gets its split-KV workspace from the stream-ordered allocator on every call; this variant keeps that
+// workspace in a fixed array inside the library image instead (about 1.1 MB on every GPU that loads the
+// library, until the process exits) and therefore accepts only shapes that fit it.
+namespace {
+
+constexpr int kStaticMaxHeads = 64;    // query heads (and KV heads)
+constexpr int kStaticMaxSplits = 32;   // context splits, the same rule as forge_attention_flash
+constexpr int kStaticMaxHeadDim = 128;
+constexpr int kStaticMaxSeq = 1 << 20;
+
+struct StaticScratch {
+    float ws[size_t(kStaticMaxHeads) * kStaticMaxSplits * (kStaticMaxHeadDim + 2)];  // partial (m, l, acc) per head and split
+    int counters[kStaticMaxHeads];                                                  // arrival tickets per KV head
+};
+
+// In host code this name is only a handle for the runtime; the device address comes from
+// cudaGetSymbolAddress below and is what the kernel receives.
+static __device__ __align__(256) unsigned char g_static_scratch[sizeof(StaticScratch)];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mutex;
+StaticScratch* g_static_ptr[kMaxDevices] = {};
+
+// Device address of the scratch on the current device; resolved once per device.
+int32_t static_scratch(StaticScratch** out) {
+    int dev = -1;
+    FORGE_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) { forge::set_error("device index %d beyond %d", dev, kMaxDevices); return FORGE_ERR_UNSUPPORTED; }
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    if (!g_static_ptr[dev]) {
+        void* p = nullptr;
+        FORGE_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
+        g_static_ptr[dev] = static_cast<StaticScratch*>(p);
+    }
+    *out = g_static_ptr[dev];
+    return FORGE_OK;
+}
+
+}  // namespace
+
+extern "C" int32_t forge_attention_flash_static(float* out, const float* q, const uint16_t* k_cache, const uint16_t* v_cache,
+                                                int32_t seq_len, int32_t num_heads, int32_t num_kv_heads, int32_t head_dim,
+                                                void* stream) {
+    using namespace forge;
+    int ndev = 0;
+    if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0) {
+        cudaGetLastError();
+        set_error("no CUDA device: this backend has no CPU fallback");
+        return FORGE_ERR_CUDA;
+    }
+    if (!out || !q || !k_cache || !v_cache || seq_len <= 0 || num_heads <= 0 || num_kv_heads <= 0) {
+        set_error("bad argument to forge_attention_flash_static");
+        return FORGE_ERR_INVALID_ARG;
+    }
+    if (num_heads > kStaticMaxHeads || num_kv_heads > kStaticMaxHeads || head_dim > kStaticMaxHeadDim || seq_len > kStaticMaxSeq) {
+        set_error("forge_attention_flash_static: shape (%d heads, %d kv heads, head_dim %d, %d positions) exceeds the built-in scratch "
+                  "(%d heads, head_dim %d, %d positions); use forge_attention_flash",
+                  num_heads, num_kv_heads, head_dim, seq_len, kStaticMaxHeads, kStaticMaxHeadDim, kStaticMaxSeq);
+        return FORGE_ERR_SHAPE;
+    }
+    StaticScratch* sc = nullptr;
+    FORGE_TRY(static_scratch(&sc));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int splits = std::min(kStaticMaxSplits, std::max(1, seq_len / 64));
+    // the tickets must start at zero; the partials are fully rewritten by every call that reads them
+    FORGE_CUDA(cudaMemsetAsync(sc->counters, 0, sizeof(int) * num_kv_heads, st));
+    AttnDecodeArgs a{out, q, reinterpret_cast<const __half*>(k_cache), reinterpret_cast<const __half*>(v_cache), nullptr, 0, nullptr,
+                     seq_len, 1, num_heads, num_kv_heads, head_dim, seq_len, sc->ws, sc->counters, splits};
+    return attn_decode(a, st);
+}

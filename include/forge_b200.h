@@ -124,6 +124,19 @@ int32_t forge_kv_append_f16(uint16_t* k_cache, uint16_t* v_cache, const float* k
 int32_t forge_attention_flash(float* out, const float* q, const uint16_t* k_cache,
                               const uint16_t* v_cache, int32_t seq_len, int32_t num_heads,
                               int32_t num_kv_heads, int32_t head_dim, void* stream);
+/* No counterpart in the reference.  The same operation as forge_attention_flash for callers that cannot
+ * let the library allocate device memory (a host whose own pool owns the whole GPU, or a loop that cannot
+ * afford the synchronisation an allocation may imply): the split-KV workspace is a fixed array inside the
+ * library image, about 1.1 MB on every GPU that loads the library, held until the process exits.
+ * Limits: num_heads <= 64, num_kv_heads <= 64, head_dim <= 128 (64, 96 or 128), seq_len <= 1048576;
+ * anything larger returns FORGE_ERR_SHAPE.  The first call on each device looks up the array's address
+ * (that device must be current); make that first call before any stream capture begins.  All calls on a
+ * device share the one array: two calls that overlap on the GPU (different streams) race on it, so issue
+ * them on one stream or order them yourself.  It performs no cudaMalloc / cudaFree and uses no allocating
+ * library routine. */
+int32_t forge_attention_flash_static(float* out, const float* q, const uint16_t* k_cache,
+                                     const uint16_t* v_cache, int32_t seq_len, int32_t num_heads,
+                                     int32_t num_kv_heads, int32_t head_dim, void* stream);
 /* attention_flash_batch(output, q_batch, k_cache, v_cache, .., m, base_pos, ...)  E:755-883.
  * Query row r sits at position base_pos + r and sees cache positions <= its own. */
 int32_t forge_attention_flash_batch(float* out, const float* q_batch, const uint16_t* k_cache,
