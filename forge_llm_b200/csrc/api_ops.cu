@@ -88,7 +88,7 @@ int32_t matmul_packed(float* out, int32_t m, const float* in, const ForgePacked*
     FORGE_CUDA(a16.alloc(size_t(m) * K * sizeof(__half)));
     FORGE_CUDA(a16lo.alloc(size_t(m) * K * sizeof(__half)));
     FORGE_TRY(f32_to_f16(static_cast<__half*>(a16.p), static_cast<__half*>(a16lo.p), in, size_t(m) * K, st));
-    return gemm_f16a(out, static_cast<const __half*>(a16.p), static_cast<const __half*>(a16lo.p), pk->soa, m, nullptr, st);
+    return gemm_f16a(out, static_cast<const __half*>(a16.p), static_cast<const __half*>(a16lo.p), pk->soa, m, nullptr, pk->err, st);
 }
 
 int32_t matmul_mat(int quant, float* out, int32_t m, const float* in, const uint8_t* w, int32_t K, int32_t N, void* stream) {

@@ -171,6 +171,10 @@ int32_t attn_prefill_q32(const AttnPrefillArgs& a, const float* q32, cudaStream_
 // ------------------------------------------------------------------ GEMM (prefill)
 // out f32 [m][N] = A f16 [m][K] x W^T; optional resid: out = resid + A W^T (may alias out)
 // Alo != null selects the split-precision form (A = A + Alo, weights split the same way)
-int32_t gemm_f16a(float* out, const __half* A, const __half* Alo, const QWeight& w, int m, const float* resid, cudaStream_t st);
+// err: device word set when a bounded wait in the tcgen05 kernel gives up (may be null)
+int32_t gemm_f16a(float* out, const __half* A, const __half* Alo, const QWeight& w, int m, const float* resid, int* err, cudaStream_t st);
+int32_t gemm_f16a_mma(float* out, const __half* A, const __half* Alo, const QWeight& w, int m, const float* resid, cudaStream_t st);
+bool gemm_tc5_supported(const QWeight& w);
+int32_t gemm_tc5(float* out, const __half* A, const __half* Alo, const QWeight& w, int m, const float* resid, int* err, cudaStream_t st);
 
 }  // namespace forge

@@ -6,6 +6,9 @@
 // default is the split-precision form: x = x_hi + x_lo and w = w_hi + w_lo, each an fp16 pair,
 // and out = x_hi w_hi + x_lo w_hi + x_hi w_lo (three MMA passes, ~1e-6 relative).
 // 128x128x32 CTA tile, 8 warps of 64x32, m16n8k16 MMAs, double-buffered shared memory.
+#include <cstdlib>
+#include <cstring>
+
 #include "common.cuh"
 
 namespace forge {
@@ -189,7 +192,8 @@ __global__ void __launch_bounds__(kThreads) gemm_kernel(GemmParams p) {
 
 }  // namespace
 
-int32_t gemm_f16a(float* out, const __half* A, const __half* Alo, const QWeight& w, int m, const float* resid, cudaStream_t st) {
+// mma.sync tile kernel: the path for K that is not a multiple of 64, and the cross-check for the tcgen05 kernel
+int32_t gemm_f16a_mma(float* out, const __half* A, const __half* Alo, const QWeight& w, int m, const float* resid, cudaStream_t st) {
     if (m <= 0) return FORGE_OK;
     if (w.K % 32) { set_error("gemm: K=%d must be a multiple of 32", w.K); return FORGE_ERR_SHAPE; }
     GemmParams p{out, A, Alo, w.qs, w.d, resid, m, w.N, w.K};
@@ -206,6 +210,12 @@ int32_t gemm_f16a(float* out, const __half* A, const __half* Alo, const QWeight&
 #undef FORGE_GEMM_LAUNCH
     FORGE_LAUNCH_CHECK();
     return FORGE_OK;
+}
+
+int32_t gemm_f16a(float* out, const __half* A, const __half* Alo, const QWeight& w, int m, const float* resid, int* err, cudaStream_t st) {
+    static const bool force_mma = [] { const char* e = getenv("FORGE_B200_GEMM"); return e && !strcmp(e, "mma"); }();
+    if (!force_mma && gemm_tc5_supported(w)) return gemm_tc5(out, A, Alo, w, m, resid, err, st);
+    return gemm_f16a_mma(out, A, Alo, w, m, resid, st);
 }
 
 }  // namespace forge

@@ -227,15 +227,15 @@ int32_t prefill_seq(ForgeModel* m, ForgeKV* kv, int seq, const uint32_t* tokens_
         __half* kp = kv->k_pool + size_t(l) * kv->layer_stride;
         __half* vp = kv->v_pool + size_t(l) * kv->layer_stride;
         FORGE_TRY(rms_norm_f16(m->p_normed, nlo, m->p_hidden, L.attn_norm, n, m->h, c.rms_norm_eps, st));
-        FORGE_TRY(gemm_f16a(m->p_qkv, m->p_normed, nlo, L.qkv, n, nullptr, st));
+        FORGE_TRY(gemm_f16a(m->p_qkv, m->p_normed, nlo, L.qkv, n, nullptr, m->d_err, st));
         FORGE_TRY(qkv_post(m->p_qkv, n, base, L.qkv_bias, m->rope, m->p_q16, kp, vp, page_row, m->qk, m->kv, m->hd, st));
         AttnPrefillArgs pa{m->p_attn16, alo, nullptr, m->p_q16, kp, vp, page_row, n, base, m->nq, m->nkv, m->hd};
         FORGE_TRY(attn_prefill(pa, st));
-        FORGE_TRY(gemm_f16a(m->p_hidden, m->p_attn16, alo, L.o, n, m->p_hidden, st));
+        FORGE_TRY(gemm_f16a(m->p_hidden, m->p_attn16, alo, L.o, n, m->p_hidden, m->d_err, st));
         FORGE_TRY(rms_norm_f16(m->p_normed, nlo, m->p_hidden, L.ffn_norm, n, m->h, c.rms_norm_eps, st));
-        FORGE_TRY(gemm_f16a(m->p_gu, m->p_normed, nlo, L.gateup, n, nullptr, st));
+        FORGE_TRY(gemm_f16a(m->p_gu, m->p_normed, nlo, L.gateup, n, nullptr, m->d_err, st));
         FORGE_TRY(silu_mul_f16(m->p_act16, flo, m->p_gu, n, m->ff, st));
-        FORGE_TRY(gemm_f16a(m->p_hidden, m->p_act16, flo, L.down, n, m->p_hidden, st));
+        FORGE_TRY(gemm_f16a(m->p_hidden, m->p_act16, flo, L.down, n, m->p_hidden, m->d_err, st));
         if (m->trace_on)
             FORGE_CUDA(cudaMemcpyAsync(m->trace + size_t(l) * n * m->h, m->p_hidden, sizeof(float) * n * m->h, cudaMemcpyDeviceToDevice, st));
     }
