@@ -15,6 +15,7 @@ namespace {
 
 constexpr int kThreads = 128;
 constexpr int kGC = 4;  // query heads processed per pass over the keys
+constexpr int kMaxSplits = 32;  // context splits per KV head (the merge keeps one partial per split in registers)
 
 template <int HD> struct Seg { static constexpr int W = (HD == 64) ? 8 : 16, ACTIVE = HD / 8, RPW = 32 / W; };
 
@@ -37,17 +38,19 @@ __global__ void __launch_bounds__(kThreads) attn_decode_kernel(DecParams p) {
     __shared__ float s_acc[PARTS][kGC][HD];
     __shared__ int s_last;
     const AttnDecodeArgs& a = p.a;
+    pdl_trigger();
+    pdl_wait();  // q and the newest cache row come from the kernel before this one
     const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int seg = lane / W, sl = lane % W;
     const bool act = sl < ACTIVE;
     const int G = a.nq / a.nkv, kvd = a.nkv * HD;
-    const int n_ctx = a.seq_len ? a.seq_len[b] + 1 : a.seq_len_host;
-    int chunk = (n_ctx + a.splits - 1) / a.splits;
-    chunk = (chunk + PARTS - 1) / PARTS * PARTS;
-    const int t_begin = split * chunk;
-    const int t_end = min(n_ctx, t_begin + chunk);
+    // Split s owns the logical pages s, s + splits, ...: which pages a CTA reads does not depend on the context
+    // length, so its first page-table entry is fetched together with the length and the query (one round trip).
     const int32_t* pt = a.page_table ? a.page_table + size_t(b) * a.pages_per_seq : nullptr;
+    const int page0 = (pt && split < a.pages_per_seq) ? pt[split] : split;
+    const int n_ctx = a.seq_len ? a.seq_len[b] + 1 : a.seq_len_host;
+    const int n_pages = (n_ctx + FORGE_KV_PAGE - 1) / FORGE_KV_PAGE;
     const size_t seq_base = a.page_table ? 0 : size_t(b) * a.max_ctx;  // contiguous: [batch][max_ctx][kvd]
     const int part = warp * RPW + seg;
 
@@ -67,42 +70,46 @@ __global__ void __launch_bounds__(kThreads) attn_decode_kernel(DecParams p) {
             }
         }
         constexpr int UNR = 4;  // positions per segment whose K/V loads are issued before any use
-        for (int base = t_begin + warp * RPW; base < t_end; base += PARTS * UNR) {
-            uint4 kr[UNR], vr[UNR];
+        for (int lp = split; lp < n_pages; lp += a.splits) {
+            const int page = lp == split ? page0 : (pt ? pt[lp] : lp);
+            const size_t page_row = seq_base + size_t(page) * FORGE_KV_PAGE;
+            const int t_page = lp * FORGE_KV_PAGE;
+            for (int base = warp * RPW; base < FORGE_KV_PAGE; base += PARTS * UNR) {
+                uint4 kr[UNR], vr[UNR];
 #pragma unroll
-            for (int u = 0; u < UNR; ++u) {
-                const int t = base + u * PARTS + seg;
-                kr[u] = make_uint4(0, 0, 0, 0);
-                vr[u] = make_uint4(0, 0, 0, 0);
-                if (t < t_end && act) {
-                    const int lp = t / FORGE_KV_PAGE;
-                    const size_t row = seq_base + size_t(pt ? pt[lp] : lp) * FORGE_KV_PAGE + t % FORGE_KV_PAGE;
-                    const size_t off = row * kvd + kvh * HD + sl * 8;
-                    kr[u] = __ldg(reinterpret_cast<const uint4*>(a.k_pool + off));
-                    vr[u] = __ldg(reinterpret_cast<const uint4*>(a.v_pool + off));
+                for (int u = 0; u < UNR; ++u) {
+                    const int tp = base + u * PARTS + seg;
+                    kr[u] = make_uint4(0, 0, 0, 0);
+                    vr[u] = make_uint4(0, 0, 0, 0);
+                    if (tp < FORGE_KV_PAGE && t_page + tp < n_ctx && act) {
+                        const size_t off = (page_row + tp) * kvd + kvh * HD + sl * 8;
+                        kr[u] = __ldg(reinterpret_cast<const uint4*>(a.k_pool + off));
+                        vr[u] = __ldg(reinterpret_cast<const uint4*>(a.v_pool + off));
+                    }
                 }
-            }
 #pragma unroll
-            for (int u = 0; u < UNR; ++u) {
-                const bool valid = (base + u * PARTS + seg) < t_end;
-                float kf[8], vf[8];
-                unpack8(kr[u], kf);
-                unpack8(vr[u], vf);
+                for (int u = 0; u < UNR; ++u) {
+                    const int tp = base + u * PARTS + seg;
+                    const bool valid = tp < FORGE_KV_PAGE && t_page + tp < n_ctx;
+                    float kf[8], vf[8];
+                    unpack8(kr[u], kf);
+                    unpack8(vr[u], vf);
 #pragma unroll
-                for (int g = 0; g < kGC; ++g) {
-                    float s = 0.f;
+                    for (int g = 0; g < kGC; ++g) {
+                        float s = 0.f;
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) s += q[g][i] * kf[i];
+                        for (int i = 0; i < 8; ++i) s += q[g][i] * kf[i];
 #pragma unroll
-                    for (int o = W / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-                    s *= p.scale;
-                    if (valid && g < gc) {
-                        float mn = fmaxf(mi[g], s);
-                        float es = expf(mi[g] - mn), pr = expf(s - mn);
-                        mi[g] = mn;
-                        li[g] = li[g] * es + pr;
+                        for (int o = W / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+                        s *= p.scale;
+                        if (valid && g < gc) {
+                            float mn = fmaxf(mi[g], s);
+                            float es = expf(mi[g] - mn), pr = expf(s - mn);
+                            mi[g] = mn;
+                            li[g] = li[g] * es + pr;
 #pragma unroll
-                        for (int i = 0; i < 8; ++i) acc[g][i] = acc[g][i] * es + pr * vf[i];
+                            for (int i = 0; i < 8; ++i) acc[g][i] = acc[g][i] * es + pr * vf[i];
+                        }
                     }
                 }
             }
@@ -154,18 +161,28 @@ __global__ void __launch_bounds__(kThreads) attn_decode_kernel(DecParams p) {
     __syncthreads();
     if (!s_last) return;
     __threadfence();
+    // all loads of a thread's partials are issued before the first use: one round trip, not one per split
     for (int idx = threadIdx.x; idx < G * HD; idx += kThreads) {
         const int g = idx / HD, dd = idx % HD, head = kvh * G + g;
         const float* w0 = a.ws + (size_t(b) * a.nq + head) * a.splits * (HD + 2);
+        float pm[kMaxSplits], pl[kMaxSplits], pa[kMaxSplits];
+#pragma unroll
+        for (int s = 0; s < kMaxSplits; ++s) {
+            const bool in = s < a.splits;
+            const float* w = w0 + size_t(in ? s : 0) * (HD + 2);
+            pm[s] = in ? __ldcg(w) : -INFINITY;
+            pl[s] = in ? __ldcg(w + 1) : 0.f;
+            pa[s] = in ? __ldcg(w + 2 + dd) : 0.f;
+        }
         float M = -INFINITY;
-        for (int s = 0; s < a.splits; ++s) M = fmaxf(M, __ldcg(w0 + size_t(s) * (HD + 2)));
+#pragma unroll
+        for (int s = 0; s < kMaxSplits; ++s) M = fmaxf(M, pm[s]);
         float L = 0.f, A = 0.f;
-        for (int s = 0; s < a.splits; ++s) {
-            const float* w = w0 + size_t(s) * (HD + 2);
-            float m = __ldcg(w);
-            float wt = (m == -INFINITY) ? 0.f : expf(m - M);
-            L += __ldcg(w + 1) * wt;
-            A += __ldcg(w + 2 + dd) * wt;
+#pragma unroll
+        for (int s = 0; s < kMaxSplits; ++s) {
+            const float wt = (pm[s] == -INFINITY) ? 0.f : expf(pm[s] - M);
+            L += pl[s] * wt;
+            A += pa[s] * wt;
         }
         a.out[(size_t(b) * a.nq + head) * HD + dd] = A * (1.0f / L);
     }
@@ -178,12 +195,13 @@ size_t attn_decode_ws_floats(int batch, int nq, int hd, int splits) { return siz
 int32_t attn_decode(const AttnDecodeArgs& a, cudaStream_t st) {
     if (a.nq % a.nkv) { set_error("attention: num_heads %d not a multiple of num_kv_heads %d", a.nq, a.nkv); return FORGE_ERR_SHAPE; }
     if (a.splits < 1 || (a.splits > 1 && (!a.ws || !a.counters))) { set_error("attention: split workspace missing"); return FORGE_ERR_INVALID_ARG; }
+    if (a.splits > kMaxSplits) { set_error("attention: at most %d context splits", kMaxSplits); return FORGE_ERR_INVALID_ARG; }
     DecParams p{a, 1.0f / sqrtf(float(a.hd))};
     dim3 grid(a.splits, a.nkv, a.batch);
     switch (a.hd) {
-        case 64: attn_decode_kernel<64><<<grid, kThreads, 0, st>>>(p); break;
-        case 96: attn_decode_kernel<96><<<grid, kThreads, 0, st>>>(p); break;
-        case 128: attn_decode_kernel<128><<<grid, kThreads, 0, st>>>(p); break;
+        case 64: FORGE_CUDA(launch_pdl(attn_decode_kernel<64>, grid, dim3(kThreads), 0, st, p)); break;
+        case 96: FORGE_CUDA(launch_pdl(attn_decode_kernel<96>, grid, dim3(kThreads), 0, st, p)); break;
+        case 128: FORGE_CUDA(launch_pdl(attn_decode_kernel<128>, grid, dim3(kThreads), 0, st, p)); break;
         default: set_error("attention: head_dim %d unsupported (64, 96, 128)", a.hd); return FORGE_ERR_SHAPE;
     }
     FORGE_LAUNCH_CHECK();

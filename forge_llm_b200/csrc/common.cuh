@@ -3,6 +3,7 @@
 #pragma once
 
 #include <cuda_fp16.h>
+#include <utility>
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
@@ -55,6 +56,28 @@ struct QWeight {
 // packed rows dst_row0.. with optional row interleave: dst row = dst_row0 + r*row_step.
 int32_t pack_rows(const uint8_t* raw_dev, int quant, int K_full, int row0, int rows, int blk0, int blks,
                   QWeight& dst, int dst_row0, int row_step, cudaStream_t st);
+
+// ------------------------------------------------------------------ programmatic dependent launch
+// A kernel launched with launch_pdl() may start while the kernel before it on the stream is still running.
+// It must execute pdl_wait() before it touches anything an earlier kernel writes (the wait returns when the earlier
+// kernels have completed and their writes are visible); what it does before the wait (barrier set-up, streaming
+// constant weights into shared memory) overlaps the tail of its predecessor.  pdl_trigger() lets the next kernel
+// on the stream be scheduled as soon as every CTA of this one has called it.
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at; cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, KArgs(std::forward<Args>(args))...);
+}
+#endif
 
 // ------------------------------------------------------------------ GEMV (decode)
 // EPI_PARTIAL: every K slice stores its raw partial sums at scratch[slice][row]; the reader adds them

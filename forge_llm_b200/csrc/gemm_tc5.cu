@@ -2,18 +2,18 @@
 // streamed as Q8_0 / Q4_0 blocks and dequantised on the fly (replaces matmul_mat_q8_0_KxN /
 // matmul_mat_q4_0_KxN, crates/forgellm-codegen-cpu/src/emit.rs:2278-2299 and :3792-3813).
 //
-// CTA tile: (MT x 128) activation rows x 128 weight rows, K step 64.  Warp roles (192 threads):
+// CTA tile: (MT x 128) activation rows x 128 weight rows, K step 64.  Warp roles (320 threads):
 //   warp 0      TMA producer: 2-D tiled bulk copies (SWIZZLE_128B) of the fp16 activation tiles (hi and lo
 //               parts) into shared memory, completion on an mbarrier;
 //   warp 1      allocates TMEM and issues tcgen05.mma (one elected lane): per K step and per 128-row
 //               sub-tile three products accumulate into the same f32 TMEM tile,
 //               x_hi*w_hi + x_lo*w_hi + x_hi*w_lo (split precision, see gemm_mma.cu), K = 16 per instruction;
 //               tcgen05.commit releases the shared-memory stage and finally publishes the accumulator;
-//   warps 2..5  dequantise: each thread owns one weight row, reads its 64 quantised values and two f16
-//               scales from global memory, forms w = q * d in f32, splits it into fp16 hi + lo and writes both
-//               into the K-major SWIZZLE_128B operand tiles (generic-proxy stores + fence.proxy.async);
-//               after the main loop the same warps read the accumulator with tcgen05.ld (one TMEM lane
-//               quadrant per warp) and write f32 rows (+ residual).
+//   warps 2..9  dequantise: each thread owns one 32-value block of one weight row per K step, reads it and its
+//               f16 scale from global memory, forms hi = rn16(q*d) and lo = rn16(q*d - hi) with packed-half
+//               arithmetic and writes both into the K-major SWIZZLE_128B operand tiles (generic-proxy stores +
+//               fence.proxy.async); after the main loop the same warps read the accumulator with tcgen05.ld
+//               (two warps per TMEM lane quadrant) and write f32 rows (+ residual).
 // Every wait is bounded; a wait that gives up sets an error word, and the CTA still frees its TMEM.
 #include <cuda.h>
 
@@ -24,7 +24,7 @@ namespace forge {
 namespace {
 
 constexpr int BM = 128, BN = 128, BK = 64;
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;
 constexpr int kTileBytes = BM * BK * 2;  // one 128 x 64 fp16 operand tile = 16 KB (1024-byte aligned)
 constexpr uint32_t kSpinLimit = 1u << 22;
 
@@ -82,22 +82,49 @@ struct Tc5Params {
     int* err;
 };
 
-__device__ __forceinline__ void split_store(unsigned char* hi_tile, unsigned char* lo_tile, int row, int chunk, const float (&w)[8], bool split) {
-    // K-major SWIZZLE_128B: row r at r*128 bytes, 16-byte chunk c stored at chunk (c ^ (r & 7))
-    const uint32_t off = uint32_t(row) * 128u + uint32_t((chunk ^ (row & 7)) << 4);
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t r;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+    return r;
+}
+__device__ __forceinline__ __half2 as_h2(uint32_t v) { return *reinterpret_cast<__half2*>(&v); }
+__device__ __forceinline__ uint32_t as_u32(__half2 v) { return *reinterpret_cast<uint32_t*>(&v); }
+
+// two integer weights (exact in fp16) times the block scale: hi = rn16(q*d), lo = rn16(q*d - hi).  The fp16 multiply
+// rounds the exact product once and the fused multiply-add forms q*d - hi exactly before its one rounding, so
+// hi + lo carries the 19-bit product q*d to the last bit (|lo| <= ulp(hi)/2 is itself exact in fp16).
+__device__ __forceinline__ void scale_split(__half2 q, __half2 d, uint32_t& hi, uint32_t& lo) {
+    const __half2 h = __hmul2(q, d);
+    hi = as_u32(h);
+    lo = as_u32(__hfma2(q, d, __hneg2(h)));
+}
+
+// eight consecutive weights of one row -> one 16-byte chunk of the hi tile and of the lo tile.
+// K-major SWIZZLE_128B: row r at r*128 bytes, 16-byte chunk c stored at chunk (c ^ (r & 7)).
+// w0, w1: for Q8_0 the eight int8 values; for Q4_0 eight bytes whose nibbles at bit `sh` are the values.
+template <int QUANT, bool SPLIT>
+__device__ __forceinline__ void dequant_chunk(unsigned char* hi_tile, unsigned char* lo_tile, int row, int chunk, uint32_t w0,
+                                              uint32_t w1, int sh, __half2 d2) {
     uint32_t h[4], l[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        __half2 hv = __floats2half2_rn(w[2 * i], w[2 * i + 1]);
-        h[i] = *reinterpret_cast<uint32_t*>(&hv);
-        if (split) {
-            float2 hf = __half22float2(hv);
-            __half2 lv = __floats2half2_rn(w[2 * i] - hf.x, w[2 * i + 1] - hf.y);
-            l[i] = *reinterpret_cast<uint32_t*>(&lv);
+        const uint32_t word = i < 2 ? w0 : w1;
+        const uint32_t sel = (i & 1) ? 0x4342u : 0x4140u;  // bytes (2,3) or (0,1) into the low bytes of each half
+        __half2 q;
+        if (QUANT == FORGE_Q8_0) {
+            // int8 b -> fp16: 0x6400 | (b + 128) is 1024 + b + 128
+            q = __hsub2(as_h2(prmt(word ^ 0x80808080u, 0x64646464u, sel)), __float2half2_rn(1152.f));
+        } else {
+            // nibble n -> fp16: 0x6400 | n is 1024 + n; the stored value is n - 8
+            const uint32_t two = prmt(word, 0u, sel) >> sh;
+            q = __hsub2(as_h2((two & 0x000F000Fu) | 0x64006400u), __float2half2_rn(1032.f));
         }
+        if (SPLIT) scale_split(q, d2, h[i], l[i]);
+        else h[i] = as_u32(__hmul2(q, d2));
     }
+    const uint32_t off = uint32_t(row) * 128u + uint32_t((chunk ^ (row & 7)) << 4);
     *reinterpret_cast<uint4*>(hi_tile + off) = make_uint4(h[0], h[1], h[2], h[3]);
-    if (split) *reinterpret_cast<uint4*>(lo_tile + off) = make_uint4(l[0], l[1], l[2], l[3]);
+    if (SPLIT) *reinterpret_cast<uint4*>(lo_tile + off) = make_uint4(l[0], l[1], l[2], l[3]);
 }
 
 // MT: 128-row activation sub-tiles per CTA; SPLIT: hi/lo split precision (3 passes) or one fp16 pass; STAGES: ring depth
@@ -120,7 +147,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc5_kernel(const __grid_cons
     const int nk = p.K / BK;
 
     if (tid == 0) {
-        for (int s = 0; s < STAGES; ++s) { mbar_init(&full_a[s], 1); mbar_init(&full_b[s], 4); mbar_init(&empty[s], 1); }
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&full_a[s], 1); mbar_init(&full_b[s], 8); mbar_init(&empty[s], 1); }
         mbar_init(&accum_full, 1);
         s_err = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -177,67 +204,47 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc5_kernel(const __grid_cons
             umma_commit(&accum_full);    // all MMAs done: the accumulators are complete
         }
     } else {
-        // ---------------- dequantise (warps 2..5): thread -> weight row n0 + r
-        const int r = tid - 64;
+        // ---------------- dequantise (warps 2..9): thread -> weight row n0 + r, 32-value block blk of the K step
+        const int r = (tid - 64) & 127, blk = (tid - 64) >> 7;
         const int n = n0 + r;
         const bool n_ok = n < p.N;
         const size_t qrow = QUANT == FORGE_Q8_0 ? size_t(p.K) : size_t(p.K) / 2;
-        const uint8_t* qsrc = p.qs + size_t(n_ok ? n : 0) * qrow;
-        const __half* dsrc = p.d + size_t(n_ok ? n : 0) * (p.K / 32);
-        constexpr int QV = QUANT == FORGE_Q8_0 ? 4 : 2;  // uint4 loads per 64 weights
+        constexpr int QB = QUANT == FORGE_Q8_0 ? 32 : 16;  // bytes of quantised values per block
+        constexpr int QV = QB / 16;
+        const uint8_t* qsrc = p.qs + size_t(n_ok ? n : 0) * qrow + size_t(blk) * QB;
+        const __half* dsrc = p.d + size_t(n_ok ? n : 0) * (p.K / 32) + blk;
         uint4 q[QV];
-        float dsc[2];
+        __half dsc;
         auto gload = [&](int kt) {
             if (n_ok) {
 #pragma unroll
-                for (int i = 0; i < QV; ++i) q[i] = __ldg(reinterpret_cast<const uint4*>(qsrc + size_t(kt) * (QUANT == FORGE_Q8_0 ? 64 : 32)) + i);
-                dsc[0] = __half2float(dsrc[2 * kt]);
-                dsc[1] = __half2float(dsrc[2 * kt + 1]);
+                for (int i = 0; i < QV; ++i) q[i] = __ldg(reinterpret_cast<const uint4*>(qsrc + size_t(kt) * (2 * QB)) + i);
+                dsc = dsrc[2 * kt];
             } else {
 #pragma unroll
                 for (int i = 0; i < QV; ++i) q[i] = make_uint4(0, 0, 0, 0);
-                dsc[0] = dsc[1] = 0.f;
+                dsc = __float2half(0.f);
             }
         };
         gload(0);
         bool ok = true;
         for (int kt = 0; kt < nk; ++kt) {
             const int s = kt % STAGES, use = kt / STAGES;
-            // this thread's 64 weights of the K step, as bytes
-            uint4 cur[QV];
-            float dc[2] = {dsc[0], dsc[1]};
+            uint32_t cur[4 * QV];
 #pragma unroll
-            for (int i = 0; i < QV; ++i) cur[i] = q[i];
+            for (int i = 0; i < QV; ++i) { cur[4 * i] = q[i].x; cur[4 * i + 1] = q[i].y; cur[4 * i + 2] = q[i].z; cur[4 * i + 3] = q[i].w; }
+            const __half2 d2 = __half2half2(dsc);
             if (kt + 1 < nk) gload(kt + 1);
             if (ok && use > 0 && !mbar_wait(&empty[s], (use - 1) & 1, &s_err)) { atomicExch(&s_err, 1); ok = false; }
             unsigned char* hi_tile = sB + size_t(s) * B_STAGE;
             unsigned char* lo_tile = hi_tile + kTileBytes;
 #pragma unroll
-            for (int b = 0; b < 2; ++b) {        // the two 32-value blocks of the K step
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {    // 8 values per 16-byte fp16 chunk
-                    float w[8];
-                    if (QUANT == FORGE_Q8_0) {
-                        const uint4 v = cur[2 * b + (c >> 1)];
-                        const uint32_t lo32 = (c & 1) ? v.z : v.x, hi32 = (c & 1) ? v.w : v.y;
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            w[i] = float(int(int8_t(lo32 >> (8 * i)))) * dc[b];
-                            w[4 + i] = float(int(int8_t(hi32 >> (8 * i)))) * dc[b];
-                        }
-                    } else {
-                        // block bytes j = 0..15: element j in the low nibble, element j + 16 in the high nibble
-                        const uint4 v = cur[b];
-                        const int e0 = 8 * (c & 1);           // first byte of this chunk
-                        const uint32_t w0 = e0 ? v.z : v.x, w1 = e0 ? v.w : v.y;
-                        const int sh = (c >> 1) * 4;           // chunks 0,1: low nibbles; chunks 2,3: high nibbles
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            w[i] = float(int((w0 >> (8 * i + sh)) & 15u) - 8) * dc[b];
-                            w[4 + i] = float(int((w1 >> (8 * i + sh)) & 15u) - 8) * dc[b];
-                        }
-                    }
-                    split_store(hi_tile, lo_tile, r, b * 4 + c, w, SPLIT);
+            for (int c = 0; c < 4; ++c) {  // 8 values per 16-byte fp16 chunk
+                if (QUANT == FORGE_Q8_0) {
+                    dequant_chunk<QUANT, SPLIT>(hi_tile, lo_tile, r, blk * 4 + c, cur[2 * c], cur[2 * c + 1], 0, d2);
+                } else {
+                    // block bytes j = 0..15: element j in the low nibble, element j + 16 in the high nibble
+                    dequant_chunk<QUANT, SPLIT>(hi_tile, lo_tile, r, blk * 4 + c, cur[2 * (c & 1)], cur[2 * (c & 1) + 1], (c >> 1) * 4, d2);
                 }
             }
             // make the generic-proxy stores visible to the tensor core (async proxy), then signal
@@ -249,12 +256,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc5_kernel(const __grid_cons
         // ---------------- epilogue: TMEM -> registers -> global (warp w reads lane quadrant w % 4)
         if (!mbar_wait(&accum_full, 0, &s_err)) atomicExch(&s_err, 1);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const int quad = warp & 3;
+        const int quad = warp & 3, chalf = (warp - 2) >> 2;  // two warps per lane quadrant, 64 columns each
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) {
             const int row = m0 + mt * BM + quad * 32 + lane;
 #pragma unroll
-            for (int c0 = 0; c0 < BN; c0 += 32) {
+            for (int c0 = chalf * 64; c0 < chalf * 64 + 64; c0 += 32) {
                 uint32_t v[32];
                 const uint32_t taddr = tmem + (uint32_t(quad * 32) << 16) + uint32_t(mt * BN + c0);
                 asm volatile(
@@ -350,8 +357,13 @@ int32_t gemm_tc5(float* out, const __half* A, const __half* Alo, const QWeight& 
     Tc5Params p{out, resid, w.qs, w.d, m, w.N, w.K, err};
     const bool split = Alo != nullptr;
     // two activation sub-tiles per CTA reuse every dequantised weight tile twice; use it when the grid still fills the GPU
-    const long ctas2 = long((w.N + BN - 1) / BN) * ((m + 2 * BM - 1) / (2 * BM));
-    const bool mt2 = m > BM && ctas2 >= 120;
+    // (a CTA with two sub-tiles costs about 1.5x one with a single sub-tile; compare whole rounds over the SMs)
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const long nt = (w.N + BN - 1) / BN;
+    const long ctas1 = nt * ((m + BM - 1) / BM), ctas2 = nt * ((m + 2 * BM - 1) / (2 * BM));
+    const bool mt2 = m > BM && 3 * ((ctas2 + sms - 1) / sms) <= 2 * ((ctas1 + sms - 1) / sms);
 #define FORGE_TC5(Q)                                                                             \
     do {                                                                                         \
         if (split) return mt2 ? launch<Q, 2, true>(mh, ml, p, st) : launch<Q, 1, true>(mh, ml, p, st);   \

@@ -51,6 +51,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tc_kernel(TcParams p) {
     unsigned char* ring = smem;
     uint2* xf = reinterpret_cast<uint2*>(smem + size_t(kStages) * T::STAGE_BYTES);
     const int tid = threadIdx.x, warp = tid >> 5;
+    pdl_trigger();  // the next kernel may be scheduled; it waits for this one before it reads any result
     if (tid == 0) {
         for (int s = 0; s < kStages; ++s) { mbar_init(&sh.full_bar[s], 1); mbar_init(&sh.empty_bar[s], kConsumerWarps); }
         sh.err = 0;
@@ -67,6 +68,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tc_kernel(TcParams p) {
                 if (!produce_phase<QUANT>(ph, sh, ring, cc)) break;
         return;
     }
+    // everything above (and the producer's weight stream) is independent of earlier kernels; the activation is not
+    pdl_wait();
     for (int b = 0; b < ph.a.batch; ++b) {
         const float unscale = stage_activation<QUANT, false>(xf, s_xoff, sh, ph.a.x + size_t(b) * ph.K, ph.K, ph.a.norm_w, ph.a.eps);
         consume_phase<QUANT>(ph, sh, ring, xf, s_xoff, unscale, b, cc, [](int, float) {});
@@ -144,8 +147,10 @@ int32_t launch(const QTiled& w, GemvEpilogue epi, const GemvArgs& a, const GemvS
     ph.scratch = sp.scratch;
     ph.tickets = sp.tickets;
     const int grid = ph.units < sms ? ph.units : sms;
-    FORGE_CUDA(cudaFuncSetAttribute(gemv_tc_kernel<QUANT>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
-    gemv_tc_kernel<QUANT><<<grid, kThreads, smem, st>>>(p);
+    // one limit for every launch of this kernel: a launch replayed later (a graph node re-issued by a profiler) must
+    // not find a smaller limit left behind by another matrix
+    FORGE_CUDA(cudaFuncSetAttribute(gemv_tc_kernel<QUANT>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(dyn_smem_bytes<QUANT>(kMaxKB))));
+    FORGE_CUDA(launch_pdl(gemv_tc_kernel<QUANT>, dim3(grid), dim3(kThreads), smem, st, p));
     FORGE_LAUNCH_CHECK();
     return FORGE_OK;
 }
