@@ -15,7 +15,8 @@ namespace {
 
 constexpr int kThreads = 128;
 constexpr int kGC = 4;  // query heads processed per pass over the keys
-constexpr int kMaxSplits = 32;  // context splits per KV head (the merge keeps one partial per split in registers)
+constexpr int kMaxGroup = 16;  // query heads per KV head
+constexpr int kMaxSplits = 32;    // context splits per KV head (the merge keeps one partial per split in registers)
 
 template <int HD> struct Seg { static constexpr int W = (HD == 64) ? 8 : 16, ACTIVE = HD / 8, RPW = 32 / W; };
 
@@ -30,12 +31,16 @@ __device__ __forceinline__ void unpack8(const uint4& v, float* f) {
     for (int i = 0; i < 4; ++i) { float2 t = __half22float2(h[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
 }
 
+// exp(x - m) with exp(-inf) = 0 and no NaN when both are -inf
+__device__ __forceinline__ float exp_rel(float x, float m) { return (x == -INFINITY) ? 0.f : __expf(x - m); }
+
 template <int HD>
 __global__ void __launch_bounds__(kThreads) attn_decode_kernel(DecParams p) {
     constexpr int W = Seg<HD>::W, ACTIVE = Seg<HD>::ACTIVE, RPW = Seg<HD>::RPW;
     constexpr int PARTS = (kThreads / 32) * RPW;
-    __shared__ float s_ml[PARTS][kGC][2];
+    __shared__ float s_m[PARTS][kGC], s_l[PARTS][kGC], s_w[PARTS][kGC];
     __shared__ float s_acc[PARTS][kGC][HD];
+    __shared__ float s_fw[kMaxSplits][kMaxGroup];  // final merge: weight of split s for query head g
     __shared__ int s_last;
     const AttnDecodeArgs& a = p.a;
     pdl_trigger();
@@ -65,8 +70,8 @@ __global__ void __launch_bounds__(kThreads) attn_decode_kernel(DecParams p) {
             if (g < gc && act) {
                 const float4* qp = reinterpret_cast<const float4*>(a.q + (size_t(b) * a.nq + kvh * G + g0 + g) * HD + sl * 8);
                 float4 x0 = qp[0], x1 = qp[1];
-                q[g][0] = x0.x; q[g][1] = x0.y; q[g][2] = x0.z; q[g][3] = x0.w;
-                q[g][4] = x1.x; q[g][5] = x1.y; q[g][6] = x1.z; q[g][7] = x1.w;
+                q[g][0] = x0.x * p.scale; q[g][1] = x0.y * p.scale; q[g][2] = x0.z * p.scale; q[g][3] = x0.w * p.scale;
+                q[g][4] = x1.x * p.scale; q[g][5] = x1.y * p.scale; q[g][6] = x1.z * p.scale; q[g][7] = x1.w * p.scale;
             }
         }
         constexpr int UNR = 4;  // positions per segment whose K/V loads are issued before any use
@@ -87,58 +92,90 @@ __global__ void __launch_bounds__(kThreads) attn_decode_kernel(DecParams p) {
                         vr[u] = __ldg(reinterpret_cast<const uint4*>(a.v_pool + off));
                     }
                 }
+                // the UNR scores of a head are formed independently, then folded into the running state in one
+                // softmax step (one rescale per group instead of one per position)
+                float sc[UNR][kGC];
+#pragma unroll
+                for (int u = 0; u < UNR; ++u) {
+                    float kf[8];
+                    unpack8(kr[u], kf);
+#pragma unroll
+                    for (int g = 0; g < kGC; ++g) {
+                        float d = 0.f;
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) d += q[g][i] * kf[i];
+                        sc[u][g] = d;
+                    }
+                }
+#pragma unroll
+                for (int o = W / 2; o > 0; o >>= 1)
+#pragma unroll
+                    for (int u = 0; u < UNR; ++u)
+#pragma unroll
+                        for (int g = 0; g < kGC; ++g) sc[u][g] += __shfl_xor_sync(0xffffffffu, sc[u][g], o);
 #pragma unroll
                 for (int u = 0; u < UNR; ++u) {
                     const int tp = base + u * PARTS + seg;
-                    const bool valid = tp < FORGE_KV_PAGE && t_page + tp < n_ctx;
-                    float kf[8], vf[8];
-                    unpack8(kr[u], kf);
-                    unpack8(vr[u], vf);
+                    if (!(tp < FORGE_KV_PAGE && t_page + tp < n_ctx)) {
 #pragma unroll
-                    for (int g = 0; g < kGC; ++g) {
-                        float s = 0.f;
+                        for (int g = 0; g < kGC; ++g) sc[u][g] = -INFINITY;
+                    }
+                }
+                float vf[UNR][8];
 #pragma unroll
-                        for (int i = 0; i < 8; ++i) s += q[g][i] * kf[i];
+                for (int u = 0; u < UNR; ++u) unpack8(vr[u], vf[u]);
 #pragma unroll
-                        for (int o = W / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-                        s *= p.scale;
-                        if (valid && g < gc) {
-                            float mn = fmaxf(mi[g], s);
-                            float es = expf(mi[g] - mn), pr = expf(s - mn);
-                            mi[g] = mn;
-                            li[g] = li[g] * es + pr;
+                for (int g = 0; g < kGC; ++g) {
+                    float mn = mi[g];
 #pragma unroll
-                            for (int i = 0; i < 8; ++i) acc[g][i] = acc[g][i] * es + pr * vf[i];
-                        }
+                    for (int u = 0; u < UNR; ++u) mn = fmaxf(mn, sc[u][g]);
+                    if (mn == -INFINITY || g >= gc) continue;
+                    const float es = exp_rel(mi[g], mn);
+                    float pr[UNR], ps = 0.f;
+#pragma unroll
+                    for (int u = 0; u < UNR; ++u) { pr[u] = exp_rel(sc[u][g], mn); ps += pr[u]; }
+                    mi[g] = mn;
+                    li[g] = li[g] * es + ps;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        float t = acc[g][i] * es;
+#pragma unroll
+                        for (int u = 0; u < UNR; ++u) t += pr[u] * vf[u][i];
+                        acc[g][i] = t;
                     }
                 }
             }
         }
-        // ---- merge the CTA's parts
+        // ---- merge the CTA's parts: weights once per (part, head), then one weighted sum per output
         __syncthreads();
 #pragma unroll
         for (int g = 0; g < kGC; ++g) {
-            if (sl == 0) { s_ml[part][g][0] = mi[g]; s_ml[part][g][1] = li[g]; }
+            if (sl == 0) { s_m[part][g] = mi[g]; s_l[part][g] = li[g]; }
             if (act) {
-#pragma unroll
-                for (int i = 0; i < 8; ++i) s_acc[part][g][sl * 8 + i] = acc[g][i];
+                *reinterpret_cast<float4*>(&s_acc[part][g][sl * 8]) = make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
+                *reinterpret_cast<float4*>(&s_acc[part][g][sl * 8 + 4]) = make_float4(acc[g][4], acc[g][5], acc[g][6], acc[g][7]);
             }
+        }
+        __syncthreads();
+        if (threadIdx.x < PARTS * kGC) {
+            const int pp = threadIdx.x % PARTS, g = threadIdx.x / PARTS;
+            float M = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < PARTS; ++j) M = fmaxf(M, s_m[j][g]);
+            s_w[pp][g] = exp_rel(s_m[pp][g], M);
         }
         __syncthreads();
         for (int idx = threadIdx.x; idx < gc * HD; idx += kThreads) {
             const int g = idx / HD, dd = idx % HD;
-            float M = -INFINITY;
+            float A = 0.f;
 #pragma unroll
-            for (int pp = 0; pp < PARTS; ++pp) M = fmaxf(M, s_ml[pp][g][0]);
-            float L = 0.f, A = 0.f;
-#pragma unroll
-            for (int pp = 0; pp < PARTS; ++pp) {
-                float m = s_ml[pp][g][0];
-                float w = (m == -INFINITY) ? 0.f : expf(m - M);
-                L += s_ml[pp][g][1] * w;
-                A += s_acc[pp][g][dd] * w;
-            }
+            for (int pp = 0; pp < PARTS; ++pp) A += s_acc[pp][g][dd] * s_w[pp][g];
             const int head = kvh * G + g0 + g;
+            float M = -INFINITY, L = 0.f;
+            if (dd == 0 || a.splits == 1) {
+#pragma unroll
+                for (int pp = 0; pp < PARTS; ++pp) { M = fmaxf(M, s_m[pp][g]); L += s_l[pp][g] * s_w[pp][g]; }
+            }
             if (a.splits == 1) {
                 a.out[(size_t(b) * a.nq + head) * HD + dd] = A * (1.0f / L);
             } else {
@@ -161,30 +198,43 @@ __global__ void __launch_bounds__(kThreads) attn_decode_kernel(DecParams p) {
     __syncthreads();
     if (!s_last) return;
     __threadfence();
-    // all loads of a thread's partials are issued before the first use: one round trip, not one per split
-    for (int idx = threadIdx.x; idx < G * HD; idx += kThreads) {
-        const int g = idx / HD, dd = idx % HD, head = kvh * G + g;
-        const float* w0 = a.ws + (size_t(b) * a.nq + head) * a.splits * (HD + 2);
-        float pm[kMaxSplits], pl[kMaxSplits], pa[kMaxSplits];
+    // One round trip: every thread first issues the loads of its two output columns from all splits, then the
+    // warps turn the splits' (max, sum) pairs into normalised weights (lane = split), then the weighted sums.
+    const float* ws_kvh = a.ws + (size_t(b) * a.nq + size_t(kvh) * G) * a.splits * (HD + 2);
+    const int nout2 = G * HD / 2;
+    for (int i0 = 0; i0 < nout2; i0 += kThreads) {
+        const int idx = i0 + threadIdx.x;
+        const bool on = idx < nout2;
+        const int g = on ? idx / (HD / 2) : 0, d2 = on ? idx % (HD / 2) : 0;
+        const float* w0 = ws_kvh + size_t(g) * a.splits * (HD + 2) + 2 + 2 * d2;
+        float2 pa[kMaxSplits];
+#pragma unroll
+        for (int s = 0; s < kMaxSplits; ++s)
+            pa[s] = (on && s < a.splits) ? __ldcg(reinterpret_cast<const float2*>(w0 + size_t(s) * (HD + 2))) : make_float2(0.f, 0.f);
+        if (i0 == 0) {
+            for (int g2 = warp; g2 < G; g2 += kThreads / 32) {
+                const float* w = ws_kvh + (size_t(g2) * a.splits + lane) * (HD + 2);
+                const float m = lane < a.splits ? __ldcg(w) : -INFINITY;
+                const float l = lane < a.splits ? __ldcg(w + 1) : 0.f;
+                float M = m;
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+                const float wt = exp_rel(m, M);
+                float L = l * wt;
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
+                s_fw[lane][g2] = wt * (1.0f / L);
+            }
+            __syncthreads();
+        }
+        float2 A = make_float2(0.f, 0.f);
 #pragma unroll
         for (int s = 0; s < kMaxSplits; ++s) {
-            const bool in = s < a.splits;
-            const float* w = w0 + size_t(in ? s : 0) * (HD + 2);
-            pm[s] = in ? __ldcg(w) : -INFINITY;
-            pl[s] = in ? __ldcg(w + 1) : 0.f;
-            pa[s] = in ? __ldcg(w + 2 + dd) : 0.f;
+            const float wt = s < a.splits ? s_fw[s][g] : 0.f;
+            A.x += pa[s].x * wt;
+            A.y += pa[s].y * wt;
         }
-        float M = -INFINITY;
-#pragma unroll
-        for (int s = 0; s < kMaxSplits; ++s) M = fmaxf(M, pm[s]);
-        float L = 0.f, A = 0.f;
-#pragma unroll
-        for (int s = 0; s < kMaxSplits; ++s) {
-            const float wt = (pm[s] == -INFINITY) ? 0.f : expf(pm[s] - M);
-            L += pl[s] * wt;
-            A += pa[s] * wt;
-        }
-        a.out[(size_t(b) * a.nq + head) * HD + dd] = A * (1.0f / L);
+        if (on) *reinterpret_cast<float2*>(a.out + (size_t(b) * a.nq + kvh * G + g) * HD + 2 * d2) = A;
     }
 }
 
@@ -195,6 +245,7 @@ size_t attn_decode_ws_floats(int batch, int nq, int hd, int splits) { return siz
 int32_t attn_decode(const AttnDecodeArgs& a, cudaStream_t st) {
     if (a.nq % a.nkv) { set_error("attention: num_heads %d not a multiple of num_kv_heads %d", a.nq, a.nkv); return FORGE_ERR_SHAPE; }
     if (a.splits < 1 || (a.splits > 1 && (!a.ws || !a.counters))) { set_error("attention: split workspace missing"); return FORGE_ERR_INVALID_ARG; }
+    if (a.nq / a.nkv > kMaxGroup) { set_error("attention: at most %d query heads per KV head", kMaxGroup); return FORGE_ERR_SHAPE; }
     if (a.splits > kMaxSplits) { set_error("attention: at most %d context splits", kMaxSplits); return FORGE_ERR_INVALID_ARG; }
     DecParams p{a, 1.0f / sqrtf(float(a.hd))};
     dim3 grid(a.splits, a.nkv, a.batch);

@@ -100,6 +100,10 @@ struct GemvArgs {
     const int32_t* seq_len = nullptr;     // [batch] device positions (the new row's position)
     int pages_per_seq = 0;
     int qk = 0, kv = 0, head_dim = 0;
+    // optional: constant data the NEXT kernel on the stream will read (its weights).  Every CTA asks L2 to fetch its
+    // share while this kernel runs, so HBM keeps streaming across the kernel boundary.
+    const void* next_w = nullptr;
+    size_t next_bytes = 0;
 };
 // Streaming layout of one projection for the decode GEMV: 16-row x 32-column tiles, each
 // {8 x half2 block scales}{quant bytes in MMA-fragment order}, K-major inside a 16-row band.
@@ -118,6 +122,7 @@ int gemv_slices(const QTiled& w, const GemvSplit& sp, int sms, int batch);
 constexpr int kGemvMaxSlices = 16;
 constexpr int kGemvSplitRows = 256 * 128;  // split only happens up to this many (padded) rows
 size_t qtiled_bytes(int quant, int K, int N, int bt);
+inline size_t qtiled_bytes(const QTiled& w) { return qtiled_bytes(w.quant, w.K, w.N, w.bt); }
 int gemv_band_tiles(int N, int sms);
 // row_src_dev[r] (device array of bands*16*bt device pointers): first raw GGUF block of the K
 // slice of destination row r, or null for a padding row

@@ -71,8 +71,21 @@ __device__ __forceinline__ void csync() { asm volatile("bar.sync 1, %0;" ::"n"(k
 
 // chunk range [c0, c1) of slice s when `chunks` chunks are cut into `slices` near-equal slices
 __device__ __forceinline__ void slice_range(int chunks, int slices, int s, int& c0, int& c1) {
-    c0 = int((long(chunks) * s) / slices);
-    c1 = int((long(chunks) * (s + 1)) / slices);
+    if (slices == 1) { c0 = 0; c1 = chunks; return; }
+    c0 = (chunks * s) / slices;  // chunks * slices is far below 2^31
+    c1 = (chunks * (s + 1)) / slices;
+}
+// band and slice of unit u
+__device__ __forceinline__ void unit_split(int u, int slices, int& band, int& slice) {
+    if (slices == 1) { band = u; slice = 0; return; }
+    band = u / slices;
+    slice = u - band * slices;
+}
+// k-blocks per chunk (a power of two: a chunk is always CHUNK_KB * 8 tiles) and chunks per band
+template <int QUANT>
+__device__ __forceinline__ int chunk_kb_shift(int bt) {
+    constexpr int base = (QUANT == FORGE_Q4_0) ? 3 : 2;  // log2(CHUNK_KB)
+    return bt == kBandTiles ? base : base + 3;
 }
 
 // One GEMV ("phase") as the kernels see it.
@@ -103,22 +116,36 @@ struct Shared {
 
 // first unit of CTA `cta` and the stride between its units
 __device__ __forceinline__ int first_unit(const Phase& ph, int cta, int grid) {
+    if (ph.rot == 0) return cta;
     int r = (cta - ph.rot) % grid;
     return r < 0 ? r + grid : r;
 }
 
-// ---- producer side: issue all chunks of this CTA's units of one phase (one batch row)
-template <int QUANT>
-__device__ __forceinline__ bool produce_phase(const Phase& ph, Shared& sh, unsigned char* ring, int& cc) {
+// Ask L2 to fetch this CTA's share of [p, p + bytes) (16-byte aligned; 8 KB pieces dealt round-robin over the grid).
+__device__ __forceinline__ void l2_prefetch_share(const void* p, size_t bytes) {
+    constexpr size_t kPiece = 8192;
+    const char* base = static_cast<const char*>(p);
+    for (size_t off = size_t(blockIdx.x) * kPiece; off < bytes; off += size_t(gridDim.x) * kPiece) {
+        const uint32_t n = uint32_t(min(kPiece, bytes - off)) & ~15u;
+        if (n) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(base + off), "r"(n) : "memory");
+    }
+}
+
+// ---- producer side: issue all chunks of this CTA's units of one phase (one batch row).
+// `when_ring_full()` runs once: when the ring is full for the first time, or after the last chunk if it never fills.
+template <int QUANT, typename Hook>
+__device__ __forceinline__ bool produce_phase(const Phase& ph, Shared& sh, unsigned char* ring, int& cc, Hook when_ring_full) {
     using T = Tile<QUANT>;
-    const int ckb = T::CHUNK_KB * (kBandTiles / ph.bt);  // k-blocks per chunk: a chunk is always CHUNK_KB * 8 tiles
-    const int chunks_per_band = (ph.kb + ckb - 1) / ckb;
+    const int cshift = chunk_kb_shift<QUANT>(ph.bt), ckb = 1 << cshift;
+    const int chunks_per_band = (ph.kb + ckb - 1) >> cshift;
+    bool hooked = false;
     for (int u = first_unit(ph, blockIdx.x, gridDim.x); u < ph.units; u += gridDim.x) {
-        const int band = u / ph.slices;
-        int c0, c1;
-        slice_range(chunks_per_band, ph.slices, u % ph.slices, c0, c1);
+        int band, slice, c0, c1;
+        unit_split(u, ph.slices, band, slice);
+        slice_range(chunks_per_band, ph.slices, slice, c0, c1);
         for (int c = c0; c < c1; ++c, ++cc) {
             const int st = cc % kStages, use = cc / kStages;
+            if (use > 0 && !hooked) { hooked = true; when_ring_full(); }
             if (use > 0 && !mbar_wait(&sh.empty_bar[st], (use - 1) & 1)) { atomicExch(&sh.err, 1); return false; }
             if (*reinterpret_cast<volatile int*>(&sh.err)) return false;
             const int kb0 = c * ckb;
@@ -128,7 +155,12 @@ __device__ __forceinline__ bool produce_phase(const Phase& ph, Shared& sh, unsig
             bulk_g2s(ring + size_t(st) * T::STAGE_BYTES, ph.w + (size_t(band) * ph.kb + kb0) * ph.bt * T::BYTES, bytes, &sh.full_bar[st]);
         }
     }
+    if (!hooked) when_ring_full();
     return true;
+}
+template <int QUANT>
+__device__ __forceinline__ bool produce_phase(const Phase& ph, Shared& sh, unsigned char* ring, int& cc) {
+    return produce_phase<QUANT>(ph, sh, ring, cc, [] {});
 }
 
 // ---- consumer side, step 1: stage one activation row as int8 digit fragments.
@@ -197,7 +229,11 @@ __device__ __forceinline__ float stage_finish(uint2* xf, int4* xoff, Shared& sh,
     m2 *= inv;
     // exact power-of-two scale that puts max|x| * 2^s in [2^25, 2^26): 28-bit signed fixed point
     float sc = 1.0f;
-    if (m2 > 0.f && m2 < 3.0e38f) { int ex = 0; frexpf(m2, &ex); sc = ldexpf(1.0f, 26 - ex); }
+    if (m2 > 0.f && m2 < 3.0e38f) {
+        const int E = int(__float_as_uint(m2) >> 23);  // biased exponent: m2 = f * 2^(E - 126), f in [0.5, 1)
+        if (E >= 25) sc = __uint_as_float(uint32_t(279 - E) << 23);
+        else { int ex = 0; frexpf(m2, &ex); sc = ldexpf(1.0f, 26 - ex); }
+    }
     // balanced base-128 digits without carries: with y = x + 64 * (1 + 128 + 128^2 + 128^3), digit c of x
     // is ((y >> 7c) & 127) - 64 for c < 3 and (y >> 21) - 64 for the last one
     constexpr int kBias = 64 * (1 + 128 + 128 * 128 + 128 * 128 * 128);
@@ -262,35 +298,72 @@ __device__ __forceinline__ float stage_activation(uint2* xf, int4* xoff, Shared&
 }
 
 // ---- epilogue of one finished output row (runtime-selected fusion)
-__device__ __forceinline__ void epilogue_row(const Phase& ph, int b, int row, float v, float partner) {
+// Operands that do not depend on the product, for the rows row0 (index 0) and row0 + 8 (index 1) of a thread.
+struct EpiPre {
+    float resid[2];  // EPI_RESID
+    float bias[2][2];  // EPI_QKV: bias of (row, row + 1)
+    float2 cs[2];    // EPI_QKV: rotation of the pair
+    int pos, page;   // EPI_QKV: position and physical page of the new cache row
+};
+
+__device__ __forceinline__ EpiPre epilogue_prefetch(const Phase& ph, int b, int row0, bool mine) {
+    EpiPre e;
+    e.resid[0] = e.resid[1] = 0.f;
+    e.bias[0][0] = e.bias[0][1] = e.bias[1][0] = e.bias[1][1] = 0.f;
+    e.cs[0] = e.cs[1] = make_float2(1.f, 0.f);
+    e.pos = 0; e.page = 0;
+    if (!mine) return e;
+    const GemvArgs& a = ph.a;
+    if (ph.epi == EPI_RESID) {
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const int row = row0 + 8 * j;
+            if (row < ph.N) e.resid[j] = __ldcg(a.resid + size_t(b) * ph.N + row);
+        }
+    } else if (ph.epi == EPI_QKV && (row0 & 1) == 0) {
+        e.pos = a.seq_len[b];
+        e.page = a.page_table[size_t(b) * a.pages_per_seq + e.pos / FORGE_KV_PAGE];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const int row = row0 + 8 * j;
+            if (row >= ph.N) continue;
+            if (a.bias) { e.bias[j][0] = a.bias[row]; e.bias[j][1] = a.bias[row + 1]; }
+            if (row < a.qk + a.kv) {
+                const int col = row < a.qk ? row : row - a.qk;
+                e.cs[j] = reinterpret_cast<const float2*>(a.rope)[size_t(e.pos) * (a.head_dim / 2) + (col % a.head_dim) / 2];
+            }
+        }
+    }
+    return e;
+}
+
+__device__ __forceinline__ void epilogue_row(const Phase& ph, int b, int row, float v, float partner, const EpiPre& pre, int j) {
     if (row >= ph.N) return;
     const GemvArgs& a = ph.a;
     if (ph.epi == EPI_STORE) {
         a.out[size_t(b) * ph.N + row] = v;
     } else if (ph.epi == EPI_RESID) {
-        a.out[size_t(b) * ph.N + row] = __ldcg(a.resid + size_t(b) * ph.N + row) + v;
+        a.out[size_t(b) * ph.N + row] = pre.resid[j] + v;
     } else if (ph.epi == EPI_SILU) {
         if ((row & 1) == 0)  // rows interleaved at pack time: 2j = gate_j, 2j+1 = up_j
             a.out[size_t(b) * (ph.N / 2) + (row >> 1)] = (v / (1.0f + expf(-v))) * partner;
     } else if ((row & 1) == 0) {  // EPI_QKV: the thread of the even row handles the (even, odd) pair
-        float q0 = v, q1 = partner;
-        if (a.bias) { q0 += a.bias[row]; q1 += a.bias[row + 1]; }
-        const int pos = a.seq_len[b];
-        const int qk = a.qk, kv = a.kv, hd = a.head_dim;
+        float q0 = v + pre.bias[j][0], q1 = partner + pre.bias[j][1];
+        const int pos = pre.pos;
+        const int qk = a.qk, kv = a.kv;
         int col = row, region = 0;
         if (col >= qk) { col -= qk; region = 1; }
         if (region == 1 && col >= kv) { col -= kv; region = 2; }
         if (region < 2) {
-            const float2 cs = reinterpret_cast<const float2*>(a.rope)[size_t(pos) * (hd / 2) + (col % hd) / 2];
+            const float2 cs = pre.cs[j];
             const float r0 = q0 * cs.x - q1 * cs.y, r1 = q0 * cs.y + q1 * cs.x;
             q0 = r0; q1 = r1;
         }
         if (region == 0) {
             *reinterpret_cast<float2*>(a.q_out + size_t(b) * qk + col) = make_float2(q0, q1);
         } else {
-            const int page = a.page_table[size_t(b) * a.pages_per_seq + pos / FORGE_KV_PAGE];
             __half* pool = region == 1 ? a.k_pool : a.v_pool;
-            *reinterpret_cast<__half2*>(pool + (size_t(page) * FORGE_KV_PAGE + pos % FORGE_KV_PAGE) * kv + col) =
+            *reinterpret_cast<__half2*>(pool + (size_t(pre.page) * FORGE_KV_PAGE + pos % FORGE_KV_PAGE) * kv + col) =
                 __floats2half2_rn(q0, q1);
         }
     }
@@ -305,16 +378,23 @@ __device__ __forceinline__ void consume_phase(const Phase& ph, Shared& sh, const
     using T = Tile<QUANT>;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
-    const int bt = ph.bt, kparts = kConsumerWarps / bt;            // warps sharing one row tile
-    const int r8 = warp % bt, khalf = warp / bt;                    // row tile within the band, k part of this warp
+    const int bt = ph.bt;
+    const bool wide = bt == kBandTiles;
+    const int kparts = wide ? kConsumerWarps / kBandTiles : kConsumerWarps;  // warps sharing one row tile
+    const int r8 = wide ? warp % kBandTiles : 0;                              // row tile within the band
+    const int khalf = wide ? warp / kBandTiles : warp;                        // k part of this warp
     const int KB = ph.kb;
-    const int ckb = T::CHUNK_KB * (kBandTiles / bt);
-    const int chunks_per_band = (KB + ckb - 1) / ckb;
+    const int cshift = chunk_kb_shift<QUANT>(bt), ckb = 1 << cshift;
+    const int chunks_per_band = (KB + ckb - 1) >> cshift;
     int ui = 0;
     for (int u = first_unit(ph, blockIdx.x, gridDim.x); u < ph.units; u += gridDim.x, ++ui) {
-        const int band = u / ph.slices, slice = u % ph.slices;
-        int c0, c1;
+        int band, slice, c0, c1;
+        unit_split(u, ph.slices, band, slice);
         slice_range(chunks_per_band, ph.slices, slice, c0, c1);
+        const int rt = band * bt + r8;
+        const int row0 = rt * 16 + g;  // and row0 + 8
+        // operands of the epilogue that do not depend on the product are fetched now, under the tile loop
+        const EpiPre pre = epilogue_prefetch(ph, b, row0, t == 0 && khalf == 0);
         // per-lane accumulators: rows g / g+8 of this warp's row tile x digit columns 2t / 2t+1
         float acc[4] = {0.f, 0.f, 0.f, 0.f};
         for (int c = c0; c < c1; ++c, ++cc) {
@@ -385,8 +465,6 @@ __device__ __forceinline__ void consume_phase(const Phase& ph, Shared& sh, const
         }
         v0 *= unscale;
         v1 *= unscale;
-        const int rt = band * bt + r8;
-        const int row0 = rt * 16 + g;  // and row0 + 8
         bool finish = true;
         if (ph.epi == EPI_PARTIAL) {
             // raw partial sums of this K slice; whoever reads them adds the slices in order
@@ -430,8 +508,8 @@ __device__ __forceinline__ void consume_phase(const Phase& ph, Shared& sh, const
         // pair partners (rows r^1) live in the neighbouring quad
         const float o0 = __shfl_xor_sync(0xffffffffu, v0, 4), o1 = __shfl_xor_sync(0xffffffffu, v1, 4);
         if (finish && t == 0) {
-            epilogue_row(ph, b, row0, v0, o0);
-            epilogue_row(ph, b, row0 + 8, v1, o1);
+            epilogue_row(ph, b, row0, v0, o0, pre, 0);
+            epilogue_row(ph, b, row0 + 8, v1, o1, pre, 1);
             on_row(row0, v0);
             on_row(row0 + 8, v1);
         }

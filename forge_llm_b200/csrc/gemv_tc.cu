@@ -28,6 +28,7 @@
 // [128-row band][k-block][row tile within band], so a chunk (a run of k-blocks of one band) is
 // one contiguous, 16-byte aligned bulk copy.
 #include <algorithm>
+#include <cstdlib>
 
 #include "gemv_core.cuh"
 
@@ -65,7 +66,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tc_kernel(TcParams p) {
     if (warp == kConsumerWarps) {
         if ((tid & 31) == 0)
             for (int b = 0; b < ph.a.batch; ++b)
-                if (!produce_phase<QUANT>(ph, sh, ring, cc)) break;
+                if (!produce_phase<QUANT>(ph, sh, ring, cc, [&] { if (b == 0) l2_prefetch_share(ph.a.next_w, ph.a.next_bytes); })) break;
         return;
     }
     // everything above (and the producer's weight stream) is independent of earlier kernels; the activation is not
@@ -169,9 +170,16 @@ int gemv_slices(const QTiled& w, const GemvSplit& sp, int sms, int batch) {
     return slices < 1 ? 1 : slices;
 }
 
-// Row tiles per band for an N-row matrix: the wide form (8 tiles, two warps per tile, no CTA-level
-// reduction) when there are at least four bands per SM, else one tile per band (finer units for balance).
-int gemv_band_tiles(int N, int sms) { return ((N + 127) / 128 >= 4 * sms) ? core::kBandTiles : 1; }
+// Row tiles per band for an N-row matrix.  The wide form (8 tiles = 128 rows per band, two warps per tile, no
+// CTA-level reduction per unit) streams fastest but comes in coarse units; it is used when whole rounds of 128-row
+// bands keep at least 80 % of the SMs busy.  Otherwise one tile per band (16-row units, all warps share the tile).
+int gemv_band_tiles(int N, int sms) {
+    static const int force = [] { const char* e = getenv("FORGE_B200_BAND_TILES"); return e ? atoi(e) : 0; }();
+    if (force == 1 || force == core::kBandTiles) return force;
+    const int wide = (N + 127) / 128;
+    const int rounds = (wide + sms - 1) / sms;
+    return (5 * wide >= 4 * rounds * sms) ? core::kBandTiles : 1;
+}
 
 size_t qtiled_bytes(int quant, int K, int N, int bt) {
     const size_t bands = size_t((N + 16 * bt - 1) / (16 * bt));

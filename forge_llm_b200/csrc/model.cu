@@ -263,18 +263,25 @@ int32_t decode_launches(ForgeModel* m, ForgeKV* kv, int batch, bool greedy, bool
         a.bias = L.qkv_bias; a.rope = m->rope; a.q_out = m->d_q; a.k_pool = kp; a.v_pool = vp;
         a.page_table = kv->d_page_table; a.seq_len = kv->d_seq_len; a.pages_per_seq = kv->pages_per_seq;
         a.qk = m->qk; a.kv = m->kv; a.head_dim = m->hd;
+        a.next_w = L.o_t.data; a.next_bytes = qtiled_bytes(L.o_t);
         FORGE_TRY(gemv_tc(L.qkv_t, EPI_QKV, a, m->split, m->d_err, st));
         AttnDecodeArgs da{m->d_attn, m->d_q, kp, vp, kv->d_page_table, kv->pages_per_seq, kv->d_seq_len, 0,
                           batch, m->nq, m->nkv, m->hd, kv->max_seq, kv->attn_ws, kv->attn_counters, kv->splits};
         FORGE_TRY(attn_decode(da, st));
         GemvArgs o;
         o.x = m->d_attn; o.out = m->d_hidden; o.resid = m->d_hidden; o.batch = batch;
+        o.next_w = L.gateup_t.data; o.next_bytes = qtiled_bytes(L.gateup_t);
         FORGE_TRY(gemv_tc(L.o_t, EPI_RESID, o, m->split, m->d_err, st));
         GemvArgs g;
         g.x = m->d_hidden; g.norm_w = L.ffn_norm; g.eps = c.rms_norm_eps; g.out = m->d_act; g.batch = batch;
+        g.next_w = L.down_t.data; g.next_bytes = qtiled_bytes(L.down_t);
         FORGE_TRY(gemv_tc(L.gateup_t, EPI_SILU, g, m->split, m->d_err, st));
         GemvArgs d;
         d.x = m->d_act; d.out = m->d_hidden; d.resid = m->d_hidden; d.batch = batch;
+        {   // the next projection on the stream: the next layer's QKV, or the head (a part of it: it is larger than L2)
+            const QTiled& nx = l + 1 < c.num_layers ? m->layers[l + 1].qkv_t : m->lm_head_t;
+            d.next_w = nx.data; d.next_bytes = std::min(qtiled_bytes(nx), size_t(48) << 20);
+        }
         FORGE_TRY(gemv_tc(L.down_t, EPI_RESID, d, m->split, m->d_err, st));
         if (m->trace_on)
             FORGE_CUDA(cudaMemcpyAsync(m->trace + size_t(l) * batch * m->h, m->d_hidden, sizeof(float) * batch * m->h, cudaMemcpyDeviceToDevice, st));
