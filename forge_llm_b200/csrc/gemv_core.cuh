@@ -6,8 +6,8 @@
 // tiled weight layout - into a ring of shared-memory stages.  Two consumer warps share each of
 // the band's eight 16-row tiles (even / odd k-blocks) and turn every 16 x 32 tile into one
 // integer tensor-core product (mma.sync m16n8k32, s8/u8 x s8 -> s32) against the activation held
-// in shared memory as four balanced base-128 digits of a 28-bit fixed-point value; digit sums
-// are scaled by the f16 block scale and accumulated in f32.  See gemv_tc.cu for the layout.
+// in shared memory as the four balanced base-256 digits (bytes) of a 31-bit fixed-point value; digit
+// sums are scaled by the f16 block scale and accumulated in f32.  See gemv_tc.cu for the layout.
 #pragma once
 
 #include "common.cuh"
@@ -227,21 +227,21 @@ __device__ __forceinline__ float stage_finish(uint2* xf, int4* xoff, Shared& sh,
     for (int w = 0; w < kConsumerWarps; ++w) { s2 += sh.part[w]; m2 = fmaxf(m2, sh.part[16 + w]); }
     const float inv = norm_w ? 1.0f / sqrtf(s2 / float(K) + eps) : 1.0f;
     m2 *= inv;
-    // exact power-of-two scale that puts max|x| * 2^s in [2^25, 2^26): 28-bit signed fixed point
+    // exact power-of-two scale that puts max|x| * 2^s in [2^29, 2^30): 31-bit signed fixed point
     float sc = 1.0f;
     if (m2 > 0.f && m2 < 3.0e38f) {
         const int E = int(__float_as_uint(m2) >> 23);  // biased exponent: m2 = f * 2^(E - 126), f in [0.5, 1)
-        if (E >= 25) sc = __uint_as_float(uint32_t(279 - E) << 23);
-        else { int ex = 0; frexpf(m2, &ex); sc = ldexpf(1.0f, 26 - ex); }
+        if (E >= 29) sc = __uint_as_float(uint32_t(283 - E) << 23);
+        else { int ex = 0; frexpf(m2, &ex); sc = ldexpf(1.0f, 30 - ex); }
     }
-    // balanced base-128 digits without carries: with y = x + 64 * (1 + 128 + 128^2 + 128^3), digit c of x
-    // is ((y >> 7c) & 127) - 64 for c < 3 and (y >> 21) - 64 for the last one
-    constexpr int kBias = 64 * (1 + 128 + 128 * 128 + 128 * 128 * 128);
+    // Balanced base-256 digits without carries or bit-field extraction: with y = x + 0x80808080 (no wrap for
+    // |x| < 2^30), byte c of y is digit c of x plus 128, so the digits are the bytes of y ^ 0x80808080.  Four
+    // values are turned into four digit words (byte j = value j) by a 4 x 4 byte transpose.
     for (int i0 = 0; i0 < KB * 4; i0 += kCT) {
         const int i = i0 + tid;
         const bool on = i < KB * 4;
         const int kbi = i >> 2, tt = i & 3;
-        int y[8];
+        uint32_t y[8];
         if (on) {
             const float4 r0 = *reinterpret_cast<const float4*>(xraw + kbi * 32 + 4 * tt);
             const float4 r1 = *reinterpret_cast<const float4*>(xraw + kbi * 32 + 16 + 4 * tt);
@@ -254,21 +254,25 @@ __device__ __forceinline__ float stage_finish(uint2* xf, int4* xoff, Shared& sh,
                 for (int q = 0; q < 8; ++q) xv[q] = xv[q] * inv * nw[q];
             }
 #pragma unroll
-            for (int q = 0; q < 8; ++q) y[q] = __float2int_rn(xv[q] * sc) + kBias;
+            for (int q = 0; q < 8; ++q) y[q] = uint32_t(__float2int_rn(xv[q] * sc)) + 0x80808080u;
         }
         __syncwarp();  // all four readers of a k-block are done before it is overwritten
         int dsum[4] = {0, 0, 0, 0};
         if (on) {
+            uint32_t w[2][4];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const uint32_t a = __byte_perm(y[4 * h], y[4 * h + 1], 0x5140), b = __byte_perm(y[4 * h + 2], y[4 * h + 3], 0x5140);
+                const uint32_t c = __byte_perm(y[4 * h], y[4 * h + 1], 0x7362), d = __byte_perm(y[4 * h + 2], y[4 * h + 3], 0x7362);
+                w[h][0] = __byte_perm(a, b, 0x5410) ^ 0x80808080u;
+                w[h][1] = __byte_perm(a, b, 0x7632) ^ 0x80808080u;
+                w[h][2] = __byte_perm(c, d, 0x5410) ^ 0x80808080u;
+                w[h][3] = __byte_perm(c, d, 0x7632) ^ 0x80808080u;
+            }
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
-                uint32_t w2[2] = {0u, 0u};
-#pragma unroll
-                for (int q = 0; q < 8; ++q) {
-                    const int dgt = ((c < 3) ? ((y[q] >> (7 * c)) & 127) : (y[q] >> 21)) - 64;
-                    dsum[c] += dgt;
-                    w2[q >> 2] |= uint32_t(dgt & 0xFF) << (8 * (q & 3));
-                }
-                xf[(kbi * 4 + c) * 4 + tt] = make_uint2(w2[0], w2[1]);
+                dsum[c] = __dp4a(int(w[0][c]), 0x01010101, __dp4a(int(w[1][c]), 0x01010101, 0));
+                xf[(kbi * 4 + c) * 4 + tt] = make_uint2(w[0][c], w[1][c]);
             }
         }
         if (QUANT == FORGE_Q4_0) {
@@ -306,7 +310,8 @@ struct EpiPre {
     int pos, page;   // EPI_QKV: position and physical page of the new cache row
 };
 
-__device__ __forceinline__ EpiPre epilogue_prefetch(const Phase& ph, int b, int row0, bool mine) {
+// pos_hint: the sequence position if the caller has already fetched it (saves a dependent load), else -1
+__device__ __forceinline__ EpiPre epilogue_prefetch(const Phase& ph, int b, int row0, bool mine, int pos_hint) {
     EpiPre e;
     e.resid[0] = e.resid[1] = 0.f;
     e.bias[0][0] = e.bias[0][1] = e.bias[1][0] = e.bias[1][1] = 0.f;
@@ -321,7 +326,7 @@ __device__ __forceinline__ EpiPre epilogue_prefetch(const Phase& ph, int b, int 
             if (row < ph.N) e.resid[j] = __ldcg(a.resid + size_t(b) * ph.N + row);
         }
     } else if (ph.epi == EPI_QKV && (row0 & 1) == 0) {
-        e.pos = a.seq_len[b];
+        e.pos = pos_hint >= 0 ? pos_hint : a.seq_len[b];
         e.page = a.page_table[size_t(b) * a.pages_per_seq + e.pos / FORGE_KV_PAGE];
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
@@ -374,7 +379,7 @@ __device__ __forceinline__ void epilogue_row(const Phase& ph, int b, int row, fl
 // kernel to track the arg-max of the logits); pass a no-op otherwise.
 template <int QUANT, typename RowHook>
 __device__ __forceinline__ void consume_phase(const Phase& ph, Shared& sh, const unsigned char* ring, const uint2* xf,
-                                              const int4* xoff, float unscale, int b, int& cc, RowHook on_row) {
+                                              const int4* xoff, float unscale, int b, int& cc, RowHook on_row, int pos_hint = -1) {
     using T = Tile<QUANT>;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
@@ -394,7 +399,7 @@ __device__ __forceinline__ void consume_phase(const Phase& ph, Shared& sh, const
         const int rt = band * bt + r8;
         const int row0 = rt * 16 + g;  // and row0 + 8
         // operands of the epilogue that do not depend on the product are fetched now, under the tile loop
-        const EpiPre pre = epilogue_prefetch(ph, b, row0, t == 0 && khalf == 0);
+        const EpiPre pre = epilogue_prefetch(ph, b, row0, t == 0 && khalf == 0, pos_hint);
         // per-lane accumulators: rows g / g+8 of this warp's row tile x digit columns 2t / 2t+1
         float acc[4] = {0.f, 0.f, 0.f, 0.f};
         for (int c = c0; c < c1; ++c, ++cc) {
@@ -436,9 +441,9 @@ __device__ __forceinline__ void consume_phase(const Phase& ph, Shared& sh, const
             if (lane == 0) mbar_arrive(&sh.empty_bar[st]);
         }
         // ---- the warp's part of this unit is complete: combine digits (quad lanes 0 and 1)
-        const float wgt = (t == 0) ? 1.0f : 16384.0f;  // lane 0: digits 0,1; lane 1: digits 2,3
+        const float wgt = (t == 0) ? 1.0f : 65536.0f;  // lane 0: digits 0,1; lane 1: digits 2,3 (base 256)
         const float w1 = (QUANT == FORGE_Q4_0) ? wgt * 0.0625f : wgt;  // Q4_0 rows g+8 were carried as 16 n
-        float v0 = (acc[0] + 128.0f * acc[1]) * wgt, v1 = (acc[2] + 128.0f * acc[3]) * w1;
+        float v0 = (acc[0] + 256.0f * acc[1]) * wgt, v1 = (acc[2] + 256.0f * acc[3]) * w1;
         v0 += __shfl_xor_sync(0xffffffffu, v0, 1);
         v1 += __shfl_xor_sync(0xffffffffu, v1, 1);
         if (bt == kBandTiles) {

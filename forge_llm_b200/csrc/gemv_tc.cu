@@ -10,12 +10,12 @@
 // 32-column tile (one quantisation block per row) into ONE integer tensor-core product,
 // mma.sync m16n8k32 s8 x s8 -> s32:
 //   A = the quantised weights as they are (Q8_0 bytes; Q4_0 nibbles split into bytes),
-//   B = the f32 activation in fixed point, x * 2^s rounded to a 28-bit integer and cut into four
-//       balanced base-128 digits, one digit per B column,
+//   B = the f32 activation in fixed point, x * 2^s rounded to a 31-bit integer whose four balanced
+//       base-256 digits (the bytes of x + 0x80808080, each minus 128) fill one B column each,
 // so the 32-term integer dot products are exact; each digit's sum is converted to f32,
 // multiplied by the row's f16 block scale and accumulated in f32, and the four digit
 // accumulators are combined once per row.  The result is the reference's f32 arithmetic up to
-// summation order (the activation keeps 2^-27 of its largest magnitude; it is never quantised
+// summation order (the activation keeps 2^-30 of its largest magnitude; it is never quantised
 // to 8 bits).  Warps never synchronise with each other after the activation is staged.
 //
 // Small matrices are split along K over several CTAs ("slices"); every slice writes its 16
@@ -72,8 +72,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tc_kernel(TcParams p) {
     // everything above (and the producer's weight stream) is independent of earlier kernels; the activation is not
     pdl_wait();
     for (int b = 0; b < ph.a.batch; ++b) {
+        // the position of the new cache row is needed late (epilogue) but heads a chain of dependent loads: ask now
+        const int pos = ph.epi == EPI_QKV ? ph.a.seq_len[b] : -1;
         const float unscale = stage_activation<QUANT, false>(xf, s_xoff, sh, ph.a.x + size_t(b) * ph.K, ph.K, ph.a.norm_w, ph.a.eps);
-        consume_phase<QUANT>(ph, sh, ring, xf, s_xoff, unscale, b, cc, [](int, float) {});
+        consume_phase<QUANT>(ph, sh, ring, xf, s_xoff, unscale, b, cc, [](int, float) {}, pos);
     }
     csync();
     if (tid == 0 && sh.err && p.err) atomicExch(p.err, 1);
