@@ -14,7 +14,7 @@ CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(CSRC, "build")
 LIB = os.path.join(HERE, "libforge_b200.so")
 SOURCES = ["pack.cu", "gemv_tc.cu", "decode_mega.cu", "elementwise.cu", "attn_decode.cu", "attn_prefill.cu", "gemm_mma.cu", "gemm_tc5.cu",
-           "api_ops.cu", "model.cu"]
+           "tp_comm.cu", "api_ops.cu", "model.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC,-fopenmp,-O3", "-Xptxas", "-v"]
 
@@ -55,7 +55,7 @@ def build_library(force: bool = False, verbose: bool = False) -> str:
         results = list(ex.map(compile_one, SOURCES))
     objs = [o for o, _ in results]
     if force or any(c for _, c in results) or not os.path.exists(LIB):
-        r = subprocess.run([nvcc, "--shared", "-o", LIB, *objs, "-Xcompiler", "-fopenmp", "-lgomp"],
+        r = subprocess.run([nvcc, "--shared", "-o", LIB, *objs, "-Xcompiler", "-fopenmp", "-lgomp", "-ldl"],
                            capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")

@@ -57,6 +57,13 @@ struct QWeight {
 int32_t pack_rows(const uint8_t* raw_dev, int quant, int K_full, int row0, int rows, int blk0, int blks,
                   QWeight& dst, int dst_row0, int row_step, cudaStream_t st);
 
+// ------------------------------------------------------------------ tensor-parallel sum (tp_comm.cu)
+struct TpComm;
+int32_t tp_unique_id(uint8_t* out);
+int32_t tp_init(TpComm** out, const uint8_t* id_bytes, int rank, int world);
+int32_t tp_allreduce_sum(TpComm* c, float* buf, size_t n, cudaStream_t st);  // in place, on st
+void tp_destroy(TpComm* c);
+
 // ------------------------------------------------------------------ programmatic dependent launch
 // A kernel launched with launch_pdl() may start while the kernel before it on the stream is still running.
 // It must execute pdl_wait() before it touches anything an earlier kernel writes (the wait returns when the earlier

@@ -68,6 +68,8 @@ struct ForgeModel {
     __half* p_attn16 = nullptr; float* p_gu = nullptr; __half* p_act16 = nullptr; uint32_t* p_tokens = nullptr;
     __half* p_normed_lo = nullptr; __half* p_attn16_lo = nullptr; __half* p_act16_lo = nullptr;
     int gemm_passes = 3;  // 3: split-precision prefill GEMMs (default); 1: single fp16 pass
+    TpComm* tp = nullptr;  // tensor-parallel communicator (cfg.tp_world > 1)
+    float* p_part = nullptr; float* d_part = nullptr;  // this rank's partial sums of a row-sliced projection
     bool use_mega = false; // batch-1 decode through the whole-step kernel (forge_model_set_decode_mode)
     // decode scratch (per batch row)
     int dec_batch = 0;
@@ -145,6 +147,7 @@ int32_t ensure_prefill_scratch(ForgeModel* m, int rows) {
     FORGE_TRY(dev_alloc(m, &m->p_normed_lo, r * m->h));
     FORGE_TRY(dev_alloc(m, &m->p_attn16_lo, r * m->qk));
     FORGE_TRY(dev_alloc(m, &m->p_act16_lo, r * m->ff));
+    if (m->cfg.tp_world > 1) FORGE_TRY(dev_alloc(m, &m->p_part, r * m->h));
     m->scratch_rows = rows;
     return FORGE_OK;
 }
@@ -164,6 +167,7 @@ int32_t ensure_decode_scratch(ForgeModel* m, int batch) {
     FORGE_TRY(dev_alloc(m, &m->d_amax_ticket, b));
     FORGE_CUDA(cudaMemsetAsync(m->d_amax_ticket, 0, sizeof(int) * b, m->stream));
     if (!m->d_step) { FORGE_TRY(dev_alloc(m, &m->d_step, 1)); }
+    if (m->cfg.tp_world > 1) FORGE_TRY(dev_alloc(m, &m->d_part, b * m->h));
     m->dec_batch = batch;
     return FORGE_OK;
 }
@@ -205,6 +209,22 @@ int32_t upload_len(ForgeKV* kv) {
     return FORGE_OK;
 }
 
+// hidden += W x for a projection whose K dimension is sliced over the tensor-parallel ranks: the ranks' partial
+// products are summed (all-reduce) before the residual is added, so every rank holds the same hidden state
+int32_t row_sliced_gemm(ForgeModel* m, const QWeight& w, const __half* a, const __half* alo, int n, cudaStream_t st) {
+    if (m->cfg.tp_world == 1) return gemm_f16a(m->p_hidden, a, alo, w, n, m->p_hidden, m->d_err, st);
+    FORGE_TRY(gemm_f16a(m->p_part, a, alo, w, n, nullptr, m->d_err, st));
+    FORGE_TRY(tp_allreduce_sum(m->tp, m->p_part, size_t(n) * m->h, st));
+    return residual_add_f32(m->p_hidden, m->p_part, size_t(n) * m->h, st);
+}
+int32_t row_sliced_gemv(ForgeModel* m, const QTiled& w, GemvArgs a, int batch, cudaStream_t st) {
+    if (m->cfg.tp_world == 1) return gemv_tc(w, EPI_RESID, a, m->split, m->d_err, st);
+    a.out = m->d_part; a.resid = nullptr;
+    FORGE_TRY(gemv_tc(w, EPI_STORE, a, m->split, m->d_err, st));
+    FORGE_TRY(tp_allreduce_sum(m->tp, m->d_part, size_t(batch) * m->h, st));
+    return residual_add_f32(m->d_hidden, m->d_part, size_t(batch) * m->h, st);
+}
+
 // ------------------------------------------------------------------ prefill of one sequence
 // forward_prefill_batched, emit.rs:5118-5486.  Leaves the last row's logits in m->d_logits[0..V).
 int32_t prefill_seq(ForgeModel* m, ForgeKV* kv, int seq, const uint32_t* tokens_host, int n) {
@@ -231,11 +251,11 @@ int32_t prefill_seq(ForgeModel* m, ForgeKV* kv, int seq, const uint32_t* tokens_
         FORGE_TRY(qkv_post(m->p_qkv, n, base, L.qkv_bias, m->rope, m->p_q16, kp, vp, page_row, m->qk, m->kv, m->hd, st));
         AttnPrefillArgs pa{m->p_attn16, alo, nullptr, m->p_q16, kp, vp, page_row, n, base, m->nq, m->nkv, m->hd};
         FORGE_TRY(attn_prefill(pa, st));
-        FORGE_TRY(gemm_f16a(m->p_hidden, m->p_attn16, alo, L.o, n, m->p_hidden, m->d_err, st));
+        FORGE_TRY(row_sliced_gemm(m, L.o, m->p_attn16, alo, n, st));
         FORGE_TRY(rms_norm_f16(m->p_normed, nlo, m->p_hidden, L.ffn_norm, n, m->h, c.rms_norm_eps, st));
         FORGE_TRY(gemm_f16a(m->p_gu, m->p_normed, nlo, L.gateup, n, nullptr, m->d_err, st));
         FORGE_TRY(silu_mul_f16(m->p_act16, flo, m->p_gu, n, m->ff, st));
-        FORGE_TRY(gemm_f16a(m->p_hidden, m->p_act16, flo, L.down, n, m->p_hidden, m->d_err, st));
+        FORGE_TRY(row_sliced_gemm(m, L.down, m->p_act16, flo, n, st));
         if (m->trace_on)
             FORGE_CUDA(cudaMemcpyAsync(m->trace + size_t(l) * n * m->h, m->p_hidden, sizeof(float) * n * m->h, cudaMemcpyDeviceToDevice, st));
     }
@@ -271,7 +291,7 @@ int32_t decode_launches(ForgeModel* m, ForgeKV* kv, int batch, bool greedy, bool
         GemvArgs o;
         o.x = m->d_attn; o.out = m->d_hidden; o.resid = m->d_hidden; o.batch = batch;
         o.next_w = L.gateup_t.data; o.next_bytes = qtiled_bytes(L.gateup_t);
-        FORGE_TRY(gemv_tc(L.o_t, EPI_RESID, o, m->split, m->d_err, st));
+        FORGE_TRY(row_sliced_gemv(m, L.o_t, o, batch, st));
         GemvArgs g;
         g.x = m->d_hidden; g.norm_w = L.ffn_norm; g.eps = c.rms_norm_eps; g.out = m->d_act; g.batch = batch;
         g.next_w = L.down_t.data; g.next_bytes = qtiled_bytes(L.down_t);
@@ -282,7 +302,7 @@ int32_t decode_launches(ForgeModel* m, ForgeKV* kv, int batch, bool greedy, bool
             const QTiled& nx = l + 1 < c.num_layers ? m->layers[l + 1].qkv_t : m->lm_head_t;
             d.next_w = nx.data; d.next_bytes = std::min(qtiled_bytes(nx), size_t(48) << 20);
         }
-        FORGE_TRY(gemv_tc(L.down_t, EPI_RESID, d, m->split, m->d_err, st));
+        FORGE_TRY(row_sliced_gemv(m, L.down_t, d, batch, st));
         if (m->trace_on)
             FORGE_CUDA(cudaMemcpyAsync(m->trace + size_t(l) * batch * m->h, m->d_hidden, sizeof(float) * batch * m->h, cudaMemcpyDeviceToDevice, st));
     }
@@ -318,7 +338,7 @@ int32_t decode_step_one_kernel(ForgeModel* m, ForgeKV* kv, bool greedy) {
 
 int32_t decode_step_graph(ForgeModel* m, ForgeKV* kv, int batch, bool greedy) {
     if (m->trace_on) return decode_launches(m, kv, batch, greedy, greedy);
-    if (batch == 1 && m->use_mega && kv->d_phases && kv->mega_grid <= kArgmaxSlices && (m->nq / m->nkv) * m->hd <= 512) return decode_step_one_kernel(m, kv, greedy);
+    if (batch == 1 && m->use_mega && m->cfg.tp_world == 1 && kv->d_phases && kv->mega_grid <= kArgmaxSlices && (m->nq / m->nkv) * m->hd <= 512) return decode_step_one_kernel(m, kv, greedy);
     if (!kv->graph || kv->graph_batch != batch || kv->graph_greedy != greedy) {
         if (kv->graph) { cudaGraphExecDestroy(kv->graph); kv->graph = nullptr; }
         cudaGraph_t g = nullptr;
@@ -497,6 +517,7 @@ void forge_model_destroy(ForgeModel* m) {
     if (!m) return;
     cudaSetDevice(m->device);
     if (m->stream) cudaStreamSynchronize(m->stream);
+    tp_destroy(m->tp);
     for (void* q : m->allocs) cudaFree(q);
     for (auto& e : m->ev) if (e) cudaEventDestroy(e);
     if (m->stream) cudaStreamDestroy(m->stream);
@@ -504,6 +525,19 @@ void forge_model_destroy(ForgeModel* m) {
 }
 
 void* forge_model_stream(ForgeModel* m) { return m ? static_cast<void*>(m->stream) : nullptr; }
+
+int32_t forge_tp_unique_id(uint8_t* id_out) {
+    if (!id_out) { set_error("null id buffer"); return FORGE_ERR_INVALID_ARG; }
+    return tp_unique_id(id_out);
+}
+
+int32_t forge_model_tp_init(ForgeModel* m, const uint8_t* id) {
+    if (!m || !id) { set_error("bad argument to forge_model_tp_init"); return FORGE_ERR_INVALID_ARG; }
+    if (m->cfg.tp_world < 2) { set_error("the model was created with tp_world = 1"); return FORGE_ERR_INVALID_ARG; }
+    if (m->tp) { set_error("the model already has a communicator"); return FORGE_ERR_INVALID_ARG; }
+    FORGE_CUDA(cudaSetDevice(m->device));
+    return tp_init(&m->tp, id, m->cfg.tp_rank, m->cfg.tp_world);
+}
 
 int32_t forge_kv_create(ForgeModel* m, int32_t max_seq, int32_t batch, ForgeKV** out) {
     if (!m || !out || max_seq <= 0 || batch <= 0) { set_error("bad argument to forge_kv_create"); return FORGE_ERR_INVALID_ARG; }

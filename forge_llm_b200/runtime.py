@@ -82,6 +82,9 @@ class KVCache:
             pass
 
 
+TP_ID_BYTES = 128  # FORGE_TP_ID_BYTES
+
+
 class Model:
     """``Weights`` + ``forward`` / ``forward_prefill`` of the generated module."""
 
@@ -98,6 +101,20 @@ class Model:
     @property
     def stream(self) -> int:
         return int(lib.forge_model_stream(self._h) or 0)
+
+    @staticmethod
+    def tp_unique_id() -> np.ndarray:
+        """Rendezvous id for the tensor-parallel ranks (rank 0 creates it, the others receive it)."""
+        out = np.zeros(TP_ID_BYTES, np.uint8)
+        check(lib.forge_tp_unique_id(_p(out)))
+        return out
+
+    def tp_init(self, unique_id: np.ndarray) -> None:
+        """Joins the tensor-parallel group (collective over all ``tp_world`` ranks)."""
+        uid = np.ascontiguousarray(unique_id, np.uint8)
+        if uid.size != TP_ID_BYTES:
+            raise ValueError(f"the rendezvous id is {TP_ID_BYTES} bytes")
+        check(lib.forge_model_tp_init(self._h, _p(uid)))
 
     def new_cache(self, max_seq: int | None = None, batch: int = 1) -> KVCache:
         return KVCache(self, max_seq, batch)

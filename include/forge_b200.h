@@ -169,6 +169,18 @@ void forge_model_destroy(ForgeModel* model);
 /* The CUDA stream (cudaStream_t) all work of this model is launched on. */
 void* forge_model_stream(ForgeModel* model);
 
+/* Tensor parallelism (one process per GPU, cfg.tp_world ranks).  The attention-output and FFN-down projections are
+ * row-sliced, so their results are summed over the ranks (an NCCL all-reduce on the model's stream) before the
+ * residual is added; every rank ends with the same hidden state and computes the full logits.
+ *   forge_tp_unique_id: rank 0 creates the rendezvous id (FORGE_TP_ID_BYTES bytes) and hands it to the other
+ *     ranks by any host channel (a process-group broadcast, MPI, a file);
+ *   forge_model_tp_init: every rank, after forge_model_create with the same tp_world; collective.
+ * A model created with tp_world > 1 returns FORGE_ERR_INVALID_ARG from the forward calls until it has a communicator.
+ * NCCL (libnccl.so.2) is bound at run time; without it these two calls return FORGE_ERR_UNSUPPORTED. */
+#define FORGE_TP_ID_BYTES 128
+int32_t forge_tp_unique_id(uint8_t* id_out);
+int32_t forge_model_tp_init(ForgeModel* model, const uint8_t* id);
+
 /* Numeric form of the prefill GEMMs (matmul_mat_*, E:2278-2299).  3 (default): both operands
  * are carried as fp16 hi+lo pairs and three tensor-core passes are accumulated in f32 (~1e-6
  * relative to the reference's all-f32 arithmetic); 1: one fp16 pass (~3e-4 relative per GEMM,
