@@ -167,7 +167,16 @@ def run_gpu(args, rank: int, world: int, local_rank: int):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     c, blob, toks = make_model_inputs(args.config)
     n_prompt, n_dec = N_PROMPT[args.config], N_DECODE[args.config]
-    model = runtime.Model(c, blob, device=local_rank)
+    tp = args.tp and world > 1
+    if tp:
+        # one model cut over all ranks: rank 0's rendezvous id reaches the others through the process group
+        uid = torch.from_numpy(runtime.Model.tp_unique_id() if rank == 0 else np.zeros(runtime.TP_ID_BYTES, np.uint8)).cuda()
+        dist.broadcast(uid, 0)
+        model = runtime.Model(c, blob, device=local_rank, tp_rank=rank, tp_world=world)
+        model.tp_init(uid.cpu().numpy())
+    else:
+        model = runtime.Model(c, blob, device=local_rank)
+    jobs = 1 if tp else world  # independent requests in flight
     kv = model.new_cache(max_seq=n_prompt + n_dec + 8)
     pinned_prompt = torch.from_numpy(toks.astype(np.int32)).pin_memory()  # H2D source of every step
     prompt_np = pinned_prompt.numpy().view(np.uint32)
@@ -248,11 +257,11 @@ def run_gpu(args, rank: int, world: int, local_rank: int):
         flops = configs.prefill_flops(c, n_prompt)
         pre_tf = flops / (pre_s / K) / 1e12
         line = {
-            "metric": "decode_tok_s", "value": world * K * n_dec / dec_s, "unit": "tok/s", "n_gpus": world, "steps": K,
-            "warmup": n_warm, "ms_per_step": 1e3 * wall / K, "higher_is_better": True, "scaling": "weak",
+            "metric": "decode_tok_s", "value": jobs * K * n_dec / dec_s, "unit": "tok/s", "n_gpus": world, "steps": K,
+            "warmup": n_warm, "ms_per_step": 1e3 * wall / K, "higher_is_better": True, "scaling": "strong" if tp else "weak",
             "vs_baseline": None, "dtype": dtype_name(c), "data": "synthetic",
-            "config": workload_config(args.config, c),
-            "prefill": {"value": world * K * n_prompt / pre_s, "unit": "tok/s", "gemm": "fp16 hi/lo split, 3 tensor-core passes",
+            "config": dict(workload_config(args.config, c), **({"parallelism": f"tensor-parallel over {world} GPUs (NCCL all-reduce after O and down)"} if tp else {})),
+            "prefill": {"value": jobs * K * n_prompt / pre_s, "unit": "tok/s", "gemm": "fp16 hi/lo split, 3 tensor-core passes",
                         "roofline": {"bound": "tensor", "achieved": pre_tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                                      "frac": pre_tf / peaks["bf16_tflops"], "traffic": None, "peak_source": peaks["source"],
                                      "flops_per_step": flops}},
@@ -260,8 +269,8 @@ def run_gpu(args, rank: int, world: int, local_rank: int):
                          "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
                          "traffic": None, "peak_source": peaks["source"], "bytes_per_launch": bytes_tok, "ctx": ctx_mid,
                          "us_per_launch": step_s * 1e6},
-            "e2e": {"value": world * K * n_dec / e2e_dec_s, "unit": "tok/s", "h2d_bytes_per_step": int(prompt_np.nbytes + 4),
-                    "d2h_bytes_per_step": int(c["vocab_size"] * 4 + n_dec * 4), "prefill_tok_s": world * K * n_prompt / e2e_pre_s},
+            "e2e": {"value": jobs * K * n_dec / e2e_dec_s, "unit": "tok/s", "h2d_bytes_per_step": int(prompt_np.nbytes + 4),
+                    "d2h_bytes_per_step": int(c["vocab_size"] * 4 + n_dec * 4), "prefill_tok_s": jobs * K * n_prompt / e2e_pre_s},
             "gpu_launches": int(cnt.item()),
             "clocks": clocks,
         }
@@ -288,6 +297,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--prompt-tokens", type=int, default=None, help="override the prompt length (profiling / experiments)")
     ap.add_argument("--decode-steps", type=int, default=None, help="override the number of decode steps")
+    ap.add_argument("--tp", action="store_true", help="N > 1: cut ONE model over the N GPUs (tensor parallel, strong scaling) instead of N replicas")
     ap.add_argument("--profile", action="store_true", help="short run for ncu: one warm-up, no CPU baseline; prints a non-benchmark line")
     args = ap.parse_args()
     if args.prompt_tokens:
