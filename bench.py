@@ -232,8 +232,6 @@ def run_gpu(args, rank: int, world: int, local_rank: int):
         a, b, ids_e = one_step_e2e()
         e2e_pre.append(a)
         e2e_dec.append(b)
-        if args.profile:
-            break
     barrier()
     t1 = time.time()
     clocks = sampler.stop(t0, t1) if sampler else None

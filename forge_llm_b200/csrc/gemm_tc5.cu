@@ -213,28 +213,38 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc5_kernel(const __grid_cons
         constexpr int QV = QB / 16;
         const uint8_t* qsrc = p.qs + size_t(n_ok ? n : 0) * qrow + size_t(blk) * QB;
         const __half* dsrc = p.d + size_t(n_ok ? n : 0) * (p.K / 32) + blk;
-        uint4 q[QV];
-        __half dsc;
-        auto gload = [&](int kt) {
-            if (n_ok) {
+        // the quantised values travel through a small register queue, kPrefetch K steps ahead of their use: the
+        // rows are far apart in memory, so each load is a separate L2 / HBM round trip that must be hidden
+        constexpr int kPrefetch = 4;
+        uint4 q[kPrefetch][QV];
+        __half dsc[kPrefetch];
+        auto gload = [&](int kt, int slot) {
+            if (n_ok && kt < nk) {
 #pragma unroll
-                for (int i = 0; i < QV; ++i) q[i] = __ldg(reinterpret_cast<const uint4*>(qsrc + size_t(kt) * (2 * QB)) + i);
-                dsc = dsrc[2 * kt];
+                for (int i = 0; i < QV; ++i) q[slot][i] = __ldg(reinterpret_cast<const uint4*>(qsrc + size_t(kt) * (2 * QB)) + i);
+                dsc[slot] = dsrc[2 * kt];
             } else {
 #pragma unroll
-                for (int i = 0; i < QV; ++i) q[i] = make_uint4(0, 0, 0, 0);
-                dsc = __float2half(0.f);
+                for (int i = 0; i < QV; ++i) q[slot][i] = make_uint4(0, 0, 0, 0);
+                dsc[slot] = __float2half(0.f);
             }
         };
-        gload(0);
+#pragma unroll
+        for (int j = 0; j < kPrefetch; ++j) gload(j, j);
         bool ok = true;
         for (int kt = 0; kt < nk; ++kt) {
             const int s = kt % STAGES, use = kt / STAGES;
             uint32_t cur[4 * QV];
 #pragma unroll
-            for (int i = 0; i < QV; ++i) { cur[4 * i] = q[i].x; cur[4 * i + 1] = q[i].y; cur[4 * i + 2] = q[i].z; cur[4 * i + 3] = q[i].w; }
-            const __half2 d2 = __half2half2(dsc);
-            if (kt + 1 < nk) gload(kt + 1);
+            for (int i = 0; i < QV; ++i) { cur[4 * i] = q[0][i].x; cur[4 * i + 1] = q[0][i].y; cur[4 * i + 2] = q[0][i].z; cur[4 * i + 3] = q[0][i].w; }
+            const __half2 d2 = __half2half2(dsc[0]);
+#pragma unroll
+            for (int j = 0; j + 1 < kPrefetch; ++j) {
+#pragma unroll
+                for (int i = 0; i < QV; ++i) q[j][i] = q[j + 1][i];
+                dsc[j] = dsc[j + 1];
+            }
+            gload(kt + kPrefetch, kPrefetch - 1);
             if (ok && use > 0 && !mbar_wait(&empty[s], (use - 1) & 1, &s_err)) { atomicExch(&s_err, 1); ok = false; }
             unsigned char* hi_tile = sB + size_t(s) * B_STAGE;
             unsigned char* lo_tile = hi_tile + kTileBytes;
