@@ -2,20 +2,29 @@
 // streamed as Q8_0 / Q4_0 blocks and dequantised on the fly (replaces matmul_mat_q8_0_KxN /
 // matmul_mat_q4_0_KxN, crates/forgellm-codegen-cpu/src/emit.rs:2278-2299 and :3792-3813).
 //
-// CTA tile: (MT x 128) activation rows x 128 weight rows, K step 64.  Warp roles (320 threads):
+// CTA tile: 128 weight rows (MMA M) x NT tokens (MMA N = 128, 192 or 256), K step 64.  The dequantised weight
+// tile is the A operand and lives in TENSOR memory; the activation tile is the B operand in shared memory;
+// D[weight row][token] accumulates in tensor memory (f32).  Warp roles (320 threads):
 //   warp 0      TMA producer: 2-D tiled bulk copies (SWIZZLE_128B) of the fp16 activation tiles (hi and lo
-//               parts) into shared memory, completion on an mbarrier;
-//   warp 1      allocates TMEM and issues tcgen05.mma (one elected lane): per K step and per 128-row
-//               sub-tile three products accumulate into the same f32 TMEM tile,
-//               x_hi*w_hi + x_lo*w_hi + x_hi*w_lo (split precision, see gemm_mma.cu), K = 16 per instruction;
-//               tcgen05.commit releases the shared-memory stage and finally publishes the accumulator;
+//               parts) into a ring of shared-memory stages, completion on an mbarrier;
+//   warp 1      allocates TMEM and issues tcgen05.mma (one lane), K = 16 per instruction: per K step three products
+//               accumulate into the same tile, w_hi*x_hi + w_hi*x_lo + w_lo*x_hi (split precision, see
+//               gemm_mma.cu); tcgen05.commit releases the activation stage and the weight stage and finally
+//               publishes the accumulator;
 //   warps 2..9  dequantise: each thread owns one 32-value block of one weight row per K step, reads it and its
-//               f16 scale from global memory, forms hi = rn16(q*d) and lo = rn16(q*d - hi) with packed-half
-//               arithmetic and writes both into the K-major SWIZZLE_128B operand tiles (generic-proxy stores +
-//               fence.proxy.async); after the main loop the same warps read the accumulator with tcgen05.ld
-//               (two warps per TMEM lane quadrant) and write f32 rows (+ residual).
+//               f16 scale from global memory (through a register queue four K steps deep), forms
+//               hi = rn16(q*d) and lo = rn16(q*d - hi) with packed-half arithmetic and writes both with
+//               tcgen05.st into one of four weight stages in tensor memory (row = TMEM lane, two fp16 per
+//               32-bit column); after the main loop the same warps read the accumulator with tcgen05.ld (two
+//               warps per lane quadrant) and store f32 rows (+ residual): a warp writes 32 consecutive output
+//               columns of one token, so the stores are coalesced.
+// Shared memory carries only the activations: one operand read per product.  (With both operands in shared memory
+// the reads of a 128 x 128 x 16 product, 8 KB per ~68 clocks, saturate the 128 B/clk shared-memory port.)
 // Every wait is bounded; a wait that gives up sets an error word, and the CTA still frees its TMEM.
 #include <cuda.h>
+
+#include <cstdlib>
+#include <cstring>
 
 #include "common.cuh"
 
@@ -23,9 +32,8 @@ namespace forge {
 
 namespace {
 
-constexpr int BM = 128, BN = 128, BK = 64;
+constexpr int BK = 64;  // K step: one 128-byte swizzle row of fp16
 constexpr int kThreads = 320;
-constexpr int kTileBytes = BM * BK * 2;  // one 128 x 64 fp16 operand tile = 16 KB (1024-byte aligned)
 constexpr uint32_t kSpinLimit = 1u << 22;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
@@ -64,13 +72,6 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
     d |= uint64_t(2) << 61;                  // SWIZZLE_128B
     return d;
 }
-// instruction descriptor: D f32, A/B f16, both K-major, M = 128, N = 128
-constexpr uint32_t kIdesc = (1u << 4) | (uint32_t(BN >> 3) << 17) | (uint32_t(BM >> 4) << 24);
-
-__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t accumulate) {
-    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
-                 ::"r"(tmem_d), "l"(da), "l"(db), "r"(kIdesc), "r"(accumulate) : "memory");
-}
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
@@ -99,61 +100,74 @@ __device__ __forceinline__ void scale_split(__half2 q, __half2 d, uint32_t& hi, 
     lo = as_u32(__hfma2(q, d, __hneg2(h)));
 }
 
-// eight consecutive weights of one row -> one 16-byte chunk of the hi tile and of the lo tile.
-// K-major SWIZZLE_128B: row r at r*128 bytes, 16-byte chunk c stored at chunk (c ^ (r & 7)).
-// w0, w1: for Q8_0 the eight int8 values; for Q4_0 eight bytes whose nibbles at bit `sh` are the values.
-template <int QUANT, bool SPLIT>
-__device__ __forceinline__ void dequant_chunk(unsigned char* hi_tile, unsigned char* lo_tile, int row, int chunk, uint32_t w0,
-                                              uint32_t w1, int sh, __half2 d2) {
-    uint32_t h[4], l[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const uint32_t word = i < 2 ? w0 : w1;
-        const uint32_t sel = (i & 1) ? 0x4342u : 0x4140u;  // bytes (2,3) or (0,1) into the low bytes of each half
-        __half2 q;
-        if (QUANT == FORGE_Q8_0) {
-            // int8 b -> fp16: 0x6400 | (b + 128) is 1024 + b + 128
-            q = __hsub2(as_h2(prmt(word ^ 0x80808080u, 0x64646464u, sel)), __float2half2_rn(1152.f));
-        } else {
-            // nibble n -> fp16: 0x6400 | n is 1024 + n; the stored value is n - 8
-            const uint32_t two = prmt(word, 0u, sel) >> sh;
-            q = __hsub2(as_h2((two & 0x000F000Fu) | 0x64006400u), __float2half2_rn(1032.f));
-        }
-        if (SPLIT) scale_split(q, d2, h[i], l[i]);
-        else h[i] = as_u32(__hmul2(q, d2));
-    }
-    const uint32_t off = uint32_t(row) * 128u + uint32_t((chunk ^ (row & 7)) << 4);
-    *reinterpret_cast<uint4*>(hi_tile + off) = make_uint4(h[0], h[1], h[2], h[3]);
-    if (SPLIT) *reinterpret_cast<uint4*>(lo_tile + off) = make_uint4(l[0], l[1], l[2], l[3]);
+// instruction descriptor: D f32, A/B f16, both K-major, M = 128 weight rows, N = NT tokens
+template <int NT> struct TsIdesc { static constexpr uint32_t value = (1u << 4) | (uint32_t(NT >> 3) << 17) | (uint32_t(128 >> 4) << 24); };
+
+template <int NT>
+__device__ __forceinline__ void umma_ts_f16(uint32_t tmem_d, uint32_t tmem_a, uint64_t db, uint32_t accumulate) {
+    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}"
+                 ::"r"(tmem_d), "r"(tmem_a), "l"(db), "r"(TsIdesc<NT>::value), "r"(accumulate) : "memory");
 }
 
-// MT: 128-row activation sub-tiles per CTA; SPLIT: hi/lo split precision (3 passes) or one fp16 pass; STAGES: ring depth
-template <int QUANT, int MT, bool SPLIT, int STAGES>
-__global__ void __launch_bounds__(kThreads, 1) gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_hi,
-                                                               const __grid_constant__ CUtensorMap map_lo, Tc5Params p) {
-    constexpr int NP = SPLIT ? 2 : 1;                     // operand parts (hi, lo)
-    constexpr int A_STAGE = MT * NP * kTileBytes, B_STAGE = NP * kTileBytes;
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+                 ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
+                   "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]) : "memory");
+}
+
+// 32 consecutive weights of one row (one quantisation block) -> 16 + 16 packed fp16 pairs (hi, lo)
+template <int QUANT, bool SPLIT>
+__device__ __forceinline__ void dequant_block(const uint32_t* cur, __half2 d2, uint32_t (&hi)[16], uint32_t (&lo)[16]) {
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {      // 8 values per group
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {  // 2 values per register
+            __half2 q;
+            const uint32_t sel = (i & 1) ? 0x4342u : 0x4140u;
+            if (QUANT == FORGE_Q8_0) {
+                const uint32_t word = cur[2 * c + (i >> 1)];
+                q = __hsub2(as_h2(prmt(word ^ 0x80808080u, 0x64646464u, sel)), __float2half2_rn(1152.f));
+            } else {
+                const uint32_t word = cur[2 * (c & 1) + (i >> 1)];
+                const uint32_t two = prmt(word, 0u, sel) >> ((c >> 1) * 4);
+                q = __hsub2(as_h2((two & 0x000F000Fu) | 0x64006400u), __float2half2_rn(1032.f));
+            }
+            if (SPLIT) scale_split(q, d2, hi[4 * c + i], lo[4 * c + i]);
+            else hi[4 * c + i] = as_u32(__hmul2(q, d2));
+        }
+    }
+}
+
+template <int QUANT, int NT, bool SPLIT, int XS>
+__global__ void __launch_bounds__(kThreads, 1) gemm_ts_kernel(const __grid_constant__ CUtensorMap map_hi,
+                                                              const __grid_constant__ CUtensorMap map_lo, Tc5Params p) {
+    constexpr int NP = SPLIT ? 2 : 1;
+    constexpr int X_TILE = NT * BK * 2;          // bytes of one activation tile (NT tokens x 64 k fp16)
+    constexpr int X_STAGE = NP * X_TILE;
+    constexpr int WS = 4;                        // weight stages in tensor memory
+    constexpr int W_COLS = NP * (BK / 2);        // 32-bit columns of one weight stage (hi | lo)
+    constexpr uint32_t kTmemCols = 512;          // accumulator at columns [0, NT), weight stages from column 256
+    constexpr uint32_t kWBase = 256;
+    static_assert(NT <= 256 && kWBase + WS * W_COLS <= kTmemCols, "tensor memory budget");
     extern __shared__ __align__(1024) unsigned char smem_raw[];
-    // 1024-byte alignment for the swizzle atoms
-    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    unsigned char* sA = smem;                              // [STAGES][MT][NP][16 KB]
-    unsigned char* sB = smem + size_t(STAGES) * A_STAGE;   // [STAGES][NP][16 KB]
-    __shared__ uint64_t full_a[STAGES], full_b[STAGES], empty[STAGES], accum_full;
+    unsigned char* sX = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    __shared__ uint64_t full_x[XS], empty_x[XS], full_w[WS], empty_w[WS], accum_full;
     __shared__ uint32_t s_tmem;
     __shared__ int s_err;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int n0 = blockIdx.x * BN, m0 = blockIdx.y * (BM * MT);
+    const int n0 = blockIdx.x * 128, m0 = blockIdx.y * NT;
     const int nk = p.K / BK;
 
     if (tid == 0) {
-        for (int s = 0; s < STAGES; ++s) { mbar_init(&full_a[s], 1); mbar_init(&full_b[s], 8); mbar_init(&empty[s], 1); }
+        for (int s = 0; s < XS; ++s) { mbar_init(&full_x[s], 1); mbar_init(&empty_x[s], 1); }
+        for (int s = 0; s < WS; ++s) { mbar_init(&full_w[s], 8); mbar_init(&empty_w[s], 1); }
         mbar_init(&accum_full, 1);
         s_err = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1) {  // TMEM: MT accumulators of 128 lanes x 128 f32 columns
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem)), "n"(MT * BN) : "memory");
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem)), "n"(kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -162,59 +176,53 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc5_kernel(const __grid_cons
     const uint32_t tmem = s_tmem;
 
     if (warp == 0) {
-        // ---------------- TMA producer (activation tiles)
+        // ---------------- TMA producer: activation tiles (B operand)
         if (lane == 0) {
             for (int kt = 0; kt < nk; ++kt) {
-                const int s = kt % STAGES, use = kt / STAGES;
-                if (use > 0 && !mbar_wait(&empty[s], (use - 1) & 1, &s_err)) { atomicExch(&s_err, 1); break; }
-                mbar_expect_tx(&full_a[s], uint32_t(A_STAGE));
-#pragma unroll
-                for (int mt = 0; mt < MT; ++mt) {
-                    unsigned char* dst = sA + size_t(s) * A_STAGE + size_t(mt) * NP * kTileBytes;
-                    tma_load_2d(dst, &map_hi, kt * BK, m0 + mt * BM, &full_a[s]);
-                    if (SPLIT) tma_load_2d(dst + kTileBytes, &map_lo, kt * BK, m0 + mt * BM, &full_a[s]);
-                }
+                const int s = kt % XS, use = kt / XS;
+                if (use > 0 && !mbar_wait(&empty_x[s], (use - 1) & 1, &s_err)) { atomicExch(&s_err, 1); break; }
+                mbar_expect_tx(&full_x[s], uint32_t(X_STAGE));
+                unsigned char* dst = sX + size_t(s) * X_STAGE;
+                tma_load_2d(dst, &map_hi, kt * BK, m0, &full_x[s]);
+                if (SPLIT) tma_load_2d(dst + X_TILE, &map_lo, kt * BK, m0, &full_x[s]);
             }
         }
     } else if (warp == 1) {
-        // ---------------- MMA issuer
+        // ---------------- MMA issuer: D[weight row][token] += W(TMEM) * X(smem)^T
         if (lane == 0) {
-            bool ok = true;
-            for (int kt = 0; kt < nk && ok; ++kt) {
-                const int s = kt % STAGES, use = kt / STAGES;
-                if (!mbar_wait(&full_a[s], use & 1, &s_err) || !mbar_wait(&full_b[s], use & 1, &s_err)) { atomicExch(&s_err, 1); ok = false; break; }
+            for (int kt = 0; kt < nk; ++kt) {
+                const int sx = kt % XS, sw = kt % WS;
+                if (!mbar_wait(&full_x[sx], (kt / XS) & 1, &s_err) || !mbar_wait(&full_w[sw], (kt / WS) & 1, &s_err)) { atomicExch(&s_err, 1); break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t a_base = smem_u32(sA + size_t(s) * A_STAGE), b_base = smem_u32(sB + size_t(s) * B_STAGE);
+                const uint32_t x_base = smem_u32(sX + size_t(sx) * X_STAGE);
+                const uint32_t w_base = tmem + kWBase + uint32_t(sw * W_COLS);
 #pragma unroll
-                for (int mt = 0; mt < MT; ++mt) {
+                for (int pass = 0; pass < (SPLIT ? 3 : 1); ++pass) {
+                    // pass 0: w_hi x_hi   pass 1: w_hi x_lo   pass 2: w_lo x_hi
+                    const uint32_t x_tile = x_base + uint32_t(pass == 1 ? X_TILE : 0);
+                    const uint32_t w_tile = w_base + uint32_t(pass == 2 ? BK / 2 : 0);
 #pragma unroll
-                    for (int pass = 0; pass < (SPLIT ? 3 : 1); ++pass) {
-                        // pass 0: x_hi w_hi   pass 1: x_lo w_hi   pass 2: x_hi w_lo
-                        const uint32_t a_tile = a_base + uint32_t(mt * NP + (pass == 1 ? 1 : 0)) * kTileBytes;
-                        const uint32_t b_tile = b_base + uint32_t(pass == 2 ? 1 : 0) * kTileBytes;
-#pragma unroll
-                        for (int k16 = 0; k16 < BK / 16; ++k16) {
-                            const uint32_t acc = (kt > 0 || pass > 0 || k16 > 0) ? 1u : 0u;
-                            umma_f16(tmem + uint32_t(mt * BN), umma_desc(a_tile + k16 * 32), umma_desc(b_tile + k16 * 32), acc);
-                        }
+                    for (int k16 = 0; k16 < BK / 16; ++k16) {
+                        const uint32_t acc = (kt > 0 || pass > 0 || k16 > 0) ? 1u : 0u;
+                        umma_ts_f16<NT>(tmem, w_tile + uint32_t(k16 * 8), umma_desc(x_tile + k16 * 32), acc);
                     }
                 }
-                umma_commit(&empty[s]);  // the stage may be refilled once these MMAs have read it
+                umma_commit(&empty_x[sx]);
+                umma_commit(&empty_w[sw]);
             }
-            umma_commit(&accum_full);    // all MMAs done: the accumulators are complete
+            umma_commit(&accum_full);
         }
     } else {
-        // ---------------- dequantise (warps 2..9): thread -> weight row n0 + r, 32-value block blk of the K step
-        const int r = (tid - 64) & 127, blk = (tid - 64) >> 7;
+        // ---------------- dequantise (warps 2..9): TMEM lane = weight row; a warp may only touch its lane quadrant
+        const int quad = warp & 3, blk = (warp - 2) >> 2;
+        const int r = quad * 32 + lane;
         const int n = n0 + r;
         const bool n_ok = n < p.N;
         const size_t qrow = QUANT == FORGE_Q8_0 ? size_t(p.K) : size_t(p.K) / 2;
-        constexpr int QB = QUANT == FORGE_Q8_0 ? 32 : 16;  // bytes of quantised values per block
+        constexpr int QB = QUANT == FORGE_Q8_0 ? 32 : 16;
         constexpr int QV = QB / 16;
         const uint8_t* qsrc = p.qs + size_t(n_ok ? n : 0) * qrow + size_t(blk) * QB;
         const __half* dsrc = p.d + size_t(n_ok ? n : 0) * (p.K / 32) + blk;
-        // the quantised values travel through a small register queue, kPrefetch K steps ahead of their use: the
-        // rows are far apart in memory, so each load is a separate L2 / HBM round trip that must be hidden
         constexpr int kPrefetch = 4;
         uint4 q[kPrefetch][QV];
         __half dsc[kPrefetch];
@@ -232,8 +240,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc5_kernel(const __grid_cons
 #pragma unroll
         for (int j = 0; j < kPrefetch; ++j) gload(j, j);
         bool ok = true;
+        const uint32_t lane_base = tmem + (uint32_t(quad * 32) << 16) + kWBase + uint32_t(blk * 16);
         for (int kt = 0; kt < nk; ++kt) {
-            const int s = kt % STAGES, use = kt / STAGES;
+            const int sw = kt % WS, use = kt / WS;
             uint32_t cur[4 * QV];
 #pragma unroll
             for (int i = 0; i < QV; ++i) { cur[4 * i] = q[0][i].x; cur[4 * i + 1] = q[0][i].y; cur[4 * i + 2] = q[0][i].z; cur[4 * i + 3] = q[0][i].w; }
@@ -245,57 +254,43 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc5_kernel(const __grid_cons
                 dsc[j] = dsc[j + 1];
             }
             gload(kt + kPrefetch, kPrefetch - 1);
-            if (ok && use > 0 && !mbar_wait(&empty[s], (use - 1) & 1, &s_err)) { atomicExch(&s_err, 1); ok = false; }
-            unsigned char* hi_tile = sB + size_t(s) * B_STAGE;
-            unsigned char* lo_tile = hi_tile + kTileBytes;
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {  // 8 values per 16-byte fp16 chunk
-                if (QUANT == FORGE_Q8_0) {
-                    dequant_chunk<QUANT, SPLIT>(hi_tile, lo_tile, r, blk * 4 + c, cur[2 * c], cur[2 * c + 1], 0, d2);
-                } else {
-                    // block bytes j = 0..15: element j in the low nibble, element j + 16 in the high nibble
-                    dequant_chunk<QUANT, SPLIT>(hi_tile, lo_tile, r, blk * 4 + c, cur[2 * (c & 1)], cur[2 * (c & 1) + 1], (c >> 1) * 4, d2);
-                }
-            }
-            // make the generic-proxy stores visible to the tensor core (async proxy), then signal
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            uint32_t hi[16], lo[16];
+            dequant_block<QUANT, SPLIT>(cur, d2, hi, lo);
+            if (ok && use > 0 && !mbar_wait(&empty_w[sw], (use - 1) & 1, &s_err)) { atomicExch(&s_err, 1); ok = false; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t col = lane_base + uint32_t(sw * W_COLS);
+            tmem_st16(col, hi);
+            if (SPLIT) tmem_st16(col + BK / 2, lo);
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
-            if (lane == 0) mbar_arrive(&full_b[s]);
+            if (lane == 0) mbar_arrive(&full_w[sw]);
         }
 
-        // ---------------- epilogue: TMEM -> registers -> global (warp w reads lane quadrant w % 4)
+        // ---------------- epilogue: lane = weight row, columns = tokens; two warps per lane quadrant split the tokens
         if (!mbar_wait(&accum_full, 0, &s_err)) atomicExch(&s_err, 1);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const int quad = warp & 3, chalf = (warp - 2) >> 2;  // two warps per lane quadrant, 64 columns each
+        const int col_n = n0 + r;
+#pragma unroll 1
+        for (int c0 = blk * (NT / 2); c0 < (blk + 1) * (NT / 2); c0 += 32) {
+            uint32_t v[32];
+            const uint32_t taddr = tmem + (uint32_t(quad * 32) << 16) + uint32_t(c0);
+            asm volatile(
+                "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+                "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+                  "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+                  "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+                  "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                : "r"(taddr) : "memory");
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            if (col_n < p.N) {
 #pragma unroll
-        for (int mt = 0; mt < MT; ++mt) {
-            const int row = m0 + mt * BM + quad * 32 + lane;
-#pragma unroll
-            for (int c0 = chalf * 64; c0 < chalf * 64 + 64; c0 += 32) {
-                uint32_t v[32];
-                const uint32_t taddr = tmem + (uint32_t(quad * 32) << 16) + uint32_t(mt * BN + c0);
-                asm volatile(
-                    "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-                    "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-                    : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-                      "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
-                      "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
-                      "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-                    : "r"(taddr) : "memory");
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (row < p.m) {
-                    float* orow = p.out + size_t(row) * p.N + n0 + c0;
-                    const float* rrow = p.resid ? p.resid + size_t(row) * p.N + n0 + c0 : nullptr;
-                    if (n0 + c0 + 32 <= p.N && (p.N & 3) == 0) {
-#pragma unroll
-                        for (int j = 0; j < 32; j += 4) {
-                            float4 o = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]), __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
-                            if (rrow) { const float4 rr = *reinterpret_cast<const float4*>(rrow + j); o.x += rr.x; o.y += rr.y; o.z += rr.z; o.w += rr.w; }
-                            *reinterpret_cast<float4*>(orow + j) = o;
-                        }
-                    } else {
-                        for (int j = 0; j < 32; ++j)
-                            if (n0 + c0 + j < p.N) orow[j] = (rrow ? rrow[j] : 0.f) + __uint_as_float(v[j]);
+                for (int j = 0; j < 32; ++j) {
+                    const int row = m0 + c0 + j;
+                    if (row < p.m) {
+                        const size_t off = size_t(row) * p.N + col_n;
+                        p.out[off] = (p.resid ? p.resid[off] : 0.f) + __uint_as_float(v[j]);
                     }
                 }
             }
@@ -305,7 +300,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc5_kernel(const __grid_cons
     __syncthreads();
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "n"(MT * BN) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "n"(kTmemCols) : "memory");
     }
     if (tid == 0 && s_err && p.err) atomicExch(p.err, 1);
 }
@@ -325,12 +320,12 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
-int32_t make_map(CUtensorMap* map, const __half* base, int m, int K) {
+int32_t make_map(CUtensorMap* map, const __half* base, int m, int K, int box_rows) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) { set_error("cuTensorMapEncodeTiled is not available from this driver"); return FORGE_ERR_UNSUPPORTED; }
     const cuuint64_t dims[2] = {cuuint64_t(K), cuuint64_t(m)};
     const cuuint64_t strides[1] = {cuuint64_t(K) * 2};
-    const cuuint32_t box[2] = {BK, BM};
+    const cuuint32_t box[2] = {BK, cuuint32_t(box_rows)};
     const cuuint32_t estr[2] = {1, 1};
     CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half*>(base), dims, strides, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
@@ -339,16 +334,19 @@ int32_t make_map(CUtensorMap* map, const __half* base, int m, int K) {
     return FORGE_OK;
 }
 
-template <int QUANT, int MT, bool SPLIT>
-int32_t launch(const CUtensorMap& mh, const CUtensorMap& ml, const Tc5Params& p, cudaStream_t st) {
+template <int QUANT, int NT, bool SPLIT>
+int32_t launch_ts(const __half* A, const __half* Alo, const Tc5Params& p, cudaStream_t st) {
     constexpr int NP = SPLIT ? 2 : 1;
-    constexpr int STAGE = (MT * NP + NP) * kTileBytes;
-    constexpr int STAGES = (200 * 1024) / STAGE >= 4 ? 4 : (200 * 1024) / STAGE;
-    static_assert(STAGES >= 2, "pipeline needs at least two stages");
-    const size_t smem = size_t(STAGES) * STAGE + 1024;
-    auto kern = gemm_tc5_kernel<QUANT, MT, SPLIT, STAGES>;
+    constexpr int STAGE = NP * NT * BK * 2;
+    constexpr int XS = (200 * 1024) / STAGE >= 4 ? 4 : (200 * 1024) / STAGE;
+    static_assert(XS >= 2, "pipeline needs at least two stages");
+    CUtensorMap mh, ml;
+    FORGE_TRY(make_map(&mh, A, p.m, p.K, NT));
+    FORGE_TRY(make_map(&ml, Alo ? Alo : A, p.m, p.K, NT));
+    const size_t smem = size_t(XS) * STAGE + 1024;
+    auto kern = gemm_ts_kernel<QUANT, NT, SPLIT, XS>;
     FORGE_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
-    dim3 grid((p.N + BN - 1) / BN, (p.m + BM * MT - 1) / (BM * MT));
+    dim3 grid((p.N + 127) / 128, (p.m + NT - 1) / NT);
     kern<<<grid, kThreads, smem, st>>>(mh, ml, p);
     FORGE_LAUNCH_CHECK();
     return FORGE_OK;
@@ -361,27 +359,39 @@ bool gemm_tc5_supported(const QWeight& w) { return w.K % BK == 0 && w.K >= BK; }
 int32_t gemm_tc5(float* out, const __half* A, const __half* Alo, const QWeight& w, int m, const float* resid, int* err, cudaStream_t st) {
     if (m <= 0) return FORGE_OK;
     if (!gemm_tc5_supported(w)) { set_error("tcgen05 gemm: K=%d must be a multiple of %d", w.K, BK); return FORGE_ERR_SHAPE; }
-    CUtensorMap mh, ml;
-    FORGE_TRY(make_map(&mh, A, m, w.K));
-    FORGE_TRY(make_map(&ml, Alo ? Alo : A, m, w.K));
     Tc5Params p{out, resid, w.qs, w.d, m, w.N, w.K, err};
     const bool split = Alo != nullptr;
-    // two activation sub-tiles per CTA reuse every dequantised weight tile twice; use it when the grid still fills the GPU
-    // (a CTA with two sub-tiles costs about 1.5x one with a single sub-tile; compare whole rounds over the SMs)
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    const long nt = (w.N + BN - 1) / BN;
-    const long ctas1 = nt * ((m + BM - 1) / BM), ctas2 = nt * ((m + 2 * BM - 1) / (2 * BM));
-    const bool mt2 = m > BM && 3 * ((ctas2 + sms - 1) / sms) <= 2 * ((ctas1 + sms - 1) / sms);
-#define FORGE_TC5(Q)                                                                             \
-    do {                                                                                         \
-        if (split) return mt2 ? launch<Q, 2, true>(mh, ml, p, st) : launch<Q, 1, true>(mh, ml, p, st);   \
-        return mt2 ? launch<Q, 2, false>(mh, ml, p, st) : launch<Q, 1, false>(mh, ml, p, st);   \
+    // Token tile: 128, 192 or 256.  A tile's cost is a fixed share (dequantising the 128 x K weight panel, prologue,
+    // epilogue) plus a share proportional to its tokens (measured on B200: 0.77 / 0.90 / 1.0 per CTA round); CTAs run
+    // in whole rounds over the SMs.  Pick the cheapest.
+    const long nt = (w.N + 127) / 128;
+    int best = 128;
+    double best_cost = 1e30;
+    for (int cand : {128, 192, 256}) {
+        if (cand > 128 && m <= cand - 64) continue;
+        const long ctas = nt * ((m + cand - 1) / cand);
+        const double cost = double((ctas + sms - 1) / sms) * (0.55 + 0.45 * cand / 256.0);
+        if (cost < best_cost - 1e-9) { best_cost = cost; best = cand; }
+    }
+    static const int force_nt = [] { const char* e = getenv("FORGE_B200_NT"); return e ? atoi(e) : 0; }();  // experiments
+    if (force_nt == 128 || force_nt == 192 || force_nt == 256) best = force_nt;
+#define FORGE_TS(Q)                                                                  \
+    do {                                                                             \
+        if (split) {                                                                 \
+            if (best == 256) return launch_ts<Q, 256, true>(A, Alo, p, st);          \
+            if (best == 192) return launch_ts<Q, 192, true>(A, Alo, p, st);          \
+            return launch_ts<Q, 128, true>(A, Alo, p, st);                           \
+        }                                                                            \
+        if (best == 256) return launch_ts<Q, 256, false>(A, Alo, p, st);             \
+        if (best == 192) return launch_ts<Q, 192, false>(A, Alo, p, st);             \
+        return launch_ts<Q, 128, false>(A, Alo, p, st);                              \
     } while (0)
-    if (w.quant == FORGE_Q8_0) FORGE_TC5(FORGE_Q8_0);
-    FORGE_TC5(FORGE_Q4_0);
-#undef FORGE_TC5
+    if (w.quant == FORGE_Q8_0) FORGE_TS(FORGE_Q8_0);
+    FORGE_TS(FORGE_Q4_0);
+#undef FORGE_TS
 }
 
 }  // namespace forge
