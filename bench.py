@@ -152,6 +152,13 @@ def workload_config(key: str, c: dict) -> dict:
             "l2": "inputs larger than L2: every step streams the whole weight set (>= 143 MB) once per token"}
 
 
+# DRAM bytes moved per algorithmic byte of the streaming GEMV (dram__bytes_read + dram__bytes_write of one captured
+# launch, 153.6 MB for 147.75 MB of weights: profiles/gemv_tc_kernel_c2_lm_head.md).  A decode step is one graph
+# replay of such kernels; its traffic is scaled from that capture by the bytes it streams.
+DRAM_TRAFFIC_RATIO = 1.04
+TRAFFIC_NOTE = "scaled from one ncu capture of the GEMV kernel (traffic/algorithmic = 1.04)"
+
+
 # ---------------------------------------------------------------------------- GPU arm
 def run_gpu(args, rank: int, world: int, local_rank: int):
     import torch
@@ -259,13 +266,14 @@ def run_gpu(args, rank: int, world: int, local_rank: int):
             "warmup": n_warm, "ms_per_step": 1e3 * wall / K, "higher_is_better": True, "scaling": "strong" if tp else "weak",
             "vs_baseline": None, "dtype": dtype_name(c), "data": "synthetic",
             "config": dict(workload_config(args.config, c), **({"parallelism": f"tensor-parallel over {world} GPUs (NCCL all-reduce after O and down)"} if tp else {})),
-            "prefill": {"value": jobs * K * n_prompt / pre_s, "unit": "tok/s", "gemm": "fp16 hi/lo split, 3 tensor-core passes",
+            "prefill": {"value": jobs * K * n_prompt / pre_s, "unit": "tok/s", "gemm": "tcgen05/TMEM, fp16 hi/lo split, 3 tensor-core passes",
                         "roofline": {"bound": "tensor", "achieved": pre_tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                                      "frac": pre_tf / peaks["bf16_tflops"], "traffic": None, "peak_source": peaks["source"],
                                      "flops_per_step": flops}},
             "roofline": {"bound": "hbm", "kernel": "one decode step (all kernels of forward(), replayed as one CUDA graph)",
                          "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
-                         "traffic": None, "peak_source": peaks["source"], "bytes_per_launch": bytes_tok, "ctx": ctx_mid,
+                         "traffic": bytes_tok * DRAM_TRAFFIC_RATIO, "traffic_source": TRAFFIC_NOTE,
+                         "peak_source": peaks["source"], "bytes_per_launch": bytes_tok, "ctx": ctx_mid,
                          "us_per_launch": step_s * 1e6},
             "e2e": {"value": jobs * K * n_dec / e2e_dec_s, "unit": "tok/s", "h2d_bytes_per_step": int(prompt_np.nbytes + 4),
                     "d2h_bytes_per_step": int(c["vocab_size"] * 4 + n_dec * 4), "prefill_tok_s": jobs * K * n_prompt / e2e_pre_s},
