@@ -1,0 +1,56 @@
+"""Committed outputs of the CPU restatement on seeded tiny models (tests/golden/tiny_models.npz).
+
+CPU: the oracle still reproduces them bit for bit.  GPU: the CUDA path meets the parity gates against the committed
+values (no oracle involved at run time)."""
+import importlib.util
+import os
+
+import numpy as np
+import pytest
+
+from util import rel_l2
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+spec = importlib.util.spec_from_file_location("make_golden", os.path.join(HERE, "golden", "make_golden.py"))
+mg = importlib.util.module_from_spec(spec)
+spec.loader.exec_module(mg)
+GOLD = np.load(os.path.join(HERE, "golden", "tiny_models.npz"))
+
+
+def _inputs(name):
+    from forge_llm_b200 import configs, synth
+    c = configs.tiny(**mg.CASES[name])
+    return c, synth.make_weights_bin(c), synth.prompt_tokens(c, mg.N_PROMPT)
+
+
+@pytest.mark.parametrize("name", sorted(mg.CASES))
+def test_oracle_reproduces_fixture(name, oracle):
+    c, blob, toks = _inputs(name)
+    om = oracle.OracleModel(c, blob, kv_mode=oracle.KV_F16)
+    logits, trace = om.forward_prefill(toks, trace=True)
+    assert np.array_equal(logits, GOLD[name + "/prefill_logits"])
+    assert np.array_equal(trace[-1, -1], GOLD[name + "/last_hidden"])
+    om.reset()
+    ids, last = om.generate_greedy(toks, mg.N_NEW)
+    assert np.array_equal(ids, GOLD[name + "/greedy_ids"])
+    assert np.array_equal(last, GOLD[name + "/final_logits"])
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", sorted(mg.CASES))
+def test_cuda_path_matches_fixture(name):
+    from forge_llm_b200 import runtime
+    c, blob, toks = _inputs(name)
+    gm = runtime.Model(c, blob)
+    kv = gm.new_cache(max_seq=mg.N_PROMPT + mg.N_NEW + 8)
+    gm.trace(True)
+    lg = gm.forward_prefill(toks, kv)
+    tr = gm.read_trace(mg.N_PROMPT)
+    gm.trace(False)
+    assert np.abs(lg - GOLD[name + "/prefill_logits"]).max() < 2e-2
+    assert rel_l2(tr[-1, -1], GOLD[name + "/last_hidden"]) < 1e-3
+    kv.reset()
+    ids = gm.generate_greedy(toks, mg.N_NEW, kv)
+    assert np.array_equal(ids, GOLD[name + "/greedy_ids"])
+    kv.close()
+    gm.close()
