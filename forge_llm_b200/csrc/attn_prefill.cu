@@ -3,8 +3,11 @@
 // position base_pos + r and sees cache positions <= its own (:815-818); K/V tiles stop at the
 // tile's last query (:782, :792-793); GQA mapping kv_head = h / (nq/nkv) (:763, :775).
 // One CTA = 64 query rows of one head (16 per warp); K/V stream in 64-key tiles (one KV page);
-// S = Q K^T and O += P V are m16n8k16 fp16 MMAs with f32 accumulators, the softmax state is
-// f32 and uses expf.
+// S = Q K^T and O += P V are m16n8k16 fp16 MMAs with f32 accumulators.  The softmax state is f32 in the base-2
+// domain (scores are scaled by scale * log2(e) once, probabilities are ex2 of the difference: the hardware
+// exponential, relative error ~2^-22, far below the fp16 rounding of P); the causal mask is applied only on tiles
+// that reach past a query's position.  K/V tiles are double-buffered with cp.async; CTAs with the most key tiles
+// (the last query tiles) are scheduled first.
 #include "common.cuh"
 
 namespace forge {
@@ -33,6 +36,15 @@ __device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], 
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+// 16-byte global -> shared copy that bypasses registers; src_bytes = 0 writes zeros
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, int src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(src_bytes) : "memory");
+}
 __device__ __forceinline__ uint32_t pack_h2(float a, float b) {
     __half2 h = __floats2half2_rn(a, b);
     return *reinterpret_cast<uint32_t*>(&h);
@@ -44,10 +56,9 @@ __global__ void __launch_bounds__(kThreads) attn_prefill_kernel(PrefillParams p)
     constexpr int CH = HD / 8;       // 16-byte chunks per row
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __half* sQ = reinterpret_cast<__half*>(smem_raw);
-    __half* sK = sQ + BM * LD;
-    __half* sV = sK + BN * LD;
+    __half* sKV = sQ + BM * LD;  // [2 buffers][K | V][BN][LD]
     const AttnPrefillArgs& a = p.a;
-    const int qt = blockIdx.x, h = blockIdx.y;
+    const int qt = int(gridDim.x) - 1 - int(blockIdx.x), h = blockIdx.y;  // longest CTAs first
     const int G = a.nq / a.nkv, kvh = h / G, kvd = a.nkv * HD;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
     const int row0 = qt * BM;
@@ -83,21 +94,31 @@ __global__ void __launch_bounds__(kThreads) attn_prefill_kernel(PrefillParams p)
     const int ntiles = (n_keys + BN - 1) / BN;
     const int qpos0 = a.base_pos + row0 + warp * 16 + g;  // position of this thread's first row
 
-    for (int j = 0; j < ntiles; ++j) {
-        __syncthreads();
+    auto load_tile = [&](int j, int buf) {
         const int page = a.page_row ? a.page_row[j] : j;
+        __half* dK = sKV + size_t(buf) * 2 * BN * LD;
+        __half* dV = dK + BN * LD;
         for (int idx = tid; idx < BN * CH; idx += kThreads) {
-            int r = idx / CH, c = idx % CH;
-            uint4 kv4 = make_uint4(0, 0, 0, 0), vv4 = make_uint4(0, 0, 0, 0);
-            if (j * BN + r < n_keys) {
-                size_t off = (size_t(page) * FORGE_KV_PAGE + r) * kvd + kvh * HD + c * 8;
-                kv4 = *reinterpret_cast<const uint4*>(a.k_pool + off);
-                vv4 = *reinterpret_cast<const uint4*>(a.v_pool + off);
-            }
-            *reinterpret_cast<uint4*>(sK + r * LD + c * 8) = kv4;
-            *reinterpret_cast<uint4*>(sV + r * LD + c * 8) = vv4;
+            const int r = idx / CH, c = idx % CH;
+            const bool in = j * BN + r < n_keys;
+            const size_t off = (size_t(page) * FORGE_KV_PAGE + (in ? r : 0)) * kvd + kvh * HD + c * 8;
+            cp_async16(dK + r * LD + c * 8, a.k_pool + off, in ? 16 : 0);
+            cp_async16(dV + r * LD + c * 8, a.v_pool + off, in ? 16 : 0);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    const float sl2 = p.scale * 1.4426950408889634f;  // scores in the base-2 domain
+    load_tile(0, 0);
+    for (int j = 0; j < ntiles; ++j) {
+        if (j + 1 < ntiles) {
+            load_tile(j + 1, (j + 1) & 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
         }
         __syncthreads();
+        const __half* sK = sKV + size_t(j & 1) * 2 * BN * LD;
+        const __half* sV = sK + BN * LD;
 
         float s[BN / 8][4];
 #pragma unroll
@@ -112,7 +133,9 @@ __global__ void __launch_bounds__(kThreads) attn_prefill_kernel(PrefillParams p)
                 mma16816(s[nb], qf[ks + 1], r[2], r[3]);
             }
         }
-        // scale, causal mask, online softmax (rows g and g+8 of the warp's 16)
+        // scale, causal mask (only where the tile reaches past the row), online softmax in base 2
+        // (rows g and g+8 of the warp's 16)
+        const bool diag = j * BN + BN - 1 > a.base_pos + row0 + warp * 16;  // some key of the tile may be masked for this warp
 #pragma unroll
         for (int rr = 0; rr < 2; ++rr) {
             const int qpos = qpos0 + rr * 8;
@@ -121,9 +144,8 @@ __global__ void __launch_bounds__(kThreads) attn_prefill_kernel(PrefillParams p)
             for (int nb = 0; nb < BN / 8; ++nb) {
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
-                    int key = j * BN + nb * 8 + 2 * t + e;
-                    float v = s[nb][rr * 2 + e] * p.scale;
-                    if (key > qpos) v = -INFINITY;
+                    float v = s[nb][rr * 2 + e] * sl2;
+                    if (diag && j * BN + nb * 8 + 2 * t + e > qpos) v = -INFINITY;
                     s[nb][rr * 2 + e] = v;
                     mx = fmaxf(mx, v);
                 }
@@ -131,14 +153,14 @@ __global__ void __launch_bounds__(kThreads) attn_prefill_kernel(PrefillParams p)
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
             const float mn = fmaxf(mrow[rr], mx);
-            const float es = (mn == -INFINITY) ? 1.f : expf(mrow[rr] - mn);
+            const float msub = (mn == -INFINITY) ? 0.f : mn;  // a fully masked row keeps exponent arguments finite
+            const float es = ex2(mrow[rr] - msub);            // ex2(-inf) = 0
             float ls = 0.f;
 #pragma unroll
             for (int nb = 0; nb < BN / 8; ++nb) {
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
-                    float v = s[nb][rr * 2 + e];
-                    float pr = (v == -INFINITY) ? 0.f : expf(v - mn);
+                    const float pr = ex2(s[nb][rr * 2 + e] - msub);
                     s[nb][rr * 2 + e] = pr;
                     ls += pr;
                 }
@@ -164,6 +186,7 @@ __global__ void __launch_bounds__(kThreads) attn_prefill_kernel(PrefillParams p)
                 mma16816(o[2 * nb2 + 1], pa, r[2], r[3]);
             }
         }
+        __syncthreads();  // the buffer is refilled by the prefetch of the next iteration
     }
 #pragma unroll
     for (int rr = 0; rr < 2; ++rr) {
@@ -194,7 +217,7 @@ __global__ void __launch_bounds__(kThreads) attn_prefill_kernel(PrefillParams p)
 
 template <int HD>
 int32_t launch(const PrefillParams& p, cudaStream_t st) {
-    constexpr size_t smem = size_t(BM + 2 * BN) * (HD + 8) * sizeof(__half);
+    constexpr size_t smem = size_t(BM + 4 * BN) * (HD + 8) * sizeof(__half);
     FORGE_CUDA(cudaFuncSetAttribute(attn_prefill_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
     dim3 grid((p.a.m + BM - 1) / BM, p.a.nq);
     attn_prefill_kernel<HD><<<grid, kThreads, smem, st>>>(p);
