@@ -181,6 +181,12 @@ def run_gpu(args, rank: int, world: int, local_rank: int):
         dist.broadcast(uid, 0)
         model = runtime.Model(c, blob, device=local_rank, tp_rank=rank, tp_world=world)
         model.tp_init(uid.cpu().numpy())
+        if not args.tp_nccl_only:  # decode sums over peer memory (NVLink stores from the GEMV epilogue)
+            mine_h = torch.from_numpy(model.tp_exchange_handle()).cuda()
+            all_h = [torch.empty_like(mine_h) for _ in range(world)]
+            dist.all_gather(all_h, mine_h)
+            model.tp_exchange_attach(torch.cat(all_h).cpu().numpy())
+            dist.barrier()
     else:
         model = runtime.Model(c, blob, device=local_rank)
     jobs = 1 if tp else world  # independent requests in flight
@@ -265,7 +271,7 @@ def run_gpu(args, rank: int, world: int, local_rank: int):
             "metric": "decode_tok_s", "value": jobs * K * n_dec / dec_s, "unit": "tok/s", "n_gpus": world, "steps": K,
             "warmup": n_warm, "ms_per_step": 1e3 * wall / K, "higher_is_better": True, "scaling": "strong" if tp else "weak",
             "vs_baseline": None, "dtype": dtype_name(c), "data": "synthetic",
-            "config": dict(workload_config(args.config, c), **({"parallelism": f"tensor-parallel over {world} GPUs (NCCL all-reduce after O and down)"} if tp else {})),
+            "config": dict(workload_config(args.config, c), **({"parallelism": f"tensor-parallel over {world} GPUs (sum after O and down: " + ("NCCL all-reduce" if args.tp_nccl_only else "NCCL in prefill, peer-memory stores fused into the GEMV in decode") + ")"} if tp else {})),
             "prefill": {"value": jobs * K * n_prompt / pre_s, "unit": "tok/s", "gemm": "tcgen05/TMEM, fp16 hi/lo split, 3 tensor-core passes",
                         "roofline": {"bound": "tensor", "achieved": pre_tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                                      "frac": pre_tf / peaks["bf16_tflops"], "traffic": None, "peak_source": peaks["source"],
@@ -304,6 +310,7 @@ def main():
     ap.add_argument("--prompt-tokens", type=int, default=None, help="override the prompt length (profiling / experiments)")
     ap.add_argument("--decode-steps", type=int, default=None, help="override the number of decode steps")
     ap.add_argument("--tp", action="store_true", help="N > 1: cut ONE model over the N GPUs (tensor parallel, strong scaling) instead of N replicas")
+    ap.add_argument("--tp-nccl-only", action="store_true", help="with --tp: keep the library all-reduce in the decode step (no peer-memory sums)")
     ap.add_argument("--profile", action="store_true", help="short run for ncu: one warm-up, no CPU baseline; prints a non-benchmark line")
     args = ap.parse_args()
     if args.prompt_tokens:

@@ -88,7 +88,7 @@ inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, siz
 
 // ------------------------------------------------------------------ GEMV (decode)
 // EPI_PARTIAL: every K slice stores its raw partial sums at scratch[slice][row]; the reader adds them
-enum GemvEpilogue { EPI_STORE = 0, EPI_RESID = 1, EPI_QKV = 2, EPI_SILU = 3, EPI_PARTIAL = 4 };
+enum GemvEpilogue { EPI_STORE = 0, EPI_RESID = 1, EPI_QKV = 2, EPI_SILU = 3, EPI_PARTIAL = 4, EPI_TP_PUSH = 5 };
 
 struct GemvArgs {
     const float* x = nullptr;       // [batch][K] input rows
@@ -111,6 +111,24 @@ struct GemvArgs {
     // share while this kernel runs, so HBM keeps streaming across the kernel boundary.
     const void* next_w = nullptr;
     size_t next_bytes = 0;
+    // Tensor-parallel sum over peer memory (decode, batch 1).  Every rank owns an exchange buffer
+    // {flags[2 slots][world], parts[2 slots][world][h]} that its peers map (CUDA IPC).
+    //  * EPI_TP_PUSH (the row-sliced projection): each finished row of this rank's partial product is stored into
+    //    parts[slot][tp.rank] of EVERY rank's buffer (NVLink stores); the last CTA to finish publishes the step number
+    //    in flags[slot][tp.rank] of every rank and advances the local step counter.  slot = step & 1.
+    //  * tp.consume (the kernel that reads the result next): waits (bounded) until all `world` flags of the slot carry
+    //    the current step, then stages x = x + sum over ranks of parts[slot][r] (rank order, so every rank forms the
+    //    same bits) and writes the sum once to x_writeback (the residual stream for the kernels after it).
+    struct Tp {
+        int world = 0, rank = 0, consume = 0;
+        float* const* peer_parts = nullptr;     // device array [world]: parts base of every rank (own entry = local)
+        uint32_t* const* peer_flags = nullptr;  // device array [world]: flags base of every rank
+        const float* parts = nullptr;           // local parts base
+        const uint32_t* flags = nullptr;        // local flags base
+        uint32_t* seq = nullptr;                // local step counter (device)
+        int* done = nullptr;                    // CTA completion counter of the pushing kernel (self-resetting)
+        float* x_writeback = nullptr;
+    } tp;
 };
 // Streaming layout of one projection for the decode GEMV: 16-row x 32-column tiles, each
 // {8 x half2 block scales}{quant bytes in MMA-fragment order}, K-major inside a 16-row band.

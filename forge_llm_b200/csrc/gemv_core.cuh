@@ -325,6 +325,8 @@ __device__ __forceinline__ EpiPre epilogue_prefetch(const Phase& ph, int b, int 
             const int row = row0 + 8 * j;
             if (row < ph.N) e.resid[j] = __ldcg(a.resid + size_t(b) * ph.N + row);
         }
+    } else if (ph.epi == EPI_TP_PUSH) {
+        e.pos = int(__ldcg(a.tp.seq)) + 1;  // the step this kernel publishes
     } else if (ph.epi == EPI_QKV && (row0 & 1) == 0) {
         e.pos = pos_hint >= 0 ? pos_hint : a.seq_len[b];
         e.page = a.page_table[size_t(b) * a.pages_per_seq + e.pos / FORGE_KV_PAGE];
@@ -349,6 +351,9 @@ __device__ __forceinline__ void epilogue_row(const Phase& ph, int b, int row, fl
         a.out[size_t(b) * ph.N + row] = v;
     } else if (ph.epi == EPI_RESID) {
         a.out[size_t(b) * ph.N + row] = pre.resid[j] + v;
+    } else if (ph.epi == EPI_TP_PUSH) {
+        const size_t off = (size_t(pre.pos & 1) * a.tp.world + a.tp.rank) * ph.N + row;
+        for (int r = 0; r < a.tp.world; ++r) a.tp.peer_parts[r][off] = v;
     } else if (ph.epi == EPI_SILU) {
         if ((row & 1) == 0)  // rows interleaved at pack time: 2j = gate_j, 2j+1 = up_j
             a.out[size_t(b) * (ph.N / 2) + (row >> 1)] = (v / (1.0f + expf(-v))) * partner;

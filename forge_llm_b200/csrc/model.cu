@@ -69,6 +69,9 @@ struct ForgeModel {
     __half* p_normed_lo = nullptr; __half* p_attn16_lo = nullptr; __half* p_act16_lo = nullptr;
     int gemm_passes = 3;  // 3: split-precision prefill GEMMs (default); 1: single fp16 pass
     TpComm* tp = nullptr;  // tensor-parallel communicator (cfg.tp_world > 1)
+    // peer-memory exchange of the decode step (forge_model_tp_exchange_*): local buffer, peers' mappings, device tables
+    void* tpx_local = nullptr; std::vector<void*> tpx_peer; bool tpx_ready = false;
+    float** d_tpx_parts = nullptr; uint32_t** d_tpx_flags = nullptr; uint32_t* d_tpx_seq = nullptr; int* d_tpx_done = nullptr;
     float* p_part = nullptr; float* d_part = nullptr;  // this rank's partial sums of a row-sliced projection
     bool use_mega = false; // batch-1 decode through the whole-step kernel (forge_model_set_decode_mode)
     // decode scratch (per batch row)
@@ -267,19 +270,46 @@ int32_t prefill_seq(ForgeModel* m, ForgeKV* kv, int seq, const uint32_t* tokens_
     return FORGE_OK;
 }
 
+// exchange buffer layout: flags[2][world] (padded to 256 bytes), then parts[2][world][h]
+inline const uint32_t* tpx_flags(const ForgeModel* m) { return static_cast<const uint32_t*>(m->tpx_local); }
+inline const float* tpx_parts(const ForgeModel* m) { return reinterpret_cast<const float*>(static_cast<const char*>(m->tpx_local) + 256); }
+inline size_t tpx_bytes(const ForgeModel* m) { return 256 + sizeof(float) * 2 * size_t(m->cfg.tp_world) * m->h; }
+
 // ------------------------------------------------------------------ one decode step (launch sequence)
 // forward(), emit.rs:4029-4500, for `batch` sequences.  Tokens are read from m->d_tok, positions
 // from kv->d_seq_len; with `greedy` the next token is selected on the device into m->d_tok.
 int32_t decode_launches(ForgeModel* m, ForgeKV* kv, int batch, bool greedy, bool record) {
     const ForgeModelConfig& c = m->cfg;
     cudaStream_t st = m->stream;
+    // tensor-parallel sums over peer memory: the residual stream alternates between two buffers, because the kernel
+    // that forms hidden + sum(parts) while staging writes it for its successors and other CTAs still read the old one
+    const bool px = c.tp_world > 1 && m->tpx_ready && batch == 1 && !m->trace_on;
+    float* hid[2] = {m->d_hidden, m->d_hidden2};
+    int cur = 0;
+    bool pending = false;  // a pushed sum has not been consumed yet
+    auto tp_consume = [&](GemvArgs& a) {   // a.x is the residual stream: take the pending sum in while staging
+        if (!pending) return;
+        a.tp.world = c.tp_world; a.tp.rank = c.tp_rank; a.tp.consume = 1;
+        a.tp.parts = tpx_parts(m); a.tp.flags = tpx_flags(m); a.tp.seq = m->d_tpx_seq;
+        a.tp.x_writeback = hid[cur ^ 1];
+        cur ^= 1;
+        pending = false;
+    };
+    auto tp_push = [&](const QTiled& w, GemvArgs a) -> int32_t {
+        a.out = nullptr; a.resid = nullptr;
+        a.tp.world = c.tp_world; a.tp.rank = c.tp_rank; a.tp.consume = 0;
+        a.tp.peer_parts = m->d_tpx_parts; a.tp.peer_flags = m->d_tpx_flags; a.tp.seq = m->d_tpx_seq; a.tp.done = m->d_tpx_done;
+        pending = true;
+        return gemv_tc(w, EPI_TP_PUSH, a, m->split, m->d_err, st);
+    };
     FORGE_TRY(embedding_rows(m->d_hidden, m->embed, m->d_tok, batch, m->h, record ? m->d_hist : nullptr, m->d_step, st));
     for (int l = 0; l < c.num_layers; ++l) {
         ForgeLayer& L = m->layers[l];
         __half* kp = kv->k_pool + size_t(l) * kv->layer_stride;
         __half* vp = kv->v_pool + size_t(l) * kv->layer_stride;
         GemvArgs a;
-        a.x = m->d_hidden; a.norm_w = L.attn_norm; a.eps = c.rms_norm_eps; a.batch = batch;
+        a.x = hid[cur]; a.norm_w = L.attn_norm; a.eps = c.rms_norm_eps; a.batch = batch;
+        if (px) tp_consume(a);
         a.bias = L.qkv_bias; a.rope = m->rope; a.q_out = m->d_q; a.k_pool = kp; a.v_pool = vp;
         a.page_table = kv->d_page_table; a.seq_len = kv->d_seq_len; a.pages_per_seq = kv->pages_per_seq;
         a.qk = m->qk; a.kv = m->kv; a.head_dim = m->hd;
@@ -289,25 +319,27 @@ int32_t decode_launches(ForgeModel* m, ForgeKV* kv, int batch, bool greedy, bool
                           batch, m->nq, m->nkv, m->hd, kv->max_seq, kv->attn_ws, kv->attn_counters, kv->splits};
         FORGE_TRY(attn_decode(da, st));
         GemvArgs o;
-        o.x = m->d_attn; o.out = m->d_hidden; o.resid = m->d_hidden; o.batch = batch;
+        o.x = m->d_attn; o.out = hid[cur]; o.resid = hid[cur]; o.batch = batch;
         o.next_w = L.gateup_t.data; o.next_bytes = qtiled_bytes(L.gateup_t);
-        FORGE_TRY(row_sliced_gemv(m, L.o_t, o, batch, st));
+        if (px) FORGE_TRY(tp_push(L.o_t, o)); else FORGE_TRY(row_sliced_gemv(m, L.o_t, o, batch, st));
         GemvArgs g;
-        g.x = m->d_hidden; g.norm_w = L.ffn_norm; g.eps = c.rms_norm_eps; g.out = m->d_act; g.batch = batch;
+        g.x = hid[cur]; g.norm_w = L.ffn_norm; g.eps = c.rms_norm_eps; g.out = m->d_act; g.batch = batch;
+        if (px) tp_consume(g);
         g.next_w = L.down_t.data; g.next_bytes = qtiled_bytes(L.down_t);
         FORGE_TRY(gemv_tc(L.gateup_t, EPI_SILU, g, m->split, m->d_err, st));
         GemvArgs d;
-        d.x = m->d_act; d.out = m->d_hidden; d.resid = m->d_hidden; d.batch = batch;
+        d.x = m->d_act; d.out = hid[cur]; d.resid = hid[cur]; d.batch = batch;
         {   // the next projection on the stream: the next layer's QKV, or the head (a part of it: it is larger than L2)
             const QTiled& nx = l + 1 < c.num_layers ? m->layers[l + 1].qkv_t : m->lm_head_t;
             d.next_w = nx.data; d.next_bytes = std::min(qtiled_bytes(nx), size_t(48) << 20);
         }
-        FORGE_TRY(row_sliced_gemv(m, L.down_t, d, batch, st));
+        if (px) FORGE_TRY(tp_push(L.down_t, d)); else FORGE_TRY(row_sliced_gemv(m, L.down_t, d, batch, st));
         if (m->trace_on)
             FORGE_CUDA(cudaMemcpyAsync(m->trace + size_t(l) * batch * m->h, m->d_hidden, sizeof(float) * batch * m->h, cudaMemcpyDeviceToDevice, st));
     }
     GemvArgs lm;
-    lm.x = m->d_hidden; lm.norm_w = m->final_norm; lm.eps = c.rms_norm_eps; lm.out = m->d_logits; lm.batch = batch;
+    lm.x = hid[cur]; lm.norm_w = m->final_norm; lm.eps = c.rms_norm_eps; lm.out = m->d_logits; lm.batch = batch;
+    if (px) tp_consume(lm);
     FORGE_TRY(gemv_tc(m->lm_head_t, EPI_STORE, lm, m->split, m->d_err, st));
     if (greedy) FORGE_TRY(argmax_slices(m->d_tok, m->d_logits, m->V, batch, m->d_amax_val, m->d_amax_idx, m->d_amax_ticket, st));
     FORGE_TRY(step_advance(kv->d_seq_len, batch, m->d_step, st));
@@ -518,6 +550,8 @@ void forge_model_destroy(ForgeModel* m) {
     cudaSetDevice(m->device);
     if (m->stream) cudaStreamSynchronize(m->stream);
     tp_destroy(m->tp);
+    for (void* q : m->tpx_peer) if (q) cudaIpcCloseMemHandle(q);
+    if (m->tpx_local) cudaFree(m->tpx_local);
     for (void* q : m->allocs) cudaFree(q);
     for (auto& e : m->ev) if (e) cudaEventDestroy(e);
     if (m->stream) cudaStreamDestroy(m->stream);
@@ -525,6 +559,56 @@ void forge_model_destroy(ForgeModel* m) {
 }
 
 void* forge_model_stream(ForgeModel* m) { return m ? static_cast<void*>(m->stream) : nullptr; }
+
+int32_t forge_model_tp_exchange_export(ForgeModel* m, uint8_t* handle_out) {
+    if (!m || !handle_out) { set_error("bad argument to forge_model_tp_exchange_export"); return FORGE_ERR_INVALID_ARG; }
+    if (m->cfg.tp_world < 2 || m->cfg.tp_world > 16) { set_error("peer exchange needs 2..16 tensor-parallel ranks"); return FORGE_ERR_INVALID_ARG; }
+    static_assert(sizeof(cudaIpcMemHandle_t) == FORGE_TP_HANDLE_BYTES, "FORGE_TP_HANDLE_BYTES must match cudaIpcMemHandle_t");
+    FORGE_CUDA(cudaSetDevice(m->device));
+    if (!m->tpx_local) {
+        FORGE_CUDA(cudaMalloc(&m->tpx_local, tpx_bytes(m)));
+        FORGE_CUDA(cudaMemset(m->tpx_local, 0, tpx_bytes(m)));
+        FORGE_CUDA(cudaDeviceSynchronize());
+    }
+    cudaIpcMemHandle_t h;
+    FORGE_CUDA(cudaIpcGetMemHandle(&h, m->tpx_local));
+    memcpy(handle_out, &h, sizeof(h));
+    return FORGE_OK;
+}
+
+int32_t forge_model_tp_exchange_attach(ForgeModel* m, const uint8_t* handles) {
+    if (!m || !handles) { set_error("bad argument to forge_model_tp_exchange_attach"); return FORGE_ERR_INVALID_ARG; }
+    if (!m->tpx_local) { set_error("call forge_model_tp_exchange_export first"); return FORGE_ERR_INVALID_ARG; }
+    if (m->tpx_ready) { set_error("the exchange is already attached"); return FORGE_ERR_INVALID_ARG; }
+    FORGE_CUDA(cudaSetDevice(m->device));
+    const int world = m->cfg.tp_world, rank = m->cfg.tp_rank;
+    m->tpx_peer.assign(world, nullptr);
+    std::vector<float*> parts(world);
+    std::vector<uint32_t*> flags(world);
+    for (int r = 0; r < world; ++r) {
+        void* base = m->tpx_local;
+        if (r != rank) {
+            cudaIpcMemHandle_t h;
+            memcpy(&h, handles + size_t(r) * FORGE_TP_HANDLE_BYTES, sizeof(h));
+            cudaError_t e = cudaIpcOpenMemHandle(&base, h, cudaIpcMemLazyEnablePeerAccess);
+            if (e != cudaSuccess) { set_error("cudaIpcOpenMemHandle(rank %d): %s", r, cudaGetErrorString(e)); return FORGE_ERR_COMM; }
+            m->tpx_peer[r] = base;
+        }
+        flags[r] = static_cast<uint32_t*>(base);
+        parts[r] = reinterpret_cast<float*>(static_cast<char*>(base) + 256);
+    }
+    FORGE_TRY(dev_alloc(m, &m->d_tpx_parts, size_t(world)));
+    FORGE_TRY(dev_alloc(m, &m->d_tpx_flags, size_t(world)));
+    FORGE_TRY(dev_alloc(m, &m->d_tpx_seq, 1));
+    FORGE_TRY(dev_alloc(m, &m->d_tpx_done, 1));
+    FORGE_CUDA(cudaMemcpy(m->d_tpx_parts, parts.data(), sizeof(float*) * world, cudaMemcpyHostToDevice));
+    FORGE_CUDA(cudaMemcpy(m->d_tpx_flags, flags.data(), sizeof(uint32_t*) * world, cudaMemcpyHostToDevice));
+    FORGE_CUDA(cudaMemset(m->d_tpx_seq, 0, sizeof(uint32_t)));
+    FORGE_CUDA(cudaMemset(m->d_tpx_done, 0, sizeof(int)));
+    FORGE_CUDA(cudaDeviceSynchronize());
+    m->tpx_ready = true;
+    return FORGE_OK;
+}
 
 int32_t forge_tp_unique_id(uint8_t* id_out) {
     if (!id_out) { set_error("null id buffer"); return FORGE_ERR_INVALID_ARG; }

@@ -83,6 +83,7 @@ class KVCache:
 
 
 TP_ID_BYTES = 128  # FORGE_TP_ID_BYTES
+TP_HANDLE_BYTES = 64  # FORGE_TP_HANDLE_BYTES
 
 
 class Model:
@@ -115,6 +116,19 @@ class Model:
         if uid.size != TP_ID_BYTES:
             raise ValueError(f"the rendezvous id is {TP_ID_BYTES} bytes")
         check(lib.forge_model_tp_init(self._h, _p(uid)))
+
+    def tp_exchange_handle(self) -> np.ndarray:
+        """This rank's handle to its peer-memory exchange buffer (to be gathered over all ranks, in rank order)."""
+        out = np.zeros(TP_HANDLE_BYTES, np.uint8)
+        check(lib.forge_model_tp_exchange_export(self._h, _p(out)))
+        return out
+
+    def tp_exchange_attach(self, handles: np.ndarray) -> None:
+        """Maps the peers' exchange buffers; the batch-1 decode step then sums over peer memory."""
+        h = np.ascontiguousarray(handles, np.uint8).reshape(-1)
+        if h.size != TP_HANDLE_BYTES * self.tp_world:
+            raise ValueError("one handle per rank, in rank order")
+        check(lib.forge_model_tp_exchange_attach(self._h, _p(h)))
 
     def new_cache(self, max_seq: int | None = None, batch: int = 1) -> KVCache:
         return KVCache(self, max_seq, batch)

@@ -181,6 +181,17 @@ void* forge_model_stream(ForgeModel* model);
 int32_t forge_tp_unique_id(uint8_t* id_out);
 int32_t forge_model_tp_init(ForgeModel* model, const uint8_t* id);
 
+/* Optional, after forge_model_tp_init: sum the decode step's partial products over peer memory instead of calling the
+ * collective library.  Each rank exports a handle (CUDA IPC) to a small exchange buffer it owns; after every rank has
+ * all `tp_world` handles (rank order, FORGE_TP_HANDLE_BYTES each, gathered over any host channel) it attaches them.
+ * From then on the batch-1 decode step pushes each row-sliced projection's partial rows straight into the peers'
+ * buffers from the GEMV epilogue (NVLink stores) and the next kernel adds the ranks' parts while it stages its input;
+ * prefill and batched decode keep the library all-reduce.  Needs peer access between the GPUs (one process per GPU,
+ * all GPUs visible to every process). */
+#define FORGE_TP_HANDLE_BYTES 64
+int32_t forge_model_tp_exchange_export(ForgeModel* model, uint8_t* handle_out);
+int32_t forge_model_tp_exchange_attach(ForgeModel* model, const uint8_t* handles);
+
 /* Numeric form of the prefill GEMMs (matmul_mat_*, E:2278-2299).  3 (default): both operands
  * are carried as fp16 hi+lo pairs and three tensor-core passes are accumulated in f32 (~1e-6
  * relative to the reference's all-f32 arithmetic); 1: one fp16 pass (~3e-4 relative per GEMM,

@@ -219,3 +219,40 @@ def test_whole_step_decode_kernel(oracle, quant, hd, nq, nkv, bias):
     assert kv.len() == 182
     kv.close()
     gm.close()
+
+
+@pytest.mark.gpu
+def test_c2_full_size_properties():
+    """Configuration 2 at the benchmark's full size (16 layers, 128256-token vocabulary, 1501-token prompt), where the
+    CPU restatement would take minutes: size-independent properties instead.  (a) Splitting the prompt into two
+    prefill calls gives the same logits and greedy ids as one call; (b) the device-side greedy loop equals
+    forward() + host arg-max token by token; (c) a repeated request is bit-identical."""
+    from forge_llm_b200 import configs, runtime, synth
+    c = configs.CONFIGS["c2"]
+    blob = synth.make_weights_bin(c)
+    toks = synth.prompt_tokens(c, 1501)
+    gm = runtime.Model(c, blob)
+    kv = gm.new_cache(max_seq=1501 + 24)
+    whole = gm.forward_prefill(toks, kv)
+    ids = []
+    lg = whole
+    for _ in range(8):
+        t = int(np.flatnonzero(lg == lg.max())[-1])  # last index on ties, as the reference's argmax
+        ids.append(t)
+        lg = gm.forward(t, kv)
+    kv.reset()
+    gm.forward_prefill(toks[:1000], kv, want_logits=False)
+    split = gm.forward_prefill(toks[1000:], kv)
+    # the two calls tile the rows differently, so tensor-core sums associate differently: tolerance, not equality
+    assert np.abs(split - whole).max() < 2e-2
+    assert int(np.argmax(split)) == int(np.argmax(whole))
+    kv.reset()
+    dev_ids = gm.generate_greedy(toks, 8, kv)
+    assert list(dev_ids) == ids
+    kv.reset()
+    again = gm.generate_greedy(toks, 8, kv)
+    assert np.array_equal(again, dev_ids)
+    kv.reset()
+    assert np.array_equal(gm.forward_prefill(toks, kv), whole)
+    kv.close()
+    gm.close()
