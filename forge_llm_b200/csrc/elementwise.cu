@@ -42,6 +42,40 @@ __global__ void rms_norm_kernel(OutT* __restrict__ out, __half* __restrict__ lo,
     }
 }
 
+// fp16 hi/lo output for rows of at most 256 * 4 * NV floats: the row is read once with 128-bit loads and stays in
+// registers between the sum of squares and the scaling
+template <int NV>
+__global__ void __launch_bounds__(256) rms_norm_f16_vec_kernel(__half* __restrict__ out, __half* __restrict__ lo, const float* __restrict__ in,
+                                                                const float* __restrict__ w, int n, float eps) {
+    __shared__ float red[32];
+    const float* x = in + size_t(blockIdx.x) * n;
+    float4 v[NV];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int e = (threadIdx.x + i * 256) * 4;
+        v[i] = e < n ? *reinterpret_cast<const float4*>(x + e) : make_float4(0.f, 0.f, 0.f, 0.f);
+        ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+    }
+    ss = block_sum(ss, red);
+    const float inv = 1.0f / sqrtf(ss / float(n) + eps);
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int e = (threadIdx.x + i * 256) * 4;
+        if (e >= n) continue;
+        const float4 ww = *reinterpret_cast<const float4*>(w + e);
+        const float r[4] = {v[i].x * inv * ww.x, v[i].y * inv * ww.y, v[i].z * inv * ww.z, v[i].w * inv * ww.w};
+        const __half2 h0 = __floats2half2_rn(r[0], r[1]), h1 = __floats2half2_rn(r[2], r[3]);
+        const size_t o = size_t(blockIdx.x) * n + e;
+        *reinterpret_cast<uint2*>(out + o) = make_uint2(*reinterpret_cast<const uint32_t*>(&h0), *reinterpret_cast<const uint32_t*>(&h1));
+        if (lo) {
+            const float2 f0 = __half22float2(h0), f1 = __half22float2(h1);
+            const __half2 l0 = __floats2half2_rn(r[0] - f0.x, r[1] - f0.y), l1 = __floats2half2_rn(r[2] - f1.x, r[3] - f1.y);
+            *reinterpret_cast<uint2*>(lo + o) = make_uint2(*reinterpret_cast<const uint32_t*>(&l0), *reinterpret_cast<const uint32_t*>(&l1));
+        }
+    }
+}
+
 // thread per (row, head, pair): adjacent-pair rotation, table = {cos, sin}[pos][hd/2]
 __global__ void rope_kernel(float* data, int rows, int base_pos, int hd, int heads, const float2* __restrict__ table) {
     int half = hd / 2;
@@ -232,7 +266,10 @@ int32_t rms_norm_f32(float* out, const float* in, const float* w, int rows, int 
 }
 int32_t rms_norm_f16(__half* out, __half* lo, const float* in, const float* w, int rows, int n, float eps, cudaStream_t st) {
     if (rows <= 0) return FORGE_OK;
-    rms_norm_kernel<__half><<<rows, 256, 0, st>>>(out, lo, in, w, n, eps);
+    if (n % 4 == 0 && n <= 2048) rms_norm_f16_vec_kernel<2><<<rows, 256, 0, st>>>(out, lo, in, w, n, eps);
+    else if (n % 4 == 0 && n <= 4096) rms_norm_f16_vec_kernel<4><<<rows, 256, 0, st>>>(out, lo, in, w, n, eps);
+    else if (n % 4 == 0 && n <= 8192) rms_norm_f16_vec_kernel<8><<<rows, 256, 0, st>>>(out, lo, in, w, n, eps);
+    else rms_norm_kernel<__half><<<rows, 256, 0, st>>>(out, lo, in, w, n, eps);
     FORGE_LAUNCH_CHECK();
     return FORGE_OK;
 }

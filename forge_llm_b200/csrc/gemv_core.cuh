@@ -311,6 +311,7 @@ struct EpiPre {
 };
 
 // pos_hint: the sequence position if the caller has already fetched it (saves a dependent load), else -1
+template <bool TP>
 __device__ __forceinline__ EpiPre epilogue_prefetch(const Phase& ph, int b, int row0, bool mine, int pos_hint) {
     EpiPre e;
     e.resid[0] = e.resid[1] = 0.f;
@@ -325,7 +326,7 @@ __device__ __forceinline__ EpiPre epilogue_prefetch(const Phase& ph, int b, int 
             const int row = row0 + 8 * j;
             if (row < ph.N) e.resid[j] = __ldcg(a.resid + size_t(b) * ph.N + row);
         }
-    } else if (ph.epi == EPI_TP_PUSH) {
+    } else if (TP && ph.epi == EPI_TP_PUSH) {
         e.pos = int(__ldcg(a.tp.seq)) + 1;  // the step this kernel publishes
     } else if (ph.epi == EPI_QKV && (row0 & 1) == 0) {
         e.pos = pos_hint >= 0 ? pos_hint : a.seq_len[b];
@@ -344,6 +345,7 @@ __device__ __forceinline__ EpiPre epilogue_prefetch(const Phase& ph, int b, int 
     return e;
 }
 
+template <bool TP>
 __device__ __forceinline__ void epilogue_row(const Phase& ph, int b, int row, float v, float partner, const EpiPre& pre, int j) {
     if (row >= ph.N) return;
     const GemvArgs& a = ph.a;
@@ -351,7 +353,7 @@ __device__ __forceinline__ void epilogue_row(const Phase& ph, int b, int row, fl
         a.out[size_t(b) * ph.N + row] = v;
     } else if (ph.epi == EPI_RESID) {
         a.out[size_t(b) * ph.N + row] = pre.resid[j] + v;
-    } else if (ph.epi == EPI_TP_PUSH) {
+    } else if (TP && ph.epi == EPI_TP_PUSH) {
         const size_t off = (size_t(pre.pos & 1) * a.tp.world + a.tp.rank) * ph.N + row;
         for (int r = 0; r < a.tp.world; ++r) a.tp.peer_parts[r][off] = v;
     } else if (ph.epi == EPI_SILU) {
@@ -382,7 +384,7 @@ __device__ __forceinline__ void epilogue_row(const Phase& ph, int b, int row, fl
 // ---- consumer side, step 2: all units of this CTA for one phase and one batch row.
 // `on_row(row, value)` is called by the finishing thread after the epilogue (used by the whole-step
 // kernel to track the arg-max of the logits); pass a no-op otherwise.
-template <int QUANT, typename RowHook>
+template <int QUANT, typename RowHook, bool TP = false>
 __device__ __forceinline__ void consume_phase(const Phase& ph, Shared& sh, const unsigned char* ring, const uint2* xf,
                                               const int4* xoff, float unscale, int b, int& cc, RowHook on_row, int pos_hint = -1) {
     using T = Tile<QUANT>;
@@ -404,7 +406,7 @@ __device__ __forceinline__ void consume_phase(const Phase& ph, Shared& sh, const
         const int rt = band * bt + r8;
         const int row0 = rt * 16 + g;  // and row0 + 8
         // operands of the epilogue that do not depend on the product are fetched now, under the tile loop
-        const EpiPre pre = epilogue_prefetch(ph, b, row0, t == 0 && khalf == 0, pos_hint);
+        const EpiPre pre = epilogue_prefetch<TP>(ph, b, row0, t == 0 && khalf == 0, pos_hint);
         // per-lane accumulators: rows g / g+8 of this warp's row tile x digit columns 2t / 2t+1
         float acc[4] = {0.f, 0.f, 0.f, 0.f};
         for (int c = c0; c < c1; ++c, ++cc) {
@@ -518,8 +520,8 @@ __device__ __forceinline__ void consume_phase(const Phase& ph, Shared& sh, const
         // pair partners (rows r^1) live in the neighbouring quad
         const float o0 = __shfl_xor_sync(0xffffffffu, v0, 4), o1 = __shfl_xor_sync(0xffffffffu, v1, 4);
         if (finish && t == 0) {
-            epilogue_row(ph, b, row0, v0, o0, pre, 0);
-            epilogue_row(ph, b, row0 + 8, v1, o1, pre, 1);
+            epilogue_row<TP>(ph, b, row0, v0, o0, pre, 0);
+            epilogue_row<TP>(ph, b, row0 + 8, v1, o1, pre, 1);
             on_row(row0, v0);
             on_row(row0 + 8, v1);
         }

@@ -43,7 +43,9 @@ struct TcParams {
     int* err;  // device error word (set when a bounded wait gives up)
 };
 
-template <int QUANT>
+// TP: the instantiation that can take part in the tensor-parallel sums over peer memory (its extra code stays out
+// of the single-GPU kernel: every decode kernel starts with a cold instruction cache, so size matters)
+template <int QUANT, bool TP>
 __global__ void __launch_bounds__(kThreads, 1) gemv_tc_kernel(TcParams p) {
     using T = Tile<QUANT>;
     extern __shared__ __align__(128) unsigned char smem[];
@@ -75,7 +77,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tc_kernel(TcParams p) {
         // the position of the new cache row is needed late (epilogue) but heads a chain of dependent loads: ask now
         const int pos = ph.epi == EPI_QKV ? ph.a.seq_len[b] : -1;
         float unscale;
-        if (ph.a.tp.consume) {
+        if (TP && ph.a.tp.consume) {
             // the input is a sum over the tensor-parallel ranks that arrives through peer stores (see GemvArgs::Tp)
             const GemvArgs::Tp& tp = ph.a.tp;
             const uint32_t step = __ldcg(tp.seq);
@@ -96,10 +98,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tc_kernel(TcParams p) {
         } else {
             unscale = stage_activation<QUANT, false>(xf, s_xoff, sh, ph.a.x + size_t(b) * ph.K, ph.K, ph.a.norm_w, ph.a.eps);
         }
-        consume_phase<QUANT>(ph, sh, ring, xf, s_xoff, unscale, b, cc, [](int, float) {}, pos);
+        auto no_hook = [](int, float) {};
+        consume_phase<QUANT, decltype(no_hook), TP>(ph, sh, ring, xf, s_xoff, unscale, b, cc, no_hook, pos);
     }
     csync();
-    if (ph.epi == EPI_TP_PUSH && tid == 0) {
+    if (TP && ph.epi == EPI_TP_PUSH && tid == 0) {
         // this CTA's partial rows are on their way to the peers; the last CTA to get here publishes the step
         const GemvArgs::Tp& tp = ph.a.tp;
         __threadfence_system();
@@ -188,8 +191,10 @@ int32_t launch(const QTiled& w, GemvEpilogue epi, const GemvArgs& a, const GemvS
     const int grid = ph.units < sms ? ph.units : sms;
     // one limit for every launch of this kernel: a launch replayed later (a graph node re-issued by a profiler) must
     // not find a smaller limit left behind by another matrix
-    FORGE_CUDA(cudaFuncSetAttribute(gemv_tc_kernel<QUANT>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(dyn_smem_bytes<QUANT>(kMaxKB))));
-    FORGE_CUDA(launch_pdl(gemv_tc_kernel<QUANT>, dim3(grid), dim3(kThreads), smem, st, p));
+    const bool tp = a.tp.consume || epi == EPI_TP_PUSH;
+    auto kern = tp ? gemv_tc_kernel<QUANT, true> : gemv_tc_kernel<QUANT, false>;
+    FORGE_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(dyn_smem_bytes<QUANT>(kMaxKB))));
+    FORGE_CUDA(launch_pdl(kern, dim3(grid), dim3(kThreads), smem, st, p));
     FORGE_LAUNCH_CHECK();
     return FORGE_OK;
 }
