@@ -406,7 +406,8 @@ __device__ __forceinline__ void consume_phase(const Phase& ph, Shared& sh, const
         const int rt = band * bt + r8;
         const int row0 = rt * 16 + g;  // and row0 + 8
         // operands of the epilogue that do not depend on the product are fetched now, under the tile loop
-        const EpiPre pre = epilogue_prefetch<TP>(ph, b, row0, t == 0 && khalf == 0, pos_hint);
+        // (the warp that will finish the unit: the even-k warp of the tile, or the unit's turn in the 16-row form)
+        const EpiPre pre = epilogue_prefetch<TP>(ph, b, row0, t == 0 && (wide ? khalf == 0 : warp == ui % kConsumerWarps), pos_hint);
         // per-lane accumulators: rows g / g+8 of this warp's row tile x digit columns 2t / 2t+1
         float acc[4] = {0.f, 0.f, 0.f, 0.f};
         for (int c = c0; c < c1; ++c, ++cc) {
@@ -465,15 +466,26 @@ __device__ __forceinline__ void consume_phase(const Phase& ph, Shared& sh, const
             v1 += sh.pair[r8][g + 8];
             asm volatile("bar.sync %0, 64;" ::"r"(2 + r8) : "memory");
         } else {
-            // all sixteen warps worked on the same row tile: warp 0 adds their sums (double-buffered by unit
-            // parity; the next unit's barrier orders the reuse)
+            // All sixteen warps worked on the same row tile: one of them adds their sums and runs the epilogue, the
+            // others go straight on to the next unit.  The duty rotates (unit ui -> warp ui % 16), so no warp is the
+            // bottleneck, and nobody waits for the epilogue: the sums travel through red[ui & 1], guarded by two
+            // pairs of named barriers in producer/consumer form -
+            //   "full" (ids 12, 13): 15 warps arrive after writing, the finisher syncs before reading;
+            //   "free" (ids 10, 11): the finisher arrives after reading, the other 15 warps sync before they write the
+            //                        same buffer again two units later (only armed if that unit exists).
             const int par = ui & 1;
+            const int fin = ui % kConsumerWarps;
+            if (ui >= 2 && warp != (ui - 2) % kConsumerWarps) asm volatile("bar.sync %0, %1;" ::"r"(10 + par), "n"(kCT) : "memory");
             if (t == 0) { sh.red[par][warp][g] = v0; sh.red[par][warp][g + 8] = v1; }
-            csync();
-            if (warp != 0) continue;
+            if (warp != fin) {
+                asm volatile("bar.arrive %0, %1;" ::"r"(12 + par), "n"(kCT) : "memory");
+                continue;
+            }
+            asm volatile("bar.sync %0, %1;" ::"r"(12 + par), "n"(kCT) : "memory");
             v0 = 0.f; v1 = 0.f;
 #pragma unroll
             for (int w = 0; w < kConsumerWarps; ++w) { v0 += sh.red[par][w][g]; v1 += sh.red[par][w][g + 8]; }
+            if (u + 2 * int(gridDim.x) < ph.units) asm volatile("bar.arrive %0, %1;" ::"r"(10 + par), "n"(kCT) : "memory");
         }
         v0 *= unscale;
         v1 *= unscale;
