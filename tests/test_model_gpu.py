@@ -256,3 +256,29 @@ def test_c2_full_size_properties():
     assert np.array_equal(gm.forward_prefill(toks, kv), whole)
     kv.close()
     gm.close()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("quant", [8, 4])
+def test_page_and_tile_boundaries(oracle, quant):
+    """Context lengths on both sides of the 64-position page (and attention tile) boundary and of the 128/192/256
+    token tiles of the GEMM: prefill logits, then decode steps that cross the next boundary."""
+    from forge_llm_b200 import configs, runtime, synth
+    c = configs.tiny(quant, hd=64, nq=4, nkv=2, layers=2)
+    blob = synth.make_weights_bin(c)
+    gm = runtime.Model(c, blob)
+    for n in (63, 64, 65, 127, 128, 129, 191, 193, 255, 257):
+        toks = synth.prompt_tokens(c, n, seed=100 + n)
+        om = oracle.OracleModel(c, blob, kv_mode=oracle.KV_F16)
+        kv = gm.new_cache(max_seq=n + 8)
+        lo = om.forward_prefill(toks)
+        lg = gm.forward_prefill(toks, kv)
+        assert np.abs(lg - lo).max() < LOGIT_TOL, n
+        for _ in range(3):
+            t = oracle.argmax(lo)
+            lo = om.forward(t)
+            lg = gm.forward(t, kv)
+            assert np.abs(lg - lo).max() < LOGIT_TOL, n
+        assert kv.len() == n + 3
+        kv.close()
+    gm.close()
