@@ -241,31 +241,40 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_ts_kernel(const __grid_const
         for (int j = 0; j < kPrefetch; ++j) gload(j, j);
         bool ok = true;
         const uint32_t lane_base = tmem + (uint32_t(quad * 32) << 16) + kWBase + uint32_t(blk * 16);
-        for (int kt = 0; kt < nk; ++kt) {
-            const int sw = kt % WS, use = kt / WS;
-            uint32_t cur[4 * QV];
-#pragma unroll
-            for (int i = 0; i < QV; ++i) { cur[4 * i] = q[0][i].x; cur[4 * i + 1] = q[0][i].y; cur[4 * i + 2] = q[0][i].z; cur[4 * i + 3] = q[0][i].w; }
-            const __half2 d2 = __half2half2(dsc[0]);
-#pragma unroll
-            for (int j = 0; j + 1 < kPrefetch; ++j) {
-#pragma unroll
-                for (int i = 0; i < QV; ++i) q[j][i] = q[j + 1][i];
-                dsc[j] = dsc[j + 1];
-            }
-            gload(kt + kPrefetch, kPrefetch - 1);
-            uint32_t hi[16], lo[16];
-            dequant_block<QUANT, SPLIT>(cur, d2, hi, lo);
-            if (ok && use > 0 && !mbar_wait(&empty_w[sw], (use - 1) & 1, &s_err)) { atomicExch(&s_err, 1); ok = false; }
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t col = lane_base + uint32_t(sw * W_COLS);
-            tmem_st16(col, hi);
-            if (SPLIT) tmem_st16(col + BK / 2, lo);
+        // The queue is a ring with compile-time slot indices (the K loop is unrolled by its depth): a slot is refilled
+        // right after it is read and not touched again until kPrefetch steps later.  (Shifting the queue instead
+        // would make every step wait for the youngest load.)
+        // The stores of step i into tensor memory complete under the arithmetic of step i + 1: a stage is published
+        // (wait::st, fence, arrive) one step late.
+        static_assert(kPrefetch == WS, "one unrolled round covers the weight stages once");
+        auto publish = [&](int stage) {
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
-            if (lane == 0) mbar_arrive(&full_w[sw]);
+            if (lane == 0) mbar_arrive(&full_w[stage]);
+        };
+        for (int kt0 = 0; kt0 < nk; kt0 += kPrefetch) {
+#pragma unroll
+            for (int j = 0; j < kPrefetch; ++j) {
+                const int kt = kt0 + j;
+                if (kt >= nk) break;
+                const int sw = j, use = kt0 / WS;
+                uint32_t cur[4 * QV];
+#pragma unroll
+                for (int i = 0; i < QV; ++i) { cur[4 * i] = q[j][i].x; cur[4 * i + 1] = q[j][i].y; cur[4 * i + 2] = q[j][i].z; cur[4 * i + 3] = q[j][i].w; }
+                const __half2 d2 = __half2half2(dsc[j]);
+                gload(kt + kPrefetch, j);
+                uint32_t hi[16], lo[16];
+                dequant_block<QUANT, SPLIT>(cur, d2, hi, lo);
+                if (kt > 0) publish((j + WS - 1) % WS);
+                if (ok && use > 0 && !mbar_wait(&empty_w[sw], (use - 1) & 1, &s_err)) { atomicExch(&s_err, 1); ok = false; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t col = lane_base + uint32_t(sw * W_COLS);
+                tmem_st16(col, hi);
+                if (SPLIT) tmem_st16(col + BK / 2, lo);
+            }
         }
+        publish((nk - 1) % WS);
 
         // ---------------- epilogue: lane = weight row, columns = tokens; two warps per lane quadrant split the tokens
         if (!mbar_wait(&accum_full, 0, &s_err)) atomicExch(&s_err, 1);
