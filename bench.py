@@ -153,7 +153,7 @@ def workload_config(key: str, c: dict) -> dict:
 
 
 # DRAM bytes moved per algorithmic byte of the streaming GEMV (dram__bytes_read + dram__bytes_write of one captured
-# launch, 153.6 MB for 147.75 MB of weights: profiles/gemv_tc_kernel_c2_lm_head.md).  A decode step is one graph
+# launch, 153.6 MB for 147.75 MB of weights; the capture is summarised under profiles/).  A decode step is one graph
 # replay of such kernels; its traffic is scaled from that capture by the bytes it streams.
 DRAM_TRAFFIC_RATIO = 1.04
 TRAFFIC_NOTE = "scaled from one ncu capture of the GEMV kernel (traffic/algorithmic = 1.04)"
