@@ -112,21 +112,22 @@ struct GemvArgs {
     const void* next_w = nullptr;
     size_t next_bytes = 0;
     // Tensor-parallel sum over peer memory (decode, batch 1).  Every rank owns an exchange buffer
-    // {flags[2 slots][world], parts[2 slots][world][h]} that its peers map (CUDA IPC).
-    //  * EPI_TP_PUSH (the row-sliced projection): each finished row of this rank's partial product is stored into
-    //    parts[slot][tp.rank] of EVERY rank's buffer (NVLink stores); the last CTA to finish publishes the step number
-    //    in flags[slot][tp.rank] of every rank and advances the local step counter.  slot = step & 1.
-    //  * tp.consume (the kernel that reads the result next): waits (bounded) until all `world` flags of the slot carry
-    //    the current step, then stages x = x + sum over ranks of parts[slot][r] (rank order, so every rank forms the
-    //    same bits) and writes the sum once to x_writeback (the residual stream for the kernels after it).
+    // ll[2 slots][world][h] of {value, step} pairs that its peers map (CUDA IPC).
+    //  * EPI_TP_PUSH (the row-sliced projection): each finished row of this rank's partial product is stored as one
+    //    8-byte {value, step} pair into ll[slot][tp.rank] of EVERY rank's buffer (NVLink stores).  The pair is written
+    //    atomically, so the value needs no fence and no completion flag: a reader sees it as soon as the step matches.
+    //  * tp.consume (the kernel that reads the result next): stages x = x + sum over ranks of ll[slot][r] in rank
+    //    order (every rank forms the same bits), spinning - bounded - on pairs whose step is not the current one yet,
+    //    and writes the sum once to x_writeback (the residual stream for the kernels after it).
+    // step = *step_counter * step_mul + step_add: the device-side decode step counter makes it unique across graph
+    // replays; step_add (>= 1) numbers the sums inside a step.  Two slots alternate: a rank can be at most one sum
+    // ahead of its slowest peer.
     struct Tp {
-        int world = 0, rank = 0, consume = 0;
-        float* const* peer_parts = nullptr;     // device array [world]: parts base of every rank (own entry = local)
-        uint32_t* const* peer_flags = nullptr;  // device array [world]: flags base of every rank
-        const float* parts = nullptr;           // local parts base
-        const uint32_t* flags = nullptr;        // local flags base
-        uint32_t* seq = nullptr;                // local step counter (device)
-        int* done = nullptr;                    // CTA completion counter of the pushing kernel (self-resetting)
+        int world = 0, rank = 0, consume = 0, slot = 0;
+        uint2* const* peer_ll = nullptr;        // device array [world]: exchange buffer of every rank (own entry = local)
+        const uint2* ll = nullptr;              // local exchange buffer
+        const uint32_t* step_counter = nullptr; // device, advanced once per decode step
+        uint32_t step_mul = 0, step_add = 0;
         float* x_writeback = nullptr;
     } tp;
 };
@@ -194,7 +195,7 @@ int32_t argmax_last(uint32_t* result, const float* logits, int n, int batch, cud
 constexpr int kArgmaxSlices = 148;
 int32_t argmax_slices(uint32_t* result, const float* logits, int n, int batch, float* sval, int* sidx, int* ticket, cudaStream_t st);
 int32_t f32_to_f16(__half* out, __half* lo, const float* in, size_t n, cudaStream_t st);
-int32_t step_advance(int32_t* seq_len, int batch, int32_t* step, cudaStream_t st);
+int32_t step_advance(int32_t* seq_len, int batch, int32_t* step, cudaStream_t st, uint32_t* extra_counter = nullptr);
 int32_t gather_rows_f16(float* out, const __half* pool, const int32_t* page_row, int len, int kvd, cudaStream_t st);
 
 // ------------------------------------------------------------------ attention

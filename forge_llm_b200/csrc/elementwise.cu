@@ -236,10 +236,11 @@ __global__ void f32_to_f16_kernel(__half* out, __half* lo, const float* in, size
     for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < n; i += size_t(gridDim.x) * blockDim.x) store_split(out, lo, i, in[i]);
 }
 
-__global__ void step_advance_kernel(int32_t* seq_len, int batch, int32_t* step) {
+__global__ void step_advance_kernel(int32_t* seq_len, int batch, int32_t* step, uint32_t* extra_counter) {
     int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < batch) seq_len[i] += 1;
     if (i == 0 && step) *step += 1;
+    if (i == 0 && extra_counter) *extra_counter += 1;
 }
 
 __global__ void gather_rows_kernel(float* out, const __half* pool, const int32_t* page_row, int len, int kvd) {
@@ -336,8 +337,8 @@ int32_t f32_to_f16(__half* out, __half* lo, const float* in, size_t n, cudaStrea
     FORGE_LAUNCH_CHECK();
     return FORGE_OK;
 }
-int32_t step_advance(int32_t* seq_len, int batch, int32_t* step, cudaStream_t st) {
-    step_advance_kernel<<<(batch + 127) / 128, 128, 0, st>>>(seq_len, batch, step);
+int32_t step_advance(int32_t* seq_len, int batch, int32_t* step, cudaStream_t st, uint32_t* extra_counter) {
+    step_advance_kernel<<<(batch + 127) / 128, 128, 0, st>>>(seq_len, batch, step, extra_counter);
     FORGE_LAUNCH_CHECK();
     return FORGE_OK;
 }

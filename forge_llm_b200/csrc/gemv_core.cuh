@@ -211,6 +211,36 @@ __device__ __forceinline__ FillStat stage_fill_global(uint2* xf, const float* ba
     return st;
 }
 
+// Fill for the tensor-parallel sum: x = base + the ranks' partial rows, which arrive as {value, step} pairs written by
+// peer GPUs (see GemvArgs::Tp).  A pair is valid once its step is `step`; the wait is bounded and reports through *err.
+// Rank order is fixed, so every rank forms the same bits.  The sum is written once (element group i by CTA
+// i % gridDim.x) to `writeback`.
+__device__ __forceinline__ FillStat stage_fill_pairs(uint2* xf, const float* base, const uint2* ll, int world, uint32_t step,
+                                                     float* writeback, int K, const float* norm_w, int* err) {
+    float* xraw = reinterpret_cast<float*>(xf);
+    FillStat st;
+    csync();  // the previous contents of the fragment area are no longer read
+    for (int e = threadIdx.x * 4; e < K; e += kCT * 4) {
+        float4 v = __ldcg(reinterpret_cast<const float4*>(base + e));
+        for (int r = 0; r < world; ++r) {
+            const uint2* src = ll + size_t(r) * K + e;
+            uint4 a, b;
+            bool ok = false;
+            for (uint32_t i = 0; i < (1u << 20) && !ok; ++i) {  // about a second
+                asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w) : "l"(src) : "memory");
+                asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(b.x), "=r"(b.y), "=r"(b.z), "=r"(b.w) : "l"(src + 2) : "memory");
+                ok = a.y == step && a.w == step && b.y == step && b.w == step;
+            }
+            if (!ok) atomicExch(err, 1);
+            v.x += __uint_as_float(a.x); v.y += __uint_as_float(a.z); v.z += __uint_as_float(b.x); v.w += __uint_as_float(b.z);
+        }
+        if (writeback && ((e >> 2) % int(gridDim.x)) == int(blockIdx.x)) *reinterpret_cast<float4*>(writeback + e) = v;
+        fill_note(st, v, norm_w, e);
+        *reinterpret_cast<float4*>(xraw + e) = v;
+    }
+    return st;
+}
+
 // Convert the filled row in place; returns 1/scale.
 template <int QUANT>
 __device__ __forceinline__ float stage_finish(uint2* xf, int4* xoff, Shared& sh, FillStat st, int K, const float* norm_w, float eps) {
@@ -327,7 +357,7 @@ __device__ __forceinline__ EpiPre epilogue_prefetch(const Phase& ph, int b, int 
             if (row < ph.N) e.resid[j] = __ldcg(a.resid + size_t(b) * ph.N + row);
         }
     } else if (TP && ph.epi == EPI_TP_PUSH) {
-        e.pos = int(__ldcg(a.tp.seq)) + 1;  // the step this kernel publishes
+        e.pos = int(__ldcg(a.tp.step_counter) * a.tp.step_mul + a.tp.step_add);  // the step this kernel publishes
     } else if (ph.epi == EPI_QKV && (row0 & 1) == 0) {
         e.pos = pos_hint >= 0 ? pos_hint : a.seq_len[b];
         e.page = a.page_table[size_t(b) * a.pages_per_seq + e.pos / FORGE_KV_PAGE];
@@ -354,8 +384,9 @@ __device__ __forceinline__ void epilogue_row(const Phase& ph, int b, int row, fl
     } else if (ph.epi == EPI_RESID) {
         a.out[size_t(b) * ph.N + row] = pre.resid[j] + v;
     } else if (TP && ph.epi == EPI_TP_PUSH) {
-        const size_t off = (size_t(pre.pos & 1) * a.tp.world + a.tp.rank) * ph.N + row;
-        for (int r = 0; r < a.tp.world; ++r) a.tp.peer_parts[r][off] = v;
+        const size_t off = (size_t(a.tp.slot) * a.tp.world + a.tp.rank) * ph.N + row;
+        const uint2 pair = make_uint2(__float_as_uint(v), uint32_t(pre.pos));
+        for (int r = 0; r < a.tp.world; ++r) a.tp.peer_ll[r][off] = pair;  // one 8-byte store: value and step together
     } else if (ph.epi == EPI_SILU) {
         if ((row & 1) == 0)  // rows interleaved at pack time: 2j = gate_j, 2j+1 = up_j
             a.out[size_t(b) * (ph.N / 2) + (row >> 1)] = (v / (1.0f + expf(-v))) * partner;

@@ -80,20 +80,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tc_kernel(TcParams p) {
         if (TP && ph.a.tp.consume) {
             // the input is a sum over the tensor-parallel ranks that arrives through peer stores (see GemvArgs::Tp)
             const GemvArgs::Tp& tp = ph.a.tp;
-            const uint32_t step = __ldcg(tp.seq);
-            const int slot = int(step & 1u);
-            if (tid < tp.world) {
-                const uint32_t* f = tp.flags + slot * tp.world + tid;
-                uint32_t seen = 0;
-                for (uint32_t i = 0; i < (1u << 21); ++i) {  // about a second
-                    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(f) : "memory");
-                    if (seen == step) break;
-                }
-                if (seen != step) atomicExch(&sh.err, 1);
-            }
-            csync();
-            const FillStat st = stage_fill_global<true>(xf, ph.a.x, tp.parts + size_t(slot) * tp.world * ph.K, tp.world, size_t(ph.K),
-                                                       tp.x_writeback, ph.K, ph.a.norm_w);
+            const uint32_t step = __ldcg(tp.step_counter) * tp.step_mul + tp.step_add;
+            const FillStat st = stage_fill_pairs(xf, ph.a.x, tp.ll + size_t(tp.slot) * tp.world * ph.K, tp.world, step, tp.x_writeback,
+                                                 ph.K, ph.a.norm_w, &sh.err);
             unscale = stage_finish<QUANT>(xf, s_xoff, sh, st, ph.K, ph.a.norm_w, ph.a.eps);
         } else {
             unscale = stage_activation<QUANT, false>(xf, s_xoff, sh, ph.a.x + size_t(b) * ph.K, ph.K, ph.a.norm_w, ph.a.eps);
@@ -102,21 +91,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tc_kernel(TcParams p) {
         consume_phase<QUANT, decltype(no_hook), TP>(ph, sh, ring, xf, s_xoff, unscale, b, cc, no_hook, pos);
     }
     csync();
-    if (TP && ph.epi == EPI_TP_PUSH && tid == 0) {
-        // this CTA's partial rows are on their way to the peers; the last CTA to get here publishes the step
-        const GemvArgs::Tp& tp = ph.a.tp;
-        __threadfence_system();
-        if (atomicAdd(tp.done, 1) == int(gridDim.x) - 1) {
-            *tp.done = 0;
-            __threadfence_system();
-            const uint32_t step = __ldcg(tp.seq) + 1;
-            for (int r = 0; r < tp.world; ++r) {
-                uint32_t* f = tp.peer_flags[r] + (step & 1u) * tp.world + tp.rank;
-                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(step) : "memory");
-            }
-            *tp.seq = step;
-        }
-    }
     if (tid == 0 && sh.err && p.err) atomicExch(p.err, 1);
 }
 

@@ -71,7 +71,7 @@ struct ForgeModel {
     TpComm* tp = nullptr;  // tensor-parallel communicator (cfg.tp_world > 1)
     // peer-memory exchange of the decode step (forge_model_tp_exchange_*): local buffer, peers' mappings, device tables
     void* tpx_local = nullptr; std::vector<void*> tpx_peer; bool tpx_ready = false;
-    float** d_tpx_parts = nullptr; uint32_t** d_tpx_flags = nullptr; uint32_t* d_tpx_seq = nullptr; int* d_tpx_done = nullptr;
+    uint2** d_tpx_ll = nullptr; uint32_t* d_tpx_step = nullptr;  // peers' buffers (device table), decode step counter
     float* p_part = nullptr; float* d_part = nullptr;  // this rank's partial sums of a row-sliced projection
     bool use_mega = false; // batch-1 decode through the whole-step kernel (forge_model_set_decode_mode)
     // decode scratch (per batch row)
@@ -270,10 +270,8 @@ int32_t prefill_seq(ForgeModel* m, ForgeKV* kv, int seq, const uint32_t* tokens_
     return FORGE_OK;
 }
 
-// exchange buffer layout: flags[2][world] (padded to 256 bytes), then parts[2][world][h]
-inline const uint32_t* tpx_flags(const ForgeModel* m) { return static_cast<const uint32_t*>(m->tpx_local); }
-inline const float* tpx_parts(const ForgeModel* m) { return reinterpret_cast<const float*>(static_cast<const char*>(m->tpx_local) + 256); }
-inline size_t tpx_bytes(const ForgeModel* m) { return 256 + sizeof(float) * 2 * size_t(m->cfg.tp_world) * m->h; }
+// exchange buffer: ll[2 slots][world][h] of {value, step} pairs
+inline size_t tpx_bytes(const ForgeModel* m) { return sizeof(uint2) * 2 * size_t(m->cfg.tp_world) * m->h; }
 
 // ------------------------------------------------------------------ one decode step (launch sequence)
 // forward(), emit.rs:4029-4500, for `batch` sequences.  Tokens are read from m->d_tok, positions
@@ -287,18 +285,23 @@ int32_t decode_launches(ForgeModel* m, ForgeKV* kv, int batch, bool greedy, bool
     float* hid[2] = {m->d_hidden, m->d_hidden2};
     int cur = 0;
     bool pending = false;  // a pushed sum has not been consumed yet
+    int sums = 0;          // sums issued in this step so far (numbers them; slot = parity)
+    auto tp_common = [&](GemvArgs& a, int index) {
+        a.tp.world = c.tp_world; a.tp.rank = c.tp_rank; a.tp.slot = index & 1;
+        a.tp.step_counter = m->d_tpx_step; a.tp.step_mul = uint32_t(2 * c.num_layers + 1); a.tp.step_add = uint32_t(index + 1);
+    };
     auto tp_consume = [&](GemvArgs& a) {   // a.x is the residual stream: take the pending sum in while staging
         if (!pending) return;
-        a.tp.world = c.tp_world; a.tp.rank = c.tp_rank; a.tp.consume = 1;
-        a.tp.parts = tpx_parts(m); a.tp.flags = tpx_flags(m); a.tp.seq = m->d_tpx_seq;
+        tp_common(a, sums - 1);
+        a.tp.consume = 1; a.tp.ll = static_cast<const uint2*>(m->tpx_local);
         a.tp.x_writeback = hid[cur ^ 1];
         cur ^= 1;
         pending = false;
     };
     auto tp_push = [&](const QTiled& w, GemvArgs a) -> int32_t {
         a.out = nullptr; a.resid = nullptr;
-        a.tp.world = c.tp_world; a.tp.rank = c.tp_rank; a.tp.consume = 0;
-        a.tp.peer_parts = m->d_tpx_parts; a.tp.peer_flags = m->d_tpx_flags; a.tp.seq = m->d_tpx_seq; a.tp.done = m->d_tpx_done;
+        tp_common(a, sums++);
+        a.tp.consume = 0; a.tp.peer_ll = m->d_tpx_ll;
         pending = true;
         return gemv_tc(w, EPI_TP_PUSH, a, m->split, m->d_err, st);
     };
@@ -342,7 +345,7 @@ int32_t decode_launches(ForgeModel* m, ForgeKV* kv, int batch, bool greedy, bool
     if (px) tp_consume(lm);
     FORGE_TRY(gemv_tc(m->lm_head_t, EPI_STORE, lm, m->split, m->d_err, st));
     if (greedy) FORGE_TRY(argmax_slices(m->d_tok, m->d_logits, m->V, batch, m->d_amax_val, m->d_amax_idx, m->d_amax_ticket, st));
-    FORGE_TRY(step_advance(kv->d_seq_len, batch, m->d_step, st));
+    FORGE_TRY(step_advance(kv->d_seq_len, batch, m->d_step, st, px ? m->d_tpx_step : nullptr));
     return FORGE_OK;
 }
 
@@ -583,8 +586,7 @@ int32_t forge_model_tp_exchange_attach(ForgeModel* m, const uint8_t* handles) {
     FORGE_CUDA(cudaSetDevice(m->device));
     const int world = m->cfg.tp_world, rank = m->cfg.tp_rank;
     m->tpx_peer.assign(world, nullptr);
-    std::vector<float*> parts(world);
-    std::vector<uint32_t*> flags(world);
+    std::vector<uint2*> ll(world);
     for (int r = 0; r < world; ++r) {
         void* base = m->tpx_local;
         if (r != rank) {
@@ -594,17 +596,12 @@ int32_t forge_model_tp_exchange_attach(ForgeModel* m, const uint8_t* handles) {
             if (e != cudaSuccess) { set_error("cudaIpcOpenMemHandle(rank %d): %s", r, cudaGetErrorString(e)); return FORGE_ERR_COMM; }
             m->tpx_peer[r] = base;
         }
-        flags[r] = static_cast<uint32_t*>(base);
-        parts[r] = reinterpret_cast<float*>(static_cast<char*>(base) + 256);
+        ll[r] = static_cast<uint2*>(base);
     }
-    FORGE_TRY(dev_alloc(m, &m->d_tpx_parts, size_t(world)));
-    FORGE_TRY(dev_alloc(m, &m->d_tpx_flags, size_t(world)));
-    FORGE_TRY(dev_alloc(m, &m->d_tpx_seq, 1));
-    FORGE_TRY(dev_alloc(m, &m->d_tpx_done, 1));
-    FORGE_CUDA(cudaMemcpy(m->d_tpx_parts, parts.data(), sizeof(float*) * world, cudaMemcpyHostToDevice));
-    FORGE_CUDA(cudaMemcpy(m->d_tpx_flags, flags.data(), sizeof(uint32_t*) * world, cudaMemcpyHostToDevice));
-    FORGE_CUDA(cudaMemset(m->d_tpx_seq, 0, sizeof(uint32_t)));
-    FORGE_CUDA(cudaMemset(m->d_tpx_done, 0, sizeof(int)));
+    FORGE_TRY(dev_alloc(m, &m->d_tpx_ll, size_t(world)));
+    FORGE_TRY(dev_alloc(m, &m->d_tpx_step, 1));
+    FORGE_CUDA(cudaMemcpy(m->d_tpx_ll, ll.data(), sizeof(uint2*) * world, cudaMemcpyHostToDevice));
+    FORGE_CUDA(cudaMemset(m->d_tpx_step, 0, sizeof(uint32_t)));
     FORGE_CUDA(cudaDeviceSynchronize());
     m->tpx_ready = true;
     return FORGE_OK;
