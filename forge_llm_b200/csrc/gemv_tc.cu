@@ -3,12 +3,11 @@
 // patterns as prologue/epilogue: RMSNorm :327-334, residual :455-459, bias + RoPE + cache write
 // :4108-4153, silu_mul :381-386).
 //
-// HBM-bound by design: one persistent CTA per SM pulls its share of the weight stream with 1-D
-// bulk copies (cp.async.bulk, completion on an mbarrier) into a ring of shared-memory stages, so
-// the bytes in flight (~140 KB per SM) do not depend on the instruction stream.  Each of the
-// eight consumer warps owns one 16-row tile of a 128-row band and turns every 16-row x
-// 32-column tile (one quantisation block per row) into ONE integer tensor-core product,
-// mma.sync m16n8k32 s8 x s8 -> s32:
+// One persistent CTA per SM pulls its share of the weight stream with 1-D bulk copies (cp.async.bulk,
+// completion on an mbarrier) into a ring of shared-memory stages, so the bytes in flight (~140 KB per
+// SM) do not depend on the instruction stream.  Sixteen consumer warps turn every 16-row x 32-column
+// tile (one quantisation block per row) into ONE integer tensor-core product, mma.sync m16n8k32
+// s8/u8 x s8 -> s32:
 //   A = the quantised weights as they are (Q8_0 bytes; Q4_0 nibbles split into bytes),
 //   B = the f32 activation in fixed point, x * 2^s rounded to a 31-bit integer whose four balanced
 //       base-256 digits (the bytes of x + 0x80808080, each minus 128) fill one B column each,
@@ -16,11 +15,22 @@
 // multiplied by the row's f16 block scale and accumulated in f32, and the four digit
 // accumulators are combined once per row.  The result is the reference's f32 arithmetic up to
 // summation order (the activation keeps 2^-30 of its largest magnitude; it is never quantised
-// to 8 bits).  Warps never synchronise with each other after the activation is staged.
+// to 8 bits).
 //
-// Small matrices are split along K over several CTAs ("slices"); every slice writes its 16
-// partial sums per row tile to scratch, and the warp that completes a row tile (atomic ticket)
-// adds the slices in fixed order and runs the epilogue, so results do not depend on timing.
+// Units of work: a "wide" band is 128 rows (8 row tiles, two warps per tile taking the even / odd
+// k-blocks, no CTA-level reduction); a "narrow" band is one row tile shared by all sixteen warps
+// (16-row units for matrices too small to fill the SMs with 128-row bands; the warps' sums meet in
+// shared memory and the finishing duty rotates over the warps).  Small matrices are also split along
+// K over several CTAs ("slices"): every slice writes its partial sums to scratch and the warp that
+// completes a row tile (atomic ticket) adds the slices in fixed order and runs the epilogue, so
+// results do not depend on timing.
+//
+// Latency: a batch-1 decode step is a chain of short dependent kernels, so the kernel is launched
+// with programmatic dependent launch (barrier set-up and the weight stream start under the previous
+// kernel's tail, griddepcontrol.wait precedes the first dependent read), asks L2 for the next
+// kernel's weights, and fetches its epilogue operands under the tile loop.  All decode GEMVs share
+// this one kernel on purpose: its code stays in the instruction caches from launch to launch
+// (specialising it per epilogue made the step 3 % slower, merging rarely used code into it 1-3 %).
 //
 // Weight layout ("tiled"): 16-row x 32-column tiles; a tile is {8 x half2 (d[row g], d[row g+8])}
 // {quant bytes in A-fragment order, 16 (Q8_0) or 8 (Q4_0) bytes per lane} = 544 or 288 bytes:
