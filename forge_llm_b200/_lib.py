@@ -55,6 +55,16 @@ SIGNATURES = {
     "forge_argmax": (i32, [vp, vp, i32, vp]),
     "forge_quantize_q8_0_host": (i32, [vp, sz, vp]),
     "forge_quantize_q4_0_host": (i32, [vp, sz, vp, i32]),
+    "forge_gguf_open": (i32, [vp, sz, C.POINTER(vp)]),
+    "forge_gguf_close": (None, [vp]),
+    "forge_gguf_version": (i32, [vp]),
+    "forge_gguf_tensor_count": (C.c_int64, [vp]),
+    "forge_gguf_data_offset": (C.c_uint64, [vp]),
+    "forge_gguf_tensor_info": (i32, [vp, C.c_int64, C.POINTER(C.c_char_p), C.POINTER(i32), C.POINTER(i32), C.POINTER(C.c_uint64),
+                                    C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
+    "forge_gguf_model_config": (i32, [vp, C.POINTER(ForgeModelConfig)]),
+    "forge_gguf_weights_bin_size": (sz, [vp]),
+    "forge_gguf_export_weights_bin": (i32, [vp, vp, sz]),
     "forge_weights_bin_size": (sz, [C.POINTER(ForgeModelConfig)]),
     "forge_model_create": (i32, [C.POINTER(ForgeModelConfig), vp, sz, i32, C.POINTER(vp)]),
     "forge_model_destroy": (None, [vp]),

@@ -252,6 +252,34 @@ int32_t forge_hidden_trace_read(ForgeModel* model, float* out_host, size_t capac
  * number of kernels of this library launched by that call. */
 int32_t forge_last_timing(ForgeModel* model, float* prefill_ms, float* decode_ms, int64_t* launches);
 
+/* ------------------------------------------------------------------------------------
+ * GGUF input (host only): the reference's `export-weights` step, so a GGUF checkpoint can feed
+ * forge_model_create directly.  Parser: crates/forgellm-frontend/src/gguf.rs:484-551 (v2 / v3,
+ * little endian); configuration rules: crates/forgellm-cli/src/main.rs:689-811 (head_dim =
+ * hidden / heads, defaults, Qwen2 has QKV bias) and the dtype vote :479-560; tensor names:
+ * crates/forgellm-frontend/src/weight_loader.rs:400-441; write order: main.rs:2506-2757.
+ * Supported: llama / qwen2 / mistral (no sliding window) whose projections are Q8_0 or Q4_0;
+ * embedding and norms F32 / F16 / BF16 (or a Q8_0 embedding); dense or Q8_0 projections in a
+ * Q4_0 model are re-quantised with the reference's rule; a missing output.weight ties the head
+ * to the embedding.  Anything else returns FORGE_ERR_UNSUPPORTED; a malformed or truncated
+ * file returns FORGE_ERR_SHAPE.  `data` must stay mapped while the handle lives.
+ * ------------------------------------------------------------------------------------ */
+typedef struct ForgeGguf ForgeGguf;
+int32_t forge_gguf_open(const void* data, size_t len, ForgeGguf** out);
+void forge_gguf_close(ForgeGguf* gguf);
+int32_t forge_gguf_version(const ForgeGguf* gguf);
+int64_t forge_gguf_tensor_count(const ForgeGguf* gguf);
+/* Byte offset of the tensor data section (aligned to general.alignment, default 32). */
+uint64_t forge_gguf_data_offset(const ForgeGguf* gguf);
+/* Descriptor `index`: dims[4] (innermost first, unused = 0), offset from the data section,
+ * size in bytes.  Any output pointer may be null. */
+int32_t forge_gguf_tensor_info(const ForgeGguf* gguf, int64_t index, const char** name, int32_t* ggml_type,
+                               int32_t* n_dims, uint64_t* dims, uint64_t* offset, uint64_t* data_size);
+int32_t forge_gguf_model_config(const ForgeGguf* gguf, ForgeModelConfig* cfg);
+/* Size of the weights.bin image (0 on error, see forge_last_error) and the image itself. */
+size_t forge_gguf_weights_bin_size(const ForgeGguf* gguf);
+int32_t forge_gguf_export_weights_bin(const ForgeGguf* gguf, void* out, size_t capacity);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,182 @@
+"""GGUF reader and weights.bin exporter (host code of the library; no GPU needed).
+
+The parser cases restate the reference's own parser tests (crates/forgellm-frontend/src/gguf.rs:562-700: minimal v3,
+several tensors with metadata, v2, bad magic, unsupported version).  The export cases write a synthetic GGUF from the
+same seeded tensors `synth.make_weights_bin` uses and require the exported image to equal it byte for byte."""
+import os
+import struct
+import sys
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+from forge_llm_b200 import configs, gguf, synth  # noqa: E402
+from forge_llm_b200._lib import ForgeError  # noqa: E402
+
+MAGIC = 0x46554747
+F32, F16, Q4_0, Q8_0, BF16 = 0, 1, 2, 8, 30
+
+
+def _s(text: str) -> bytes:
+    b = text.encode()
+    return struct.pack("<Q", len(b)) + b
+
+
+def build_gguf(version, metadata, tensors, alignment=32, data=b""):
+    """metadata: [(key, type_id, raw value bytes)]; tensors: [(name, dims, ggml_type, offset)]; data: tensor section."""
+    out = struct.pack("<IIQQ", MAGIC, version, len(tensors), len(metadata))
+    for key, tid, raw in metadata:
+        out += _s(key) + struct.pack("<I", tid) + raw
+    for name, dims, typ, off in tensors:
+        out += _s(name) + struct.pack("<I", len(dims)) + b"".join(struct.pack("<Q", d) for d in dims) + struct.pack("<IQ", typ, off)
+    pad = (-len(out)) % alignment
+    return out + b"\0" * pad + data
+
+
+def u32(v): return struct.pack("<I", v)
+def f32(v): return struct.pack("<f", v)
+
+
+def test_parse_minimal_v3():
+    g = gguf.GgufFile(build_gguf(3, [("general.architecture", 8, _s("llama"))], [("token_embd.weight", [32000, 2048], F16, 0)]))
+    assert g.version == 3
+    t = g.tensors()
+    assert len(t) == 1 and t[0]["name"] == "token_embd.weight" and t[0]["dims"] == [32000, 2048] and t[0]["type"] == F16
+    assert t[0]["size"] == 32000 * 2048 * 2
+
+
+def test_parse_several_tensors_and_block_sizes():
+    g = gguf.GgufFile(build_gguf(3, [("general.architecture", 8, _s("llama")), ("llama.embedding_length", 4, u32(2048)),
+                                     ("llama.attention.layer_norm_rms_epsilon", 6, f32(1e-5))],
+                                 [("token_embd.weight", [32000, 2048], F16, 0), ("blk.0.attn_q.weight", [2048, 2048], Q8_0, 4096),
+                                  ("blk.0.ffn_gate.weight", [5632, 2048], Q4_0, 8192)]))
+    t = {x["name"]: x for x in g.tensors()}
+    assert t["blk.0.attn_q.weight"]["size"] == 2048 * 2048 // 32 * 34   # 34 bytes per 32 weights
+    assert t["blk.0.ffn_gate.weight"]["size"] == 5632 * 2048 // 32 * 18  # 18 bytes per 32 weights
+    assert t["blk.0.attn_q.weight"]["offset"] == 4096
+
+
+def test_parse_v2_and_alignment():
+    g = gguf.GgufFile(build_gguf(2, [], []))
+    assert g.version == 2 and g.tensors() == []
+    raw = build_gguf(3, [("general.alignment", 4, u32(64))], [("a", [4], F32, 0)], alignment=64, data=b"\0" * 16)
+    g = gguf.GgufFile(raw)
+    assert g.data_offset % 64 == 0 and g.data_offset == len(raw) - 16
+    # every metadata value type, arrays of scalars and of strings included, is skipped correctly
+    arr = struct.pack("<IQ", 4, 3) + struct.pack("<III", 1, 2, 3)
+    sarr = struct.pack("<IQ", 8, 2) + _s("a") + _s("bc")
+    meta = [("k0", 0, b"\1"), ("k1", 1, b"\xff"), ("k2", 2, b"\1\0"), ("k3", 3, b"\1\0"), ("k5", 5, u32(7)), ("k7", 7, b"\1"),
+            ("k9", 9, arr), ("k9s", 9, sarr), ("k10", 10, struct.pack("<Q", 9)), ("k11", 11, struct.pack("<q", -9)),
+            ("k12", 12, struct.pack("<d", 0.5))]
+    assert gguf.GgufFile(build_gguf(3, meta, [("a", [4], F32, 0)], data=b"\0" * 16)).tensors()[0]["name"] == "a"
+
+
+def test_rejects_bad_files():
+    with pytest.raises(ForgeError):
+        gguf.GgufFile(struct.pack("<I", 0xDEADBEEF) + b"\0" * 28)           # bad magic
+    with pytest.raises(ForgeError):
+        gguf.GgufFile(struct.pack("<IIQQ", MAGIC, 99, 0, 0))                # unsupported version
+    with pytest.raises(ForgeError):
+        gguf.GgufFile(build_gguf(3, [], [("t", [1, 1, 1, 1, 1], F32, 0)]))   # five dimensions
+    good = build_gguf(3, [("general.architecture", 8, _s("llama"))], [("token_embd.weight", [8, 8], F16, 0)])
+    for cut in (3, 11, 30, len(good) - 40):
+        with pytest.raises(ForgeError):
+            gguf.GgufFile(good[:cut]).tensors()                              # truncated header / tables
+
+
+def synthetic_gguf(c: dict, tied: bool, embed_type: int = F32, arch: str = "llama"):
+    """A GGUF file holding exactly the tensors of synth.make_weights_bin(c), under GGUF names."""
+    blob = synth.make_weights_bin(c)
+    h, qk, kv = c["hidden_size"], c["num_heads"] * c["head_dim"], c["num_kv_heads"] * c["head_dim"]
+    ff, V, q = c["intermediate_size"], c["vocab_size"], c["quant"]
+    bs = 34 if q == 8 else 18
+    qt = Q8_0 if q == 8 else Q4_0
+    off = 0
+
+    def take(n):
+        nonlocal off
+        b = blob[off:off + n].tobytes()
+        off += n
+        return b
+
+    tensors = []
+    embed = np.frombuffer(take(V * h * 4), np.float32)
+    if embed_type == F16:
+        tensors.append(("token_embd.weight", [h, V], F16, embed.astype(np.float16).tobytes()))
+    else:
+        tensors.append(("token_embd.weight", [h, V], F32, embed.tobytes()))
+    for l in range(c["num_layers"]):
+        p = f"blk.{l}."
+        tensors.append((p + "attn_norm.weight", [h], F32, take(h * 4)))
+        tensors.append((p + "attn_q.weight", [h, qk], qt, take(qk * h // 32 * bs)))
+        tensors.append((p + "attn_k.weight", [h, kv], qt, take(kv * h // 32 * bs)))
+        tensors.append((p + "attn_v.weight", [h, kv], qt, take(kv * h // 32 * bs)))
+        if c.get("qkv_bias"):
+            tensors.append((p + "attn_q.bias", [qk], F32, take(qk * 4)))
+            tensors.append((p + "attn_k.bias", [kv], F32, take(kv * 4)))
+            tensors.append((p + "attn_v.bias", [kv], F32, take(kv * 4)))
+        tensors.append((p + "attn_output.weight", [qk, h], qt, take(h * qk // 32 * bs)))
+        tensors.append((p + "ffn_norm.weight", [h], F32, take(h * 4)))
+        tensors.append((p + "ffn_gate.weight", [h, ff], qt, take(ff * h // 32 * bs)))
+        tensors.append((p + "ffn_up.weight", [h, ff], qt, take(ff * h // 32 * bs)))
+        tensors.append((p + "ffn_down.weight", [ff, h], qt, take(h * ff // 32 * bs)))
+    tensors.append(("output_norm.weight", [h], F32, take(h * 4)))
+    head = take(V * h // 32 * bs)
+    assert off == blob.size
+    if not tied:
+        tensors.append(("output.weight", [h, V], qt, head))
+    data, table = b"", []
+    for name, dims, typ, raw in tensors[::-1]:  # file order differs from export order on purpose
+        data += b"\0" * ((-len(data)) % 32)
+        table.append((name, dims, typ, len(data)))
+        data += raw
+    meta = [("general.architecture", 8, _s(arch)), (f"{arch}.embedding_length", 4, u32(h)), (f"{arch}.block_count", 4, u32(c["num_layers"])),
+            (f"{arch}.attention.head_count", 4, u32(c["num_heads"])), (f"{arch}.attention.head_count_kv", 4, u32(c["num_kv_heads"])),
+            (f"{arch}.feed_forward_length", 4, u32(ff)), (f"{arch}.vocab_size", 4, u32(V)), (f"{arch}.context_length", 4, u32(c["max_seq_len"])),
+            (f"{arch}.attention.layer_norm_rms_epsilon", 6, f32(c["rms_norm_eps"])), (f"{arch}.rope.freq_base", 6, f32(c["rope_theta"]))]
+    return build_gguf(3, meta, table, data=data), blob, embed
+
+
+@pytest.mark.parametrize("quant,bias", [(8, 0), (4, 0), (4, 1)])
+def test_export_equals_the_reference_order_image(quant, bias):
+    c = configs.tiny(quant, hd=64, nq=4, nkv=2, bias=bias, layers=2)
+    raw, blob, _ = synthetic_gguf(c, tied=False, arch="qwen2" if bias else "llama")
+    g = gguf.GgufFile(raw)
+    got = g.config()
+    for k in ("hidden_size", "intermediate_size", "num_layers", "num_heads", "num_kv_heads", "head_dim", "vocab_size", "max_seq_len", "quant", "qkv_bias"):
+        assert got[k] == c[k] if k != "qkv_bias" else got[k] == bias, k
+    assert abs(got["rms_norm_eps"] - c["rms_norm_eps"]) < 1e-12 and got["rope_theta"] == c["rope_theta"]
+    assert np.array_equal(g.weights_bin(), blob)
+
+
+@pytest.mark.parametrize("quant", [8, 4])
+def test_tied_head_and_f16_embedding(quant, oracle):
+    c = configs.tiny(quant, hd=64, nq=4, nkv=2, layers=1)
+    raw, blob, embed = synthetic_gguf(c, tied=True, embed_type=F16)
+    out = gguf.GgufFile(raw).weights_bin()
+    V, h = c["vocab_size"], c["hidden_size"]
+    e16 = embed.astype(np.float16).astype(np.float32)
+    assert np.array_equal(out[:V * h * 4].view(np.float32), e16)             # embedding widened from f16
+    head_bytes = V * h // 32 * (34 if quant == 8 else 18)
+    assert np.array_equal(out[V * h * 4:-head_bytes], blob[V * h * 4:-head_bytes])  # everything between is verbatim
+    # head = the embedding re-quantised with the exporter's own rules (the CPU restatement's quantisers)
+    want = oracle.quantize_q8_0(e16) if quant == 8 else oracle.quantize_q4_0(e16, rule="ref")
+    assert np.array_equal(out[-head_bytes:], np.asarray(want).reshape(-1).view(np.uint8))
+
+
+def test_defaults_and_unsupported():
+    # missing optional keys take the reference's defaults: kv heads = heads, ffn = 4 * hidden, eps 1e-5, theta 1e4, ctx 2048
+    meta = [("general.architecture", 8, _s("llama")), ("llama.embedding_length", 4, u32(256)), ("llama.block_count", 4, u32(1)),
+            ("llama.attention.head_count", 4, u32(4)), ("tokenizer.ggml.tokens", 9, struct.pack("<IQ", 8, 3) + _s("a") + _s("b") + _s("c"))]
+    g = gguf.GgufFile(build_gguf(3, meta, [("blk.0.attn_q.weight", [256, 256], Q8_0, 0)], data=b"\0" * (256 * 256 // 32 * 34)))
+    c = g.config()
+    assert (c["num_kv_heads"], c["intermediate_size"], c["vocab_size"], c["max_seq_len"], c["head_dim"]) == (4, 1024, 3, 2048, 64)
+    assert abs(c["rms_norm_eps"] - 1e-5) < 1e-12 and c["rope_theta"] == 10000.0 and c["quant"] == 8
+    with pytest.raises(ForgeError):
+        g.weights_bin()  # tensors are missing
+    meta[0] = ("general.architecture", 8, _s("gemma"))
+    with pytest.raises(ForgeError):
+        gguf.GgufFile(build_gguf(3, meta, [("blk.0.attn_q.weight", [256, 256], Q8_0, 0)], data=b"\0" * 69632)).config()

@@ -282,3 +282,24 @@ def test_page_and_tile_boundaries(oracle, quant):
         assert kv.len() == n + 3
         kv.close()
     gm.close()
+
+
+@pytest.mark.gpu
+def test_model_from_gguf_file(oracle):
+    """A synthetic GGUF (tied head, f16 embedding) through the library's reader, then the usual parity gate."""
+    from test_gguf_cpu import synthetic_gguf, F16
+    from forge_llm_b200 import configs, gguf, runtime, synth
+    c = configs.tiny(4, hd=64, nq=4, nkv=2, layers=2)
+    raw, _, _ = synthetic_gguf(c, tied=True, embed_type=F16)
+    g = gguf.GgufFile(raw)
+    cfg, blob = g.config(), g.weights_bin()
+    toks = synth.prompt_tokens(c, 50)
+    gm = runtime.Model(cfg, blob)
+    kv = gm.new_cache(max_seq=80)
+    om = oracle.OracleModel(cfg, blob, kv_mode=oracle.KV_F16)
+    assert np.abs(gm.forward_prefill(toks, kv) - om.forward_prefill(toks)).max() < LOGIT_TOL
+    kv.reset()
+    om.reset()
+    assert np.array_equal(gm.generate_greedy(toks, 16, kv), om.generate_greedy(toks, 16)[0])
+    kv.close()
+    gm.close()
