@@ -19,7 +19,7 @@ class ForgeModelConfig(C.Structure):
         ("num_heads", C.c_int32), ("num_kv_heads", C.c_int32), ("head_dim", C.c_int32),
         ("vocab_size", C.c_int32), ("max_seq_len", C.c_int32),
         ("rms_norm_eps", C.c_float), ("rope_theta", C.c_float),
-        ("quant", C.c_int32), ("qkv_bias", C.c_int32), ("tp_rank", C.c_int32), ("tp_world", C.c_int32),
+        ("quant", C.c_int32), ("qkv_bias", C.c_int32), ("tp_rank", C.c_int32), ("tp_world", C.c_int32), ("sliding_window", C.c_int32),
     ]
 
 
@@ -53,6 +53,8 @@ SIGNATURES = {
     "forge_attention_flash_static": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, vp]),
     "forge_attention_flash_batch": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, i32, vp]),
     "forge_argmax": (i32, [vp, vp, i32, vp]),
+    "forge_attention_sliding": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, i32, vp]),
+    "forge_attention_sliding_batch": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp]),
     "forge_quantize_q8_0_host": (i32, [vp, sz, vp]),
     "forge_quantize_q4_0_host": (i32, [vp, sz, vp, i32]),
     "forge_gguf_open": (i32, [vp, sz, C.POINTER(vp)]),

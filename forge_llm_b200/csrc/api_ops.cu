@@ -208,6 +208,31 @@ int32_t forge_attention_flash_batch(float* out, const float* q_batch, const uint
     return attn_prefill_q32(a, q_batch, static_cast<cudaStream_t>(stream));
 }
 
+int32_t forge_attention_sliding(float* out, const float* q, const uint16_t* k_cache, const uint16_t* v_cache, int32_t seq_len,
+                                int32_t window, int32_t num_heads, int32_t num_kv_heads, int32_t head_dim, void* stream) {
+    FORGE_TRY(need_device());
+    if (!out || !q || !k_cache || !v_cache || seq_len <= 0 || window <= 0 || num_heads <= 0 || num_kv_heads <= 0) { set_error("bad argument to forge_attention_sliding"); return FORGE_ERR_INVALID_ARG; }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int splits = std::min(32, std::max(1, seq_len / 64));
+    AsyncBuf ws(st), cnt(st);
+    FORGE_CUDA(ws.alloc(sizeof(float) * attn_decode_ws_floats(1, num_heads, head_dim, splits)));
+    FORGE_CUDA(cnt.alloc(sizeof(int) * num_kv_heads));
+    FORGE_CUDA(cudaMemsetAsync(cnt.p, 0, sizeof(int) * num_kv_heads, st));
+    AttnDecodeArgs a{out, q, reinterpret_cast<const __half*>(k_cache), reinterpret_cast<const __half*>(v_cache), nullptr, 0, nullptr,
+                     seq_len, 1, num_heads, num_kv_heads, head_dim, seq_len, static_cast<float*>(ws.p), static_cast<int*>(cnt.p), splits, window};
+    return attn_decode(a, st);
+}
+
+int32_t forge_attention_sliding_batch(float* out, const float* q_batch, const uint16_t* k_cache, const uint16_t* v_cache, int32_t m,
+                                      int32_t base_pos, int32_t window, int32_t num_heads, int32_t num_kv_heads, int32_t head_dim,
+                                      void* stream) {
+    FORGE_TRY(need_device());
+    if (!out || !q_batch || !k_cache || !v_cache || m < 0 || base_pos < 0 || window <= 0 || num_heads <= 0 || num_kv_heads <= 0) { set_error("bad argument to forge_attention_sliding_batch"); return FORGE_ERR_INVALID_ARG; }
+    AttnPrefillArgs a{nullptr, nullptr, out, nullptr, reinterpret_cast<const __half*>(k_cache), reinterpret_cast<const __half*>(v_cache), nullptr,
+                      m, base_pos, num_heads, num_kv_heads, head_dim, window};
+    return attn_prefill_q32(a, q_batch, static_cast<cudaStream_t>(stream));
+}
+
 int32_t forge_argmax(uint32_t* result, const float* logits, int32_t n, void* stream) {
     FORGE_TRY(need_device());
     if (!result || !logits || n <= 0) { set_error("bad argument to forge_argmax"); return FORGE_ERR_INVALID_ARG; }

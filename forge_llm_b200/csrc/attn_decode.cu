@@ -56,6 +56,7 @@ __global__ void __launch_bounds__(kThreads) attn_decode_kernel(DecParams p) {
     const int page0 = (pt && split < a.pages_per_seq) ? pt[split] : split;
     const int n_ctx = a.seq_len ? a.seq_len[b] + 1 : a.seq_len_host;
     const int n_pages = (n_ctx + FORGE_KV_PAGE - 1) / FORGE_KV_PAGE;
+    const int t_first = (a.window > 0 && n_ctx > a.window) ? n_ctx - a.window : 0;  // sliding window: first position seen
     const size_t seq_base = a.page_table ? 0 : size_t(b) * a.max_ctx;  // contiguous: [batch][max_ctx][kvd]
     const int part = warp * RPW + seg;
 
@@ -76,6 +77,7 @@ __global__ void __launch_bounds__(kThreads) attn_decode_kernel(DecParams p) {
         }
         constexpr int UNR = 4;  // positions per segment whose K/V loads are issued before any use
         for (int lp = split; lp < n_pages; lp += a.splits) {
+            if ((lp + 1) * FORGE_KV_PAGE <= t_first) continue;  // the whole page lies before the window
             const int page = lp == split ? page0 : (pt ? pt[lp] : lp);
             const size_t page_row = seq_base + size_t(page) * FORGE_KV_PAGE;
             const int t_page = lp * FORGE_KV_PAGE;
@@ -86,7 +88,7 @@ __global__ void __launch_bounds__(kThreads) attn_decode_kernel(DecParams p) {
                     const int tp = base + u * PARTS + seg;
                     kr[u] = make_uint4(0, 0, 0, 0);
                     vr[u] = make_uint4(0, 0, 0, 0);
-                    if (tp < FORGE_KV_PAGE && t_page + tp < n_ctx && act) {
+                    if (tp < FORGE_KV_PAGE && t_page + tp < n_ctx && t_page + tp >= t_first && act) {
                         const size_t off = (page_row + tp) * kvd + kvh * HD + sl * 8;
                         kr[u] = __ldg(reinterpret_cast<const uint4*>(a.k_pool + off));
                         vr[u] = __ldg(reinterpret_cast<const uint4*>(a.v_pool + off));
@@ -116,7 +118,7 @@ __global__ void __launch_bounds__(kThreads) attn_decode_kernel(DecParams p) {
 #pragma unroll
                 for (int u = 0; u < UNR; ++u) {
                     const int tp = base + u * PARTS + seg;
-                    if (!(tp < FORGE_KV_PAGE && t_page + tp < n_ctx)) {
+                    if (!(tp < FORGE_KV_PAGE && t_page + tp < n_ctx && t_page + tp >= t_first)) {
 #pragma unroll
                         for (int g = 0; g < kGC; ++g) sc[u][g] = -INFINITY;
                     }

@@ -108,8 +108,11 @@ __global__ void __launch_bounds__(kThreads) attn_prefill_kernel(PrefillParams p)
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
     const float sl2 = p.scale * 1.4426950408889634f;  // scores in the base-2 domain
-    load_tile(0, 0);
-    for (int j = 0; j < ntiles; ++j) {
+    // sliding window: the first query of the tile sees keys from (its position - window + 1); earlier tiles are skipped
+    const int k_first = a.window > 0 ? max(a.base_pos + row0 - (a.window - 1), 0) : 0;
+    const int j0 = k_first / BN;
+    load_tile(j0, j0 & 1);
+    for (int j = j0; j < ntiles; ++j) {
         if (j + 1 < ntiles) {
             load_tile(j + 1, (j + 1) & 1);
             asm volatile("cp.async.wait_group 1;" ::: "memory");
@@ -135,7 +138,9 @@ __global__ void __launch_bounds__(kThreads) attn_prefill_kernel(PrefillParams p)
         }
         // scale, causal mask (only where the tile reaches past the row), online softmax in base 2
         // (rows g and g+8 of the warp's 16)
-        const bool diag = j * BN + BN - 1 > a.base_pos + row0 + warp * 16;  // some key of the tile may be masked for this warp
+        // some key of the tile may be masked for this warp: past a query's position, or before its window
+        const bool diag = j * BN + BN - 1 > a.base_pos + row0 + warp * 16 ||
+                          (a.window > 0 && j * BN < a.base_pos + row0 + warp * 16 + 15 - (a.window - 1));
 #pragma unroll
         for (int rr = 0; rr < 2; ++rr) {
             const int qpos = qpos0 + rr * 8;
@@ -145,7 +150,8 @@ __global__ void __launch_bounds__(kThreads) attn_prefill_kernel(PrefillParams p)
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
                     float v = s[nb][rr * 2 + e] * sl2;
-                    if (diag && j * BN + nb * 8 + 2 * t + e > qpos) v = -INFINITY;
+                    const int key = j * BN + nb * 8 + 2 * t + e;
+                    if (diag && (key > qpos || (a.window > 0 && key < qpos - (a.window - 1)))) v = -INFINITY;
                     s[nb][rr * 2 + e] = v;
                     mx = fmaxf(mx, v);
                 }

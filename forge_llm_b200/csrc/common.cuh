@@ -208,6 +208,7 @@ struct AttnDecodeArgs {
     int batch, nq, nkv, hd, max_ctx;
     float* ws; int* counters;                // split workspace
     int splits;
+    int window = 0;                          // > 0: only the last `window` positions are attended to
 };
 size_t attn_decode_ws_floats(int batch, int nq, int hd, int splits);
 int32_t attn_decode(const AttnDecodeArgs& a, cudaStream_t st);
@@ -218,6 +219,7 @@ struct AttnPrefillArgs {
     const __half* k_pool; const __half* v_pool;
     const int32_t* page_row;                 // device [pages] physical page of logical page i (null = contiguous)
     int m, base_pos, nq, nkv, hd;
+    int window = 0;                          // > 0: query position p sees keys [max(0, p - window + 1), p]
 };
 int32_t attn_prefill(const AttnPrefillArgs& a, cudaStream_t st);
 int32_t attn_prefill_q32(const AttnPrefillArgs& a, const float* q32, cudaStream_t st);  // f32 queries, converted on load

@@ -401,7 +401,7 @@ int32_t forge_gguf_model_config(const ForgeGguf* g, ForgeModelConfig* c) {
     g->get_u32(arch + ".attention.head_count", heads);
     if (!g->get_u32(arch + ".attention.head_count_kv", kv_heads)) kv_heads = heads;
     if (hidden == 0 || layers == 0 || heads == 0) { set_error("could not extract the model configuration from the GGUF metadata"); return FORGE_ERR_SHAPE; }
-    if (g->get_u32(arch + ".attention.sliding_window", window) && window > 0) { set_error("sliding-window attention is not supported"); return FORGE_ERR_UNSUPPORTED; }
+    g->get_u32(arch + ".attention.sliding_window", window);
     if (!g->get_u32(arch + ".feed_forward_length", ff)) ff = hidden * 4;
     const MetaValue* toks = g->get("tokenizer.ggml.tokens");
     if (toks && toks->type == 9) vocab = toks->count;
@@ -419,6 +419,7 @@ int32_t forge_gguf_model_config(const ForgeGguf* g, ForgeModelConfig* c) {
     c->rms_norm_eps = eps; c->rope_theta = theta;
     c->quant = quant; c->qkv_bias = arch == "qwen2" ? 1 : 0;
     c->tp_rank = 0; c->tp_world = 1;
+    c->sliding_window = int32_t(window);
     return FORGE_OK;
 }
 

@@ -252,7 +252,7 @@ int32_t prefill_seq(ForgeModel* m, ForgeKV* kv, int seq, const uint32_t* tokens_
         FORGE_TRY(rms_norm_f16(m->p_normed, nlo, m->p_hidden, L.attn_norm, n, m->h, c.rms_norm_eps, st));
         FORGE_TRY(gemm_f16a(m->p_qkv, m->p_normed, nlo, L.qkv, n, nullptr, m->d_err, st));
         FORGE_TRY(qkv_post(m->p_qkv, n, base, L.qkv_bias, m->rope, m->p_q16, kp, vp, page_row, m->qk, m->kv, m->hd, st));
-        AttnPrefillArgs pa{m->p_attn16, alo, nullptr, m->p_q16, kp, vp, page_row, n, base, m->nq, m->nkv, m->hd};
+        AttnPrefillArgs pa{m->p_attn16, alo, nullptr, m->p_q16, kp, vp, page_row, n, base, m->nq, m->nkv, m->hd, c.sliding_window};
         FORGE_TRY(attn_prefill(pa, st));
         FORGE_TRY(row_sliced_gemm(m, L.o, m->p_attn16, alo, n, st));
         FORGE_TRY(rms_norm_f16(m->p_normed, nlo, m->p_hidden, L.ffn_norm, n, m->h, c.rms_norm_eps, st));
@@ -319,7 +319,7 @@ int32_t decode_launches(ForgeModel* m, ForgeKV* kv, int batch, bool greedy, bool
         a.next_w = L.o_t.data; a.next_bytes = qtiled_bytes(L.o_t);
         FORGE_TRY(gemv_tc(L.qkv_t, EPI_QKV, a, m->split, m->d_err, st));
         AttnDecodeArgs da{m->d_attn, m->d_q, kp, vp, kv->d_page_table, kv->pages_per_seq, kv->d_seq_len, 0,
-                          batch, m->nq, m->nkv, m->hd, kv->max_seq, kv->attn_ws, kv->attn_counters, kv->splits};
+                          batch, m->nq, m->nkv, m->hd, kv->max_seq, kv->attn_ws, kv->attn_counters, kv->splits, c.sliding_window};
         FORGE_TRY(attn_decode(da, st));
         GemvArgs o;
         o.x = m->d_attn; o.out = hid[cur]; o.resid = hid[cur]; o.batch = batch;
@@ -373,7 +373,7 @@ int32_t decode_step_one_kernel(ForgeModel* m, ForgeKV* kv, bool greedy) {
 
 int32_t decode_step_graph(ForgeModel* m, ForgeKV* kv, int batch, bool greedy) {
     if (m->trace_on) return decode_launches(m, kv, batch, greedy, greedy);
-    if (batch == 1 && m->use_mega && m->cfg.tp_world == 1 && kv->d_phases && kv->mega_grid <= kArgmaxSlices && (m->nq / m->nkv) * m->hd <= 512) return decode_step_one_kernel(m, kv, greedy);
+    if (batch == 1 && m->use_mega && m->cfg.tp_world == 1 && m->cfg.sliding_window <= 0 && kv->d_phases && kv->mega_grid <= kArgmaxSlices && (m->nq / m->nkv) * m->hd <= 512) return decode_step_one_kernel(m, kv, greedy);
     if (!kv->graph || kv->graph_batch != batch || kv->graph_greedy != greedy) {
         if (kv->graph) { cudaGraphExecDestroy(kv->graph); kv->graph = nullptr; }
         cudaGraph_t g = nullptr;

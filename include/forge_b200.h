@@ -64,6 +64,8 @@ typedef struct ForgeModelConfig {
     int32_t qkv_bias; /* 1: f32 q,k,v biases follow v_proj in weights.bin (Qwen2, E:4108-4118) */
     int32_t tp_rank;  /* tensor-parallel rank / world size; 0 / 1 when not sharded */
     int32_t tp_world;
+    int32_t sliding_window; /* > 0: position p attends to [max(0, p - window + 1), p] (Mistral, E:601-626,
+                               E:916-1046); 0: full causal attention */
 } ForgeModelConfig;
 
 typedef struct ForgeModel ForgeModel;
@@ -146,6 +148,14 @@ int32_t forge_attention_flash_batch(float* out, const float* q_batch, const uint
 /* argmax of the generated main (P:501-503): on ties the LAST maximal index wins.
  * logits: device f32 [n]; result: device u32. */
 int32_t forge_argmax(uint32_t* result, const float* logits, int32_t n, void* stream);
+
+/* attention_sliding (E:601-626) and attention_sliding_batch (E:916-1046): the two calls above restricted to the last
+ * `window` positions: the query at position p sees the cache positions [max(0, p - window + 1), p]. */
+int32_t forge_attention_sliding(float* out, const float* q, const uint16_t* k_cache, const uint16_t* v_cache, int32_t seq_len,
+                                int32_t window, int32_t num_heads, int32_t num_kv_heads, int32_t head_dim, void* stream);
+int32_t forge_attention_sliding_batch(float* out, const float* q_batch, const uint16_t* k_cache, const uint16_t* v_cache, int32_t m,
+                                      int32_t base_pos, int32_t window, int32_t num_heads, int32_t num_kv_heads, int32_t head_dim,
+                                      void* stream);
 
 /* Host-side quantisers of the reference's exporter (quantize_f32_to_q8_0 WL:1454-1486;
  * Q4_0 packing WL:1494-1544 with `signed_max` = 0, or the signed-max scale rule

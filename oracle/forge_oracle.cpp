@@ -345,6 +345,31 @@ void attention_plain(float* out, const float* q, const KVView& c, int seq, int n
     }
 }
 
+// E:601-626 (attention_sliding): the plain two-pass attention over the last `window` positions only.
+void attention_sliding(float* out, const float* q, const KVView& c, int seq, int window, int nh, int nkv, int hd) {
+    int start = seq > window ? seq - window : 0, wl = seq - start;
+    int g = nh / nkv;
+    float scale = 1.0f / std::sqrt(float(hd));
+    size_t stride = size_t(nkv) * hd;
+    std::vector<float> sc(wl);
+    for (int h = 0; h < nh; ++h) {
+        int kvh = h / g;
+        const float* qh = q + size_t(h) * hd;
+        for (int si = 0; si < wl; ++si) { int t = start + si; sc[si] = k_dot(c, qh, t * stride + size_t(kvh) * hd, t, hd) * scale; }
+        float mx = -std::numeric_limits<float>::infinity();
+        for (int si = 0; si < wl; ++si) mx = std::max(mx, sc[si]);
+        float sum = 0.0f;
+        for (int si = 0; si < wl; ++si) { sc[si] = std::exp(sc[si] - mx); sum += sc[si]; }
+        float inv = sum > 0.0f ? 1.0f / sum : 0.0f;
+        for (int si = 0; si < wl; ++si) sc[si] *= inv;
+        for (int d = 0; d < hd; ++d) {
+            float a = 0.0f;
+            for (int si = 0; si < wl; ++si) { int t = start + si; a += sc[si] * v_at(c, t * stride + size_t(kvh) * hd + d, t); }
+            out[size_t(h) * hd + d] = a;
+        }
+    }
+}
+
 // E:657-715: single-query attention, keys in blocks of 64, online softmax, per-block
 // partial P.V sum added to the accumulator.
 void attention_flash(float* out, const float* q, const KVView& c, int seq, int nh, int nkv, int hd) {
@@ -460,6 +485,76 @@ void attention_flash_batch(float* out, const float* qb, const KVView& c, int m, 
     }
 }
 
+// E:916-1046 (attention_sliding_batch): as attention_flash_batch, but query position p sees the keys
+// [max(0, p - window + 1), p]; the key blocks start at the 64-aligned block that holds the tile's first valid key.
+void attention_sliding_batch(float* out, const float* qb, const KVView& c, int m, int base_pos, int window,
+                             int nh, int nkv, int hd) {
+    int g = nh / nkv;
+    float scale = 1.0f / std::sqrt(float(hd));
+    size_t stride = size_t(nkv) * hd;
+    size_t ostride = size_t(nh) * hd;
+#pragma omp parallel for schedule(dynamic, 1)
+    for (int h = 0; h < nh; ++h) {
+        int kvh = h / g;
+        size_t qo = size_t(h) * hd;
+        std::vector<float> acc(size_t(kQTile) * hd);
+        std::vector<float> sc(size_t(kQTile) * kFlashBlock);
+        float ms[kQTile], ls[kQTile];
+        for (int t0 = 0; t0 < m; t0 += kQTile) {
+            int tl = std::min(kQTile, m - t0);
+            int first_q = base_pos + t0, maxq = base_pos + t0 + tl - 1;
+            int min_k = std::max(first_q - (window - 1), 0);
+            for (int i = 0; i < kQTile; ++i) { ms[i] = -std::numeric_limits<float>::infinity(); ls[i] = 0.0f; }
+            std::fill(acc.begin(), acc.end(), 0.0f);
+            for (int b0 = (min_k / kFlashBlock) * kFlashBlock; b0 <= maxq; b0 += kFlashBlock) {
+                int be = std::min(b0 + kFlashBlock, maxq + 1), bl = be - b0;
+                std::fill(sc.begin(), sc.end(), 0.0f);
+                for (int bi = 0; bi < bl; ++bi) {
+                    int t = b0 + bi;
+                    size_t ko = t * stride + size_t(kvh) * hd;
+                    for (int qi = 0; qi < tl; ++qi) {
+                        const float* qr = qb + size_t(t0 + qi) * ostride + qo;
+                        sc[qi * kFlashBlock + bi] = k_dot(c, qr, ko, t, hd) * scale;
+                    }
+                }
+                for (int qi = 0; qi < tl; ++qi) {
+                    int qpos = base_pos + t0 + qi;
+                    int ws = std::max(qpos - (window - 1), 0);
+                    int lo = std::max(ws, b0) - b0;
+                    int hi = std::min(std::max(qpos + 1 - b0, 0), bl);
+                    float* s = &sc[qi * kFlashBlock];
+                    if (lo >= hi) { for (int bi = 0; bi < bl; ++bi) s[bi] = 0.0f; continue; }
+                    float mb = -std::numeric_limits<float>::infinity();
+                    for (int bi = lo; bi < hi; ++bi) if (s[bi] > mb) mb = s[bi];
+                    float mp = ms[qi], mn = std::max(mp, mb);
+                    ms[qi] = mn;
+                    float es = std::exp(mp - mn);
+                    ls[qi] *= es;
+                    for (int d = 0; d < hd; ++d) acc[size_t(qi) * hd + d] *= es;
+                    float lb = 0.0f;
+                    for (int bi = lo; bi < hi; ++bi) { float e = std::exp(s[bi] - mn); s[bi] = e; lb += e; }
+                    for (int bi = 0; bi < lo; ++bi) s[bi] = 0.0f;
+                    for (int bi = hi; bi < bl; ++bi) s[bi] = 0.0f;
+                    ls[qi] += lb;
+                }
+                for (int bi = 0; bi < bl; ++bi) {
+                    int t = b0 + bi;
+                    size_t vo = t * stride + size_t(kvh) * hd;
+                    for (int d = 0; d < hd; ++d) {
+                        float vv = v_at(c, vo + d, t);
+                        for (int qi = 0; qi < tl; ++qi) acc[size_t(qi) * hd + d] += sc[qi * kFlashBlock + bi] * vv;
+                    }
+                }
+            }
+            for (int qi = 0; qi < tl; ++qi) {
+                float il = ls[qi] > 0.0f ? 1.0f / ls[qi] : 0.0f;
+                float* o = out + size_t(t0 + qi) * ostride + qo;
+                for (int d = 0; d < hd; ++d) o[d] = acc[size_t(qi) * hd + d] * il;
+            }
+        }
+    }
+}
+
 // P:501-503: max_by(partial_cmp) keeps the LAST of equal maxima.
 uint32_t argmax_last(const float* v, int n) {
     int best = 0;
@@ -478,6 +573,7 @@ struct FoConfig {
     float rms_norm_eps, rope_theta;
     int32_t quant;     // 8 = Q8_0, 4 = Q4_0
     int32_t qkv_bias;  // 1: f32 q/k/v biases follow v in weights.bin (Qwen2)
+    int32_t sliding_window;  // > 0: sliding-window attention over that many positions (Mistral), E:97, E:191
 };
 
 uint16_t fo_f32_to_f16(float x) { return f32_to_f16_bits(x); }
@@ -609,6 +705,14 @@ void fo_attention(float* out, const float* q, int kv_mode, const void* k, const 
 void fo_attention_flash(float* out, const float* q, int kv_mode, const void* k, const void* v, const float* ks,
                         const float* vs, int seq, int nh, int nkv, int hd) {
     attention_flash(out, q, make_view(kv_mode, k, v, ks, vs), seq, nh, nkv, hd);
+}
+void fo_attention_sliding(float* out, const float* q, int kv_mode, const void* k, const void* v, const float* ks,
+                          const float* vs, int seq, int window, int nh, int nkv, int hd) {
+    attention_sliding(out, q, make_view(kv_mode, k, v, ks, vs), seq, window, nh, nkv, hd);
+}
+void fo_attention_sliding_batch(float* out, const float* qb, int kv_mode, const void* k, const void* v,
+                                const float* ks, const float* vs, int m, int base_pos, int window, int nh, int nkv, int hd) {
+    attention_sliding_batch(out, qb, make_view(kv_mode, k, v, ks, vs), m, base_pos, window, nh, nkv, hd);
 }
 void fo_attention_flash_batch(float* out, const float* qb, int kv_mode, const void* k, const void* v,
                               const float* ks, const float* vs, int m, int base_pos, int nh, int nkv, int hd) {
@@ -761,7 +865,8 @@ int fo_forward(const FoModel* m, FoKV* kv, uint32_t token, float* logits, float*
         rope(k.data(), pos, c.head_dim, c.num_kv_heads, m->freqs.data());
         kv_store(kv, l, pos, k.data(), v.data());
         KVView view = kv_view(kv, l);
-        if (c.max_seq_len > 512) attention_flash(ao.data(), q.data(), view, pos + 1, c.num_heads, c.num_kv_heads, c.head_dim);  // E:126-128
+        if (c.sliding_window > 0) attention_sliding(ao.data(), q.data(), view, pos + 1, c.sliding_window, c.num_heads, c.num_kv_heads, c.head_dim);  // E:4156
+        else if (c.max_seq_len > 512) attention_flash(ao.data(), q.data(), view, pos + 1, c.num_heads, c.num_kv_heads, c.head_dim);  // E:126-128
         else attention_plain(ao.data(), q.data(), view, pos + 1, c.num_heads, c.num_kv_heads, c.head_dim);
         matmul_mat(c.quant, ap.data(), 1, ao.data(), L.o, qk, h, m->fast);
         residual_add(hid.data(), ap.data(), h);
@@ -808,8 +913,10 @@ static int forward_prefill_batched(const FoModel* m, FoKV* kv, const uint32_t* t
             kv_store(kv, l, base + r, kr, vr);
         }
         KVView view = kv_view(kv, l);
-        if (c.max_seq_len > 512) {
+        if (c.max_seq_len > 512 && c.sliding_window <= 0) {
             attention_flash_batch(ao.data(), q.data(), view, n, base, c.num_heads, c.num_kv_heads, c.head_dim);
+        } else if (c.sliding_window > 0) {  // E:5312
+            attention_sliding_batch(ao.data(), q.data(), view, n, base, c.sliding_window, c.num_heads, c.num_kv_heads, c.head_dim);
         } else {  // E: short-context fallback, per-token plain attention
 #pragma omp parallel for
             for (int r = 0; r < n; ++r)

@@ -29,7 +29,7 @@ class FoConfig(C.Structure):
         ("num_heads", C.c_int32), ("num_kv_heads", C.c_int32), ("head_dim", C.c_int32),
         ("vocab_size", C.c_int32), ("max_seq_len", C.c_int32),
         ("rms_norm_eps", C.c_float), ("rope_theta", C.c_float),
-        ("quant", C.c_int32), ("qkv_bias", C.c_int32),
+        ("quant", C.c_int32), ("qkv_bias", C.c_int32), ("sliding_window", C.c_int32),
     ]
 
 
@@ -73,6 +73,8 @@ def lib():
         "fo_attention": (None, [_f32p, _f32p, i, vp, vp, vp, vp, i, i, i, i]),
         "fo_attention_flash": (None, [_f32p, _f32p, i, vp, vp, vp, vp, i, i, i, i]),
         "fo_attention_flash_batch": (None, [_f32p, _f32p, i, vp, vp, vp, vp, i, i, i, i, i]),
+        "fo_attention_sliding": (None, [_f32p, _f32p, i, vp, vp, vp, vp, i, i, i, i, i]),
+        "fo_attention_sliding_batch": (None, [_f32p, _f32p, i, vp, vp, vp, vp, i, i, i, i, i, i]),
         "fo_weights_bin_size": (sz, [C.POINTER(FoConfig)]),
         "fo_model_create": (vp, [C.POINTER(FoConfig), vp, sz]),
         "fo_model_set_fast": (None, [vp, i]),
@@ -215,11 +217,19 @@ def attention_flash_batch(qb, mode, k, v, ks, vs, m, base_pos, nh, nkv, hd):
     return _attn(lib().fo_attention_flash_batch, qb, mode, *_kv_args(mode, k, v, ks, vs), m, base_pos, nh, nkv, hd)
 
 
+def attention_sliding(q, mode, k, v, ks, vs, seq, window, nh, nkv, hd):
+    return _attn(lib().fo_attention_sliding, q, mode, *_kv_args(mode, k, v, ks, vs), seq, window, nh, nkv, hd)
+
+
+def attention_sliding_batch(qb, mode, k, v, ks, vs, m, base_pos, window, nh, nkv, hd):
+    return _attn(lib().fo_attention_sliding_batch, qb, mode, *_kv_args(mode, k, v, ks, vs), m, base_pos, window, nh, nkv, hd)
+
+
 # ------------------------------------------------------------------ model
 def make_config(d: dict) -> FoConfig:
     return FoConfig(d["hidden_size"], d["intermediate_size"], d["num_layers"], d["num_heads"], d["num_kv_heads"],
                     d["head_dim"], d["vocab_size"], d["max_seq_len"], d["rms_norm_eps"], d["rope_theta"],
-                    d["quant"], int(d.get("qkv_bias", 0)))
+                    d["quant"], int(d.get("qkv_bias", 0)), int(d.get("sliding_window", 0) or 0))
 
 
 class OracleModel:
