@@ -34,7 +34,8 @@ __device__ __forceinline__ void unpack8(const uint4& v, float* f) {
 // exp(x - m) with exp(-inf) = 0 and no NaN when both are -inf
 __device__ __forceinline__ float exp_rel(float x, float m) { return (x == -INFINITY) ? 0.f : __expf(x - m); }
 
-template <int HD>
+// SW: sliding-window instantiation (the full-attention one carries no window tests)
+template <int HD, bool SW>
 __global__ void __launch_bounds__(kThreads) attn_decode_kernel(DecParams p) {
     constexpr int W = Seg<HD>::W, ACTIVE = Seg<HD>::ACTIVE, RPW = Seg<HD>::RPW;
     constexpr int PARTS = (kThreads / 32) * RPW;
@@ -56,7 +57,7 @@ __global__ void __launch_bounds__(kThreads) attn_decode_kernel(DecParams p) {
     const int page0 = (pt && split < a.pages_per_seq) ? pt[split] : split;
     const int n_ctx = a.seq_len ? a.seq_len[b] + 1 : a.seq_len_host;
     const int n_pages = (n_ctx + FORGE_KV_PAGE - 1) / FORGE_KV_PAGE;
-    const int t_first = (a.window > 0 && n_ctx > a.window) ? n_ctx - a.window : 0;  // sliding window: first position seen
+    const int t_first = (SW && n_ctx > a.window) ? n_ctx - a.window : 0;  // sliding window: first position seen
     const size_t seq_base = a.page_table ? 0 : size_t(b) * a.max_ctx;  // contiguous: [batch][max_ctx][kvd]
     const int part = warp * RPW + seg;
 
@@ -77,7 +78,7 @@ __global__ void __launch_bounds__(kThreads) attn_decode_kernel(DecParams p) {
         }
         constexpr int UNR = 4;  // positions per segment whose K/V loads are issued before any use
         for (int lp = split; lp < n_pages; lp += a.splits) {
-            if ((lp + 1) * FORGE_KV_PAGE <= t_first) continue;  // the whole page lies before the window
+            if (SW && (lp + 1) * FORGE_KV_PAGE <= t_first) continue;  // the whole page lies before the window
             const int page = lp == split ? page0 : (pt ? pt[lp] : lp);
             const size_t page_row = seq_base + size_t(page) * FORGE_KV_PAGE;
             const int t_page = lp * FORGE_KV_PAGE;
@@ -88,7 +89,7 @@ __global__ void __launch_bounds__(kThreads) attn_decode_kernel(DecParams p) {
                     const int tp = base + u * PARTS + seg;
                     kr[u] = make_uint4(0, 0, 0, 0);
                     vr[u] = make_uint4(0, 0, 0, 0);
-                    if (tp < FORGE_KV_PAGE && t_page + tp < n_ctx && t_page + tp >= t_first && act) {
+                    if (tp < FORGE_KV_PAGE && t_page + tp < n_ctx && (!SW || t_page + tp >= t_first) && act) {
                         const size_t off = (page_row + tp) * kvd + kvh * HD + sl * 8;
                         kr[u] = __ldg(reinterpret_cast<const uint4*>(a.k_pool + off));
                         vr[u] = __ldg(reinterpret_cast<const uint4*>(a.v_pool + off));
@@ -118,7 +119,7 @@ __global__ void __launch_bounds__(kThreads) attn_decode_kernel(DecParams p) {
 #pragma unroll
                 for (int u = 0; u < UNR; ++u) {
                     const int tp = base + u * PARTS + seg;
-                    if (!(tp < FORGE_KV_PAGE && t_page + tp < n_ctx && t_page + tp >= t_first)) {
+                    if (!(tp < FORGE_KV_PAGE && t_page + tp < n_ctx && (!SW || t_page + tp >= t_first))) {
 #pragma unroll
                         for (int g = 0; g < kGC; ++g) sc[u][g] = -INFINITY;
                     }
@@ -252,9 +253,12 @@ int32_t attn_decode(const AttnDecodeArgs& a, cudaStream_t st) {
     DecParams p{a, 1.0f / sqrtf(float(a.hd))};
     dim3 grid(a.splits, a.nkv, a.batch);
     switch (a.hd) {
-        case 64: FORGE_CUDA(launch_pdl(attn_decode_kernel<64>, grid, dim3(kThreads), 0, st, p)); break;
-        case 96: FORGE_CUDA(launch_pdl(attn_decode_kernel<96>, grid, dim3(kThreads), 0, st, p)); break;
-        case 128: FORGE_CUDA(launch_pdl(attn_decode_kernel<128>, grid, dim3(kThreads), 0, st, p)); break;
+        case 64: FORGE_CUDA(a.window > 0 ? launch_pdl(attn_decode_kernel<64, true>, grid, dim3(kThreads), 0, st, p)
+                                          : launch_pdl(attn_decode_kernel<64, false>, grid, dim3(kThreads), 0, st, p)); break;
+        case 96: FORGE_CUDA(a.window > 0 ? launch_pdl(attn_decode_kernel<96, true>, grid, dim3(kThreads), 0, st, p)
+                                          : launch_pdl(attn_decode_kernel<96, false>, grid, dim3(kThreads), 0, st, p)); break;
+        case 128: FORGE_CUDA(a.window > 0 ? launch_pdl(attn_decode_kernel<128, true>, grid, dim3(kThreads), 0, st, p)
+                                          : launch_pdl(attn_decode_kernel<128, false>, grid, dim3(kThreads), 0, st, p)); break;
         default: set_error("attention: head_dim %d unsupported (64, 96, 128)", a.hd); return FORGE_ERR_SHAPE;
     }
     FORGE_LAUNCH_CHECK();

@@ -50,7 +50,8 @@ __device__ __forceinline__ uint32_t pack_h2(float a, float b) {
     return *reinterpret_cast<uint32_t*>(&h);
 }
 
-template <int HD>
+// SW: sliding-window instantiation (the full-attention one carries no window tests)
+template <int HD, bool SW>
 __global__ void __launch_bounds__(kThreads) attn_prefill_kernel(PrefillParams p) {
     constexpr int LD = HD + 8;       // padded row (halfs): keeps ldmatrix rows on distinct banks
     constexpr int CH = HD / 8;       // 16-byte chunks per row
@@ -109,7 +110,7 @@ __global__ void __launch_bounds__(kThreads) attn_prefill_kernel(PrefillParams p)
     };
     const float sl2 = p.scale * 1.4426950408889634f;  // scores in the base-2 domain
     // sliding window: the first query of the tile sees keys from (its position - window + 1); earlier tiles are skipped
-    const int k_first = a.window > 0 ? max(a.base_pos + row0 - (a.window - 1), 0) : 0;
+    const int k_first = SW ? max(a.base_pos + row0 - (a.window - 1), 0) : 0;
     const int j0 = k_first / BN;
     load_tile(j0, j0 & 1);
     for (int j = j0; j < ntiles; ++j) {
@@ -140,7 +141,7 @@ __global__ void __launch_bounds__(kThreads) attn_prefill_kernel(PrefillParams p)
         // (rows g and g+8 of the warp's 16)
         // some key of the tile may be masked for this warp: past a query's position, or before its window
         const bool diag = j * BN + BN - 1 > a.base_pos + row0 + warp * 16 ||
-                          (a.window > 0 && j * BN < a.base_pos + row0 + warp * 16 + 15 - (a.window - 1));
+                          (SW && j * BN < a.base_pos + row0 + warp * 16 + 15 - (a.window - 1));
 #pragma unroll
         for (int rr = 0; rr < 2; ++rr) {
             const int qpos = qpos0 + rr * 8;
@@ -151,7 +152,7 @@ __global__ void __launch_bounds__(kThreads) attn_prefill_kernel(PrefillParams p)
                 for (int e = 0; e < 2; ++e) {
                     float v = s[nb][rr * 2 + e] * sl2;
                     const int key = j * BN + nb * 8 + 2 * t + e;
-                    if (diag && (key > qpos || (a.window > 0 && key < qpos - (a.window - 1)))) v = -INFINITY;
+                    if (diag && (key > qpos || (SW && key < qpos - (a.window - 1)))) v = -INFINITY;
                     s[nb][rr * 2 + e] = v;
                     mx = fmaxf(mx, v);
                 }
@@ -224,9 +225,10 @@ __global__ void __launch_bounds__(kThreads) attn_prefill_kernel(PrefillParams p)
 template <int HD>
 int32_t launch(const PrefillParams& p, cudaStream_t st) {
     constexpr size_t smem = size_t(BM + 4 * BN) * (HD + 8) * sizeof(__half);
-    FORGE_CUDA(cudaFuncSetAttribute(attn_prefill_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+    auto kern = p.a.window > 0 ? attn_prefill_kernel<HD, true> : attn_prefill_kernel<HD, false>;
+    FORGE_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
     dim3 grid((p.a.m + BM - 1) / BM, p.a.nq);
-    attn_prefill_kernel<HD><<<grid, kThreads, smem, st>>>(p);
+    kern<<<grid, kThreads, smem, st>>>(p);
     FORGE_LAUNCH_CHECK();
     return FORGE_OK;
 }
