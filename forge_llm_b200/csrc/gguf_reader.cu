@@ -213,10 +213,15 @@ int32_t vote_quant(const ForgeGguf& g, int32_t& quant) {
 }
 
 // dense tensor -> f32 (F32 / F16 / BF16), or Q8_0 blocks -> f32 (dequantize_q8_0, weight_loader.rs:860-888)
-int32_t to_f32(const ForgeGguf& g, const TensorInfo& t, uint64_t expect, std::vector<float>& out) {
+// `first`: first element of the range [first, first + expect) inside the tensor (a part of a fused tensor)
+int32_t to_f32(const ForgeGguf& g, const TensorInfo& t, uint64_t expect, std::vector<float>& out, uint64_t first = 0) {
     const uint8_t* p; uint64_t bytes;
     if (!g.span(t, p, bytes)) { set_error("tensor %s extends past the end of the file", t.name.c_str()); return FORGE_ERR_SHAPE; }
-    if (t.numel() != expect) { set_error("tensor %s has %llu elements, expected %llu", t.name.c_str(), (unsigned long long)t.numel(), (unsigned long long)expect); return FORGE_ERR_SHAPE; }
+    if (first > t.numel() || expect > t.numel() - first) { set_error("tensor %s has %llu elements, expected %llu from %llu", t.name.c_str(), (unsigned long long)t.numel(), (unsigned long long)expect, (unsigned long long)first); return FORGE_ERR_SHAPE; }
+    uint64_t block, tsz;
+    type_layout(t.type, block, tsz);
+    if (first % block) { set_error("tensor %s: part does not start on a block", t.name.c_str()); return FORGE_ERR_SHAPE; }
+    p += first / block * tsz;
     out.resize(size_t(expect));
     if (t.type == T_F32) { memcpy(out.data(), p, size_t(expect) * 4); return FORGE_OK; }
     if (t.type == T_F16 || t.type == T_BF16) {
@@ -250,6 +255,7 @@ int32_t put_f32_tensor(const ForgeGguf& g, const std::string& hf, uint64_t expec
     const TensorInfo* t = g.tensor(hf);
     if (!t) { set_error("weight not found: %s", hf.c_str()); return FORGE_ERR_SHAPE; }
     if (!s.out) { s.n += size_t(expect) * 4; return t->numel() == expect ? FORGE_OK : (set_error("tensor %s has the wrong size", hf.c_str()), FORGE_ERR_SHAPE); }
+    if (t->numel() != expect) { set_error("tensor %s has the wrong size", hf.c_str()); return FORGE_ERR_SHAPE; }
     std::vector<float> v;
     FORGE_TRY(to_f32(g, *t, expect, v));
     s.put(v.data(), v.size() * 4);
@@ -264,27 +270,60 @@ int32_t put_quantised(const std::vector<float>& v, int32_t quant, Sink& s) {
     return FORGE_OK;
 }
 
+// Where a projection's rows live: a tensor of its own, or a row range of a fused Phi-3 tensor - q | k | v in
+// attn_qkv.weight, gate | up in a double-height ffn_up.weight (split_fused_tensors, weight_loader.rs:543-582).
+struct Part { const TensorInfo* t = nullptr; uint64_t first = 0; bool fused = false; };
+
+Part find_projection(const ForgeGguf& g, const std::string& hf, uint64_t numel, const ForgeModelConfig& c) {
+    const uint64_t H = uint64_t(c.hidden_size), QK = uint64_t(c.num_heads) * c.head_dim, KV = uint64_t(c.num_kv_heads) * c.head_dim;
+    const uint64_t FF = uint64_t(c.intermediate_size);
+    const size_t dot = hf.rfind(".self_attn."), mlp = hf.rfind(".mlp.");
+    if (const TensorInfo* t = g.tensor(hf)) {
+        // a double-height up_proj without a gate_proj is the fused gate | up tensor: up is its second half
+        if (mlp != std::string::npos && hf.compare(mlp, std::string::npos, ".mlp.up_proj.weight") == 0 && t->numel() == 2 * numel &&
+            !g.tensor(hf.substr(0, mlp) + ".mlp.gate_proj.weight"))
+            return {t, FF * H, true};
+        return {t, 0, false};
+    }
+    if (dot != std::string::npos) {
+        if (const TensorInfo* t = g.tensor(hf.substr(0, dot) + ".self_attn.qkv_proj.weight")) {
+            const std::string which = hf.substr(dot);
+            if (which == ".self_attn.q_proj.weight") return {t, 0, true};
+            if (which == ".self_attn.k_proj.weight") return {t, QK * H, true};
+            if (which == ".self_attn.v_proj.weight") return {t, (QK + KV) * H, true};
+        }
+    }
+    if (mlp != std::string::npos && hf.compare(mlp, std::string::npos, ".mlp.gate_proj.weight") == 0) {
+        const TensorInfo* t = g.tensor(hf.substr(0, mlp) + ".mlp.up_proj.weight");
+        if (t && t->numel() == 2 * numel) return {t, 0, true};
+    }
+    return {};
+}
+
 // a projection [rows][cols]: raw blocks when the tensor already has the model's block format, dense tensors are
 // quantised (the reference does this for f32 projections of Q4_0 models, main.rs:2601-2607)
-int32_t put_projection(const ForgeGguf& g, const std::string& hf, uint64_t rows, uint64_t cols, int32_t quant, Sink& s) {
-    const TensorInfo* t = g.tensor(hf);
-    if (!t) { set_error("weight not found: %s", hf.c_str()); return FORGE_ERR_SHAPE; }
+int32_t put_projection(const ForgeGguf& g, const std::string& hf, uint64_t rows, uint64_t cols, const ForgeModelConfig& c, Sink& s) {
+    const int32_t quant = c.quant;
     const uint64_t numel = rows * cols, bs = quant == FORGE_Q8_0 ? 34 : 18;
-    if (t->numel() != numel || t->dims[0] != cols) { set_error("tensor %s is not [%llu][%llu]", hf.c_str(), (unsigned long long)rows, (unsigned long long)cols); return FORGE_ERR_SHAPE; }
+    const Part part = find_projection(g, hf, numel, c);
+    const TensorInfo* t = part.t;
+    if (!t) { set_error("weight not found: %s", hf.c_str()); return FORGE_ERR_SHAPE; }
+    if (part.first > t->numel() || numel > t->numel() - part.first || t->dims[0] != cols) { set_error("tensor %s does not hold a [%llu][%llu] projection", t->name.c_str(), (unsigned long long)rows, (unsigned long long)cols); return FORGE_ERR_SHAPE; }
+    if (!part.fused && t->numel() != numel) { set_error("tensor %s is not [%llu][%llu]", hf.c_str(), (unsigned long long)rows, (unsigned long long)cols); return FORGE_ERR_SHAPE; }
     if (!s.out) { s.n += size_t(numel / 32 * bs); return FORGE_OK; }
     const int32_t want = quant == FORGE_Q8_0 ? T_Q8_0 : T_Q4_0;
     if (t->type == want) {
         const uint8_t* p; uint64_t bytes;
-        if (!g.span(*t, p, bytes)) { set_error("tensor %s extends past the end of the file", hf.c_str()); return FORGE_ERR_SHAPE; }
-        s.put(p, size_t(bytes));
+        if (!g.span(*t, p, bytes)) { set_error("tensor %s extends past the end of the file", t->name.c_str()); return FORGE_ERR_SHAPE; }
+        s.put(p + part.first / 32 * bs, size_t(numel / 32 * bs));
         return FORGE_OK;
     }
     if (t->type == T_F32 || t->type == T_F16 || t->type == T_BF16 || (t->type == T_Q8_0 && quant == FORGE_Q4_0)) {
         std::vector<float> v;
-        FORGE_TRY(to_f32(g, *t, numel, v));
+        FORGE_TRY(to_f32(g, *t, numel, v, part.first));
         return put_quantised(v, quant, s);
     }
-    set_error("tensor %s: type %d in a %s model is not supported", hf.c_str(), t->type, quant == FORGE_Q8_0 ? "Q8_0" : "Q4_0");
+    set_error("tensor %s: type %d in a %s model is not supported", t->name.c_str(), t->type, quant == FORGE_Q8_0 ? "Q8_0" : "Q4_0");
     return FORGE_ERR_UNSUPPORTED;
 }
 
@@ -298,23 +337,23 @@ int32_t export_to(const ForgeGguf& g, Sink& s) {
     for (int l = 0; l < c.num_layers; ++l) {
         const std::string p = "model.layers." + std::to_string(l) + ".";
         FORGE_TRY(put_f32_tensor(g, p + "input_layernorm.weight", H, s));
-        FORGE_TRY(put_projection(g, p + "self_attn.q_proj.weight", QK, H, c.quant, s));
-        FORGE_TRY(put_projection(g, p + "self_attn.k_proj.weight", KV, H, c.quant, s));
-        FORGE_TRY(put_projection(g, p + "self_attn.v_proj.weight", KV, H, c.quant, s));
+        FORGE_TRY(put_projection(g, p + "self_attn.q_proj.weight", QK, H, c, s));
+        FORGE_TRY(put_projection(g, p + "self_attn.k_proj.weight", KV, H, c, s));
+        FORGE_TRY(put_projection(g, p + "self_attn.v_proj.weight", KV, H, c, s));
         if (c.qkv_bias) {
             FORGE_TRY(put_f32_tensor(g, p + "self_attn.q_proj.bias", QK, s));
             FORGE_TRY(put_f32_tensor(g, p + "self_attn.k_proj.bias", KV, s));
             FORGE_TRY(put_f32_tensor(g, p + "self_attn.v_proj.bias", KV, s));
         }
-        FORGE_TRY(put_projection(g, p + "self_attn.o_proj.weight", H, QK, c.quant, s));
+        FORGE_TRY(put_projection(g, p + "self_attn.o_proj.weight", H, QK, c, s));
         FORGE_TRY(put_f32_tensor(g, p + "post_attention_layernorm.weight", H, s));
-        FORGE_TRY(put_projection(g, p + "mlp.gate_proj.weight", FF, H, c.quant, s));
-        FORGE_TRY(put_projection(g, p + "mlp.up_proj.weight", FF, H, c.quant, s));
-        FORGE_TRY(put_projection(g, p + "mlp.down_proj.weight", H, FF, c.quant, s));
+        FORGE_TRY(put_projection(g, p + "mlp.gate_proj.weight", FF, H, c, s));
+        FORGE_TRY(put_projection(g, p + "mlp.up_proj.weight", FF, H, c, s));
+        FORGE_TRY(put_projection(g, p + "mlp.down_proj.weight", H, FF, c, s));
     }
     FORGE_TRY(put_f32_tensor(g, "model.norm.weight", H, s));
     // lm_head: output.weight, else the (tied) embedding in the model's block format (main.rs:2625-2667)
-    FORGE_TRY(put_projection(g, g.tensor("lm_head.weight") ? "lm_head.weight" : "model.embed_tokens.weight", V, H, c.quant, s));
+    FORGE_TRY(put_projection(g, g.tensor("lm_head.weight") ? "lm_head.weight" : "model.embed_tokens.weight", V, H, c, s));
     if (s.overflow) { set_error("output buffer too small"); return FORGE_ERR_INVALID_ARG; }
     return FORGE_OK;
 }
@@ -394,7 +433,7 @@ int32_t forge_gguf_model_config(const ForgeGguf* g, ForgeModelConfig* c) {
     if (!g || !c) { set_error("bad argument to forge_gguf_model_config"); return FORGE_ERR_INVALID_ARG; }
     const MetaValue* av = g->get("general.architecture");
     const std::string arch = av && av->type == 8 ? av->s : "unknown";
-    if (arch != "llama" && arch != "qwen2" && arch != "mistral") { set_error("unsupported GGUF architecture for this backend: %s", arch.c_str()); return FORGE_ERR_UNSUPPORTED; }
+    if (arch != "llama" && arch != "qwen2" && arch != "mistral" && arch != "phi3" && arch != "phi") { set_error("unsupported GGUF architecture for this backend: %s", arch.c_str()); return FORGE_ERR_UNSUPPORTED; }
     uint64_t hidden = 0, layers = 0, heads = 0, kv_heads = 0, ff = 0, ctx = 0, vocab = 0, window = 0;
     g->get_u32(arch + ".embedding_length", hidden);
     g->get_u32(arch + ".block_count", layers);

@@ -268,7 +268,8 @@ int32_t forge_last_timing(ForgeModel* model, float* prefill_ms, float* decode_ms
  * little endian); configuration rules: crates/forgellm-cli/src/main.rs:689-811 (head_dim =
  * hidden / heads, defaults, Qwen2 has QKV bias) and the dtype vote :479-560; tensor names:
  * crates/forgellm-frontend/src/weight_loader.rs:400-441; write order: main.rs:2506-2757.
- * Supported: llama / qwen2 / mistral (no sliding window) whose projections are Q8_0 or Q4_0;
+ * Supported: llama / qwen2 / mistral / phi3 (fused attn_qkv and gate|up tensors are split, WL:543-582)
+ * whose projections are Q8_0 or Q4_0;
  * embedding and norms F32 / F16 / BF16 (or a Q8_0 embedding); dense or Q8_0 projections in a
  * Q4_0 model are re-quantised with the reference's rule; a missing output.weight ties the head
  * to the embedding.  Anything else returns FORGE_ERR_UNSUPPORTED; a malformed or truncated

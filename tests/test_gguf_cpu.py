@@ -180,3 +180,43 @@ def test_defaults_and_unsupported():
     meta[0] = ("general.architecture", 8, _s("gemma"))
     with pytest.raises(ForgeError):
         gguf.GgufFile(build_gguf(3, meta, [("blk.0.attn_q.weight", [256, 256], Q8_0, 0)], data=b"\0" * 69632)).config()
+
+
+def test_phi3_fused_tensors_are_split():
+    """Phi-3 files carry q|k|v as one attn_qkv tensor and gate|up as one double-height ffn_up tensor
+    (weight_loader.rs:543-582): the exported image must equal the one of the unfused file."""
+    c = configs.tiny(8, hd=64, nq=4, nkv=4, layers=2)
+    raw, blob, _ = synthetic_gguf(c, tied=False, arch="phi3")
+    g = gguf.GgufFile(raw)
+    t = {x["name"]: x for x in g.tensors()}
+    off0 = g.data_offset
+    table, data = [], b""
+    def add(name, dims, typ, payload):
+        nonlocal data
+        data += b"\0" * ((-len(data)) % 32)
+        table.append((name, dims, typ, len(data)))
+        data += payload
+    def payload(name):
+        return raw[off0 + t[name]["offset"]: off0 + t[name]["offset"] + t[name]["size"]]
+    h, ff = c["hidden_size"], c["intermediate_size"]
+    rows_qkv = (c["num_heads"] + 2 * c["num_kv_heads"]) * c["head_dim"]
+    for name, x in t.items():
+        if name.endswith(("attn_k.weight", "attn_v.weight", "ffn_gate.weight")):
+            continue
+        if name.endswith("attn_q.weight"):
+            p = name[:-len("attn_q.weight")]
+            add(p + "attn_qkv.weight", [h, rows_qkv], Q8_0, payload(p + "attn_q.weight") + payload(p + "attn_k.weight") + payload(p + "attn_v.weight"))
+        elif name.endswith("ffn_up.weight"):
+            p = name[:-len("ffn_up.weight")]
+            add(name, [h, 2 * ff], Q8_0, payload(p + "ffn_gate.weight") + payload(name))
+        else:
+            add(name, x["dims"], x["type"], payload(name))
+    arch = "phi3"
+    meta = [("general.architecture", 8, _s(arch)), (f"{arch}.embedding_length", 4, u32(h)), (f"{arch}.block_count", 4, u32(c["num_layers"])),
+            (f"{arch}.attention.head_count", 4, u32(c["num_heads"])), (f"{arch}.attention.head_count_kv", 4, u32(c["num_kv_heads"])),
+            (f"{arch}.feed_forward_length", 4, u32(ff)), (f"{arch}.vocab_size", 4, u32(c["vocab_size"])),
+            (f"{arch}.context_length", 4, u32(c["max_seq_len"])), (f"{arch}.attention.layer_norm_rms_epsilon", 6, f32(c["rms_norm_eps"])),
+            (f"{arch}.rope.freq_base", 6, f32(c["rope_theta"]))]
+    fused = gguf.GgufFile(build_gguf(3, meta, table, data=data))
+    assert fused.config()["num_kv_heads"] == 4
+    assert np.array_equal(fused.weights_bin(), blob)
