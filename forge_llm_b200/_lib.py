@@ -82,6 +82,9 @@ SIGNATURES = {
     "forge_kv_len": (i32, [vp, i32]),
     "forge_kv_destroy": (None, [vp]),
     "forge_kv_read": (i32, [vp, i32, i32, i32, vp]),
+    "forge_kv_save_size": (sz, [vp, i32]),
+    "forge_kv_save": (i32, [vp, i32, vp, sz]),
+    "forge_kv_load": (i32, [vp, i32, vp, sz]),
     "forge_forward": (i32, [vp, vp, u32, vp]),
     "forge_forward_prefill": (i32, [vp, vp, vp, sz, vp]),
     "forge_forward_seq": (i32, [vp, vp, i32, u32, vp]),

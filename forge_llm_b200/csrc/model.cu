@@ -754,6 +754,97 @@ int32_t forge_kv_read(ForgeKV* kv, int32_t seq, int32_t layer, int32_t which, fl
     return rc;
 }
 
+// ---- persistence (project.rs:456-499)
+namespace {
+constexpr char kKvMagic[4] = {'F', 'K', 'V', '1'};
+struct KvHeader { char magic[4]; uint32_t layers, width; uint64_t len; };
+
+// one layer's rows [0, len) of K or V between the paged pool and a contiguous host array [len][width] of fp16
+int32_t kv_copy_rows(ForgeKV* kv, int seq, int layer, int which, int len, __half* host, bool to_host) {
+    ForgeModel* m = kv->model;
+    __half* pool = (which ? kv->v_pool : kv->k_pool) + size_t(layer) * kv->layer_stride;
+    for (int lp = 0; lp * FORGE_KV_PAGE < len; ++lp) {
+        const int rows = std::min(FORGE_KV_PAGE, len - lp * FORGE_KV_PAGE);
+        const int page = kv->h_page_table[size_t(seq) * kv->pages_per_seq + lp];
+        __half* dev = pool + size_t(page) * FORGE_KV_PAGE * m->kv;
+        __half* hst = host + size_t(lp) * FORGE_KV_PAGE * m->kv;
+        const size_t bytes = sizeof(__half) * size_t(rows) * m->kv;
+        FORGE_CUDA(to_host ? cudaMemcpyAsync(hst, dev, bytes, cudaMemcpyDeviceToHost, m->stream)
+                           : cudaMemcpyAsync(dev, hst, bytes, cudaMemcpyHostToDevice, m->stream));
+    }
+    return FORGE_OK;
+}
+}  // namespace
+
+size_t forge_kv_save_size(const ForgeKV* kv, int32_t seq) {
+    if (!kv || seq < 0 || seq >= kv->batch) return 0;
+    const ForgeModel* m = kv->model;
+    return sizeof(KvHeader) + size_t(2) * m->cfg.num_layers * kv->len[seq] * m->kv * sizeof(__half);
+}
+
+int32_t forge_kv_save(ForgeKV* kv, int32_t seq, void* out_host, size_t capacity) {
+    FORGE_TRY(check_seq(kv, seq));
+    ForgeModel* m = kv->model;
+    if (!out_host || capacity < forge_kv_save_size(kv, seq)) { set_error("forge_kv_save: buffer too small"); return FORGE_ERR_INVALID_ARG; }
+    if (m->cfg.tp_world > 1) { set_error("forge_kv_save: a tensor-parallel cache holds only this rank's heads"); return FORGE_ERR_UNSUPPORTED; }
+    FORGE_CUDA(cudaSetDevice(m->device));
+    const int len = kv->len[seq], L = m->cfg.num_layers;
+    KvHeader h;
+    memcpy(h.magic, kKvMagic, 4); h.layers = uint32_t(L); h.width = uint32_t(m->kv); h.len = uint64_t(len);
+    memcpy(out_host, &h, sizeof(h));
+    __half* dst = reinterpret_cast<__half*>(static_cast<char*>(out_host) + sizeof(h));
+    for (int which = 0; which < 2; ++which)
+        for (int l = 0; l < L; ++l) FORGE_TRY(kv_copy_rows(kv, seq, l, which, len, dst + (size_t(which) * L + l) * len * m->kv, true));
+    FORGE_CUDA(cudaStreamSynchronize(m->stream));
+    return FORGE_OK;
+}
+
+int32_t forge_kv_load(ForgeKV* kv, int32_t seq, const void* data_host, size_t n) {
+    FORGE_TRY(check_seq(kv, seq));
+    ForgeModel* m = kv->model;
+    if (!data_host || n < 8) { set_error("forge_kv_load: no data"); return FORGE_ERR_INVALID_ARG; }
+    if (m->cfg.tp_world > 1) { set_error("forge_kv_load: a tensor-parallel cache holds only this rank's heads"); return FORGE_ERR_UNSUPPORTED; }
+    FORGE_CUDA(cudaSetDevice(m->device));
+    const int L = m->cfg.num_layers;
+    const size_t W = size_t(m->kv);
+    const uint8_t* p = static_cast<const uint8_t*>(data_host);
+    std::vector<__half> rows;  // [2][L][len][W]
+    uint64_t len = 0;
+    if (n >= sizeof(KvHeader) && memcmp(p, kKvMagic, 4) == 0) {
+        KvHeader h;
+        memcpy(&h, p, sizeof(h));
+        if (h.layers != uint32_t(L) || h.width != uint32_t(W)) { set_error("forge_kv_load: the file is for %u layers x %u, the model has %d x %zu", h.layers, h.width, L, W); return FORGE_ERR_SHAPE; }
+        len = h.len;
+        if (len > uint64_t(kv->max_seq) || n != sizeof(h) + size_t(2) * L * len * W * sizeof(__half)) { set_error("forge_kv_load: bad length"); return FORGE_ERR_SHAPE; }
+        rows.resize(size_t(2) * L * len * W);
+        memcpy(rows.data(), p + sizeof(h), rows.size() * sizeof(__half));
+    } else {
+        // the reference's int8 file: u64 len | K i8 [L][len*W] | V i8 [L][len*W] | k_scales f32 [L][len] | v_scales f32 [L][len]
+        memcpy(&len, p, 8);
+        if (len > uint64_t(kv->max_seq) || n != 8 + size_t(2) * L * len * W + size_t(2) * L * len * 4) { set_error("forge_kv_load: not a cache file of this model (%zu bytes)", n); return FORGE_ERR_SHAPE; }
+        const int8_t* q = reinterpret_cast<const int8_t*>(p + 8);
+        const uint8_t* sc = p + 8 + size_t(2) * L * len * W;
+        rows.resize(size_t(2) * L * len * W);
+        for (size_t wl = 0; wl < size_t(2) * L; ++wl)
+            for (size_t t = 0; t < len; ++t) {
+                float s;
+                memcpy(&s, sc + (wl * len + t) * 4, 4);
+                for (size_t i = 0; i < W; ++i) rows[(wl * len + t) * W + i] = __float2half_rn(float(q[(wl * len + t) * W + i]) * s);
+            }
+    }
+    // the sequence starts over: its pages go back to the pool, then the saved rows are written
+    FORGE_CUDA(cudaStreamSynchronize(m->stream));
+    for (int i = 0; i < kv->pages_used[seq]; ++i) kv->free_pages.push_back(kv->h_page_table[size_t(seq) * kv->pages_per_seq + i]);
+    kv->pages_used[seq] = 0;
+    kv->len[seq] = 0;
+    FORGE_TRY(ensure_pages(kv, seq, int(len)));
+    for (int which = 0; which < 2; ++which)
+        for (int l = 0; l < L; ++l) FORGE_TRY(kv_copy_rows(kv, seq, l, which, int(len), rows.data() + (size_t(which) * L + l) * len * W, false));
+    FORGE_CUDA(cudaStreamSynchronize(m->stream));
+    kv->len[seq] = int(len);
+    return upload_len(kv);
+}
+
 int32_t forge_forward_prefill_seq(ForgeModel* m, ForgeKV* kv, int32_t seq, const uint32_t* tokens, size_t n, float* logits_host) {
     if (!m || !tokens || n == 0 || n > (1u << 20)) { set_error("bad argument to forge_forward_prefill"); return FORGE_ERR_INVALID_ARG; }
     FORGE_TRY(check_seq(kv, seq));

@@ -70,6 +70,17 @@ class KVCache:
         check(lib.forge_kv_read(self._h, seq, layer, which, _p(out)))
         return out
 
+    def save(self, seq: int = 0) -> np.ndarray:
+        """The sequence's cache as a byte image (fp16 rows behind a small header)."""
+        out = np.empty(int(lib.forge_kv_save_size(self._h, seq)), np.uint8)
+        check(lib.forge_kv_save(self._h, seq, _p(out), out.size))
+        return out
+
+    def load(self, data, seq: int = 0) -> None:
+        """Restores a saved sequence; also takes the reference's int8 cache file (converted to fp16)."""
+        buf = np.ascontiguousarray(np.frombuffer(data, np.uint8) if not isinstance(data, np.ndarray) else data, np.uint8)
+        check(lib.forge_kv_load(self._h, seq, _p(buf), buf.size))
+
     def close(self) -> None:
         if getattr(self, "_h", None):
             lib.forge_kv_destroy(self._h)

@@ -225,6 +225,16 @@ void forge_kv_destroy(ForgeKV* kv);
  * a host buffer [len][num_kv_heads*head_dim] (used by parity tests). */
 int32_t forge_kv_read(ForgeKV* kv, int32_t seq, int32_t layer, int32_t which, float* out_host);
 
+/* KV cache persistence (save_kv_cache / load_kv_cache of the generated main.rs, project.rs:456-499).
+ * forge_kv_save writes sequence `seq` as {"FKV1", u32 layers, u32 kv_width, u64 len} followed by the K rows of every
+ * layer and then the V rows of every layer, fp16 [layer][len][kv_width]; forge_kv_save_size is the byte count.
+ * forge_kv_load replaces sequence `seq` with the saved state.  It also accepts the reference's own file - u64 len,
+ * int8 K [layer][len*kv_width], int8 V, f32 k_scales [layer][len], f32 v_scales - and converts it: every value
+ * becomes fp16(int8 * scale).  A file of another model (layer count, width) or past max_seq is refused. */
+size_t forge_kv_save_size(const ForgeKV* kv, int32_t seq);
+int32_t forge_kv_save(ForgeKV* kv, int32_t seq, void* out_host, size_t capacity);
+int32_t forge_kv_load(ForgeKV* kv, int32_t seq, const void* data_host, size_t len);
+
 /* forward(token_id, &weights, &mut cache) -> Vec<f32>  E:4029-4500, sequence 0.
  * logits_host: V floats (may be NULL to skip the copy). */
 int32_t forge_forward(ForgeModel* model, ForgeKV* kv, uint32_t token, float* logits_host);

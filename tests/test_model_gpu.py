@@ -303,3 +303,49 @@ def test_model_from_gguf_file(oracle):
     assert np.array_equal(gm.generate_greedy(toks, 16, kv), om.generate_greedy(toks, 16)[0])
     kv.close()
     gm.close()
+
+
+@pytest.mark.gpu
+def test_kv_cache_save_and_load(oracle):
+    """save -> load continues bit-identically (project.rs:456-499 semantics); the reference's int8 file is accepted and
+    converted: every cached value becomes fp16(int8 * per-token scale)."""
+    import struct
+    from forge_llm_b200 import configs, runtime, synth
+    from forge_llm_b200._lib import ForgeError
+    c = configs.tiny(4, hd=64, nq=4, nkv=2, layers=3)
+    blob = synth.make_weights_bin(c)
+    toks = synth.prompt_tokens(c, 100)
+    gm = runtime.Model(c, blob)
+    kv = gm.new_cache(max_seq=160)
+    gm.forward_prefill(toks[:90], kv)
+    image = kv.save()
+    want = [gm.forward(int(t), kv) for t in toks[90:]]
+    other = gm.new_cache(max_seq=160)
+    gm.forward_prefill(toks[:7], other)          # something to overwrite
+    other.load(image)
+    assert other.len() == 90
+    for t, w in zip(toks[90:], want):
+        assert np.array_equal(gm.forward(int(t), other), w)
+    # the reference's file layout, built from this cache's rows quantised the reference's way
+    L, W, n = c["num_layers"], c["num_kv_heads"] * c["head_dim"], 90
+    q8 = np.zeros((2, L, n, W), np.int8)
+    sc = np.zeros((2, L, n), np.float32)
+    for which in (0, 1):
+        for l in range(L):
+            rows = kv.read(l, which)[:n]
+            for t in range(n):
+                q8[which, l, t], sc[which, l, t] = oracle.quantize_kv(rows[t])
+    ref_file = struct.pack("<Q", n) + q8.tobytes() + sc.tobytes()
+    other.load(ref_file)
+    assert other.len() == n
+    for which in (0, 1):
+        for l in range(L):
+            expect = (q8[which, l].astype(np.float32) * sc[which, l][:, None]).astype(np.float16).astype(np.float32)
+            assert np.array_equal(other.read(l, which), expect)
+    with pytest.raises(ForgeError):
+        other.load(ref_file[:-4])                 # wrong size
+    with pytest.raises(ForgeError):
+        gm.new_cache(max_seq=64).load(image)      # longer than this cache allows
+    for x in (kv, other):
+        x.close()
+    gm.close()
