@@ -34,6 +34,12 @@ class ForgeError(RuntimeError):
 
 vp, i32, f32, sz, u32 = C.c_void_p, C.c_int32, C.c_float, C.c_size_t, C.c_uint32
 
+
+class ForgeSampling(C.Structure):
+    _fields_ = [("temperature", C.c_float), ("top_k", C.c_int32), ("top_p", C.c_float), ("repeat_penalty", C.c_float),
+                ("seed", C.c_uint64)]
+
+
 # name -> (restype, argtypes); every symbol the public header declares
 SIGNATURES = {
     "forge_last_error": (C.c_char_p, []),
@@ -71,6 +77,10 @@ SIGNATURES = {
     "forge_model_create": (i32, [C.POINTER(ForgeModelConfig), vp, sz, i32, C.POINTER(vp)]),
     "forge_model_destroy": (None, [vp]),
     "forge_model_stream": (vp, [vp]),
+    "forge_model_vocab_size": (sz, [vp]),
+    "forge_apply_repeat_penalty": (i32, [vp, i32, vp, sz, f32]),
+    "forge_sample": (i32, [vp, i32, f32, i32, f32, C.POINTER(C.c_uint64), C.POINTER(u32)]),
+    "forge_generate": (i32, [vp, vp, vp, sz, i32, C.POINTER(ForgeSampling), vp, sz, vp, C.POINTER(i32)]),
     "forge_tp_unique_id": (i32, [vp]),
     "forge_model_tp_init": (i32, [vp, vp]),
     "forge_model_tp_exchange_export": (i32, [vp, vp]),

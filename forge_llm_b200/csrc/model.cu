@@ -562,6 +562,7 @@ void forge_model_destroy(ForgeModel* m) {
 }
 
 void* forge_model_stream(ForgeModel* m) { return m ? static_cast<void*>(m->stream) : nullptr; }
+size_t forge_model_vocab_size(const ForgeModel* m) { return m ? size_t(m->V) : 0; }
 
 int32_t forge_model_tp_exchange_export(ForgeModel* m, uint8_t* handle_out) {
     if (!m || !handle_out) { set_error("bad argument to forge_model_tp_exchange_export"); return FORGE_ERR_INVALID_ARG; }

@@ -261,6 +261,31 @@ int32_t forge_generate_greedy(ForgeModel* model, ForgeKV* kv, const uint32_t* pr
 int32_t forge_decode_greedy_batch(ForgeModel* model, ForgeKV* kv, int32_t batch,
                                   const uint32_t* first_tokens, int32_t n_new, uint32_t* out_tokens);
 
+/* Token selection of the generated main.rs, on the host logits (project.rs:501-551): argmax when temperature <= 0
+ * (last index on ties), else temperature, softmax, top-k, top-p, renormalisation and one draw of the xorshift
+ * generator, in the reference's arithmetic order; both calls modify `logits` in place.  The repeat penalty divides a
+ * positive logit and multiplies a non-positive one, once per occurrence in `recent`. */
+int32_t forge_apply_repeat_penalty(float* logits_host, int32_t n, const uint32_t* recent, size_t n_recent, float penalty);
+int32_t forge_sample(float* logits_host, int32_t n, float temperature, int32_t top_k, float top_p, uint64_t* rng_state,
+                     uint32_t* token);
+
+/* The prompt -> tokens loop of the generated main.rs (project.rs:714-751): prefill, sample, then until an EOS id or
+ * max_tokens: emit, forward, repeat penalty over prompt + emitted tokens, sample.  The reference's command-line
+ * defaults are temperature 0, top_k 0, top_p 0.9, repeat_penalty 1.1, seed 0xdeadbeef12345678 (project.rs:608-613).
+ * out_tokens: max_tokens entries; *n_out: how many were emitted. */
+typedef struct ForgeSampling {
+    float temperature;
+    int32_t top_k;
+    float top_p;
+    float repeat_penalty;
+    uint64_t seed;
+} ForgeSampling;
+int32_t forge_generate(ForgeModel* model, ForgeKV* kv, const uint32_t* prompt, size_t n_prompt, int32_t max_tokens,
+                       const ForgeSampling* sampling, const uint32_t* eos_tokens, size_t n_eos, uint32_t* out_tokens,
+                       int32_t* n_out);
+/* Vocabulary size of the model (the length of a logits row). */
+size_t forge_model_vocab_size(const ForgeModel* model);
+
 /* Parity hook: when enabled, the next forward / forward_prefill call records the hidden
  * state after every layer.  forge_hidden_trace_read copies [num_layers][rows][hidden] f32 of
  * the last call to a host buffer and returns the row count through *rows. */
