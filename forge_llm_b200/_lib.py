@@ -78,6 +78,7 @@ SIGNATURES = {
     "forge_model_destroy": (None, [vp]),
     "forge_model_stream": (vp, [vp]),
     "forge_model_vocab_size": (sz, [vp]),
+    "forge_score_chunk": (i32, [vp, vp, vp, sz, vp]),
     "forge_apply_repeat_penalty": (i32, [vp, i32, vp, sz, f32]),
     "forge_sample": (i32, [vp, i32, f32, i32, f32, C.POINTER(C.c_uint64), C.POINTER(u32)]),
     "forge_generate": (i32, [vp, vp, vp, sz, i32, C.POINTER(ForgeSampling), vp, sz, vp, C.POINTER(i32)]),

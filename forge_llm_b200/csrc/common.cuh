@@ -196,6 +196,7 @@ constexpr int kArgmaxSlices = 148;
 int32_t argmax_slices(uint32_t* result, const float* logits, int n, int batch, float* sval, int* sidx, int* ticket, cudaStream_t st);
 int32_t f32_to_f16(__half* out, __half* lo, const float* in, size_t n, cudaStream_t st);
 int32_t step_advance(int32_t* seq_len, int batch, int32_t* step, cudaStream_t st, uint32_t* extra_counter = nullptr);
+int32_t token_nll(double* out, const float* logits, int n, uint32_t target, cudaStream_t st);  // -log softmax(logits)[target], f64
 int32_t gather_rows_f16(float* out, const __half* pool, const int32_t* page_row, int len, int kvd, cudaStream_t st);
 
 // ------------------------------------------------------------------ attention

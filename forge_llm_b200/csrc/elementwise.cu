@@ -236,6 +236,31 @@ __global__ void f32_to_f16_kernel(__half* out, __half* lo, const float* in, size
     for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < n; i += size_t(gridDim.x) * blockDim.x) store_split(out, lo, i, in[i]);
 }
 
+// -log p(target) of one logits row: log_z = max + ln(sum exp((l - max) as f64)) as the reference's corpus scorer forms it
+// (crates/forgellm-codegen-cpu/src/project.rs:684-689); one CTA, f64 tree sums
+__global__ void __launch_bounds__(1024) token_nll_kernel(double* out, const float* __restrict__ logits, int n, uint32_t target) {
+    __shared__ float smax[32];
+    __shared__ double ssum[32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float mx = -INFINITY;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) mx = fmaxf(mx, logits[i]);
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    if (lane == 0) smax[warp] = mx;
+    __syncthreads();
+    mx = smax[0];
+    for (int w = 1; w < int(blockDim.x >> 5); ++w) mx = fmaxf(mx, smax[w]);
+    double s = 0.0;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) s += exp(double(logits[i] - mx));
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (lane == 0) ssum[warp] = s;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double tot = 0.0;
+        for (int w = 0; w < int(blockDim.x >> 5); ++w) tot += ssum[w];
+        *out = -(double(logits[target]) - (double(mx) + log(tot)));
+    }
+}
+
 __global__ void step_advance_kernel(int32_t* seq_len, int batch, int32_t* step, uint32_t* extra_counter) {
     int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < batch) seq_len[i] += 1;
@@ -334,6 +359,11 @@ int32_t argmax_slices(uint32_t* result, const float* logits, int n, int batch, f
 int32_t f32_to_f16(__half* out, __half* lo, const float* in, size_t n, cudaStream_t st) {
     if (n == 0) return FORGE_OK;
     f32_to_f16_kernel<<<grid_for(n), 256, 0, st>>>(out, lo, in, n);
+    FORGE_LAUNCH_CHECK();
+    return FORGE_OK;
+}
+int32_t token_nll(double* out, const float* logits, int n, uint32_t target, cudaStream_t st) {
+    token_nll_kernel<<<1, 1024, 0, st>>>(out, logits, n, target);
     FORGE_LAUNCH_CHECK();
     return FORGE_OK;
 }

@@ -755,6 +755,29 @@ int32_t forge_kv_read(ForgeKV* kv, int32_t seq, int32_t layer, int32_t which, fl
     return rc;
 }
 
+// ---- corpus scoring (--score-corpus, project.rs:652-712): per-token forward() over one chunk from an empty cache; the
+// negative log-likelihood of every next token is formed on the device from the logits row, so no logits leave the GPU
+int32_t forge_score_chunk(ForgeModel* m, ForgeKV* kv, const uint32_t* chunk, size_t n, double* nll_host) {
+    if (!m || !chunk || !nll_host || n < 2 || n > (1u << 20)) { set_error("bad argument to forge_score_chunk"); return FORGE_ERR_INVALID_ARG; }
+    FORGE_TRY(check_seq(kv, 0));
+    if (kv->model != m) { set_error("kv belongs to another model"); return FORGE_ERR_INVALID_ARG; }
+    if (int(n) - 1 > kv->max_seq) { set_error("chunk of %zu tokens does not fit the cache (max_seq %d)", n, kv->max_seq); return FORGE_ERR_KV_FULL; }
+    for (size_t i = 0; i < n; ++i) if (chunk[i] >= uint32_t(m->V)) { set_error("token id %u out of vocabulary", chunk[i]); return FORGE_ERR_INVALID_ARG; }
+    FORGE_CUDA(cudaSetDevice(m->device));
+    FORGE_TRY(forge_kv_reset(kv));
+    double* d_nll = nullptr;
+    FORGE_CUDA(cudaMalloc(&d_nll, sizeof(double) * (n - 1)));
+    int32_t rc = FORGE_OK;
+    for (size_t i = 0; i + 1 < n && rc == FORGE_OK; ++i) {
+        rc = forge_forward_seq(m, kv, 0, chunk[i], nullptr);                       // logits of position i stay in d_logits
+        if (rc == FORGE_OK) rc = token_nll(d_nll + i, m->d_logits, m->V, chunk[i + 1], m->stream);
+    }
+    if (rc == FORGE_OK && (cudaMemcpyAsync(nll_host, d_nll, sizeof(double) * (n - 1), cudaMemcpyDeviceToHost, m->stream) != cudaSuccess ||
+                           cudaStreamSynchronize(m->stream) != cudaSuccess)) { set_error("score copy failed"); rc = FORGE_ERR_CUDA; }
+    cudaFree(d_nll);
+    return rc;
+}
+
 // ---- persistence (project.rs:456-499)
 namespace {
 constexpr char kKvMagic[4] = {'F', 'K', 'V', '1'};

@@ -194,6 +194,25 @@ class Model:
             raise ForgeError(1, f"trace holds {got.value} rows, asked for {rows}")
         return out
 
+    def score_corpus(self, tokens, cache: "KVCache", chunk_size: int = 512, max_chunks: int = 0):
+        """Token-by-token perplexity like the generated binary's --score-corpus: (mean NLL in nats, perplexity, count)."""
+        t = np.ascontiguousarray(tokens, np.uint32)
+        total, count, chunks = 0.0, 0, 0
+        for start in range(0, t.size, chunk_size):
+            if max_chunks and chunks >= max_chunks:
+                break
+            chunk = t[start:start + chunk_size]
+            chunks += 1
+            if chunk.size < 2:
+                continue
+            nll = np.empty(chunk.size - 1, np.float64)
+            check(lib.forge_score_chunk(self._h, cache._h, _p(chunk), chunk.size, _p(nll)))
+            for v in nll:  # sequential f64 sum, as the reference accumulates
+                total += float(v)
+            count += nll.size
+        mean = total / max(count, 1)
+        return mean, float(np.exp(mean)), count
+
     def last_timing(self):
         a, b, n = C.c_float(), C.c_float(), C.c_int64()
         check(lib.forge_last_timing(self._h, C.byref(a), C.byref(b), C.byref(n)))

@@ -283,6 +283,10 @@ typedef struct ForgeSampling {
 int32_t forge_generate(ForgeModel* model, ForgeKV* kv, const uint32_t* prompt, size_t n_prompt, int32_t max_tokens,
                        const ForgeSampling* sampling, const uint32_t* eos_tokens, size_t n_eos, uint32_t* out_tokens,
                        int32_t* n_out);
+/* One chunk of the reference's corpus scorer (--score-corpus, project.rs:652-712): from an empty cache, per-token
+ * forward() over chunk[0 .. n-2]; nll_host[i] = -log softmax(logits after chunk[i])[chunk[i+1]] for i < n-1, formed
+ * in f64 from the f32 logits as the reference does.  Perplexity of a corpus = exp(sum of all nll / count). */
+int32_t forge_score_chunk(ForgeModel* model, ForgeKV* kv, const uint32_t* chunk, size_t n, double* nll_host);
 /* Vocabulary size of the model (the length of a logits row). */
 size_t forge_model_vocab_size(const ForgeModel* model);
 

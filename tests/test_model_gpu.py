@@ -349,3 +349,29 @@ def test_kv_cache_save_and_load(oracle):
     for x in (kv, other):
         x.close()
     gm.close()
+
+
+@pytest.mark.gpu
+def test_corpus_scoring(oracle):
+    """--score-corpus semantics (project.rs:652-712): per-token forward from an empty cache per chunk, NLL in f64."""
+    from forge_llm_b200 import configs, runtime, synth
+    c = configs.tiny(8, hd=64, nq=4, nkv=2, layers=2)
+    blob = synth.make_weights_bin(c)
+    toks = synth.prompt_tokens(c, 70)
+    gm = runtime.Model(c, blob)
+    kv = gm.new_cache(max_seq=64)
+    mean, ppl, count = gm.score_corpus(toks, kv, chunk_size=32)
+    total, n = 0.0, 0
+    for start in range(0, 70, 32):
+        chunk = toks[start:start + 32]
+        om = oracle.OracleModel(c, blob, kv_mode=oracle.KV_F16)
+        logits = om.forward(int(chunk[0]))
+        for i in range(1, len(chunk)):
+            l64 = (logits - logits.max()).astype(np.float64)
+            total -= float(logits[chunk[i]]) - (float(logits.max()) + np.log(np.exp(l64).sum()))
+            n += 1
+            logits = om.forward(int(chunk[i]))
+    assert count == n == 67
+    assert abs(mean - total / n) < 2e-3 and abs(ppl / np.exp(total / n) - 1) < 2e-3
+    kv.close()
+    gm.close()
