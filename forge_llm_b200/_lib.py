@@ -46,6 +46,8 @@ SIGNATURES = {
     "forge_device_count": (i32, []),
     "forge_matmul_mat_q8_0": (i32, [vp, i32, vp, vp, i32, i32, vp]),
     "forge_matmul_mat_q4_0": (i32, [vp, i32, vp, vp, i32, i32, vp]),
+    "forge_matmul_vec_q4_k": (i32, [vp, i32, vp, vp, i32, i32, vp]),
+    "forge_matmul_vec_q6_k": (i32, [vp, i32, vp, vp, i32, i32, vp]),
     "forge_packed_create": (i32, [i32, vp, i32, i32, vp, C.POINTER(vp)]),
     "forge_packed_destroy": (None, [vp]),
     "forge_matmul_mat_packed": (i32, [vp, i32, vp, vp, vp]),

@@ -35,17 +35,26 @@ struct ForgePacked {
 
 namespace {
 
+bool is_kquant(int quant) { return quant == FORGE_Q4_K || quant == FORGE_Q6_K; }
+// bytes of one raw weight row
+size_t raw_row_bytes(int quant, int K) {
+    if (is_kquant(quant)) return size_t(K / 256) * (quant == FORGE_Q4_K ? 144 : 210);
+    return size_t(K / 32) * (quant == FORGE_Q8_0 ? 34 : 18);
+}
+
 int32_t packed_build(int quant, const uint8_t* w, int K, int N, cudaStream_t st, ForgePacked* pk) {
-    const int BS = quant == FORGE_Q8_0 ? 34 : 18;
     pk->soa.K = K; pk->soa.N = N; pk->soa.quant = quant;
     pk->tiled.K = K; pk->tiled.N = N; pk->tiled.quant = quant; { int dev = 0, sms = 148; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
       pk->tiled.bt = gemv_band_tiles(N, sms); pk->tiled.bands = (N + 16 * pk->tiled.bt - 1) / (16 * pk->tiled.bt); }
-    FORGE_CUDA(cudaMalloc(&pk->soa.qs, size_t(N) * pk->soa.qs_row_bytes()));
-    FORGE_CUDA(cudaMalloc(&pk->soa.d, size_t(N) * (K / 32) * sizeof(__half)));
+    const bool kq = is_kquant(quant);  // K-quants have the per-token product only: no layout for the batched GEMM
+    if (!kq) {
+        FORGE_CUDA(cudaMalloc(&pk->soa.qs, size_t(N) * pk->soa.qs_row_bytes()));
+        FORGE_CUDA(cudaMalloc(&pk->soa.d, size_t(N) * (K / 32) * sizeof(__half)));
+    }
     FORGE_CUDA(cudaMalloc(&pk->tiled.data, qtiled_bytes(quant, K, N, pk->tiled.bt)));
     FORGE_CUDA(cudaMalloc(&pk->err, sizeof(int)));
     FORGE_CUDA(cudaMemsetAsync(pk->err, 0, sizeof(int), st));
-    FORGE_TRY(pack_rows(w, quant, K, 0, N, 0, K / 32, pk->soa, 0, 1, st));
+    if (!kq) FORGE_TRY(pack_rows(w, quant, K, 0, N, 0, K / 32, pk->soa, 0, 1, st));
     if (pk->tiled.bands * 16 * pk->tiled.bt <= kGemvSplitRows) {
         FORGE_CUDA(cudaMalloc(&pk->split.scratch, sizeof(float) * kGemvMaxSlices * size_t(pk->tiled.bands) * 16 * pk->tiled.bt));
         FORGE_CUDA(cudaMalloc(&pk->split.tickets, sizeof(int) * size_t(pk->tiled.bands) * pk->tiled.bt));
@@ -53,7 +62,7 @@ int32_t packed_build(int quant, const uint8_t* w, int K, int N, cudaStream_t st,
         pk->split.max_slices = kGemvMaxSlices;
     }
     std::vector<const uint8_t*> rows(size_t(pk->tiled.bands) * 16 * pk->tiled.bt, nullptr);
-    for (int r = 0; r < N; ++r) rows[r] = w + size_t(r) * (K / 32) * BS;
+    for (int r = 0; r < N; ++r) rows[r] = w + size_t(r) * raw_row_bytes(quant, K);
     const uint8_t** tab = nullptr;
     FORGE_CUDA(cudaMalloc(&tab, rows.size() * sizeof(uint8_t*)));
     cudaError_t e = cudaMemcpyAsync(tab, rows.data(), rows.size() * sizeof(uint8_t*), cudaMemcpyHostToDevice, st);
@@ -72,7 +81,7 @@ void packed_free(ForgePacked* pk) {
 
 int32_t matmul_packed(float* out, int32_t m, const float* in, const ForgePacked* pk, cudaStream_t st, bool check_err) {
     const int K = pk->soa.K;
-    if (m < FORGE_PREFILL_BATCH_THRESHOLD) {  // per-token path: the streaming GEMV, f32-exact up to summation order
+    if (m < FORGE_PREFILL_BATCH_THRESHOLD || is_kquant(pk->soa.quant)) {  // per-token path: the streaming GEMV, f32-exact up to summation order
         GemvArgs ga;
         ga.x = in; ga.out = out; ga.batch = m;
         FORGE_TRY(gemv_tc(pk->tiled, EPI_STORE, ga, pk->split, pk->err, st));
@@ -94,7 +103,7 @@ int32_t matmul_packed(float* out, int32_t m, const float* in, const ForgePacked*
 int32_t matmul_mat(int quant, float* out, int32_t m, const float* in, const uint8_t* w, int32_t K, int32_t N, void* stream) {
     FORGE_TRY(need_device());
     if (!out || !in || !w || m < 0 || K <= 0 || N <= 0) { set_error("bad argument to forge_matmul_mat"); return FORGE_ERR_INVALID_ARG; }
-    if (K % 32) { set_error("K=%d must be a multiple of 32", K); return FORGE_ERR_SHAPE; }
+    if (K % (is_kquant(quant) ? 256 : 32)) { set_error("K=%d must be a multiple of %d", K, is_kquant(quant) ? 256 : 32); return FORGE_ERR_SHAPE; }
     if (m == 0) return FORGE_OK;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     ForgePacked* pk = new ForgePacked();
@@ -116,12 +125,19 @@ int32_t forge_matmul_mat_q4_0(float* out, int32_t m, const float* in, const uint
     return matmul_mat(FORGE_Q4_0, out, m, in, w, K, N, stream);
 }
 
+int32_t forge_matmul_vec_q4_k(float* out, int32_t m, const float* in, const uint8_t* w, int32_t K, int32_t N, void* stream) {
+    return matmul_mat(FORGE_Q4_K, out, m, in, w, K, N, stream);
+}
+int32_t forge_matmul_vec_q6_k(float* out, int32_t m, const float* in, const uint8_t* w, int32_t K, int32_t N, void* stream) {
+    return matmul_mat(FORGE_Q6_K, out, m, in, w, K, N, stream);
+}
+
 int32_t forge_packed_create(int32_t quant, const uint8_t* w, int32_t K, int32_t N, void* stream, ForgePacked** out) {
     FORGE_TRY(need_device());
     if (!out) { set_error("null out pointer"); return FORGE_ERR_INVALID_ARG; }
     *out = nullptr;
-    if (!w || K <= 0 || N <= 0 || (quant != FORGE_Q8_0 && quant != FORGE_Q4_0)) { set_error("bad argument to forge_packed_create"); return FORGE_ERR_INVALID_ARG; }
-    if (K % 32) { set_error("K=%d must be a multiple of 32", K); return FORGE_ERR_SHAPE; }
+    if (!w || K <= 0 || N <= 0 || (quant != FORGE_Q8_0 && quant != FORGE_Q4_0 && !is_kquant(quant))) { set_error("bad argument to forge_packed_create"); return FORGE_ERR_INVALID_ARG; }
+    if (K % (is_kquant(quant) ? 256 : 32)) { set_error("K=%d must be a multiple of %d", K, is_kquant(quant) ? 256 : 32); return FORGE_ERR_SHAPE; }
     ForgePacked* pk = new ForgePacked();
     int32_t rc = packed_build(quant, w, K, N, static_cast<cudaStream_t>(stream), pk);
     if (rc != FORGE_OK) { packed_free(pk); return rc; }

@@ -23,10 +23,17 @@ constexpr int kStages = 8;
 constexpr int kMaxKB = 352;                          // K <= 11264
 constexpr uint32_t kSpinLimit = 1u << 24;
 
+// K-quants (256-element super-blocks) are re-tiled at load time into the same 16-row x 32-column tiles with the
+// super-block fields expanded per tile, so the tile loop stays one MMA per tile:
+//   Q4_K: 8 x float4 {d*sc[g], dmin*m[g], d*sc[g+8] / 16, dmin*m[g+8]} + nibbles as for Q4_0 (unsigned)   = 384 bytes
+//   Q6_K: 8 x float4 {d*sc_lo[g], d*sc_hi[g], d*sc_lo[g+8], d*sc_hi[g+8]} + (q6 - 32) as int8, Q8_0 order = 640 bytes
+// (all products of an f16 and a small integer: exact in f32).
+inline bool is_kquant(int quant) { return quant == FORGE_Q4_K || quant == FORGE_Q6_K; }  // host side
+template <int QUANT> struct KQuant { static constexpr bool value = QUANT == FORGE_Q4_K || QUANT == FORGE_Q6_K; };
 template <int QUANT> struct Tile {
-    static constexpr int BYTES = (QUANT == FORGE_Q4_0) ? 288 : 544;
+    static constexpr int BYTES = QUANT == FORGE_Q4_0 ? 288 : QUANT == FORGE_Q8_0 ? 544 : QUANT == FORGE_Q4_K ? 384 : 640;
     static constexpr int CHUNK_KB = (QUANT == FORGE_Q4_0) ? 8 : 4;          // k-blocks per pipeline stage
-    static constexpr int STAGE_BYTES = BYTES * CHUNK_KB * kBandTiles;       // 18432 / 17408
+    static constexpr int STAGE_BYTES = BYTES * CHUNK_KB * kBandTiles;       // 18432 / 17408 / 12288 / 20480
 };
 
 // ------------------------------------------------------------------ PTX helpers
@@ -256,6 +263,54 @@ __device__ __forceinline__ float stage_finish(uint2* xf, int4* xoff, Shared& sh,
 #pragma unroll
     for (int w = 0; w < kConsumerWarps; ++w) { s2 += sh.part[w]; m2 = fmaxf(m2, sh.part[16 + w]); }
     const float inv = norm_w ? 1.0f / sqrtf(s2 / float(K) + eps) : 1.0f;
+    if (KQuant<QUANT>::value) {
+        // K-quant products take the row quantised to Q8_0 blocks, as the functions they replace do
+        // (emit.rs:1412-1440): scale = absmax / 127 kept as f16 (1 for a zero block), q = round-half-away(x / scale)
+        // in [-127, 127].  A k-block's 128-byte slot then holds {4 x uint2 B fragments (column 0), f32 scale,
+        // f32 sum of q}; the dots are exact integers and the scale is applied per block.
+        for (int i0 = 0; i0 < KB * 4; i0 += kCT) {
+            const int i = i0 + tid;
+            const bool on = i < KB * 4;
+            const int kbi = i >> 2, tt = i & 3;
+            float xv[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            if (on) {
+                const float4 r0 = *reinterpret_cast<const float4*>(xraw + kbi * 32 + 4 * tt);
+                const float4 r1 = *reinterpret_cast<const float4*>(xraw + kbi * 32 + 16 + 4 * tt);
+                xv[0] = r0.x; xv[1] = r0.y; xv[2] = r0.z; xv[3] = r0.w; xv[4] = r1.x; xv[5] = r1.y; xv[6] = r1.z; xv[7] = r1.w;
+                if (norm_w) {
+                    const float4 n0 = *reinterpret_cast<const float4*>(norm_w + kbi * 32 + 4 * tt);
+                    const float4 n1 = *reinterpret_cast<const float4*>(norm_w + kbi * 32 + 16 + 4 * tt);
+                    const float nw[8] = {n0.x, n0.y, n0.z, n0.w, n1.x, n1.y, n1.z, n1.w};
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) xv[q] = xv[q] * inv * nw[q];
+                }
+            }
+            float amax = 0.f;
+#pragma unroll
+            for (int q = 0; q < 8; ++q) amax = fmaxf(amax, fabsf(xv[q]));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+            float bs = 1.0f, binv = 0.0f;
+            if (amax != 0.f) { bs = __fdiv_rn(amax, 127.0f); binv = __fdiv_rn(1.0f, bs); }
+            int qv[8], qsum = 0;
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                qv[q] = int(fminf(127.f, fmaxf(-127.f, roundf(xv[q] * binv))));
+                qsum += qv[q];
+            }
+            qsum += __shfl_xor_sync(0xffffffffu, qsum, 1);
+            qsum += __shfl_xor_sync(0xffffffffu, qsum, 2);
+            __syncwarp();  // all four readers of a k-block are done before it is overwritten
+            if (on) {
+                const uint32_t w0 = uint32_t(qv[0] & 255) | (uint32_t(qv[1] & 255) << 8) | (uint32_t(qv[2] & 255) << 16) | (uint32_t(qv[3] & 255) << 24);
+                const uint32_t w1 = uint32_t(qv[4] & 255) | (uint32_t(qv[5] & 255) << 8) | (uint32_t(qv[6] & 255) << 16) | (uint32_t(qv[7] & 255) << 24);
+                xf[kbi * 16 + tt] = make_uint2(w0, w1);
+                if (tt == 0) *reinterpret_cast<float2*>(xraw + kbi * 32 + 8) = make_float2(bs < 5.9604644775390625e-8f ? 0.f : __half2float(__float2half_rn(bs)), float(qsum));  // the reference's f16 conversion flushes below 2^-24
+            }
+        }
+        csync();
+        return 1.0f;
+    }
     m2 *= inv;
     // exact power-of-two scale that puts max|x| * 2^s in [2^29, 2^30): 31-bit signed fixed point
     float sc = 1.0f;
@@ -449,6 +504,31 @@ __device__ __forceinline__ void consume_phase(const Phase& ph, Shared& sh, const
             const unsigned char* base = ring + size_t(st) * T::STAGE_BYTES + size_t(r8) * T::BYTES;
             auto tile = [&](int j) {  // k-block kb0 + j of this warp's row tile
                 const unsigned char* tp = base + size_t(j) * (bt * T::BYTES);
+                if (KQuant<QUANT>::value) {
+                    // one int8 B column (the Q8_0 row); C columns 0 / 1 of lanes t == 0 carry the sums
+                    const uint2 bx = xf[(kb0 + j) * 16 + t];
+                    const float2 xs = *reinterpret_cast<const float2*>(reinterpret_cast<const float*>(xf) + (kb0 + j) * 32 + 8);
+                    const float4 sc = *reinterpret_cast<const float4*>(tp + g * 16);
+                    int cf[4] = {0, 0, 0, 0};
+                    uint32_t a[4];
+                    if (QUANT == FORGE_Q4_K) {
+                        const uint2 wq = *reinterpret_cast<const uint2*>(tp + 128 + lane * 8);
+                        a[0] = wq.x & 0x0F0F0F0Fu; a[1] = wq.x & 0xF0F0F0F0u;
+                        a[2] = wq.y & 0x0F0F0F0Fu; a[3] = wq.y & 0xF0F0F0F0u;
+                        imma16832_u8(cf, a, bx.x, bx.y);
+                        // x_scale * (d*sc * dot - dmin*m * sum(q)); rows g+8 entered as 16 q, their scale as d*sc / 16
+                        acc[0] += xs.x * (sc.x * float(cf[0]) - sc.y * xs.y);
+                        acc[2] += xs.x * (sc.z * float(cf[2]) - sc.w * xs.y);
+                    } else {
+                        // column 0 sees k 0..15 only, column 1 k 16..31 only: the two 16-element scale groups
+                        const uint4 wq = *reinterpret_cast<const uint4*>(tp + 128 + lane * 16);
+                        a[0] = wq.x; a[1] = wq.y; a[2] = wq.z; a[3] = wq.w;
+                        imma16832_s8(cf, a, (g & 1) ? 0u : bx.x, (g & 1) ? bx.y : 0u);
+                        acc[0] += xs.x * (sc.x * float(cf[0]) + sc.y * float(cf[1]));
+                        acc[2] += xs.x * (sc.z * float(cf[2]) + sc.w * float(cf[3]));
+                    }
+                    return;
+                }
                 // B fragment: digit column (g & 3); lanes g >= 4 duplicate columns whose results are never read
                 const uint2 bx = xf[((kb0 + j) * 4 + (g & 3)) * 4 + t];
                 const float2 d = __half22float2(*reinterpret_cast<const __half2*>(tp + g * 4));
@@ -483,6 +563,10 @@ __device__ __forceinline__ void consume_phase(const Phase& ph, Shared& sh, const
         const float wgt = (t == 0) ? 1.0f : 65536.0f;  // lane 0: digits 0,1; lane 1: digits 2,3 (base 256)
         const float w1 = (QUANT == FORGE_Q4_0) ? wgt * 0.0625f : wgt;  // Q4_0 rows g+8 were carried as 16 n
         float v0 = (acc[0] + 256.0f * acc[1]) * wgt, v1 = (acc[2] + 256.0f * acc[3]) * w1;
+        if (KQuant<QUANT>::value) {
+            v0 = t == 0 ? acc[0] : 0.f;  // the other quad lanes hold MMA columns nobody asked for
+            v1 = t == 0 ? acc[2] : 0.f;
+        }
         v0 += __shfl_xor_sync(0xffffffffu, v0, 1);
         v1 += __shfl_xor_sync(0xffffffffu, v1, 1);
         if (bt == kBandTiles) {

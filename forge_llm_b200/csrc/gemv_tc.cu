@@ -37,6 +37,13 @@
 // exactly the 34 / 18 bytes per block of the GGUF stream.  Tiles are ordered
 // [128-row band][k-block][row tile within band], so a chunk (a run of k-blocks of one band) is
 // one contiguous, 16-byte aligned bulk copy.
+//
+// K-quants (matmul_vec_q4_k_KxN / matmul_vec_q6_k_KxN, emit.rs:3411-3487 and :3636-3652) run through the same
+// kernel: their 256-element super-blocks are re-tiled at load time into 16 x 32 tiles that carry the block's own
+// f32 scale fields (see Tile in gemv_core.cuh), and the activation is staged as the Q8_0 blocks those functions
+// quantise their input to (one int8 B column instead of four digit columns), so the integer dots are the
+// reference's own.  Q6_K's two 16-element scale groups per block come out of ONE MMA: B column 0 holds k 0..15
+// only and column 1 holds k 16..31 only.
 #include <algorithm>
 #include <cstdlib>
 
@@ -107,6 +114,44 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tc_kernel(TcParams p) {
 // ------------------------------------------------------------------ packing
 // thread per (tile, lane): gathers the lane's A-fragment bytes from the two raw GGUF rows it owns
 // (rows g and g+8 of the 16-row tile; k = 4t..4t+3 and 16+4t..16+4t+3 of the block)
+__device__ __forceinline__ float f16_at(const uint8_t* p) { return __half2float(__ushort_as_half(uint16_t(p[0] | (p[1] << 8)))); }
+
+// One 32-element block (k-block kb of the row) of a raw K-quant row, as the fields the tile needs.
+// Q4_K (emit.rs:3013-3021, :3246-3303): sub-block j = kb % 8 of super-block kb / 8; s = d * sc_j, mn = dmin * m_j;
+// element k is the low (j even) or high (j odd) nibble of qs[(j / 2) * 32 + k].
+struct KBlock4 { float s = 0.f, mn = 0.f; const uint8_t* qs = nullptr; int shift = 0; };
+__device__ __forceinline__ KBlock4 kblock_q4_k(const uint8_t* row, int kb) {
+    KBlock4 b;
+    if (!row) return b;
+    const uint8_t* sb = row + size_t(kb >> 3) * 144;
+    const int j = kb & 7;
+    const uint8_t* sc = sb + 4;
+    int s6, m6;
+    if (j < 4) { s6 = sc[j] & 63; m6 = sc[j + 4] & 63; }
+    else { s6 = (sc[j + 4] & 0x0F) | ((sc[j - 4] >> 6) << 4); m6 = (sc[j + 4] >> 4) | ((sc[j] >> 6) << 4); }
+    b.s = f16_at(sb) * float(s6);
+    b.mn = f16_at(sb + 2) * float(m6);
+    b.qs = sb + 16 + (j >> 1) * 32;
+    b.shift = (j & 1) * 4;
+    return b;
+}
+// Q6_K (emit.rs:3560-3607): block j = kb % 8 reads ql[ql_off + l] >> nib and qh[qh_off + l] >> hsh; scale groups 2j, 2j+1.
+struct KBlock6 { float s_lo = 0.f, s_hi = 0.f; const uint8_t* ql = nullptr; const uint8_t* qh = nullptr; int nib = 0, hsh = 0; };
+__device__ __forceinline__ KBlock6 kblock_q6_k(const uint8_t* row, int kb) {
+    KBlock6 b;
+    if (!row) return b;
+    const uint8_t* sb = row + size_t(kb >> 3) * 210;
+    const int j = kb & 7;
+    const float d = f16_at(sb + 208);
+    b.s_lo = d * float(int(int8_t(sb[192 + 2 * j])));
+    b.s_hi = d * float(int(int8_t(sb[192 + 2 * j + 1])));
+    b.ql = sb + (j >> 2) * 64 + (j & 1) * 32;
+    b.qh = sb + 128 + (j >> 2) * 32;
+    b.nib = ((j >> 1) & 1) * 4;
+    b.hsh = (j & 3) * 2;
+    return b;
+}
+
 template <int QUANT>
 __global__ void tile_pack_kernel(const uint8_t* const* __restrict__ row_src, int KB, int bands, int bt, uint8_t* __restrict__ dst) {
     constexpr int BS = QUANT == FORGE_Q8_0 ? 34 : 18;
@@ -121,6 +166,43 @@ __global__ void tile_pack_kernel(const uint8_t* const* __restrict__ row_src, int
         const int g = lane >> 2, t = lane & 3;
         const uint8_t* r0 = row_src[rt * 16 + g];
         const uint8_t* r1 = row_src[rt * 16 + g + 8];
+        if (QUANT == FORGE_Q4_K) {
+            uint8_t* tp = dst + size_t(tile) * T::BYTES;
+            const KBlock4 b0 = kblock_q4_k(r0, kb), b1 = kblock_q4_k(r1, kb);
+            if (t == 0) *reinterpret_cast<float4*>(tp + g * 16) = make_float4(b0.s, b0.mn, b1.s * 0.0625f, b1.mn);
+            uint32_t w[2] = {0u, 0u};
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int k = h * 16 + 4 * t + j;  // byte j: low nibble = row g, high nibble = row g+8
+                    const uint32_t q0 = b0.qs ? (b0.qs[k] >> b0.shift) & 15u : 0u, q1 = b1.qs ? (b1.qs[k] >> b1.shift) & 15u : 0u;
+                    w[h] |= (q0 | (q1 << 4)) << (8 * j);
+                }
+            *reinterpret_cast<uint2*>(tp + 128 + lane * 8) = make_uint2(w[0], w[1]);
+            continue;
+        }
+        if (QUANT == FORGE_Q6_K) {
+            uint8_t* tp = dst + size_t(tile) * T::BYTES;
+            const KBlock6 b0 = kblock_q6_k(r0, kb), b1 = kblock_q6_k(r1, kb);
+            if (t == 0) *reinterpret_cast<float4*>(tp + g * 16) = make_float4(b0.s_lo, b0.s_hi, b1.s_lo, b1.s_hi);
+            auto q6 = [](const KBlock6& b, int l) -> uint32_t {
+                if (!b.ql) return 0u;
+                const int v = int(((b.ql[l] >> b.nib) & 0x0F) | (((b.qh[l] >> b.hsh) & 3) << 4)) - 32;
+                return uint32_t(v) & 255u;
+            };
+            uint32_t w[4] = {0u, 0u, 0u, 0u};  // a0: row g, k lo; a1: row g+8, k lo; a2: row g, k hi; a3: row g+8, k hi
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int k = h * 16 + 4 * t + j;
+                    w[2 * h] |= q6(b0, k) << (8 * j);
+                    w[2 * h + 1] |= q6(b1, k) << (8 * j);
+                }
+            *reinterpret_cast<uint4*>(tp + 128 + lane * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+            continue;
+        }
         const uint8_t* b0 = r0 ? r0 + size_t(kb) * BS : nullptr;
         const uint8_t* b1 = r1 ? r1 + size_t(kb) * BS : nullptr;
         uint8_t* tp = dst + size_t(tile) * T::BYTES;
@@ -175,8 +257,8 @@ int32_t launch(const QTiled& w, GemvEpilogue epi, const GemvArgs& a, const GemvS
     const int grid = ph.units < sms ? ph.units : sms;
     // one limit for every launch of this kernel: a launch replayed later (a graph node re-issued by a profiler) must
     // not find a smaller limit left behind by another matrix
-    const bool tp = a.tp.consume || epi == EPI_TP_PUSH;
-    auto kern = tp ? gemv_tc_kernel<QUANT, true> : gemv_tc_kernel<QUANT, false>;
+    const bool tp = !KQuant<QUANT>::value && (a.tp.consume || epi == EPI_TP_PUSH);
+    auto kern = tp ? gemv_tc_kernel<QUANT, !KQuant<QUANT>::value> : gemv_tc_kernel<QUANT, false>;
     FORGE_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(dyn_smem_bytes<QUANT>(kMaxKB))));
     FORGE_CUDA(launch_pdl(kern, dim3(grid), dim3(kThreads), smem, st, p));
     FORGE_LAUNCH_CHECK();
@@ -210,7 +292,8 @@ int gemv_band_tiles(int N, int sms) {
 
 size_t qtiled_bytes(int quant, int K, int N, int bt) {
     const size_t bands = size_t((N + 16 * bt - 1) / (16 * bt));
-    return bands * bt * size_t(K / 32) * (quant == FORGE_Q4_0 ? 288 : 544);
+    const size_t tile = quant == FORGE_Q4_0 ? 288 : quant == FORGE_Q8_0 ? 544 : quant == FORGE_Q4_K ? 384 : 640;
+    return bands * bt * size_t(K / 32) * tile;
 }
 
 int32_t tile_pack(const uint8_t* const* row_src_dev, QTiled& dst, cudaStream_t st) {
@@ -218,7 +301,9 @@ int32_t tile_pack(const uint8_t* const* row_src_dev, QTiled& dst, cudaStream_t s
     if (total == 0) return FORGE_OK;
     const int grid = int((total + 255) / 256 < 148 * 32 ? (total + 255) / 256 : 148 * 32);
     if (dst.quant == FORGE_Q8_0) tile_pack_kernel<FORGE_Q8_0><<<grid, 256, 0, st>>>(row_src_dev, dst.K / 32, dst.bands, dst.bt, dst.data);
-    else tile_pack_kernel<FORGE_Q4_0><<<grid, 256, 0, st>>>(row_src_dev, dst.K / 32, dst.bands, dst.bt, dst.data);
+    else if (dst.quant == FORGE_Q4_0) tile_pack_kernel<FORGE_Q4_0><<<grid, 256, 0, st>>>(row_src_dev, dst.K / 32, dst.bands, dst.bt, dst.data);
+    else if (dst.quant == FORGE_Q4_K) tile_pack_kernel<FORGE_Q4_K><<<grid, 256, 0, st>>>(row_src_dev, dst.K / 32, dst.bands, dst.bt, dst.data);
+    else tile_pack_kernel<FORGE_Q6_K><<<grid, 256, 0, st>>>(row_src_dev, dst.K / 32, dst.bands, dst.bt, dst.data);
     FORGE_LAUNCH_CHECK();
     return FORGE_OK;
 }
@@ -226,6 +311,11 @@ int32_t tile_pack(const uint8_t* const* row_src_dev, QTiled& dst, cudaStream_t s
 int32_t gemv_tc(const QTiled& w, GemvEpilogue epi, const GemvArgs& a, const GemvSplit& sp, int* err, cudaStream_t st) {
     if (w.K % 32 != 0 || w.K <= 0 || w.N <= 0) { set_error("gemv: K=%d must be a positive multiple of 32", w.K); return FORGE_ERR_SHAPE; }
     if ((epi == EPI_SILU || epi == EPI_QKV) && (w.N % 2)) { set_error("gemv: paired epilogue needs even N"); return FORGE_ERR_SHAPE; }
+    if (core::is_kquant(w.quant)) {
+        if (w.K % 256) { set_error("gemv: K=%d must be a multiple of 256 for K-quants", w.K); return FORGE_ERR_SHAPE; }
+        if (a.tp.consume || epi == EPI_TP_PUSH) { set_error("gemv: K-quants take no part in the tensor-parallel sums"); return FORGE_ERR_UNSUPPORTED; }
+        return w.quant == FORGE_Q4_K ? launch<FORGE_Q4_K>(w, epi, a, sp, err, st) : launch<FORGE_Q6_K>(w, epi, a, sp, err, st);
+    }
     return w.quant == FORGE_Q8_0 ? launch<FORGE_Q8_0>(w, epi, a, sp, err, st) : launch<FORGE_Q4_0>(w, epi, a, sp, err, st);
 }
 

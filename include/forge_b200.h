@@ -43,6 +43,12 @@ typedef enum ForgeStatus {
 #define FORGE_Q8_0 8 /* GGUF Q8_0: 34-byte blocks {f16 d; int8 q[32]}        (E:1266-1268, WL:860-888) */
 #define FORGE_Q4_0 4 /* GGUF Q4_0: 18-byte blocks {f16 d; u8 qs[16]}, value = nibble-8,
                         byte j = element j (low) and j+16 (high)          (E:2337-2359, WL:893-926) */
+/* K-quants (256-element super-blocks; the numbers are the GGML type ids).  Operator level only:
+ * forge_matmul_vec_q4_k / forge_matmul_vec_q6_k and forge_packed_create; the model session takes Q8_0 / Q4_0. */
+#define FORGE_Q4_K 12 /* 144 bytes {f16 d; f16 dmin; u8 scales[12]; u8 qs[128]},
+                         value = d*sc[j]*q - dmin*m[j] per 32-element sub-block j   (E:2962-2969, WL:1146-1200) */
+#define FORGE_Q6_K 14 /* 210 bytes {u8 ql[128]; u8 qh[64]; i8 scales[16]; f16 d},
+                         value = d*scales[i/16]*(q6-32)                             (E:3542-3546, WL:997-1060) */
 
 #define FORGE_PREFILL_BATCH_THRESHOLD 8 /* E:203-206 */
 #define FORGE_KV_PAGE 64                /* positions per KV page (= FLASH_ATTN_BLOCK_SIZE, E:199-202) */
@@ -88,6 +94,16 @@ int32_t forge_matmul_mat_q8_0(float* out, int32_t m, const float* in, const uint
                               int32_t K, int32_t N, void* stream);
 /* matmul_vec_q4_0_{K}x{N} E:2910-2953 (dot_q4_0 E:2337-2359); matmul_mat_q4_0_{K}x{N} E:3792-3813 */
 int32_t forge_matmul_mat_q4_0(float* out, int32_t m, const float* in, const uint8_t* w,
+                              int32_t K, int32_t N, void* stream);
+
+/* matmul_vec_q4_k_{K}x{N}(output, input, weight)  E:3411-3487 (dot_q4_k_q8_0 E:3246-3303)
+ * matmul_vec_q6_k_{K}x{N}(output, input, weight)  E:3636-3652 (dot_q6_k_q8_0 E:3553-3611)
+ *   applied to each of the m rows of `in` (the generated module has no batched K-quant product).  As there, every
+ *   input row is first quantised to Q8_0 blocks (E:1412-1440) and the block dots are exact integers.
+ *   out f32 [m][N], in f32 [m][K], w u8 [N][K/256][144 or 210]; K must be a multiple of 256. */
+int32_t forge_matmul_vec_q4_k(float* out, int32_t m, const float* in, const uint8_t* w,
+                              int32_t K, int32_t N, void* stream);
+int32_t forge_matmul_vec_q6_k(float* out, int32_t m, const float* in, const uint8_t* w,
                               int32_t K, int32_t N, void* stream);
 
 /* The same products on a weight repacked once: forge_packed_create converts raw GGUF blocks

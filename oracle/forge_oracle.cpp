@@ -231,6 +231,145 @@ void matmul_mat(int quant, float* out, int m, const float* in, const uint8_t* w,
     }
 }
 
+// ---------------------------------------------------------------- K-quants (per-token products only)
+// The generated module has no batched K-quant product: every matmul_vec_q4_k / matmul_vec_q6_k call first
+// quantises its input row to Q8_0 blocks (E:3413-3416, E:3636-3640) and then takes one integer dot per
+// output row against the 256-element super-blocks.
+
+// E:1412-1440 (also WL `quantize_f32_to_q8_0`): per 32 values, scale = absmax / 127 stored as f16 (1.0 for an
+// all-zero block), q = round-half-away(x * (1 / scale)) clamped to [-127, 127].  Returns the scales as the f32
+// values the dots read back from the f16 bits.
+void quantize_act_q8_0(const float* in, int k, int8_t* q, float* scale) {
+    int nb = (k + 31) / 32;
+    for (int b = 0; b < nb; ++b) {
+        int lim = std::min(32, k - b * 32);
+        float absmax = 0.0f;
+        for (int j = 0; j < lim; ++j) absmax = std::max(absmax, std::fabs(in[b * 32 + j]));
+        float s = 1.0f, inv = 0.0f;
+        if (absmax != 0.0f) { s = absmax / 127.0f; inv = 1.0f / s; }
+        scale[b] = f16_bits_to_f32(f32_to_f16_bits(s));
+        for (int j = 0; j < 32; ++j) {
+            float v = j < lim ? rround(in[b * 32 + j] * inv) : 0.0f;
+            q[b * 32 + j] = int8_t(std::min(127.0f, std::max(-127.0f, v)));
+        }
+    }
+}
+
+// E:3013-3021: the 6-bit (scale, min) pair of sub-block j from the 12 packed bytes.
+inline void scale_min_k4(int j, const uint8_t* sc, int& s, int& m) {
+    if (j < 4) { s = sc[j] & 63; m = sc[j + 4] & 63; }
+    else { s = (sc[j + 4] & 0x0F) | ((sc[j - 4] >> 6) << 4); m = (sc[j + 4] >> 4) | ((sc[j] >> 6) << 4); }
+}
+
+// E:3246-3303: Q4_K super-block = {f16 d, f16 dmin, 12 scale bytes, 128 nibble bytes}; 64-element chunk c holds
+// sub-block 2c in the low nibbles and 2c+1 in the high nibbles of qs[32c .. 32c+31].
+float dot_q4_k_q8_0(const uint8_t* row, const int8_t* xq, const float* xs, int k) {
+    float acc = 0.0f;
+    for (int sb = 0; sb < k / 256; ++sb) {
+        const uint8_t* blk = row + size_t(sb) * 144;
+        float d = f16_bits_to_f32(uint16_t(blk[0] | (blk[1] << 8)));
+        float dmin = f16_bits_to_f32(uint16_t(blk[2] | (blk[3] << 8)));
+        const uint8_t* qs = blk + 16;
+        for (int chunk = 0; chunk < 4; ++chunk) {
+            for (int half = 0; half < 2; ++half) {
+                int is = chunk * 2 + half, sc, mn;
+                scale_min_k4(is, blk + 4, sc, mn);
+                float dw = d * float(sc), mw = dmin * float(mn);
+                const int8_t* x = xq + (size_t(sb) * 8 + is) * 32;
+                int dot = 0, sum = 0;
+                for (int i = 0; i < 32; ++i) {
+                    int q4 = half ? (qs[chunk * 32 + i] >> 4) : (qs[chunk * 32 + i] & 0x0F);
+                    dot += int(x[i]) * q4;
+                    sum += int(x[i]);
+                }
+                acc += xs[sb * 8 + is] * (dw * float(dot) - mw * float(sum));
+            }
+        }
+    }
+    return acc;
+}
+
+// E:3553-3611: Q6_K super-block = {128 low-nibble bytes, 64 two-bit bytes, 16 int8 scales, f16 d}; the eight
+// 32-element input blocks address it through the table below (two 16-element scale groups per block).
+float dot_q6_k_q8_0(const uint8_t* row, const int8_t* xq, const float* xs, int k) {
+    static const int tab[8][5] = {{0, 0, 0, 0, 0}, {32, 0, 0, 2, 2}, {0, 0, 4, 4, 4}, {32, 0, 4, 6, 6},
+                                  {64, 32, 0, 0, 8}, {96, 32, 0, 2, 10}, {64, 32, 4, 4, 12}, {96, 32, 4, 6, 14}};
+    float acc = 0.0f;
+    for (int sb = 0; sb < k / 256; ++sb) {
+        const uint8_t* blk = row + size_t(sb) * 210;
+        const uint8_t *ql = blk, *qh = blk + 128, *sc = blk + 192;
+        float d = f16_bits_to_f32(uint16_t(blk[208] | (blk[209] << 8)));
+        for (int b = 0; b < 8; ++b) {
+            const int8_t* x = xq + (size_t(sb) * 8 + b) * 32;
+            int dots[2] = {0, 0};
+            for (int l = 0; l < 32; ++l) {
+                int q6 = int((ql[tab[b][0] + l] >> tab[b][2]) & 0x0F) | (int((qh[tab[b][1] + l] >> tab[b][3]) & 3) << 4);
+                dots[l >> 4] += (q6 - 32) * int(x[l]);
+            }
+            float slo = float(int(int8_t(sc[tab[b][4]]))), shi = float(int(int8_t(sc[tab[b][4] + 1])));
+            acc += d * xs[sb * 8 + b] * (slo * float(dots[0]) + shi * float(dots[1]));
+        }
+    }
+    return acc;
+}
+
+inline size_t kquant_row_bytes(int quant, int k) { return size_t(k / 256) * (quant == 12 ? 144 : 210); }
+
+// E:3411-3487 (Q4_K) / E:3636-3652 (Q6_K); quant: 12 = Q4_K, 14 = Q6_K (the GGML type numbers)
+void matmul_vec_kquant(int quant, float* out, const float* in, const uint8_t* w, int k, int n) {
+    std::vector<int8_t> xq((size_t(k) + 31) / 32 * 32);
+    std::vector<float> xs((size_t(k) + 31) / 32);
+    quantize_act_q8_0(in, k, xq.data(), xs.data());
+    size_t rb = kquant_row_bytes(quant, k);
+#pragma omp parallel for schedule(static) if (size_t(n) * rb > 1000000)
+    for (int j = 0; j < n; ++j)
+        out[j] = quant == 12 ? dot_q4_k_q8_0(w + size_t(j) * rb, xq.data(), xs.data(), k)
+                             : dot_q6_k_q8_0(w + size_t(j) * rb, xq.data(), xs.data(), k);
+}
+
+// WL:1146-1200: value = d * sc * q - dmin * m
+void dequant_q4_k(const uint8_t* in, size_t n, float* out) {
+    for (size_t sb = 0; sb * 256 < n; ++sb) {
+        const uint8_t* blk = in + sb * 144;
+        float d = f16_bits_to_f32(uint16_t(blk[0] | (blk[1] << 8)));
+        float dmin = f16_bits_to_f32(uint16_t(blk[2] | (blk[3] << 8)));
+        for (int is = 0; is < 8; ++is) {
+            int sc, mn;
+            scale_min_k4(is, blk + 4, sc, mn);
+            float dw = d * float(sc), mw = dmin * float(mn);
+            for (int l = 0; l < 32; ++l) {
+                size_t o = sb * 256 + size_t(is) * 32 + l;
+                uint8_t by = blk[16 + (is >> 1) * 32 + l];
+                if (o < n) out[o] = dw * float((is & 1) ? (by >> 4) : (by & 0x0F)) - mw;
+            }
+        }
+    }
+}
+
+// WL:997-1060: value = d * scale[group of 16] * (q6 - 32)
+void dequant_q6_k(const uint8_t* in, size_t n, float* out) {
+    for (size_t sb = 0; sb * 256 < n; ++sb) {
+        const uint8_t* blk = in + sb * 210;
+        const uint8_t *ql = blk, *qh = blk + 128;
+        const int8_t* sc = reinterpret_cast<const int8_t*>(blk + 192);
+        float d = f16_bits_to_f32(uint16_t(blk[208] | (blk[209] << 8)));
+        for (int half = 0; half < 2; ++half)
+            for (int l = 0; l < 32; ++l) {
+                int is = l / 16;
+                const uint8_t* q = ql + half * 64;
+                uint8_t h = qh[half * 32 + l];
+                int q1 = int((q[l] & 0x0F) | (((h >> 0) & 3) << 4)) - 32, q2 = int((q[l + 32] & 0x0F) | (((h >> 2) & 3) << 4)) - 32;
+                int q3 = int((q[l] >> 4) | (((h >> 4) & 3) << 4)) - 32, q4 = int((q[l + 32] >> 4) | (((h >> 6) & 3) << 4)) - 32;
+                size_t o = sb * 256 + size_t(half) * 128 + l;
+                const int8_t* s = sc + half * 8 + is;
+                if (o < n) out[o] = d * float(s[0]) * float(q1);
+                if (o + 32 < n) out[o + 32] = d * float(s[2]) * float(q2);
+                if (o + 64 < n) out[o + 64] = d * float(s[4]) * float(q3);
+                if (o + 96 < n) out[o + 96] = d * float(s[6]) * float(q4);
+            }
+    }
+}
+
 // ---------------------------------------------------------------- elementwise
 // E:298-304
 inline float dot_f32(const float* a, const float* b, int n) {
@@ -680,6 +819,14 @@ void fo_matmul_vec_q4_0(float* out, const float* in, const uint8_t* w, int k, in
 // fast != 0 picks the row-vectorised twin (bit-identical values)
 void fo_matmul_mat_q8_0(float* out, int m, const float* in, const uint8_t* w, int k, int n, int fast) { matmul_mat(8, out, m, in, w, k, n, fast != 0); }
 void fo_matmul_mat_q4_0(float* out, int m, const float* in, const uint8_t* w, int k, int n, int fast) { matmul_mat(4, out, m, in, w, k, n, fast != 0); }
+
+// K-quants: quant 12 = Q4_K, 14 = Q6_K
+void fo_quantize_act_q8_0(const float* in, int k, int8_t* q, float* scale) { quantize_act_q8_0(in, k, q, scale); }
+void fo_matmul_vec_kquant(int quant, float* out, int m, const float* in, const uint8_t* w, int k, int n) {
+    for (int r = 0; r < m; ++r) matmul_vec_kquant(quant, out + size_t(r) * n, in + size_t(r) * k, w, k, n);
+}
+void fo_dequant_q4_k(const uint8_t* in, size_t n, float* out) { dequant_q4_k(in, n, out); }
+void fo_dequant_q6_k(const uint8_t* in, size_t n, float* out) { dequant_q6_k(in, n, out); }
 
 void fo_rms_norm(float* out, const float* in, const float* w, int n, float eps) { rms_norm(out, in, w, n, eps); }
 void fo_silu_mul(float* out, const float* g, const float* u, int n) { silu_mul(out, g, u, n); }

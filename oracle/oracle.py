@@ -63,6 +63,10 @@ def lib():
         "fo_matmul_vec_q4_0": (None, [_f32p, _f32p, _u8p, i, i]),
         "fo_matmul_mat_q8_0": (None, [_f32p, i, _f32p, _u8p, i, i, i]),
         "fo_matmul_mat_q4_0": (None, [_f32p, i, _f32p, _u8p, i, i, i]),
+        "fo_quantize_act_q8_0": (None, [_f32p, i, np.ctypeslib.ndpointer(np.int8, flags="C_CONTIGUOUS"), _f32p]),
+        "fo_matmul_vec_kquant": (None, [i, _f32p, i, _f32p, _u8p, i, i]),
+        "fo_dequant_q4_k": (None, [_u8p, sz, _f32p]),
+        "fo_dequant_q6_k": (None, [_u8p, sz, _f32p]),
         "fo_rms_norm": (None, [_f32p, _f32p, _f32p, i, f]),
         "fo_silu_mul": (None, [_f32p, _f32p, _f32p, i]),
         "fo_residual_add": (None, [_f32p, _f32p, i]),
@@ -151,6 +155,71 @@ def matmul_vec(quant: int, x: np.ndarray, w: np.ndarray, K: int, N: int) -> np.n
     fn = lib().fo_matmul_vec_q8_0 if quant == 8 else lib().fo_matmul_vec_q4_0
     fn(out, np.ascontiguousarray(x, np.float32), np.ascontiguousarray(w, np.uint8), K, N)
     return out
+
+
+# ---- K-quants (quant 12 = Q4_K, 14 = Q6_K: the GGML type numbers)
+Q4_K, Q6_K = 12, 14
+
+
+def kquant_row_bytes(quant: int, K: int) -> int:
+    return (K // 256) * (144 if quant == Q4_K else 210)
+
+
+def quantize_act_q8_0(x: np.ndarray):
+    """The Q8_0 form every K-quant product gives its input row: (int8 values, f16-rounded block scales)."""
+    x = np.ascontiguousarray(x, np.float32).ravel()
+    q = np.empty(((x.size + 31) // 32) * 32, np.int8)
+    s = np.empty((x.size + 31) // 32, np.float32)
+    lib().fo_quantize_act_q8_0(x, x.size, q, s)
+    return q, s
+
+
+def matmul_vec_kquant(quant: int, x: np.ndarray, w: np.ndarray, K: int, N: int) -> np.ndarray:
+    """matmul_vec_q4_k_KxN / matmul_vec_q6_k_KxN applied to every row of x."""
+    x = np.ascontiguousarray(x, np.float32).reshape(-1, K)
+    out = np.empty((x.shape[0], N), np.float32)
+    lib().fo_matmul_vec_kquant(quant, out, x.shape[0], x, np.ascontiguousarray(w, np.uint8), K, N)
+    return out
+
+
+def dequant_kquant(quant: int, b: np.ndarray, n: int) -> np.ndarray:
+    out = np.empty(n, np.float32)
+    (lib().fo_dequant_q4_k if quant == Q4_K else lib().fo_dequant_q6_k)(np.ascontiguousarray(b, np.uint8), n, out)
+    return out
+
+
+def pack_q4_k_superblock(d: float, dmin: float, scales, mins, q_lo, q_hi) -> np.ndarray:
+    """One 144-byte Q4_K super-block from its fields: scales/mins are the eight 6-bit values, q_lo[c] / q_hi[c]
+    the 32 nibbles of sub-blocks 2c / 2c+1 (the inverse of the scale unpacking, WL:2499-2542)."""
+    out = np.zeros(144, np.uint8)
+    out[0:2] = np.frombuffer(np.uint16(f32_to_f16(d)).tobytes(), np.uint8)
+    out[2:4] = np.frombuffer(np.uint16(f32_to_f16(dmin)).tobytes(), np.uint8)
+    sc, mn = [int(v) for v in scales], [int(v) for v in mins]
+    for i in range(4):
+        out[4 + i] = (sc[i] & 63) | (((sc[i + 4] >> 4) & 3) << 6)
+        out[8 + i] = (mn[i] & 63) | (((mn[i + 4] >> 4) & 3) << 6)
+        out[12 + i] = (sc[i + 4] & 15) | ((mn[i + 4] & 15) << 4)
+    lo = np.asarray(q_lo, np.uint8).reshape(4, 32) & 15
+    hi = np.asarray(q_hi, np.uint8).reshape(4, 32) & 15
+    out[16:144] = (lo | (hi << 4)).ravel()
+    return out
+
+
+def random_kquant_rows(quant: int, rng: np.random.Generator, N: int, K: int, scale: float = 0.02) -> np.ndarray:
+    """N rows of valid K-quant super-blocks with random fields (no quantiser involved): every byte pattern of the
+    quant fields is legal, only the f16 scales are drawn from a sane range."""
+    nsb = N * (K // 256)
+    if quant == Q4_K:
+        blk = rng.integers(0, 256, (nsb, 144), dtype=np.uint8)
+        d = (scale / 32 * (0.5 + rng.random(nsb))).astype(np.float16)
+        dmin = (scale / 32 * (0.5 + rng.random(nsb))).astype(np.float16)
+        blk[:, 0:2] = d.view(np.uint8).reshape(nsb, 2)
+        blk[:, 2:4] = dmin.view(np.uint8).reshape(nsb, 2)
+    else:
+        blk = rng.integers(0, 256, (nsb, 210), dtype=np.uint8)
+        d = (scale / 1024 * (0.5 + rng.random(nsb))).astype(np.float16)
+        blk[:, 208:210] = d.view(np.uint8).reshape(nsb, 2)
+    return blk.reshape(-1)
 
 
 def rms_norm(x, w, eps):

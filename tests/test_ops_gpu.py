@@ -48,6 +48,44 @@ def test_matmul_mat(L, oracle, quant, m, K, N):
     assert np.abs(got - ref).max() < 50 * tol * np.abs(ref).max()
 
 
+@pytest.mark.parametrize("quant", [12, 14])
+@pytest.mark.parametrize("m,K,N", [(1, 256, 2), (1, 512, 130), (1, 2048, 512), (1, 8192, 2048), (1, 11008 // 256 * 256, 19000),
+                                   (3, 768, 130), (9, 1536, 144), (1, 2048, 32000)])
+def test_matmul_vec_kquant(L, oracle, quant, m, K, N):
+    """matmul_vec_q4_k / matmul_vec_q6_k: the input row is quantised to Q8_0 blocks as in the reference, the block dots
+    are exact integers, so the result agrees with the oracle up to the f32 summation order."""
+    import torch
+    lib, check = L
+    rng = np.random.default_rng(100 * quant + m + K + N)
+    w = oracle.random_kquant_rows(quant, rng, N, K)
+    x = rng.standard_normal((m, K), dtype=np.float32)
+    x[:, 32:64] = 0.0  # an all-zero block (scale 1, zeros)
+    ref = oracle.matmul_vec_kquant(quant, x, w, K, N)
+    dx, dw = dev(x), dev(w)
+    out = torch.empty((m, N), dtype=torch.float32, device="cuda")
+    fn = lib.forge_matmul_vec_q4_k if quant == 12 else lib.forge_matmul_vec_q6_k
+    check(fn(out.data_ptr(), m, dx.data_ptr(), dw.data_ptr(), K, N, None))
+    _sync()
+    got = out.cpu().numpy()
+    assert rel_l2(got, ref) < 4e-6
+    assert np.abs(got - ref).max() < 2e-4 * np.abs(ref).max()
+
+
+def test_matmul_vec_kquant_known_answer(L, oracle):
+    # weight_loader.rs:2545-2569 through the C-ABI: every weight 4, every input 2 -> 2048 (the input is exactly
+    # representable in Q8_0 here, so the product is exact)
+    import torch
+    lib, check = L
+    blk = oracle.pack_q4_k_superblock(1.0, 0.0, [1] * 8, [0] * 8, np.full((4, 32), 4), np.full((4, 32), 4))
+    dx, dw = dev(np.full(256, 2.0, np.float32)), dev(blk)
+    out = torch.empty(1, dtype=torch.float32, device="cuda")
+    check(lib.forge_matmul_vec_q4_k(out.data_ptr(), 1, dx.data_ptr(), dw.data_ptr(), 256, 1, None))
+    _sync()
+    assert abs(out.item() - 2048.0) < 2048.0 * 2e-3
+    assert out.item() == oracle.matmul_vec_kquant(12, np.full(256, 2.0, np.float32), blk, 256, 1)[0, 0]
+    assert lib.forge_matmul_vec_q6_k(out.data_ptr(), 1, dx.data_ptr(), dw.data_ptr(), 224, 1, None) == 2  # K % 256
+
+
 def test_matmul_known_answer(L):
     # crates/forgellm-runtime/src/kernels.rs:327-335 through the C-ABI: [1,2] x [[1,2],[3,4]]^T = [5,11]
     import torch

@@ -238,3 +238,88 @@ def test_batched_prefill_equals_per_token_path(oracle):
     for tok in toks[:5]:
         l2 = t.forward(int(tok))
     assert np.array_equal(l1, l2)
+
+
+# ---- K-quants: the reference's own known-answer tests (crates/forgellm-frontend/src/weight_loader.rs)
+def _f16_bytes(bits):
+    return np.frombuffer(np.uint16(bits).tobytes(), np.uint8)
+
+
+def test_dequant_q4_k_basic_and_values(oracle):
+    # WL:3422-3450: d = 1, dmin = 0, all scales 1, all q = 0 -> zeros
+    b = np.zeros(144, np.uint8)
+    b[0:2] = _f16_bytes(0x3C00)
+    b[4:8] = 1
+    b[12:16] = 0x01
+    assert np.all(np.abs(oracle.dequant_kquant(oracle.Q4_K, b, 256)) < 1e-6)
+    # WL:3453-3478: d = 2, dmin = 1, sub-block 0 scale 3 and min 2, low nibbles 5 -> 2*3*5 - 1*2 = 28
+    b = np.zeros(144, np.uint8)
+    b[0:2] = _f16_bytes(0x4000)
+    b[2:4] = _f16_bytes(0x3C00)
+    b[4], b[8] = 3, 2
+    b[16:48] = 0x05
+    out = oracle.dequant_kquant(oracle.Q4_K, b, 256)
+    assert np.all(np.abs(out[:32] - 28.0) < 1e-4)
+
+
+def test_dequant_q6_k_known_answers(oracle):
+    # WL:3562-3583: all quants 0 -> (0 - 32) * 1 * 1
+    b = np.zeros(210, np.uint8)
+    b[208:210] = _f16_bytes(0x3C00)
+    b[192:208] = 1
+    assert np.all(np.abs(oracle.dequant_kquant(oracle.Q6_K, b, 256) + 32.0) < 1e-4)
+    # WL:3586-3609: d = 0.5, scale[0] = 2, ql[0] = 0x0A, qh[0] = 2 -> 0.5 * 2 * ((10 | 32) - 32) = 10
+    c = np.zeros(210, np.uint8)
+    c[208:210] = _f16_bytes(0x3800)
+    c[192], c[0], c[128] = 2, 0x0A, 0x02
+    assert abs(oracle.dequant_kquant(oracle.Q6_K, c, 256)[0] - 10.0) < 1e-4
+    # WL:3612-3657: the four values interleaved in one (ql, ql+32, qh) triple
+    b[0], b[32], b[128] = 0x31, 0x52, 0xE4
+    out = oracle.dequant_kquant(oracle.Q6_K, b, 256)
+    assert [out[0], out[32], out[64], out[96]] == [-31.0, -14.0, 3.0, 21.0]
+
+
+def test_dot_q4_k_uniform_block(oracle):
+    # WL:2545-2569: every weight dequantises to 4, every input is 2 -> 256 * 2 * 4 = 2048 within 1 %
+    blk = oracle.pack_q4_k_superblock(1.0, 0.0, [1] * 8, [0] * 8, np.full((4, 32), 4), np.full((4, 32), 4))
+    assert np.all(np.abs(oracle.dequant_kquant(oracle.Q4_K, blk, 256) - 4.0) < 1e-5)
+    got = oracle.matmul_vec_kquant(oracle.Q4_K, np.full(256, 2.0, np.float32), blk, 256, 1)[0, 0]
+    assert abs(got - 2048.0) / 2048.0 < 0.01
+
+
+def test_dot_q4_k_varied_block(oracle):
+    # WL:2572-2605: varied scales / mins / nibbles against the f32 product of the dequantised weights, within 2 %
+    c, i = np.arange(4)[:, None], np.arange(32)[None, :]
+    blk = oracle.pack_q4_k_superblock(0.03, 0.01, [3, 5, 7, 2, 10, 4, 6, 8], [1, 2, 3, 1, 2, 1, 1, 2],
+                                      (c * 4 + i // 8) % 16, (c * 2 + i % 16) % 16)
+    x = (np.sin(np.arange(256, dtype=np.float32) * np.float32(0.1)) * 0.5).astype(np.float32)
+    want = float(np.sum(oracle.dequant_kquant(oracle.Q4_K, blk, 256) * x, dtype=np.float32))
+    got = oracle.matmul_vec_kquant(oracle.Q4_K, x, blk, 256, 1)[0, 0]
+    assert abs(got - want) / max(abs(want), 1e-6) < 0.02
+
+
+@pytest.mark.parametrize("quant", [12, 14])
+def test_kquant_dot_equals_product_of_dequantised_operands(oracle, quant):
+    # the property behind WL:2979-3001: the integer block dots reproduce dequant(W) . dequant(Q8_0(x)) up to f32 rounding
+    rng = np.random.default_rng(quant)
+    K, N = 1024, 24
+    w = oracle.random_kquant_rows(quant, rng, N, K)
+    x = rng.standard_normal((3, K)).astype(np.float32)
+    got = oracle.matmul_vec_kquant(quant, x, w, K, N)
+    W = oracle.dequant_kquant(quant, w, N * K).reshape(N, K).astype(np.float64)
+    for r in range(3):
+        q, s = oracle.quantize_act_q8_0(x[r])
+        xd = (q.reshape(-1, 32).astype(np.float64) * s[:, None]).ravel()
+        assert np.abs(got[r] - W @ xd).max() < 2e-5 * np.abs(W @ xd).max()
+
+
+def test_activation_q8_0_blocks(oracle):
+    # emit.rs:1412-1440: absmax maps to +-127, a zero block keeps scale 1 and zeros, ties round away from zero
+    x = np.zeros(96, np.float32)
+    x[0:32] = np.linspace(-1.0, 1.0, 32)
+    x[64:96] = 127.0
+    x[64] = 0.5
+    x[65] = -2.5
+    q, s = oracle.quantize_act_q8_0(x)
+    assert q[0] == -127 and q[31] == 127 and np.all(q[32:64] == 0) and s[1] == 1.0
+    assert s[2] == 1.0 and q[64] == 1 and q[65] == -3 and np.all(q[66:96] == 127)
