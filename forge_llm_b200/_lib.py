@@ -20,6 +20,7 @@ class ForgeModelConfig(C.Structure):
         ("vocab_size", C.c_int32), ("max_seq_len", C.c_int32),
         ("rms_norm_eps", C.c_float), ("rope_theta", C.c_float),
         ("quant", C.c_int32), ("qkv_bias", C.c_int32), ("tp_rank", C.c_int32), ("tp_world", C.c_int32), ("sliding_window", C.c_int32),
+        ("proj_quant", C.c_int32 * 8),
     ]
 
 

@@ -46,6 +46,34 @@ def tiny(quant: int = 8, hd: int = 64, nq: int = 4, nkv: int = 2, bias: int = 0,
     return _cfg(f"tiny-q{quant}-hd{hd}", hidden, layers, nq, nkv, hd, ffn, vocab, 1e4, quant, bias=bias)
 
 
+PROJ_ORDER = ("q", "k", "v", "o", "gate", "up", "down", "lm_head")
+Q4_K, Q6_K = 12, 14  # K-quants carry their GGML type numbers
+
+
+def proj_quants(c: dict) -> list[int]:
+    """Storage format of every projection category in PROJ_ORDER: ``c["proj_quant"][i]`` (the reference's
+    ``ProjectionDTypes``, ir.rs:411-421), or ``c["quant"]`` where that is absent or 0."""
+    pq = c.get("proj_quant") or [0] * 8
+    return [int(v) or int(c["quant"]) for v in pq]
+
+
+def with_proj_quant(c: dict, **cats: int) -> dict:
+    """Copy of ``c`` with the named categories (PROJ_ORDER names) stored in the given formats."""
+    d = dict(c)
+    pq = list(c.get("proj_quant") or [0] * 8)
+    for name, q in cats.items():
+        pq[PROJ_ORDER.index(name)] = int(q)
+    d["proj_quant"] = pq
+    d["name"] = c["name"] + "-" + "-".join(f"{n}{q}" for n, q in cats.items())
+    return d
+
+
+def raw_row_bytes(quant: int, k: int) -> int:
+    if quant in (Q4_K, Q6_K):
+        return (k // 256) * (144 if quant == Q4_K else 210)
+    return (k // 32) * (34 if quant == 8 else 18)
+
+
 def weight_elems(c: dict) -> int:
     """Quantised weight elements streamed per decoded token (projections + lm_head)."""
     h, qk, kv, ff = c["hidden_size"], c["num_heads"] * c["head_dim"], c["num_kv_heads"] * c["head_dim"], c["intermediate_size"]

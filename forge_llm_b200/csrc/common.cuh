@@ -107,6 +107,7 @@ struct GemvArgs {
     const int32_t* seq_len = nullptr;     // [batch] device positions (the new row's position)
     int pages_per_seq = 0;
     int qk = 0, kv = 0, head_dim = 0;
+    int kv_stride = 0;              // values per cache row (= kv of the layer; a V-only matrix passes qk = kv = 0)
     // optional: constant data the NEXT kernel on the stream will read (its weights).  Every CTA asks L2 to fetch its
     // share while this kernel runs, so HBM keeps streaming across the kernel boundary.
     const void* next_w = nullptr;

@@ -461,7 +461,7 @@ __device__ __forceinline__ void epilogue_row(const Phase& ph, int b, int row, fl
             *reinterpret_cast<float2*>(a.q_out + size_t(b) * qk + col) = make_float2(q0, q1);
         } else {
             __half* pool = region == 1 ? a.k_pool : a.v_pool;
-            *reinterpret_cast<__half2*>(pool + (size_t(pre.page) * FORGE_KV_PAGE + pos % FORGE_KV_PAGE) * kv + col) =
+            *reinterpret_cast<__half2*>(pool + (size_t(pre.page) * FORGE_KV_PAGE + pos % FORGE_KV_PAGE) * a.kv_stride + col) =
                 __floats2half2_rn(q0, q1);
         }
     }

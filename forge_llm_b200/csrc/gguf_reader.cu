@@ -21,7 +21,7 @@ using namespace forge;
 
 constexpr uint32_t kMagic = 0x46554747u;  // "GGUF"
 constexpr uint64_t kDefaultAlignment = 32;
-enum : int32_t { T_F32 = 0, T_F16 = 1, T_Q4_0 = 2, T_Q8_0 = 8, T_BF16 = 30 };
+enum : int32_t { T_F32 = 0, T_F16 = 1, T_Q4_0 = 2, T_Q8_0 = 8, T_Q4_K = 12, T_Q6_K = 14, T_BF16 = 30 };
 
 struct MetaValue {
     int type = -1;         // GGUF value type id (0..12)
@@ -196,20 +196,66 @@ struct ForgeGguf {
 
 namespace {
 
-// the projection dtype of the model: majority vote over the projection tensors (main.rs:479-560); this backend
-// carries Q8_0 and Q4_0 only
+// the projection dtype of the model: majority vote over the projection tensors (detect_gguf_dtype, main.rs:479-556).
+// Other block formats count towards Q8_0 as there; a dense (f16 / f32) majority has no kernel in this backend.
 int32_t vote_quant(const ForgeGguf& g, int32_t& quant) {
-    size_t q8 = 0, q4 = 0, other = 0;
+    size_t q8 = 0, q4 = 0, q4k = 0, dense = 0;
     for (const TensorInfo& t : g.tensors) {
         const std::string& n = t.name;
         const bool proj = n.find(".weight") != std::string::npos && n.find("token_embd") == std::string::npos &&
                           n.find("output.weight") == std::string::npos && n.find("_norm") == std::string::npos;
         if (!proj) continue;
-        if (t.type == T_Q8_0) ++q8; else if (t.type == T_Q4_0) ++q4; else ++other;
+        if (t.type == T_Q8_0) ++q8;
+        else if (t.type == T_Q4_0) ++q4;
+        else if (t.type == T_Q4_K) ++q4k;
+        else if (t.type == T_F32 || t.type == T_F16 || t.type == T_BF16) ++dense;
+        else if (t.type == 3 || (t.type >= 6 && t.type <= 23)) ++q8;  // Q4_1, Q5_x, Q8_1, the other K- and I-quants
     }
-    if (other > q8 + q4 || q8 + q4 == 0) { set_error("GGUF projections are not Q8_0 / Q4_0 (%zu other, %zu Q8_0, %zu Q4_0)", other, q8, q4); return FORGE_ERR_UNSUPPORTED; }
-    quant = q4 > q8 ? FORGE_Q4_0 : FORGE_Q8_0;
+    const size_t total = q8 + q4 + q4k + dense;
+    if (total > 0 && q4k > total / 2) quant = FORGE_Q4_K;
+    else if (total > 0 && q8 > total / 2) quant = FORGE_Q8_0;
+    else if (total > 0 && q4 > total / 2) quant = FORGE_Q4_0;
+    else { set_error("GGUF projections have no Q8_0 / Q4_0 / Q4_K majority (%zu dense, %zu Q8_0-class, %zu Q4_0, %zu Q4_K)", dense, q8, q4, q4k); return FORGE_ERR_UNSUPPORTED; }
     return FORGE_OK;
+}
+
+// Storage format per projection category (detect_gguf_proj_dtypes, main.rs:603-690): the majority format of the
+// category's tensors, count ties going to the higher precision (dense > Q8_0 > Q6_K > Q4_K > Q4_0); formats without
+// a kernel do not vote; an empty category, or one with a dense majority (which the exporter quantises), takes the
+// model's format; without an output tensor the head follows the embedding.  pq: q, k, v, o, gate, up, down, lm_head.
+void detect_proj_quants(const ForgeGguf& g, int32_t fallback, int32_t (&pq)[8]) {
+    static const char* const suffix[8] = {"self_attn.q_proj.weight", "self_attn.k_proj.weight", "self_attn.v_proj.weight",
+                                          "self_attn.o_proj.weight", "mlp.gate_proj.weight", "mlp.up_proj.weight",
+                                          "mlp.down_proj.weight", "lm_head.weight"};
+    auto pick = [&](auto&& in_category) -> int32_t {
+        // index: 0 dense, 1 Q8_0, 2 Q6_K, 3 Q4_K, 4 Q4_0 (precision order)
+        size_t count[5] = {0, 0, 0, 0, 0};
+        static const int32_t fmt[5] = {0, FORGE_Q8_0, FORGE_Q6_K, FORGE_Q4_K, FORGE_Q4_0};
+        for (const TensorInfo& t : g.tensors) {
+            if (!in_category(hf_name(t.name))) continue;
+            if (t.type == T_F32 || t.type == T_F16 || t.type == T_BF16) ++count[0];
+            else if (t.type == T_Q8_0) ++count[1];
+            else if (t.type == T_Q6_K) ++count[2];
+            else if (t.type == T_Q4_K) ++count[3];
+            else if (t.type == T_Q4_0) ++count[4];
+        }
+        int best = -1;
+        for (int i = 0; i < 5; ++i) if (count[i] > 0 && (best < 0 || count[i] > count[best])) best = i;
+        return best <= 0 ? fallback : fmt[best];
+    };
+    for (int i = 0; i < 8; ++i) {
+        const std::string sfx = suffix[i];
+        pq[i] = pick([&](const std::string& n) {
+            if (i == 7) return n == sfx;
+            return n.compare(0, 13, "model.layers.") == 0 && n.size() > sfx.size() && n.compare(n.size() - sfx.size(), sfx.size(), sfx) == 0 &&
+                   n[n.size() - sfx.size() - 1] == '.';
+        });
+    }
+    if (!g.tensor("lm_head.weight")) pq[7] = pick([](const std::string& n) { return n == "model.embed_tokens.weight"; });
+    // fused Phi-3 tensors carry several categories at once
+    const int32_t qkv = pick([](const std::string& n) { return n.find(".self_attn.qkv_proj.weight") != std::string::npos; });
+    if (!g.tensor("model.layers.0.self_attn.q_proj.weight") && g.tensor("model.layers.0.self_attn.qkv_proj.weight")) pq[0] = pq[1] = pq[2] = qkv;
+    if (!g.tensor("model.layers.0.mlp.gate_proj.weight")) pq[4] = pq[5];
 }
 
 // dense tensor -> f32 (F32 / F16 / BF16), or Q8_0 blocks -> f32 (dequantize_q8_0, weight_loader.rs:860-888)
@@ -239,9 +285,63 @@ int32_t to_f32(const ForgeGguf& g, const TensorInfo& t, uint64_t expect, std::ve
         }
         return FORGE_OK;
     }
+    if (t.type == T_Q4_0 && expect % 32 == 0) {  // weight_loader.rs:893-926
+        for (uint64_t b = 0; b < expect / 32; ++b) {
+            uint16_t h; memcpy(&h, p + 18 * b, 2);
+            const float d = f16_to_f32(h);
+            for (int i = 0; i < 16; ++i) {
+                out[size_t(b * 32 + i)] = float(int(p[18 * b + 2 + i] & 0x0F) - 8) * d;
+                out[size_t(b * 32 + i + 16)] = float(int(p[18 * b + 2 + i] >> 4) - 8) * d;
+            }
+        }
+        return FORGE_OK;
+    }
+    if (t.type == T_Q4_K && expect % 256 == 0) {  // weight_loader.rs:1146-1200: d * sc * q - dmin * m per 32-element sub-block
+        for (uint64_t sb = 0; sb < expect / 256; ++sb) {
+            const uint8_t* blk = p + 144 * sb;
+            uint16_t h0, h1; memcpy(&h0, blk, 2); memcpy(&h1, blk + 2, 2);
+            const float d = f16_to_f32(h0), dmin = f16_to_f32(h1);
+            const uint8_t* sc = blk + 4;
+            for (int j = 0; j < 8; ++j) {
+                int s6, m6;
+                if (j < 4) { s6 = sc[j] & 63; m6 = sc[j + 4] & 63; }
+                else { s6 = (sc[j + 4] & 0x0F) | ((sc[j - 4] >> 6) << 4); m6 = (sc[j + 4] >> 4) | ((sc[j] >> 6) << 4); }
+                const float dw = d * float(s6), mw = dmin * float(m6);
+                for (int l = 0; l < 32; ++l) {
+                    const uint8_t by = blk[16 + (j >> 1) * 32 + l];
+                    out[size_t(sb * 256 + j * 32 + l)] = dw * float((j & 1) ? (by >> 4) : (by & 0x0F)) - mw;
+                }
+            }
+        }
+        return FORGE_OK;
+    }
+    if (t.type == T_Q6_K && expect % 256 == 0) {  // weight_loader.rs:997-1060: d * scale[group of 16] * (q6 - 32)
+        for (uint64_t sb = 0; sb < expect / 256; ++sb) {
+            const uint8_t* blk = p + 210 * sb;
+            uint16_t h; memcpy(&h, blk + 208, 2);
+            const float d = f16_to_f32(h);
+            for (int j = 0; j < 8; ++j) {  // 32-element group j: see the block table of dot_q6_k_q8_0 (emit.rs:3560-3570)
+                const uint8_t* ql = blk + (j >> 2) * 64 + (j & 1) * 32;
+                const uint8_t* qh = blk + 128 + (j >> 2) * 32;
+                const int nib = ((j >> 1) & 1) * 4, hsh = (j & 3) * 2;
+                for (int l = 0; l < 32; ++l) {
+                    const int q6 = int(((ql[l] >> nib) & 0x0F) | (((qh[l] >> hsh) & 3) << 4)) - 32;
+                    out[size_t(sb * 256 + j * 32 + l)] = d * float(int(int8_t(blk[192 + 2 * j + (l >> 4)]))) * float(q6);
+                }
+            }
+        }
+        return FORGE_OK;
+    }
     set_error("tensor %s: type %d cannot be read as f32 here", t.name.c_str(), t.type);
     return FORGE_ERR_UNSUPPORTED;
 }
+
+bool is_kquant(int32_t q) { return q == FORGE_Q4_K || q == FORGE_Q6_K; }
+uint64_t row_bytes(int32_t quant, uint64_t cols) {
+    if (is_kquant(quant)) return cols / 256 * (quant == FORGE_Q4_K ? 144 : 210);
+    return cols / 32 * (quant == FORGE_Q8_0 ? 34 : 18);
+}
+int32_t quant_of(const ForgeModelConfig& c, int cat) { return c.proj_quant[cat] ? c.proj_quant[cat] : c.quant; }
 
 struct Sink {  // counts bytes, and writes them when there is a buffer
     uint8_t* out; size_t cap, n = 0; bool overflow = false;
@@ -300,30 +400,34 @@ Part find_projection(const ForgeGguf& g, const std::string& hf, uint64_t numel, 
     return {};
 }
 
-// a projection [rows][cols]: raw blocks when the tensor already has the model's block format, dense tensors are
-// quantised (the reference does this for f32 projections of Q4_0 models, main.rs:2601-2607)
-int32_t put_projection(const ForgeGguf& g, const std::string& hf, uint64_t rows, uint64_t cols, const ForgeModelConfig& c, Sink& s) {
-    const int32_t quant = c.quant;
-    const uint64_t numel = rows * cols, bs = quant == FORGE_Q8_0 ? 34 : 18;
+// a projection [rows][cols] of category `cat`: raw blocks when the tensor already has the category's block format;
+// dense tensors are quantised to Q8_0 / Q4_0 (the reference does this for f32 projections of Q4_0 models,
+// main.rs:2601-2607).  Re-quantisation to a K-quant (a Q4_K tensor in a Q6_K category, which the reference sends
+// through its own K-quant quantisers) is not carried out here.
+int32_t put_projection(const ForgeGguf& g, const std::string& hf, int cat, uint64_t rows, uint64_t cols, const ForgeModelConfig& c, Sink& s) {
+    const int32_t quant = quant_of(c, cat);
+    const uint64_t numel = rows * cols, rb = row_bytes(quant, cols);
+    const uint64_t blk = is_kquant(quant) ? 256 : 32;
+    if (cols % blk) { set_error("tensor %s: %llu columns are not a multiple of the %llu-element block", hf.c_str(), (unsigned long long)cols, (unsigned long long)blk); return FORGE_ERR_SHAPE; }
     const Part part = find_projection(g, hf, numel, c);
     const TensorInfo* t = part.t;
     if (!t) { set_error("weight not found: %s", hf.c_str()); return FORGE_ERR_SHAPE; }
     if (part.first > t->numel() || numel > t->numel() - part.first || t->dims[0] != cols) { set_error("tensor %s does not hold a [%llu][%llu] projection", t->name.c_str(), (unsigned long long)rows, (unsigned long long)cols); return FORGE_ERR_SHAPE; }
     if (!part.fused && t->numel() != numel) { set_error("tensor %s is not [%llu][%llu]", hf.c_str(), (unsigned long long)rows, (unsigned long long)cols); return FORGE_ERR_SHAPE; }
-    if (!s.out) { s.n += size_t(numel / 32 * bs); return FORGE_OK; }
-    const int32_t want = quant == FORGE_Q8_0 ? T_Q8_0 : T_Q4_0;
+    if (!s.out) { s.n += size_t(rows * rb); return FORGE_OK; }
+    const int32_t want = quant == FORGE_Q8_0 ? T_Q8_0 : quant == FORGE_Q4_0 ? T_Q4_0 : quant == FORGE_Q4_K ? T_Q4_K : T_Q6_K;
     if (t->type == want) {
         const uint8_t* p; uint64_t bytes;
         if (!g.span(*t, p, bytes)) { set_error("tensor %s extends past the end of the file", t->name.c_str()); return FORGE_ERR_SHAPE; }
-        s.put(p + part.first / 32 * bs, size_t(numel / 32 * bs));
+        s.put(p + part.first / cols * rb, size_t(rows * rb));
         return FORGE_OK;
     }
-    if (t->type == T_F32 || t->type == T_F16 || t->type == T_BF16 || (t->type == T_Q8_0 && quant == FORGE_Q4_0)) {
+    if (!is_kquant(quant) && (t->type == T_F32 || t->type == T_F16 || t->type == T_BF16 || (t->type == T_Q8_0 && quant == FORGE_Q4_0))) {
         std::vector<float> v;
         FORGE_TRY(to_f32(g, *t, numel, v, part.first));
         return put_quantised(v, quant, s);
     }
-    set_error("tensor %s: type %d in a %s model is not supported", t->name.c_str(), t->type, quant == FORGE_Q8_0 ? "Q8_0" : "Q4_0");
+    set_error("tensor %s: type %d in a category stored as format %d would need re-quantisation, which this exporter does not do", t->name.c_str(), t->type, quant);
     return FORGE_ERR_UNSUPPORTED;
 }
 
@@ -337,23 +441,23 @@ int32_t export_to(const ForgeGguf& g, Sink& s) {
     for (int l = 0; l < c.num_layers; ++l) {
         const std::string p = "model.layers." + std::to_string(l) + ".";
         FORGE_TRY(put_f32_tensor(g, p + "input_layernorm.weight", H, s));
-        FORGE_TRY(put_projection(g, p + "self_attn.q_proj.weight", QK, H, c, s));
-        FORGE_TRY(put_projection(g, p + "self_attn.k_proj.weight", KV, H, c, s));
-        FORGE_TRY(put_projection(g, p + "self_attn.v_proj.weight", KV, H, c, s));
+        FORGE_TRY(put_projection(g, p + "self_attn.q_proj.weight", 0, QK, H, c, s));
+        FORGE_TRY(put_projection(g, p + "self_attn.k_proj.weight", 1, KV, H, c, s));
+        FORGE_TRY(put_projection(g, p + "self_attn.v_proj.weight", 2, KV, H, c, s));
         if (c.qkv_bias) {
             FORGE_TRY(put_f32_tensor(g, p + "self_attn.q_proj.bias", QK, s));
             FORGE_TRY(put_f32_tensor(g, p + "self_attn.k_proj.bias", KV, s));
             FORGE_TRY(put_f32_tensor(g, p + "self_attn.v_proj.bias", KV, s));
         }
-        FORGE_TRY(put_projection(g, p + "self_attn.o_proj.weight", H, QK, c, s));
+        FORGE_TRY(put_projection(g, p + "self_attn.o_proj.weight", 3, H, QK, c, s));
         FORGE_TRY(put_f32_tensor(g, p + "post_attention_layernorm.weight", H, s));
-        FORGE_TRY(put_projection(g, p + "mlp.gate_proj.weight", FF, H, c, s));
-        FORGE_TRY(put_projection(g, p + "mlp.up_proj.weight", FF, H, c, s));
-        FORGE_TRY(put_projection(g, p + "mlp.down_proj.weight", H, FF, c, s));
+        FORGE_TRY(put_projection(g, p + "mlp.gate_proj.weight", 4, FF, H, c, s));
+        FORGE_TRY(put_projection(g, p + "mlp.up_proj.weight", 5, FF, H, c, s));
+        FORGE_TRY(put_projection(g, p + "mlp.down_proj.weight", 6, H, FF, c, s));
     }
     FORGE_TRY(put_f32_tensor(g, "model.norm.weight", H, s));
     // lm_head: output.weight, else the (tied) embedding in the model's block format (main.rs:2625-2667)
-    FORGE_TRY(put_projection(g, g.tensor("lm_head.weight") ? "lm_head.weight" : "model.embed_tokens.weight", V, H, c, s));
+    FORGE_TRY(put_projection(g, g.tensor("lm_head.weight") ? "lm_head.weight" : "model.embed_tokens.weight", 7, V, H, c, s));
     if (s.overflow) { set_error("output buffer too small"); return FORGE_ERR_INVALID_ARG; }
     return FORGE_OK;
 }
@@ -459,6 +563,11 @@ int32_t forge_gguf_model_config(const ForgeGguf* g, ForgeModelConfig* c) {
     c->quant = quant; c->qkv_bias = arch == "qwen2" ? 1 : 0;
     c->tp_rank = 0; c->tp_world = 1;
     c->sliding_window = int32_t(window);
+    int32_t pq[8];
+    detect_proj_quants(*g, quant, pq);
+    bool uniform = true;
+    for (int i = 0; i < 8; ++i) uniform = uniform && pq[i] == quant;
+    if (!uniform) memcpy(c->proj_quant, pq, sizeof(pq));
     return FORGE_OK;
 }
 

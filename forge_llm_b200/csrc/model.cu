@@ -36,6 +36,7 @@ struct ForgeLayer {
     float* attn_norm = nullptr;
     QWeight qkv;           // rows: [q ; k ; v] of this rank (row-major split layout: prefill GEMM)
     QTiled qkv_t;          // the same matrix in the tiled streaming layout (decode GEMV)
+    QTiled v_t;            // only when v_proj is stored in another format than q/k: qkv holds [q ; k], this holds v
     float* qkv_bias = nullptr;
     QWeight o;
     QTiled o_t;
@@ -63,11 +64,14 @@ struct ForgeModel {
     int max_seq = 0;
     std::vector<void*> allocs;
     // prefill scratch (grown on demand)
-    int scratch_rows = 0;
+    int scratch_rows = 0, tok_cap = 0;
     float* p_hidden = nullptr; __half* p_normed = nullptr; float* p_qkv = nullptr; __half* p_q16 = nullptr;
     __half* p_attn16 = nullptr; float* p_gu = nullptr; __half* p_act16 = nullptr; uint32_t* p_tokens = nullptr;
     __half* p_normed_lo = nullptr; __half* p_attn16_lo = nullptr; __half* p_act16_lo = nullptr;
     int gemm_passes = 3;  // 3: split-precision prefill GEMMs (default); 1: single fp16 pass
+    int pq[8] = {0, 0, 0, 0, 0, 0, 0, 0};  // storage format of q, k, v, o, gate, up, down, lm_head (cfg.proj_quant or cfg.quant)
+    bool uniform_basic = true;             // every projection is stored in cfg.quant (Q8_0 / Q4_0): what the whole-step kernel takes
+    bool per_token_prefill = false;        // K-quant (or split-V) models: the prompt runs token by token like the reference's forward_prefill
     TpComm* tp = nullptr;  // tensor-parallel communicator (cfg.tp_world > 1)
     // peer-memory exchange of the decode step (forge_model_tp_exchange_*): local buffer, peers' mappings, device tables
     void* tpx_local = nullptr; std::vector<void*> tpx_peer; bool tpx_ready = false;
@@ -119,11 +123,29 @@ int32_t alloc_qweight(ForgeModel* m, QWeight& w, int quant, int K, int N) {
     return FORGE_OK;
 }
 
-size_t raw_bytes(int quant, size_t n, size_t k) { return n * (k / 32) * (quant == FORGE_Q8_0 ? 34 : 18); }
+bool is_kquant(int quant) { return quant == FORGE_Q4_K || quant == FORGE_Q6_K; }
+size_t raw_row_bytes(int quant, size_t k) {
+    if (is_kquant(quant)) return (k / 256) * (quant == FORGE_Q4_K ? 144 : 210);
+    return (k / 32) * (quant == FORGE_Q8_0 ? 34 : 18);
+}
+size_t raw_bytes(int quant, size_t n, size_t k) { return n * raw_row_bytes(quant, k); }
+
+enum ProjIndex { PQ_Q = 0, PQ_K, PQ_V, PQ_O, PQ_GATE, PQ_UP, PQ_DOWN, PQ_LM };
+// storage format of every projection category: cfg.proj_quant[i], or cfg.quant where that is 0
+void proj_quants(const ForgeModelConfig* c, int (&pq)[8]) {
+    for (int i = 0; i < 8; ++i) pq[i] = c->proj_quant[i] ? c->proj_quant[i] : c->quant;
+}
 
 int32_t check_cfg(const ForgeModelConfig* c) {
     if (!c) { set_error("null config"); return FORGE_ERR_INVALID_ARG; }
-    if (c->quant != FORGE_Q8_0 && c->quant != FORGE_Q4_0) { set_error("quant must be FORGE_Q8_0 or FORGE_Q4_0"); return FORGE_ERR_INVALID_ARG; }
+    int pq[8];
+    proj_quants(c, pq);
+    bool anyk = false;
+    for (int i = 0; i < 8; ++i) {
+        if (pq[i] != FORGE_Q8_0 && pq[i] != FORGE_Q4_0 && !is_kquant(pq[i])) { set_error("quant / proj_quant[%d] = %d is not FORGE_Q8_0, FORGE_Q4_0, FORGE_Q4_K or FORGE_Q6_K", i, pq[i]); return FORGE_ERR_INVALID_ARG; }
+        anyk = anyk || is_kquant(pq[i]);
+    }
+    if (pq[PQ_Q] != pq[PQ_K] || pq[PQ_GATE] != pq[PQ_UP]) { set_error("q/k and gate/up must share a storage format (they are fused into one product)"); return FORGE_ERR_UNSUPPORTED; }
     if (c->hidden_size <= 0 || c->intermediate_size <= 0 || c->num_layers <= 0 || c->num_heads <= 0 || c->num_kv_heads <= 0 ||
         c->vocab_size <= 0 || c->max_seq_len <= 0) { set_error("non-positive dimension in config"); return FORGE_ERR_INVALID_ARG; }
     if (c->head_dim != 64 && c->head_dim != 96 && c->head_dim != 128) { set_error("head_dim %d unsupported (64, 96, 128)", c->head_dim); return FORGE_ERR_SHAPE; }
@@ -132,6 +154,11 @@ int32_t check_cfg(const ForgeModelConfig* c) {
     int tp = c->tp_world < 1 ? 1 : c->tp_world;
     if (c->tp_rank < 0 || c->tp_rank >= tp) { set_error("tp_rank out of range"); return FORGE_ERR_INVALID_ARG; }
     if (c->num_kv_heads % tp || (c->intermediate_size / tp) % 32 || c->intermediate_size % tp) { set_error("tensor-parallel world %d does not divide kv heads / intermediate blocks", tp); return FORGE_ERR_SHAPE; }
+    if ((anyk || pq[PQ_V] != pq[PQ_Q]) && tp > 1) { set_error("K-quant and mixed q/v formats are not sharded over tensor-parallel ranks"); return FORGE_ERR_UNSUPPORTED; }
+    const int kdim[8] = {c->hidden_size, c->hidden_size, c->hidden_size, c->num_heads * c->head_dim, c->hidden_size, c->hidden_size,
+                         c->intermediate_size, c->hidden_size};
+    for (int i = 0; i < 8; ++i)
+        if (is_kquant(pq[i]) && kdim[i] % 256) { set_error("projection %d is a K-quant but its input width %d is not a multiple of 256", i, kdim[i]); return FORGE_ERR_SHAPE; }
     return FORGE_OK;
 }
 
@@ -228,6 +255,9 @@ int32_t row_sliced_gemv(ForgeModel* m, const QTiled& w, GemvArgs a, int batch, c
     return residual_add_f32(m->d_hidden, m->d_part, size_t(batch) * m->h, st);
 }
 
+int32_t decode_launches(ForgeModel* m, ForgeKV* kv, int batch, bool greedy, bool record, const struct PrefillToken* pt);
+int32_t prefill_per_token(ForgeModel* m, ForgeKV* kv, int seq, const uint32_t* tokens_host, int n);
+
 // ------------------------------------------------------------------ prefill of one sequence
 // forward_prefill_batched, emit.rs:5118-5486.  Leaves the last row's logits in m->d_logits[0..V).
 int32_t prefill_seq(ForgeModel* m, ForgeKV* kv, int seq, const uint32_t* tokens_host, int n) {
@@ -235,6 +265,7 @@ int32_t prefill_seq(ForgeModel* m, ForgeKV* kv, int seq, const uint32_t* tokens_
     cudaStream_t st = m->stream;
     const int base = kv->len[seq];
     FORGE_TRY(ensure_pages(kv, seq, base + n));
+    if (m->per_token_prefill) return prefill_per_token(m, kv, seq, tokens_host, n);
     FORGE_TRY(ensure_prefill_scratch(m, n));
     FORGE_TRY(ensure_decode_scratch(m, 1));
     if (m->trace_on) FORGE_TRY(ensure_trace(m, n));
@@ -276,9 +307,14 @@ inline size_t tpx_bytes(const ForgeModel* m) { return sizeof(uint2) * 2 * size_t
 // ------------------------------------------------------------------ one decode step (launch sequence)
 // forward(), emit.rs:4029-4500, for `batch` sequences.  Tokens are read from m->d_tok, positions
 // from kv->d_seq_len; with `greedy` the next token is selected on the device into m->d_tok.
-int32_t decode_launches(ForgeModel* m, ForgeKV* kv, int batch, bool greedy, bool record) {
+// `pt` (per-token prefill): the step runs for sequence pt->seq with the token at pt->tok, without the head unless
+// pt->head, and leaves the step counter of the generation history alone.
+struct PrefillToken { int seq; const uint32_t* tok; bool head; float* trace_dst; size_t trace_stride; };
+int32_t decode_launches(ForgeModel* m, ForgeKV* kv, int batch, bool greedy, bool record, const PrefillToken* pt = nullptr) {
     const ForgeModelConfig& c = m->cfg;
     cudaStream_t st = m->stream;
+    const int32_t* page_table = kv->d_page_table + (pt ? size_t(pt->seq) * kv->pages_per_seq : 0);
+    int32_t* seq_len = kv->d_seq_len + (pt ? pt->seq : 0);
     // tensor-parallel sums over peer memory: the residual stream alternates between two buffers, because the kernel
     // that forms hidden + sum(parts) while staging writes it for its successors and other CTAs still read the old one
     const bool px = c.tp_world > 1 && m->tpx_ready && batch == 1 && !m->trace_on;
@@ -305,7 +341,7 @@ int32_t decode_launches(ForgeModel* m, ForgeKV* kv, int batch, bool greedy, bool
         pending = true;
         return gemv_tc(w, EPI_TP_PUSH, a, m->split, m->d_err, st);
     };
-    FORGE_TRY(embedding_rows(m->d_hidden, m->embed, m->d_tok, batch, m->h, record ? m->d_hist : nullptr, m->d_step, st));
+    FORGE_TRY(embedding_rows(m->d_hidden, m->embed, pt ? pt->tok : m->d_tok, batch, m->h, record ? m->d_hist : nullptr, m->d_step, st));
     for (int l = 0; l < c.num_layers; ++l) {
         ForgeLayer& L = m->layers[l];
         __half* kp = kv->k_pool + size_t(l) * kv->layer_stride;
@@ -314,11 +350,21 @@ int32_t decode_launches(ForgeModel* m, ForgeKV* kv, int batch, bool greedy, bool
         a.x = hid[cur]; a.norm_w = L.attn_norm; a.eps = c.rms_norm_eps; a.batch = batch;
         if (px) tp_consume(a);
         a.bias = L.qkv_bias; a.rope = m->rope; a.q_out = m->d_q; a.k_pool = kp; a.v_pool = vp;
-        a.page_table = kv->d_page_table; a.seq_len = kv->d_seq_len; a.pages_per_seq = kv->pages_per_seq;
-        a.qk = m->qk; a.kv = m->kv; a.head_dim = m->hd;
+        a.page_table = page_table; a.seq_len = seq_len; a.pages_per_seq = kv->pages_per_seq;
+        a.qk = m->qk; a.kv = m->kv; a.kv_stride = m->kv; a.head_dim = m->hd;
         a.next_w = L.o_t.data; a.next_bytes = qtiled_bytes(L.o_t);
+        if (L.v_t.data) { a.next_w = L.v_t.data; a.next_bytes = qtiled_bytes(L.v_t); }
         FORGE_TRY(gemv_tc(L.qkv_t, EPI_QKV, a, m->split, m->d_err, st));
-        AttnDecodeArgs da{m->d_attn, m->d_q, kp, vp, kv->d_page_table, kv->pages_per_seq, kv->d_seq_len, 0,
+        if (L.v_t.data) {
+            // v_proj stored in its own format: a second product whose rows all land in the V cache (no rotation)
+            GemvArgs v = a;
+            v.tp = GemvArgs::Tp();
+            v.qk = 0; v.kv = 0; v.q_out = nullptr;
+            v.bias = L.qkv_bias ? L.qkv_bias + m->qk + m->kv : nullptr;
+            v.next_w = L.o_t.data; v.next_bytes = qtiled_bytes(L.o_t);
+            FORGE_TRY(gemv_tc(L.v_t, EPI_QKV, v, m->split, m->d_err, st));
+        }
+        AttnDecodeArgs da{m->d_attn, m->d_q, kp, vp, page_table, kv->pages_per_seq, seq_len, 0,
                           batch, m->nq, m->nkv, m->hd, kv->max_seq, kv->attn_ws, kv->attn_counters, kv->splits, c.sliding_window};
         FORGE_TRY(attn_decode(da, st));
         GemvArgs o;
@@ -337,15 +383,40 @@ int32_t decode_launches(ForgeModel* m, ForgeKV* kv, int batch, bool greedy, bool
             d.next_w = nx.data; d.next_bytes = std::min(qtiled_bytes(nx), size_t(48) << 20);
         }
         if (px) FORGE_TRY(tp_push(L.down_t, d)); else FORGE_TRY(row_sliced_gemv(m, L.down_t, d, batch, st));
-        if (m->trace_on)
+        if (pt && pt->trace_dst)
+            FORGE_CUDA(cudaMemcpyAsync(pt->trace_dst + size_t(l) * pt->trace_stride, m->d_hidden, sizeof(float) * m->h, cudaMemcpyDeviceToDevice, st));
+        else if (m->trace_on && !pt)
             FORGE_CUDA(cudaMemcpyAsync(m->trace + size_t(l) * batch * m->h, m->d_hidden, sizeof(float) * batch * m->h, cudaMemcpyDeviceToDevice, st));
     }
-    GemvArgs lm;
-    lm.x = hid[cur]; lm.norm_w = m->final_norm; lm.eps = c.rms_norm_eps; lm.out = m->d_logits; lm.batch = batch;
-    if (px) tp_consume(lm);
-    FORGE_TRY(gemv_tc(m->lm_head_t, EPI_STORE, lm, m->split, m->d_err, st));
+    if (!pt || pt->head) {
+        GemvArgs lm;
+        lm.x = hid[cur]; lm.norm_w = m->final_norm; lm.eps = c.rms_norm_eps; lm.out = m->d_logits; lm.batch = batch;
+        if (px) tp_consume(lm);
+        FORGE_TRY(gemv_tc(m->lm_head_t, EPI_STORE, lm, m->split, m->d_err, st));
+    }
     if (greedy) FORGE_TRY(argmax_slices(m->d_tok, m->d_logits, m->V, batch, m->d_amax_val, m->d_amax_idx, m->d_amax_ticket, st));
-    FORGE_TRY(step_advance(kv->d_seq_len, batch, m->d_step, st, px ? m->d_tpx_step : nullptr));
+    FORGE_TRY(step_advance(seq_len, batch, pt ? nullptr : m->d_step, st, px ? m->d_tpx_step : nullptr));
+    return FORGE_OK;
+}
+
+// forward_prefill, emit.rs:4511-5050: the generated module has batched products only for Q8_0 / Q4_0, so a model with
+// K-quant projections takes its prompt through the per-token step, the head running for the last token only.  Pages
+// for [base, base + n) are already reserved; the device-side length of the sequence advances with every token.
+int32_t prefill_per_token(ForgeModel* m, ForgeKV* kv, int seq, const uint32_t* tokens_host, int n) {
+    cudaStream_t st = m->stream;
+    FORGE_TRY(ensure_decode_scratch(m, 1));
+    if (m->trace_on) FORGE_TRY(ensure_trace(m, n));
+    if (n > m->tok_cap) {
+        FORGE_TRY(dev_alloc(m, &m->p_tokens, size_t(n)));
+        m->tok_cap = n;
+    }
+    FORGE_CUDA(cudaMemcpyAsync(m->p_tokens, tokens_host, sizeof(uint32_t) * n, cudaMemcpyHostToDevice, st));
+    FORGE_TRY(upload_len(kv));
+    for (int i = 0; i < n; ++i) {
+        PrefillToken pt{seq, m->p_tokens + i, i == n - 1, m->trace_on ? m->trace + size_t(i) * m->h : nullptr, size_t(n) * m->h};
+        FORGE_TRY(decode_launches(m, kv, 1, false, false, &pt));
+    }
+    kv->len[seq] += n;
     return FORGE_OK;
 }
 
@@ -373,7 +444,7 @@ int32_t decode_step_one_kernel(ForgeModel* m, ForgeKV* kv, bool greedy) {
 
 int32_t decode_step_graph(ForgeModel* m, ForgeKV* kv, int batch, bool greedy) {
     if (m->trace_on) return decode_launches(m, kv, batch, greedy, greedy);
-    if (batch == 1 && m->use_mega && m->cfg.tp_world == 1 && m->cfg.sliding_window <= 0 && kv->d_phases && kv->mega_grid <= kArgmaxSlices && (m->nq / m->nkv) * m->hd <= 512) return decode_step_one_kernel(m, kv, greedy);
+    if (batch == 1 && m->use_mega && m->uniform_basic && m->cfg.tp_world == 1 && m->cfg.sliding_window <= 0 && kv->d_phases && kv->mega_grid <= kArgmaxSlices && (m->nq / m->nkv) * m->hd <= 512) return decode_step_one_kernel(m, kv, greedy);
     if (!kv->graph || kv->graph_batch != batch || kv->graph_greedy != greedy) {
         if (kv->graph) { cudaGraphExecDestroy(kv->graph); kv->graph = nullptr; }
         cudaGraph_t g = nullptr;
@@ -417,10 +488,11 @@ size_t forge_weights_bin_size(const ForgeModelConfig* c) {
     if (!c) return 0;
     size_t h = c->hidden_size, qk = size_t(c->num_heads) * c->head_dim, kv = size_t(c->num_kv_heads) * c->head_dim;
     size_t ff = c->intermediate_size, V = c->vocab_size;
-    int q = c->quant;
-    size_t per = h * 4 + raw_bytes(q, qk, h) + 2 * raw_bytes(q, kv, h) + (c->qkv_bias ? (qk + 2 * kv) * 4 : 0) + raw_bytes(q, h, qk) +
-                 h * 4 + 2 * raw_bytes(q, ff, h) + raw_bytes(q, h, ff);
-    return V * h * 4 + per * c->num_layers + h * 4 + raw_bytes(q, V, h);
+    int pq[8];
+    proj_quants(c, pq);
+    size_t per = h * 4 + raw_bytes(pq[PQ_Q], qk, h) + raw_bytes(pq[PQ_K], kv, h) + raw_bytes(pq[PQ_V], kv, h) + (c->qkv_bias ? (qk + 2 * kv) * 4 : 0) +
+                 raw_bytes(pq[PQ_O], h, qk) + h * 4 + raw_bytes(pq[PQ_GATE], ff, h) + raw_bytes(pq[PQ_UP], ff, h) + raw_bytes(pq[PQ_DOWN], h, ff);
+    return V * h * 4 + per * c->num_layers + h * 4 + raw_bytes(pq[PQ_LM], V, h);
 }
 
 int32_t forge_model_create(const ForgeModelConfig* cfg, const void* weights_bin, size_t len, int32_t device, ForgeModel** out) {
@@ -437,7 +509,15 @@ int32_t forge_model_create(const ForgeModelConfig* cfg, const void* weights_bin,
     m->cfg = *cfg;
     if (m->cfg.tp_world < 1) { m->cfg.tp_world = 1; m->cfg.tp_rank = 0; }
     m->device = device;
-    const int tp = m->cfg.tp_world, rk = m->cfg.tp_rank, quant = cfg->quant;
+    const int tp = m->cfg.tp_world, rk = m->cfg.tp_rank;
+    proj_quants(cfg, m->pq);
+    const int* pq = m->pq;
+    const bool split_v = pq[PQ_V] != pq[PQ_Q];
+    m->per_token_prefill = split_v;
+    for (int i = 0; i < 8; ++i) {
+        m->per_token_prefill = m->per_token_prefill || is_kquant(pq[i]);
+        m->uniform_basic = m->uniform_basic && pq[i] == cfg->quant && !is_kquant(pq[i]);
+    }
     const int H = cfg->hidden_size, QK = cfg->num_heads * cfg->head_dim, KV = cfg->num_kv_heads * cfg->head_dim, FF = cfg->intermediate_size;
     m->h = H; m->hd = cfg->head_dim; m->V = cfg->vocab_size;
     m->nq = cfg->num_heads / tp; m->nkv = cfg->num_kv_heads / tp;
@@ -452,11 +532,11 @@ int32_t forge_model_create(const ForgeModelConfig* cfg, const void* weights_bin,
     // Staging buffer for the raw blocks of one group of tensors (q,k,v | o | gate,up | down | lm_head): the
     // group is repacked on the device into (a) the row-major split layout the prefill GEMM reads and (b) the
     // tiled layout the decode GEMV streams, then the stage is reused.
-    const int BS = quant == FORGE_Q8_0 ? 34 : 18;
     int sm_count = 148;
     cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device);
-    size_t max_raw = std::max({raw_bytes(quant, size_t(cfg->vocab_size), H), 2 * raw_bytes(quant, FF, H) + 64,
-                               raw_bytes(quant, QK, H) + 2 * raw_bytes(quant, KV, H) + 64});
+    size_t max_raw = std::max({raw_bytes(pq[PQ_LM], size_t(cfg->vocab_size), H), 2 * raw_bytes(pq[PQ_GATE], FF, H) + 64,
+                               raw_bytes(pq[PQ_Q], QK, H) + raw_bytes(pq[PQ_K], KV, H) + raw_bytes(pq[PQ_V], KV, H) + 64,
+                               raw_bytes(pq[PQ_O], H, QK), raw_bytes(pq[PQ_DOWN], H, FF)});
     size_t max_rows = std::max({size_t(cfg->vocab_size), size_t(2 * FF), size_t(QK + 2 * KV), size_t(H)}) + 128;
     uint8_t* stage = nullptr;
     const uint8_t** d_rowsrc = nullptr;
@@ -472,8 +552,9 @@ int32_t forge_model_create(const ForgeModelConfig* cfg, const void* weights_bin,
     // one source tensor of a group: raw [N_full][K_full/32] blocks on the host; this rank keeps rows
     // [row0, row0+rows) and blocks [blk0, blk0+blks), landing at destination rows dst_row0 + r*step
     struct Part { const uint8_t* host; int N_full, K_full, row0, rows, blk0, blks, dst_row0, step; };
-    auto load_group = [&](const std::vector<Part>& parts, QWeight& soa, QTiled& tiled, int K_local, int N_local) -> int32_t {
-        FORGE_TRY(alloc_qweight(m, soa, quant, K_local, N_local));
+    auto load_group = [&](int quant, const std::vector<Part>& parts, QWeight& soa, QTiled& tiled, int K_local, int N_local) -> int32_t {
+        const bool kq = is_kquant(quant);  // K-quants have the per-token product only: no layout for the batched GEMM
+        if (!kq) FORGE_TRY(alloc_qweight(m, soa, quant, K_local, N_local));
         tiled.K = K_local; tiled.N = N_local; tiled.quant = quant; tiled.bt = gemv_band_tiles(N_local, sm_count); tiled.bands = (N_local + 16 * tiled.bt - 1) / (16 * tiled.bt);
         FORGE_TRY(dev_alloc(m, &tiled.data, qtiled_bytes(quant, K_local, N_local, tiled.bt)));
         std::vector<const uint8_t*> table(size_t(tiled.bands) * 16 * tiled.bt, nullptr);
@@ -481,9 +562,10 @@ int32_t forge_model_create(const ForgeModelConfig* cfg, const void* weights_bin,
         for (const Part& pt : parts) {
             const size_t bytes = raw_bytes(quant, pt.N_full, pt.K_full);
             FORGE_CUDA(cudaMemcpyAsync(stage + off, pt.host, bytes, cudaMemcpyHostToDevice, st));
-            FORGE_TRY(pack_rows(stage + off, quant, pt.K_full, pt.row0, pt.rows, pt.blk0, pt.blks, soa, pt.dst_row0, pt.step, st));
+            if (!kq) FORGE_TRY(pack_rows(stage + off, quant, pt.K_full, pt.row0, pt.rows, pt.blk0, pt.blks, soa, pt.dst_row0, pt.step, st));
+            const size_t blk_bytes = kq ? 0 : (quant == FORGE_Q8_0 ? 34 : 18);  // K-quant rows are never sliced along K (one rank)
             for (int r = 0; r < pt.rows; ++r)
-                table[size_t(pt.dst_row0) + size_t(r) * pt.step] = stage + off + (size_t(pt.row0 + r) * (pt.K_full / 32) + pt.blk0) * BS;
+                table[size_t(pt.dst_row0) + size_t(r) * pt.step] = stage + off + size_t(pt.row0 + r) * raw_row_bytes(quant, pt.K_full) + pt.blk0 * blk_bytes;
             off += (bytes + 15) & ~size_t(15);
         }
         FORGE_CUDA(cudaMemcpyAsync(d_rowsrc, table.data(), table.size() * sizeof(uint8_t*), cudaMemcpyHostToDevice, st));
@@ -498,12 +580,18 @@ int32_t forge_model_create(const ForgeModelConfig* cfg, const void* weights_bin,
     for (int l = 0; l < cfg->num_layers; ++l) {
         ForgeLayer& L = m->layers[l];
         MC(upload_f32(&L.attn_norm, H, p)); p += size_t(H) * 4;
-        const uint8_t* pq = p; p += raw_bytes(quant, QK, H);
-        const uint8_t* pk = p; p += raw_bytes(quant, KV, H);
-        const uint8_t* pv = p; p += raw_bytes(quant, KV, H);
-        MC(load_group({{pq, QK, H, rk * m->qk, m->qk, 0, H / 32, 0, 1},
-                       {pk, KV, H, rk * m->kv, m->kv, 0, H / 32, m->qk, 1},
-                       {pv, KV, H, rk * m->kv, m->kv, 0, H / 32, m->qk + m->kv, 1}}, L.qkv, L.qkv_t, H, m->qk + 2 * m->kv));
+        const uint8_t* wq = p; p += raw_bytes(pq[PQ_Q], QK, H);
+        const uint8_t* wk = p; p += raw_bytes(pq[PQ_K], KV, H);
+        const uint8_t* wv = p; p += raw_bytes(pq[PQ_V], KV, H);
+        if (!split_v) {
+            MC(load_group(pq[PQ_Q], {{wq, QK, H, rk * m->qk, m->qk, 0, H / 32, 0, 1},
+                                     {wk, KV, H, rk * m->kv, m->kv, 0, H / 32, m->qk, 1},
+                                     {wv, KV, H, rk * m->kv, m->kv, 0, H / 32, m->qk + m->kv, 1}}, L.qkv, L.qkv_t, H, m->qk + 2 * m->kv));
+        } else {
+            QWeight unused;
+            MC(load_group(pq[PQ_Q], {{wq, QK, H, 0, m->qk, 0, H / 32, 0, 1}, {wk, KV, H, 0, m->kv, 0, H / 32, m->qk, 1}}, L.qkv, L.qkv_t, H, m->qk + m->kv));
+            MC(load_group(pq[PQ_V], {{wv, KV, H, 0, m->kv, 0, H / 32, 0, 1}}, unused, L.v_t, H, m->kv));
+        }
         if (cfg->qkv_bias) {
             MC(dev_alloc(m, &L.qkv_bias, size_t(m->qk + 2 * m->kv)));
             const float* bq = reinterpret_cast<const float*>(p);
@@ -515,16 +603,16 @@ int32_t forge_model_create(const ForgeModelConfig* cfg, const void* weights_bin,
             }
             p += size_t(QK + 2 * KV) * 4;
         }
-        MC(load_group({{p, H, QK, 0, H, rk * (m->qk / 32), m->qk / 32, 0, 1}}, L.o, L.o_t, m->qk, H)); p += raw_bytes(quant, H, QK);
+        MC(load_group(pq[PQ_O], {{p, H, QK, 0, H, rk * (m->qk / 32), m->qk / 32, 0, 1}}, L.o, L.o_t, m->qk, H)); p += raw_bytes(pq[PQ_O], H, QK);
         MC(upload_f32(&L.ffn_norm, H, p)); p += size_t(H) * 4;
-        const uint8_t* pg = p; p += raw_bytes(quant, FF, H);
-        const uint8_t* pu = p; p += raw_bytes(quant, FF, H);
-        MC(load_group({{pg, FF, H, rk * m->ff, m->ff, 0, H / 32, 0, 2}, {pu, FF, H, rk * m->ff, m->ff, 0, H / 32, 1, 2}},
+        const uint8_t* pg = p; p += raw_bytes(pq[PQ_GATE], FF, H);
+        const uint8_t* pu = p; p += raw_bytes(pq[PQ_UP], FF, H);
+        MC(load_group(pq[PQ_GATE], {{pg, FF, H, rk * m->ff, m->ff, 0, H / 32, 0, 2}, {pu, FF, H, rk * m->ff, m->ff, 0, H / 32, 1, 2}},
                       L.gateup, L.gateup_t, H, 2 * m->ff));
-        MC(load_group({{p, H, FF, 0, H, rk * (m->ff / 32), m->ff / 32, 0, 1}}, L.down, L.down_t, m->ff, H)); p += raw_bytes(quant, H, FF);
+        MC(load_group(pq[PQ_DOWN], {{p, H, FF, 0, H, rk * (m->ff / 32), m->ff / 32, 0, 1}}, L.down, L.down_t, m->ff, H)); p += raw_bytes(pq[PQ_DOWN], H, FF);
     }
     MC(upload_f32(&m->final_norm, H, p)); p += size_t(H) * 4;
-    MC(load_group({{p, cfg->vocab_size, H, 0, cfg->vocab_size, 0, H / 32, 0, 1}}, m->lm_head, m->lm_head_t, H, cfg->vocab_size));
+    MC(load_group(pq[PQ_LM], {{p, cfg->vocab_size, H, 0, cfg->vocab_size, 0, H / 32, 0, 1}}, m->lm_head, m->lm_head_t, H, cfg->vocab_size));
     MC(dev_alloc(m, &m->d_err, 1));
     MC(dev_alloc(m, &m->split.scratch, size_t(kGemvMaxSlices) * kGemvSplitRows));
     MC(dev_alloc(m, &m->split.tickets, size_t(kGemvSplitRows) / 16));
@@ -681,7 +769,7 @@ int32_t forge_kv_create(ForgeModel* m, int32_t max_seq, int32_t batch, ForgeKV**
             q.a.x = m->d_hidden; q.a.norm_w = L.attn_norm; q.a.eps = m->cfg.rms_norm_eps; q.a.bias = L.qkv_bias; q.a.rope = m->rope;
             q.a.q_out = m->d_q; q.a.k_pool = kv->k_pool + size_t(l) * kv->layer_stride; q.a.v_pool = kv->v_pool + size_t(l) * kv->layer_stride;
             q.a.page_table = kv->d_page_table; q.a.seq_len = kv->d_seq_len; q.a.pages_per_seq = kv->pages_per_seq;
-            q.a.qk = m->qk; q.a.kv = m->kv; q.a.head_dim = m->hd;
+            q.a.qk = m->qk; q.a.kv = m->kv; q.a.kv_stride = m->kv; q.a.head_dim = m->hd;
             core::Phase& o = ph[4 * l + 1];
             fill(o, L.o_t, EPI_PARTIAL); o.scratch = kv->mega_scr[1];
             o.a.x = m->d_attn; o.a.out = m->d_hidden; o.a.resid = m->d_hidden;

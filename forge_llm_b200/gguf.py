@@ -55,7 +55,8 @@ class GgufFile:
         return {"hidden_size": c.hidden_size, "intermediate_size": c.intermediate_size, "num_layers": c.num_layers,
                 "num_heads": c.num_heads, "num_kv_heads": c.num_kv_heads, "head_dim": c.head_dim, "vocab_size": c.vocab_size,
                 "max_seq_len": c.max_seq_len, "rms_norm_eps": c.rms_norm_eps, "rope_theta": c.rope_theta, "quant": c.quant,
-                "qkv_bias": c.qkv_bias, "sliding_window": c.sliding_window, "name": "gguf"}
+                "qkv_bias": c.qkv_bias, "sliding_window": c.sliding_window, "name": "gguf",
+                "proj_quant": [int(v) for v in c.proj_quant]}
 
     def weights_bin(self) -> np.ndarray:
         n = int(lib.forge_gguf_weights_bin_size(self._h))

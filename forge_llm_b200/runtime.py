@@ -21,7 +21,8 @@ def _cfg_struct(c: dict, tp_rank: int = 0, tp_world: int = 1) -> ForgeModelConfi
     return ForgeModelConfig(c["hidden_size"], c["intermediate_size"], c["num_layers"], c["num_heads"],
                             c["num_kv_heads"], c["head_dim"], c["vocab_size"], c["max_seq_len"],
                             c["rms_norm_eps"], c["rope_theta"], c["quant"], int(c.get("qkv_bias", 0)),
-                            tp_rank, tp_world, int(c.get("sliding_window", 0) or 0))
+                            tp_rank, tp_world, int(c.get("sliding_window", 0) or 0),
+                            (C.c_int32 * 8)(*[int(v) for v in (c.get("proj_quant") or [0] * 8)]))
 
 
 def _p(a: np.ndarray | None):

@@ -87,20 +87,40 @@ def quantize(quant: int, x: np.ndarray) -> np.ndarray:
     return quantize_q8_0(x) if quant == 8 else quantize_q4_0(x)
 
 
+def random_kquant(quant: int, rng: np.random.Generator, n: int, k: int, std: float) -> np.ndarray:
+    """n rows of K-quant super-blocks drawn field by field (no quantiser is involved: every bit pattern of the
+    scale and quant fields is a legal block); the f16 super-block scales are sized so that the dequantised weights
+    have about the magnitude ``std``.  Q4_K: 144 bytes {d, dmin, 12 scale bytes, 128 nibble bytes}; Q6_K: 210 bytes
+    {128 low-nibble bytes, 64 two-bit bytes, 16 int8 scales, d} (emit.rs:2962-2969, :3542-3546)."""
+    nsb = n * (k // 256)
+    if quant == 12:
+        blk = rng.integers(0, 256, (nsb, 144), dtype=np.uint8)
+        blk[:, 0:2] = (std / 256 * (0.5 + rng.random(nsb))).astype(np.float16).view(np.uint8).reshape(nsb, 2)
+        blk[:, 2:4] = (std / 256 * (0.5 + rng.random(nsb))).astype(np.float16).view(np.uint8).reshape(nsb, 2)
+    else:
+        blk = rng.integers(0, 256, (nsb, 210), dtype=np.uint8)
+        blk[:, 208:210] = (std / 1024 * (0.5 + rng.random(nsb))).astype(np.float16).view(np.uint8).reshape(nsb, 2)
+    return blk.reshape(-1)
+
+
 def weights_bin_size(c: dict) -> int:
+    from .configs import proj_quants, raw_row_bytes
     h, qk, kv = c["hidden_size"], c["num_heads"] * c["head_dim"], c["num_kv_heads"] * c["head_dim"]
-    ff, V, bb = c["intermediate_size"], c["vocab_size"], (34 if c["quant"] == 8 else 18)
-    mb = lambda n, k: n * (k // 32) * bb
-    per = h * 4 + mb(qk, h) + 2 * mb(kv, h) + ((qk + 2 * kv) * 4 if c.get("qkv_bias") else 0) + mb(h, qk) + h * 4 \
-        + 2 * mb(ff, h) + mb(h, ff)
-    return V * h * 4 + per * c["num_layers"] + h * 4 + mb(V, h)
+    ff, V = c["intermediate_size"], c["vocab_size"]
+    pq = proj_quants(c)
+    mb = lambda cat, n, k: n * raw_row_bytes(pq[cat], k)
+    per = h * 4 + mb(0, qk, h) + mb(1, kv, h) + mb(2, kv, h) + ((qk + 2 * kv) * 4 if c.get("qkv_bias") else 0) + mb(3, h, qk) + h * 4 \
+        + mb(4, ff, h) + mb(5, ff, h) + mb(6, h, ff)
+    return V * h * 4 + per * c["num_layers"] + h * 4 + mb(7, V, h)
 
 
 def make_weights_bin(c: dict, seed: int = 0, std: float = 0.02, chunk_rows: int = 8192) -> np.ndarray:
     """Return the whole ``weights.bin`` image as a uint8 array."""
     rng = np.random.default_rng(seed)
     h, qk, kv = c["hidden_size"], c["num_heads"] * c["head_dim"], c["num_kv_heads"] * c["head_dim"]
-    ff, V, quant = c["intermediate_size"], c["vocab_size"], c["quant"]
+    from .configs import proj_quants
+    ff, V = c["intermediate_size"], c["vocab_size"]
+    pq = proj_quants(c)
     out = np.empty(weights_bin_size(c), np.uint8)
     off = 0
 
@@ -110,7 +130,10 @@ def make_weights_bin(c: dict, seed: int = 0, std: float = 0.02, chunk_rows: int 
         out[off:off + b.size] = b
         off += b.size
 
-    def draw_quant(n: int, k: int) -> np.ndarray:
+    def draw_quant(n: int, k: int, cat: int) -> np.ndarray:
+        quant = pq[cat]
+        if quant in (12, 14):
+            return random_kquant(quant, rng, n, k, std)
         parts = []
         for r0 in range(0, n, chunk_rows):
             r = min(chunk_rows, n - r0)
@@ -130,24 +153,25 @@ def make_weights_bin(c: dict, seed: int = 0, std: float = 0.02, chunk_rows: int 
     ones = np.ones(h, np.float32)
     for _ in range(c["num_layers"]):
         put(ones)
-        put(draw_quant(qk, h))
-        put(draw_quant(kv, h))
-        put(draw_quant(kv, h))
+        put(draw_quant(qk, h, 0))
+        put(draw_quant(kv, h, 1))
+        put(draw_quant(kv, h, 2))
         if c.get("qkv_bias"):
             put(rng.standard_normal(qk, dtype=np.float32) * np.float32(std))
             put(rng.standard_normal(kv, dtype=np.float32) * np.float32(std))
             put(rng.standard_normal(kv, dtype=np.float32) * np.float32(std))
-        put(draw_quant(h, qk))
+        put(draw_quant(h, qk, 3))
         put(ones)
-        put(draw_quant(ff, h))
-        put(draw_quant(ff, h))
-        put(draw_quant(h, ff))
+        put(draw_quant(ff, h, 4))
+        put(draw_quant(ff, h, 5))
+        put(draw_quant(h, ff, 6))
     put(ones)
-    lm = draw_quant(V, h)
+    lm = draw_quant(V, h, 7)
     put(lm)
     assert off == out.size
     if c.get("tied"):
-        emb = dequantize(quant, lm, V * h)
+        assert pq[7] in (8, 4), "tied synthetic models need a Q8_0 / Q4_0 head"
+        emb = dequantize(pq[7], lm, V * h)
         out[embed_off:embed_off + V * h * 4] = emb.view(np.uint8)
     return out
 

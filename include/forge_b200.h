@@ -44,7 +44,7 @@ typedef enum ForgeStatus {
 #define FORGE_Q4_0 4 /* GGUF Q4_0: 18-byte blocks {f16 d; u8 qs[16]}, value = nibble-8,
                         byte j = element j (low) and j+16 (high)          (E:2337-2359, WL:893-926) */
 /* K-quants (256-element super-blocks; the numbers are the GGML type ids).  Operator level only:
- * forge_matmul_vec_q4_k / forge_matmul_vec_q6_k and forge_packed_create; the model session takes Q8_0 / Q4_0. */
+ * per-token products only, as in the generated module (no batched K-quant product exists there). */
 #define FORGE_Q4_K 12 /* 144 bytes {f16 d; f16 dmin; u8 scales[12]; u8 qs[128]},
                          value = d*sc[j]*q - dmin*m[j] per 32-element sub-block j   (E:2962-2969, WL:1146-1200) */
 #define FORGE_Q6_K 14 /* 210 bytes {u8 ql[128]; u8 qh[64]; i8 scales[16]; f16 d},
@@ -66,12 +66,16 @@ typedef struct ForgeModelConfig {
     int32_t max_seq_len; /* capped at 4096 like MAX_SEQ_LEN (E:178) */
     float rms_norm_eps;
     float rope_theta;
-    int32_t quant;    /* FORGE_Q8_0 or FORGE_Q4_0, for every projection and lm_head */
+    int32_t quant;    /* FORGE_Q8_0, FORGE_Q4_0, FORGE_Q4_K or FORGE_Q6_K: every projection and lm_head, unless proj_quant says otherwise */
     int32_t qkv_bias; /* 1: f32 q,k,v biases follow v_proj in weights.bin (Qwen2, E:4108-4118) */
     int32_t tp_rank;  /* tensor-parallel rank / world size; 0 / 1 when not sharded */
     int32_t tp_world;
     int32_t sliding_window; /* > 0: position p attends to [max(0, p - window + 1), p] (Mistral, E:601-626,
                                E:916-1046); 0: full causal attention */
+    int32_t proj_quant[8];  /* storage format per projection category, in the order q, k, v, o, gate, up, down, lm_head
+                               (ProjectionDTypes, crates/forgellm-frontend/src/ir.rs:411-421, without the f32 embedding);
+                               0 = `quant`.  q/k and gate/up must agree.  A model with a K-quant category runs its prompt
+                               token by token like the generated forward_prefill (E:4511-5050) and takes one GPU. */
 } ForgeModelConfig;
 
 typedef struct ForgeModel ForgeModel;

@@ -195,7 +195,11 @@ void mat16_rows(const float* in, int m, int k, const uint8_t* w, size_t row_byte
         for (int r = 0; r < rows; ++r) out[size_t(t) * n_stride + r] = accv[size_t(t) * 16 + r];
 }
 
-inline size_t row_bytes_of(int quant, int k) { return size_t((k + 31) / 32) * (quant == 8 ? 34 : 18); }
+inline size_t row_bytes_of(int quant, int k) {
+    if (quant == 12 || quant == 14) return size_t(k / 256) * (quant == 12 ? 144 : 210);
+    return size_t((k + 31) / 32) * (quant == 8 ? 34 : 18);
+}
+void matmul_vec_kquant(int quant, float* out, const float* in, const uint8_t* w, int k, int n);
 
 // E:2047-2087 (Q8_0) / E:2910-2953 (Q4_0): one dot per output row.
 void matmul_vec(int quant, float* out, const float* in, const uint8_t* w, int k, int n) {
@@ -209,6 +213,10 @@ void matmul_vec(int quant, float* out, const float* in, const uint8_t* w, int k,
 // (the reference splits rows in chunks of 256 through rayon, E:2053).  `fast` selects the
 // row-vectorised twin (same values).
 void matmul_mat(int quant, float* out, int m, const float* in, const uint8_t* w, int k, int n, bool fast) {
+    if (quant == 12 || quant == 14) {  // K-quants: the per-token product, row by row (there is no batched form)
+        for (int r = 0; r < m; ++r) matmul_vec_kquant(quant, out + size_t(r) * n, in + size_t(r) * k, w, k, n);
+        return;
+    }
     size_t rb = row_bytes_of(quant, k);
     if (fast && (k % 32) == 0) {
         int groups = (n + 15) / 16;
@@ -713,7 +721,9 @@ struct FoConfig {
     int32_t quant;     // 8 = Q8_0, 4 = Q4_0
     int32_t qkv_bias;  // 1: f32 q/k/v biases follow v in weights.bin (Qwen2)
     int32_t sliding_window;  // > 0: sliding-window attention over that many positions (Mistral), E:97, E:191
+    int32_t proj_quant[8];   // ProjectionDTypes (ir.rs:411-421) as q, k, v, o, gate, up, down, lm_head; 0 = quant; 12 = Q4_K, 14 = Q6_K
 };
+inline int pq_of(const FoConfig& c, int i) { return c.proj_quant[i] ? c.proj_quant[i] : c.quant; }
 
 uint16_t fo_f32_to_f16(float x) { return f32_to_f16_bits(x); }
 float fo_f16_to_f32(uint16_t h) { return f16_bits_to_f32(h); }
@@ -888,10 +898,10 @@ struct FoKV {
 size_t fo_weights_bin_size(const FoConfig* c) {
     size_t h = c->hidden_size, qk = size_t(c->num_heads) * c->head_dim, kv = size_t(c->num_kv_heads) * c->head_dim;
     size_t ff = c->intermediate_size, V = c->vocab_size;
-    auto mb = [&](size_t n, size_t k) { return n * row_bytes_of(c->quant, int(k)); };
-    size_t per = h * 4 + mb(qk, h) + 2 * mb(kv, h) + (c->qkv_bias ? (qk + 2 * kv) * 4 : 0) + mb(h, qk) + h * 4 +
-                 2 * mb(ff, h) + mb(h, ff);
-    return V * h * 4 + per * c->num_layers + h * 4 + mb(V, h);
+    auto mb = [&](int cat, size_t n, size_t k) { return n * row_bytes_of(pq_of(*c, cat), int(k)); };
+    size_t per = h * 4 + mb(0, qk, h) + mb(1, kv, h) + mb(2, kv, h) + (c->qkv_bias ? (qk + 2 * kv) * 4 : 0) + mb(3, h, qk) + h * 4 +
+                 mb(4, ff, h) + mb(5, ff, h) + mb(6, h, ff);
+    return V * h * 4 + per * c->num_layers + h * 4 + mb(7, V, h);
 }
 
 FoModel* fo_model_create(const FoConfig* c, const uint8_t* blob, size_t len) {
@@ -901,25 +911,25 @@ FoModel* fo_model_create(const FoConfig* c, const uint8_t* blob, size_t len) {
     m->fast = 0;
     size_t h = c->hidden_size, qk = size_t(c->num_heads) * c->head_dim, kv = size_t(c->num_kv_heads) * c->head_dim;
     size_t ff = c->intermediate_size, V = c->vocab_size;
-    auto mb = [&](size_t n, size_t k) { return n * row_bytes_of(c->quant, int(k)); };
+    auto mb = [&](int cat, size_t n, size_t k) { return n * row_bytes_of(pq_of(*c, cat), int(k)); };
     const uint8_t* p = blob;
     m->embed = (const float*)p; p += V * h * 4;
     for (int l = 0; l < c->num_layers; ++l) {
         FoLayer L{};
         L.attn_norm = (const float*)p; p += h * 4;
-        L.q = p; p += mb(qk, h);
-        L.k = p; p += mb(kv, h);
-        L.v = p; p += mb(kv, h);
+        L.q = p; p += mb(0, qk, h);
+        L.k = p; p += mb(1, kv, h);
+        L.v = p; p += mb(2, kv, h);
         if (c->qkv_bias) {
             L.qb = (const float*)p; p += qk * 4;
             L.kb = (const float*)p; p += kv * 4;
             L.vb = (const float*)p; p += kv * 4;
         }
-        L.o = p; p += mb(h, qk);
+        L.o = p; p += mb(3, h, qk);
         L.ffn_norm = (const float*)p; p += h * 4;
-        L.gate = p; p += mb(ff, h);
-        L.up = p; p += mb(ff, h);
-        L.down = p; p += mb(h, ff);
+        L.gate = p; p += mb(4, ff, h);
+        L.up = p; p += mb(5, ff, h);
+        L.down = p; p += mb(6, h, ff);
         m->layers.push_back(L);
     }
     m->final_norm = (const float*)p; p += h * 4;
@@ -1000,9 +1010,9 @@ int fo_forward(const FoModel* m, FoKV* kv, uint32_t token, float* logits, float*
     for (int l = 0; l < c.num_layers; ++l) {
         const FoLayer& L = m->layers[l];
         rms_norm(nrm.data(), hid.data(), L.attn_norm, h, c.rms_norm_eps);
-        matmul_mat(c.quant, q.data(), 1, nrm.data(), L.q, h, qk, m->fast);
-        matmul_mat(c.quant, k.data(), 1, nrm.data(), L.k, h, kvs, m->fast);
-        matmul_mat(c.quant, v.data(), 1, nrm.data(), L.v, h, kvs, m->fast);
+        matmul_mat(pq_of(c, 0), q.data(), 1, nrm.data(), L.q, h, qk, m->fast);
+        matmul_mat(pq_of(c, 1), k.data(), 1, nrm.data(), L.k, h, kvs, m->fast);
+        matmul_mat(pq_of(c, 2), v.data(), 1, nrm.data(), L.v, h, kvs, m->fast);
         if (c.qkv_bias) {  // E:4108-4118
             for (int i = 0; i < qk; ++i) q[i] += L.qb[i];
             for (int i = 0; i < kvs; ++i) k[i] += L.kb[i];
@@ -1015,18 +1025,18 @@ int fo_forward(const FoModel* m, FoKV* kv, uint32_t token, float* logits, float*
         if (c.sliding_window > 0) attention_sliding(ao.data(), q.data(), view, pos + 1, c.sliding_window, c.num_heads, c.num_kv_heads, c.head_dim);  // E:4156
         else if (c.max_seq_len > 512) attention_flash(ao.data(), q.data(), view, pos + 1, c.num_heads, c.num_kv_heads, c.head_dim);  // E:126-128
         else attention_plain(ao.data(), q.data(), view, pos + 1, c.num_heads, c.num_kv_heads, c.head_dim);
-        matmul_mat(c.quant, ap.data(), 1, ao.data(), L.o, qk, h, m->fast);
+        matmul_mat(pq_of(c, 3), ap.data(), 1, ao.data(), L.o, qk, h, m->fast);
         residual_add(hid.data(), ap.data(), h);
         rms_norm(nrm.data(), hid.data(), L.ffn_norm, h, c.rms_norm_eps);
-        matmul_mat(c.quant, g.data(), 1, nrm.data(), L.gate, h, ff, m->fast);
-        matmul_mat(c.quant, u.data(), 1, nrm.data(), L.up, h, ff, m->fast);
+        matmul_mat(pq_of(c, 4), g.data(), 1, nrm.data(), L.gate, h, ff, m->fast);
+        matmul_mat(pq_of(c, 5), u.data(), 1, nrm.data(), L.up, h, ff, m->fast);
         silu_mul(fh.data(), g.data(), u.data(), ff);
-        matmul_mat(c.quant, fo.data(), 1, fh.data(), L.down, ff, h, m->fast);
+        matmul_mat(pq_of(c, 6), fo.data(), 1, fh.data(), L.down, ff, h, m->fast);
         residual_add(hid.data(), fo.data(), h);
         if (trace) std::memcpy(trace + size_t(l) * h, hid.data(), size_t(h) * 4);
     }
     rms_norm(nrm.data(), hid.data(), m->final_norm, h, c.rms_norm_eps);
-    matmul_mat(c.quant, logits, 1, nrm.data(), m->lm_head, h, c.vocab_size, m->fast);
+    matmul_mat(pq_of(c, 7), logits, 1, nrm.data(), m->lm_head, h, c.vocab_size, m->fast);
     kv->len += 1;
     return 0;
 }
@@ -1044,9 +1054,9 @@ static int forward_prefill_batched(const FoModel* m, FoKV* kv, const uint32_t* t
         const FoLayer& L = m->layers[l];
 #pragma omp parallel for
         for (int r = 0; r < n; ++r) rms_norm(&nrm[size_t(r) * h], &hid[size_t(r) * h], L.attn_norm, h, c.rms_norm_eps);
-        matmul_mat(c.quant, q.data(), n, nrm.data(), L.q, h, qk, m->fast);
-        matmul_mat(c.quant, k.data(), n, nrm.data(), L.k, h, kvs, m->fast);
-        matmul_mat(c.quant, v.data(), n, nrm.data(), L.v, h, kvs, m->fast);
+        matmul_mat(pq_of(c, 0), q.data(), n, nrm.data(), L.q, h, qk, m->fast);
+        matmul_mat(pq_of(c, 1), k.data(), n, nrm.data(), L.k, h, kvs, m->fast);
+        matmul_mat(pq_of(c, 2), v.data(), n, nrm.data(), L.v, h, kvs, m->fast);
 #pragma omp parallel for
         for (int r = 0; r < n; ++r) {  // E:5232-5285
             float *qr = &q[size_t(r) * qk], *kr = &k[size_t(r) * kvs], *vr = &v[size_t(r) * kvs];
@@ -1069,21 +1079,21 @@ static int forward_prefill_batched(const FoModel* m, FoKV* kv, const uint32_t* t
             for (int r = 0; r < n; ++r)
                 attention_plain(&ao[size_t(r) * qk], &q[size_t(r) * qk], view, base + r + 1, c.num_heads, c.num_kv_heads, c.head_dim);
         }
-        matmul_mat(c.quant, ap.data(), n, ao.data(), L.o, qk, h, m->fast);
+        matmul_mat(pq_of(c, 3), ap.data(), n, ao.data(), L.o, qk, h, m->fast);
         for (int r = 0; r < n; ++r) residual_add(&hid[size_t(r) * h], &ap[size_t(r) * h], h);
 #pragma omp parallel for
         for (int r = 0; r < n; ++r) rms_norm(&nrm[size_t(r) * h], &hid[size_t(r) * h], L.ffn_norm, h, c.rms_norm_eps);
-        matmul_mat(c.quant, g.data(), n, nrm.data(), L.gate, h, ff, m->fast);
-        matmul_mat(c.quant, u.data(), n, nrm.data(), L.up, h, ff, m->fast);
+        matmul_mat(pq_of(c, 4), g.data(), n, nrm.data(), L.gate, h, ff, m->fast);
+        matmul_mat(pq_of(c, 5), u.data(), n, nrm.data(), L.up, h, ff, m->fast);
 #pragma omp parallel for
         for (int r = 0; r < n; ++r) silu_mul(&fh[size_t(r) * ff], &g[size_t(r) * ff], &u[size_t(r) * ff], ff);
-        matmul_mat(c.quant, fo.data(), n, fh.data(), L.down, ff, h, m->fast);
+        matmul_mat(pq_of(c, 6), fo.data(), n, fh.data(), L.down, ff, h, m->fast);
         for (int r = 0; r < n; ++r) residual_add(&hid[size_t(r) * h], &fo[size_t(r) * h], h);
         if (trace) std::memcpy(trace + size_t(l) * M * h, hid.data(), M * h * 4);
     }
     std::vector<float> last(h);
     rms_norm(last.data(), &hid[(M - 1) * h], m->final_norm, h, c.rms_norm_eps);  // E:5439-5443
-    matmul_mat(c.quant, logits, 1, last.data(), m->lm_head, h, c.vocab_size, m->fast);
+    matmul_mat(pq_of(c, 7), logits, 1, last.data(), m->lm_head, h, c.vocab_size, m->fast);
     kv->len += n;
     return 0;
 }

@@ -30,6 +30,7 @@ class FoConfig(C.Structure):
         ("vocab_size", C.c_int32), ("max_seq_len", C.c_int32),
         ("rms_norm_eps", C.c_float), ("rope_theta", C.c_float),
         ("quant", C.c_int32), ("qkv_bias", C.c_int32), ("sliding_window", C.c_int32),
+        ("proj_quant", C.c_int32 * 8),
     ]
 
 
@@ -298,7 +299,8 @@ def attention_sliding_batch(qb, mode, k, v, ks, vs, m, base_pos, window, nh, nkv
 def make_config(d: dict) -> FoConfig:
     return FoConfig(d["hidden_size"], d["intermediate_size"], d["num_layers"], d["num_heads"], d["num_kv_heads"],
                     d["head_dim"], d["vocab_size"], d["max_seq_len"], d["rms_norm_eps"], d["rope_theta"],
-                    d["quant"], int(d.get("qkv_bias", 0)), int(d.get("sliding_window", 0) or 0))
+                    d["quant"], int(d.get("qkv_bias", 0)), int(d.get("sliding_window", 0) or 0),
+                    (C.c_int32 * 8)(*[int(v) for v in (d.get("proj_quant") or [0] * 8)]))
 
 
 class OracleModel:

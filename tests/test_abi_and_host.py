@@ -42,7 +42,9 @@ def test_product_never_touches_the_oracle():
 
 def test_weights_bin_size_agrees(oracle):
     from forge_llm_b200 import configs, runtime, synth
-    for c in list(configs.CONFIGS.values()) + [configs.tiny(4, bias=1)]:
+    mixed = [configs.tiny(12, ffn=512), configs.with_proj_quant(configs.tiny(12, ffn=512, bias=1), v=14, down=14, lm_head=14),
+             configs.with_proj_quant(configs.tiny(4), lm_head=8)]
+    for c in list(configs.CONFIGS.values()) + [configs.tiny(4, bias=1)] + mixed:
         oc = oracle.make_config(c)
         assert runtime.weights_bin_size(c) == synth.weights_bin_size(c) == oracle.lib().fo_weights_bin_size(C.byref(oc))
 

@@ -91,10 +91,13 @@ def synthetic_gguf(c: dict, tied: bool, embed_type: int = F32, arch: str = "llam
     """A GGUF file holding exactly the tensors of synth.make_weights_bin(c), under GGUF names."""
     blob = synth.make_weights_bin(c)
     h, qk, kv = c["hidden_size"], c["num_heads"] * c["head_dim"], c["num_kv_heads"] * c["head_dim"]
-    ff, V, q = c["intermediate_size"], c["vocab_size"], c["quant"]
-    bs = 34 if q == 8 else 18
-    qt = Q8_0 if q == 8 else Q4_0
+    ff, V = c["intermediate_size"], c["vocab_size"]
+    pq = configs.proj_quants(c)
+    gtype = {8: Q8_0, 4: Q4_0, 12: 12, 14: 14}  # the K-quants carry their GGML type numbers
     off = 0
+
+    def proj(name, dims, cat, n, k):
+        return (name, dims, gtype[pq[cat]], take(n * configs.raw_row_bytes(pq[cat], k)))
 
     def take(n):
         nonlocal off
@@ -111,23 +114,23 @@ def synthetic_gguf(c: dict, tied: bool, embed_type: int = F32, arch: str = "llam
     for l in range(c["num_layers"]):
         p = f"blk.{l}."
         tensors.append((p + "attn_norm.weight", [h], F32, take(h * 4)))
-        tensors.append((p + "attn_q.weight", [h, qk], qt, take(qk * h // 32 * bs)))
-        tensors.append((p + "attn_k.weight", [h, kv], qt, take(kv * h // 32 * bs)))
-        tensors.append((p + "attn_v.weight", [h, kv], qt, take(kv * h // 32 * bs)))
+        tensors.append(proj(p + "attn_q.weight", [h, qk], 0, qk, h))
+        tensors.append(proj(p + "attn_k.weight", [h, kv], 1, kv, h))
+        tensors.append(proj(p + "attn_v.weight", [h, kv], 2, kv, h))
         if c.get("qkv_bias"):
             tensors.append((p + "attn_q.bias", [qk], F32, take(qk * 4)))
             tensors.append((p + "attn_k.bias", [kv], F32, take(kv * 4)))
             tensors.append((p + "attn_v.bias", [kv], F32, take(kv * 4)))
-        tensors.append((p + "attn_output.weight", [qk, h], qt, take(h * qk // 32 * bs)))
+        tensors.append(proj(p + "attn_output.weight", [qk, h], 3, h, qk))
         tensors.append((p + "ffn_norm.weight", [h], F32, take(h * 4)))
-        tensors.append((p + "ffn_gate.weight", [h, ff], qt, take(ff * h // 32 * bs)))
-        tensors.append((p + "ffn_up.weight", [h, ff], qt, take(ff * h // 32 * bs)))
-        tensors.append((p + "ffn_down.weight", [ff, h], qt, take(h * ff // 32 * bs)))
+        tensors.append(proj(p + "ffn_gate.weight", [h, ff], 4, ff, h))
+        tensors.append(proj(p + "ffn_up.weight", [h, ff], 5, ff, h))
+        tensors.append(proj(p + "ffn_down.weight", [ff, h], 6, h, ff))
     tensors.append(("output_norm.weight", [h], F32, take(h * 4)))
-    head = take(V * h // 32 * bs)
+    head = proj("output.weight", [h, V], 7, V, h)
     assert off == blob.size
     if not tied:
-        tensors.append(("output.weight", [h, V], qt, head))
+        tensors.append(head)
     data, table = b"", []
     for name, dims, typ, raw in tensors[::-1]:  # file order differs from export order on purpose
         data += b"\0" * ((-len(data)) % 32)
@@ -150,6 +153,50 @@ def test_export_equals_the_reference_order_image(quant, bias):
         assert got[k] == c[k] if k != "qkv_bias" else got[k] == bias, k
     assert abs(got["rms_norm_eps"] - c["rms_norm_eps"]) < 1e-12 and got["rope_theta"] == c["rope_theta"]
     assert np.array_equal(g.weights_bin(), blob)
+
+
+def test_k_quant_file_keeps_its_per_category_formats(oracle):
+    """A Q4_K_M-shaped file (main.rs:603-607): Q4_K for q/k/o/gate/up, Q6_K for v/down/output.  The configuration
+    reports the mix, the projections are exported verbatim, and a K-quant embedding is dequantised to f32."""
+    base = configs.tiny(12, hd=64, nq=4, nkv=2, layers=2, ffn=512)
+    c = configs.with_proj_quant(base, v=14, down=14, lm_head=14)
+    raw, blob, _ = synthetic_gguf(c, tied=False)
+    g = gguf.GgufFile(raw)
+    got = g.config()
+    assert got["quant"] == 12 and got["proj_quant"] == [12, 12, 14, 12, 12, 12, 14, 14]
+    assert np.array_equal(g.weights_bin(), blob)
+    # uniform Q6_K projections under the same vote rules: other block formats count towards Q8_0 (main.rs:512-536),
+    # so the model format is Q8_0 and every category reports Q6_K
+    c6 = configs.tiny(14, hd=64, nq=4, nkv=2, layers=1, ffn=512)
+    raw6, blob6, _ = synthetic_gguf(c6, tied=False)
+    got6 = gguf.GgufFile(raw6).config()
+    assert got6["quant"] == 8 and got6["proj_quant"] == [14] * 8
+    assert np.array_equal(gguf.GgufFile(raw6).weights_bin(), blob6)
+
+
+def test_k_quant_embedding_is_dequantised_and_tied_head_stays_raw(oracle):
+    c = configs.tiny(12, hd=64, nq=4, nkv=2, layers=1, ffn=512)
+    V, h = c["vocab_size"], c["hidden_size"]
+    raw, blob, _ = synthetic_gguf(c, tied=False)
+    # rebuild the file with the head tensor renamed to the embedding: a tied model whose token_embd is Q4_K
+    head_bytes = V * configs.raw_row_bytes(12, h)
+    head = blob[-head_bytes:]
+    g0 = gguf.GgufFile(raw)
+    tensors, data = [], b""
+    for t in g0.tensors():
+        name, typ, dims, off, size = t["name"], t["type"], t["dims"], t["offset"], t["size"]
+        if name == "output.weight":
+            continue
+        payload = head.tobytes() if name == "token_embd.weight" else raw[g0.data_offset + off:g0.data_offset + off + size]
+        data += b"\0" * ((-len(data)) % 32)
+        tensors.append((name, dims, 12 if name == "token_embd.weight" else typ, len(data)))
+        data += payload
+    meta = [("general.architecture", 8, _s("llama")), ("llama.embedding_length", 4, u32(h)), ("llama.block_count", 4, u32(1)),
+            ("llama.attention.head_count", 4, u32(c["num_heads"])), ("llama.attention.head_count_kv", 4, u32(c["num_kv_heads"])),
+            ("llama.feed_forward_length", 4, u32(c["intermediate_size"])), ("llama.vocab_size", 4, u32(V))]
+    out = gguf.GgufFile(build_gguf(3, meta, tensors, data=data)).weights_bin()
+    assert np.array_equal(out[:V * h * 4].view(np.float32), oracle.dequant_kquant(12, head, V * h))
+    assert np.array_equal(out[-head_bytes:], head)
 
 
 @pytest.mark.parametrize("quant", [8, 4])

@@ -17,7 +17,7 @@ HIDDEN_TOL = 1e-3
 LOGIT_TOL = 2e-2
 
 
-def _run_case(oracle, c, n_prompt, n_decode, n_greedy=32, kv_cap=None, int8_report=True):
+def _run_case(oracle, c, n_prompt, n_decode, n_greedy=32, kv_cap=None, int8_report=True, row_tol=2 * HIDDEN_TOL, step_tol=HIDDEN_TOL):
     from forge_llm_b200 import runtime, synth
     blob = synth.make_weights_bin(c)
     toks = synth.prompt_tokens(c, n_prompt)
@@ -33,13 +33,13 @@ def _run_case(oracle, c, n_prompt, n_decode, n_greedy=32, kv_cap=None, int8_repo
     per_layer = [rel_l2(trg[l], tro[l]) for l in range(L)]
     worst_row = max(rel_l2(trg[L - 1, r], tro[L - 1, r]) for r in range(n_prompt))
     assert max(per_layer) < HIDDEN_TOL, per_layer
-    assert worst_row < 2 * HIDDEN_TOL
+    assert worst_row < row_tol
     assert np.abs(lg - lo).max() < LOGIT_TOL
     assert kv.len() == om.len == n_prompt
     # the cache itself: fp16 K/V rows of the first and last layer
     for layer in (0, L - 1):
         for which in (0, 1):
-            assert rel_l2(kv.read(layer, which), om.kv_read(layer, which)) < HIDDEN_TOL
+            assert rel_l2(kv.read(layer, which), om.kv_read(layer, which)) < max(HIDDEN_TOL, row_tol / 3)
 
     # teacher-forced decode: both sides are fed the oracle's greedy token
     for _ in range(n_decode):
@@ -47,7 +47,7 @@ def _run_case(oracle, c, n_prompt, n_decode, n_greedy=32, kv_cap=None, int8_repo
         lo, tr1 = om.forward(t, trace=True)
         lg = gm.forward(t, kv)
         tr2 = gm.read_trace(1)
-        assert max(rel_l2(tr2[l, 0], tr1[l]) for l in range(L)) < HIDDEN_TOL
+        assert max(rel_l2(tr2[l, 0], tr1[l]) for l in range(L)) < step_tol
         assert np.abs(lg - lo).max() < LOGIT_TOL
     gm.trace(False)
 
@@ -82,6 +82,48 @@ def test_tiny_models(oracle, quant, hd, nq, nkv, bias):
     from forge_llm_b200 import configs
     c = configs.tiny(quant, hd=hd, nq=nq, nkv=nkv, bias=bias, hidden=nq * hd if (nq * hd) % 32 == 0 else 448)
     _run_case(oracle, c, n_prompt=150, n_decode=4, n_greedy=32)
+
+
+KQ_CASES = {
+    "q4_k": dict(quant=12),
+    "q6_k": dict(quant=14),
+    # the mix the reference detects in Q4_K_M files (main.rs:603-607): Q4_K for q/k/o/gate/up, Q6_K for v/down/lm_head
+    "q4_k_m": dict(quant=12, mix=dict(v=14, down=14, lm_head=14)),
+    "q4_k_m_bias": dict(quant=12, bias=1, mix=dict(v=14, down=14, lm_head=14)),
+    # lm_head_dtype override (ir.rs:497-502): Q4_0 projections under a Q8_0 head, still on the batched prefill
+    "q4_0_head_q8_0": dict(quant=4, mix=dict(lm_head=8)),
+    # v_proj in another basic format than q/k: the split-V path without K-quants
+    "q8_0_v_q4_0": dict(quant=8, mix=dict(v=4)),
+}
+
+
+@pytest.mark.parametrize("case", sorted(KQ_CASES))
+def test_kquant_and_mixed_format_models(oracle, case):
+    """Per-projection storage formats (ProjectionDTypes): K-quant categories run the reference's per-token products
+    (Q8_0-quantised activations, integer block dots), also for the prompt.  The per-layer gate (1e-3 over the prompt),
+    the logit gate and the greedy ids are those of the Q8_0 / Q4_0 models.  Single rows get a wider bound where
+    activations are quantised: the two sides' f32 inputs to the 8-bit rounding differ in the last bits (summation
+    order, fp16 cache), so now and then one value lands on the other side of a rounding boundary and moves by a whole
+    step (1/127 of its block's maximum); the CPU restatement shows the same jump against itself when its embedding
+    is perturbed by 1e-6.  The products themselves are checked to 4e-6 on identical inputs in test_ops_gpu.py."""
+    from forge_llm_b200 import configs
+    k = KQ_CASES[case]
+    c = configs.tiny(k["quant"], hd=64, nq=4, nkv=2, bias=k.get("bias", 0), ffn=512)
+    if k.get("mix"):
+        c = configs.with_proj_quant(c, **k["mix"])
+    kq = any(q in (12, 14) for q in configs.proj_quants(c))
+    _run_case(oracle, c, n_prompt=37, n_decode=4, n_greedy=24, row_tol=3e-2 if kq else 2 * HIDDEN_TOL, step_tol=1e-2 if kq else HIDDEN_TOL)
+
+
+def test_mixed_format_rejections():
+    from forge_llm_b200 import configs, runtime, synth
+    from forge_llm_b200._lib import ForgeError
+    c = configs.with_proj_quant(configs.tiny(8, ffn=512), k=4)  # q and k are one fused product
+    with pytest.raises(ForgeError):
+        runtime.Model(c, np.zeros(16, np.uint8))
+    c = configs.with_proj_quant(configs.tiny(8, ffn=320), down=12)  # K-quant rows need K % 256 == 0
+    with pytest.raises(ForgeError):
+        runtime.Model(c, np.zeros(16, np.uint8))
 
 
 def test_short_prompt_takes_per_token_path(oracle):
