@@ -66,6 +66,8 @@ SIGNATURES = {
     "forge_attention_sliding_batch": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp]),
     "forge_quantize_q8_0_host": (i32, [vp, sz, vp]),
     "forge_quantize_q4_0_host": (i32, [vp, sz, vp, i32]),
+    "forge_quantize_q4_k_host": (i32, [vp, sz, vp]),
+    "forge_quantize_q6_k_host": (i32, [vp, sz, vp]),
     "forge_gguf_open": (i32, [vp, sz, C.POINTER(vp)]),
     "forge_gguf_close": (None, [vp]),
     "forge_gguf_version": (i32, [vp]),

@@ -363,8 +363,11 @@ int32_t put_f32_tensor(const ForgeGguf& g, const std::string& hf, uint64_t expec
 }
 
 int32_t put_quantised(const std::vector<float>& v, int32_t quant, Sink& s) {
-    std::vector<uint8_t> q(v.size() / 32 * (quant == FORGE_Q8_0 ? 34 : 18));
+    const bool kq = quant == FORGE_Q4_K || quant == FORGE_Q6_K;
+    std::vector<uint8_t> q(kq ? v.size() / 256 * (quant == FORGE_Q4_K ? 144 : 210) : v.size() / 32 * (quant == FORGE_Q8_0 ? 34 : 18));
     if (quant == FORGE_Q8_0) FORGE_TRY(forge_quantize_q8_0_host(v.data(), v.size(), q.data()));
+    else if (quant == FORGE_Q4_K) FORGE_TRY(forge_quantize_q4_k_host(v.data(), v.size(), q.data()));
+    else if (quant == FORGE_Q6_K) FORGE_TRY(forge_quantize_q6_k_host(v.data(), v.size(), q.data()));
     else FORGE_TRY(forge_quantize_q4_0_host(v.data(), v.size(), q.data(), 0));
     s.put(q.data(), q.size());
     return FORGE_OK;
@@ -400,10 +403,11 @@ Part find_projection(const ForgeGguf& g, const std::string& hf, uint64_t numel, 
     return {};
 }
 
-// a projection [rows][cols] of category `cat`: raw blocks when the tensor already has the category's block format;
-// dense tensors are quantised to Q8_0 / Q4_0 (the reference does this for f32 projections of Q4_0 models,
-// main.rs:2601-2607).  Re-quantisation to a K-quant (a Q4_K tensor in a Q6_K category, which the reference sends
-// through its own K-quant quantisers) is not carried out here.
+// a projection [rows][cols] of category `cat`: raw blocks when the tensor already has the category's block format.
+// Otherwise the tensor is dequantised and quantised again in the category's format, as the reference's loader does
+// for K-quant categories (load_from_file_mixed_per_tensor, weight_loader.rs:193-218: the alternating Q4_K / Q6_K
+// attn_v and ffn_down tensors of a Q4_K_M file) and its exporter for dense projections of Q4_0 models
+// (main.rs:2601-2607).  Source formats this reader cannot dequantise (Q4_1, Q5_x, Q2_K, Q3_K, Q5_K, I-quants) are reported.
 int32_t put_projection(const ForgeGguf& g, const std::string& hf, int cat, uint64_t rows, uint64_t cols, const ForgeModelConfig& c, Sink& s) {
     const int32_t quant = quant_of(c, cat);
     const uint64_t numel = rows * cols, rb = row_bytes(quant, cols);
@@ -422,12 +426,14 @@ int32_t put_projection(const ForgeGguf& g, const std::string& hf, int cat, uint6
         s.put(p + part.first / cols * rb, size_t(rows * rb));
         return FORGE_OK;
     }
-    if (!is_kquant(quant) && (t->type == T_F32 || t->type == T_F16 || t->type == T_BF16 || (t->type == T_Q8_0 && quant == FORGE_Q4_0))) {
+    const bool dense = t->type == T_F32 || t->type == T_F16 || t->type == T_BF16;
+    const bool blocks = t->type == T_Q8_0 || t->type == T_Q4_0 || t->type == T_Q4_K || t->type == T_Q6_K;
+    if ((dense && !is_kquant(quant)) || (blocks && (is_kquant(quant) || quant == FORGE_Q8_0 || t->type == T_Q8_0))) {
         std::vector<float> v;
         FORGE_TRY(to_f32(g, *t, numel, v, part.first));
         return put_quantised(v, quant, s);
     }
-    set_error("tensor %s: type %d in a category stored as format %d would need re-quantisation, which this exporter does not do", t->name.c_str(), t->type, quant);
+    set_error("tensor %s: type %d cannot be converted to the format %d of its category here", t->name.c_str(), t->type, quant);
     return FORGE_ERR_UNSUPPORTED;
 }
 

@@ -49,6 +49,14 @@ def quantize_q4_0(x: np.ndarray, signed_max: bool = True) -> np.ndarray:
     return out
 
 
+def quantize_kquant(quant: int, x: np.ndarray) -> np.ndarray:
+    """f32 -> Q4_K (quant 12) or Q6_K (quant 14) super-blocks with the exporter's host quantisers."""
+    x = np.ascontiguousarray(x, np.float32).ravel()
+    out = np.empty(x.size // 256 * (144 if quant == 12 else 210), np.uint8)
+    check((lib.forge_quantize_q4_k_host if quant == 12 else lib.forge_quantize_q6_k_host)(_p(x), x.size, _p(out)))
+    return out
+
+
 class KVCache:
     """``KVCache`` of the generated module (emit.rs:3954-4015): fp16, paged, ``batch`` sequences."""
 

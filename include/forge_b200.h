@@ -182,6 +182,11 @@ int32_t forge_attention_sliding_batch(float* out, const float* q_batch, const ui
  * d = largest-magnitude value / -8 with `signed_max` = 1).  n must be a multiple of 32. */
 int32_t forge_quantize_q8_0_host(const float* x, size_t n, uint8_t* out);
 int32_t forge_quantize_q4_0_host(const float* x, size_t n, uint8_t* out, int32_t signed_max);
+/* quantize_f32_to_q4_k (WL:1773-1900) / quantize_f32_to_q6_k (WL:2025-2125): n a multiple of 256; out receives
+ * n/256 super-blocks of 144 / 210 bytes.  The exporter uses them where a tensor is not stored in its category's
+ * format (load_from_file_mixed_per_tensor, WL:193-218). */
+int32_t forge_quantize_q4_k_host(const float* x, size_t n, uint8_t* out);
+int32_t forge_quantize_q6_k_host(const float* x, size_t n, uint8_t* out);
 
 /* ------------------------------------------------------------------------------------
  * Session surface: Weights / KVCache / forward / forward_prefill of the generated module.

@@ -378,6 +378,125 @@ void dequant_q6_k(const uint8_t* in, size_t n, float* out) {
     }
 }
 
+// ---------------------------------------------------------------- K-quant quantisers (exporter side)
+// WL:1663-1771 make_qkx2_quants(x, nmax = 15, rmin = -1, rdelta = 0.1, nstep = 20) on one 32-element sub-block:
+// returns scale and the_min (= -min) and fills L.
+void qkx2_fit(const float* x, float& scale_out, float& the_min_out, uint8_t* L) {
+    const int n = 32;
+    const float nmax = 15.0f;
+    float mn = x[0], mx = x[0];
+    for (int i = 1; i < n; ++i) { mn = std::min(mn, x[i]); mx = std::max(mx, x[i]); }
+    if (mx == mn) { scale_out = 0.0f; the_min_out = -mn; std::fill(L, L + n, uint8_t(0)); return; }
+    if (mn > 0.0f) mn = 0.0f;
+    float iscale = nmax / (mx - mn), scale = 1.0f / iscale, best_mad = 0.0f;
+    auto level = [&](float v, float is) { return std::min(nmax, std::max(0.0f, rround((v - mn) * is))); };
+    for (int i = 0; i < n; ++i) {
+        float li = level(x[i], iscale);
+        L[i] = uint8_t(li);
+        float diff = scale * li + mn - x[i];
+        best_mad += diff * diff;
+    }
+    float best_scale = scale, best_min = mn;
+    std::vector<uint8_t> laux(n);
+    for (int is = 0; is <= 20; ++is) {
+        float iscale_try = (-1.0f + 0.1f * float(is) + nmax) / (mx - mn);
+        float sum_l = 0, sum_l2 = 0, sum_x = 0, sum_xl = 0;
+        for (int i = 0; i < n; ++i) {
+            float li = level(x[i], iscale_try);
+            laux[i] = uint8_t(li);
+            sum_l += li; sum_l2 += li * li; sum_x += x[i]; sum_xl += li * x[i];
+        }
+        float det = float(n) * sum_l2 - sum_l * sum_l;
+        if (det > 0.0f) {
+            float this_scale = (float(n) * sum_xl - sum_x * sum_l) / det;
+            float this_min = (sum_l2 * sum_x - sum_l * sum_xl) / det;
+            if (this_min > 0.0f) { this_min = 0.0f; if (sum_l2 > 0.0f) this_scale = sum_xl / sum_l2; }
+            if (this_scale > 0.0f) {
+                float mad = 0.0f;
+                for (int i = 0; i < n; ++i) { float diff = this_scale * float(laux[i]) + this_min - x[i]; mad += diff * diff; }
+                if (mad < best_mad) { std::copy(laux.begin(), laux.end(), L); best_mad = mad; best_scale = this_scale; best_min = this_min; }
+            }
+        }
+    }
+    scale_out = best_scale;
+    the_min_out = -best_min;
+}
+
+// WL:1773-1900
+void quantize_q4_k(const float* data, size_t n, uint8_t* out) {
+    for (size_t sb = 0; sb < n / 256; ++sb) {
+        const float* x = data + sb * 256;
+        uint8_t* o = out + sb * 144;
+        float scales[8], mins[8];
+        uint8_t q[8][32];
+        for (int j = 0; j < 8; ++j) qkx2_fit(x + j * 32, scales[j], mins[j], q[j]);
+        float max_scale = 0.0f, max_min = 0.0f;
+        for (int j = 0; j < 8; ++j) { if (scales[j] > max_scale) max_scale = scales[j]; if (mins[j] > max_min) max_min = mins[j]; }
+        float inv_scale = max_scale > 0 ? 63.0f / max_scale : 0.0f, inv_min = max_min > 0 ? 63.0f / max_min : 0.0f;
+        float d = max_scale > 0 ? max_scale / 63.0f : 0.0f, dmin = max_min > 0 ? max_min / 63.0f : 0.0f;
+        uint8_t sq[8], mq[8];
+        for (int j = 0; j < 8; ++j) {
+            sq[j] = uint8_t(std::min(63.0f, std::max(0.0f, rround(scales[j] * inv_scale))));
+            mq[j] = uint8_t(std::min(63.0f, std::max(0.0f, rround(mins[j] * inv_min))));
+        }
+        uint16_t d_bits = f32_to_f16_bits(d), dmin_bits = f32_to_f16_bits(dmin);
+        float d_stored = f16_bits_to_f32(d_bits), dmin_stored = f16_bits_to_f32(dmin_bits);
+        for (int j = 0; j < 8; ++j) {
+            float s_eff = d_stored * float(sq[j]);
+            if (s_eff == 0.0f) { std::fill(q[j], q[j] + 32, uint8_t(0)); continue; }
+            float inv_s = 1.0f / s_eff, dm = dmin_stored * float(mq[j]);
+            for (int i = 0; i < 32; ++i) q[j][i] = uint8_t(std::min(15.0f, std::max(0.0f, rround((x[j * 32 + i] + dm) * inv_s))));
+        }
+        o[0] = uint8_t(d_bits); o[1] = uint8_t(d_bits >> 8); o[2] = uint8_t(dmin_bits); o[3] = uint8_t(dmin_bits >> 8);
+        for (int i = 0; i < 4; ++i) {
+            o[4 + i] = uint8_t((sq[i] & 63) | (((sq[i + 4] >> 4) & 3) << 6));
+            o[8 + i] = uint8_t((mq[i] & 63) | (((mq[i + 4] >> 4) & 3) << 6));
+            o[12 + i] = uint8_t((sq[i + 4] & 0x0F) | ((mq[i + 4] & 0x0F) << 4));
+        }
+        for (int c = 0; c < 4; ++c)
+            for (int i = 0; i < 32; ++i) o[16 + c * 32 + i] = uint8_t((q[2 * c][i] & 0x0F) | ((q[2 * c + 1][i] & 0x0F) << 4));
+    }
+}
+
+// WL:1989-2125
+void quantize_q6_k(const float* data, size_t n, uint8_t* out) {
+    for (size_t sb = 0; sb < n / 256; ++sb) {
+        const float* x = data + sb * 256;
+        uint8_t* o = out + sb * 210;
+        float sub[16];
+        for (int j = 0; j < 16; ++j) {
+            float mx = 0.0f, amax = 0.0f;
+            for (int i = 0; i < 16; ++i) { float av = std::fabs(x[j * 16 + i]); if (av > amax) { amax = av; mx = x[j * 16 + i]; } }
+            if (amax < 1e-30f) { sub[j] = 0.0f; continue; }
+            float iscale = -32.0f / mx;
+            sub[j] = 1.0f / iscale;
+        }
+        float max_scale = 0.0f, max_abs = 0.0f;
+        for (int j = 0; j < 16; ++j) if (std::fabs(sub[j]) > max_abs) { max_abs = std::fabs(sub[j]); max_scale = sub[j]; }
+        if (max_abs < 1e-30f) { std::fill(o, o + 210, uint8_t(0)); continue; }
+        float super_iscale = -128.0f / max_scale, super_d = 1.0f / super_iscale;
+        uint16_t d_bits = f32_to_f16_bits(super_d);
+        o[208] = uint8_t(d_bits); o[209] = uint8_t(d_bits >> 8);
+        float d_stored = f16_bits_to_f32(d_bits);
+        int8_t L[256] = {0};
+        for (int j = 0; j < 16; ++j) {
+            int qs = std::min(127, std::max(-128, int(rround(super_iscale * sub[j]))));
+            o[192 + j] = uint8_t(int8_t(qs));
+            float s_eff = d_stored * float(qs);
+            if (s_eff == 0.0f) continue;
+            float inv = 1.0f / s_eff;
+            for (int i = 0; i < 16; ++i) L[j * 16 + i] = int8_t(std::min(31, std::max(-32, int(rround(inv * x[j * 16 + i])))));
+        }
+        for (int chunk = 0; chunk < 256; chunk += 128)
+            for (int l = 0; l < 32; ++l) {
+                uint8_t q1 = uint8_t(L[chunk + l] + 32), q2 = uint8_t(L[chunk + l + 32] + 32), q3 = uint8_t(L[chunk + l + 64] + 32), q4 = uint8_t(L[chunk + l + 96] + 32);
+                o[chunk / 2 + l] = uint8_t((q1 & 0x0F) | ((q3 & 0x0F) << 4));
+                o[chunk / 2 + l + 32] = uint8_t((q2 & 0x0F) | ((q4 & 0x0F) << 4));
+                o[128 + chunk / 4 + l] = uint8_t((q1 >> 4) | ((q2 >> 4) << 2) | ((q3 >> 4) << 4) | ((q4 >> 4) << 6));
+            }
+    }
+}
+
 // ---------------------------------------------------------------- elementwise
 // E:298-304
 inline float dot_f32(const float* a, const float* b, int n) {
@@ -835,6 +954,8 @@ void fo_quantize_act_q8_0(const float* in, int k, int8_t* q, float* scale) { qua
 void fo_matmul_vec_kquant(int quant, float* out, int m, const float* in, const uint8_t* w, int k, int n) {
     for (int r = 0; r < m; ++r) matmul_vec_kquant(quant, out + size_t(r) * n, in + size_t(r) * k, w, k, n);
 }
+void fo_quantize_q4_k(const float* x, size_t n, uint8_t* out) { quantize_q4_k(x, n, out); }
+void fo_quantize_q6_k(const float* x, size_t n, uint8_t* out) { quantize_q6_k(x, n, out); }
 void fo_dequant_q4_k(const uint8_t* in, size_t n, float* out) { dequant_q4_k(in, n, out); }
 void fo_dequant_q6_k(const uint8_t* in, size_t n, float* out) { dequant_q6_k(in, n, out); }
 

@@ -66,6 +66,8 @@ def lib():
         "fo_matmul_mat_q4_0": (None, [_f32p, i, _f32p, _u8p, i, i, i]),
         "fo_quantize_act_q8_0": (None, [_f32p, i, np.ctypeslib.ndpointer(np.int8, flags="C_CONTIGUOUS"), _f32p]),
         "fo_matmul_vec_kquant": (None, [i, _f32p, i, _f32p, _u8p, i, i]),
+        "fo_quantize_q4_k": (None, [_f32p, sz, _u8p]),
+        "fo_quantize_q6_k": (None, [_f32p, sz, _u8p]),
         "fo_dequant_q4_k": (None, [_u8p, sz, _f32p]),
         "fo_dequant_q6_k": (None, [_u8p, sz, _f32p]),
         "fo_rms_norm": (None, [_f32p, _f32p, _f32p, i, f]),
@@ -186,6 +188,15 @@ def matmul_vec_kquant(quant: int, x: np.ndarray, w: np.ndarray, K: int, N: int) 
 def dequant_kquant(quant: int, b: np.ndarray, n: int) -> np.ndarray:
     out = np.empty(n, np.float32)
     (lib().fo_dequant_q4_k if quant == Q4_K else lib().fo_dequant_q6_k)(np.ascontiguousarray(b, np.uint8), n, out)
+    return out
+
+
+def quantize_kquant(quant: int, x: np.ndarray) -> np.ndarray:
+    """quantize_f32_to_q4_k / quantize_f32_to_q6_k (WL:1773-1900, :2025-2125); x.size must be a multiple of 256."""
+    x = np.ascontiguousarray(x, np.float32).ravel()
+    assert x.size % 256 == 0
+    out = np.empty(x.size // 256 * (144 if quant == Q4_K else 210), np.uint8)
+    (lib().fo_quantize_q4_k if quant == Q4_K else lib().fo_quantize_q6_k)(x, x.size, out)
     return out
 
 

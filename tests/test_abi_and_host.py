@@ -64,6 +64,19 @@ def test_host_quantisers_match_oracle_bit_for_bit(oracle):
     assert np.array_equal(synth.dequantize(4, q4, x.size), oracle.dequant_q4_0(q4, x.size))
 
 
+def test_host_kquant_quantisers_match_oracle_bit_for_bit(oracle):
+    from forge_llm_b200 import runtime
+    rng = np.random.default_rng(9)
+    n = 256 * 48
+    cases = [rng.standard_normal(n).astype(np.float32) * 0.05, np.zeros(n, np.float32), np.full(n, 0.3, np.float32),
+             (np.abs(rng.standard_normal(n)) + 1).astype(np.float32), ((np.arange(n) - n / 2) * 0.005).astype(np.float32)]
+    spiky = rng.standard_normal(n).astype(np.float32) * 0.02
+    spiky[::97] *= 30
+    for x in cases + [spiky]:
+        for q in (12, 14):
+            assert np.array_equal(runtime.quantize_kquant(q, x), oracle.quantize_kquant(q, x))
+
+
 def test_rope_table_matches_oracle(oracle):
     from forge_llm_b200._lib import lib
     for hd, theta in ((64, 1e5), (96, 1e4), (128, 5e5)):

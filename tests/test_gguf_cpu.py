@@ -174,6 +174,53 @@ def test_k_quant_file_keeps_its_per_category_formats(oracle):
     assert np.array_equal(gguf.GgufFile(raw6).weights_bin(), blob6)
 
 
+def test_tensors_off_their_category_format_are_requantised(oracle):
+    """A real Q4_K_M file alternates Q4_K and Q6_K for attn_v / ffn_down from layer to layer.  The category takes the
+    majority format (ties go to the higher precision, main.rs:628-660) and the other tensors are dequantised and
+    quantised again in it (weight_loader.rs:193-218)."""
+    base = configs.tiny(12, hd=64, nq=4, nkv=2, layers=2, ffn=512)
+    c = configs.with_proj_quant(base, v=14, down=14, lm_head=14)
+    raw, blob, _ = synthetic_gguf(c, tied=False)
+    g0 = gguf.GgufFile(raw)
+    h, kv, ff = c["hidden_size"], c["num_kv_heads"] * c["head_dim"], c["intermediate_size"]
+    # layer 1 keeps attn_v and ffn_down as Q4_K (1:1 tie -> Q6_K wins), layer 0 has them in Q6_K
+    rng = np.random.default_rng(77)
+    swapped = {"blk.1.attn_v.weight": synth.random_kquant(12, rng, kv, h, 0.02), "blk.1.ffn_down.weight": synth.random_kquant(12, rng, h, ff, 0.02)}
+    tensors, data = [], b""
+    for t in g0.tensors():
+        payload = raw[g0.data_offset + t["offset"]:g0.data_offset + t["offset"] + t["size"]]
+        typ = t["type"]
+        if t["name"] in swapped:
+            payload, typ = swapped[t["name"]].tobytes(), 12
+        data += b"\0" * ((-len(data)) % 32)
+        tensors.append((t["name"], t["dims"], typ, len(data)))
+        data += payload
+    meta = [("general.architecture", 8, _s("llama")), ("llama.embedding_length", 4, u32(h)), ("llama.block_count", 4, u32(2)),
+            ("llama.attention.head_count", 4, u32(c["num_heads"])), ("llama.attention.head_count_kv", 4, u32(c["num_kv_heads"])),
+            ("llama.feed_forward_length", 4, u32(ff)), ("llama.vocab_size", 4, u32(c["vocab_size"])),
+            ("llama.context_length", 4, u32(c["max_seq_len"]))]
+    g = gguf.GgufFile(build_gguf(3, meta, tensors, data=data))
+    assert g.config()["proj_quant"] == [12, 12, 14, 12, 12, 12, 14, 14]
+    out = g.weights_bin()
+    assert out.size == blob.size
+    # locate layer 1's v_proj and down_proj in the image and compare with dequantise -> quantise of the Q4_K payloads
+    V, qk = c["vocab_size"], c["num_heads"] * c["head_dim"]
+    rb = configs.raw_row_bytes
+    per_layer = h * 4 + qk * rb(12, h) + kv * rb(12, h) + kv * rb(14, h) + h * rb(12, qk) + h * 4 + 2 * ff * rb(12, h) + h * rb(14, ff)
+    l1 = V * h * 4 + per_layer
+    v_off = l1 + h * 4 + qk * rb(12, h) + kv * rb(12, h)
+    want_v = oracle.quantize_kquant(14, oracle.dequant_kquant(12, swapped["blk.1.attn_v.weight"], kv * h))
+    assert np.array_equal(out[v_off:v_off + kv * rb(14, h)], want_v)
+    d_off = l1 + per_layer - h * rb(14, ff)
+    want_d = oracle.quantize_kquant(14, oracle.dequant_kquant(12, swapped["blk.1.ffn_down.weight"], h * ff))
+    assert np.array_equal(out[d_off:d_off + h * rb(14, ff)], want_d)
+    # everything else is the verbatim image
+    keep = np.ones(out.size, bool)
+    keep[v_off:v_off + kv * rb(14, h)] = False
+    keep[d_off:d_off + h * rb(14, ff)] = False
+    assert np.array_equal(out[keep], blob[keep])
+
+
 def test_k_quant_embedding_is_dequantised_and_tied_head_stays_raw(oracle):
     c = configs.tiny(12, hd=64, nq=4, nkv=2, layers=1, ffn=512)
     V, h = c["vocab_size"], c["hidden_size"]

@@ -323,3 +323,33 @@ def test_activation_q8_0_blocks(oracle):
     q, s = oracle.quantize_act_q8_0(x)
     assert q[0] == -127 and q[31] == 127 and np.all(q[32:64] == 0) and s[1] == 1.0
     assert s[2] == 1.0 and q[64] == 1 and q[65] == -3 and np.all(q[66:96] == 127)
+
+
+# ---- K-quant quantisers: the reference's own tests (weight_loader.rs:2733-2975), run on the CPU restatement
+def test_quantize_q4_k_round_trips(oracle):
+    ramp = ((np.arange(512, dtype=np.float32) - np.float32(256.0)) * np.float32(0.005)).astype(np.float32)
+    q = oracle.quantize_kquant(oracle.Q4_K, ramp)
+    assert q.size == 2 * 144
+    assert np.abs(oracle.dequant_kquant(oracle.Q4_K, q, 512) - ramp).max() < 0.05          # WL:2735-2755
+    state, vals = 0xDEADBEEF, []
+    for _ in range(512):                                                                  # WL:2758-2780
+        state = (state * 1664525 + 1013904223) & 0xFFFFFFFF
+        vals.append((np.float32(state >> 16) / np.float32(65535.0) - np.float32(0.5)) * np.float32(0.2))
+    v = np.array(vals, np.float32)
+    d = oracle.dequant_kquant(oracle.Q4_K, oracle.quantize_kquant(oracle.Q4_K, v), 512)
+    assert np.sqrt(np.mean((d.astype(np.float64) - v) ** 2)) < 0.005
+    z = oracle.dequant_kquant(oracle.Q4_K, oracle.quantize_kquant(oracle.Q4_K, np.zeros(256, np.float32)), 256)
+    assert np.all(np.abs(z) < 1e-3)                                                        # WL:2895-2903
+
+
+def test_quantize_q6_k_round_trips_and_is_unbiased(oracle):
+    ramp = ((np.arange(512, dtype=np.float32) - np.float32(256.0)) * np.float32(0.005)).astype(np.float32)
+    q = oracle.quantize_kquant(oracle.Q6_K, ramp)
+    assert q.size == 2 * 210
+    assert np.abs(oracle.dequant_kquant(oracle.Q6_K, q, 512) - ramp).max() < 0.02          # WL:2906-2921
+    v = (np.random.default_rng(0xFEED).standard_normal(4096) * 0.05).astype(np.float32)    # WL:2924-2966 (Gaussian weights)
+    d = oracle.dequant_kquant(oracle.Q6_K, oracle.quantize_kquant(oracle.Q6_K, v), 4096).astype(np.float64)
+    err = d - v
+    assert abs(err.mean()) < 5.0 * np.sqrt(np.mean(err ** 2)) / np.sqrt(4096)
+    z = oracle.dequant_kquant(oracle.Q6_K, oracle.quantize_kquant(oracle.Q6_K, np.zeros(256, np.float32)), 256)
+    assert np.all(np.abs(z) < 1e-3)                                                        # WL:2969-2976
