@@ -17,7 +17,7 @@ HIDDEN_TOL = 1e-3
 LOGIT_TOL = 2e-2
 
 
-def _run_case(oracle, c, n_prompt, n_decode, n_greedy=32, kv_cap=None, int8_report=True, row_tol=2 * HIDDEN_TOL, step_tol=HIDDEN_TOL):
+def _run_case(oracle, c, n_prompt, n_decode, n_greedy=32, kv_cap=None, int8_report=True, row_tol=2 * HIDDEN_TOL, step_tol=HIDDEN_TOL, logit_tol=LOGIT_TOL, layer_tol=HIDDEN_TOL):
     from forge_llm_b200 import runtime, synth
     blob = synth.make_weights_bin(c)
     toks = synth.prompt_tokens(c, n_prompt)
@@ -32,9 +32,9 @@ def _run_case(oracle, c, n_prompt, n_decode, n_greedy=32, kv_cap=None, int8_repo
     trg = gm.read_trace(n_prompt)
     per_layer = [rel_l2(trg[l], tro[l]) for l in range(L)]
     worst_row = max(rel_l2(trg[L - 1, r], tro[L - 1, r]) for r in range(n_prompt))
-    assert max(per_layer) < HIDDEN_TOL, per_layer
+    assert max(per_layer) < layer_tol, per_layer
     assert worst_row < row_tol
-    assert np.abs(lg - lo).max() < LOGIT_TOL
+    assert np.abs(lg - lo).max() < logit_tol
     assert kv.len() == om.len == n_prompt
     # the cache itself: fp16 K/V rows of the first and last layer
     for layer in (0, L - 1):
@@ -48,7 +48,7 @@ def _run_case(oracle, c, n_prompt, n_decode, n_greedy=32, kv_cap=None, int8_repo
         lg = gm.forward(t, kv)
         tr2 = gm.read_trace(1)
         assert max(rel_l2(tr2[l, 0], tr1[l]) for l in range(L)) < step_tol
-        assert np.abs(lg - lo).max() < LOGIT_TOL
+        assert np.abs(lg - lo).max() < logit_tol
     gm.trace(False)
 
     # free-running greedy generation, token selection on the device
@@ -113,6 +113,19 @@ def test_kquant_and_mixed_format_models(oracle, case):
         c = configs.with_proj_quant(c, **k["mix"])
     kq = any(q in (12, 14) for q in configs.proj_quants(c))
     _run_case(oracle, c, n_prompt=37, n_decode=4, n_greedy=24, row_tol=3e-2 if kq else 2 * HIDDEN_TOL, step_tol=1e-2 if kq else HIDDEN_TOL)
+
+
+def test_kquant_mix_at_configuration_2_widths(oracle):
+    """The Q4_K_M mix on Llama-3.2-1B's layer shapes (two layers, 4096-entry vocabulary): wide 128-row bands, the
+    K = 8192 down projection, paired epilogues and the separate V product at real widths.  With ~30 k activations
+    rounded to 8 bits per token, a value crossing a rounding boundary is an every-token event here, so the
+    bounds are the wide ones (see test_kquant_and_mixed_format_models): the CPU restatement run against itself with
+    its embedding perturbed by 1e-6 moves by 1.6e-3 per layer and 2.6e-2 in the logits on this model."""
+    from forge_llm_b200 import configs
+    c = configs.reduced("c2", layers=2, vocab=4096)
+    c["quant"] = 12
+    c = configs.with_proj_quant(c, v=14, down=14, lm_head=14)
+    _run_case(oracle, c, n_prompt=9, n_decode=2, n_greedy=8, int8_report=False, row_tol=3e-2, step_tol=1e-2, logit_tol=5e-2, layer_tol=5e-3)
 
 
 def test_mixed_format_rejections():
