@@ -46,15 +46,15 @@ int32_t packed_build(int quant, const uint8_t* w, int K, int N, cudaStream_t st,
     pk->soa.K = K; pk->soa.N = N; pk->soa.quant = quant;
     pk->tiled.K = K; pk->tiled.N = N; pk->tiled.quant = quant; { int dev = 0, sms = 148; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
       pk->tiled.bt = gemv_band_tiles(N, sms); pk->tiled.bands = (N + 16 * pk->tiled.bt - 1) / (16 * pk->tiled.bt); }
-    const bool kq = is_kquant(quant);  // K-quants have the per-token product only: no layout for the batched GEMM
-    if (!kq) {
-        FORGE_CUDA(cudaMalloc(&pk->soa.qs, size_t(N) * pk->soa.qs_row_bytes()));
-        FORGE_CUDA(cudaMalloc(&pk->soa.d, size_t(N) * (K / 32) * sizeof(__half)));
-    }
+    const bool kq = is_kquant(quant);
+    if (kq) pk->soa.quant = FORGE_KQ_SOA;  // K-quant rows of either kind share the expanded row-major layout
+    FORGE_CUDA(cudaMalloc(&pk->soa.qs, size_t(N) * pk->soa.qs_row_bytes()));
+    if (kq) FORGE_CUDA(cudaMalloc(&pk->soa.sf, size_t(N) * (K / 32) * sizeof(float4)));
+    else FORGE_CUDA(cudaMalloc(&pk->soa.d, size_t(N) * (K / 32) * sizeof(__half)));
     FORGE_CUDA(cudaMalloc(&pk->tiled.data, qtiled_bytes(quant, K, N, pk->tiled.bt)));
     FORGE_CUDA(cudaMalloc(&pk->err, sizeof(int)));
     FORGE_CUDA(cudaMemsetAsync(pk->err, 0, sizeof(int), st));
-    if (!kq) FORGE_TRY(pack_rows(w, quant, K, 0, N, 0, K / 32, pk->soa, 0, 1, st));
+    FORGE_TRY(pack_rows(w, quant, K, 0, N, 0, K / 32, pk->soa, 0, 1, st));
     if (pk->tiled.bands * 16 * pk->tiled.bt <= kGemvSplitRows) {
         FORGE_CUDA(cudaMalloc(&pk->split.scratch, sizeof(float) * kGemvMaxSlices * size_t(pk->tiled.bands) * 16 * pk->tiled.bt));
         FORGE_CUDA(cudaMalloc(&pk->split.tickets, sizeof(int) * size_t(pk->tiled.bands) * pk->tiled.bt));
@@ -75,13 +75,13 @@ int32_t packed_build(int quant, const uint8_t* w, int K, int N, cudaStream_t st,
 
 void packed_free(ForgePacked* pk) {
     if (!pk) return;
-    cudaFree(pk->soa.qs); cudaFree(pk->soa.d); cudaFree(pk->tiled.data); cudaFree(pk->err); cudaFree(pk->split.scratch); cudaFree(pk->split.tickets);
+    cudaFree(pk->soa.qs); cudaFree(pk->soa.d); cudaFree(pk->soa.sf); cudaFree(pk->tiled.data); cudaFree(pk->err); cudaFree(pk->split.scratch); cudaFree(pk->split.tickets);
     delete pk;
 }
 
 int32_t matmul_packed(float* out, int32_t m, const float* in, const ForgePacked* pk, cudaStream_t st, bool check_err) {
     const int K = pk->soa.K;
-    if (m < FORGE_PREFILL_BATCH_THRESHOLD || is_kquant(pk->soa.quant)) {  // per-token path: the streaming GEMV, f32-exact up to summation order
+    if (m < FORGE_PREFILL_BATCH_THRESHOLD) {  // per-token path: the streaming GEMV, f32-exact up to summation order
         GemvArgs ga;
         ga.x = in; ga.out = out; ga.batch = m;
         FORGE_TRY(gemv_tc(pk->tiled, EPI_STORE, ga, pk->split, pk->err, st));
@@ -97,6 +97,8 @@ int32_t matmul_packed(float* out, int32_t m, const float* in, const ForgePacked*
     FORGE_CUDA(a16.alloc(size_t(m) * K * sizeof(__half)));
     FORGE_CUDA(a16lo.alloc(size_t(m) * K * sizeof(__half)));
     FORGE_TRY(f32_to_f16(static_cast<__half*>(a16.p), static_cast<__half*>(a16lo.p), in, size_t(m) * K, st));
+    // K-quant products take their input rows as Q8_0 blocks (emit.rs:1412-1440); the batched form keeps that rounding
+    if (pk->soa.quant == FORGE_KQ_SOA) FORGE_TRY(q8_round_f16(static_cast<__half*>(a16.p), static_cast<__half*>(a16lo.p), size_t(m) * K, st));
     return gemm_f16a(out, static_cast<const __half*>(a16.p), static_cast<const __half*>(a16lo.p), pk->soa, m, nullptr, pk->err, st);
 }
 

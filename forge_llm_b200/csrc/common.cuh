@@ -45,11 +45,17 @@ extern thread_local long long g_launches;  // kernels of this library launched o
 // Load-time layout of one projection: the 32 (Q8_0) or 16 (Q4_0) quant bytes of every block,
 // verbatim and contiguous per row, and the f16 block scales in a second array.  Same bytes
 // per weight as the GGUF stream (34/32 and 18/32), but every row starts 16-byte aligned.
+// Row-major layout of the batched GEMM.  Q8_0 / Q4_0: quant bytes verbatim + f16 block scales.  K-quant rows
+// (Q4_K and Q6_K alike, so rows of both may share one matrix) are expanded to FORGE_KQ_SOA: one int8 per weight
+// (the nibble 0..15, or q6 - 32) and per 32-element block a float4 {s_lo, s_hi, mn, 0} with
+// value = s_lo * q (k < 16) or s_hi * q (k >= 16), minus mn  (Q4_K: s_lo = s_hi = d*sc, mn = dmin*m; Q6_K: mn = 0).
+constexpr int FORGE_KQ_SOA = 100;
 struct QWeight {
     uint8_t* qs = nullptr;  // [N][K] int8  or  [N][K/2] nibble pairs
-    __half* d = nullptr;    // [N][K/32]
+    __half* d = nullptr;    // [N][K/32]  (Q8_0 / Q4_0)
+    float4* sf = nullptr;   // [N][K/32]  (FORGE_KQ_SOA)
     int K = 0, N = 0, quant = 0;
-    size_t qs_row_bytes() const { return quant == FORGE_Q8_0 ? size_t(K) : size_t(K) / 2; }
+    size_t qs_row_bytes() const { return quant == FORGE_Q4_0 ? size_t(K) / 2 : size_t(K); }
 };
 
 // raw GGUF rows [row0, row0+rows) x blocks [blk0, blk0+blks) of a [N][K/32] block matrix ->
@@ -196,6 +202,9 @@ int32_t argmax_last(uint32_t* result, const float* logits, int n, int batch, cud
 constexpr int kArgmaxSlices = 148;
 int32_t argmax_slices(uint32_t* result, const float* logits, int n, int batch, float* sval, int* sidx, int* ticket, cudaStream_t st);
 int32_t f32_to_f16(__half* out, __half* lo, const float* in, size_t n, cudaStream_t st);
+// In place: the rows (hi + lo) become their Q8_0 form q * f16(scale) per 32 values (emit.rs:1412-1440), the input of
+// every K-quant product, again split into hi + lo (exact: an 8-bit integer times an f16).
+int32_t q8_round_f16(__half* hi, __half* lo, size_t n, cudaStream_t st);
 int32_t step_advance(int32_t* seq_len, int batch, int32_t* step, cudaStream_t st, uint32_t* extra_counter = nullptr);
 int32_t token_nll(double* out, const float* logits, int n, uint32_t target, cudaStream_t st);  // -log softmax(logits)[target], f64
 int32_t gather_rows_f16(float* out, const __half* pool, const int32_t* page_row, int len, int kvd, cudaStream_t st);

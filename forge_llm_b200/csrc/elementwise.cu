@@ -356,6 +356,50 @@ int32_t argmax_slices(uint32_t* result, const float* logits, int n, int batch, f
     FORGE_LAUNCH_CHECK();
     return FORGE_OK;
 }
+// four threads per 32-value block, eight values each; whole warps stay in the loop (shuffles)
+__global__ void q8_round_f16_kernel(__half* __restrict__ hi, __half* __restrict__ lo, size_t groups) {
+    for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < ((groups + 31) & ~size_t(31)); i += size_t(gridDim.x) * blockDim.x) {
+        const bool on = i < groups;
+        float x[8];
+        uint4 h = make_uint4(0, 0, 0, 0), l = make_uint4(0, 0, 0, 0);
+        if (on) { h = reinterpret_cast<const uint4*>(hi)[i]; if (lo) l = reinterpret_cast<const uint4*>(lo)[i]; }
+        const __half2* hp = reinterpret_cast<const __half2*>(&h);
+        const __half2* lp = reinterpret_cast<const __half2*>(&l);
+        float amax = 0.f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 a = __half22float2(hp[j]), b = __half22float2(lp[j]);
+            x[2 * j] = a.x + b.x; x[2 * j + 1] = a.y + b.y;
+            amax = fmaxf(amax, fmaxf(fabsf(x[2 * j]), fabsf(x[2 * j + 1])));
+        }
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+        float bs = 1.0f, binv = 0.0f;
+        if (amax != 0.f) { bs = __fdiv_rn(amax, 127.0f); binv = __fdiv_rn(1.0f, bs); }
+        const float s16 = bs < 5.9604644775390625e-8f ? 0.f : __half2float(__float2half_rn(bs));  // the reference's f16 conversion flushes below 2^-24
+        uint4 oh, ol;
+        __half2* ohp = reinterpret_cast<__half2*>(&oh);
+        __half2* olp = reinterpret_cast<__half2*>(&ol);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float v0 = s16 * fminf(127.f, fmaxf(-127.f, roundf(x[2 * j] * binv)));
+            const float v1 = s16 * fminf(127.f, fmaxf(-127.f, roundf(x[2 * j + 1] * binv)));
+            ohp[j] = __floats2half2_rn(v0, v1);
+            const float2 hf = __half22float2(ohp[j]);
+            olp[j] = __floats2half2_rn(v0 - hf.x, v1 - hf.y);
+        }
+        if (on) { reinterpret_cast<uint4*>(hi)[i] = oh; if (lo) reinterpret_cast<uint4*>(lo)[i] = ol; }
+    }
+}
+
+int32_t q8_round_f16(__half* hi, __half* lo, size_t n, cudaStream_t st) {
+    if (n % 32) { set_error("q8_round_f16: n must be a multiple of 32"); return FORGE_ERR_SHAPE; }
+    if (n == 0) return FORGE_OK;
+    q8_round_f16_kernel<<<grid_for(n / 8), 256, 0, st>>>(hi, lo, n / 8);
+    FORGE_LAUNCH_CHECK();
+    return FORGE_OK;
+}
+
 int32_t f32_to_f16(__half* out, __half* lo, const float* in, size_t n, cudaStream_t st) {
     if (n == 0) return FORGE_OK;
     f32_to_f16_kernel<<<grid_for(n), 256, 0, st>>>(out, lo, in, n);

@@ -78,7 +78,7 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
 
 struct Tc5Params {
     float* out; const float* resid;
-    const uint8_t* qs; const __half* d;
+    const uint8_t* qs; const __half* d; const float4* sf;
     int m, N, K;
     int* err;
 };
@@ -134,6 +134,25 @@ __device__ __forceinline__ void dequant_block(const uint32_t* cur, __half2 d2, u
             }
             if (SPLIT) scale_split(q, d2, hi[4 * c + i], lo[4 * c + i]);
             else hi[4 * c + i] = as_u32(__hmul2(q, d2));
+        }
+    }
+}
+
+// K-quant rows in the expanded row-major layout (FORGE_KQ_SOA): 32 int8 values and {s_lo, s_hi, mn}; the value
+// s * q - mn is formed in f32 (one fused rounding) and split into hi = rn16(w), lo = rn16(w - hi): 22 bits of w.
+template <bool SPLIT>
+__device__ __forceinline__ void dequant_block_kq(const uint32_t* cur, float4 sc, uint32_t (&hi)[16], uint32_t (&lo)[16]) {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {  // register j = elements 2j, 2j + 1
+        const uint32_t word = cur[j >> 1];
+        const int q0 = int(int8_t(word >> (16 * (j & 1)))), q1 = int(int8_t(word >> (16 * (j & 1) + 8)));
+        const float s = j < 8 ? sc.x : sc.y;
+        const float w0 = fmaf(s, float(q0), -sc.z), w1 = fmaf(s, float(q1), -sc.z);
+        const __half2 h = __floats2half2_rn(w0, w1);
+        hi[j] = as_u32(h);
+        if (SPLIT) {
+            const float2 hf = __half22float2(h);
+            lo[j] = as_u32(__floats2half2_rn(w0 - hf.x, w1 - hf.y));
         }
     }
 }
@@ -218,23 +237,28 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_ts_kernel(const __grid_const
         const int r = quad * 32 + lane;
         const int n = n0 + r;
         const bool n_ok = n < p.N;
-        const size_t qrow = QUANT == FORGE_Q8_0 ? size_t(p.K) : size_t(p.K) / 2;
-        constexpr int QB = QUANT == FORGE_Q8_0 ? 32 : 16;
+        constexpr bool KQ = QUANT == FORGE_KQ_SOA;
+        const size_t qrow = QUANT == FORGE_Q4_0 ? size_t(p.K) / 2 : size_t(p.K);
+        constexpr int QB = QUANT == FORGE_Q4_0 ? 16 : 32;
         constexpr int QV = QB / 16;
         const uint8_t* qsrc = p.qs + size_t(n_ok ? n : 0) * qrow + size_t(blk) * QB;
-        const __half* dsrc = p.d + size_t(n_ok ? n : 0) * (p.K / 32) + blk;
+        const __half* dsrc = KQ ? nullptr : p.d + size_t(n_ok ? n : 0) * (p.K / 32) + blk;
+        const float4* fsrc = KQ ? p.sf + size_t(n_ok ? n : 0) * (p.K / 32) + blk : nullptr;
         constexpr int kPrefetch = 4;
         uint4 q[kPrefetch][QV];
         __half dsc[kPrefetch];
+        float4 fsc[KQ ? kPrefetch : 1];
         auto gload = [&](int kt, int slot) {
             if (n_ok && kt < nk) {
 #pragma unroll
                 for (int i = 0; i < QV; ++i) q[slot][i] = __ldg(reinterpret_cast<const uint4*>(qsrc + size_t(kt) * (2 * QB)) + i);
-                dsc[slot] = dsrc[2 * kt];
+                if (KQ) fsc[KQ ? slot : 0] = __ldg(fsrc + 2 * kt);
+                else dsc[slot] = dsrc[2 * kt];
             } else {
 #pragma unroll
                 for (int i = 0; i < QV; ++i) q[slot][i] = make_uint4(0, 0, 0, 0);
-                dsc[slot] = __float2half(0.f);
+                if (KQ) fsc[KQ ? slot : 0] = make_float4(0.f, 0.f, 0.f, 0.f);
+                else dsc[slot] = __float2half(0.f);
             }
         };
 #pragma unroll
@@ -263,9 +287,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_ts_kernel(const __grid_const
 #pragma unroll
                 for (int i = 0; i < QV; ++i) { cur[4 * i] = q[j][i].x; cur[4 * i + 1] = q[j][i].y; cur[4 * i + 2] = q[j][i].z; cur[4 * i + 3] = q[j][i].w; }
                 const __half2 d2 = __half2half2(dsc[j]);
+                const float4 f4 = fsc[KQ ? j : 0];
                 gload(kt + kPrefetch, j);
                 uint32_t hi[16], lo[16];
-                dequant_block<QUANT, SPLIT>(cur, d2, hi, lo);
+                if (KQ) dequant_block_kq<SPLIT>(cur, f4, hi, lo);
+                else dequant_block<QUANT == FORGE_KQ_SOA ? FORGE_Q8_0 : QUANT, SPLIT>(cur, d2, hi, lo);
                 if (kt > 0) publish((j + WS - 1) % WS);
                 if (ok && use > 0 && !mbar_wait(&empty_w[sw], (use - 1) & 1, &s_err)) { atomicExch(&s_err, 1); ok = false; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -368,7 +394,7 @@ bool gemm_tc5_supported(const QWeight& w) { return w.K % BK == 0 && w.K >= BK; }
 int32_t gemm_tc5(float* out, const __half* A, const __half* Alo, const QWeight& w, int m, const float* resid, int* err, cudaStream_t st) {
     if (m <= 0) return FORGE_OK;
     if (!gemm_tc5_supported(w)) { set_error("tcgen05 gemm: K=%d must be a multiple of %d", w.K, BK); return FORGE_ERR_SHAPE; }
-    Tc5Params p{out, resid, w.qs, w.d, m, w.N, w.K, err};
+    Tc5Params p{out, resid, w.qs, w.d, w.sf, m, w.N, w.K, err};
     const bool split = Alo != nullptr;
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
@@ -399,6 +425,7 @@ int32_t gemm_tc5(float* out, const __half* A, const __half* Alo, const QWeight& 
         return launch_ts<Q, 128, false>(A, Alo, p, st);                              \
     } while (0)
     if (w.quant == FORGE_Q8_0) FORGE_TS(FORGE_Q8_0);
+    if (w.quant == FORGE_KQ_SOA) FORGE_TS(FORGE_KQ_SOA);
     FORGE_TS(FORGE_Q4_0);
 #undef FORGE_TS
 }

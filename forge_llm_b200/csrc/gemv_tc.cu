@@ -48,6 +48,7 @@
 #include <cstdlib>
 
 #include "gemv_core.cuh"
+#include "kquant_decode.cuh"
 
 namespace forge {
 
@@ -114,44 +115,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tc_kernel(TcParams p) {
 // ------------------------------------------------------------------ packing
 // thread per (tile, lane): gathers the lane's A-fragment bytes from the two raw GGUF rows it owns
 // (rows g and g+8 of the 16-row tile; k = 4t..4t+3 and 16+4t..16+4t+3 of the block)
-__device__ __forceinline__ float f16_at(const uint8_t* p) { return __half2float(__ushort_as_half(uint16_t(p[0] | (p[1] << 8)))); }
-
-// One 32-element block (k-block kb of the row) of a raw K-quant row, as the fields the tile needs.
-// Q4_K (emit.rs:3013-3021, :3246-3303): sub-block j = kb % 8 of super-block kb / 8; s = d * sc_j, mn = dmin * m_j;
-// element k is the low (j even) or high (j odd) nibble of qs[(j / 2) * 32 + k].
-struct KBlock4 { float s = 0.f, mn = 0.f; const uint8_t* qs = nullptr; int shift = 0; };
-__device__ __forceinline__ KBlock4 kblock_q4_k(const uint8_t* row, int kb) {
-    KBlock4 b;
-    if (!row) return b;
-    const uint8_t* sb = row + size_t(kb >> 3) * 144;
-    const int j = kb & 7;
-    const uint8_t* sc = sb + 4;
-    int s6, m6;
-    if (j < 4) { s6 = sc[j] & 63; m6 = sc[j + 4] & 63; }
-    else { s6 = (sc[j + 4] & 0x0F) | ((sc[j - 4] >> 6) << 4); m6 = (sc[j + 4] >> 4) | ((sc[j] >> 6) << 4); }
-    b.s = f16_at(sb) * float(s6);
-    b.mn = f16_at(sb + 2) * float(m6);
-    b.qs = sb + 16 + (j >> 1) * 32;
-    b.shift = (j & 1) * 4;
-    return b;
-}
-// Q6_K (emit.rs:3560-3607): block j = kb % 8 reads ql[ql_off + l] >> nib and qh[qh_off + l] >> hsh; scale groups 2j, 2j+1.
-struct KBlock6 { float s_lo = 0.f, s_hi = 0.f; const uint8_t* ql = nullptr; const uint8_t* qh = nullptr; int nib = 0, hsh = 0; };
-__device__ __forceinline__ KBlock6 kblock_q6_k(const uint8_t* row, int kb) {
-    KBlock6 b;
-    if (!row) return b;
-    const uint8_t* sb = row + size_t(kb >> 3) * 210;
-    const int j = kb & 7;
-    const float d = f16_at(sb + 208);
-    b.s_lo = d * float(int(int8_t(sb[192 + 2 * j])));
-    b.s_hi = d * float(int(int8_t(sb[192 + 2 * j + 1])));
-    b.ql = sb + (j >> 2) * 64 + (j & 1) * 32;
-    b.qh = sb + 128 + (j >> 2) * 32;
-    b.nib = ((j >> 1) & 1) * 4;
-    b.hsh = (j & 3) * 2;
-    return b;
-}
-
 template <int QUANT>
 __global__ void tile_pack_kernel(const uint8_t* const* __restrict__ row_src, int KB, int bands, int bt, uint8_t* __restrict__ dst) {
     constexpr int BS = QUANT == FORGE_Q8_0 ? 34 : 18;
@@ -176,7 +139,7 @@ __global__ void tile_pack_kernel(const uint8_t* const* __restrict__ row_src, int
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const int k = h * 16 + 4 * t + j;  // byte j: low nibble = row g, high nibble = row g+8
-                    const uint32_t q0 = b0.qs ? (b0.qs[k] >> b0.shift) & 15u : 0u, q1 = b1.qs ? (b1.qs[k] >> b1.shift) & 15u : 0u;
+                    const uint32_t q0 = b0.q(k), q1 = b1.q(k);
                     w[h] |= (q0 | (q1 << 4)) << (8 * j);
                 }
             *reinterpret_cast<uint2*>(tp + 128 + lane * 8) = make_uint2(w[0], w[1]);
@@ -186,11 +149,7 @@ __global__ void tile_pack_kernel(const uint8_t* const* __restrict__ row_src, int
             uint8_t* tp = dst + size_t(tile) * T::BYTES;
             const KBlock6 b0 = kblock_q6_k(r0, kb), b1 = kblock_q6_k(r1, kb);
             if (t == 0) *reinterpret_cast<float4*>(tp + g * 16) = make_float4(b0.s_lo, b0.s_hi, b1.s_lo, b1.s_hi);
-            auto q6 = [](const KBlock6& b, int l) -> uint32_t {
-                if (!b.ql) return 0u;
-                const int v = int(((b.ql[l] >> b.nib) & 0x0F) | (((b.qh[l] >> b.hsh) & 3) << 4)) - 32;
-                return uint32_t(v) & 255u;
-            };
+            auto q6 = [](const KBlock6& b, int l) -> uint32_t { return uint32_t(b.q(l)) & 255u; };
             uint32_t w[4] = {0u, 0u, 0u, 0u};  // a0: row g, k lo; a1: row g+8, k lo; a2: row g, k hi; a3: row g+8, k hi
 #pragma unroll
             for (int h = 0; h < 2; ++h)

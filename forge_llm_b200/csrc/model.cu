@@ -71,7 +71,9 @@ struct ForgeModel {
     int gemm_passes = 3;  // 3: split-precision prefill GEMMs (default); 1: single fp16 pass
     int pq[8] = {0, 0, 0, 0, 0, 0, 0, 0};  // storage format of q, k, v, o, gate, up, down, lm_head (cfg.proj_quant or cfg.quant)
     bool uniform_basic = true;             // every projection is stored in cfg.quant (Q8_0 / Q4_0): what the whole-step kernel takes
-    bool per_token_prefill = false;        // K-quant (or split-V) models: the prompt runs token by token like the reference's forward_prefill
+    bool per_token_prefill = false;        // no batched layout for this mix of formats: the prompt always runs token by token
+    bool any_kquant = false;               // a projection is stored as Q4_K / Q6_K
+    bool kquant_batched = false;           // K-quant models: prompt through the batched GEMMs (forge_model_set_prefill_mode)
     TpComm* tp = nullptr;  // tensor-parallel communicator (cfg.tp_world > 1)
     // peer-memory exchange of the decode step (forge_model_tp_exchange_*): local buffer, peers' mappings, device tables
     void* tpx_local = nullptr; std::vector<void*> tpx_peer; bool tpx_ready = false;
@@ -119,7 +121,8 @@ int32_t dev_alloc(ForgeModel* m, T** p, size_t count) {
 int32_t alloc_qweight(ForgeModel* m, QWeight& w, int quant, int K, int N) {
     w.K = K; w.N = N; w.quant = quant;
     FORGE_TRY(dev_alloc(m, &w.qs, size_t(N) * w.qs_row_bytes()));
-    FORGE_TRY(dev_alloc(m, &w.d, size_t(N) * (K / 32)));
+    if (quant == FORGE_KQ_SOA) FORGE_TRY(dev_alloc(m, &w.sf, size_t(N) * (K / 32)));
+    else FORGE_TRY(dev_alloc(m, &w.d, size_t(N) * (K / 32)));
     return FORGE_OK;
 }
 
@@ -265,7 +268,7 @@ int32_t prefill_seq(ForgeModel* m, ForgeKV* kv, int seq, const uint32_t* tokens_
     cudaStream_t st = m->stream;
     const int base = kv->len[seq];
     FORGE_TRY(ensure_pages(kv, seq, base + n));
-    if (m->per_token_prefill) return prefill_per_token(m, kv, seq, tokens_host, n);
+    if (m->per_token_prefill || (m->any_kquant && !m->kquant_batched)) return prefill_per_token(m, kv, seq, tokens_host, n);
     FORGE_TRY(ensure_prefill_scratch(m, n));
     FORGE_TRY(ensure_decode_scratch(m, 1));
     if (m->trace_on) FORGE_TRY(ensure_trace(m, n));
@@ -281,14 +284,18 @@ int32_t prefill_seq(ForgeModel* m, ForgeKV* kv, int seq, const uint32_t* tokens_
         __half* kp = kv->k_pool + size_t(l) * kv->layer_stride;
         __half* vp = kv->v_pool + size_t(l) * kv->layer_stride;
         FORGE_TRY(rms_norm_f16(m->p_normed, nlo, m->p_hidden, L.attn_norm, n, m->h, c.rms_norm_eps, st));
+        if (L.qkv.quant == FORGE_KQ_SOA) FORGE_TRY(q8_round_f16(m->p_normed, nlo, size_t(n) * m->h, st));
         FORGE_TRY(gemm_f16a(m->p_qkv, m->p_normed, nlo, L.qkv, n, nullptr, m->d_err, st));
         FORGE_TRY(qkv_post(m->p_qkv, n, base, L.qkv_bias, m->rope, m->p_q16, kp, vp, page_row, m->qk, m->kv, m->hd, st));
         AttnPrefillArgs pa{m->p_attn16, alo, nullptr, m->p_q16, kp, vp, page_row, n, base, m->nq, m->nkv, m->hd, c.sliding_window};
         FORGE_TRY(attn_prefill(pa, st));
+        if (L.o.quant == FORGE_KQ_SOA) FORGE_TRY(q8_round_f16(m->p_attn16, alo, size_t(n) * m->qk, st));
         FORGE_TRY(row_sliced_gemm(m, L.o, m->p_attn16, alo, n, st));
         FORGE_TRY(rms_norm_f16(m->p_normed, nlo, m->p_hidden, L.ffn_norm, n, m->h, c.rms_norm_eps, st));
+        if (L.gateup.quant == FORGE_KQ_SOA) FORGE_TRY(q8_round_f16(m->p_normed, nlo, size_t(n) * m->h, st));
         FORGE_TRY(gemm_f16a(m->p_gu, m->p_normed, nlo, L.gateup, n, nullptr, m->d_err, st));
         FORGE_TRY(silu_mul_f16(m->p_act16, flo, m->p_gu, n, m->ff, st));
+        if (L.down.quant == FORGE_KQ_SOA) FORGE_TRY(q8_round_f16(m->p_act16, flo, size_t(n) * m->ff, st));
         FORGE_TRY(row_sliced_gemm(m, L.down, m->p_act16, flo, n, st));
         if (m->trace_on)
             FORGE_CUDA(cudaMemcpyAsync(m->trace + size_t(l) * n * m->h, m->p_hidden, sizeof(float) * n * m->h, cudaMemcpyDeviceToDevice, st));
@@ -513,11 +520,11 @@ int32_t forge_model_create(const ForgeModelConfig* cfg, const void* weights_bin,
     proj_quants(cfg, m->pq);
     const int* pq = m->pq;
     const bool split_v = pq[PQ_V] != pq[PQ_Q];
-    m->per_token_prefill = split_v;
-    for (int i = 0; i < 8; ++i) {
-        m->per_token_prefill = m->per_token_prefill || is_kquant(pq[i]);
-        m->uniform_basic = m->uniform_basic && pq[i] == cfg->quant && !is_kquant(pq[i]);
-    }
+    // The prompt takes the batched GEMMs unless q/k and v differ in a way the row-major layout cannot hold in one
+    // matrix (a basic format next to anything else); K-quant inputs are rounded to Q8_0 blocks in front of each GEMM.
+    m->per_token_prefill = split_v && !(is_kquant(pq[PQ_Q]) && is_kquant(pq[PQ_V]));
+    for (int i = 0; i < 8; ++i) m->any_kquant = m->any_kquant || is_kquant(pq[i]);
+    for (int i = 0; i < 8; ++i) m->uniform_basic = m->uniform_basic && pq[i] == cfg->quant && !is_kquant(pq[i]);
     const int H = cfg->hidden_size, QK = cfg->num_heads * cfg->head_dim, KV = cfg->num_kv_heads * cfg->head_dim, FF = cfg->intermediate_size;
     m->h = H; m->hd = cfg->head_dim; m->V = cfg->vocab_size;
     m->nq = cfg->num_heads / tp; m->nkv = cfg->num_kv_heads / tp;
@@ -551,25 +558,35 @@ int32_t forge_model_create(const ForgeModelConfig* cfg, const void* weights_bin,
     };
     // one source tensor of a group: raw [N_full][K_full/32] blocks on the host; this rank keeps rows
     // [row0, row0+rows) and blocks [blk0, blk0+blks), landing at destination rows dst_row0 + r*step
-    struct Part { const uint8_t* host; int N_full, K_full, row0, rows, blk0, blks, dst_row0, step; };
-    auto load_group = [&](int quant, const std::vector<Part>& parts, QWeight& soa, QTiled& tiled, int K_local, int N_local) -> int32_t {
-        const bool kq = is_kquant(quant);  // K-quants have the per-token product only: no layout for the batched GEMM
-        if (!kq) FORGE_TRY(alloc_qweight(m, soa, quant, K_local, N_local));
-        tiled.K = K_local; tiled.N = N_local; tiled.quant = quant; tiled.bt = gemv_band_tiles(N_local, sm_count); tiled.bands = (N_local + 16 * tiled.bt - 1) / (16 * tiled.bt);
-        FORGE_TRY(dev_alloc(m, &tiled.data, qtiled_bytes(quant, K_local, N_local, tiled.bt)));
-        std::vector<const uint8_t*> table(size_t(tiled.bands) * 16 * tiled.bt, nullptr);
+    struct Part { const uint8_t* host; int N_full, K_full, row0, rows, blk0, blks, dst_row0, step; int quant = 0; };
+    // `quant`: the format of the parts (a part may name its own: K-quant rows of both kinds share the row-major
+    // layout).  soa / tiled: which of the two layouts to build (null = skip).
+    auto load_group = [&](int quant, const std::vector<Part>& parts, QWeight* soa, QTiled* tiled, int K_local, int N_local) -> int32_t {
+        bool kq = false;
+        for (const Part& pt : parts) kq = kq || is_kquant(pt.quant ? pt.quant : quant);
+        if (soa) FORGE_TRY(alloc_qweight(m, *soa, kq ? FORGE_KQ_SOA : quant, K_local, N_local));
+        std::vector<const uint8_t*> table;
+        if (tiled) {
+            tiled->K = K_local; tiled->N = N_local; tiled->quant = quant; tiled->bt = gemv_band_tiles(N_local, sm_count); tiled->bands = (N_local + 16 * tiled->bt - 1) / (16 * tiled->bt);
+            FORGE_TRY(dev_alloc(m, &tiled->data, qtiled_bytes(quant, K_local, N_local, tiled->bt)));
+            table.assign(size_t(tiled->bands) * 16 * tiled->bt, nullptr);
+        }
         size_t off = 0;
         for (const Part& pt : parts) {
-            const size_t bytes = raw_bytes(quant, pt.N_full, pt.K_full);
+            const int pquant = pt.quant ? pt.quant : quant;
+            const size_t bytes = raw_bytes(pquant, pt.N_full, pt.K_full);
             FORGE_CUDA(cudaMemcpyAsync(stage + off, pt.host, bytes, cudaMemcpyHostToDevice, st));
-            if (!kq) FORGE_TRY(pack_rows(stage + off, quant, pt.K_full, pt.row0, pt.rows, pt.blk0, pt.blks, soa, pt.dst_row0, pt.step, st));
-            const size_t blk_bytes = kq ? 0 : (quant == FORGE_Q8_0 ? 34 : 18);  // K-quant rows are never sliced along K (one rank)
-            for (int r = 0; r < pt.rows; ++r)
-                table[size_t(pt.dst_row0) + size_t(r) * pt.step] = stage + off + size_t(pt.row0 + r) * raw_row_bytes(quant, pt.K_full) + pt.blk0 * blk_bytes;
+            if (soa) FORGE_TRY(pack_rows(stage + off, pquant, pt.K_full, pt.row0, pt.rows, pt.blk0, pt.blks, *soa, pt.dst_row0, pt.step, st));
+            const size_t blk_bytes = is_kquant(pquant) ? 0 : (pquant == FORGE_Q8_0 ? 34 : 18);  // K-quant rows are never sliced along K (one rank)
+            if (tiled)
+                for (int r = 0; r < pt.rows; ++r)
+                    table[size_t(pt.dst_row0) + size_t(r) * pt.step] = stage + off + size_t(pt.row0 + r) * raw_row_bytes(pquant, pt.K_full) + pt.blk0 * blk_bytes;
             off += (bytes + 15) & ~size_t(15);
         }
-        FORGE_CUDA(cudaMemcpyAsync(d_rowsrc, table.data(), table.size() * sizeof(uint8_t*), cudaMemcpyHostToDevice, st));
-        FORGE_TRY(tile_pack(d_rowsrc, tiled, st));
+        if (tiled) {
+            FORGE_CUDA(cudaMemcpyAsync(d_rowsrc, table.data(), table.size() * sizeof(uint8_t*), cudaMemcpyHostToDevice, st));
+            FORGE_TRY(tile_pack(d_rowsrc, *tiled, st));
+        }
         FORGE_CUDA(cudaStreamSynchronize(st));  // stage, table and the host vector are reused by the next group
         return FORGE_OK;
     };
@@ -586,11 +603,15 @@ int32_t forge_model_create(const ForgeModelConfig* cfg, const void* weights_bin,
         if (!split_v) {
             MC(load_group(pq[PQ_Q], {{wq, QK, H, rk * m->qk, m->qk, 0, H / 32, 0, 1},
                                      {wk, KV, H, rk * m->kv, m->kv, 0, H / 32, m->qk, 1},
-                                     {wv, KV, H, rk * m->kv, m->kv, 0, H / 32, m->qk + m->kv, 1}}, L.qkv, L.qkv_t, H, m->qk + 2 * m->kv));
+                                     {wv, KV, H, rk * m->kv, m->kv, 0, H / 32, m->qk + m->kv, 1}}, &L.qkv, &L.qkv_t, H, m->qk + 2 * m->kv));
         } else {
-            QWeight unused;
-            MC(load_group(pq[PQ_Q], {{wq, QK, H, 0, m->qk, 0, H / 32, 0, 1}, {wk, KV, H, 0, m->kv, 0, H / 32, m->qk, 1}}, L.qkv, L.qkv_t, H, m->qk + m->kv));
-            MC(load_group(pq[PQ_V], {{wv, KV, H, 0, m->kv, 0, H / 32, 0, 1}}, unused, L.v_t, H, m->kv));
+            // the streamed layout keeps V apart (its tiles differ); the row-major layout of the batched GEMM holds
+            // [q ; k ; v] in one matrix when both formats are K-quants (they share that layout)
+            MC(load_group(pq[PQ_Q], {{wq, QK, H, 0, m->qk, 0, H / 32, 0, 1}, {wk, KV, H, 0, m->kv, 0, H / 32, m->qk, 1}}, nullptr, &L.qkv_t, H, m->qk + m->kv));
+            MC(load_group(pq[PQ_V], {{wv, KV, H, 0, m->kv, 0, H / 32, 0, 1}}, nullptr, &L.v_t, H, m->kv));
+            if (!m->per_token_prefill)
+                MC(load_group(pq[PQ_Q], {{wq, QK, H, 0, m->qk, 0, H / 32, 0, 1, pq[PQ_Q]}, {wk, KV, H, 0, m->kv, 0, H / 32, m->qk, 1, pq[PQ_K]},
+                                         {wv, KV, H, 0, m->kv, 0, H / 32, m->qk + m->kv, 1, pq[PQ_V]}}, &L.qkv, nullptr, H, m->qk + 2 * m->kv));
         }
         if (cfg->qkv_bias) {
             MC(dev_alloc(m, &L.qkv_bias, size_t(m->qk + 2 * m->kv)));
@@ -603,16 +624,16 @@ int32_t forge_model_create(const ForgeModelConfig* cfg, const void* weights_bin,
             }
             p += size_t(QK + 2 * KV) * 4;
         }
-        MC(load_group(pq[PQ_O], {{p, H, QK, 0, H, rk * (m->qk / 32), m->qk / 32, 0, 1}}, L.o, L.o_t, m->qk, H)); p += raw_bytes(pq[PQ_O], H, QK);
+        MC(load_group(pq[PQ_O], {{p, H, QK, 0, H, rk * (m->qk / 32), m->qk / 32, 0, 1}}, &L.o, &L.o_t, m->qk, H)); p += raw_bytes(pq[PQ_O], H, QK);
         MC(upload_f32(&L.ffn_norm, H, p)); p += size_t(H) * 4;
         const uint8_t* pg = p; p += raw_bytes(pq[PQ_GATE], FF, H);
         const uint8_t* pu = p; p += raw_bytes(pq[PQ_UP], FF, H);
         MC(load_group(pq[PQ_GATE], {{pg, FF, H, rk * m->ff, m->ff, 0, H / 32, 0, 2}, {pu, FF, H, rk * m->ff, m->ff, 0, H / 32, 1, 2}},
-                      L.gateup, L.gateup_t, H, 2 * m->ff));
-        MC(load_group(pq[PQ_DOWN], {{p, H, FF, 0, H, rk * (m->ff / 32), m->ff / 32, 0, 1}}, L.down, L.down_t, m->ff, H)); p += raw_bytes(pq[PQ_DOWN], H, FF);
+                      &L.gateup, &L.gateup_t, H, 2 * m->ff));
+        MC(load_group(pq[PQ_DOWN], {{p, H, FF, 0, H, rk * (m->ff / 32), m->ff / 32, 0, 1}}, &L.down, &L.down_t, m->ff, H)); p += raw_bytes(pq[PQ_DOWN], H, FF);
     }
     MC(upload_f32(&m->final_norm, H, p)); p += size_t(H) * 4;
-    MC(load_group(pq[PQ_LM], {{p, cfg->vocab_size, H, 0, cfg->vocab_size, 0, H / 32, 0, 1}}, m->lm_head, m->lm_head_t, H, cfg->vocab_size));
+    MC(load_group(pq[PQ_LM], {{p, cfg->vocab_size, H, 0, cfg->vocab_size, 0, H / 32, 0, 1}}, pq[PQ_LM] == FORGE_Q8_0 || pq[PQ_LM] == FORGE_Q4_0 ? &m->lm_head : nullptr, &m->lm_head_t, H, cfg->vocab_size));
     MC(dev_alloc(m, &m->d_err, 1));
     MC(dev_alloc(m, &m->split.scratch, size_t(kGemvMaxSlices) * kGemvSplitRows));
     MC(dev_alloc(m, &m->split.tickets, size_t(kGemvSplitRows) / 16));
@@ -1092,6 +1113,13 @@ int32_t forge_generate_greedy(ForgeModel* m, ForgeKV* kv, const uint32_t* prompt
 int32_t forge_model_set_gemm_passes(ForgeModel* m, int32_t passes) {
     if (!m || (passes != 1 && passes != 3)) { set_error("gemm passes must be 1 or 3"); return FORGE_ERR_INVALID_ARG; }
     m->gemm_passes = passes;
+    return FORGE_OK;
+}
+
+int32_t forge_model_set_prefill_mode(ForgeModel* m, int32_t mode) {
+    if (!m || (mode != 0 && mode != 1)) { set_error("prefill mode must be 0 or 1"); return FORGE_ERR_INVALID_ARG; }
+    if (mode == 1 && m->per_token_prefill) { set_error("this mix of storage formats has no batched prompt path"); return FORGE_ERR_UNSUPPORTED; }
+    m->kquant_batched = mode == 1;
     return FORGE_OK;
 }
 

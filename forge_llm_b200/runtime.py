@@ -188,6 +188,10 @@ class Model:
         """3 = split-precision prefill GEMMs (default), 1 = a single fp16 tensor-core pass."""
         check(lib.forge_model_set_gemm_passes(self._h, passes))
 
+    def set_prefill_mode(self, mode: int) -> None:
+        """K-quant models: 0 = prompt token by token (default, the reference's structure), 1 = batched GEMMs."""
+        check(lib.forge_model_set_prefill_mode(self._h, mode))
+
     def set_decode_mode(self, mode: int) -> None:
         """0 = CUDA-graph replay of the per-operator kernels (default), 1 = one persistent kernel per step."""
         check(lib.forge_model_set_decode_mode(self._h, mode))

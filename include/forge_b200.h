@@ -232,6 +232,13 @@ int32_t forge_model_tp_exchange_attach(ForgeModel* model, const uint8_t* handles
  * relative to the reference's all-f32 arithmetic); 1: one fp16 pass (~3e-4 relative per GEMM,
  * which exceeds 1e-3 on the hidden state after ~20 layers). */
 int32_t forge_model_set_gemm_passes(ForgeModel* model, int32_t passes);
+/* Prompt path of a model with K-quant projections.  0 (default): token by token through the per-token products, the
+ * structure of the generated forward_prefill (E:4511-5050), which has no batched K-quant product.  1: the batched
+ * GEMMs, every K-quant product still taking its input rows as Q8_0 blocks; ~75x faster on a 1500-token prompt, but
+ * the batched attention's fp16 probabilities move its outputs by ~1e-4, enough to carry some values across an
+ * 8-bit rounding boundary in most rows (measured per-layer deviation 3e-3 on the tiny test models, against 1e-3
+ * for mode 0).  No effect on Q8_0 / Q4_0 models (always batched). */
+int32_t forge_model_set_prefill_mode(ForgeModel* model, int32_t mode);
 
 /* How batch-1 decode steps of sequence 0 are issued.  0 (default): one kernel per fused operator, the
  * step replayed as a CUDA graph.  1: the whole step as one persistent cooperative kernel (a CTA per SM,

@@ -115,6 +115,46 @@ def test_kquant_and_mixed_format_models(oracle, case):
     _run_case(oracle, c, n_prompt=37, n_decode=4, n_greedy=24, row_tol=3e-2 if kq else 2 * HIDDEN_TOL, step_tol=1e-2 if kq else HIDDEN_TOL)
 
 
+@pytest.mark.parametrize("case", ["q4_k", "q6_k", "q4_k_m_bias"])
+def test_kquant_batched_prompt_mode(oracle, case):
+    """forge_model_set_prefill_mode(1): the prompt of a K-quant model through the batched GEMMs (inputs still rounded to
+    Q8_0 blocks).  The batched attention's fp16 probabilities perturb its outputs by ~1e-4, which carries values across
+    8-bit rounding boundaries in most rows, so the bounds are wide here; the GEMM itself is checked on identical inputs
+    in test_ops_gpu.py::test_matmul_vec_kquant (m >= 8).  Also: both prompt modes leave caches that decode alike."""
+    from forge_llm_b200 import configs, runtime, synth
+    k = KQ_CASES[case]
+    c = configs.tiny(k["quant"], hd=64, nq=4, nkv=2, bias=k.get("bias", 0), ffn=512)
+    if k.get("mix"):
+        c = configs.with_proj_quant(c, **k["mix"])
+    blob = synth.make_weights_bin(c)
+    toks = synth.prompt_tokens(c, 37)
+    L = c["num_layers"]
+    om = oracle.OracleModel(c, blob, kv_mode=oracle.KV_F16)
+    lo, tro = om.forward_prefill(toks, trace=True)
+    gm = runtime.Model(c, blob)
+    kv = gm.new_cache(max_seq=96)
+    gm.set_prefill_mode(1)
+    gm.trace(True)
+    lg = gm.forward_prefill(toks, kv)
+    trg = gm.read_trace(37)
+    gm.trace(False)
+    assert max(rel_l2(trg[l], tro[l]) for l in range(L)) < 1e-2
+    assert np.abs(lg - lo).max() < 0.1
+    assert kv.len() == 37
+    for which in (0, 1):  # layer 0's cache comes from the first GEMM alone: exact up to fp16 ties
+        assert rel_l2(kv.read(0, which), om.kv_read(0, which)) < 1e-3
+    kv.reset()
+    ids_batched = gm.generate_greedy(toks, 8, kv)
+    gm.set_prefill_mode(0)
+    kv.reset()
+    ids_token = gm.generate_greedy(toks, 8, kv)
+    ref_ids, _ = oracle.OracleModel(c, blob, kv_mode=oracle.KV_F16).generate_greedy(toks, 8)
+    assert np.array_equal(ids_token, ref_ids)
+    assert (ids_batched == ref_ids).mean() >= 0.5  # the same continuation unless a near-tie flips
+    kv.close()
+    gm.close()
+
+
 def test_kquant_mix_at_configuration_2_widths(oracle):
     """The Q4_K_M mix on Llama-3.2-1B's layer shapes (two layers, 4096-entry vocabulary): wide 128-row bands, the
     K = 8192 down projection, paired epilogues and the separate V product at real widths.  With ~30 k activations

@@ -50,10 +50,12 @@ def test_matmul_mat(L, oracle, quant, m, K, N):
 
 @pytest.mark.parametrize("quant", [12, 14])
 @pytest.mark.parametrize("m,K,N", [(1, 256, 2), (1, 512, 130), (1, 2048, 512), (1, 8192, 2048), (1, 11008 // 256 * 256, 19000),
-                                   (3, 768, 130), (9, 1536, 144), (1, 2048, 32000)])
+                                   (3, 768, 130), (7, 1536, 144), (1, 2048, 32000),
+                                   (9, 1536, 144), (37, 512, 256), (37, 256, 512), (100, 2048, 520), (130, 8192, 256)])
 def test_matmul_vec_kquant(L, oracle, quant, m, K, N):
     """matmul_vec_q4_k / matmul_vec_q6_k: the input row is quantised to Q8_0 blocks as in the reference, the block dots
-    are exact integers, so the result agrees with the oracle up to the f32 summation order."""
+    are exact integers, so the result agrees with the oracle up to the f32 summation order.  From 8 rows on the rows
+    go through the tensor-core GEMM together (same Q8_0 rounding of the input, weights dequantised to split fp16)."""
     import torch
     lib, check = L
     rng = np.random.default_rng(100 * quant + m + K + N)
@@ -67,8 +69,14 @@ def test_matmul_vec_kquant(L, oracle, quant, m, K, N):
     check(fn(out.data_ptr(), m, dx.data_ptr(), dw.data_ptr(), K, N, None))
     _sync()
     got = out.cpu().numpy()
-    assert rel_l2(got, ref) < 4e-6
-    assert np.abs(got - ref).max() < 2e-4 * np.abs(ref).max()
+    if m < 8:
+        assert rel_l2(got, ref) < 4e-6
+        assert np.abs(got - ref).max() < 2e-4 * np.abs(ref).max()
+    else:
+        # the batched form rounds hi + lo of the f32 input (22 bits of it), so a value on a rounding boundary may land on
+        # the other side: allow a few such rows, everything else agrees to the GEMM's split-precision accuracy
+        rows = np.array([rel_l2(got[r], ref[r]) for r in range(m)])
+        assert np.median(rows) < 6e-5 and (rows > 6e-5).sum() <= max(1, m // 10) and rows.max() < 2e-2
 
 
 def test_matmul_vec_kquant_known_answer(L, oracle):
