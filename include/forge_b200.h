@@ -103,7 +103,8 @@ int32_t forge_matmul_mat_q4_0(float* out, int32_t m, const float* in, const uint
 /* matmul_vec_q4_k_{K}x{N}(output, input, weight)  E:3411-3487 (dot_q4_k_q8_0 E:3246-3303)
  * matmul_vec_q6_k_{K}x{N}(output, input, weight)  E:3636-3652 (dot_q6_k_q8_0 E:3553-3611)
  *   applied to each of the m rows of `in` (the generated module has no batched K-quant product).  As there, every
- *   input row is first quantised to Q8_0 blocks (E:1412-1440) and the block dots are exact integers.
+ *   input row is first quantised to Q8_0 blocks (E:1412-1440); below 8 rows the block dots are exact integers, from
+ *   8 rows on the rows share one tensor-core GEMM (weights dequantised to split fp16, ~1e-5 relative).
  *   out f32 [m][N], in f32 [m][K], w u8 [N][K/256][144 or 210]; K must be a multiple of 256. */
 int32_t forge_matmul_vec_q4_k(float* out, int32_t m, const float* in, const uint8_t* w,
                               int32_t K, int32_t N, void* stream);
