@@ -19,7 +19,7 @@ constexpr int kBandTiles = 8;                        // 16-row tiles per band in
 constexpr int kConsumerWarps = 16;                   // two warps per row tile (even / odd k-blocks of a chunk)
 constexpr int kCT = kConsumerWarps * 32;             // consumer threads
 constexpr int kThreads = (kConsumerWarps + 1) * 32;  // + one producer warp
-constexpr int kStages = 8;
+constexpr int kStages = 8;                           // most stages any format uses (Tile<QUANT>::STAGES)
 constexpr int kMaxKB = 352;                          // K <= 11264
 constexpr uint32_t kSpinLimit = 1u << 24;
 
@@ -32,8 +32,12 @@ inline bool is_kquant(int quant) { return quant == FORGE_Q4_K || quant == FORGE_
 template <int QUANT> struct KQuant { static constexpr bool value = QUANT == FORGE_Q4_K || QUANT == FORGE_Q6_K; };
 template <int QUANT> struct Tile {
     static constexpr int BYTES = QUANT == FORGE_Q4_0 ? 288 : QUANT == FORGE_Q8_0 ? 544 : QUANT == FORGE_Q4_K ? 384 : 640;
-    static constexpr int CHUNK_KB = (QUANT == FORGE_Q4_0) ? 8 : 4;          // k-blocks per pipeline stage
-    static constexpr int STAGE_BYTES = BYTES * CHUNK_KB * kBandTiles;       // 18432 / 17408 / 12288 / 20480
+    // k-blocks per pipeline stage and stages in the ring.  The per-stage work of a warp (wait, arrive, loop) is
+    // amortised over CHUNK_KB / 2 tiles, so the K-quants take 8 k-blocks per stage and fewer, larger stages
+    // (the bytes in flight stay at 144-160 KB per SM).
+    static constexpr int CHUNK_KB = (QUANT == FORGE_Q8_0) ? 4 : 8;
+    static constexpr int STAGES = QUANT == FORGE_Q4_K ? 6 : QUANT == FORGE_Q6_K ? 4 : kStages;
+    static constexpr int STAGE_BYTES = BYTES * CHUNK_KB * kBandTiles;       // 18432 / 17408 / 24576 / 40960
 };
 
 // ------------------------------------------------------------------ PTX helpers
@@ -91,7 +95,7 @@ __device__ __forceinline__ void unit_split(int u, int slices, int& band, int& sl
 // k-blocks per chunk (a power of two: a chunk is always CHUNK_KB * 8 tiles) and chunks per band
 template <int QUANT>
 __device__ __forceinline__ int chunk_kb_shift(int bt) {
-    constexpr int base = (QUANT == FORGE_Q4_0) ? 3 : 2;  // log2(CHUNK_KB)
+    constexpr int base = Tile<QUANT>::CHUNK_KB == 8 ? 3 : 2;  // log2(CHUNK_KB)
     return bt == kBandTiles ? base : base + 3;
 }
 
@@ -151,7 +155,7 @@ __device__ __forceinline__ bool produce_phase(const Phase& ph, Shared& sh, unsig
         unit_split(u, ph.slices, band, slice);
         slice_range(chunks_per_band, ph.slices, slice, c0, c1);
         for (int c = c0; c < c1; ++c, ++cc) {
-            const int st = cc % kStages, use = cc / kStages;
+            const int st = cc % T::STAGES, use = cc / T::STAGES;
             if (use > 0 && !hooked) { hooked = true; when_ring_full(); }
             if (use > 0 && !mbar_wait(&sh.empty_bar[st], (use - 1) & 1)) { atomicExch(&sh.err, 1); return false; }
             if (*reinterpret_cast<volatile int*>(&sh.err)) return false;
@@ -497,7 +501,7 @@ __device__ __forceinline__ void consume_phase(const Phase& ph, Shared& sh, const
         // per-lane accumulators: rows g / g+8 of this warp's row tile x digit columns 2t / 2t+1
         float acc[4] = {0.f, 0.f, 0.f, 0.f};
         for (int c = c0; c < c1; ++c, ++cc) {
-            const int st = cc % kStages, use = cc / kStages;
+            const int st = cc % T::STAGES, use = cc / T::STAGES;
             if (!mbar_wait(&sh.full_bar[st], use & 1)) atomicExch(&sh.err, 1);
             const int kb0 = c * ckb;
             const int nkb = min(ckb, KB - kb0);
@@ -657,7 +661,7 @@ __device__ __forceinline__ void consume_phase(const Phase& ph, Shared& sh, const
 
 // shared-memory bytes of the ring plus the activation fragments for the largest K in use
 template <int QUANT>
-inline size_t dyn_smem_bytes(int max_kb) { return size_t(kStages) * Tile<QUANT>::STAGE_BYTES + size_t(max_kb) * 128; }
+inline size_t dyn_smem_bytes(int max_kb) { return size_t(Tile<QUANT>::STAGES) * Tile<QUANT>::STAGE_BYTES + size_t(max_kb) * 128; }
 
 }  // namespace core
 }  // namespace forge

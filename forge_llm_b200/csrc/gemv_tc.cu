@@ -70,7 +70,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tc_kernel(TcParams p) {
     __shared__ Shared sh;
     __shared__ int4 s_xoff[QUANT == FORGE_Q4_0 ? 2 * kMaxKB : 1];
     unsigned char* ring = smem;
-    uint2* xf = reinterpret_cast<uint2*>(smem + size_t(kStages) * T::STAGE_BYTES);
+    uint2* xf = reinterpret_cast<uint2*>(smem + size_t(T::STAGES) * T::STAGE_BYTES);
     const int tid = threadIdx.x, warp = tid >> 5;
     pdl_trigger();  // the next kernel may be scheduled; it waits for this one before it reads any result
     if (tid == 0) {
@@ -230,7 +230,7 @@ int32_t launch(const QTiled& w, GemvEpilogue epi, const GemvArgs& a, const GemvS
 // least half of the SMs would idle; one batch row only (the scratch holds one row), never finer than one
 // pipeline chunk.
 int gemv_slices(const QTiled& w, const GemvSplit& sp, int sms, int batch) {
-    const int ckb = (w.quant == FORGE_Q4_0 ? 8 : 4) * (core::kBandTiles / w.bt);
+    const int ckb = (w.quant == FORGE_Q8_0 ? 4 : 8) * (core::kBandTiles / w.bt);
     const int chunks = (w.K / 32 + ckb - 1) / ckb;
     if (!sp.scratch || !sp.tickets || batch != 1 || 2 * w.bands > sms) return 1;
     int slices = (sms + w.bands - 1) / w.bands;
