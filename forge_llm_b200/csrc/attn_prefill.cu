@@ -50,14 +50,22 @@ __device__ __forceinline__ uint32_t pack_h2(float a, float b) {
     return *reinterpret_cast<uint32_t*>(&h);
 }
 
+__device__ __forceinline__ uint32_t pack_h2_lo(float a, float b, uint32_t hi) {  // what pack_h2 dropped
+    const float2 hf = __half22float2(*reinterpret_cast<const __half2*>(&hi));
+    return pack_h2(a - hf.x, b - hf.y);
+}
+
 // SW: sliding-window instantiation (the full-attention one carries no window tests)
-template <int HD, bool SW>
+// PRECISE: Q and P enter the MMAs as fp16 hi + lo pairs (S = Q_hi K + Q_lo K, O += P_hi V + P_lo V); K and V are the
+// cache's fp16 values either way, so the result is the f32 attention over those values to ~1e-6
+template <int HD, bool SW, bool PRECISE>
 __global__ void __launch_bounds__(kThreads) attn_prefill_kernel(PrefillParams p) {
     constexpr int LD = HD + 8;       // padded row (halfs): keeps ldmatrix rows on distinct banks
     constexpr int CH = HD / 8;       // 16-byte chunks per row
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __half* sQ = reinterpret_cast<__half*>(smem_raw);
     __half* sKV = sQ + BM * LD;  // [2 buffers][K | V][BN][LD]
+    __half* sQlo = sKV + 4 * BN * LD;  // PRECISE only
     const AttnPrefillArgs& a = p.a;
     const int qt = int(gridDim.x) - 1 - int(blockIdx.x), h = blockIdx.y;  // longest CTAs first
     const int G = a.nq / a.nkv, kvh = h / G, kvd = a.nkv * HD;
@@ -67,23 +75,32 @@ __global__ void __launch_bounds__(kThreads) attn_prefill_kernel(PrefillParams p)
 
     for (int idx = tid; idx < BM * CH; idx += kThreads) {
         int r = idx / CH, c = idx % CH, qr = row0 + r;
-        uint4 v = make_uint4(0, 0, 0, 0);
+        uint4 v = make_uint4(0, 0, 0, 0), vl = make_uint4(0, 0, 0, 0);
         if (qr < a.m) {
             if (p.q32) {
                 const float4* s = reinterpret_cast<const float4*>(p.q32 + qr * qstride + h * HD + c * 8);
                 float4 x0 = s[0], x1 = s[1];
                 v.x = pack_h2(x0.x, x0.y); v.y = pack_h2(x0.z, x0.w); v.z = pack_h2(x1.x, x1.y); v.w = pack_h2(x1.z, x1.w);
+                if (PRECISE) {
+                    vl.x = pack_h2_lo(x0.x, x0.y, v.x); vl.y = pack_h2_lo(x0.z, x0.w, v.y);
+                    vl.z = pack_h2_lo(x1.x, x1.y, v.z); vl.w = pack_h2_lo(x1.z, x1.w, v.w);
+                }
             } else {
                 v = *reinterpret_cast<const uint4*>(a.q16 + qr * qstride + h * HD + c * 8);
+                if (PRECISE && a.q16_lo) vl = *reinterpret_cast<const uint4*>(a.q16_lo + qr * qstride + h * HD + c * 8);
             }
         }
         *reinterpret_cast<uint4*>(sQ + r * LD + c * 8) = v;
+        if (PRECISE) *reinterpret_cast<uint4*>(sQlo + r * LD + c * 8) = vl;
     }
     __syncthreads();
     uint32_t qf[HD / 16][4];
+    uint32_t qfl[PRECISE ? HD / 16 : 1][4];
 #pragma unroll
-    for (int ks = 0; ks < HD / 16; ++ks)
+    for (int ks = 0; ks < HD / 16; ++ks) {
         ldsm_x4(qf[ks], smem_u32(sQ + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LD + ks * 16 + (lane >> 4) * 8));
+        if (PRECISE) ldsm_x4(qfl[PRECISE ? ks : 0], smem_u32(sQlo + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LD + ks * 16 + (lane >> 4) * 8));
+    }
 
     float o[HD / 8][4];
 #pragma unroll
@@ -135,6 +152,10 @@ __global__ void __launch_bounds__(kThreads) attn_prefill_kernel(PrefillParams p)
                 ldsm_x4(r, smem_u32(sK + (nb * 8 + (lane & 7)) * LD + ks * 16 + (lane >> 3) * 8));
                 mma16816(s[nb], qf[ks], r[0], r[1]);
                 mma16816(s[nb], qf[ks + 1], r[2], r[3]);
+                if (PRECISE) {
+                    mma16816(s[nb], qfl[PRECISE ? ks : 0], r[0], r[1]);
+                    mma16816(s[nb], qfl[PRECISE ? ks + 1 : 0], r[2], r[3]);
+                }
             }
         }
         // scale, causal mask (only where the tile reaches past the row), online softmax in base 2
@@ -185,12 +206,23 @@ __global__ void __launch_bounds__(kThreads) attn_prefill_kernel(PrefillParams p)
             pa[1] = pack_h2(s[2 * kk][2], s[2 * kk][3]);
             pa[2] = pack_h2(s[2 * kk + 1][0], s[2 * kk + 1][1]);
             pa[3] = pack_h2(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+            uint32_t pl[4] = {0u, 0u, 0u, 0u};
+            if (PRECISE) {
+                pl[0] = pack_h2_lo(s[2 * kk][0], s[2 * kk][1], pa[0]);
+                pl[1] = pack_h2_lo(s[2 * kk][2], s[2 * kk][3], pa[1]);
+                pl[2] = pack_h2_lo(s[2 * kk + 1][0], s[2 * kk + 1][1], pa[2]);
+                pl[3] = pack_h2_lo(s[2 * kk + 1][2], s[2 * kk + 1][3], pa[3]);
+            }
 #pragma unroll
             for (int nb2 = 0; nb2 < HD / 16; ++nb2) {
                 uint32_t r[4];
                 ldsm_x4_t(r, smem_u32(sV + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LD + nb2 * 16 + (lane >> 4) * 8));
                 mma16816(o[2 * nb2], pa, r[0], r[1]);
                 mma16816(o[2 * nb2 + 1], pa, r[2], r[3]);
+                if (PRECISE) {
+                    mma16816(o[2 * nb2], pl, r[0], r[1]);
+                    mma16816(o[2 * nb2 + 1], pl, r[2], r[3]);
+                }
             }
         }
         __syncthreads();  // the buffer is refilled by the prefetch of the next iteration
@@ -224,8 +256,9 @@ __global__ void __launch_bounds__(kThreads) attn_prefill_kernel(PrefillParams p)
 
 template <int HD>
 int32_t launch(const PrefillParams& p, cudaStream_t st) {
-    constexpr size_t smem = size_t(BM + 4 * BN) * (HD + 8) * sizeof(__half);
-    auto kern = p.a.window > 0 ? attn_prefill_kernel<HD, true> : attn_prefill_kernel<HD, false>;
+    const size_t smem = size_t((p.a.precise ? 2 : 1) * BM + 4 * BN) * (HD + 8) * sizeof(__half);
+    auto kern = p.a.precise ? (p.a.window > 0 ? attn_prefill_kernel<HD, true, true> : attn_prefill_kernel<HD, false, true>)
+                            : (p.a.window > 0 ? attn_prefill_kernel<HD, true, false> : attn_prefill_kernel<HD, false, false>);
     FORGE_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
     dim3 grid((p.a.m + BM - 1) / BM, p.a.nq);
     kern<<<grid, kThreads, smem, st>>>(p);

@@ -195,7 +195,7 @@ int32_t residual_add_f32(float* a, const float* b, size_t n, cudaStream_t st);
 int32_t embedding_rows(float* out, const float* table, const uint32_t* tokens, int rows, int h, uint32_t* hist, const int32_t* step, cudaStream_t st);
 int32_t kv_append_contig(__half* kc, __half* vc, const float* k, const float* v, int rows, int base_pos, int kvd, cudaStream_t st);
 // prefill QKV epilogue: bias, RoPE, q -> fp16 [m][qk], k/v -> paged fp16 cache
-int32_t qkv_post(const float* qkv, int m, int base_pos, const float* bias, const float* rope, __half* q16,
+int32_t qkv_post(const float* qkv, int m, int base_pos, const float* bias, const float* rope, __half* q16, __half* q16_lo,
                  __half* k_pool, __half* v_pool, const int32_t* page_row, int qk, int kv, int hd, cudaStream_t st);
 int32_t argmax_last(uint32_t* result, const float* logits, int n, int batch, cudaStream_t st);
 // many-CTA form; sval/sidx: [batch][kArgmaxSlices] scratch, ticket: [batch] zero-initialised counters
@@ -231,6 +231,10 @@ struct AttnPrefillArgs {
     const int32_t* page_row;                 // device [pages] physical page of logical page i (null = contiguous)
     int m, base_pos, nq, nkv, hd;
     int window = 0;                          // > 0: query position p sees keys [max(0, p - window + 1), p]
+    // precise: queries and probabilities enter the tensor cores as fp16 hi + lo pairs (two MMAs each), which takes the
+    // output from ~1e-4 to ~1e-6 of the f32 result; used where the output feeds an 8-bit rounding (K-quant models)
+    const __half* q16_lo = nullptr;          // [m][nq*hd] low parts of q16 (precise mode; null = zeros)
+    int precise = 0;
 };
 int32_t attn_prefill(const AttnPrefillArgs& a, cudaStream_t st);
 int32_t attn_prefill_q32(const AttnPrefillArgs& a, const float* q32, cudaStream_t st);  // f32 queries, converted on load

@@ -126,7 +126,7 @@ __global__ void kv_append_contig_kernel(__half* kc, __half* vc, const float* k, 
 
 // prefill glue: fused [q;k;v] f32 rows -> (+bias) -> RoPE on q,k -> q fp16, k/v into the paged cache
 __global__ void qkv_post_kernel(const float* __restrict__ qkv, int m, int base_pos, const float* __restrict__ bias,
-                                const float2* __restrict__ rope, __half* __restrict__ q16, __half* __restrict__ k_pool,
+                                const float2* __restrict__ rope, __half* __restrict__ q16, __half* __restrict__ q16_lo, __half* __restrict__ k_pool,
                                 __half* __restrict__ v_pool, const int32_t* __restrict__ page_row, int qk, int kv, int hd) {
     const int npairs = (qk + 2 * kv) / 2;
     const int r = blockIdx.x;
@@ -146,8 +146,13 @@ __global__ void qkv_post_kernel(const float* __restrict__ qkv, int m, int base_p
             v = make_float2(v.x * cs.x - v.y * cs.y, v.x * cs.y + v.y * cs.x);
         }
         __half2 hv = __floats2half2_rn(v.x, v.y);
-        if (region == 0) *reinterpret_cast<__half2*>(q16 + size_t(r) * qk + col) = hv;
-        else *reinterpret_cast<__half2*>((region == 1 ? k_pool : v_pool) + prow + col) = hv;
+        if (region == 0) {
+            *reinterpret_cast<__half2*>(q16 + size_t(r) * qk + col) = hv;
+            if (q16_lo) {  // the part of the query fp16 drops, for the precise attention
+                const float2 hf = __half22float2(hv);
+                *reinterpret_cast<__half2*>(q16_lo + size_t(r) * qk + col) = __floats2half2_rn(v.x - hf.x, v.y - hf.y);
+            }
+        } else *reinterpret_cast<__half2*>((region == 1 ? k_pool : v_pool) + prow + col) = hv;
     }
 }
 
@@ -338,10 +343,10 @@ int32_t kv_append_contig(__half* kc, __half* vc, const float* k, const float* v,
     FORGE_LAUNCH_CHECK();
     return FORGE_OK;
 }
-int32_t qkv_post(const float* qkv, int m, int base_pos, const float* bias, const float* rope, __half* q16,
+int32_t qkv_post(const float* qkv, int m, int base_pos, const float* bias, const float* rope, __half* q16, __half* q16_lo,
                  __half* k_pool, __half* v_pool, const int32_t* page_row, int qk, int kv, int hd, cudaStream_t st) {
     if (m <= 0) return FORGE_OK;
-    qkv_post_kernel<<<m, 256, 0, st>>>(qkv, m, base_pos, bias, reinterpret_cast<const float2*>(rope), q16, k_pool, v_pool, page_row, qk, kv, hd);
+    qkv_post_kernel<<<m, 256, 0, st>>>(qkv, m, base_pos, bias, reinterpret_cast<const float2*>(rope), q16, q16_lo, k_pool, v_pool, page_row, qk, kv, hd);
     FORGE_LAUNCH_CHECK();
     return FORGE_OK;
 }

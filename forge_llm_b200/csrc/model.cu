@@ -65,10 +65,11 @@ struct ForgeModel {
     std::vector<void*> allocs;
     // prefill scratch (grown on demand)
     int scratch_rows = 0, tok_cap = 0;
-    float* p_hidden = nullptr; __half* p_normed = nullptr; float* p_qkv = nullptr; __half* p_q16 = nullptr;
+    float* p_hidden = nullptr; __half* p_normed = nullptr; float* p_qkv = nullptr; __half* p_q16 = nullptr; __half* p_q16_lo = nullptr;
     __half* p_attn16 = nullptr; float* p_gu = nullptr; __half* p_act16 = nullptr; uint32_t* p_tokens = nullptr;
     __half* p_normed_lo = nullptr; __half* p_attn16_lo = nullptr; __half* p_act16_lo = nullptr;
     int gemm_passes = 3;  // 3: split-precision prefill GEMMs (default); 1: single fp16 pass
+    std::vector<struct ForgeKV*> caches;   // live caches of this model (released with it if the caller did not)
     int pq[8] = {0, 0, 0, 0, 0, 0, 0, 0};  // storage format of q, k, v, o, gate, up, down, lm_head (cfg.proj_quant or cfg.quant)
     bool uniform_basic = true;             // every projection is stored in cfg.quant (Q8_0 / Q4_0): what the whole-step kernel takes
     bool per_token_prefill = false;        // no batched layout for this mix of formats: the prompt always runs token by token
@@ -173,6 +174,7 @@ int32_t ensure_prefill_scratch(ForgeModel* m, int rows) {
     FORGE_TRY(dev_alloc(m, &m->p_normed, r * m->h));
     FORGE_TRY(dev_alloc(m, &m->p_qkv, r * (m->qk + 2 * m->kv)));
     FORGE_TRY(dev_alloc(m, &m->p_q16, r * m->qk));
+    FORGE_TRY(dev_alloc(m, &m->p_q16_lo, r * m->qk));
     FORGE_TRY(dev_alloc(m, &m->p_attn16, r * m->qk));
     FORGE_TRY(dev_alloc(m, &m->p_gu, r * 2 * m->ff));
     FORGE_TRY(dev_alloc(m, &m->p_act16, r * m->ff));
@@ -286,8 +288,11 @@ int32_t prefill_seq(ForgeModel* m, ForgeKV* kv, int seq, const uint32_t* tokens_
         FORGE_TRY(rms_norm_f16(m->p_normed, nlo, m->p_hidden, L.attn_norm, n, m->h, c.rms_norm_eps, st));
         if (L.qkv.quant == FORGE_KQ_SOA) FORGE_TRY(q8_round_f16(m->p_normed, nlo, size_t(n) * m->h, st));
         FORGE_TRY(gemm_f16a(m->p_qkv, m->p_normed, nlo, L.qkv, n, nullptr, m->d_err, st));
-        FORGE_TRY(qkv_post(m->p_qkv, n, base, L.qkv_bias, m->rope, m->p_q16, kp, vp, page_row, m->qk, m->kv, m->hd, st));
+        // K-quant models round the attention output to 8 bits in front of o_proj: the attention runs in its precise form
+        const bool precise = m->any_kquant;
+        FORGE_TRY(qkv_post(m->p_qkv, n, base, L.qkv_bias, m->rope, m->p_q16, precise ? m->p_q16_lo : nullptr, kp, vp, page_row, m->qk, m->kv, m->hd, st));
         AttnPrefillArgs pa{m->p_attn16, alo, nullptr, m->p_q16, kp, vp, page_row, n, base, m->nq, m->nkv, m->hd, c.sliding_window};
+        if (precise) { pa.q16_lo = m->p_q16_lo; pa.precise = 1; }
         FORGE_TRY(attn_prefill(pa, st));
         if (L.o.quant == FORGE_KQ_SOA) FORGE_TRY(q8_round_f16(m->p_attn16, alo, size_t(n) * m->qk, st));
         FORGE_TRY(row_sliced_gemm(m, L.o, m->p_attn16, alo, n, st));
@@ -475,6 +480,7 @@ int32_t decode_step_graph(ForgeModel* m, ForgeKV* kv, int batch, bool greedy) {
 
 int32_t check_seq(const ForgeKV* kv, int seq) {
     if (!kv || seq < 0 || seq >= kv->batch) { set_error("sequence index out of range"); return FORGE_ERR_INVALID_ARG; }
+    if (!kv->model) { set_error("the model of this cache has been destroyed"); return FORGE_ERR_INVALID_ARG; }
     return FORGE_OK;
 }
 
@@ -657,10 +663,14 @@ int32_t forge_model_create(const ForgeModelConfig* cfg, const void* weights_bin,
     return FORGE_OK;
 }
 
+static void kv_release_device(ForgeKV* kv);
+
 void forge_model_destroy(ForgeModel* m) {
     if (!m) return;
     cudaSetDevice(m->device);
     if (m->stream) cudaStreamSynchronize(m->stream);
+    for (ForgeKV* kv : m->caches) kv_release_device(kv);
+    m->caches.clear();
     tp_destroy(m->tp);
     for (void* q : m->tpx_peer) if (q) cudaIpcCloseMemHandle(q);
     if (m->tpx_local) cudaFree(m->tpx_local);
@@ -818,12 +828,13 @@ int32_t forge_kv_create(ForgeModel* m, int32_t max_seq, int32_t batch, ForgeKV**
         if (cudaStreamSynchronize(m->stream) != cudaSuccess) { set_error("KV init failed"); return fail(FORGE_ERR_CUDA); }
     }
     if (cudaStreamSynchronize(m->stream) != cudaSuccess) { set_error("KV init failed"); return fail(FORGE_ERR_CUDA); }
+    m->caches.push_back(kv);
     *out = kv;
     return FORGE_OK;
 }
 
 int32_t forge_kv_reset(ForgeKV* kv) {
-    if (!kv) { set_error("null kv"); return FORGE_ERR_INVALID_ARG; }
+    if (!kv || !kv->model) { set_error("null kv, or a cache whose model has been destroyed"); return FORGE_ERR_INVALID_ARG; }
     FORGE_CUDA(cudaSetDevice(kv->model->device));
     FORGE_CUDA(cudaStreamSynchronize(kv->model->stream));
     std::fill(kv->len.begin(), kv->len.end(), 0);
@@ -837,14 +848,29 @@ int32_t forge_kv_len(const ForgeKV* kv, int32_t seq) { return (kv && seq >= 0 &&
 
 void forge_kv_destroy(ForgeKV* kv) {
     if (!kv) return;
+    if (!kv->model) { delete kv; return; }  // the model went first and took the device memory with it
     cudaSetDevice(kv->model->device);
     cudaStreamSynchronize(kv->model->stream);
+    auto& reg = kv->model->caches;
+    reg.erase(std::remove(reg.begin(), reg.end(), kv), reg.end());
     if (kv->graph) cudaGraphExecDestroy(kv->graph);
     cudaFree(kv->k_pool); cudaFree(kv->v_pool); cudaFree(kv->d_page_table); cudaFree(kv->d_seq_len);
     cudaFree(kv->attn_ws); cudaFree(kv->attn_counters);
     cudaFree(kv->d_phases); cudaFree(kv->mega_ws); cudaFree(kv->d_bar);
     for (float* q : kv->mega_scr) cudaFree(q);
     delete kv;
+}
+
+// device memory of a cache whose model is being destroyed; the handle itself stays valid for forge_kv_destroy
+static void kv_release_device(ForgeKV* kv) {
+    if (kv->graph) cudaGraphExecDestroy(kv->graph);
+    cudaFree(kv->k_pool); cudaFree(kv->v_pool); cudaFree(kv->d_page_table); cudaFree(kv->d_seq_len);
+    cudaFree(kv->attn_ws); cudaFree(kv->attn_counters);
+    cudaFree(kv->d_phases); cudaFree(kv->mega_ws); cudaFree(kv->d_bar);
+    for (float*& q : kv->mega_scr) { cudaFree(q); q = nullptr; }
+    kv->graph = nullptr; kv->k_pool = kv->v_pool = nullptr; kv->d_page_table = kv->d_seq_len = nullptr;
+    kv->attn_ws = nullptr; kv->attn_counters = nullptr; kv->d_phases = nullptr; kv->mega_ws = nullptr; kv->d_bar = nullptr;
+    kv->model = nullptr;
 }
 
 int32_t forge_kv_read(ForgeKV* kv, int32_t seq, int32_t layer, int32_t which, float* out_host) {
@@ -910,7 +936,7 @@ int32_t kv_copy_rows(ForgeKV* kv, int seq, int layer, int which, int len, __half
 }  // namespace
 
 size_t forge_kv_save_size(const ForgeKV* kv, int32_t seq) {
-    if (!kv || seq < 0 || seq >= kv->batch) return 0;
+    if (!kv || !kv->model || seq < 0 || seq >= kv->batch) return 0;
     const ForgeModel* m = kv->model;
     return sizeof(KvHeader) + size_t(2) * m->cfg.num_layers * kv->len[seq] * m->kv * sizeof(__half);
 }

@@ -201,6 +201,8 @@ size_t forge_weights_bin_size(const ForgeModelConfig* cfg);
  * the rank keeps its column slice of q/k/v/gate/up and its row slice of o/down. */
 int32_t forge_model_create(const ForgeModelConfig* cfg, const void* weights_bin, size_t len,
                            int32_t device, ForgeModel** out);
+/* Also releases the device memory of caches of this model that are still alive; their handles stay valid for
+ * forge_kv_destroy only (every other call on them reports an error), so the two can be destroyed in either order. */
 void forge_model_destroy(ForgeModel* model);
 /* The CUDA stream (cudaStream_t) all work of this model is launched on. */
 void* forge_model_stream(ForgeModel* model);
@@ -235,10 +237,11 @@ int32_t forge_model_tp_exchange_attach(ForgeModel* model, const uint8_t* handles
 int32_t forge_model_set_gemm_passes(ForgeModel* model, int32_t passes);
 /* Prompt path of a model with K-quant projections.  0 (default): token by token through the per-token products, the
  * structure of the generated forward_prefill (E:4511-5050), which has no batched K-quant product.  1: the batched
- * GEMMs, every K-quant product still taking its input rows as Q8_0 blocks; ~75x faster on a 1500-token prompt, but
- * the batched attention's fp16 probabilities move its outputs by ~1e-4, enough to carry some values across an
- * 8-bit rounding boundary in most rows (measured per-layer deviation 3e-3 on the tiny test models, against 1e-3
- * for mode 0).  No effect on Q8_0 / Q4_0 models (always batched). */
+ * GEMMs, every K-quant product still taking its input rows as Q8_0 blocks, and the attention in its precise form
+ * (queries and probabilities as fp16 hi + lo pairs); ~75x faster on a 1500-token prompt.  The GEMMs carry their
+ * operands as 22-bit fp16 pairs, so their outputs differ from the per-token integer dots by ~1e-6, which moves a
+ * value across an 8-bit rounding boundary in about one row of five on the tiny test models (per-layer deviation
+ * 1e-3 .. 4e-3 there, against < 1e-3 for mode 0).  No effect on Q8_0 / Q4_0 models (always batched). */
 int32_t forge_model_set_prefill_mode(ForgeModel* model, int32_t mode);
 
 /* How batch-1 decode steps of sequence 0 are issued.  0 (default): one kernel per fused operator, the

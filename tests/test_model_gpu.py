@@ -118,9 +118,10 @@ def test_kquant_and_mixed_format_models(oracle, case):
 @pytest.mark.parametrize("case", ["q4_k", "q6_k", "q4_k_m_bias"])
 def test_kquant_batched_prompt_mode(oracle, case):
     """forge_model_set_prefill_mode(1): the prompt of a K-quant model through the batched GEMMs (inputs still rounded to
-    Q8_0 blocks).  The batched attention's fp16 probabilities perturb its outputs by ~1e-4, which carries values across
-    8-bit rounding boundaries in most rows, so the bounds are wide here; the GEMM itself is checked on identical inputs
-    in test_ops_gpu.py::test_matmul_vec_kquant (m >= 8).  Also: both prompt modes leave caches that decode alike."""
+    Q8_0 blocks, attention in its precise hi + lo form).  The split-fp16 GEMM operands leave ~1e-6 in every product,
+    which carries a value across an 8-bit rounding boundary in about one row of five, so the bounds are wide here; the
+    GEMM itself is checked on identical inputs in test_ops_gpu.py::test_matmul_vec_kquant (m >= 8).  Also: both
+    prompt modes leave caches that decode alike."""
     from forge_llm_b200 import configs, runtime, synth
     k = KQ_CASES[case]
     c = configs.tiny(k["quant"], hd=64, nq=4, nkv=2, bias=k.get("bias", 0), ffn=512)
@@ -166,6 +167,20 @@ def test_kquant_mix_at_configuration_2_widths(oracle):
     c["quant"] = 12
     c = configs.with_proj_quant(c, v=14, down=14, lm_head=14)
     _run_case(oracle, c, n_prompt=9, n_decode=2, n_greedy=8, int8_report=False, row_tol=3e-2, step_tol=1e-2, logit_tol=5e-2, layer_tol=5e-3)
+
+
+def test_model_and_cache_may_be_destroyed_in_either_order():
+    from forge_llm_b200 import configs, runtime, synth
+    from forge_llm_b200._lib import ForgeError
+    c = configs.tiny(8)
+    gm = runtime.Model(c, synth.make_weights_bin(c))
+    kv = gm.new_cache(max_seq=64)
+    gm.forward_prefill(synth.prompt_tokens(c, 9), kv)
+    gm.close()                      # the model first: the cache's device memory goes with it
+    with pytest.raises(ForgeError):
+        kv.reset()
+    assert kv.len() == 9            # host-side state is still readable
+    kv.close()                      # and the handle can still be released
 
 
 def test_mixed_format_rejections():
