@@ -18,16 +18,28 @@ CASES = {  # name -> arguments of configs.tiny
     "q4_hd64_gqa": dict(quant=4, hd=64, nq=4, nkv=2, layers=2),
     "q4_hd128_mha_bias": dict(quant=4, hd=128, nq=2, nkv=2, bias=1, layers=3),
     "q8_hd96_gqa": dict(quant=8, hd=96, nq=4, nkv=1, layers=2, hidden=384),
+    # K-quants: uniform Q6_K, and the Q4_K_M mix (Q4_K for q/k/o/gate/up, Q6_K for v/down/lm_head); "mix" names the
+    # categories configs.with_proj_quant overrides
+    "q6k_hd64_gqa": dict(quant=14, hd=64, nq=4, nkv=2, layers=2, ffn=512),
+    "q4km_hd64_gqa_bias": dict(quant=12, hd=64, nq=4, nkv=2, layers=2, ffn=512, bias=1, mix=dict(v=14, down=14, lm_head=14)),
 }
 N_PROMPT, N_NEW = 37, 12
 
 
+def case_config(name):
+    from forge_llm_b200 import configs
+    kw = dict(CASES[name])
+    mix = kw.pop("mix", None)
+    c = configs.tiny(**kw)
+    return configs.with_proj_quant(c, **mix) if mix else c
+
+
 def main():
-    from forge_llm_b200 import configs, synth
+    from forge_llm_b200 import synth
     from oracle import oracle
     out = {}
-    for name, kw in CASES.items():
-        c = configs.tiny(**kw)
+    for name in CASES:
+        c = case_config(name)
         blob = synth.make_weights_bin(c)
         toks = synth.prompt_tokens(c, N_PROMPT)
         om = oracle.OracleModel(c, blob, kv_mode=oracle.KV_F16)

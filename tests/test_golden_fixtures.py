@@ -18,8 +18,8 @@ GOLD = np.load(os.path.join(HERE, "golden", "tiny_models.npz"))
 
 
 def _inputs(name):
-    from forge_llm_b200 import configs, synth
-    c = configs.tiny(**mg.CASES[name])
+    from forge_llm_b200 import synth
+    c = mg.case_config(name)
     return c, synth.make_weights_bin(c), synth.prompt_tokens(c, mg.N_PROMPT)
 
 
@@ -39,7 +39,7 @@ def test_oracle_reproduces_fixture(name, oracle):
 @pytest.mark.gpu
 @pytest.mark.parametrize("name", sorted(mg.CASES))
 def test_cuda_path_matches_fixture(name):
-    from forge_llm_b200 import runtime
+    from forge_llm_b200 import configs, runtime
     c, blob, toks = _inputs(name)
     gm = runtime.Model(c, blob)
     kv = gm.new_cache(max_seq=mg.N_PROMPT + mg.N_NEW + 8)
@@ -47,8 +47,11 @@ def test_cuda_path_matches_fixture(name):
     lg = gm.forward_prefill(toks, kv)
     tr = gm.read_trace(mg.N_PROMPT)
     gm.trace(False)
-    assert np.abs(lg - GOLD[name + "/prefill_logits"]).max() < 2e-2
-    assert rel_l2(tr[-1, -1], GOLD[name + "/last_hidden"]) < 1e-3
+    # K-quant models round activations to 8 bits: a value on a rounding boundary may land on the other side (see
+    # test_model_gpu.py::test_kquant_and_mixed_format_models), so their single-row bounds are wider
+    kq = any(q in (12, 14) for q in configs.proj_quants(c))
+    assert np.abs(lg - GOLD[name + "/prefill_logits"]).max() < (5e-2 if kq else 2e-2)
+    assert rel_l2(tr[-1, -1], GOLD[name + "/last_hidden"]) < (3e-2 if kq else 1e-3)
     kv.reset()
     ids = gm.generate_greedy(toks, mg.N_NEW, kv)
     assert np.array_equal(ids, GOLD[name + "/greedy_ids"])
