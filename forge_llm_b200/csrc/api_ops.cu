@@ -44,8 +44,12 @@ size_t raw_row_bytes(int quant, int K) {
 
 int32_t packed_build(int quant, const uint8_t* w, int K, int N, cudaStream_t st, ForgePacked* pk) {
     pk->soa.K = K; pk->soa.N = N; pk->soa.quant = quant;
-    pk->tiled.K = K; pk->tiled.N = N; pk->tiled.quant = quant; { int dev = 0, sms = 148; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-      pk->tiled.bt = gemv_band_tiles(N, sms); pk->tiled.bands = (N + 16 * pk->tiled.bt - 1) / (16 * pk->tiled.bt); }
+    pk->tiled.K = K; pk->tiled.N = N; pk->tiled.quant = quant;
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    pk->tiled.bt = gemv_band_tiles(N, sms);
+    pk->tiled.bands = (N + 16 * pk->tiled.bt - 1) / (16 * pk->tiled.bt);
     const bool kq = is_kquant(quant);
     if (kq) pk->soa.quant = FORGE_KQ_SOA;  // K-quant rows of either kind share the expanded row-major layout
     FORGE_CUDA(cudaMalloc(&pk->soa.qs, size_t(N) * pk->soa.qs_row_bytes()));

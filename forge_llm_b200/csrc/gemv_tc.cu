@@ -43,7 +43,8 @@
 // f32 scale fields (see Tile in gemv_core.cuh), and the activation is staged as the Q8_0 blocks those functions
 // quantise their input to (one int8 B column instead of four digit columns), so the integer dots are the
 // reference's own.  Q6_K's two 16-element scale groups per block come out of ONE MMA: B column 0 holds k 0..15
-// only and column 1 holds k 16..31 only.
+// only and column 1 holds k 16..31 only.  Their pipeline stages hold 8 k-blocks (6 / 4 stages in the ring): a warp's
+// per-stage work (barrier wait, arrive, loop) is then spread over four tiles instead of two.
 #include <algorithm>
 #include <cstdlib>
 
