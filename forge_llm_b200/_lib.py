@@ -76,6 +76,7 @@ SIGNATURES = {
     "forge_gguf_tensor_info": (i32, [vp, C.c_int64, C.POINTER(C.c_char_p), C.POINTER(i32), C.POINTER(i32), C.POINTER(C.c_uint64),
                                     C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
     "forge_gguf_model_config": (i32, [vp, C.POINTER(ForgeModelConfig)]),
+    "forge_gguf_tensor_to_f32": (i32, [vp, C.c_int64, vp, sz]),
     "forge_gguf_weights_bin_size": (sz, [vp]),
     "forge_gguf_export_weights_bin": (i32, [vp, vp, sz]),
     "forge_weights_bin_size": (sz, [C.POINTER(ForgeModelConfig)]),

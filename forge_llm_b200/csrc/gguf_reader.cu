@@ -21,7 +21,7 @@ using namespace forge;
 
 constexpr uint32_t kMagic = 0x46554747u;  // "GGUF"
 constexpr uint64_t kDefaultAlignment = 32;
-enum : int32_t { T_F32 = 0, T_F16 = 1, T_Q4_0 = 2, T_Q8_0 = 8, T_Q4_K = 12, T_Q6_K = 14, T_BF16 = 30 };
+enum : int32_t { T_F32 = 0, T_F16 = 1, T_Q4_0 = 2, T_Q4_1 = 3, T_Q8_0 = 8, T_Q4_K = 12, T_Q5_K = 13, T_Q6_K = 14, T_BF16 = 30 };
 
 struct MetaValue {
     int type = -1;         // GGUF value type id (0..12)
@@ -296,6 +296,37 @@ int32_t to_f32(const ForgeGguf& g, const TensorInfo& t, uint64_t expect, std::ve
         }
         return FORGE_OK;
     }
+    if (t.type == T_Q4_1 && expect % 32 == 0) {  // weight_loader.rs:931-966: {f16 scale, f16 min, 16 nibble bytes}, q * scale + min
+        for (uint64_t b = 0; b < expect / 32; ++b) {
+            uint16_t h0, h1; memcpy(&h0, p + 20 * b, 2); memcpy(&h1, p + 20 * b + 2, 2);
+            const float d = f16_to_f32(h0), mn = f16_to_f32(h1);
+            for (int i = 0; i < 16; ++i) {
+                out[size_t(b * 32 + i)] = float(p[20 * b + 4 + i] & 0x0F) * d + mn;
+                out[size_t(b * 32 + i + 16)] = float(p[20 * b + 4 + i] >> 4) * d + mn;
+            }
+        }
+        return FORGE_OK;
+    }
+    if (t.type == T_Q5_K && expect % 256 == 0) {  // weight_loader.rs:1071-1140: Q4_K's layout plus one high bit per value
+        for (uint64_t sb = 0; sb < expect / 256; ++sb) {
+            const uint8_t* blk = p + 176 * sb;
+            uint16_t h0, h1; memcpy(&h0, blk, 2); memcpy(&h1, blk + 2, 2);
+            const float d = f16_to_f32(h0), dmin = f16_to_f32(h1);
+            const uint8_t *sc = blk + 4, *qh = blk + 16, *qs = blk + 48;
+            for (int j = 0; j < 8; ++j) {  // sub-block j: nibble (j & 1) of qs[(j / 2) * 32 + l], high bit = bit j of qh[l]
+                int s6, m6;
+                if (j < 4) { s6 = sc[j] & 63; m6 = sc[j + 4] & 63; }
+                else { s6 = (sc[j + 4] & 0x0F) | ((sc[j - 4] >> 6) << 4); m6 = (sc[j + 4] >> 4) | ((sc[j] >> 6) << 4); }
+                const float dw = d * float(s6), mw = dmin * float(m6);
+                for (int l = 0; l < 32; ++l) {
+                    const uint8_t by = qs[(j >> 1) * 32 + l];
+                    const uint32_t q5 = uint32_t((j & 1) ? (by >> 4) : (by & 0x0F)) + (((qh[l] >> j) & 1) ? 16u : 0u);
+                    out[size_t(sb * 256 + j * 32 + l)] = dw * float(q5) - mw;
+                }
+            }
+        }
+        return FORGE_OK;
+    }
     if (t.type == T_Q4_K && expect % 256 == 0) {  // weight_loader.rs:1146-1200: d * sc * q - dmin * m per 32-element sub-block
         for (uint64_t sb = 0; sb < expect / 256; ++sb) {
             const uint8_t* blk = p + 144 * sb;
@@ -407,7 +438,7 @@ Part find_projection(const ForgeGguf& g, const std::string& hf, uint64_t numel, 
 // Otherwise the tensor is dequantised and quantised again in the category's format, as the reference's loader does
 // for K-quant categories (load_from_file_mixed_per_tensor, weight_loader.rs:193-218: the alternating Q4_K / Q6_K
 // attn_v and ffn_down tensors of a Q4_K_M file) and its exporter for dense projections of Q4_0 models
-// (main.rs:2601-2607).  Source formats this reader cannot dequantise (Q4_1, Q5_x, Q2_K, Q3_K, Q5_K, I-quants) are reported.
+// (main.rs:2601-2607).  Source formats this reader cannot dequantise (Q5_0, Q5_1, Q8_1, Q2_K, Q3_K, Q8_K, I-quants) are reported.
 int32_t put_projection(const ForgeGguf& g, const std::string& hf, int cat, uint64_t rows, uint64_t cols, const ForgeModelConfig& c, Sink& s) {
     const int32_t quant = quant_of(c, cat);
     const uint64_t numel = rows * cols, rb = row_bytes(quant, cols);
@@ -427,7 +458,7 @@ int32_t put_projection(const ForgeGguf& g, const std::string& hf, int cat, uint6
         return FORGE_OK;
     }
     const bool dense = t->type == T_F32 || t->type == T_F16 || t->type == T_BF16;
-    const bool blocks = t->type == T_Q8_0 || t->type == T_Q4_0 || t->type == T_Q4_K || t->type == T_Q6_K;
+    const bool blocks = t->type == T_Q8_0 || t->type == T_Q4_0 || t->type == T_Q4_1 || t->type == T_Q4_K || t->type == T_Q5_K || t->type == T_Q6_K;
     if ((dense && !is_kquant(quant)) || (blocks && (is_kquant(quant) || quant == FORGE_Q8_0 || t->type == T_Q8_0))) {
         std::vector<float> v;
         FORGE_TRY(to_f32(g, *t, numel, v, part.first));
@@ -574,6 +605,16 @@ int32_t forge_gguf_model_config(const ForgeGguf* g, ForgeModelConfig* c) {
     bool uniform = true;
     for (int i = 0; i < 8; ++i) uniform = uniform && pq[i] == quant;
     if (!uniform) memcpy(c->proj_quant, pq, sizeof(pq));
+    return FORGE_OK;
+}
+
+int32_t forge_gguf_tensor_to_f32(const ForgeGguf* g, int64_t index, float* out, size_t capacity) {
+    if (!g || !out || index < 0 || size_t(index) >= g->tensors.size()) { set_error("bad argument to forge_gguf_tensor_to_f32"); return FORGE_ERR_INVALID_ARG; }
+    const TensorInfo& t = g->tensors[size_t(index)];
+    if (capacity < t.numel()) { set_error("tensor %s has %llu elements, the buffer holds %zu", t.name.c_str(), (unsigned long long)t.numel(), capacity); return FORGE_ERR_INVALID_ARG; }
+    std::vector<float> v;
+    FORGE_TRY(to_f32(*g, t, t.numel(), v));
+    memcpy(out, v.data(), v.size() * sizeof(float));
     return FORGE_OK;
 }
 

@@ -49,6 +49,14 @@ class GgufFile:
                         "offset": int(off.value), "size": int(size.value)})
         return out
 
+    def tensor_f32(self, index: int) -> np.ndarray:
+        """Tensor ``index`` dequantised to f32 (flat)."""
+        t = self.tensors()[index]
+        n = int(np.prod(t["dims"])) if t["dims"] else 1
+        out = np.empty(n, np.float32)
+        check(lib.forge_gguf_tensor_to_f32(self._h, index, out.ctypes.data_as(C.c_void_p), n))
+        return out
+
     def config(self) -> dict:
         c = ForgeModelConfig()
         check(lib.forge_gguf_model_config(self._h, C.byref(c)))

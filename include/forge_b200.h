@@ -361,6 +361,9 @@ uint64_t forge_gguf_data_offset(const ForgeGguf* gguf);
  * size in bytes.  Any output pointer may be null. */
 int32_t forge_gguf_tensor_info(const ForgeGguf* gguf, int64_t index, const char** name, int32_t* ggml_type,
                                int32_t* n_dims, uint64_t* dims, uint64_t* offset, uint64_t* data_size);
+/* Tensor `index` as f32 (dequantize, weight_loader.rs:809-826): F32, F16, BF16, Q8_0, Q4_0, Q4_1, Q4_K, Q5_K, Q6_K;
+ * `capacity` in floats. */
+int32_t forge_gguf_tensor_to_f32(const ForgeGguf* gguf, int64_t index, float* out, size_t capacity);
 int32_t forge_gguf_model_config(const ForgeGguf* gguf, ForgeModelConfig* cfg);
 /* Size of the weights.bin image (0 on error, see forge_last_error) and the image itself. */
 size_t forge_gguf_weights_bin_size(const ForgeGguf* gguf);

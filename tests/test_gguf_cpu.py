@@ -314,3 +314,79 @@ def test_phi3_fused_tensors_are_split():
     fused = gguf.GgufFile(build_gguf(3, meta, table, data=data))
     assert fused.config()["num_kv_heads"] == 4
     assert np.array_equal(fused.weights_bin(), blob)
+
+
+# ---- tensor -> f32 for the block formats the exporter reads (dequantize, weight_loader.rs:809-826)
+def _one_tensor_file(typ, dims, payload):
+    return gguf.GgufFile(build_gguf(3, [("general.architecture", 8, _s("llama"))], [("t.weight", dims, typ, 0)], data=bytes(payload)))
+
+
+def _scale_min_k4(j, sc):
+    if j < 4:
+        return int(sc[j] & 63), int(sc[j + 4] & 63)
+    return int((sc[j + 4] & 0x0F) | ((sc[j - 4] >> 6) << 4)), int((sc[j + 4] >> 4) | ((sc[j] >> 6) << 4))
+
+
+def _dq_q4_1(raw, n):  # weight_loader.rs:931-966
+    b = np.frombuffer(raw, np.uint8).reshape(-1, 20)
+    d = b[:, 0:2].copy().view(np.float16).astype(np.float32)
+    m = b[:, 2:4].copy().view(np.float16).astype(np.float32)
+    lo, hi = (b[:, 4:] & 0x0F).astype(np.float32), (b[:, 4:] >> 4).astype(np.float32)
+    return (np.concatenate([lo, hi], axis=1) * d + m).reshape(-1)[:n]
+
+
+def _dq_q5_k(raw, n):  # weight_loader.rs:1071-1140
+    out = np.zeros(n, np.float32)
+    blocks = np.frombuffer(raw, np.uint8).reshape(-1, 176)
+    for sb, blk in enumerate(blocks):
+        d = blk[0:2].copy().view(np.float16).astype(np.float32)[0]
+        dmin = blk[2:4].copy().view(np.float16).astype(np.float32)[0]
+        sc, qh, qs = blk[4:16], blk[16:48], blk[48:176]
+        for j in range(8):
+            s6, m6 = _scale_min_k4(j, sc)
+            by = qs[(j >> 1) * 32:(j >> 1) * 32 + 32]
+            q = ((by >> 4) if j & 1 else (by & 0x0F)).astype(np.uint32) + (((qh >> j) & 1).astype(np.uint32) << 4)
+            out[sb * 256 + j * 32:sb * 256 + j * 32 + 32] = (d * np.float32(s6)) * q.astype(np.float32) - dmin * np.float32(m6)
+    return out
+
+
+def test_dequant_q4_1_and_q5_k_known_answers():
+    # weight_loader.rs:3245-3260: scale 2, min 1, all nibbles 0 -> 1.0
+    blk = np.zeros(20, np.uint8)
+    blk[0:2] = np.frombuffer(np.uint16(0x4000).tobytes(), np.uint8)
+    blk[2:4] = np.frombuffer(np.uint16(0x3C00).tobytes(), np.uint8)
+    assert np.all(_one_tensor_file(3, [32], blk).tensor_f32(0) == 1.0)
+    # weight_loader.rs:3509-3533: d = 1, sub-block 0 scale 1, qs[0] low nibble 3, qh[0] bit 0 -> 3 + 16 = 19
+    b = np.zeros(176, np.uint8)
+    b[0:2] = np.frombuffer(np.uint16(0x3C00).tobytes(), np.uint8)
+    b[4], b[16], b[48] = 1, 0x01, 0x03
+    assert _one_tensor_file(13, [256], b).tensor_f32(0)[0] == 19.0
+    # weight_loader.rs:3536-3558: sub-block 1 scale 2, qs[0] high nibble 7, qh[0] bit 1 -> 2 * (7 + 16) = 46 at element 32
+    b = np.zeros(176, np.uint8)
+    b[0:2] = np.frombuffer(np.uint16(0x3C00).tobytes(), np.uint8)
+    b[5], b[16], b[48] = 2, 0x02, 0x70
+    assert _one_tensor_file(13, [256], b).tensor_f32(0)[32] == 46.0
+
+
+def test_tensor_to_f32_matches_the_restatements(oracle):
+    rng = np.random.default_rng(21)
+    n = 256 * 6
+
+    def blocks(count, size, scale_cols, mag):
+        raw = rng.integers(0, 256, (count, size), dtype=np.uint8)
+        for c in scale_cols:
+            raw[:, c:c + 2] = (mag * (0.5 + rng.random(count))).astype(np.float16).view(np.uint8).reshape(count, 2)
+        return raw.reshape(-1)
+
+    q41 = blocks(n // 32, 20, (0, 2), 0.01)
+    assert np.array_equal(_one_tensor_file(3, [n], q41).tensor_f32(0), _dq_q4_1(q41.tobytes(), n))
+    q5k = blocks(n // 256, 176, (0, 2), 1e-4)
+    assert np.array_equal(_one_tensor_file(13, [n], q5k).tensor_f32(0), _dq_q5_k(q5k.tobytes(), n))
+    q4k = synth.random_kquant(12, rng, 1, n, 0.02)
+    assert np.array_equal(_one_tensor_file(12, [n], q4k).tensor_f32(0), oracle.dequant_kquant(12, q4k, n))
+    q6k = synth.random_kquant(14, rng, 1, n, 0.02)
+    assert np.array_equal(_one_tensor_file(14, [n], q6k).tensor_f32(0), oracle.dequant_kquant(14, q6k, n))
+    q80 = oracle.quantize_q8_0(rng.standard_normal(n).astype(np.float32))
+    assert np.array_equal(_one_tensor_file(8, [n], q80).tensor_f32(0), oracle.dequant_q8_0(q80, n))
+    q40 = oracle.quantize_q4_0(rng.standard_normal(n).astype(np.float32))
+    assert np.array_equal(_one_tensor_file(2, [n], q40).tensor_f32(0), oracle.dequant_q4_0(q40, n))
