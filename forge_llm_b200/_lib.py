@@ -52,6 +52,7 @@ SIGNATURES = {
     "forge_packed_create": (i32, [i32, vp, i32, i32, vp, C.POINTER(vp)]),
     "forge_packed_destroy": (None, [vp]),
     "forge_matmul_mat_packed": (i32, [vp, i32, vp, vp, vp]),
+    "forge_packed_check": (i32, [vp, vp]),
     "forge_rms_norm": (i32, [vp, vp, vp, i32, i32, f32, vp]),
     "forge_rope_table": (i32, [vp, i32, i32, f32]),
     "forge_rope": (i32, [vp, i32, i32, i32, i32, vp, vp]),
@@ -95,6 +96,7 @@ SIGNATURES = {
     "forge_model_set_gemm_passes": (i32, [vp, i32]),
     "forge_model_set_prefill_mode": (i32, [vp, i32]),
     "forge_model_set_decode_mode": (i32, [vp, i32]),
+    "forge_model_set_wait_limit": (i32, [vp, u32]),
     "forge_kv_create": (i32, [vp, i32, i32, C.POINTER(vp)]),
     "forge_kv_reset": (i32, [vp]),
     "forge_kv_len": (i32, [vp, i32]),

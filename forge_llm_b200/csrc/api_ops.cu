@@ -83,19 +83,25 @@ void packed_free(ForgePacked* pk) {
     delete pk;
 }
 
+// Reads the error word a bounded device-side wait sets when it gives up, and clears it so that one timeout does not
+// mark every later call on the same packed matrix.  Synchronises the stream.
+int32_t packed_check_err(const ForgePacked* pk, cudaStream_t st) {
+    int herr = 0;
+    FORGE_CUDA(cudaMemcpyAsync(&herr, pk->err, sizeof(int), cudaMemcpyDeviceToHost, st));
+    FORGE_CUDA(cudaStreamSynchronize(st));
+    if (!herr) return FORGE_OK;
+    FORGE_CUDA(cudaMemsetAsync(pk->err, 0, sizeof(int), st));
+    set_error("matmul: a bounded device-side wait gave up");
+    return FORGE_ERR_TIMEOUT;
+}
+
 int32_t matmul_packed(float* out, int32_t m, const float* in, const ForgePacked* pk, cudaStream_t st, bool check_err) {
     const int K = pk->soa.K;
     if (m < FORGE_PREFILL_BATCH_THRESHOLD) {  // per-token path: the streaming GEMV, f32-exact up to summation order
         GemvArgs ga;
         ga.x = in; ga.out = out; ga.batch = m;
         FORGE_TRY(gemv_tc(pk->tiled, EPI_STORE, ga, pk->split, pk->err, st));
-        if (check_err) {
-            int herr = 0;
-            FORGE_CUDA(cudaMemcpyAsync(&herr, pk->err, sizeof(int), cudaMemcpyDeviceToHost, st));
-            FORGE_CUDA(cudaStreamSynchronize(st));
-            if (herr) { set_error("gemv: a bounded device-side wait gave up"); return FORGE_ERR_TIMEOUT; }
-        }
-        return FORGE_OK;
+        return check_err ? packed_check_err(pk, st) : FORGE_OK;
     }
     AsyncBuf a16(st), a16lo(st);
     FORGE_CUDA(a16.alloc(size_t(m) * K * sizeof(__half)));
@@ -103,7 +109,8 @@ int32_t matmul_packed(float* out, int32_t m, const float* in, const ForgePacked*
     FORGE_TRY(f32_to_f16(static_cast<__half*>(a16.p), static_cast<__half*>(a16lo.p), in, size_t(m) * K, st));
     // K-quant products take their input rows as Q8_0 blocks (emit.rs:1412-1440); the batched form keeps that rounding
     if (pk->soa.quant == FORGE_KQ_SOA) FORGE_TRY(q8_round_f16(static_cast<__half*>(a16.p), static_cast<__half*>(a16lo.p), size_t(m) * K, st));
-    return gemm_f16a(out, static_cast<const __half*>(a16.p), static_cast<const __half*>(a16lo.p), pk->soa, m, nullptr, pk->err, st);
+    FORGE_TRY(gemm_f16a(out, static_cast<const __half*>(a16.p), static_cast<const __half*>(a16lo.p), pk->soa, m, nullptr, pk->err, st));
+    return check_err ? packed_check_err(pk, st) : FORGE_OK;
 }
 
 int32_t matmul_mat(int quant, float* out, int32_t m, const float* in, const uint8_t* w, int32_t K, int32_t N, void* stream) {
@@ -158,6 +165,12 @@ int32_t forge_matmul_mat_packed(float* out, int32_t m, const float* in, const Fo
     if (!out || !in || !w || m < 0) { set_error("bad argument to forge_matmul_mat_packed"); return FORGE_ERR_INVALID_ARG; }
     if (m == 0) return FORGE_OK;
     return matmul_packed(out, m, in, w, static_cast<cudaStream_t>(stream), false);
+}
+
+int32_t forge_packed_check(const ForgePacked* w, void* stream) {
+    FORGE_TRY(need_device());
+    if (!w) { set_error("bad argument to forge_packed_check"); return FORGE_ERR_INVALID_ARG; }
+    return packed_check_err(w, static_cast<cudaStream_t>(stream));
 }
 
 int32_t forge_rms_norm(float* out, const float* in, const float* weight, int32_t rows, int32_t n, float eps, void* stream) {

@@ -94,7 +94,8 @@ inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, siz
 
 // ------------------------------------------------------------------ GEMV (decode)
 // EPI_PARTIAL: every K slice stores its raw partial sums at scratch[slice][row]; the reader adds them
-enum GemvEpilogue { EPI_STORE = 0, EPI_RESID = 1, EPI_QKV = 2, EPI_SILU = 3, EPI_PARTIAL = 4, EPI_TP_PUSH = 5 };
+// EPI_HOOK: no built-in epilogue; the caller's row hook takes the finished rows
+enum GemvEpilogue { EPI_STORE = 0, EPI_RESID = 1, EPI_QKV = 2, EPI_SILU = 3, EPI_PARTIAL = 4, EPI_TP_PUSH = 5, EPI_HOOK = 6 };
 
 struct GemvArgs {
     const float* x = nullptr;       // [batch][K] input rows
@@ -135,6 +136,7 @@ struct GemvArgs {
         const uint2* ll = nullptr;              // local exchange buffer
         const uint32_t* step_counter = nullptr; // device, advanced once per decode step
         uint32_t step_mul = 0, step_add = 0;
+        uint32_t wait_limit = 1u << 20;         // polls per pair before the wait gives up
         float* x_writeback = nullptr;
     } tp;
 };
@@ -163,25 +165,31 @@ int32_t tile_pack(const uint8_t* const* row_src_dev, QTiled& dst, cudaStream_t s
 // err: device int set to 1 if a bounded wait inside the kernel gave up (may be null)
 int32_t gemv_tc(const QTiled& w, GemvEpilogue epi, const GemvArgs& a, const GemvSplit& sp, int* err, cudaStream_t st);
 
-// ------------------------------------------------------------------ whole-step decode kernel (batch 1)
+// ------------------------------------------------------------------ whole-sequence decode kernel (batch 1)
+// One persistent kernel runs `n_steps` decode steps of one sequence.  Its CTAs hand vectors to one another as
+// {value, tag} pairs in global memory (tag = epoch + step; a reader polls until the tag matches, bounded), so there
+// is no grid-wide barrier and no kernel boundary between the operators of a step or between steps.
 namespace core { struct Phase; }
-struct MegaParams {
-    const core::Phase* phases;   // device array: per layer {QKV, O, gate/up, down}, then lm_head
-    int num_layers, h;
-    // attention of sequence 0
+struct FlowParams {
+    const core::Phase* phases;   // device array: per layer {QKV, O, gate/up, down}, then lm_head (epi = EPI_HOOK, slices = 1)
+    int num_layers, h, qk, kvd, ff, V, nq, nkv, hd, attn_splits;
     __half* k_pool; __half* v_pool; size_t layer_stride;
-    const int32_t* page_table; const int32_t* seq_len;
-    int nq, nkv, hd, attn_splits;
-    float* attn_ws;              // [nq][attn_splits][hd + 2] partials (m, l, acc)
-    // token in / out, bookkeeping updated by the last CTA
-    const float* embed; float* hidden0; float* hidden1;  // residual stream, double-buffered
-    uint32_t* tok; uint32_t* hist; int32_t* step; int32_t* seq_len_mut;
-    int greedy;
-    float* amax_val; int* amax_idx; int* amax_ticket;
-    unsigned* bar; int* err;
+    const int32_t* page_table; int32_t* seq_len;   // of the sequence; seq_len is advanced by n_steps at the end
+    const float* rope; const float* embed;
+    uint2* xbuf; size_t x_layer_stride;            // per layer: q | new k,v | attention partials | o | act | down
+    uint2* xamax;                                  // [2 * grid] per-CTA arg-max of the logits
+    uint32_t epoch;                                // tag of the first step (never 0; unique over the model's lifetime)
+    int n_steps, greedy;
+    int max_kb;                                    // largest K/32 of any operator (sizes the staging area)
+    uint32_t wait_limit;                           // polls per wait before it gives up and raises *err
+    uint32_t* tok; uint32_t* hist; int32_t* step;  // token in / out, generation history, history cursor
+    float* logits;                                 // [V] logits of the last step
+    int* err;
 };
+size_t flow_layer_pairs(int h, int qk, int kvd, int ff, int nq, int hd, int splits);
+int flow_attn_splits(int nkv, int sms);
 // launches the cooperative kernel on `grid` CTAs (one per SM); max_kb = largest K/32 of any phase
-int32_t decode_step_mega(const MegaParams& p, int quant, int hd, int max_kb, int grid, cudaStream_t st);
+int32_t decode_flow(const FlowParams& p, int quant, int max_kb, int grid, cudaStream_t st);
 
 // ------------------------------------------------------------------ elementwise
 int32_t rms_norm_f32(float* out, const float* in, const float* w, int rows, int n, float eps, cudaStream_t st);

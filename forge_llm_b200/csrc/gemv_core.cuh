@@ -227,7 +227,7 @@ __device__ __forceinline__ FillStat stage_fill_global(uint2* xf, const float* ba
 // Rank order is fixed, so every rank forms the same bits.  The sum is written once (element group i by CTA
 // i % gridDim.x) to `writeback`.
 __device__ __forceinline__ FillStat stage_fill_pairs(uint2* xf, const float* base, const uint2* ll, int world, uint32_t step,
-                                                     float* writeback, int K, const float* norm_w, int* err) {
+                                                     float* writeback, int K, const float* norm_w, int* err, uint32_t limit) {
     float* xraw = reinterpret_cast<float*>(xf);
     FillStat st;
     csync();  // the previous contents of the fragment area are no longer read
@@ -237,7 +237,7 @@ __device__ __forceinline__ FillStat stage_fill_pairs(uint2* xf, const float* bas
             const uint2* src = ll + size_t(r) * K + e;
             uint4 a, b;
             bool ok = false;
-            for (uint32_t i = 0; i < (1u << 20) && !ok; ++i) {  // about a second
+            for (uint32_t i = 0; i < limit && !ok && !*reinterpret_cast<volatile int*>(err); ++i) {  // the default limit is about a second
                 asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w) : "l"(src) : "memory");
                 asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(b.x), "=r"(b.y), "=r"(b.z), "=r"(b.w) : "l"(src + 2) : "memory");
                 ok = a.y == step && a.w == step && b.y == step && b.w == step;
@@ -438,6 +438,7 @@ template <bool TP>
 __device__ __forceinline__ void epilogue_row(const Phase& ph, int b, int row, float v, float partner, const EpiPre& pre, int j) {
     if (row >= ph.N) return;
     const GemvArgs& a = ph.a;
+    if (ph.epi == EPI_HOOK) return;
     if (ph.epi == EPI_STORE) {
         a.out[size_t(b) * ph.N + row] = v;
     } else if (ph.epi == EPI_RESID) {
@@ -472,8 +473,9 @@ __device__ __forceinline__ void epilogue_row(const Phase& ph, int b, int row, fl
 }
 
 // ---- consumer side, step 2: all units of this CTA for one phase and one batch row.
-// `on_row(row, value)` is called by the finishing thread after the epilogue (used by the whole-step
-// kernel to track the arg-max of the logits); pass a no-op otherwise.
+// `on_row(row, value, partner)` is called by the finishing thread after the epilogue, `partner` being the value of
+// row ^ 1 (the whole-step kernel publishes its results from there: ph.epi = EPI_HOOK leaves the built-in epilogues
+// out); pass a no-op otherwise.  It is also called for the padding rows (row >= N).
 template <int QUANT, typename RowHook, bool TP = false>
 __device__ __forceinline__ void consume_phase(const Phase& ph, Shared& sh, const unsigned char* ring, const uint2* xf,
                                               const int4* xoff, float unscale, int b, int& cc, RowHook on_row, int pos_hint = -1) {
@@ -653,8 +655,8 @@ __device__ __forceinline__ void consume_phase(const Phase& ph, Shared& sh, const
         if (finish && t == 0) {
             epilogue_row<TP>(ph, b, row0, v0, o0, pre, 0);
             epilogue_row<TP>(ph, b, row0 + 8, v1, o1, pre, 1);
-            on_row(row0, v0);
-            on_row(row0 + 8, v1);
+            on_row(row0, v0, o0);
+            on_row(row0 + 8, v1, o1);
         }
     }
 }

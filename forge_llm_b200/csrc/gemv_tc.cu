@@ -101,12 +101,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tc_kernel(TcParams p) {
             const GemvArgs::Tp& tp = ph.a.tp;
             const uint32_t step = __ldcg(tp.step_counter) * tp.step_mul + tp.step_add;
             const FillStat st = stage_fill_pairs(xf, ph.a.x, tp.ll + size_t(tp.slot) * tp.world * ph.K, tp.world, step, tp.x_writeback,
-                                                 ph.K, ph.a.norm_w, &sh.err);
+                                                 ph.K, ph.a.norm_w, &sh.err, tp.wait_limit);
             unscale = stage_finish<QUANT>(xf, s_xoff, sh, st, ph.K, ph.a.norm_w, ph.a.eps);
         } else {
             unscale = stage_activation<QUANT, false>(xf, s_xoff, sh, ph.a.x + size_t(b) * ph.K, ph.K, ph.a.norm_w, ph.a.eps);
         }
-        auto no_hook = [](int, float) {};
+        auto no_hook = [](int, float, float) {};
         consume_phase<QUANT, decltype(no_hook), TP>(ph, sh, ring, xf, s_xoff, unscale, b, cc, no_hook, pos);
     }
     csync();

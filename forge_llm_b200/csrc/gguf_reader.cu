@@ -209,7 +209,7 @@ int32_t vote_quant(const ForgeGguf& g, int32_t& quant) {
         else if (t.type == T_Q4_0) ++q4;
         else if (t.type == T_Q4_K) ++q4k;
         else if (t.type == T_F32 || t.type == T_F16 || t.type == T_BF16) ++dense;
-        else if (t.type == 3 || (t.type >= 6 && t.type <= 23)) ++q8;  // Q4_1, Q5_x, Q8_1, the other K- and I-quants
+        else if (t.type == 3 || (t.type >= 6 && t.type <= 23) || t.type == 29) ++q8;  // Q4_1, Q5_x, Q8_1, the other K- and I-quants (IQ1_M = 29)
     }
     const size_t total = q8 + q4 + q4k + dense;
     if (total > 0 && q4k > total / 2) quant = FORGE_Q4_K;
@@ -541,7 +541,11 @@ int32_t forge_gguf_open(const void* data, size_t len, ForgeGguf** out) {
         g->tensors.push_back(std::move(t));
     }
     uint64_t a = 0;
-    if (g->get_u32("general.alignment", a) && a > 0) g->alignment = a;
+    if (g->get_u32("general.alignment", a) && a > 0) {
+        // a power of two no larger than the file: anything else cannot be a real alignment and would overflow the round-up below
+        if ((a & (a - 1)) != 0 || uint64_t(a) > uint64_t(len)) { set_error("GGUF general.alignment %llu is not a power of two within the file", (unsigned long long)a); return fail(FORGE_ERR_SHAPE); }
+        g->alignment = a;
+    }
     g->data_offset = (uint64_t(r.pos) + g->alignment - 1) / g->alignment * g->alignment;
     *out = g;
     return FORGE_OK;

@@ -80,9 +80,15 @@ struct ForgeModel {
     void* tpx_local = nullptr; std::vector<void*> tpx_peer; bool tpx_ready = false;
     uint2** d_tpx_ll = nullptr; uint32_t* d_tpx_step = nullptr;  // peers' buffers (device table), decode step counter
     float* p_part = nullptr; float* d_part = nullptr;  // this rank's partial sums of a row-sliced projection
-    bool use_mega = false; // batch-1 decode through the whole-step kernel (forge_model_set_decode_mode)
-    // decode scratch (per batch row)
-    int dec_batch = 0;
+    // batch-1 decode as one persistent kernel (decode_flow.cu): operator table, pair buffers, tag counter
+    bool use_flow = true;   // forge_model_set_decode_mode
+    core::Phase* d_flow_phases = nullptr; int flow_grid = 0, flow_max_kb = 0, flow_splits = 1;
+    uint2* d_xbuf = nullptr; size_t x_layer_stride = 0; uint2* d_xamax = nullptr;
+    uint32_t flow_epoch = 1;            // tag of the next step (never 0)
+    uint32_t wait_limit = 1u << 21;     // polls per device-side wait (forge_model_set_wait_limit)
+    // decode scratch (per batch row).  Growing it moves every buffer: scratch_gen counts the moves, and whatever holds the
+    // old addresses (a cache's captured decode graph) is rebuilt when its generation differs.
+    int dec_batch = 0; int scratch_gen = 0;
     float* d_hidden2 = nullptr;
     float* d_hidden = nullptr; float* d_q = nullptr; float* d_attn = nullptr; float* d_act = nullptr; float* d_logits = nullptr;
     uint32_t* d_tok = nullptr; uint32_t* d_hist = nullptr; int hist_cap = 0; int32_t* d_step = nullptr;
@@ -102,10 +108,7 @@ struct ForgeKV {
     int32_t* d_page_table = nullptr; int32_t* d_seq_len = nullptr;
     std::vector<int32_t> h_page_table; std::vector<int> free_pages; std::vector<int> pages_used; std::vector<int> len;
     float* attn_ws = nullptr; int* attn_counters = nullptr; int splits = 1;
-    cudaGraphExec_t graph = nullptr; int graph_batch = 0; bool graph_greedy = false;
-    // whole-step decode kernel (batch 1, sequence 0)
-    core::Phase* d_phases = nullptr; int mega_grid = 0, mega_max_kb = 0, mega_splits = 1;
-    float* mega_ws = nullptr; float* mega_scr[3] = {nullptr, nullptr, nullptr}; unsigned* d_bar = nullptr;
+    cudaGraphExec_t graph = nullptr; int graph_batch = 0; bool graph_greedy = false; int graph_gen = -1;  // scratch generation the graph was captured with
 };
 
 namespace {
@@ -204,6 +207,7 @@ int32_t ensure_decode_scratch(ForgeModel* m, int batch) {
     if (!m->d_step) { FORGE_TRY(dev_alloc(m, &m->d_step, 1)); }
     if (m->cfg.tp_world > 1) FORGE_TRY(dev_alloc(m, &m->d_part, b * m->h));
     m->dec_batch = batch;
+    ++m->scratch_gen;
     return FORGE_OK;
 }
 
@@ -242,6 +246,21 @@ int32_t upload_len(ForgeKV* kv) {
     FORGE_CUDA(cudaMemcpyAsync(kv->d_seq_len, l.data(), sizeof(int32_t) * kv->batch, cudaMemcpyHostToDevice, kv->model->stream));
     FORGE_CUDA(cudaStreamSynchronize(kv->model->stream));
     return FORGE_OK;
+}
+
+// The synchronisation point of a session call.  Also reads the word the bounded device-side waits raise when they give
+// up (a pipeline stage, a peer's contribution or another CTA's result never arrived): the call then fails with
+// FORGE_ERR_TIMEOUT, the word is cleared and the device-side positions are put back to the host's (`kv`, may be null).
+int32_t sync_and_check(ForgeModel* m, ForgeKV* kv) {
+    int herr = 0;
+    FORGE_CUDA(cudaMemcpyAsync(&herr, m->d_err, sizeof(int), cudaMemcpyDeviceToHost, m->stream));
+    FORGE_CUDA(cudaStreamSynchronize(m->stream));
+    if (!herr) return FORGE_OK;
+    FORGE_CUDA(cudaMemsetAsync(m->d_err, 0, sizeof(int), m->stream));
+    if (kv) FORGE_TRY(upload_len(kv));
+    FORGE_CUDA(cudaStreamSynchronize(m->stream));
+    set_error("a bounded device-side wait gave up: the step did not complete");
+    return FORGE_ERR_TIMEOUT;
 }
 
 // hidden += W x for a projection whose K dimension is sliced over the tensor-parallel ranks: the ranks' partial
@@ -337,6 +356,7 @@ int32_t decode_launches(ForgeModel* m, ForgeKV* kv, int batch, bool greedy, bool
     auto tp_common = [&](GemvArgs& a, int index) {
         a.tp.world = c.tp_world; a.tp.rank = c.tp_rank; a.tp.slot = index & 1;
         a.tp.step_counter = m->d_tpx_step; a.tp.step_mul = uint32_t(2 * c.num_layers + 1); a.tp.step_add = uint32_t(index + 1);
+        a.tp.wait_limit = m->wait_limit;
     };
     auto tp_consume = [&](GemvArgs& a) {   // a.x is the residual stream: take the pending sum in while staging
         if (!pending) return;
@@ -438,26 +458,89 @@ int32_t decode_prepare(ForgeKV* kv, int batch) {
     return FORGE_OK;
 }
 
-// batch 1 on sequence 0: the whole step is one persistent kernel
-int32_t decode_step_one_kernel(ForgeModel* m, ForgeKV* kv, bool greedy) {
-    MegaParams p;
-    p.phases = kv->d_phases; p.num_layers = m->cfg.num_layers; p.h = m->h;
+// ---- batch-1 decode as one persistent kernel (decode_flow.cu)
+// Models it takes: every projection in the model's basic format, one GPU, full attention.
+bool flow_eligible(const ForgeModel* m) {
+    return m->use_flow && m->uniform_basic && m->cfg.tp_world == 1 && m->cfg.sliding_window <= 0 && !m->trace_on &&
+           (m->nq / m->nkv) * m->hd <= 512 && m->nq * flow_attn_splits(m->nkv, 148) <= 512 && m->h % 4 == 0 && m->ff % 4 == 0;
+}
+
+// operator table and pair buffers, built on first use
+int32_t ensure_flow(ForgeModel* m) {
+    if (m->d_flow_phases) return FORGE_OK;
+    int sms = 148;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, m->device);
+    const int L = m->cfg.num_layers;
+    std::vector<core::Phase> ph(size_t(4) * L + 1);
+    int rot = 0, max_kb = 0;
+    auto fill = [&](core::Phase& P, const QTiled& w) {
+        P.w = w.data; P.K = w.K; P.N = w.N; P.kb = w.K / 32; P.bands = w.bands; P.bt = w.bt;
+        P.slices = 1; P.units = w.bands;
+        P.rot = rot;   // operators are dealt round-robin, so every SM streams about the same bytes per step
+        rot = (rot + P.units) % sms;
+        P.epi = EPI_HOOK; P.scratch = nullptr; P.tickets = nullptr;
+        P.a = GemvArgs();
+        max_kb = std::max(max_kb, P.kb);
+    };
+    for (int l = 0; l < L; ++l) {
+        ForgeLayer& Ly = m->layers[l];
+        core::Phase& q = ph[4 * l];
+        fill(q, Ly.qkv_t);
+        q.a.norm_w = Ly.attn_norm; q.a.eps = m->cfg.rms_norm_eps; q.a.bias = Ly.qkv_bias;
+        fill(ph[4 * l + 1], Ly.o_t);
+        core::Phase& g = ph[4 * l + 2];
+        fill(g, Ly.gateup_t);
+        g.a.norm_w = Ly.ffn_norm; g.a.eps = m->cfg.rms_norm_eps;
+        fill(ph[4 * l + 3], Ly.down_t);
+    }
+    core::Phase& lm = ph.back();
+    fill(lm, m->lm_head_t);
+    lm.a.norm_w = m->final_norm; lm.a.eps = m->cfg.rms_norm_eps;
+    m->flow_grid = sms;
+    m->flow_max_kb = max_kb;
+    m->flow_splits = flow_attn_splits(m->nkv, sms);
+    m->x_layer_stride = flow_layer_pairs(m->h, m->qk, m->kv, m->ff, m->nq, m->hd, m->flow_splits);
+    FORGE_TRY(dev_alloc(m, &m->d_xbuf, m->x_layer_stride * L));
+    FORGE_TRY(dev_alloc(m, &m->d_xamax, size_t(2) * sms));
+    FORGE_CUDA(cudaMemsetAsync(m->d_xbuf, 0, sizeof(uint2) * m->x_layer_stride * L, m->stream));
+    FORGE_CUDA(cudaMemsetAsync(m->d_xamax, 0, sizeof(uint2) * 2 * sms, m->stream));
+    core::Phase* d = nullptr;
+    FORGE_TRY(dev_alloc(m, &d, ph.size()));
+    FORGE_CUDA(cudaMemcpyAsync(d, ph.data(), ph.size() * sizeof(core::Phase), cudaMemcpyHostToDevice, m->stream));
+    FORGE_CUDA(cudaStreamSynchronize(m->stream));   // the host vector goes away
+    m->d_flow_phases = d;
+    return FORGE_OK;
+}
+
+// n_steps decode steps of the sequence whose page-table row and length word are given; the token comes from
+// m->d_tok.  greedy: every step feeds the arg-max of its logits to the next one and the history is recorded.
+int32_t decode_flow_steps(ForgeModel* m, ForgeKV* kv, const int32_t* page_table, int32_t* seq_len, int n_steps, bool greedy) {
+    FORGE_TRY(ensure_flow(m));
+    FlowParams p{};
+    p.phases = m->d_flow_phases; p.num_layers = m->cfg.num_layers;
+    p.h = m->h; p.qk = m->qk; p.kvd = m->kv; p.ff = m->ff; p.V = m->V; p.nq = m->nq; p.nkv = m->nkv; p.hd = m->hd;
+    p.attn_splits = m->flow_splits;
     p.k_pool = kv->k_pool; p.v_pool = kv->v_pool; p.layer_stride = kv->layer_stride;
-    p.page_table = kv->d_page_table; p.seq_len = kv->d_seq_len;
-    p.nq = m->nq; p.nkv = m->nkv; p.hd = m->hd; p.attn_splits = kv->mega_splits;
-    p.attn_ws = kv->mega_ws;
-    p.embed = m->embed; p.hidden0 = m->d_hidden; p.hidden1 = m->d_hidden2;
-    p.tok = m->d_tok; p.hist = greedy ? m->d_hist : nullptr; p.step = m->d_step; p.seq_len_mut = kv->d_seq_len;
-    p.greedy = greedy ? 1 : 0;
-    p.amax_val = m->d_amax_val; p.amax_idx = m->d_amax_idx; p.amax_ticket = m->d_amax_ticket;
-    p.bar = kv->d_bar; p.err = m->d_err;
-    return decode_step_mega(p, m->cfg.quant, m->hd, kv->mega_max_kb, kv->mega_grid, m->stream);
+    p.page_table = page_table; p.seq_len = seq_len;
+    p.rope = m->rope; p.embed = m->embed;
+    p.xbuf = m->d_xbuf; p.x_layer_stride = m->x_layer_stride; p.xamax = m->d_xamax;
+    if (m->flow_epoch == 0 || m->flow_epoch + uint32_t(n_steps) < m->flow_epoch) {   // the tag space wrapped: start over
+        FORGE_CUDA(cudaMemsetAsync(m->d_xbuf, 0, sizeof(uint2) * m->x_layer_stride * m->cfg.num_layers, m->stream));
+        FORGE_CUDA(cudaMemsetAsync(m->d_xamax, 0, sizeof(uint2) * 2 * m->flow_grid, m->stream));
+        m->flow_epoch = 1;
+    }
+    p.epoch = m->flow_epoch;
+    m->flow_epoch += uint32_t(n_steps);
+    p.n_steps = n_steps; p.greedy = greedy ? 1 : 0;
+    p.wait_limit = m->wait_limit;
+    p.tok = m->d_tok; p.hist = greedy ? m->d_hist : nullptr; p.step = greedy ? m->d_step : nullptr;
+    p.logits = m->d_logits; p.err = m->d_err;
+    return decode_flow(p, m->cfg.quant, m->flow_max_kb, m->flow_grid, m->stream);
 }
 
 int32_t decode_step_graph(ForgeModel* m, ForgeKV* kv, int batch, bool greedy) {
     if (m->trace_on) return decode_launches(m, kv, batch, greedy, greedy);
-    if (batch == 1 && m->use_mega && m->uniform_basic && m->cfg.tp_world == 1 && m->cfg.sliding_window <= 0 && kv->d_phases && kv->mega_grid <= kArgmaxSlices && (m->nq / m->nkv) * m->hd <= 512) return decode_step_one_kernel(m, kv, greedy);
-    if (!kv->graph || kv->graph_batch != batch || kv->graph_greedy != greedy) {
+    if (!kv->graph || kv->graph_batch != batch || kv->graph_greedy != greedy || kv->graph_gen != m->scratch_gen) {
         if (kv->graph) { cudaGraphExecDestroy(kv->graph); kv->graph = nullptr; }
         cudaGraph_t g = nullptr;
         FORGE_CUDA(cudaStreamBeginCapture(m->stream, cudaStreamCaptureModeThreadLocal));
@@ -470,7 +553,7 @@ int32_t decode_step_graph(ForgeModel* m, ForgeKV* kv, int batch, bool greedy) {
         cudaError_t ie = cudaGraphInstantiate(&kv->graph, g, 0);
         cudaGraphDestroy(g);
         if (ie != cudaSuccess) { set_error("graph instantiate: %s", cudaGetErrorString(ie)); return FORGE_ERR_CUDA; }
-        kv->graph_batch = batch; kv->graph_greedy = greedy;
+        kv->graph_batch = batch; kv->graph_greedy = greedy; kv->graph_gen = m->scratch_gen;
     }
     FORGE_CUDA(cudaGraphLaunch(kv->graph, m->stream));
     // kernels inside one replay: embedding + 5 per layer + lm_head + (argmax) + advance
@@ -709,7 +792,11 @@ int32_t forge_model_tp_exchange_attach(ForgeModel* m, const uint8_t* handles) {
     std::vector<uint2*> ll(world);
     for (int r = 0; r < world; ++r) {
         void* base = m->tpx_local;
-        if (r != rank) {
+        cudaIpcMemHandle_t own;
+        FORGE_CUDA(cudaIpcGetMemHandle(&own, m->tpx_local));
+        // a peer entry that repeats this rank's own handle maps the local buffer: nothing will ever be pushed into that
+        // slot, which is how a single-process test makes the bounded peer wait run out
+        if (r != rank && memcmp(&own, handles + size_t(r) * FORGE_TP_HANDLE_BYTES, sizeof(own)) != 0) {
             cudaIpcMemHandle_t h;
             memcpy(&h, handles + size_t(r) * FORGE_TP_HANDLE_BYTES, sizeof(h));
             cudaError_t e = cudaIpcOpenMemHandle(&base, h, cudaIpcMemLazyEnablePeerAccess);
@@ -774,59 +861,6 @@ int32_t forge_kv_create(ForgeModel* m, int32_t max_seq, int32_t batch, ForgeKV**
     if (cudaMalloc(&kv->attn_ws, sizeof(float) * attn_decode_ws_floats(batch, m->nq, m->hd, kv->splits)) != cudaSuccess ||
         cudaMalloc(&kv->attn_counters, sizeof(int) * batch * m->nkv) != cudaSuccess) { set_error("attention workspace allocation failed"); return fail(FORGE_ERR_CUDA); }
     cudaMemsetAsync(kv->attn_counters, 0, sizeof(int) * batch * m->nkv, m->stream);
-    {   // phase table of the whole-step decode kernel
-        std::vector<core::Phase> ph(size_t(4) * m->cfg.num_layers + 1);
-        int rot = 0, max_kb = 0;
-        auto fill = [&](core::Phase& P, const QTiled& w, int epi) {
-            P.w = w.data; P.K = w.K; P.N = w.N; P.kb = w.K / 32; P.bands = w.bands; P.bt = w.bt;
-            P.slices = gemv_slices(w, m->split, sms, 1);
-            P.units = w.bands * P.slices;
-            P.rot = rot;
-            rot = (rot + P.units) % sms;
-            P.epi = epi; P.scratch = m->split.scratch; P.tickets = m->split.tickets;
-            P.a = GemvArgs();
-            max_kb = std::max(max_kb, P.kb);
-        };
-        if (ensure_decode_scratch(m, 1) != FORGE_OK) return fail(FORGE_ERR_CUDA);
-        {   // raw partial sums of the K-split projections: [slices][rows padded to 128]
-            const size_t rows[3] = {size_t((m->qk + 2 * m->kv + 127) / 128) * 128, size_t((m->h + 127) / 128) * 128, size_t((m->h + 127) / 128) * 128};
-            for (int i = 0; i < 3; ++i)
-                if (cudaMalloc(&kv->mega_scr[i], sizeof(float) * kGemvMaxSlices * rows[i]) != cudaSuccess) { set_error("decode scratch allocation failed"); return fail(FORGE_ERR_CUDA); }
-        }
-        for (int l = 0; l < m->cfg.num_layers; ++l) {
-            ForgeLayer& L = m->layers[l];
-            core::Phase& q = ph[4 * l];
-            fill(q, L.qkv_t, EPI_PARTIAL); q.scratch = kv->mega_scr[0];
-            q.a.x = m->d_hidden; q.a.norm_w = L.attn_norm; q.a.eps = m->cfg.rms_norm_eps; q.a.bias = L.qkv_bias; q.a.rope = m->rope;
-            q.a.q_out = m->d_q; q.a.k_pool = kv->k_pool + size_t(l) * kv->layer_stride; q.a.v_pool = kv->v_pool + size_t(l) * kv->layer_stride;
-            q.a.page_table = kv->d_page_table; q.a.seq_len = kv->d_seq_len; q.a.pages_per_seq = kv->pages_per_seq;
-            q.a.qk = m->qk; q.a.kv = m->kv; q.a.kv_stride = m->kv; q.a.head_dim = m->hd;
-            core::Phase& o = ph[4 * l + 1];
-            fill(o, L.o_t, EPI_PARTIAL); o.scratch = kv->mega_scr[1];
-            o.a.x = m->d_attn; o.a.out = m->d_hidden; o.a.resid = m->d_hidden;
-            core::Phase& g = ph[4 * l + 2];
-            fill(g, L.gateup_t, EPI_SILU);
-            g.a.x = m->d_hidden; g.a.norm_w = L.ffn_norm; g.a.eps = m->cfg.rms_norm_eps; g.a.out = m->d_act;
-            core::Phase& d = ph[4 * l + 3];
-            fill(d, L.down_t, EPI_PARTIAL); d.scratch = kv->mega_scr[2];
-            d.a.x = m->d_act; d.a.out = m->d_hidden; d.a.resid = m->d_hidden;
-        }
-        core::Phase& lm = ph.back();
-        fill(lm, m->lm_head_t, EPI_STORE);
-        lm.a.x = m->d_hidden; lm.a.norm_w = m->final_norm; lm.a.eps = m->cfg.rms_norm_eps; lm.a.out = m->d_logits;
-        kv->mega_grid = sms;
-        kv->mega_max_kb = max_kb;
-        // context splits per KV head: cover the SMs, at most 16, and nq * splits <= 512 (limits of decode_mega.cu)
-        kv->mega_splits = std::max(1, std::min({(sms + m->nkv - 1) / m->nkv, 16, 512 / m->nq}));
-        if (cudaMalloc(&kv->d_phases, ph.size() * sizeof(core::Phase)) != cudaSuccess ||
-            cudaMalloc(&kv->mega_ws, sizeof(float) * size_t(m->nq) * kv->mega_splits * (m->hd + 2)) != cudaSuccess ||
-            cudaMalloc(&kv->d_bar, sizeof(unsigned)) != cudaSuccess) {
-            set_error("decode kernel tables allocation failed"); return fail(FORGE_ERR_CUDA);
-        }
-        cudaMemcpyAsync(kv->d_phases, ph.data(), ph.size() * sizeof(core::Phase), cudaMemcpyHostToDevice, m->stream);
-        cudaMemsetAsync(kv->d_bar, 0, sizeof(unsigned), m->stream);
-        if (cudaStreamSynchronize(m->stream) != cudaSuccess) { set_error("KV init failed"); return fail(FORGE_ERR_CUDA); }
-    }
     if (cudaStreamSynchronize(m->stream) != cudaSuccess) { set_error("KV init failed"); return fail(FORGE_ERR_CUDA); }
     m->caches.push_back(kv);
     *out = kv;
@@ -856,8 +890,6 @@ void forge_kv_destroy(ForgeKV* kv) {
     if (kv->graph) cudaGraphExecDestroy(kv->graph);
     cudaFree(kv->k_pool); cudaFree(kv->v_pool); cudaFree(kv->d_page_table); cudaFree(kv->d_seq_len);
     cudaFree(kv->attn_ws); cudaFree(kv->attn_counters);
-    cudaFree(kv->d_phases); cudaFree(kv->mega_ws); cudaFree(kv->d_bar);
-    for (float* q : kv->mega_scr) cudaFree(q);
     delete kv;
 }
 
@@ -866,10 +898,8 @@ static void kv_release_device(ForgeKV* kv) {
     if (kv->graph) cudaGraphExecDestroy(kv->graph);
     cudaFree(kv->k_pool); cudaFree(kv->v_pool); cudaFree(kv->d_page_table); cudaFree(kv->d_seq_len);
     cudaFree(kv->attn_ws); cudaFree(kv->attn_counters);
-    cudaFree(kv->d_phases); cudaFree(kv->mega_ws); cudaFree(kv->d_bar);
-    for (float*& q : kv->mega_scr) { cudaFree(q); q = nullptr; }
     kv->graph = nullptr; kv->k_pool = kv->v_pool = nullptr; kv->d_page_table = kv->d_seq_len = nullptr;
-    kv->attn_ws = nullptr; kv->attn_counters = nullptr; kv->d_phases = nullptr; kv->mega_ws = nullptr; kv->d_bar = nullptr;
+    kv->attn_ws = nullptr; kv->attn_counters = nullptr;
     kv->model = nullptr;
 }
 
@@ -916,7 +946,9 @@ int32_t forge_score_chunk(ForgeModel* m, ForgeKV* kv, const uint32_t* chunk, siz
 // ---- persistence (project.rs:456-499)
 namespace {
 constexpr char kKvMagic[4] = {'F', 'K', 'V', '1'};
-struct KvHeader { char magic[4]; uint32_t layers, width; uint64_t len; };
+// 24 bytes on disk: magic 'FKV1' | u32 layers | u32 width (values per cache row) | u32 zero | u64 positions
+struct KvHeader { char magic[4]; uint32_t layers, width, reserved; uint64_t len; };
+static_assert(sizeof(KvHeader) == 24, "the saved-cache header is a fixed 24-byte layout");
 
 // one layer's rows [0, len) of K or V between the paged pool and a contiguous host array [len][width] of fp16
 int32_t kv_copy_rows(ForgeKV* kv, int seq, int layer, int which, int len, __half* host, bool to_host) {
@@ -948,7 +980,7 @@ int32_t forge_kv_save(ForgeKV* kv, int32_t seq, void* out_host, size_t capacity)
     if (m->cfg.tp_world > 1) { set_error("forge_kv_save: a tensor-parallel cache holds only this rank's heads"); return FORGE_ERR_UNSUPPORTED; }
     FORGE_CUDA(cudaSetDevice(m->device));
     const int len = kv->len[seq], L = m->cfg.num_layers;
-    KvHeader h;
+    KvHeader h{};
     memcpy(h.magic, kKvMagic, 4); h.layers = uint32_t(L); h.width = uint32_t(m->kv); h.len = uint64_t(len);
     memcpy(out_host, &h, sizeof(h));
     __half* dst = reinterpret_cast<__half*>(static_cast<char*>(out_host) + sizeof(h));
@@ -1016,11 +1048,14 @@ int32_t forge_forward_prefill_seq(ForgeModel* m, ForgeKV* kv, int32_t seq, const
         for (size_t i = 0; i < n; ++i) FORGE_TRY(forge_forward_seq(m, kv, seq, tokens[i], (i + 1 == n) ? logits_host : nullptr));
         return FORGE_OK;
     }
+    const int len0 = kv->len[seq];
     FORGE_TRY(prefill_seq(m, kv, seq, tokens, int(n)));
     FORGE_TRY(upload_len(kv));
     if (logits_host) FORGE_CUDA(cudaMemcpyAsync(logits_host, m->d_logits, sizeof(float) * m->V, cudaMemcpyDeviceToHost, m->stream));
-    FORGE_CUDA(cudaStreamSynchronize(m->stream));
-    return FORGE_OK;
+    kv->len[seq] = len0;   // until the check has passed
+    FORGE_TRY(sync_and_check(m, kv));
+    kv->len[seq] = len0 + int(n);
+    return upload_len(kv);
 }
 
 int32_t forge_forward_prefill(ForgeModel* m, ForgeKV* kv, const uint32_t* tokens, size_t n, float* logits_host) {
@@ -1044,16 +1079,18 @@ int32_t forge_forward_seq(ForgeModel* m, ForgeKV* kv, int32_t seq, uint32_t toke
     view.d_seq_len = kv->d_seq_len + seq;
     view.graph = nullptr;
     int32_t rc;
-    if (seq == 0 && kv->batch >= 1 && !m->trace_on) {
+    if (flow_eligible(m)) {
+        rc = decode_flow_steps(m, kv, view.d_page_table, view.d_seq_len, 1, false);
+    } else if (seq == 0 && kv->batch >= 1 && !m->trace_on) {
         rc = decode_step_graph(m, kv, 1, false);
     } else {
         rc = decode_launches(m, &view, 1, false, false);
     }
     view.h_page_table.clear();
     FORGE_TRY(rc);
-    kv->len[seq] += 1;
     if (logits_host) FORGE_CUDA(cudaMemcpyAsync(logits_host, m->d_logits, sizeof(float) * m->V, cudaMemcpyDeviceToHost, m->stream));
-    FORGE_CUDA(cudaStreamSynchronize(m->stream));
+    FORGE_TRY(sync_and_check(m, kv));
+    kv->len[seq] += 1;
     return FORGE_OK;
 }
 
@@ -1068,9 +1105,9 @@ int32_t forge_forward_batch(ForgeModel* m, ForgeKV* kv, int32_t batch, const uin
     if (m->trace_on) FORGE_TRY(ensure_trace(m, batch));
     FORGE_CUDA(cudaMemcpyAsync(m->d_tok, tokens, sizeof(uint32_t) * batch, cudaMemcpyHostToDevice, m->stream));
     FORGE_TRY(decode_step_graph(m, kv, batch, false));
-    for (int b = 0; b < batch; ++b) kv->len[b] += 1;
     if (logits_host) FORGE_CUDA(cudaMemcpyAsync(logits_host, m->d_logits, sizeof(float) * size_t(batch) * m->V, cudaMemcpyDeviceToHost, m->stream));
-    FORGE_CUDA(cudaStreamSynchronize(m->stream));
+    FORGE_TRY(sync_and_check(m, kv));
+    for (int b = 0; b < batch; ++b) kv->len[b] += 1;
     return FORGE_OK;
 }
 
@@ -1094,16 +1131,30 @@ int32_t forge_decode_greedy_batch(ForgeModel* m, ForgeKV* kv, int32_t batch, con
     FORGE_CUDA(cudaEventRecord(m->ev[1], m->stream));
     bool saved_trace = m->trace_on;
     m->trace_on = false;
-    for (int i = 0; i < n_new; ++i) {
-        int32_t rc = decode_prepare(kv, batch);
-        if (rc == FORGE_OK) rc = decode_step_graph(m, kv, batch, true);
-        if (rc != FORGE_OK) { m->trace_on = saved_trace; return rc; }
-        for (int b = 0; b < batch; ++b) kv->len[b] += 1;
+    const std::vector<int> len0 = kv->len;
+    int32_t rc = FORGE_OK;
+    if (batch == 1 && flow_eligible(m)) {
+        // all n_new steps in one launch: the kernel feeds every arg-max to the next step itself
+        rc = ensure_pages(kv, 0, kv->len[0] + n_new);
+        if (rc == FORGE_OK) rc = decode_flow_steps(m, kv, kv->d_page_table, kv->d_seq_len, n_new, true);
+        if (rc == FORGE_OK) kv->len[0] += n_new;
+    } else {
+        for (int i = 0; i < n_new && rc == FORGE_OK; ++i) {
+            rc = decode_prepare(kv, batch);
+            if (rc == FORGE_OK) rc = decode_step_graph(m, kv, batch, true);
+            if (rc == FORGE_OK) for (int b = 0; b < batch; ++b) kv->len[b] += 1;
+        }
     }
     m->trace_on = saved_trace;
+    if (rc != FORGE_OK) { cudaStreamSynchronize(m->stream); kv->len = len0; upload_len(kv); return rc; }
     FORGE_CUDA(cudaEventRecord(m->ev[2], m->stream));
     FORGE_CUDA(cudaMemcpyAsync(out_tokens, m->d_hist, sizeof(uint32_t) * size_t(n_new) * batch, cudaMemcpyDeviceToHost, m->stream));
-    FORGE_CUDA(cudaStreamSynchronize(m->stream));
+    {
+        const std::vector<int> len1 = kv->len;
+        kv->len = len0;   // what the device is put back to if the check fails
+        FORGE_TRY(sync_and_check(m, kv));
+        kv->len = len1;
+    }
     FORGE_CUDA(cudaEventElapsedTime(&m->decode_ms, m->ev[1], m->ev[2]));
     m->last_launches = g_launches - l0;
     return FORGE_OK;
@@ -1116,6 +1167,7 @@ int32_t forge_generate_greedy(ForgeModel* m, ForgeKV* kv, const uint32_t* prompt
     for (size_t i = 0; i < n; ++i) if (prompt[i] >= uint32_t(m->V)) { set_error("token id %u out of vocabulary", prompt[i]); return FORGE_ERR_INVALID_ARG; }
     FORGE_TRY(ensure_decode_scratch(m, 1));
     long long l0 = g_launches;
+    const int len_entry = kv->len[0];
     FORGE_CUDA(cudaEventRecord(m->ev[0], m->stream));
     if (n < FORGE_PREFILL_BATCH_THRESHOLD) {
         for (size_t i = 0; i < n; ++i) FORGE_TRY(forge_forward_seq(m, kv, 0, prompt[i], nullptr));
@@ -1127,7 +1179,12 @@ int32_t forge_generate_greedy(ForgeModel* m, ForgeKV* kv, const uint32_t* prompt
     FORGE_TRY(argmax_slices(m->d_tok, m->d_logits, m->V, 1, m->d_amax_val, m->d_amax_idx, m->d_amax_ticket, m->stream));
     uint32_t first = 0;
     FORGE_CUDA(cudaMemcpyAsync(&first, m->d_tok, sizeof(uint32_t), cudaMemcpyDeviceToHost, m->stream));
-    FORGE_CUDA(cudaStreamSynchronize(m->stream));
+    {
+        const int len1 = kv->len[0];
+        kv->len[0] = len_entry;
+        FORGE_TRY(sync_and_check(m, kv));
+        kv->len[0] = len1;
+    }
     long long lp = g_launches - l0;
     int32_t rc = forge_decode_greedy_batch(m, kv, 1, &first, n_new, out_tokens);
     if (rc != FORGE_OK) return rc;
@@ -1151,7 +1208,13 @@ int32_t forge_model_set_prefill_mode(ForgeModel* m, int32_t mode) {
 
 int32_t forge_model_set_decode_mode(ForgeModel* m, int32_t mode) {
     if (!m || (mode != 0 && mode != 1)) { set_error("decode mode must be 0 or 1"); return FORGE_ERR_INVALID_ARG; }
-    m->use_mega = mode == 1;
+    m->use_flow = mode == 1;
+    return FORGE_OK;
+}
+
+int32_t forge_model_set_wait_limit(ForgeModel* m, uint32_t polls) {
+    if (!m || polls == 0) { set_error("the wait limit must be at least one poll"); return FORGE_ERR_INVALID_ARG; }
+    m->wait_limit = polls;
     return FORGE_OK;
 }
 
