@@ -95,7 +95,6 @@ SIGNATURES = {
     "forge_model_tp_exchange_attach": (i32, [vp, vp]),
     "forge_model_set_gemm_passes": (i32, [vp, i32]),
     "forge_model_set_prefill_mode": (i32, [vp, i32]),
-    "forge_model_set_decode_mode": (i32, [vp, i32]),
     "forge_model_set_wait_limit": (i32, [vp, u32]),
     "forge_kv_create": (i32, [vp, i32, i32, C.POINTER(vp)]),
     "forge_kv_reset": (i32, [vp]),

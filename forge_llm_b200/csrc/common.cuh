@@ -94,8 +94,7 @@ inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, siz
 
 // ------------------------------------------------------------------ GEMV (decode)
 // EPI_PARTIAL: every K slice stores its raw partial sums at scratch[slice][row]; the reader adds them
-// EPI_HOOK: no built-in epilogue; the caller's row hook takes the finished rows
-enum GemvEpilogue { EPI_STORE = 0, EPI_RESID = 1, EPI_QKV = 2, EPI_SILU = 3, EPI_PARTIAL = 4, EPI_TP_PUSH = 5, EPI_HOOK = 6 };
+enum GemvEpilogue { EPI_STORE = 0, EPI_RESID = 1, EPI_QKV = 2, EPI_SILU = 3, EPI_PARTIAL = 4, EPI_TP_PUSH = 5 };
 
 struct GemvArgs {
     const float* x = nullptr;       // [batch][K] input rows
@@ -165,32 +164,6 @@ int32_t tile_pack(const uint8_t* const* row_src_dev, QTiled& dst, cudaStream_t s
 // err: device int set to 1 if a bounded wait inside the kernel gave up (may be null)
 int32_t gemv_tc(const QTiled& w, GemvEpilogue epi, const GemvArgs& a, const GemvSplit& sp, int* err, cudaStream_t st);
 
-// ------------------------------------------------------------------ whole-sequence decode kernel (batch 1)
-// One persistent kernel runs `n_steps` decode steps of one sequence.  Its CTAs hand vectors to one another as
-// {value, tag} pairs in global memory (tag = epoch + step; a reader polls until the tag matches, bounded), so there
-// is no grid-wide barrier and no kernel boundary between the operators of a step or between steps.
-namespace core { struct Phase; }
-struct FlowParams {
-    const core::Phase* phases;   // device array: per layer {QKV, O, gate/up, down}, then lm_head (epi = EPI_HOOK, slices = 1)
-    int num_layers, h, qk, kvd, ff, V, nq, nkv, hd, attn_splits;
-    __half* k_pool; __half* v_pool; size_t layer_stride;
-    const int32_t* page_table; int32_t* seq_len;   // of the sequence; seq_len is advanced by n_steps at the end
-    const float* rope; const float* embed;
-    uint2* xbuf; size_t x_layer_stride;            // per layer: q | new k,v | attention partials | o | act | down
-    uint2* xamax;                                  // [2 * grid] per-CTA arg-max of the logits
-    uint32_t epoch;                                // tag of the first step (never 0; unique over the model's lifetime)
-    int n_steps, greedy;
-    int max_kb;                                    // largest K/32 of any operator (sizes the staging area)
-    uint32_t wait_limit;                           // polls per wait before it gives up and raises *err
-    uint32_t* tok; uint32_t* hist; int32_t* step;  // token in / out, generation history, history cursor
-    float* logits;                                 // [V] logits of the last step
-    int* err;
-};
-size_t flow_layer_pairs(int h, int qk, int kvd, int ff, int nq, int hd, int splits);
-int flow_attn_splits(int nkv, int sms);
-// launches the cooperative kernel on `grid` CTAs (one per SM); max_kb = largest K/32 of any phase
-int32_t decode_flow(const FlowParams& p, int quant, int max_kb, int grid, cudaStream_t st);
-
 // ------------------------------------------------------------------ elementwise
 int32_t rms_norm_f32(float* out, const float* in, const float* w, int rows, int n, float eps, cudaStream_t st);
 // fp16 outputs come as a hi/lo pair when `lo` is given: hi = fp16(x), lo = fp16(x - hi)
@@ -205,6 +178,9 @@ int32_t kv_append_contig(__half* kc, __half* vc, const float* k, const float* v,
 // prefill QKV epilogue: bias, RoPE, q -> fp16 [m][qk], k/v -> paged fp16 cache
 int32_t qkv_post(const float* qkv, int m, int base_pos, const float* bias, const float* rope, __half* q16, __half* q16_lo,
                  __half* k_pool, __half* v_pool, const int32_t* page_row, int qk, int kv, int hd, cudaStream_t st);
+// batched decode QKV epilogue: row b is sequence b at position seq_len[b]; q stays f32, k/v go to the sequence's page
+int32_t qkv_post_rows(const float* qkv, int batch, const float* bias, const float* rope, float* q_out, __half* k_pool, __half* v_pool,
+                      const int32_t* page_table, const int32_t* seq_len, int pages_per_seq, int qk, int kv, int hd, cudaStream_t st);
 int32_t argmax_last(uint32_t* result, const float* logits, int n, int batch, cudaStream_t st);
 // many-CTA form; sval/sidx: [batch][kArgmaxSlices] scratch, ticket: [batch] zero-initialised counters
 constexpr int kArgmaxSlices = 148;

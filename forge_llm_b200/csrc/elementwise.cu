@@ -156,6 +156,33 @@ __global__ void qkv_post_kernel(const float* __restrict__ qkv, int m, int base_p
     }
 }
 
+// batched decode glue: row b of the fused [q;k;v] product belongs to sequence b at position seq_len[b]:
+// (+bias) -> RoPE on q,k -> q f32 [b][qk], k/v into that sequence's cache page
+__global__ void qkv_post_rows_kernel(const float* __restrict__ qkv, const float* __restrict__ bias, const float2* __restrict__ rope,
+                                     float* __restrict__ q_out, __half* __restrict__ k_pool, __half* __restrict__ v_pool,
+                                     const int32_t* __restrict__ page_table, const int32_t* __restrict__ seq_len, int pages_per_seq,
+                                     int qk, int kv, int hd) {
+    const int npairs = (qk + 2 * kv) / 2;
+    const int b = blockIdx.x;
+    const int pos = seq_len[b];
+    const float2* src = reinterpret_cast<const float2*>(qkv + size_t(b) * (qk + 2 * kv));
+    const size_t prow = (size_t(page_table[size_t(b) * pages_per_seq + pos / FORGE_KV_PAGE]) * FORGE_KV_PAGE + pos % FORGE_KV_PAGE) * kv;
+    for (int i = threadIdx.x; i < npairs; i += blockDim.x) {
+        float2 v = src[i];
+        int col = 2 * i;
+        if (bias) { v.x += bias[col]; v.y += bias[col + 1]; }
+        int region = 0;
+        if (col >= qk) { col -= qk; region = 1; }
+        if (region == 1 && col >= kv) { col -= kv; region = 2; }
+        if (region < 2) {
+            const float2 cs = rope[size_t(pos) * (hd / 2) + (col % hd) / 2];
+            v = make_float2(v.x * cs.x - v.y * cs.y, v.x * cs.y + v.y * cs.x);
+        }
+        if (region == 0) *reinterpret_cast<float2*>(q_out + size_t(b) * qk + col) = v;
+        else *reinterpret_cast<__half2*>((region == 1 ? k_pool : v_pool) + prow + col) = __floats2half2_rn(v.x, v.y);
+    }
+}
+
 // Greedy pick with the generated main's tie rule: the LAST index among equal maxima.
 __global__ void argmax_kernel(uint32_t* result, const float* logits, int n) {
     __shared__ float bv[32];
@@ -347,6 +374,14 @@ int32_t qkv_post(const float* qkv, int m, int base_pos, const float* bias, const
                  __half* k_pool, __half* v_pool, const int32_t* page_row, int qk, int kv, int hd, cudaStream_t st) {
     if (m <= 0) return FORGE_OK;
     qkv_post_kernel<<<m, 256, 0, st>>>(qkv, m, base_pos, bias, reinterpret_cast<const float2*>(rope), q16, q16_lo, k_pool, v_pool, page_row, qk, kv, hd);
+    FORGE_LAUNCH_CHECK();
+    return FORGE_OK;
+}
+int32_t qkv_post_rows(const float* qkv, int batch, const float* bias, const float* rope, float* q_out, __half* k_pool, __half* v_pool,
+                      const int32_t* page_table, const int32_t* seq_len, int pages_per_seq, int qk, int kv, int hd, cudaStream_t st) {
+    if (batch <= 0) return FORGE_OK;
+    qkv_post_rows_kernel<<<batch, 256, 0, st>>>(qkv, bias, reinterpret_cast<const float2*>(rope), q_out, k_pool, v_pool, page_table, seq_len,
+                                                pages_per_seq, qk, kv, hd);
     FORGE_LAUNCH_CHECK();
     return FORGE_OK;
 }

@@ -2,7 +2,7 @@
 // streamed as Q8_0 / Q4_0 blocks and dequantised on the fly (replaces matmul_mat_q8_0_KxN /
 // matmul_mat_q4_0_KxN, crates/forgellm-codegen-cpu/src/emit.rs:2278-2299 and :3792-3813).
 //
-// CTA tile: 128 weight rows (MMA M) x NT tokens (MMA N = 128, 192 or 256), K step 64.  The dequantised weight
+// CTA tile: 128 weight rows (MMA M) x NT tokens (MMA N = 128, 192 or 256; 32 for a batched decode step), K step 64.  The dequantised weight
 // tile is the A operand and lives in TENSOR memory; the activation tile is the B operand in shared memory;
 // D[weight row][token] accumulates in tensor memory (f32).  Warp roles (320 threads):
 //   warp 0      TMA producer: 2-D tiled bulk copies (SWIZZLE_128B) of the fp16 activation tiles (hi and lo
@@ -306,8 +306,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_ts_kernel(const __grid_const
         if (!mbar_wait(&accum_full, 0, &s_err)) atomicExch(&s_err, 1);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const int col_n = n0 + r;
+        // (a 32-token tile is one 32-column read: the first warp of the quadrant takes it)
 #pragma unroll 1
-        for (int c0 = blk * (NT / 2); c0 < (blk + 1) * (NT / 2); c0 += 32) {
+        for (int c0 = NT >= 64 ? blk * (NT / 2) : 0; c0 < (NT >= 64 ? (blk + 1) * (NT / 2) : (blk == 0 ? NT : 0)); c0 += 32) {
             uint32_t v[32];
             const uint32_t taddr = tmem + (uint32_t(quad * 32) << 16) + uint32_t(c0);
             asm volatile(
@@ -404,6 +405,7 @@ int32_t gemm_tc5(float* out, const __half* A, const __half* Alo, const QWeight& 
     // in whole rounds over the SMs.  Pick the cheapest.
     const long nt = (w.N + 127) / 128;
     int best = 128;
+    const bool narrow = m <= 32;   // a batched decode step: the tensor-core time shrinks with the tile, the weight panel is streamed once
     double best_cost = 1e30;
     for (int cand : {128, 192, 256}) {
         if (cand > 128 && m <= cand - 64) continue;
@@ -415,6 +417,10 @@ int32_t gemm_tc5(float* out, const __half* A, const __half* Alo, const QWeight& 
     if (force_nt == 128 || force_nt == 192 || force_nt == 256) best = force_nt;
 #define FORGE_TS(Q)                                                                  \
     do {                                                                             \
+        if (narrow) {                                                                \
+            if (split) return launch_ts<Q, 32, true>(A, Alo, p, st);                 \
+            return launch_ts<Q, 32, false>(A, Alo, p, st);                           \
+        }                                                                            \
         if (split) {                                                                 \
             if (best == 256) return launch_ts<Q, 256, true>(A, Alo, p, st);          \
             if (best == 192) return launch_ts<Q, 192, true>(A, Alo, p, st);          \

@@ -1,5 +1,4 @@
-// Device-side core of the streaming decode GEMV, shared by the stand-alone kernel (gemv_tc.cu)
-// and the whole-step decode kernel (decode_mega.cu).
+// Device-side core of the streaming decode GEMV (gemv_tc.cu).
 //
 // One CTA = 16 consumer warps + 1 producer warp.  The producer lane issues 1-D bulk copies
 // (cp.async.bulk, mbarrier completion) of "chunks" - runs of k-blocks of one 128-row band of the
@@ -51,14 +50,16 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-// bounded wait: returns false when the limit ran out (the caller records an error and goes on)
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+// bounded wait: returns false when the limit ran out, or as soon as *stop is set (somebody in the CTA has already
+// given up, so whatever this wait is for may never come); the caller records an error and goes on
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const int* stop = nullptr) {
     uint32_t addr = smem_u32(bar);
     for (uint32_t i = 0; i < kSpinLimit; ++i) {
         uint32_t done;
         asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
                      : "=r"(done) : "r"(addr), "r"(parity) : "memory");
         if (done) return true;
+        if (stop && (i & 15) == 15 && *reinterpret_cast<const volatile int*>(stop)) return false;
     }
     return false;
 }
@@ -157,7 +158,7 @@ __device__ __forceinline__ bool produce_phase(const Phase& ph, Shared& sh, unsig
         for (int c = c0; c < c1; ++c, ++cc) {
             const int st = cc % T::STAGES, use = cc / T::STAGES;
             if (use > 0 && !hooked) { hooked = true; when_ring_full(); }
-            if (use > 0 && !mbar_wait(&sh.empty_bar[st], (use - 1) & 1)) { atomicExch(&sh.err, 1); return false; }
+            if (use > 0 && !mbar_wait(&sh.empty_bar[st], (use - 1) & 1, &sh.err)) { atomicExch(&sh.err, 1); return false; }
             if (*reinterpret_cast<volatile int*>(&sh.err)) return false;
             const int kb0 = c * ckb;
             const int nkb = min(ckb, ph.kb - kb0);
@@ -438,7 +439,6 @@ template <bool TP>
 __device__ __forceinline__ void epilogue_row(const Phase& ph, int b, int row, float v, float partner, const EpiPre& pre, int j) {
     if (row >= ph.N) return;
     const GemvArgs& a = ph.a;
-    if (ph.epi == EPI_HOOK) return;
     if (ph.epi == EPI_STORE) {
         a.out[size_t(b) * ph.N + row] = v;
     } else if (ph.epi == EPI_RESID) {
@@ -474,8 +474,7 @@ __device__ __forceinline__ void epilogue_row(const Phase& ph, int b, int row, fl
 
 // ---- consumer side, step 2: all units of this CTA for one phase and one batch row.
 // `on_row(row, value, partner)` is called by the finishing thread after the epilogue, `partner` being the value of
-// row ^ 1 (the whole-step kernel publishes its results from there: ph.epi = EPI_HOOK leaves the built-in epilogues
-// out); pass a no-op otherwise.  It is also called for the padding rows (row >= N).
+// row ^ 1; pass a no-op when there is nothing to add.  It is also called for the padding rows (row >= N).
 template <int QUANT, typename RowHook, bool TP = false>
 __device__ __forceinline__ void consume_phase(const Phase& ph, Shared& sh, const unsigned char* ring, const uint2* xf,
                                               const int4* xoff, float unscale, int b, int& cc, RowHook on_row, int pos_hint = -1) {
@@ -504,7 +503,7 @@ __device__ __forceinline__ void consume_phase(const Phase& ph, Shared& sh, const
         float acc[4] = {0.f, 0.f, 0.f, 0.f};
         for (int c = c0; c < c1; ++c, ++cc) {
             const int st = cc % T::STAGES, use = cc / T::STAGES;
-            if (!mbar_wait(&sh.full_bar[st], use & 1)) atomicExch(&sh.err, 1);
+            if (!mbar_wait(&sh.full_bar[st], use & 1, &sh.err)) atomicExch(&sh.err, 1);
             const int kb0 = c * ckb;
             const int nkb = min(ckb, KB - kb0);
             const unsigned char* base = ring + size_t(st) * T::STAGE_BYTES + size_t(r8) * T::BYTES;

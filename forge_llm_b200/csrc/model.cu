@@ -80,12 +80,7 @@ struct ForgeModel {
     void* tpx_local = nullptr; std::vector<void*> tpx_peer; bool tpx_ready = false;
     uint2** d_tpx_ll = nullptr; uint32_t* d_tpx_step = nullptr;  // peers' buffers (device table), decode step counter
     float* p_part = nullptr; float* d_part = nullptr;  // this rank's partial sums of a row-sliced projection
-    // batch-1 decode as one persistent kernel (decode_flow.cu): operator table, pair buffers, tag counter
-    bool use_flow = true;   // forge_model_set_decode_mode
-    core::Phase* d_flow_phases = nullptr; int flow_grid = 0, flow_max_kb = 0, flow_splits = 1;
-    uint2* d_xbuf = nullptr; size_t x_layer_stride = 0; uint2* d_xamax = nullptr;
-    uint32_t flow_epoch = 1;            // tag of the next step (never 0)
-    uint32_t wait_limit = 1u << 21;     // polls per device-side wait (forge_model_set_wait_limit)
+    uint32_t wait_limit = 1u << 20;     // polls per device-side peer wait (forge_model_set_wait_limit)
     // decode scratch (per batch row).  Growing it moves every buffer: scratch_gen counts the moves, and whatever holds the
     // old addresses (a cache's captured decode graph) is rebuilt when its generation differs.
     int dec_batch = 0; int scratch_gen = 0;
@@ -187,6 +182,7 @@ int32_t ensure_prefill_scratch(ForgeModel* m, int rows) {
     FORGE_TRY(dev_alloc(m, &m->p_act16_lo, r * m->ff));
     if (m->cfg.tp_world > 1) FORGE_TRY(dev_alloc(m, &m->p_part, r * m->h));
     m->scratch_rows = rows;
+    ++m->scratch_gen;   // a captured batched decode step holds these addresses
     return FORGE_OK;
 }
 
@@ -206,6 +202,7 @@ int32_t ensure_decode_scratch(ForgeModel* m, int batch) {
     FORGE_CUDA(cudaMemsetAsync(m->d_amax_ticket, 0, sizeof(int) * b, m->stream));
     if (!m->d_step) { FORGE_TRY(dev_alloc(m, &m->d_step, 1)); }
     if (m->cfg.tp_world > 1) FORGE_TRY(dev_alloc(m, &m->d_part, b * m->h));
+    if (batch >= FORGE_PREFILL_BATCH_THRESHOLD) FORGE_TRY(ensure_prefill_scratch(m, batch));   // batched steps run on the prompt scratch
     m->dec_batch = batch;
     ++m->scratch_gen;
     return FORGE_OK;
@@ -341,6 +338,44 @@ inline size_t tpx_bytes(const ForgeModel* m) { return sizeof(uint2) * 2 * size_t
 // `pt` (per-token prefill): the step runs for sequence pt->seq with the token at pt->tok, without the head unless
 // pt->head, and leaves the step counter of the generation history alone.
 struct PrefillToken { int seq; const uint32_t* tok; bool head; float* trace_dst; size_t trace_stride; };
+
+// A decode step of `batch` >= 8 sequences: every projection is ONE tensor-core product over the batch rows (the rule the
+// generated module applies to prompts, PREFILL_BATCH_THRESHOLD, emit.rs:203-206 and :4576-4587), so the weights are
+// streamed once per step instead of once per sequence.  The launch sequence is forward()'s operator order
+// (emit.rs:4029-4500) with the batched products of forward_prefill_batched (emit.rs:5118-5486); attention is the
+// single-query kernel over each sequence's own pages.  The rows live in the prompt scratch (fp16 hi/lo operands).
+int32_t decode_launches_gemm(ForgeModel* m, ForgeKV* kv, int batch, bool greedy, bool record) {
+    const ForgeModelConfig& c = m->cfg;
+    cudaStream_t st = m->stream;
+    const int n = batch;
+    const bool split = m->gemm_passes == 3;
+    __half* nlo = split ? m->p_normed_lo : nullptr;
+    __half* alo = split ? m->p_attn16_lo : nullptr;
+    __half* flo = split ? m->p_act16_lo : nullptr;
+    FORGE_TRY(embedding_rows(m->p_hidden, m->embed, m->d_tok, n, m->h, record ? m->d_hist : nullptr, m->d_step, st));
+    for (int l = 0; l < c.num_layers; ++l) {
+        ForgeLayer& L = m->layers[l];
+        __half* kp = kv->k_pool + size_t(l) * kv->layer_stride;
+        __half* vp = kv->v_pool + size_t(l) * kv->layer_stride;
+        FORGE_TRY(rms_norm_f16(m->p_normed, nlo, m->p_hidden, L.attn_norm, n, m->h, c.rms_norm_eps, st));
+        FORGE_TRY(gemm_f16a(m->p_qkv, m->p_normed, nlo, L.qkv, n, nullptr, m->d_err, st));
+        FORGE_TRY(qkv_post_rows(m->p_qkv, n, L.qkv_bias, m->rope, m->d_q, kp, vp, kv->d_page_table, kv->d_seq_len, kv->pages_per_seq,
+                                m->qk, m->kv, m->hd, st));
+        AttnDecodeArgs da{m->d_attn, m->d_q, kp, vp, kv->d_page_table, kv->pages_per_seq, kv->d_seq_len, 0,
+                          n, m->nq, m->nkv, m->hd, kv->max_seq, kv->attn_ws, kv->attn_counters, kv->splits, c.sliding_window};
+        FORGE_TRY(attn_decode(da, st));
+        FORGE_TRY(f32_to_f16(m->p_attn16, alo, m->d_attn, size_t(n) * m->qk, st));
+        FORGE_TRY(row_sliced_gemm(m, L.o, m->p_attn16, alo, n, st));
+        FORGE_TRY(rms_norm_f16(m->p_normed, nlo, m->p_hidden, L.ffn_norm, n, m->h, c.rms_norm_eps, st));
+        FORGE_TRY(gemm_f16a(m->p_gu, m->p_normed, nlo, L.gateup, n, nullptr, m->d_err, st));
+        FORGE_TRY(silu_mul_f16(m->p_act16, flo, m->p_gu, n, m->ff, st));
+        FORGE_TRY(row_sliced_gemm(m, L.down, m->p_act16, flo, n, st));
+    }
+    FORGE_TRY(rms_norm_f16(m->p_normed, nlo, m->p_hidden, m->final_norm, n, m->h, c.rms_norm_eps, st));
+    FORGE_TRY(gemm_f16a(m->d_logits, m->p_normed, nlo, m->lm_head, n, nullptr, m->d_err, st));
+    if (greedy) FORGE_TRY(argmax_slices(m->d_tok, m->d_logits, m->V, n, m->d_amax_val, m->d_amax_idx, m->d_amax_ticket, st));
+    return step_advance(kv->d_seq_len, n, m->d_step, st, nullptr);
+}
 int32_t decode_launches(ForgeModel* m, ForgeKV* kv, int batch, bool greedy, bool record, const PrefillToken* pt = nullptr) {
     const ForgeModelConfig& c = m->cfg;
     cudaStream_t st = m->stream;
@@ -373,6 +408,8 @@ int32_t decode_launches(ForgeModel* m, ForgeKV* kv, int batch, bool greedy, bool
         pending = true;
         return gemv_tc(w, EPI_TP_PUSH, a, m->split, m->d_err, st);
     };
+    if (batch >= FORGE_PREFILL_BATCH_THRESHOLD && !pt && !m->any_kquant && !m->per_token_prefill && !m->trace_on && m->lm_head.qs)
+        return decode_launches_gemm(m, kv, batch, greedy, record);
     FORGE_TRY(embedding_rows(m->d_hidden, m->embed, pt ? pt->tok : m->d_tok, batch, m->h, record ? m->d_hist : nullptr, m->d_step, st));
     for (int l = 0; l < c.num_layers; ++l) {
         ForgeLayer& L = m->layers[l];
@@ -456,86 +493,6 @@ int32_t prefill_per_token(ForgeModel* m, ForgeKV* kv, int seq, const uint32_t* t
 int32_t decode_prepare(ForgeKV* kv, int batch) {
     for (int b = 0; b < batch; ++b) FORGE_TRY(ensure_pages(kv, b, kv->len[b] + 1));
     return FORGE_OK;
-}
-
-// ---- batch-1 decode as one persistent kernel (decode_flow.cu)
-// Models it takes: every projection in the model's basic format, one GPU, full attention.
-bool flow_eligible(const ForgeModel* m) {
-    return m->use_flow && m->uniform_basic && m->cfg.tp_world == 1 && m->cfg.sliding_window <= 0 && !m->trace_on &&
-           (m->nq / m->nkv) * m->hd <= 512 && m->nq * flow_attn_splits(m->nkv, 148) <= 512 && m->h % 4 == 0 && m->ff % 4 == 0;
-}
-
-// operator table and pair buffers, built on first use
-int32_t ensure_flow(ForgeModel* m) {
-    if (m->d_flow_phases) return FORGE_OK;
-    int sms = 148;
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, m->device);
-    const int L = m->cfg.num_layers;
-    std::vector<core::Phase> ph(size_t(4) * L + 1);
-    int rot = 0, max_kb = 0;
-    auto fill = [&](core::Phase& P, const QTiled& w) {
-        P.w = w.data; P.K = w.K; P.N = w.N; P.kb = w.K / 32; P.bands = w.bands; P.bt = w.bt;
-        P.slices = 1; P.units = w.bands;
-        P.rot = rot;   // operators are dealt round-robin, so every SM streams about the same bytes per step
-        rot = (rot + P.units) % sms;
-        P.epi = EPI_HOOK; P.scratch = nullptr; P.tickets = nullptr;
-        P.a = GemvArgs();
-        max_kb = std::max(max_kb, P.kb);
-    };
-    for (int l = 0; l < L; ++l) {
-        ForgeLayer& Ly = m->layers[l];
-        core::Phase& q = ph[4 * l];
-        fill(q, Ly.qkv_t);
-        q.a.norm_w = Ly.attn_norm; q.a.eps = m->cfg.rms_norm_eps; q.a.bias = Ly.qkv_bias;
-        fill(ph[4 * l + 1], Ly.o_t);
-        core::Phase& g = ph[4 * l + 2];
-        fill(g, Ly.gateup_t);
-        g.a.norm_w = Ly.ffn_norm; g.a.eps = m->cfg.rms_norm_eps;
-        fill(ph[4 * l + 3], Ly.down_t);
-    }
-    core::Phase& lm = ph.back();
-    fill(lm, m->lm_head_t);
-    lm.a.norm_w = m->final_norm; lm.a.eps = m->cfg.rms_norm_eps;
-    m->flow_grid = sms;
-    m->flow_max_kb = max_kb;
-    m->flow_splits = flow_attn_splits(m->nkv, sms);
-    m->x_layer_stride = flow_layer_pairs(m->h, m->qk, m->kv, m->ff, m->nq, m->hd, m->flow_splits);
-    FORGE_TRY(dev_alloc(m, &m->d_xbuf, m->x_layer_stride * L));
-    FORGE_TRY(dev_alloc(m, &m->d_xamax, size_t(2) * sms));
-    FORGE_CUDA(cudaMemsetAsync(m->d_xbuf, 0, sizeof(uint2) * m->x_layer_stride * L, m->stream));
-    FORGE_CUDA(cudaMemsetAsync(m->d_xamax, 0, sizeof(uint2) * 2 * sms, m->stream));
-    core::Phase* d = nullptr;
-    FORGE_TRY(dev_alloc(m, &d, ph.size()));
-    FORGE_CUDA(cudaMemcpyAsync(d, ph.data(), ph.size() * sizeof(core::Phase), cudaMemcpyHostToDevice, m->stream));
-    FORGE_CUDA(cudaStreamSynchronize(m->stream));   // the host vector goes away
-    m->d_flow_phases = d;
-    return FORGE_OK;
-}
-
-// n_steps decode steps of the sequence whose page-table row and length word are given; the token comes from
-// m->d_tok.  greedy: every step feeds the arg-max of its logits to the next one and the history is recorded.
-int32_t decode_flow_steps(ForgeModel* m, ForgeKV* kv, const int32_t* page_table, int32_t* seq_len, int n_steps, bool greedy) {
-    FORGE_TRY(ensure_flow(m));
-    FlowParams p{};
-    p.phases = m->d_flow_phases; p.num_layers = m->cfg.num_layers;
-    p.h = m->h; p.qk = m->qk; p.kvd = m->kv; p.ff = m->ff; p.V = m->V; p.nq = m->nq; p.nkv = m->nkv; p.hd = m->hd;
-    p.attn_splits = m->flow_splits;
-    p.k_pool = kv->k_pool; p.v_pool = kv->v_pool; p.layer_stride = kv->layer_stride;
-    p.page_table = page_table; p.seq_len = seq_len;
-    p.rope = m->rope; p.embed = m->embed;
-    p.xbuf = m->d_xbuf; p.x_layer_stride = m->x_layer_stride; p.xamax = m->d_xamax;
-    if (m->flow_epoch == 0 || m->flow_epoch + uint32_t(n_steps) < m->flow_epoch) {   // the tag space wrapped: start over
-        FORGE_CUDA(cudaMemsetAsync(m->d_xbuf, 0, sizeof(uint2) * m->x_layer_stride * m->cfg.num_layers, m->stream));
-        FORGE_CUDA(cudaMemsetAsync(m->d_xamax, 0, sizeof(uint2) * 2 * m->flow_grid, m->stream));
-        m->flow_epoch = 1;
-    }
-    p.epoch = m->flow_epoch;
-    m->flow_epoch += uint32_t(n_steps);
-    p.n_steps = n_steps; p.greedy = greedy ? 1 : 0;
-    p.wait_limit = m->wait_limit;
-    p.tok = m->d_tok; p.hist = greedy ? m->d_hist : nullptr; p.step = greedy ? m->d_step : nullptr;
-    p.logits = m->d_logits; p.err = m->d_err;
-    return decode_flow(p, m->cfg.quant, m->flow_max_kb, m->flow_grid, m->stream);
 }
 
 int32_t decode_step_graph(ForgeModel* m, ForgeKV* kv, int batch, bool greedy) {
@@ -1079,9 +1036,7 @@ int32_t forge_forward_seq(ForgeModel* m, ForgeKV* kv, int32_t seq, uint32_t toke
     view.d_seq_len = kv->d_seq_len + seq;
     view.graph = nullptr;
     int32_t rc;
-    if (flow_eligible(m)) {
-        rc = decode_flow_steps(m, kv, view.d_page_table, view.d_seq_len, 1, false);
-    } else if (seq == 0 && kv->batch >= 1 && !m->trace_on) {
+    if (seq == 0 && kv->batch >= 1 && !m->trace_on) {
         rc = decode_step_graph(m, kv, 1, false);
     } else {
         rc = decode_launches(m, &view, 1, false, false);
@@ -1133,17 +1088,10 @@ int32_t forge_decode_greedy_batch(ForgeModel* m, ForgeKV* kv, int32_t batch, con
     m->trace_on = false;
     const std::vector<int> len0 = kv->len;
     int32_t rc = FORGE_OK;
-    if (batch == 1 && flow_eligible(m)) {
-        // all n_new steps in one launch: the kernel feeds every arg-max to the next step itself
-        rc = ensure_pages(kv, 0, kv->len[0] + n_new);
-        if (rc == FORGE_OK) rc = decode_flow_steps(m, kv, kv->d_page_table, kv->d_seq_len, n_new, true);
-        if (rc == FORGE_OK) kv->len[0] += n_new;
-    } else {
-        for (int i = 0; i < n_new && rc == FORGE_OK; ++i) {
-            rc = decode_prepare(kv, batch);
-            if (rc == FORGE_OK) rc = decode_step_graph(m, kv, batch, true);
-            if (rc == FORGE_OK) for (int b = 0; b < batch; ++b) kv->len[b] += 1;
-        }
+    for (int i = 0; i < n_new && rc == FORGE_OK; ++i) {
+        rc = decode_prepare(kv, batch);
+        if (rc == FORGE_OK) rc = decode_step_graph(m, kv, batch, true);
+        if (rc == FORGE_OK) for (int b = 0; b < batch; ++b) kv->len[b] += 1;
     }
     m->trace_on = saved_trace;
     if (rc != FORGE_OK) { cudaStreamSynchronize(m->stream); kv->len = len0; upload_len(kv); return rc; }
@@ -1203,12 +1151,6 @@ int32_t forge_model_set_prefill_mode(ForgeModel* m, int32_t mode) {
     if (!m || (mode != 0 && mode != 1)) { set_error("prefill mode must be 0 or 1"); return FORGE_ERR_INVALID_ARG; }
     if (mode == 1 && m->per_token_prefill) { set_error("this mix of storage formats has no batched prompt path"); return FORGE_ERR_UNSUPPORTED; }
     m->kquant_batched = mode == 1;
-    return FORGE_OK;
-}
-
-int32_t forge_model_set_decode_mode(ForgeModel* m, int32_t mode) {
-    if (!m || (mode != 0 && mode != 1)) { set_error("decode mode must be 0 or 1"); return FORGE_ERR_INVALID_ARG; }
-    m->use_flow = mode == 1;
     return FORGE_OK;
 }
 

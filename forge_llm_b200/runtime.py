@@ -192,10 +192,6 @@ class Model:
         """K-quant models: 0 = prompt token by token (default, the reference's structure), 1 = batched GEMMs."""
         check(lib.forge_model_set_prefill_mode(self._h, mode))
 
-    def set_decode_mode(self, mode: int) -> None:
-        """1 = one persistent kernel for all the steps of a call (default), 0 = CUDA-graph replay of per-operator kernels."""
-        check(lib.forge_model_set_decode_mode(self._h, mode))
-
     def set_wait_limit(self, polls: int) -> None:
         """Polls a device-side wait makes before it gives up (the call then fails with status TIMEOUT)."""
         check(lib.forge_model_set_wait_limit(self._h, polls))

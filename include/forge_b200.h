@@ -247,20 +247,13 @@ int32_t forge_model_set_gemm_passes(ForgeModel* model, int32_t passes);
  * 1e-3 .. 4e-3 there, against < 1e-3 for mode 0).  No effect on Q8_0 / Q4_0 models (always batched). */
 int32_t forge_model_set_prefill_mode(ForgeModel* model, int32_t mode);
 
-/* How batch-1 decode steps (forward(), E:4029-4500, and the greedy loop around it, P:727-751) are issued.
- * 1 (default): one persistent cooperative kernel runs all the steps of a call - a CTA per SM, weights streamed
- *   continuously, operators handing their results to one another as {value, tag} pairs in global memory with
- *   bounded waits (no grid barrier, no kernel boundary); it needs every SM of the GPU while it runs.  Taken for
- *   Q8_0 / Q4_0 models on one GPU with full attention; everything else falls back to mode 0.
- * 0: one kernel per fused operator, the step replayed as a CUDA graph. */
-int32_t forge_model_set_decode_mode(ForgeModel* model, int32_t mode);
-
-/* Polls a device-side wait makes before it gives up (the reference has no counterpart: its CPU threads join).
- * Every wait inside the kernels - a pipeline stage, another CTA's result, a tensor-parallel peer's contribution - is
+/* Polls a device-side wait for a tensor-parallel peer's contribution makes before it gives up (the reference has no
+ * counterpart: its CPU threads join).  Every wait inside the kernels - a pipeline stage, a peer's partial sums - is
  * bounded; when one runs out the kernel finishes by itself, and the session call that launched it returns
  * FORGE_ERR_TIMEOUT at its synchronisation point, with the cache positions as they were before the call.
- * The default (2^21 polls, a fraction of a second) suits production; tests set it small. */
+ * The default (2^20 polls, about a second) suits production; tests set it small. */
 int32_t forge_model_set_wait_limit(ForgeModel* model, uint32_t polls);
+
 
 /* KVCache::new (E:3978-4000) for `batch` independent sequences of up to max_seq positions,
  * fp16, paged (FORGE_KV_PAGE positions per page, pages handed out on demand). */

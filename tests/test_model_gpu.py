@@ -256,15 +256,16 @@ def test_kv_overflow_is_an_error_status(oracle):
     gm.close()
 
 
-def test_batched_decode_equals_independent_sequences(oracle):
-    # the reference has no batched decode: a batch is B independent forward() calls
+@pytest.mark.parametrize("quant,hd,nq,nkv,bias,B", [(8, 64, 4, 2, 0, 5), (8, 64, 4, 2, 1, 8), (4, 96, 2, 2, 0, 16), (8, 128, 2, 1, 1, 16)])
+def test_batched_decode_equals_independent_sequences(oracle, quant, hd, nq, nkv, bias, B):
+    # the reference has no batched decode: a batch is B independent forward() calls.  Fewer than 8 sequences run through
+    # the per-token products; 8 and more through one tensor-core product per projection (the weights are read once)
     from forge_llm_b200 import configs, runtime, synth
-    c = configs.tiny(8, hd=64, nq=4, nkv=2)
+    c = configs.tiny(quant, hd=hd, nq=nq, nkv=nkv, bias=bias)
     blob = synth.make_weights_bin(c)
     gm = runtime.Model(c, blob)
-    B = 5
     kv = gm.new_cache(max_seq=256, batch=B)
-    lens = [9, 64, 100, 17, 130]
+    lens = [9, 64, 100, 17, 130, 63, 65, 1, 128, 33, 77, 12, 150, 2, 90, 129][:B]
     oms, last = [], []
     for b in range(B):
         toks = synth.prompt_tokens(c, lens[b], seed=10 + b)
@@ -274,6 +275,12 @@ def test_batched_decode_equals_independent_sequences(oracle):
         assert np.abs(lg - lo).max() < LOGIT_TOL
         oms.append(om)
         last.append(lo)
+    # one teacher-forced step with the logits of every sequence compared
+    ts = np.array([oracle.argmax(l) for l in last], np.uint32)
+    lg = gm.forward_batch(ts, kv)
+    for b in range(B):
+        last[b] = oms[b].forward(int(ts[b]))
+        assert np.abs(lg[b] - last[b]).max() < LOGIT_TOL
     first = np.array([oracle.argmax(l) for l in last], np.uint32)
     ref = np.zeros((12, B), np.uint32)
     for b in range(B):
@@ -284,7 +291,7 @@ def test_batched_decode_equals_independent_sequences(oracle):
             lo = oms[b].forward(t)
     got = gm.decode_greedy_batch(first, 12, kv)
     assert np.array_equal(got, ref)
-    assert [kv.len(b) for b in range(B)] == [l + 12 for l in lens]
+    assert [kv.len(b) for b in range(B)] == [l + 13 for l in lens]
     kv.close()
     gm.close()
 
@@ -302,33 +309,6 @@ def test_reduced_configs(oracle, key, layers, vocab, n_prompt):
     # that the oracle finishes in seconds
     from forge_llm_b200 import configs
     _run_case(oracle, configs.reduced(key, layers, vocab), n_prompt=n_prompt, n_decode=2, n_greedy=32)
-
-
-@pytest.mark.parametrize("quant,hd,nq,nkv,bias", [(4, 64, 4, 2, 0), (8, 64, 7, 1, 1), (8, 96, 2, 2, 0), (4, 128, 2, 1, 1)])
-def test_whole_step_decode_kernel(oracle, quant, hd, nq, nkv, bias):
-    # decode mode 1: the step as one persistent cooperative kernel; same gates as the default mode
-    from forge_llm_b200 import configs, runtime, synth
-    c = configs.tiny(quant, hd=hd, nq=nq, nkv=nkv, bias=bias, hidden=nq * hd if (nq * hd) % 32 == 0 else 448)
-    blob = synth.make_weights_bin(c)
-    toks = synth.prompt_tokens(c, 150)
-    gm = runtime.Model(c, blob)
-    gm.set_decode_mode(1)
-    kv = gm.new_cache(max_seq=256)
-    om = oracle.OracleModel(c, blob, kv_mode=oracle.KV_F16)
-    lo = om.forward_prefill(toks)
-    gm.forward_prefill(toks, kv)
-    for _ in range(6):
-        t = oracle.argmax(lo)
-        lo = om.forward(t)
-        lg = gm.forward(t, kv)
-        assert np.abs(lg - lo).max() < LOGIT_TOL
-    kv.reset()
-    om.reset()
-    ref_ids, _ = om.generate_greedy(toks, 32)
-    assert np.array_equal(gm.generate_greedy(toks, 32, kv), ref_ids)
-    assert kv.len() == 182
-    kv.close()
-    gm.close()
 
 
 @pytest.mark.gpu
