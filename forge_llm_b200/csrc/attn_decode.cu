@@ -45,14 +45,15 @@ __global__ void __launch_bounds__(kThreads) attn_decode_kernel(DecParams p) {
     __shared__ int s_last;
     const AttnDecodeArgs& a = p.a;
     pdl_trigger();
-    pdl_wait();  // q and the newest cache row come from the kernel before this one
     const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int seg = lane / W, sl = lane % W;
     const bool act = sl < ACTIVE;
     const int G = a.nq / a.nkv, kvd = a.nkv * HD;
     // Split s owns the logical pages s, s + splits, ...: which pages a CTA reads does not depend on the context
-    // length, so its first page-table entry is fetched together with the length and the query (one round trip).
+    // length.  The length, the page table and every cached row but the newest were written before the kernel in front
+    // of this one started, so they are read BEFORE the dependency wait: the first batch of K/V loads of the CTA is in
+    // flight while that kernel (which produces q and the newest row) is still running.
     const int32_t* pt = a.page_table ? a.page_table + size_t(b) * a.pages_per_seq : nullptr;
     const int page0 = (pt && split < a.pages_per_seq) ? pt[split] : split;
     const int n_ctx = a.seq_len ? a.seq_len[b] + 1 : a.seq_len_host;
@@ -60,6 +61,39 @@ __global__ void __launch_bounds__(kThreads) attn_decode_kernel(DecParams p) {
     const int t_first = (SW && n_ctx > a.window) ? n_ctx - a.window : 0;  // sliding window: first position seen
     const size_t seq_base = a.page_table ? 0 : size_t(b) * a.max_ctx;  // contiguous: [batch][max_ctx][kvd]
     const int part = warp * RPW + seg;
+    constexpr int UNR = 4;  // positions per segment whose K/V loads are issued before any use
+    // loads of one batch of positions of logical page lp; `hold` (a position, or -1) is left out
+    auto issue = [&](int lp, int page, int base, uint4 (&kr)[UNR], uint4 (&vr)[UNR], int hold) {
+        const size_t page_row = seq_base + size_t(page) * FORGE_KV_PAGE;
+        const int t_page = lp * FORGE_KV_PAGE;
+#pragma unroll
+        for (int u = 0; u < UNR; ++u) {
+            const int tp = base + u * PARTS + seg;
+            kr[u] = make_uint4(0, 0, 0, 0);
+            vr[u] = make_uint4(0, 0, 0, 0);
+            if (tp < FORGE_KV_PAGE && t_page + tp < n_ctx && t_page + tp != hold && (!SW || t_page + tp >= t_first) && act) {
+                const size_t off = (page_row + tp) * kvd + kvh * HD + sl * 8;
+                kr[u] = __ldg(reinterpret_cast<const uint4*>(a.k_pool + off));
+                vr[u] = __ldg(reinterpret_cast<const uint4*>(a.v_pool + off));
+            }
+        }
+    };
+    uint4 kr0[UNR], vr0[UNR];
+    const bool early = split < n_pages && !(SW && (split + 1) * FORGE_KV_PAGE <= t_first);
+    if (early) issue(split, page0, warp * RPW, kr0, vr0, n_ctx - 1);
+    pdl_wait();  // q and the newest cache row come from the kernel before this one
+    if (early) {   // the newest row, if it is in the first batch
+        const int t_page = split * FORGE_KV_PAGE;
+#pragma unroll
+        for (int u = 0; u < UNR; ++u) {
+            const int tp = warp * RPW + u * PARTS + seg;
+            if (tp < FORGE_KV_PAGE && t_page + tp == n_ctx - 1 && act) {
+                const size_t off = (seq_base + size_t(page0) * FORGE_KV_PAGE + tp) * kvd + kvh * HD + sl * 8;
+                kr0[u] = __ldcg(reinterpret_cast<const uint4*>(a.k_pool + off));
+                vr0[u] = __ldcg(reinterpret_cast<const uint4*>(a.v_pool + off));
+            }
+        }
+    }
 
     for (int g0 = 0; g0 < G; g0 += kGC) {
         const int gc = min(kGC, G - g0);
@@ -76,24 +110,17 @@ __global__ void __launch_bounds__(kThreads) attn_decode_kernel(DecParams p) {
                 q[g][4] = x1.x * p.scale; q[g][5] = x1.y * p.scale; q[g][6] = x1.z * p.scale; q[g][7] = x1.w * p.scale;
             }
         }
-        constexpr int UNR = 4;  // positions per segment whose K/V loads are issued before any use
         for (int lp = split; lp < n_pages; lp += a.splits) {
             if (SW && (lp + 1) * FORGE_KV_PAGE <= t_first) continue;  // the whole page lies before the window
             const int page = lp == split ? page0 : (pt ? pt[lp] : lp);
-            const size_t page_row = seq_base + size_t(page) * FORGE_KV_PAGE;
             const int t_page = lp * FORGE_KV_PAGE;
             for (int base = warp * RPW; base < FORGE_KV_PAGE; base += PARTS * UNR) {
                 uint4 kr[UNR], vr[UNR];
+                if (g0 == 0 && lp == split && base == warp * RPW) {   // the batch that was requested before the wait
 #pragma unroll
-                for (int u = 0; u < UNR; ++u) {
-                    const int tp = base + u * PARTS + seg;
-                    kr[u] = make_uint4(0, 0, 0, 0);
-                    vr[u] = make_uint4(0, 0, 0, 0);
-                    if (tp < FORGE_KV_PAGE && t_page + tp < n_ctx && (!SW || t_page + tp >= t_first) && act) {
-                        const size_t off = (page_row + tp) * kvd + kvh * HD + sl * 8;
-                        kr[u] = __ldg(reinterpret_cast<const uint4*>(a.k_pool + off));
-                        vr[u] = __ldg(reinterpret_cast<const uint4*>(a.v_pool + off));
-                    }
+                    for (int u = 0; u < UNR; ++u) { kr[u] = kr0[u]; vr[u] = vr0[u]; }
+                } else {
+                    issue(lp, page, base, kr, vr, -1);
                 }
                 // the UNR scores of a head are formed independently, then folded into the running state in one
                 // softmax step (one rescale per group instead of one per position)

@@ -391,6 +391,113 @@ __device__ __forceinline__ float stage_activation(uint2* xf, int4* xoff, Shared&
     return stage_finish<QUANT>(xf, xoff, sh, st, K, norm_w, eps);
 }
 
+// The same for Q8_0 / Q4_0 in one pass: item i of a thread covers elements 4tt..4tt+3 and 16+4tt..16+4tt+3 of k-block kb
+// (i = 4 kb + tt), exactly the values whose digits that thread writes, so they stay in registers from the load to
+// the conversion.  The row and the norm weights are requested together (one memory round trip), warps without an
+// item only take part in the barriers, and there are two barriers instead of three.  `fresh`: nobody can still be
+// reading the fragment area (first row of a launch).
+constexpr int kStageItems = 3;
+// the register form takes rows of up to kStageItems items per thread; a normalised row must fit one item per thread
+__device__ __forceinline__ bool stage_regs_ok(int K, const float* norm_w) { return K <= (norm_w ? 1 : kStageItems) * kCT * 8; }
+template <int QUANT>
+__device__ __forceinline__ float stage_activation_regs(uint2* xf, int4* xoff, Shared& sh, const float* x, int K,
+                                                       const float* norm_w, float eps, bool fresh) {
+    static_assert(!KQuant<QUANT>::value, "K-quant inputs are staged as Q8_0 blocks");
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int nitems = K / 8;
+    const bool busy = (warp << 5) < nitems;
+    float xv[kStageItems][8], nw[8];
+    float ss = 0.f, mx = 0.f;
+#pragma unroll
+    for (int q = 0; q < 8; ++q) nw[q] = 1.0f;
+#pragma unroll
+    for (int it = 0; it < kStageItems; ++it) {
+        const int i = it * kCT + tid;
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+        if (i < nitems) {
+            const int e0 = (i >> 2) * 32 + 4 * (i & 3);
+            a = *reinterpret_cast<const float4*>(x + e0);
+            b = *reinterpret_cast<const float4*>(x + e0 + 16);
+            if (norm_w && it == 0) {
+                const float4 na = __ldg(reinterpret_cast<const float4*>(norm_w + e0)), nb = __ldg(reinterpret_cast<const float4*>(norm_w + e0 + 16));
+                nw[0] = na.x; nw[1] = na.y; nw[2] = na.z; nw[3] = na.w; nw[4] = nb.x; nw[5] = nb.y; nw[6] = nb.z; nw[7] = nb.w;
+            }
+        }
+        xv[it][0] = a.x; xv[it][1] = a.y; xv[it][2] = a.z; xv[it][3] = a.w; xv[it][4] = b.x; xv[it][5] = b.y; xv[it][6] = b.z; xv[it][7] = b.w;
+    }
+    if (busy) {
+#pragma unroll
+        for (int it = 0; it < kStageItems; ++it)
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                ss += xv[it][q] * xv[it][q];
+                mx = fmaxf(mx, fabsf(it == 0 ? xv[it][q] * nw[q] : xv[it][q]));
+            }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) { ss += __shfl_xor_sync(0xffffffffu, ss, o); mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o)); }
+    }
+    if (!fresh) csync();  // the previous contents of the fragment area (and of sh.part) are no longer read
+    if (lane == 0) { sh.part[warp] = ss; sh.part[16 + warp] = mx; }
+    csync();
+    float s2 = 0.f, m2 = 0.f;
+#pragma unroll
+    for (int w = 0; w < kConsumerWarps; ++w) { s2 += sh.part[w]; m2 = fmaxf(m2, sh.part[16 + w]); }
+    const float inv = norm_w ? 1.0f / sqrtf(s2 / float(K) + eps) : 1.0f;
+    m2 *= inv;
+    // exact power-of-two scale that puts max|x| * 2^s in [2^29, 2^30): 31-bit signed fixed point
+    float sc = 1.0f;
+    if (m2 > 0.f && m2 < 3.0e38f) {
+        const int E = int(__float_as_uint(m2) >> 23);  // biased exponent: m2 = f * 2^(E - 126), f in [0.5, 1)
+        if (E >= 29) sc = __uint_as_float(uint32_t(283 - E) << 23);
+        else { int ex = 0; frexpf(m2, &ex); sc = ldexpf(1.0f, 30 - ex); }
+    }
+    // balanced base-256 digits (see stage_finish)
+#pragma unroll
+    for (int it = 0; it < kStageItems; ++it) {
+        if (it * kCT + (warp << 5) >= nitems) break;   // nothing left for this warp (warp-uniform)
+        const int i = it * kCT + tid;
+        const bool on = i < nitems;
+        const int kbi = i >> 2, tt = i & 3;
+        uint32_t y[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            const float v = (norm_w && it == 0) ? xv[it][q] * inv * nw[q] : xv[it][q];
+            y[q] = uint32_t(__float2int_rn(v * sc)) + 0x80808080u;
+        }
+        int dsum[4] = {0, 0, 0, 0};
+        if (on) {
+            uint32_t w[2][4];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const uint32_t a = __byte_perm(y[4 * h], y[4 * h + 1], 0x5140), b = __byte_perm(y[4 * h + 2], y[4 * h + 3], 0x5140);
+                const uint32_t c = __byte_perm(y[4 * h], y[4 * h + 1], 0x7362), d = __byte_perm(y[4 * h + 2], y[4 * h + 3], 0x7362);
+                w[h][0] = __byte_perm(a, b, 0x5410) ^ 0x80808080u;
+                w[h][1] = __byte_perm(a, b, 0x7632) ^ 0x80808080u;
+                w[h][2] = __byte_perm(c, d, 0x5410) ^ 0x80808080u;
+                w[h][3] = __byte_perm(c, d, 0x7632) ^ 0x80808080u;
+            }
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                dsum[c] = __dp4a(int(w[0][c]), 0x01010101, __dp4a(int(w[1][c]), 0x01010101, 0));
+                xf[(kbi * 4 + c) * 4 + tt] = make_uint2(w[0][c], w[1][c]);
+            }
+        }
+        if (QUANT == FORGE_Q4_0) {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                dsum[c] += __shfl_xor_sync(0xffffffffu, dsum[c], 1);
+                dsum[c] += __shfl_xor_sync(0xffffffffu, dsum[c], 2);
+            }
+            if (on && tt == 0) {
+                xoff[2 * kbi] = make_int4(-8 * dsum[0], -8 * dsum[1], -128 * dsum[0], -128 * dsum[1]);
+                xoff[2 * kbi + 1] = make_int4(-8 * dsum[2], -8 * dsum[3], -128 * dsum[2], -128 * dsum[3]);
+            }
+        }
+    }
+    csync();
+    return 1.0f / sc;
+}
+
 // ---- epilogue of one finished output row (runtime-selected fusion)
 // Operands that do not depend on the product, for the rows row0 (index 0) and row0 + 8 (index 1) of a thread.
 struct EpiPre {
@@ -475,9 +582,24 @@ __device__ __forceinline__ void epilogue_row(const Phase& ph, int b, int row, fl
 // ---- consumer side, step 2: all units of this CTA for one phase and one batch row.
 // `on_row(row, value, partner)` is called by the finishing thread after the epilogue, `partner` being the value of
 // row ^ 1; pass a no-op when there is nothing to add.  It is also called for the padding rows (row >= N).
+// Row pair (row0, row0 + 8) a thread finishes in unit u, and whether it is the thread that runs the epilogue
+// (shared by the consumer loop and by callers that fetch the first unit's epilogue operands ahead of time).
+__device__ __forceinline__ void unit_rows(const Phase& ph, int u, int ui, int& row0, bool& mine) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const bool wide = ph.bt == kBandTiles;
+    const int r8 = wide ? warp % kBandTiles : 0, khalf = wide ? warp / kBandTiles : warp;
+    int band, slice;
+    unit_split(u, ph.slices, band, slice);
+    row0 = (band * ph.bt + r8) * 16 + g;
+    mine = t == 0 && (wide ? khalf == 0 : warp == ui % kConsumerWarps);
+}
+
+// pre_first: the first unit's epilogue operands if the caller has fetched them already (have_pre_first)
 template <int QUANT, typename RowHook, bool TP = false>
 __device__ __forceinline__ void consume_phase(const Phase& ph, Shared& sh, const unsigned char* ring, const uint2* xf,
-                                              const int4* xoff, float unscale, int b, int& cc, RowHook on_row, int pos_hint = -1) {
+                                              const int4* xoff, float unscale, int b, int& cc, RowHook on_row, int pos_hint = -1,
+                                              bool have_pre_first = false, const EpiPre pre_first = EpiPre()) {
     using T = Tile<QUANT>;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
@@ -498,7 +620,8 @@ __device__ __forceinline__ void consume_phase(const Phase& ph, Shared& sh, const
         const int row0 = rt * 16 + g;  // and row0 + 8
         // operands of the epilogue that do not depend on the product are fetched now, under the tile loop
         // (the warp that will finish the unit: the even-k warp of the tile, or the unit's turn in the 16-row form)
-        const EpiPre pre = epilogue_prefetch<TP>(ph, b, row0, t == 0 && (wide ? khalf == 0 : warp == ui % kConsumerWarps), pos_hint);
+        const EpiPre pre = (ui == 0 && have_pre_first) ? pre_first
+                                                       : epilogue_prefetch<TP>(ph, b, row0, t == 0 && (wide ? khalf == 0 : warp == ui % kConsumerWarps), pos_hint);
         // per-lane accumulators: rows g / g+8 of this warp's row tile x digit columns 2t / 2t+1
         float acc[4] = {0.f, 0.f, 0.f, 0.f};
         for (int c = c0; c < c1; ++c, ++cc) {

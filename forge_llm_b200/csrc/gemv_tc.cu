@@ -96,6 +96,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tc_kernel(TcParams p) {
         // the position of the new cache row is needed late (epilogue) but heads a chain of dependent loads: ask now
         const int pos = ph.epi == EPI_QKV ? ph.a.seq_len[b] : -1;
         float unscale;
+        EpiPre pre0 = EpiPre();
+        bool have_pre0 = false;
         if (TP && ph.a.tp.consume) {
             // the input is a sum over the tensor-parallel ranks that arrives through peer stores (see GemvArgs::Tp)
             const GemvArgs::Tp& tp = ph.a.tp;
@@ -104,10 +106,27 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tc_kernel(TcParams p) {
                                                  ph.K, ph.a.norm_w, &sh.err, tp.wait_limit);
             unscale = stage_finish<QUANT>(xf, s_xoff, sh, st, ph.K, ph.a.norm_w, ph.a.eps);
         } else {
-            unscale = stage_activation<QUANT, false>(xf, s_xoff, sh, ph.a.x + size_t(b) * ph.K, ph.K, ph.a.norm_w, ph.a.eps);
+            bool staged = false;
+            if constexpr (!KQuant<QUANT>::value) {
+                if (stage_regs_ok(ph.K, ph.a.norm_w)) {
+                    // the first unit's epilogue operands (residual, position -> page -> rotation) are asked for now, so
+                    // their round trips run under the staging
+                    const int u0 = first_unit(ph, blockIdx.x, gridDim.x);
+                    if (u0 < ph.units) {
+                        int row0;
+                        bool mine;
+                        unit_rows(ph, u0, 0, row0, mine);
+                        pre0 = epilogue_prefetch<TP>(ph, b, row0, mine, pos);
+                        have_pre0 = true;
+                    }
+                    unscale = stage_activation_regs<QUANT>(xf, s_xoff, sh, ph.a.x + size_t(b) * ph.K, ph.K, ph.a.norm_w, ph.a.eps, b == 0);
+                    staged = true;
+                }
+            }
+            if (!staged) unscale = stage_activation<QUANT, false>(xf, s_xoff, sh, ph.a.x + size_t(b) * ph.K, ph.K, ph.a.norm_w, ph.a.eps);
         }
         auto no_hook = [](int, float, float) {};
-        consume_phase<QUANT, decltype(no_hook), TP>(ph, sh, ring, xf, s_xoff, unscale, b, cc, no_hook, pos);
+        consume_phase<QUANT, decltype(no_hook), TP>(ph, sh, ring, xf, s_xoff, unscale, b, cc, no_hook, pos, have_pre0, pre0);
     }
     csync();
     if (tid == 0 && sh.err && p.err) atomicExch(p.err, 1);
