@@ -52,6 +52,7 @@ SIGNATURES = {
     "forge_packed_create": (i32, [i32, vp, i32, i32, vp, C.POINTER(vp)]),
     "forge_packed_destroy": (None, [vp]),
     "forge_matmul_mat_packed": (i32, [vp, i32, vp, vp, vp]),
+    "forge_matmul_decode_batch": (i32, [vp, i32, vp, vp, vp]),
     "forge_packed_check": (i32, [vp, vp]),
     "forge_rms_norm": (i32, [vp, vp, vp, i32, i32, f32, vp]),
     "forge_rope_table": (i32, [vp, i32, i32, f32]),

@@ -31,6 +31,8 @@ struct ForgePacked {
     QTiled tiled;
     int* err = nullptr;
     GemvSplit split;
+    GemvSplit bsplit;         // split-K scratch of the batched decode product
+    uint2* bact = nullptr;    // its packed activations (sixteen rows)
 };
 
 namespace {
@@ -80,6 +82,7 @@ int32_t packed_build(int quant, const uint8_t* w, int K, int N, cudaStream_t st,
 void packed_free(ForgePacked* pk) {
     if (!pk) return;
     cudaFree(pk->soa.qs); cudaFree(pk->soa.d); cudaFree(pk->soa.sf); cudaFree(pk->tiled.data); cudaFree(pk->err); cudaFree(pk->split.scratch); cudaFree(pk->split.tickets);
+    cudaFree(pk->bsplit.scratch); cudaFree(pk->bsplit.tickets); cudaFree(pk->bact);
     delete pk;
 }
 
@@ -165,6 +168,29 @@ int32_t forge_matmul_mat_packed(float* out, int32_t m, const float* in, const Fo
     if (!out || !in || !w || m < 0) { set_error("bad argument to forge_matmul_mat_packed"); return FORGE_ERR_INVALID_ARG; }
     if (m == 0) return FORGE_OK;
     return matmul_packed(out, m, in, w, static_cast<cudaStream_t>(stream), false);
+}
+
+int32_t forge_matmul_decode_batch(float* out, int32_t nb, const float* in, ForgePacked* w, void* stream) {
+    FORGE_TRY(need_device());
+    if (!out || !in || !w || nb < 0 || nb > 16) { set_error("bad argument to forge_matmul_decode_batch (1..16 rows)"); return FORGE_ERR_INVALID_ARG; }
+    if (nb == 0) return FORGE_OK;
+    if (is_kquant(w->tiled.quant)) { set_error("forge_matmul_decode_batch takes Q8_0 / Q4_0 weights"); return FORGE_ERR_UNSUPPORTED; }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (!w->bact) {   // first use: the product's buffers
+        int dev = 0, sms = 148;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        FORGE_CUDA(cudaMalloc(&w->bact, sizeof(uint2) * gemv_batch_act_words(w->tiled.K, 16)));
+        const size_t fl = gemv_batch_scratch_floats(w->tiled.N, w->tiled.K, w->tiled.quant, sms), tk = gemv_batch_tickets(w->tiled.N);
+        if (fl) {
+            FORGE_CUDA(cudaMalloc(&w->bsplit.scratch, sizeof(float) * fl));
+            FORGE_CUDA(cudaMalloc(&w->bsplit.tickets, sizeof(int) * tk));
+            FORGE_CUDA(cudaMemsetAsync(w->bsplit.tickets, 0, sizeof(int) * tk, st));
+            w->bsplit.max_slices = kGemvMaxSlices;
+        }
+    }
+    FORGE_TRY(gemv_batch_pack(w->bact, in, size_t(w->tiled.K), nb, w->tiled.K, w->tiled.quant, 0, nullptr, 0.f, st));
+    return gemv_batch(w->tiled, w->bact, nb, out, nullptr, w->bsplit, w->err, st);
 }
 
 int32_t forge_packed_check(const ForgePacked* w, void* stream) {

@@ -164,10 +164,26 @@ int32_t tile_pack(const uint8_t* const* row_src_dev, QTiled& dst, cudaStream_t s
 // err: device int set to 1 if a bounded wait inside the kernel gave up (may be null)
 int32_t gemv_tc(const QTiled& w, GemvEpilogue epi, const GemvArgs& a, const GemvSplit& sp, int* err, cudaStream_t st);
 
+// ------------------------------------------------------------------ batched decode products (gemv_batch.cu)
+// out[b][N] (+ resid) = x[b][K] . W^T for nb <= 16 rows per launch, the tiled weights streamed once.  The activations
+// are packed first (gemv_batch_pack) into fp16 hi/lo B fragments; mode: 0 plain rows, 1 RMSNorm(x) * norm_w,
+// 2 SiLU(gate) * up of interleaved [2 * K] rows.
+int gemv_batch_ncg(int nb);
+size_t gemv_batch_act_words(int K, int nb);          // uint2 entries the packed activations take
+size_t gemv_batch_scratch_floats(int N, int K, int quant, int sms);   // split-K scratch a matrix needs (0: not split)
+size_t gemv_batch_tickets(int N);
+int gemv_batch_slices(int groups, int chunks, int sms);
+int32_t gemv_batch_pack(uint2* dst, const float* x, size_t x_stride, int nb, int K, int quant, int mode, const float* norm_w, float eps, cudaStream_t st);
+int32_t gemv_batch(const QTiled& w, const uint2* act, int nb, float* out, const float* resid, const GemvSplit& sp, int* err, cudaStream_t st);
+
 // ------------------------------------------------------------------ elementwise
 int32_t rms_norm_f32(float* out, const float* in, const float* w, int rows, int n, float eps, cudaStream_t st);
 // fp16 outputs come as a hi/lo pair when `lo` is given: hi = fp16(x), lo = fp16(x - hi)
 int32_t rms_norm_f16(__half* out, __half* lo, const float* in, const float* w, int rows, int n, float eps, cudaStream_t st);
+// hidden[r] += parts[0][r] + parts[1][r] + ... (fixed order; part s at parts + s * pstride), then, if w is given,
+// out / lo = RMSNorm(hidden[r]) * w as an fp16 hi/lo pair: the residual add and the next operator's normalisation in one pass
+int32_t add_parts_rms_norm_f16(float* hidden, const float* parts, int nparts, size_t pstride, __half* out, __half* lo, const float* w,
+                               int rows, int n, float eps, cudaStream_t st);
 int32_t rope_rows(float* data, int rows, int base_pos, int head_dim, int heads, const float* table, cudaStream_t st);
 int32_t silu_mul_f32(float* out, const float* g, const float* u, size_t n, cudaStream_t st);
 int32_t silu_mul_f16(__half* out, __half* lo, const float* gu, int rows, int ffn, cudaStream_t st);  // gu = interleaved [rows][2*ffn]
@@ -176,8 +192,9 @@ int32_t residual_add_f32(float* a, const float* b, size_t n, cudaStream_t st);
 int32_t embedding_rows(float* out, const float* table, const uint32_t* tokens, int rows, int h, uint32_t* hist, const int32_t* step, cudaStream_t st);
 int32_t kv_append_contig(__half* kc, __half* vc, const float* k, const float* v, int rows, int base_pos, int kvd, cudaStream_t st);
 // prefill QKV epilogue: bias, RoPE, q -> fp16 [m][qk], k/v -> paged fp16 cache
+// nparts > 1: the product arrives as K-slice partials (pstride floats apart), added in slice order
 int32_t qkv_post(const float* qkv, int m, int base_pos, const float* bias, const float* rope, __half* q16, __half* q16_lo,
-                 __half* k_pool, __half* v_pool, const int32_t* page_row, int qk, int kv, int hd, cudaStream_t st);
+                 __half* k_pool, __half* v_pool, const int32_t* page_row, int qk, int kv, int hd, cudaStream_t st, int nparts = 1, size_t pstride = 0);
 // batched decode QKV epilogue: row b is sequence b at position seq_len[b]; q stays f32, k/v go to the sequence's page
 int32_t qkv_post_rows(const float* qkv, int batch, const float* bias, const float* rope, float* q_out, __half* k_pool, __half* v_pool,
                       const int32_t* page_table, const int32_t* seq_len, int pages_per_seq, int qk, int kv, int hd, cudaStream_t st);
@@ -230,6 +247,9 @@ int32_t attn_prefill_q32(const AttnPrefillArgs& a, const float* q32, cudaStream_
 int32_t gemm_f16a(float* out, const __half* A, const __half* Alo, const QWeight& w, int m, const float* resid, int* err, cudaStream_t st);
 int32_t gemm_f16a_mma(float* out, const __half* A, const __half* Alo, const QWeight& w, int m, const float* resid, cudaStream_t st);
 bool gemm_tc5_supported(const QWeight& w);
-int32_t gemm_tc5(float* out, const __half* A, const __half* Alo, const QWeight& w, int m, const float* resid, int* err, cudaStream_t st);
+// ksplit > 1: K slice z leaves its partial product (no residual) at out + z * part_stride; the caller adds the slices
+int32_t gemm_tc5(float* out, const __half* A, const __half* Alo, const QWeight& w, int m, const float* resid, int* err, cudaStream_t st,
+                 int ksplit = 1, size_t part_stride = 0);
+int gemm_tc5_ksplit(const QWeight& w);
 
 }  // namespace forge

@@ -76,6 +76,50 @@ __global__ void __launch_bounds__(256) rms_norm_f16_vec_kernel(__half* __restric
     }
 }
 
+// residual_add (emit.rs:455-459) of a product that arrives as K-slice partials, fused with the rms_norm (emit.rs:327-334)
+// of the next operator: hidden += part_0 + part_1 + ... in slice order, the row stays in registers for the normalisation
+template <int NV>
+__global__ void __launch_bounds__(256) add_parts_norm_kernel(float* __restrict__ hidden, const float* __restrict__ parts, int nparts, size_t pstride,
+                                                              __half* __restrict__ out, __half* __restrict__ lo, const float* __restrict__ w, int n, float eps) {
+    __shared__ float red[32];
+    float* x = hidden + size_t(blockIdx.x) * n;
+    const float* pr = parts + size_t(blockIdx.x) * n;
+    float4 v[NV];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int e = (threadIdx.x + i * 256) * 4;
+        v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (e < n) {
+            v[i] = *reinterpret_cast<const float4*>(x + e);
+            for (int s = 0; s < nparts; ++s) {
+                const float4 a = *reinterpret_cast<const float4*>(pr + size_t(s) * pstride + e);
+                v[i].x += a.x; v[i].y += a.y; v[i].z += a.z; v[i].w += a.w;
+            }
+            *reinterpret_cast<float4*>(x + e) = v[i];
+        }
+        ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+    }
+    if (!w) return;
+    ss = block_sum(ss, red);
+    const float inv = 1.0f / sqrtf(ss / float(n) + eps);
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int e = (threadIdx.x + i * 256) * 4;
+        if (e >= n) continue;
+        const float4 ww = *reinterpret_cast<const float4*>(w + e);
+        const float r[4] = {v[i].x * inv * ww.x, v[i].y * inv * ww.y, v[i].z * inv * ww.z, v[i].w * inv * ww.w};
+        const __half2 h0 = __floats2half2_rn(r[0], r[1]), h1 = __floats2half2_rn(r[2], r[3]);
+        const size_t o = size_t(blockIdx.x) * n + e;
+        *reinterpret_cast<uint2*>(out + o) = make_uint2(*reinterpret_cast<const uint32_t*>(&h0), *reinterpret_cast<const uint32_t*>(&h1));
+        if (lo) {
+            const float2 f0 = __half22float2(h0), f1 = __half22float2(h1);
+            const __half2 l0 = __floats2half2_rn(r[0] - f0.x, r[1] - f0.y), l1 = __floats2half2_rn(r[2] - f1.x, r[3] - f1.y);
+            *reinterpret_cast<uint2*>(lo + o) = make_uint2(*reinterpret_cast<const uint32_t*>(&l0), *reinterpret_cast<const uint32_t*>(&l1));
+        }
+    }
+}
+
 // thread per (row, head, pair): adjacent-pair rotation, table = {cos, sin}[pos][hd/2]
 __global__ void rope_kernel(float* data, int rows, int base_pos, int hd, int heads, const float2* __restrict__ table) {
     int half = hd / 2;
@@ -125,7 +169,8 @@ __global__ void kv_append_contig_kernel(__half* kc, __half* vc, const float* k, 
 }
 
 // prefill glue: fused [q;k;v] f32 rows -> (+bias) -> RoPE on q,k -> q fp16, k/v into the paged cache
-__global__ void qkv_post_kernel(const float* __restrict__ qkv, int m, int base_pos, const float* __restrict__ bias,
+// (the product may arrive as `nparts` K-slice partials, pstride floats apart: they are added in slice order)
+__global__ void qkv_post_kernel(const float* __restrict__ qkv, int nparts, size_t pstride, int m, int base_pos, const float* __restrict__ bias,
                                 const float2* __restrict__ rope, __half* __restrict__ q16, __half* __restrict__ q16_lo, __half* __restrict__ k_pool,
                                 __half* __restrict__ v_pool, const int32_t* __restrict__ page_row, int qk, int kv, int hd) {
     const int npairs = (qk + 2 * kv) / 2;
@@ -136,6 +181,10 @@ __global__ void qkv_post_kernel(const float* __restrict__ qkv, int m, int base_p
     const size_t prow = (size_t(page_row ? page_row[lp] : lp) * FORGE_KV_PAGE + pos % FORGE_KV_PAGE) * kv;
     for (int i = threadIdx.x; i < npairs; i += blockDim.x) {
         float2 v = src[i];
+        for (int s = 1; s < nparts; ++s) {
+            const float2 a = reinterpret_cast<const float2*>(qkv + size_t(s) * pstride + size_t(r) * (qk + 2 * kv))[i];
+            v.x += a.x; v.y += a.y;
+        }
         int col = 2 * i;
         if (bias) { v.x += bias[col]; v.y += bias[col + 1]; }
         int region = 0;
@@ -331,6 +380,16 @@ int32_t rms_norm_f16(__half* out, __half* lo, const float* in, const float* w, i
     FORGE_LAUNCH_CHECK();
     return FORGE_OK;
 }
+int32_t add_parts_rms_norm_f16(float* hidden, const float* parts, int nparts, size_t pstride, __half* out, __half* lo, const float* w,
+                               int rows, int n, float eps, cudaStream_t st) {
+    if (rows <= 0) return FORGE_OK;
+    if (n % 4 || n > 8192) { set_error("add_parts_rms_norm: row length %d unsupported", n); return FORGE_ERR_SHAPE; }
+    if (n <= 2048) add_parts_norm_kernel<2><<<rows, 256, 0, st>>>(hidden, parts, nparts, pstride, out, lo, w, n, eps);
+    else if (n <= 4096) add_parts_norm_kernel<4><<<rows, 256, 0, st>>>(hidden, parts, nparts, pstride, out, lo, w, n, eps);
+    else add_parts_norm_kernel<8><<<rows, 256, 0, st>>>(hidden, parts, nparts, pstride, out, lo, w, n, eps);
+    FORGE_LAUNCH_CHECK();
+    return FORGE_OK;
+}
 int32_t rope_rows(float* data, int rows, int base_pos, int head_dim, int heads, const float* table, cudaStream_t st) {
     size_t n = size_t(rows) * heads * (head_dim / 2);
     if (n == 0) return FORGE_OK;
@@ -371,9 +430,9 @@ int32_t kv_append_contig(__half* kc, __half* vc, const float* k, const float* v,
     return FORGE_OK;
 }
 int32_t qkv_post(const float* qkv, int m, int base_pos, const float* bias, const float* rope, __half* q16, __half* q16_lo,
-                 __half* k_pool, __half* v_pool, const int32_t* page_row, int qk, int kv, int hd, cudaStream_t st) {
+                 __half* k_pool, __half* v_pool, const int32_t* page_row, int qk, int kv, int hd, cudaStream_t st, int nparts, size_t pstride) {
     if (m <= 0) return FORGE_OK;
-    qkv_post_kernel<<<m, 256, 0, st>>>(qkv, m, base_pos, bias, reinterpret_cast<const float2*>(rope), q16, q16_lo, k_pool, v_pool, page_row, qk, kv, hd);
+    qkv_post_kernel<<<m, 256, 0, st>>>(qkv, nparts, pstride, m, base_pos, bias, reinterpret_cast<const float2*>(rope), q16, q16_lo, k_pool, v_pool, page_row, qk, kv, hd);
     FORGE_LAUNCH_CHECK();
     return FORGE_OK;
 }

@@ -2,7 +2,7 @@
 // streamed as Q8_0 / Q4_0 blocks and dequantised on the fly (replaces matmul_mat_q8_0_KxN /
 // matmul_mat_q4_0_KxN, crates/forgellm-codegen-cpu/src/emit.rs:2278-2299 and :3792-3813).
 //
-// CTA tile: 128 weight rows (MMA M) x NT tokens (MMA N = 128, 192 or 256; 32 for a batched decode step), K step 64.  The dequantised weight
+// CTA tile: 128 weight rows (MMA M) x NT tokens (MMA N = 128, 192 or 256), K step 64.  The dequantised weight
 // tile is the A operand and lives in TENSOR memory; the activation tile is the B operand in shared memory;
 // D[weight row][token] accumulates in tensor memory (f32).  Warp roles (320 threads):
 //   warp 0      TMA producer: 2-D tiled bulk copies (SWIZZLE_128B) of the fp16 activation tiles (hi and lo
@@ -23,6 +23,7 @@
 // Every wait is bounded; a wait that gives up sets an error word, and the CTA still frees its TMEM.
 #include <cuda.h>
 
+#include <algorithm>
 #include <cstdlib>
 #include <cstring>
 
@@ -81,6 +82,8 @@ struct Tc5Params {
     const uint8_t* qs; const __half* d; const float4* sf;
     int m, N, K;
     int* err;
+    int ksplit;            // K slices (grid.z); slice z leaves its partial product at out + z * part_stride
+    size_t part_stride;
 };
 
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
@@ -176,7 +179,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_ts_kernel(const __grid_const
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n0 = blockIdx.x * 128, m0 = blockIdx.y * NT;
-    const int nk = p.K / BK;
+    // K steps of this CTA: the whole K, or slice blockIdx.z of it (a shorter accumulation chain per accumulator, and
+    // more CTAs for matrices with few row tiles; the slices' partial products are added by the consumer)
+    const int nk_all = p.K / BK;
+    const int kt_begin = (nk_all * int(blockIdx.z)) / p.ksplit;
+    const int nk = (nk_all * (int(blockIdx.z) + 1)) / p.ksplit - kt_begin;
 
     if (tid == 0) {
         for (int s = 0; s < XS; ++s) { mbar_init(&full_x[s], 1); mbar_init(&empty_x[s], 1); }
@@ -202,8 +209,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_ts_kernel(const __grid_const
                 if (use > 0 && !mbar_wait(&empty_x[s], (use - 1) & 1, &s_err)) { atomicExch(&s_err, 1); break; }
                 mbar_expect_tx(&full_x[s], uint32_t(X_STAGE));
                 unsigned char* dst = sX + size_t(s) * X_STAGE;
-                tma_load_2d(dst, &map_hi, kt * BK, m0, &full_x[s]);
-                if (SPLIT) tma_load_2d(dst + X_TILE, &map_lo, kt * BK, m0, &full_x[s]);
+                tma_load_2d(dst, &map_hi, (kt_begin + kt) * BK, m0, &full_x[s]);
+                if (SPLIT) tma_load_2d(dst + X_TILE, &map_lo, (kt_begin + kt) * BK, m0, &full_x[s]);
             }
         }
     } else if (warp == 1) {
@@ -241,9 +248,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_ts_kernel(const __grid_const
         const size_t qrow = QUANT == FORGE_Q4_0 ? size_t(p.K) / 2 : size_t(p.K);
         constexpr int QB = QUANT == FORGE_Q4_0 ? 16 : 32;
         constexpr int QV = QB / 16;
-        const uint8_t* qsrc = p.qs + size_t(n_ok ? n : 0) * qrow + size_t(blk) * QB;
-        const __half* dsrc = KQ ? nullptr : p.d + size_t(n_ok ? n : 0) * (p.K / 32) + blk;
-        const float4* fsrc = KQ ? p.sf + size_t(n_ok ? n : 0) * (p.K / 32) + blk : nullptr;
+        const uint8_t* qsrc = p.qs + size_t(n_ok ? n : 0) * qrow + size_t(blk) * QB + size_t(kt_begin) * (2 * QB);
+        const __half* dsrc = KQ ? nullptr : p.d + size_t(n_ok ? n : 0) * (p.K / 32) + blk + 2 * kt_begin;
+        const float4* fsrc = KQ ? p.sf + size_t(n_ok ? n : 0) * (p.K / 32) + blk + 2 * kt_begin : nullptr;
         constexpr int kPrefetch = 4;
         uint4 q[kPrefetch][QV];
         __half dsc[kPrefetch];
@@ -306,9 +313,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_ts_kernel(const __grid_const
         if (!mbar_wait(&accum_full, 0, &s_err)) atomicExch(&s_err, 1);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const int col_n = n0 + r;
-        // (a 32-token tile is one 32-column read: the first warp of the quadrant takes it)
+        float* const outp = p.out + size_t(blockIdx.z) * p.part_stride;
 #pragma unroll 1
-        for (int c0 = NT >= 64 ? blk * (NT / 2) : 0; c0 < (NT >= 64 ? (blk + 1) * (NT / 2) : (blk == 0 ? NT : 0)); c0 += 32) {
+        for (int c0 = blk * (NT / 2); c0 < (blk + 1) * (NT / 2); c0 += 32) {
             uint32_t v[32];
             const uint32_t taddr = tmem + (uint32_t(quad * 32) << 16) + uint32_t(c0);
             asm volatile(
@@ -326,7 +333,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_ts_kernel(const __grid_const
                     const int row = m0 + c0 + j;
                     if (row < p.m) {
                         const size_t off = size_t(row) * p.N + col_n;
-                        p.out[off] = (p.resid ? p.resid[off] : 0.f) + __uint_as_float(v[j]);
+                        outp[off] = (p.resid ? p.resid[off] : 0.f) + __uint_as_float(v[j]);
                     }
                 }
             }
@@ -382,7 +389,7 @@ int32_t launch_ts(const __half* A, const __half* Alo, const Tc5Params& p, cudaSt
     const size_t smem = size_t(XS) * STAGE + 1024;
     auto kern = gemm_ts_kernel<QUANT, NT, SPLIT, XS>;
     FORGE_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
-    dim3 grid((p.N + 127) / 128, (p.m + NT - 1) / NT);
+    dim3 grid((p.N + 127) / 128, (p.m + NT - 1) / NT, p.ksplit);
     kern<<<grid, kThreads, smem, st>>>(mh, ml, p);
     FORGE_LAUNCH_CHECK();
     return FORGE_OK;
@@ -392,10 +399,18 @@ int32_t launch_ts(const __half* A, const __half* Alo, const Tc5Params& p, cudaSt
 
 bool gemm_tc5_supported(const QWeight& w) { return w.K % BK == 0 && w.K >= BK; }
 
-int32_t gemm_tc5(float* out, const __half* A, const __half* Alo, const QWeight& w, int m, const float* resid, int* err, cudaStream_t st) {
+// K slices for a product whose result is added to a residual stream anyway (the consumer adds the slices): as many as
+// keep at least 16 K steps (1024 columns) per slice, at most 4.  A tensor-memory accumulator rounds toward zero at every
+// accumulation, a bias that grows with the chain (measured: 7e-6 of the result at K = 2048, 2.7e-5 at K = 8192) and,
+// being one-sided, adds up over the layers; shorter chains keep it at the K = 2048 level.
+int gemm_tc5_ksplit(const QWeight& w) { return std::max(1, std::min(4, w.K / 2048)); }
+
+int32_t gemm_tc5(float* out, const __half* A, const __half* Alo, const QWeight& w, int m, const float* resid, int* err, cudaStream_t st,
+                 int ksplit, size_t part_stride) {
     if (m <= 0) return FORGE_OK;
     if (!gemm_tc5_supported(w)) { set_error("tcgen05 gemm: K=%d must be a multiple of %d", w.K, BK); return FORGE_ERR_SHAPE; }
-    Tc5Params p{out, resid, w.qs, w.d, w.sf, m, w.N, w.K, err};
+    if (ksplit < 1 || ksplit > w.K / BK || (ksplit > 1 && resid)) { set_error("tcgen05 gemm: bad K split"); return FORGE_ERR_INVALID_ARG; }
+    Tc5Params p{out, resid, w.qs, w.d, w.sf, m, w.N, w.K, err, ksplit, part_stride};
     const bool split = Alo != nullptr;
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
@@ -405,11 +420,10 @@ int32_t gemm_tc5(float* out, const __half* A, const __half* Alo, const QWeight& 
     // in whole rounds over the SMs.  Pick the cheapest.
     const long nt = (w.N + 127) / 128;
     int best = 128;
-    const bool narrow = m <= 32;   // a batched decode step: the tensor-core time shrinks with the tile, the weight panel is streamed once
     double best_cost = 1e30;
     for (int cand : {128, 192, 256}) {
         if (cand > 128 && m <= cand - 64) continue;
-        const long ctas = nt * ((m + cand - 1) / cand);
+        const long ctas = nt * ((m + cand - 1) / cand) * ksplit;
         const double cost = double((ctas + sms - 1) / sms) * (0.55 + 0.45 * cand / 256.0);
         if (cost < best_cost - 1e-9) { best_cost = cost; best = cand; }
     }
@@ -417,10 +431,6 @@ int32_t gemm_tc5(float* out, const __half* A, const __half* Alo, const QWeight& 
     if (force_nt == 128 || force_nt == 192 || force_nt == 256) best = force_nt;
 #define FORGE_TS(Q)                                                                  \
     do {                                                                             \
-        if (narrow) {                                                                \
-            if (split) return launch_ts<Q, 32, true>(A, Alo, p, st);                 \
-            return launch_ts<Q, 32, false>(A, Alo, p, st);                           \
-        }                                                                            \
         if (split) {                                                                 \
             if (best == 256) return launch_ts<Q, 256, true>(A, Alo, p, st);          \
             if (best == 192) return launch_ts<Q, 192, true>(A, Alo, p, st);          \

@@ -60,6 +60,8 @@ struct ForgeModel {
     QTiled lm_head_t;
     int* d_err = nullptr;  // set by a kernel whose bounded wait gave up
     GemvSplit split;       // split-K scratch shared by the decode GEMVs (one launch at a time on the stream)
+    GemvSplit bsplit;      // the same for the batched decode products
+    uint2* d_bact = nullptr;  // packed activations of one batched product (sixteen rows)
     float* rope = nullptr;  // [max_seq][hd/2]{cos,sin}
     int max_seq = 0;
     std::vector<void*> allocs;
@@ -68,6 +70,8 @@ struct ForgeModel {
     float* p_hidden = nullptr; __half* p_normed = nullptr; float* p_qkv = nullptr; __half* p_q16 = nullptr; __half* p_q16_lo = nullptr;
     __half* p_attn16 = nullptr; float* p_gu = nullptr; __half* p_act16 = nullptr; uint32_t* p_tokens = nullptr;
     __half* p_normed_lo = nullptr; __half* p_attn16_lo = nullptr; __half* p_act16_lo = nullptr;
+    float* p_parts = nullptr;   // [4][rows][h] partial products of the K-sliced o / down projections
+    float* p_qkv_parts = nullptr;   // [4][rows][qk + 2 kv] the same for the QKV projection
     int gemm_passes = 3;  // 3: split-precision prefill GEMMs (default); 1: single fp16 pass
     std::vector<struct ForgeKV*> caches;   // live caches of this model (released with it if the caller did not)
     int pq[8] = {0, 0, 0, 0, 0, 0, 0, 0};  // storage format of q, k, v, o, gate, up, down, lm_head (cfg.proj_quant or cfg.quant)
@@ -164,6 +168,8 @@ int32_t check_cfg(const ForgeModelConfig* c) {
     return FORGE_OK;
 }
 
+int32_t ensure_batch_buffers(ForgeModel* m);
+
 int32_t ensure_prefill_scratch(ForgeModel* m, int rows) {
     if (rows <= m->scratch_rows) return FORGE_OK;
     // scratch is only ever grown between calls; old buffers stay alive until model destroy
@@ -181,6 +187,10 @@ int32_t ensure_prefill_scratch(ForgeModel* m, int rows) {
     FORGE_TRY(dev_alloc(m, &m->p_attn16_lo, r * m->qk));
     FORGE_TRY(dev_alloc(m, &m->p_act16_lo, r * m->ff));
     if (m->cfg.tp_world > 1) FORGE_TRY(dev_alloc(m, &m->p_part, r * m->h));
+    else if (m->h % 4 == 0 && m->h <= 8192) {   // K-slice partials of o / down and of q/k/v
+        FORGE_TRY(dev_alloc(m, &m->p_parts, 4 * r * m->h));
+        FORGE_TRY(dev_alloc(m, &m->p_qkv_parts, 4 * r * (m->qk + 2 * m->kv)));
+    }
     m->scratch_rows = rows;
     ++m->scratch_gen;   // a captured batched decode step holds these addresses
     return FORGE_OK;
@@ -202,7 +212,10 @@ int32_t ensure_decode_scratch(ForgeModel* m, int batch) {
     FORGE_CUDA(cudaMemsetAsync(m->d_amax_ticket, 0, sizeof(int) * b, m->stream));
     if (!m->d_step) { FORGE_TRY(dev_alloc(m, &m->d_step, 1)); }
     if (m->cfg.tp_world > 1) FORGE_TRY(dev_alloc(m, &m->d_part, b * m->h));
-    if (batch >= FORGE_PREFILL_BATCH_THRESHOLD) FORGE_TRY(ensure_prefill_scratch(m, batch));   // batched steps run on the prompt scratch
+    if (batch >= 2) {   // batched steps keep their q/k/v and gate/up rows in the prompt scratch; their buffers must exist before a capture
+        FORGE_TRY(ensure_prefill_scratch(m, batch));
+        FORGE_TRY(ensure_batch_buffers(m));
+    }
     m->dec_batch = batch;
     ++m->scratch_gen;
     return FORGE_OK;
@@ -268,6 +281,21 @@ int32_t row_sliced_gemm(ForgeModel* m, const QWeight& w, const __half* a, const 
     FORGE_TRY(tp_allreduce_sum(m->tp, m->p_part, size_t(n) * m->h, st));
     return residual_add_f32(m->p_hidden, m->p_part, size_t(n) * m->h, st);
 }
+// hidden += W x, then (next_norm given) normed = RMSNorm(hidden) * next_norm as the fp16 hi/lo input of the next
+// product.  On one GPU a long-K product runs as K slices whose partial products are added by the normalisation pass
+// itself (residual add + RMSNorm fused, emit.rs:455-459 and :327-334): shorter accumulation chains in tensor memory
+// and more CTAs for these few-row-tile matrices.
+int32_t row_sliced_gemm_norm(ForgeModel* m, const QWeight& w, const __half* a, const __half* alo, int n, const float* next_norm, __half* nlo, cudaStream_t st) {
+    const int ks = gemm_tc5_ksplit(w);
+    if (m->cfg.tp_world == 1 && ks > 1 && gemm_tc5_supported(w) && m->p_parts) {
+        const size_t stride = size_t(n) * m->h;
+        FORGE_TRY(gemm_tc5(m->p_parts, a, alo, w, n, nullptr, m->d_err, st, ks, stride));
+        return add_parts_rms_norm_f16(m->p_hidden, m->p_parts, ks, stride, m->p_normed, nlo, next_norm, n, m->h, m->cfg.rms_norm_eps, st);
+    }
+    FORGE_TRY(row_sliced_gemm(m, w, a, alo, n, st));
+    if (next_norm) FORGE_TRY(rms_norm_f16(m->p_normed, nlo, m->p_hidden, next_norm, n, m->h, m->cfg.rms_norm_eps, st));
+    return FORGE_OK;
+}
 int32_t row_sliced_gemv(ForgeModel* m, const QTiled& w, GemvArgs a, int batch, cudaStream_t st) {
     if (m->cfg.tp_world == 1) return gemv_tc(w, EPI_RESID, a, m->split, m->d_err, st);
     a.out = m->d_part; a.resid = nullptr;
@@ -297,27 +325,37 @@ int32_t prefill_seq(ForgeModel* m, ForgeKV* kv, int seq, const uint32_t* tokens_
     __half* nlo = split ? m->p_normed_lo : nullptr;
     __half* alo = split ? m->p_attn16_lo : nullptr;
     __half* flo = split ? m->p_act16_lo : nullptr;
+    FORGE_TRY(rms_norm_f16(m->p_normed, nlo, m->p_hidden, m->layers[0].attn_norm, n, m->h, c.rms_norm_eps, st));
     for (int l = 0; l < c.num_layers; ++l) {
         ForgeLayer& L = m->layers[l];
         __half* kp = kv->k_pool + size_t(l) * kv->layer_stride;
         __half* vp = kv->v_pool + size_t(l) * kv->layer_stride;
-        FORGE_TRY(rms_norm_f16(m->p_normed, nlo, m->p_hidden, L.attn_norm, n, m->h, c.rms_norm_eps, st));
+        // (normed = RMSNorm(hidden) * attn_norm was formed together with the residual add in front of it)
         if (L.qkv.quant == FORGE_KQ_SOA) FORGE_TRY(q8_round_f16(m->p_normed, nlo, size_t(n) * m->h, st));
-        FORGE_TRY(gemm_f16a(m->p_qkv, m->p_normed, nlo, L.qkv, n, nullptr, m->d_err, st));
-        // K-quant models round the attention output to 8 bits in front of o_proj: the attention runs in its precise form
-        const bool precise = m->any_kquant;
-        FORGE_TRY(qkv_post(m->p_qkv, n, base, L.qkv_bias, m->rope, m->p_q16, precise ? m->p_q16_lo : nullptr, kp, vp, page_row, m->qk, m->kv, m->hd, st));
+        // K and V are rounded to fp16 on their way into the cache, which turns a difference of e before the rounding into
+        // ~sqrt(e * 2^-11) after it: the QKV product therefore runs as K slices (shorter accumulation chains in tensor
+        // memory, see gemm_tc5_ksplit) whose partials the epilogue kernel adds
+        const int qks = (m->cfg.tp_world == 1 && gemm_tc5_supported(L.qkv) && m->p_qkv_parts) ? std::max(1, std::min(4, L.qkv.K / 1024)) : 1;
+        const size_t qstride = size_t(n) * (m->qk + 2 * m->kv);
+        if (qks > 1) FORGE_TRY(gemm_tc5(m->p_qkv_parts, m->p_normed, nlo, L.qkv, n, nullptr, m->d_err, st, qks, qstride));
+        else FORGE_TRY(gemm_f16a(m->p_qkv, m->p_normed, nlo, L.qkv, n, nullptr, m->d_err, st));
+        const float* qkv_src = qks > 1 ? m->p_qkv_parts : m->p_qkv;
+        // The attention runs in its precise form (queries and probabilities as fp16 hi + lo pairs, output to ~1e-6) whenever
+        // the products are split-precision too: with fp16 queries and probabilities alone the layer error is ~3e-4, which
+        // compounds past the 1e-3 per-layer gate on 32-layer models.  K-quant models need it in any case (their attention
+        // output is rounded to 8 bits in front of o_proj).
+        const bool precise = m->any_kquant || m->gemm_passes == 3;
+        FORGE_TRY(qkv_post(qkv_src, n, base, L.qkv_bias, m->rope, m->p_q16, precise ? m->p_q16_lo : nullptr, kp, vp, page_row, m->qk, m->kv, m->hd, st, qks, qstride));
         AttnPrefillArgs pa{m->p_attn16, alo, nullptr, m->p_q16, kp, vp, page_row, n, base, m->nq, m->nkv, m->hd, c.sliding_window};
         if (precise) { pa.q16_lo = m->p_q16_lo; pa.precise = 1; }
         FORGE_TRY(attn_prefill(pa, st));
         if (L.o.quant == FORGE_KQ_SOA) FORGE_TRY(q8_round_f16(m->p_attn16, alo, size_t(n) * m->qk, st));
-        FORGE_TRY(row_sliced_gemm(m, L.o, m->p_attn16, alo, n, st));
-        FORGE_TRY(rms_norm_f16(m->p_normed, nlo, m->p_hidden, L.ffn_norm, n, m->h, c.rms_norm_eps, st));
+        FORGE_TRY(row_sliced_gemm_norm(m, L.o, m->p_attn16, alo, n, L.ffn_norm, nlo, st));
         if (L.gateup.quant == FORGE_KQ_SOA) FORGE_TRY(q8_round_f16(m->p_normed, nlo, size_t(n) * m->h, st));
         FORGE_TRY(gemm_f16a(m->p_gu, m->p_normed, nlo, L.gateup, n, nullptr, m->d_err, st));
         FORGE_TRY(silu_mul_f16(m->p_act16, flo, m->p_gu, n, m->ff, st));
         if (L.down.quant == FORGE_KQ_SOA) FORGE_TRY(q8_round_f16(m->p_act16, flo, size_t(n) * m->ff, st));
-        FORGE_TRY(row_sliced_gemm(m, L.down, m->p_act16, flo, n, st));
+        FORGE_TRY(row_sliced_gemm_norm(m, L.down, m->p_act16, flo, n, l + 1 < c.num_layers ? m->layers[l + 1].attn_norm : nullptr, nlo, st));
         if (m->trace_on)
             FORGE_CUDA(cudaMemcpyAsync(m->trace + size_t(l) * n * m->h, m->p_hidden, sizeof(float) * n * m->h, cudaMemcpyDeviceToDevice, st));
     }
@@ -339,11 +377,79 @@ inline size_t tpx_bytes(const ForgeModel* m) { return sizeof(uint2) * 2 * size_t
 // pt->head, and leaves the step counter of the generation history alone.
 struct PrefillToken { int seq; const uint32_t* tok; bool head; float* trace_dst; size_t trace_stride; };
 
-// A decode step of `batch` >= 8 sequences: every projection is ONE tensor-core product over the batch rows (the rule the
-// generated module applies to prompts, PREFILL_BATCH_THRESHOLD, emit.rs:203-206 and :4576-4587), so the weights are
-// streamed once per step instead of once per sequence.  The launch sequence is forward()'s operator order
-// (emit.rs:4029-4500) with the batched products of forward_prefill_batched (emit.rs:5118-5486); attention is the
-// single-query kernel over each sequence's own pages.  The rows live in the prompt scratch (fp16 hi/lo operands).
+// A decode step of several sequences: every projection streams its weights ONCE for up to sixteen sequences (the
+// generated module has no batched decode: a batch there is B calls of forward(), emit.rs:4029-4500, whose operator
+// order this follows).  Activations are packed as fp16 hi/lo fragments in front of each product (with the RMSNorm or
+// SiLU*up that feeds it), bias + RoPE + cache append and the single-query attention run per sequence.
+constexpr int kBatchGroup = 16;
+int32_t ensure_batch_buffers(ForgeModel* m) {
+    if (m->d_bact) return FORGE_OK;
+    const int maxK = std::max({m->h, m->qk, m->ff});
+    FORGE_TRY(dev_alloc(m, &m->d_bact, gemv_batch_act_words(maxK, kBatchGroup)));
+    int sms = 148;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, m->device);
+    size_t fl = 1, tk = 1;   // the largest need over the model's matrices (one product at a time on the stream)
+    auto need = [&](const QTiled& w) {
+        fl = std::max(fl, gemv_batch_scratch_floats(w.N, w.K, w.quant, sms));
+        tk = std::max(tk, gemv_batch_tickets(w.N));
+    };
+    for (const ForgeLayer& L : m->layers) { need(L.qkv_t); need(L.o_t); need(L.gateup_t); need(L.down_t); }
+    need(m->lm_head_t);
+    FORGE_TRY(dev_alloc(m, &m->bsplit.scratch, fl));
+    FORGE_TRY(dev_alloc(m, &m->bsplit.tickets, tk));
+    FORGE_CUDA(cudaMemsetAsync(m->bsplit.tickets, 0, sizeof(int) * tk, m->stream));
+    m->bsplit.max_slices = kGemvMaxSlices;
+    return FORGE_OK;
+}
+
+// out[n][N] (+ resid) = f(x)[n][K] . W^T in groups of sixteen rows
+int32_t batched_product(ForgeModel* m, const QTiled& w, const float* x, size_t x_stride, int mode, const float* norm_w, int n,
+                        float* out, const float* resid, cudaStream_t st) {
+    for (int g0 = 0; g0 < n; g0 += kBatchGroup) {
+        const int nb = std::min(kBatchGroup, n - g0);
+        FORGE_TRY(gemv_batch_pack(m->d_bact, x + size_t(g0) * x_stride, x_stride, nb, w.K, w.quant, mode, norm_w, m->cfg.rms_norm_eps, st));
+        FORGE_TRY(gemv_batch(w, m->d_bact, nb, out + size_t(g0) * w.N, resid ? resid + size_t(g0) * w.N : nullptr, m->bsplit, m->d_err, st));
+    }
+    return FORGE_OK;
+}
+
+// hidden += W f(x) for a projection whose K dimension is sliced over the tensor-parallel ranks
+int32_t batched_row_sliced(ForgeModel* m, const QTiled& w, const float* x, size_t x_stride, int mode, int n, cudaStream_t st) {
+    if (m->cfg.tp_world == 1) return batched_product(m, w, x, x_stride, mode, nullptr, n, m->d_hidden, m->d_hidden, st);
+    FORGE_TRY(batched_product(m, w, x, x_stride, mode, nullptr, n, m->d_part, nullptr, st));
+    FORGE_TRY(tp_allreduce_sum(m->tp, m->d_part, size_t(n) * m->h, st));
+    return residual_add_f32(m->d_hidden, m->d_part, size_t(n) * m->h, st);
+}
+
+int32_t decode_launches_batched(ForgeModel* m, ForgeKV* kv, int batch, bool greedy, bool record) {
+    const ForgeModelConfig& c = m->cfg;
+    cudaStream_t st = m->stream;
+    const int n = batch;
+    enum { PLAIN = 0, NORM = 1, SILU = 2 };
+    FORGE_TRY(embedding_rows(m->d_hidden, m->embed, m->d_tok, n, m->h, record ? m->d_hist : nullptr, m->d_step, st));
+    for (int l = 0; l < c.num_layers; ++l) {
+        ForgeLayer& L = m->layers[l];
+        __half* kp = kv->k_pool + size_t(l) * kv->layer_stride;
+        __half* vp = kv->v_pool + size_t(l) * kv->layer_stride;
+        FORGE_TRY(batched_product(m, L.qkv_t, m->d_hidden, m->h, NORM, L.attn_norm, n, m->p_qkv, nullptr, st));
+        FORGE_TRY(qkv_post_rows(m->p_qkv, n, L.qkv_bias, m->rope, m->d_q, kp, vp, kv->d_page_table, kv->d_seq_len, kv->pages_per_seq,
+                                m->qk, m->kv, m->hd, st));
+        AttnDecodeArgs da{m->d_attn, m->d_q, kp, vp, kv->d_page_table, kv->pages_per_seq, kv->d_seq_len, 0,
+                          n, m->nq, m->nkv, m->hd, kv->max_seq, kv->attn_ws, kv->attn_counters, kv->splits, c.sliding_window};
+        FORGE_TRY(attn_decode(da, st));
+        FORGE_TRY(batched_row_sliced(m, L.o_t, m->d_attn, m->qk, PLAIN, n, st));
+        FORGE_TRY(batched_product(m, L.gateup_t, m->d_hidden, m->h, NORM, L.ffn_norm, n, m->p_gu, nullptr, st));
+        FORGE_TRY(batched_row_sliced(m, L.down_t, m->p_gu, size_t(2) * m->ff, SILU, n, st));
+    }
+    FORGE_TRY(batched_product(m, m->lm_head_t, m->d_hidden, m->h, NORM, m->final_norm, n, m->d_logits, nullptr, st));
+    if (greedy) FORGE_TRY(argmax_slices(m->d_tok, m->d_logits, m->V, n, m->d_amax_val, m->d_amax_idx, m->d_amax_ticket, st));
+    return step_advance(kv->d_seq_len, n, m->d_step, st, nullptr);
+}
+
+// A decode step of more than 32 sequences: every projection is one tensor-core product over the batch rows (the rule
+// the generated module applies to prompts, PREFILL_BATCH_THRESHOLD, emit.rs:203-206 and :4576-4587), the weights
+// dequantised once per step.  Operator order of forward() (emit.rs:4029-4500) with the batched products of
+// forward_prefill_batched (emit.rs:5118-5486); the rows live in the prompt scratch (fp16 hi/lo operands).
 int32_t decode_launches_gemm(ForgeModel* m, ForgeKV* kv, int batch, bool greedy, bool record) {
     const ForgeModelConfig& c = m->cfg;
     cudaStream_t st = m->stream;
@@ -353,11 +459,11 @@ int32_t decode_launches_gemm(ForgeModel* m, ForgeKV* kv, int batch, bool greedy,
     __half* alo = split ? m->p_attn16_lo : nullptr;
     __half* flo = split ? m->p_act16_lo : nullptr;
     FORGE_TRY(embedding_rows(m->p_hidden, m->embed, m->d_tok, n, m->h, record ? m->d_hist : nullptr, m->d_step, st));
+    FORGE_TRY(rms_norm_f16(m->p_normed, nlo, m->p_hidden, m->layers[0].attn_norm, n, m->h, c.rms_norm_eps, st));
     for (int l = 0; l < c.num_layers; ++l) {
         ForgeLayer& L = m->layers[l];
         __half* kp = kv->k_pool + size_t(l) * kv->layer_stride;
         __half* vp = kv->v_pool + size_t(l) * kv->layer_stride;
-        FORGE_TRY(rms_norm_f16(m->p_normed, nlo, m->p_hidden, L.attn_norm, n, m->h, c.rms_norm_eps, st));
         FORGE_TRY(gemm_f16a(m->p_qkv, m->p_normed, nlo, L.qkv, n, nullptr, m->d_err, st));
         FORGE_TRY(qkv_post_rows(m->p_qkv, n, L.qkv_bias, m->rope, m->d_q, kp, vp, kv->d_page_table, kv->d_seq_len, kv->pages_per_seq,
                                 m->qk, m->kv, m->hd, st));
@@ -365,17 +471,16 @@ int32_t decode_launches_gemm(ForgeModel* m, ForgeKV* kv, int batch, bool greedy,
                           n, m->nq, m->nkv, m->hd, kv->max_seq, kv->attn_ws, kv->attn_counters, kv->splits, c.sliding_window};
         FORGE_TRY(attn_decode(da, st));
         FORGE_TRY(f32_to_f16(m->p_attn16, alo, m->d_attn, size_t(n) * m->qk, st));
-        FORGE_TRY(row_sliced_gemm(m, L.o, m->p_attn16, alo, n, st));
-        FORGE_TRY(rms_norm_f16(m->p_normed, nlo, m->p_hidden, L.ffn_norm, n, m->h, c.rms_norm_eps, st));
+        FORGE_TRY(row_sliced_gemm_norm(m, L.o, m->p_attn16, alo, n, L.ffn_norm, nlo, st));
         FORGE_TRY(gemm_f16a(m->p_gu, m->p_normed, nlo, L.gateup, n, nullptr, m->d_err, st));
         FORGE_TRY(silu_mul_f16(m->p_act16, flo, m->p_gu, n, m->ff, st));
-        FORGE_TRY(row_sliced_gemm(m, L.down, m->p_act16, flo, n, st));
+        FORGE_TRY(row_sliced_gemm_norm(m, L.down, m->p_act16, flo, n, l + 1 < c.num_layers ? m->layers[l + 1].attn_norm : m->final_norm, nlo, st));
     }
-    FORGE_TRY(rms_norm_f16(m->p_normed, nlo, m->p_hidden, m->final_norm, n, m->h, c.rms_norm_eps, st));
     FORGE_TRY(gemm_f16a(m->d_logits, m->p_normed, nlo, m->lm_head, n, nullptr, m->d_err, st));
     if (greedy) FORGE_TRY(argmax_slices(m->d_tok, m->d_logits, m->V, n, m->d_amax_val, m->d_amax_idx, m->d_amax_ticket, st));
     return step_advance(kv->d_seq_len, n, m->d_step, st, nullptr);
 }
+
 int32_t decode_launches(ForgeModel* m, ForgeKV* kv, int batch, bool greedy, bool record, const PrefillToken* pt = nullptr) {
     const ForgeModelConfig& c = m->cfg;
     cudaStream_t st = m->stream;
@@ -408,8 +513,11 @@ int32_t decode_launches(ForgeModel* m, ForgeKV* kv, int batch, bool greedy, bool
         pending = true;
         return gemv_tc(w, EPI_TP_PUSH, a, m->split, m->d_err, st);
     };
-    if (batch >= FORGE_PREFILL_BATCH_THRESHOLD && !pt && !m->any_kquant && !m->per_token_prefill && !m->trace_on && m->lm_head.qs)
-        return decode_launches_gemm(m, kv, batch, greedy, record);
+    if (batch >= 2 && !pt && m->uniform_basic && !m->trace_on) {
+        // up to 32 sequences: the streaming product, sixteen rows per pass over the weights; beyond: the tensor-core GEMM
+        if (batch > 2 * kBatchGroup && m->lm_head.qs) return decode_launches_gemm(m, kv, batch, greedy, record);
+        return decode_launches_batched(m, kv, batch, greedy, record);
+    }
     FORGE_TRY(embedding_rows(m->d_hidden, m->embed, pt ? pt->tok : m->d_tok, batch, m->h, record ? m->d_hist : nullptr, m->d_step, st));
     for (int l = 0; l < c.num_layers; ++l) {
         ForgeLayer& L = m->layers[l];

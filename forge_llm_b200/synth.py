@@ -114,9 +114,16 @@ def weights_bin_size(c: dict) -> int:
     return V * h * 4 + per * c["num_layers"] + h * 4 + mb(7, V, h)
 
 
-def make_weights_bin(c: dict, seed: int = 0, std: float = 0.02, chunk_rows: int = 8192) -> np.ndarray:
-    """Return the whole ``weights.bin`` image as a uint8 array."""
+def make_weights_bin(c: dict, seed: int = 0, std: float = 0.02, chunk_rows: int = 8192, quantize_fn=None,
+                     repeat_layers: bool = False) -> np.ndarray:
+    """Return the whole ``weights.bin`` image as a uint8 array.
+
+    ``quantize_fn(quant, f32 array) -> uint8 array`` replaces the default quantiser (callers that must not load the
+    CUDA library pass their own).  ``repeat_layers``: layer 0 is drawn from the generator and its bytes are repeated
+    for the other layers - same shapes, sizes and value distribution at a fraction of the host time (timing runs of
+    the multi-billion-parameter shapes, and the full-depth parity runs of those two shapes; every other test draws every layer)."""
     rng = np.random.default_rng(seed)
+    qfn = quantize_fn or quantize
     h, qk, kv = c["hidden_size"], c["num_heads"] * c["head_dim"], c["num_kv_heads"] * c["head_dim"]
     from .configs import proj_quants
     ff, V = c["intermediate_size"], c["vocab_size"]
@@ -138,7 +145,7 @@ def make_weights_bin(c: dict, seed: int = 0, std: float = 0.02, chunk_rows: int 
         for r0 in range(0, n, chunk_rows):
             r = min(chunk_rows, n - r0)
             w = rng.standard_normal((r, k), dtype=np.float32) * np.float32(std)
-            parts.append(quantize(quant, w))
+            parts.append(qfn(quant, w))
         return np.concatenate(parts) if len(parts) > 1 else parts[0]
 
     embed_off = off
@@ -151,7 +158,15 @@ def make_weights_bin(c: dict, seed: int = 0, std: float = 0.02, chunk_rows: int 
             put(rng.standard_normal((r, h), dtype=np.float32) * np.float32(std))
         off = save
     ones = np.ones(h, np.float32)
-    for _ in range(c["num_layers"]):
+    layer0 = off
+    for li in range(c["num_layers"]):
+        if repeat_layers and li > 0:
+            n = off - layer0 if li == 1 else layer_bytes
+            if li == 1:
+                layer_bytes = n
+            out[off:off + layer_bytes] = out[layer0:layer0 + layer_bytes]
+            off += layer_bytes
+            continue
         put(ones)
         put(draw_quant(qk, h, 0))
         put(draw_quant(kv, h, 1))

@@ -119,6 +119,11 @@ typedef struct ForgePacked ForgePacked;
 int32_t forge_packed_create(int32_t quant, const uint8_t* w, int32_t K, int32_t N, void* stream, ForgePacked** out);
 void forge_packed_destroy(ForgePacked* w);
 int32_t forge_matmul_mat_packed(float* out, int32_t m, const float* in, const ForgePacked* w, void* stream);
+/* The product of a decode step for nb <= 16 sequences at once (the reference has no batched decode: it calls
+ * matmul_vec_* once per sequence, E:2047-2087 / E:2910-2953, and this returns those calls' values): out f32 [nb][N],
+ * in f32 [nb][K], the weights streamed once for all rows.  Q8_0 / Q4_0.  The first call on a packed matrix allocates
+ * the product's buffers; it only enqueues work (see forge_packed_check). */
+int32_t forge_matmul_decode_batch(float* out, int32_t nb, const float* in, ForgePacked* w, void* stream);
 /* forge_matmul_mat_packed only enqueues work.  This call synchronises `stream` and reports whether a bounded
  * device-side wait of any product on `w` since the last check gave up (FORGE_ERR_TIMEOUT; the word is cleared). */
 int32_t forge_packed_check(const ForgePacked* w, void* stream);

@@ -1244,4 +1244,14 @@ int fo_num_threads() {
 #endif
 }
 
+// Host threads the row / head loops may use (rayon's pool size in the reference).  Launchers that pin
+// OMP_NUM_THREADS=1 for their workers (torchrun) would otherwise leave the CPU baseline on one core.
+void fo_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 }  // extern "C"

@@ -94,6 +94,7 @@ def lib():
         "fo_forward": (i, [vp, vp, C.c_uint32, _f32p, vp]),
         "fo_forward_prefill": (i, [vp, vp, _u32p, i, _f32p, vp, i]),
         "fo_num_threads": (i, []),
+        "fo_set_num_threads": (None, [i]),
     }
     for name, (res, args) in sigs.items():
         fn = getattr(L, name)

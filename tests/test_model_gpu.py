@@ -17,9 +17,10 @@ HIDDEN_TOL = 1e-3
 LOGIT_TOL = 2e-2
 
 
-def _run_case(oracle, c, n_prompt, n_decode, n_greedy=32, kv_cap=None, int8_report=True, row_tol=2 * HIDDEN_TOL, step_tol=HIDDEN_TOL, logit_tol=LOGIT_TOL, layer_tol=HIDDEN_TOL):
+def _run_case(oracle, c, n_prompt, n_decode, n_greedy=32, kv_cap=None, int8_report=True, row_tol=2 * HIDDEN_TOL, step_tol=HIDDEN_TOL, logit_tol=LOGIT_TOL, layer_tol=HIDDEN_TOL,
+              repeat_layers=False, int8_bound=5e-2):
     from forge_llm_b200 import runtime, synth
-    blob = synth.make_weights_bin(c)
+    blob = synth.make_weights_bin(c, repeat_layers=repeat_layers)
     toks = synth.prompt_tokens(c, n_prompt)
     gm = runtime.Model(c, blob)
     kv = gm.new_cache(max_seq=kv_cap or (n_prompt + max(n_decode, n_greedy) + 8))
@@ -36,10 +37,11 @@ def _run_case(oracle, c, n_prompt, n_decode, n_greedy=32, kv_cap=None, int8_repo
     assert worst_row < row_tol
     assert np.abs(lg - lo).max() < logit_tol
     assert kv.len() == om.len == n_prompt
-    # the cache itself: fp16 K/V rows of the first and last layer
+    # the cache itself: fp16 K/V rows of the first and last layer.  Both sides round to fp16, and a hidden-state difference
+    # inside the gate flips roundings of one fp16 ulp (2^-11 relative), so the bound is the gate plus half an ulp
     for layer in (0, L - 1):
         for which in (0, 1):
-            assert rel_l2(kv.read(layer, which), om.kv_read(layer, which)) < max(HIDDEN_TOL, row_tol / 3)
+            assert rel_l2(kv.read(layer, which), om.kv_read(layer, which)) < max(HIDDEN_TOL, row_tol / 3) + 2.0 ** -12
 
     # teacher-forced decode: both sides are fed the oracle's greedy token
     for _ in range(n_decode):
@@ -70,7 +72,7 @@ def _run_case(oracle, c, n_prompt, n_decode, n_greedy=32, kv_cap=None, int8_repo
         gm.trace(False)
         d8 = max(rel_l2(trg[l], tr8[l]) for l in range(L))
         print(f"[{c['name']}] vs int8-KV oracle: hidden rel L2 max {d8:.2e}, logit max-abs {np.abs(lg - l8).max():.2e}")
-        assert d8 < 5e-2
+        assert d8 < int8_bound
     kv.close()
     gm.close()
     return per_layer
@@ -256,16 +258,16 @@ def test_kv_overflow_is_an_error_status(oracle):
     gm.close()
 
 
-@pytest.mark.parametrize("quant,hd,nq,nkv,bias,B", [(8, 64, 4, 2, 0, 5), (8, 64, 4, 2, 1, 8), (4, 96, 2, 2, 0, 16), (8, 128, 2, 1, 1, 16)])
+@pytest.mark.parametrize("quant,hd,nq,nkv,bias,B", [(8, 64, 4, 2, 0, 5), (8, 64, 4, 2, 1, 8), (4, 96, 2, 2, 0, 16), (8, 128, 2, 1, 1, 16), (4, 64, 4, 2, 1, 21), (8, 64, 4, 2, 0, 40)])
 def test_batched_decode_equals_independent_sequences(oracle, quant, hd, nq, nkv, bias, B):
-    # the reference has no batched decode: a batch is B independent forward() calls.  Fewer than 8 sequences run through
-    # the per-token products; 8 and more through one tensor-core product per projection (the weights are read once)
+    # the reference has no batched decode: a batch is B independent forward() calls.  Up to 32 sequences run through the
+    # streaming product that reads the weights once per sixteen rows; more through one tensor-core GEMM per projection
     from forge_llm_b200 import configs, runtime, synth
     c = configs.tiny(quant, hd=hd, nq=nq, nkv=nkv, bias=bias)
     blob = synth.make_weights_bin(c)
     gm = runtime.Model(c, blob)
     kv = gm.new_cache(max_seq=256, batch=B)
-    lens = [9, 64, 100, 17, 130, 63, 65, 1, 128, 33, 77, 12, 150, 2, 90, 129][:B]
+    lens = ([9, 64, 100, 17, 130, 63, 65, 1, 128, 33, 77, 12, 150, 2, 90, 129] + [(37 * i) % 140 + 3 for i in range(B)])[:B]
     oms, last = [], []
     for b in range(B):
         toks = synth.prompt_tokens(c, lens[b], seed=10 + b)
@@ -283,14 +285,20 @@ def test_batched_decode_equals_independent_sequences(oracle, quant, hd, nq, nkv,
         assert np.abs(lg[b] - last[b]).max() < LOGIT_TOL
     first = np.array([oracle.argmax(l) for l in last], np.uint32)
     ref = np.zeros((12, B), np.uint32)
+    sure = np.full(B, 12)   # steps of sequence b before the CPU path's own top-2 gap falls below 1e-4 (a coin flip from there on)
     for b in range(B):
         lo = last[b]
         for i in range(12):
             t = oracle.argmax(lo)
             ref[i, b] = t
+            top2 = np.partition(lo, -2)[-2:]
+            if top2[1] - top2[0] < 1e-4:
+                sure[b] = min(sure[b], i)
             lo = oms[b].forward(t)
     got = gm.decode_greedy_batch(first, 12, kv)
-    assert np.array_equal(got, ref)
+    assert sure.sum() >= 11 * B   # the rule must not hollow the test out
+    for b in range(B):
+        assert np.array_equal(got[:sure[b], b], ref[:sure[b], b]), (b, got[:, b], ref[:, b])
     assert [kv.len(b) for b in range(B)] == [l + 13 for l in lens]
     kv.close()
     gm.close()
@@ -301,6 +309,17 @@ def test_c1_smollm2_full_size(oracle):
     from forge_llm_b200 import configs
     per_layer = _run_case(oracle, configs.CONFIGS["c1"], n_prompt=100, n_decode=3, n_greedy=64)
     print("c1 per-layer hidden rel L2:", " ".join(f"{e:.1e}" for e in per_layer))
+
+
+@pytest.mark.parametrize("key,n_prompt,n_greedy,repeat", [("c2", 64, 32, False), ("c3", 80, 32, False), ("c4", 32, 32, True), ("c5", 32, 32, True)])
+def test_full_depth_configs(oracle, key, n_prompt, n_greedy, repeat):
+    """Configurations 2-5 at their full depth and full vocabulary (a short prompt keeps the CPU restatement to a minute):
+    the per-layer gate over ALL layers, the logits, 32 greedy ids, and the distance to the int8-KV arithmetic.  The two
+    largest shapes repeat layer 0's weights in every layer (host time); depth still compounds the error."""
+    from forge_llm_b200 import configs
+    # (the distance to the int8-KV arithmetic grows with depth and width - 6e-2 on the 32-layer 7B shape - and is only reported)
+    per_layer = _run_case(oracle, configs.CONFIGS[key], n_prompt=n_prompt, n_decode=2, n_greedy=n_greedy, repeat_layers=repeat, int8_bound=1e-1)
+    print(f"{key} per-layer hidden rel L2:", " ".join(f"{e:.1e}" for e in per_layer))
 
 
 @pytest.mark.parametrize("key,layers,vocab,n_prompt", [("c2", 4, 8192, 200), ("c3", 3, 4096, 130), ("c4", 2, 4096, 150), ("c5", 2, 4096, 140)])

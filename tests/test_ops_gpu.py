@@ -48,6 +48,34 @@ def test_matmul_mat(L, oracle, quant, m, K, N):
     assert np.abs(got - ref).max() < 50 * tol * np.abs(ref).max()
 
 
+@pytest.mark.parametrize("quant", [8, 4])
+@pytest.mark.parametrize("nb,K,N", [(1, 32, 2), (2, 576, 192), (4, 2048, 512), (5, 896, 130), (8, 8192, 2048), (9, 11008, 4096),
+                                    (16, 2048, 128), (16, 4096, 22016), (13, 3072, 9216), (16, 576, 49152), (7, 8192, 3072)])
+def test_matmul_decode_batch(L, oracle, quant, nb, K, N):
+    """The batched decode product (weights streamed once for up to 16 rows) against the per-row CPU products: the rows
+    enter as fp16 hi + lo pairs (22 bits), the block scales are applied in f32."""
+    import ctypes as C
+    import torch
+    from forge_llm_b200 import synth
+    lib, check = L
+    rng = np.random.default_rng(77 * quant + nb + K + N)
+    w = synth.quantize(quant, rng.standard_normal((N, K), dtype=np.float32) * 0.02)
+    x = rng.standard_normal((nb, K), dtype=np.float32)
+    ref = oracle.matmul_mat(quant, x, w, K, N)
+    dx, dw = dev(x), dev(w)
+    out = torch.empty((nb, N), dtype=torch.float32, device="cuda")
+    pk = C.c_void_p()
+    check(lib.forge_packed_create(quant, dw.data_ptr(), K, N, None, C.byref(pk)))
+    for _ in range(2):   # the second call reuses the buffers (and the self-resetting tickets)
+        out.zero_()
+        check(lib.forge_matmul_decode_batch(out.data_ptr(), nb, dx.data_ptr(), pk, None))
+        check(lib.forge_packed_check(pk, None))
+        got = out.cpu().numpy()
+        assert rel_l2(got, ref) < 2e-6
+        assert np.abs(got - ref).max() < 1e-4 * np.abs(ref).max()
+    lib.forge_packed_destroy(pk)
+
+
 @pytest.mark.parametrize("quant", [12, 14])
 @pytest.mark.parametrize("m,K,N", [(1, 256, 2), (1, 512, 130), (1, 2048, 512), (1, 8192, 2048), (1, 11008 // 256 * 256, 19000),
                                    (3, 768, 130), (7, 1536, 144), (1, 2048, 32000),
