@@ -1,9 +1,14 @@
 // Single-query decode attention over the paged fp16 KV cache (replaces attention_flash,
 // crates/forgellm-codegen-cpu/src/emit.rs:657-715; GQA mapping kv_head = h / (nq/nkv), :660-666).
-// HBM-bound on K/V: the context is split over CTAs (split-KV), every K/V row is read once per
-// KV head with 128-bit loads and shared by the query heads of its group, the online-softmax
-// state (m, l, acc) is f32, exp is expf.  Split partials are merged by the last CTA to finish
-// a KV head (atomic ticket), so no second launch is needed.
+// HBM-bound on K/V: the context is split over CTAs (split-KV); a producer lane pulls the CTA's pages - 64 rows of one
+// KV head, K and V - into a ring of shared-memory stages with 3-D tiled TMA copies (cp.async.bulk.tensor, mbarrier
+// completion; the tensor map spans this GPU's own pool), so the bytes in flight do not depend on registers or on
+// the instruction stream, and it starts before the dependency wait: every cached row but the newest was written by
+// earlier steps.  Four consumer warps read the rows from shared memory with 128-bit loads, every row shared by the
+// query heads of its group; the online-softmax state (m, l, acc) is f32.  Split partials are merged by the last CTA
+// to finish a KV head (atomic ticket), so no second launch is needed.  Every wait is bounded.
+#include <cuda.h>
+
 #include <algorithm>
 #include <mutex>
 
@@ -13,16 +18,20 @@ namespace forge {
 
 namespace {
 
-constexpr int kThreads = 128;
-constexpr int kGC = 4;  // query heads processed per pass over the keys
+constexpr int kThreads = 128;     // consumer threads (four warps); warp 4 is the producer
+constexpr int kBlock = kThreads + 32;
+constexpr int kStages = 4;        // most pages (K and V) in flight per CTA (a CTA with one or two pages takes a ring of two)
+constexpr int kGC = 4;  // most query heads processed per pass over the keys (the kernel is built for 1, 2 and 4)
 constexpr int kMaxGroup = 16;  // query heads per KV head
 constexpr int kMaxSplits = 32;    // context splits per KV head (the merge keeps one partial per split in registers)
+constexpr uint32_t kSpin = 1u << 22;
 
 template <int HD> struct Seg { static constexpr int W = (HD == 64) ? 8 : 16, ACTIVE = HD / 8, RPW = 32 / W; };
 
 struct DecParams {
     AttnDecodeArgs a;
     float scale;
+    int stages;   // ring depth of this launch (<= kStages)
 };
 
 __device__ __forceinline__ void unpack8(const uint4& v, float* f) {
@@ -34,13 +43,46 @@ __device__ __forceinline__ void unpack8(const uint4& v, float* f) {
 // exp(x - m) with exp(-inf) = 0 and no NaN when both are -inf
 __device__ __forceinline__ float exp_rel(float x, float m) { return (x == -INFINITY) ? 0.f : __expf(x - m); }
 
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    const uint32_t addr = smem_u32(bar);
+    for (uint32_t i = 0; i < kSpin; ++i) {
+        uint32_t done;
+        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+                     : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+// one page of one KV head: box {head_dim, 1, 64 rows} at {0, kv head, row}
+__device__ __forceinline__ void tma_page(void* dst, const CUtensorMap* map, int kvh, int row, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+                 ::"r"(smem_u32(dst)), "l"(map), "r"(0), "r"(kvh), "r"(row), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void csync() { asm volatile("bar.sync 1, %0;" ::"n"(kThreads) : "memory"); }
+
 // SW: sliding-window instantiation (the full-attention one carries no window tests)
-template <int HD, bool SW>
-__global__ void __launch_bounds__(kThreads) attn_decode_kernel(DecParams p) {
+// GC: query heads folded per pass over the keys: min(4, query heads per KV head), so that multi-head attention (one
+// query head per KV head) forms one score per key, not four
+template <int HD, bool SW, int GC>
+__global__ void __launch_bounds__(kBlock, (HD == 128 || GC == 4) ? 2 : 3) attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                                                             DecParams p) {
     constexpr int W = Seg<HD>::W, ACTIVE = Seg<HD>::ACTIVE, RPW = Seg<HD>::RPW;
     constexpr int PARTS = (kThreads / 32) * RPW;
-    __shared__ float s_m[PARTS][kGC], s_l[PARTS][kGC], s_w[PARTS][kGC];
-    __shared__ float s_acc[PARTS][kGC][HD];
+    constexpr int PAGE_BYTES = FORGE_KV_PAGE * HD * 2;
+    extern __shared__ __align__(1024) unsigned char ring[];   // [kStages][K page | V page]
+    __shared__ uint64_t full_bar[kStages], empty_bar[kStages];
+    __shared__ float s_m[PARTS][GC], s_l[PARTS][GC], s_w[PARTS][GC];
+    __shared__ float s_acc[PARTS][GC][HD];
     __shared__ float s_fw[kMaxSplits][kMaxGroup];  // final merge: weight of split s for query head g
     __shared__ int s_last;
     const AttnDecodeArgs& a = p.a;
@@ -50,56 +92,51 @@ __global__ void __launch_bounds__(kThreads) attn_decode_kernel(DecParams p) {
     const int seg = lane / W, sl = lane % W;
     const bool act = sl < ACTIVE;
     const int G = a.nq / a.nkv, kvd = a.nkv * HD;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], kThreads / 32); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
     // Split s owns the logical pages s, s + splits, ...: which pages a CTA reads does not depend on the context
     // length.  The length, the page table and every cached row but the newest were written before the kernel in front
-    // of this one started, so they are read BEFORE the dependency wait: the first batch of K/V loads of the CTA is in
-    // flight while that kernel (which produces q and the newest row) is still running.
+    // of this one started, so they are read without waiting for it.
     const int32_t* pt = a.page_table ? a.page_table + size_t(b) * a.pages_per_seq : nullptr;
-    const int page0 = (pt && split < a.pages_per_seq) ? pt[split] : split;
     const int n_ctx = a.seq_len ? a.seq_len[b] + 1 : a.seq_len_host;
     const int n_pages = (n_ctx + FORGE_KV_PAGE - 1) / FORGE_KV_PAGE;
     const int t_first = (SW && n_ctx > a.window) ? n_ctx - a.window : 0;  // sliding window: first position seen
     const size_t seq_base = a.page_table ? 0 : size_t(b) * a.max_ctx;  // contiguous: [batch][max_ctx][kvd]
     const int part = warp * RPW + seg;
-    constexpr int UNR = 4;  // positions per segment whose K/V loads are issued before any use
-    // loads of one batch of positions of logical page lp; `hold` (a position, or -1) is left out
-    auto issue = [&](int lp, int page, int base, uint4 (&kr)[UNR], uint4 (&vr)[UNR], int hold) {
-        const size_t page_row = seq_base + size_t(page) * FORGE_KV_PAGE;
-        const int t_page = lp * FORGE_KV_PAGE;
-#pragma unroll
-        for (int u = 0; u < UNR; ++u) {
-            const int tp = base + u * PARTS + seg;
-            kr[u] = make_uint4(0, 0, 0, 0);
-            vr[u] = make_uint4(0, 0, 0, 0);
-            if (tp < FORGE_KV_PAGE && t_page + tp < n_ctx && t_page + tp != hold && (!SW || t_page + tp >= t_first) && act) {
-                const size_t off = (page_row + tp) * kvd + kvh * HD + sl * 8;
-                kr[u] = __ldg(reinterpret_cast<const uint4*>(a.k_pool + off));
-                vr[u] = __ldg(reinterpret_cast<const uint4*>(a.v_pool + off));
-            }
-        }
-    };
-    uint4 kr0[UNR], vr0[UNR];
-    const bool early = split < n_pages && !(SW && (split + 1) * FORGE_KV_PAGE <= t_first);
-    if (early) issue(split, page0, warp * RPW, kr0, vr0, n_ctx - 1);
-    pdl_wait();  // q and the newest cache row come from the kernel before this one
-    if (early) {   // the newest row, if it is in the first batch
-        const int t_page = split * FORGE_KV_PAGE;
-#pragma unroll
-        for (int u = 0; u < UNR; ++u) {
-            const int tp = warp * RPW + u * PARTS + seg;
-            if (tp < FORGE_KV_PAGE && t_page + tp == n_ctx - 1 && act) {
-                const size_t off = (seq_base + size_t(page0) * FORGE_KV_PAGE + tp) * kvd + kvh * HD + sl * 8;
-                kr0[u] = __ldcg(reinterpret_cast<const uint4*>(a.k_pool + off));
-                vr0[u] = __ldcg(reinterpret_cast<const uint4*>(a.v_pool + off));
-            }
-        }
-    }
+    // positions per segment folded into the running softmax state in one step (a whole page per warp step when one
+    // query head leaves the registers for it)
+    constexpr int UNR = (GC == 1 && W == 16) ? 8 : 4;
 
-    for (int g0 = 0; g0 < G; g0 += kGC) {
-        const int gc = min(kGC, G - g0);
-        float q[kGC][8], acc[kGC][8], mi[kGC], li[kGC];
+    if (warp == kThreads / 32) {
+        // ---- producer: the CTA's pages, once per pass over the query heads, as ring space frees up
+        if (lane == 0) {
+            int i = 0;
+            for (int g0 = 0; g0 < G; g0 += GC)
+                for (int lp = split; lp < n_pages; lp += a.splits) {
+                    if (SW && (lp + 1) * FORGE_KV_PAGE <= t_first) continue;
+                    const int st = i % p.stages, use = i / p.stages;
+                    if (use > 0 && !mbar_wait(&empty_bar[st], (use - 1) & 1)) { if (a.err) atomicExch(a.err, 1); return; }
+                    const int row = a.row_base + int(seq_base) + (pt ? pt[lp] : lp) * FORGE_KV_PAGE;
+                    unsigned char* dst = ring + size_t(st) * 2 * PAGE_BYTES;
+                    mbar_expect_tx(&full_bar[st], 2 * PAGE_BYTES);
+                    tma_page(dst, &map_k, kvh, row, &full_bar[st]);
+                    tma_page(dst + PAGE_BYTES, &map_v, kvh, row, &full_bar[st]);
+                    ++i;
+                }
+        }
+        return;
+    }
+    pdl_wait();  // q and the newest cache row come from the kernel before this one
+    int pi = 0;  // pages consumed so far (ring position)
+
+    for (int g0 = 0; g0 < G; g0 += GC) {
+        const int gc = min(GC, G - g0);
+        float q[GC][8], acc[GC][8], mi[GC], li[GC];
 #pragma unroll
-        for (int g = 0; g < kGC; ++g) {
+        for (int g = 0; g < GC; ++g) {
             mi[g] = -INFINITY; li[g] = 0.f;
 #pragma unroll
             for (int i = 0; i < 8; ++i) { acc[g][i] = 0.f; q[g][i] = 0.f; }
@@ -112,25 +149,40 @@ __global__ void __launch_bounds__(kThreads) attn_decode_kernel(DecParams p) {
         }
         for (int lp = split; lp < n_pages; lp += a.splits) {
             if (SW && (lp + 1) * FORGE_KV_PAGE <= t_first) continue;  // the whole page lies before the window
-            const int page = lp == split ? page0 : (pt ? pt[lp] : lp);
             const int t_page = lp * FORGE_KV_PAGE;
+            const int st = pi % p.stages;
+            if (!mbar_wait(&full_bar[st], (pi / p.stages) & 1) && a.err) atomicExch(a.err, 1);
+            const unsigned char* ks = ring + size_t(st) * 2 * PAGE_BYTES;
+            const unsigned char* vs = ks + PAGE_BYTES;
             for (int base = warp * RPW; base < FORGE_KV_PAGE; base += PARTS * UNR) {
                 uint4 kr[UNR], vr[UNR];
-                if (g0 == 0 && lp == split && base == warp * RPW) {   // the batch that was requested before the wait
 #pragma unroll
-                    for (int u = 0; u < UNR; ++u) { kr[u] = kr0[u]; vr[u] = vr0[u]; }
-                } else {
-                    issue(lp, page, base, kr, vr, -1);
+                for (int u = 0; u < UNR; ++u) {
+                    const int tp = base + u * PARTS + seg;
+                    kr[u] = make_uint4(0, 0, 0, 0);
+                    vr[u] = make_uint4(0, 0, 0, 0);
+                    if (tp < FORGE_KV_PAGE && t_page + tp < n_ctx && (!SW || t_page + tp >= t_first) && act) {
+                        if (t_page + tp == n_ctx - 1) {
+                            // the newest row is being written by the kernel in front while the page is copied: it is
+                            // read from global memory, after the wait
+                            const size_t off = (size_t(seq_base) + size_t(pt ? pt[lp] : lp) * FORGE_KV_PAGE + tp) * kvd + size_t(kvh) * HD + sl * 8;
+                            kr[u] = __ldcg(reinterpret_cast<const uint4*>(a.k_pool + off));
+                            vr[u] = __ldcg(reinterpret_cast<const uint4*>(a.v_pool + off));
+                        } else {
+                            kr[u] = *reinterpret_cast<const uint4*>(ks + size_t(tp) * HD * 2 + sl * 16);
+                            vr[u] = *reinterpret_cast<const uint4*>(vs + size_t(tp) * HD * 2 + sl * 16);
+                        }
+                    }
                 }
                 // the UNR scores of a head are formed independently, then folded into the running state in one
                 // softmax step (one rescale per group instead of one per position)
-                float sc[UNR][kGC];
+                float sc[UNR][GC];
 #pragma unroll
                 for (int u = 0; u < UNR; ++u) {
                     float kf[8];
                     unpack8(kr[u], kf);
 #pragma unroll
-                    for (int g = 0; g < kGC; ++g) {
+                    for (int g = 0; g < GC; ++g) {
                         float d = 0.f;
 #pragma unroll
                         for (int i = 0; i < 8; ++i) d += q[g][i] * kf[i];
@@ -142,20 +194,20 @@ __global__ void __launch_bounds__(kThreads) attn_decode_kernel(DecParams p) {
 #pragma unroll
                     for (int u = 0; u < UNR; ++u)
 #pragma unroll
-                        for (int g = 0; g < kGC; ++g) sc[u][g] += __shfl_xor_sync(0xffffffffu, sc[u][g], o);
+                        for (int g = 0; g < GC; ++g) sc[u][g] += __shfl_xor_sync(0xffffffffu, sc[u][g], o);
 #pragma unroll
                 for (int u = 0; u < UNR; ++u) {
                     const int tp = base + u * PARTS + seg;
                     if (!(tp < FORGE_KV_PAGE && t_page + tp < n_ctx && (!SW || t_page + tp >= t_first))) {
 #pragma unroll
-                        for (int g = 0; g < kGC; ++g) sc[u][g] = -INFINITY;
+                        for (int g = 0; g < GC; ++g) sc[u][g] = -INFINITY;
                     }
                 }
                 float vf[UNR][8];
 #pragma unroll
                 for (int u = 0; u < UNR; ++u) unpack8(vr[u], vf[u]);
 #pragma unroll
-                for (int g = 0; g < kGC; ++g) {
+                for (int g = 0; g < GC; ++g) {
                     float mn = mi[g];
 #pragma unroll
                     for (int u = 0; u < UNR; ++u) mn = fmaxf(mn, sc[u][g]);
@@ -175,26 +227,29 @@ __global__ void __launch_bounds__(kThreads) attn_decode_kernel(DecParams p) {
                     }
                 }
             }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty_bar[st]);
+            ++pi;
         }
         // ---- merge the CTA's parts: weights once per (part, head), then one weighted sum per output
-        __syncthreads();
+        csync();
 #pragma unroll
-        for (int g = 0; g < kGC; ++g) {
+        for (int g = 0; g < GC; ++g) {
             if (sl == 0) { s_m[part][g] = mi[g]; s_l[part][g] = li[g]; }
             if (act) {
                 *reinterpret_cast<float4*>(&s_acc[part][g][sl * 8]) = make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
                 *reinterpret_cast<float4*>(&s_acc[part][g][sl * 8 + 4]) = make_float4(acc[g][4], acc[g][5], acc[g][6], acc[g][7]);
             }
         }
-        __syncthreads();
-        if (threadIdx.x < PARTS * kGC) {
+        csync();
+        if (threadIdx.x < PARTS * GC) {
             const int pp = threadIdx.x % PARTS, g = threadIdx.x / PARTS;
             float M = -INFINITY;
 #pragma unroll
             for (int j = 0; j < PARTS; ++j) M = fmaxf(M, s_m[j][g]);
             s_w[pp][g] = exp_rel(s_m[pp][g], M);
         }
-        __syncthreads();
+        csync();
         for (int idx = threadIdx.x; idx < gc * HD; idx += kThreads) {
             const int g = idx / HD, dd = idx % HD;
             float A = 0.f;
@@ -219,13 +274,13 @@ __global__ void __launch_bounds__(kThreads) attn_decode_kernel(DecParams p) {
 
     // ---- last CTA of this (batch, kv head) merges the splits
     __threadfence();
-    __syncthreads();
+    csync();
     if (threadIdx.x == 0) {
         int old = atomicAdd(a.counters + b * a.nkv + kvh, 1);
         s_last = (old == a.splits - 1);
         if (s_last) a.counters[b * a.nkv + kvh] = 0;  // ready for the next launch
     }
-    __syncthreads();
+    csync();
     if (!s_last) return;
     __threadfence();
     // One round trip: every thread first issues the loads of its two output columns from all splits, then the
@@ -255,7 +310,7 @@ __global__ void __launch_bounds__(kThreads) attn_decode_kernel(DecParams p) {
                 for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
                 s_fw[lane][g2] = wt * (1.0f / L);
             }
-            __syncthreads();
+            csync();
         }
         float2 A = make_float2(0.f, 0.f);
 #pragma unroll
@@ -270,26 +325,60 @@ __global__ void __launch_bounds__(kThreads) attn_decode_kernel(DecParams p) {
 
 }  // namespace
 
+int attn_decode_splits(int pages, int groups, int sms) {
+    // about three CTAs per SM (what the kernel's registers and page ring allow to be resident), never more splits than pages
+    const int want = (3 * sms + groups - 1) / std::max(1, groups);
+    return std::max(1, std::min({want, pages, kMaxSplits}));
+}
+
 size_t attn_decode_ws_floats(int batch, int nq, int hd, int splits) { return size_t(batch) * nq * splits * (hd + 2); }
+
+template <int HD, bool SW, int GC>
+int32_t launch_decode(const CUtensorMap& mk, const CUtensorMap& mv, const DecParams& p, dim3 grid, cudaStream_t st) {
+    const size_t smem = size_t(p.stages) * 2 * FORGE_KV_PAGE * HD * 2;
+    auto kern = attn_decode_kernel<HD, SW, GC>;
+    FORGE_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(size_t(kStages) * 2 * FORGE_KV_PAGE * HD * 2)));
+    FORGE_CUDA(launch_pdl(kern, grid, dim3(kBlock), smem, st, mk, mv, p));
+    FORGE_LAUNCH_CHECK();
+    return FORGE_OK;
+}
+
+template <int GC>
+int32_t launch_decode_hd(int hd, bool sw, const CUtensorMap& mk, const CUtensorMap& mv, const DecParams& p, dim3 grid, cudaStream_t st) {
+    if (hd == 64) return sw ? launch_decode<64, true, GC>(mk, mv, p, grid, st) : launch_decode<64, false, GC>(mk, mv, p, grid, st);
+    if (hd == 96) return sw ? launch_decode<96, true, GC>(mk, mv, p, grid, st) : launch_decode<96, false, GC>(mk, mv, p, grid, st);
+    return sw ? launch_decode<128, true, GC>(mk, mv, p, grid, st) : launch_decode<128, false, GC>(mk, mv, p, grid, st);
+}
 
 int32_t attn_decode(const AttnDecodeArgs& a, cudaStream_t st) {
     if (a.nq % a.nkv) { set_error("attention: num_heads %d not a multiple of num_kv_heads %d", a.nq, a.nkv); return FORGE_ERR_SHAPE; }
     if (a.splits < 1 || (a.splits > 1 && (!a.ws || !a.counters))) { set_error("attention: split workspace missing"); return FORGE_ERR_INVALID_ARG; }
     if (a.nq / a.nkv > kMaxGroup) { set_error("attention: at most %d query heads per KV head", kMaxGroup); return FORGE_ERR_SHAPE; }
     if (a.splits > kMaxSplits) { set_error("attention: at most %d context splits", kMaxSplits); return FORGE_ERR_INVALID_ARG; }
-    DecParams p{a, 1.0f / sqrtf(float(a.hd))};
-    dim3 grid(a.splits, a.nkv, a.batch);
-    switch (a.hd) {
-        case 64: FORGE_CUDA(a.window > 0 ? launch_pdl(attn_decode_kernel<64, true>, grid, dim3(kThreads), 0, st, p)
-                                          : launch_pdl(attn_decode_kernel<64, false>, grid, dim3(kThreads), 0, st, p)); break;
-        case 96: FORGE_CUDA(a.window > 0 ? launch_pdl(attn_decode_kernel<96, true>, grid, dim3(kThreads), 0, st, p)
-                                          : launch_pdl(attn_decode_kernel<96, false>, grid, dim3(kThreads), 0, st, p)); break;
-        case 128: FORGE_CUDA(a.window > 0 ? launch_pdl(attn_decode_kernel<128, true>, grid, dim3(kThreads), 0, st, p)
-                                          : launch_pdl(attn_decode_kernel<128, false>, grid, dim3(kThreads), 0, st, p)); break;
-        default: set_error("attention: head_dim %d unsupported (64, 96, 128)", a.hd); return FORGE_ERR_SHAPE;
+    if (a.hd != 64 && a.hd != 96 && a.hd != 128) { set_error("attention: head_dim %d unsupported (64, 96, 128)", a.hd); return FORGE_ERR_SHAPE; }
+    // tensor maps of the two pools: the caller's (a paged cache keeps them), or made here for a contiguous cache
+    CUtensorMap mk, mv;
+    if (a.map_k && a.map_v) {
+        mk = *static_cast<const CUtensorMap*>(a.map_k);
+        mv = *static_cast<const CUtensorMap*>(a.map_v);
+    } else {
+        const size_t rows = a.page_table ? 0 : size_t(a.batch) * a.max_ctx;
+        if (!rows) { set_error("attention: a paged cache needs its tensor maps"); return FORGE_ERR_INVALID_ARG; }
+        FORGE_TRY(make_kv_map(&mk, a.k_pool, a.hd, a.nkv, rows));
+        FORGE_TRY(make_kv_map(&mv, a.v_pool, a.hd, a.nkv, rows));
     }
-    FORGE_LAUNCH_CHECK();
-    return FORGE_OK;
+    // ring depth: the pages a CTA will see (per pass over the query heads), at most kStages
+    const int ctx = a.seq_len ? a.max_ctx : a.seq_len_host;
+    const int pages_per_cta = ((ctx + FORGE_KV_PAGE - 1) / FORGE_KV_PAGE + a.splits - 1) / a.splits;
+    // three CTAs per SM (two with 128-wide heads) share its shared memory with their merge buffers: a ring of 48 KB
+    // each for 64- and 96-wide heads (3 and 2 pages of K and V), 64 KB (2 pages) for 128-wide
+    const int fit = std::max(2, int((56u << 10) / (2u * FORGE_KV_PAGE * a.hd * sizeof(__half))));
+    DecParams p{a, 1.0f / sqrtf(float(a.hd)), pages_per_cta <= 2 ? 2 : std::min(kStages, fit)};
+    dim3 grid(a.splits, a.nkv, a.batch);
+    const int group = a.nq / a.nkv;
+    if (group == 1) return launch_decode_hd<1>(a.hd, a.window > 0, mk, mv, p, grid, st);
+    if (group == 2) return launch_decode_hd<2>(a.hd, a.window > 0, mk, mv, p, grid, st);
+    return launch_decode_hd<4>(a.hd, a.window > 0, mk, mv, p, grid, st);
 }
 
 }  // namespace forge
@@ -363,7 +452,7 @@ extern "C" int32_t forge_attention_flash_static(float* out, const float* q, cons
     StaticScratch* sc = nullptr;
     FORGE_TRY(static_scratch(&sc));
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    const int splits = std::min(kStaticMaxSplits, std::max(1, seq_len / 64));
+    const int splits = std::min(kStaticMaxSplits, attn_decode_splits((seq_len + FORGE_KV_PAGE - 1) / FORGE_KV_PAGE, num_kv_heads, 148));
     // the tickets must start at zero; the partials are fully rewritten by every call that reads them
     FORGE_CUDA(cudaMemsetAsync(sc->counters, 0, sizeof(int) * num_kv_heads, st));
     AttnDecodeArgs a{out, q, reinterpret_cast<const __half*>(k_cache), reinterpret_cast<const __half*>(v_cache), nullptr, 0, nullptr,

@@ -221,8 +221,18 @@ struct AttnDecodeArgs {
     float* ws; int* counters;                // split workspace
     int splits;
     int window = 0;                          // > 0: only the last `window` positions are attended to
+    // tensor maps (CUtensorMap, host memory) of the K and V pools as {head_dim, kv heads, rows}: a paged cache passes its
+    // own (made once, see make_kv_map) with row_base = first row of the layer; a contiguous cache may leave them null
+    const void* map_k = nullptr; const void* map_v = nullptr;
+    int row_base = 0;
+    int* err = nullptr;                      // set when a bounded wait gave up
 };
+// context splits for `groups` = batch * kv_heads independent (sequence, KV head) pairs over `pages` pages
+int attn_decode_splits(int pages, int groups, int sms);
 size_t attn_decode_ws_floats(int batch, int nq, int hd, int splits);
+// Tiled tensor map over an fp16 K or V pool of `rows` rows of kv_heads * head_dim values: dimensions {head_dim, kv_heads,
+// rows}, box {head_dim, 1, 64} = one page of one KV head (`out`: a CUtensorMap in host memory)
+int32_t make_kv_map(void* out, const __half* pool, int head_dim, int kv_heads, size_t rows);
 int32_t attn_decode(const AttnDecodeArgs& a, cudaStream_t st);
 
 struct AttnPrefillArgs {

@@ -377,6 +377,24 @@ int32_t make_map(CUtensorMap* map, const __half* base, int m, int K, int box_row
     return FORGE_OK;
 }
 
+}  // namespace
+
+int32_t make_kv_map(void* out, const __half* pool, int head_dim, int kv_heads, size_t rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) { set_error("cuTensorMapEncodeTiled is not available from this driver"); return FORGE_ERR_UNSUPPORTED; }
+    const cuuint64_t dims[3] = {cuuint64_t(head_dim), cuuint64_t(kv_heads), cuuint64_t(rows)};
+    const cuuint64_t strides[2] = {cuuint64_t(head_dim) * 2, cuuint64_t(kv_heads) * head_dim * 2};
+    const cuuint32_t box[3] = {cuuint32_t(head_dim), 1, cuuint32_t(FORGE_KV_PAGE)};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(static_cast<CUtensorMap*>(out), CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<__half*>(pool), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled failed for a KV pool (%d)", int(r)); return FORGE_ERR_CUDA; }
+    return FORGE_OK;
+}
+
+namespace {
+
 template <int QUANT, int NT, bool SPLIT>
 int32_t launch_ts(const __half* A, const __half* Alo, const Tc5Params& p, cudaStream_t st) {
     constexpr int NP = SPLIT ? 2 : 1;

@@ -107,6 +107,7 @@ struct ForgeKV {
     int32_t* d_page_table = nullptr; int32_t* d_seq_len = nullptr;
     std::vector<int32_t> h_page_table; std::vector<int> free_pages; std::vector<int> pages_used; std::vector<int> len;
     float* attn_ws = nullptr; int* attn_counters = nullptr; int splits = 1;
+    alignas(64) unsigned char k_map[128], v_map[128];   // CUtensorMap of the two pools (all layers), for the decode attention's page copies
     cudaGraphExec_t graph = nullptr; int graph_batch = 0; bool graph_greedy = false; int graph_gen = -1;  // scratch generation the graph was captured with
 };
 
@@ -436,6 +437,7 @@ int32_t decode_launches_batched(ForgeModel* m, ForgeKV* kv, int batch, bool gree
                                 m->qk, m->kv, m->hd, st));
         AttnDecodeArgs da{m->d_attn, m->d_q, kp, vp, kv->d_page_table, kv->pages_per_seq, kv->d_seq_len, 0,
                           n, m->nq, m->nkv, m->hd, kv->max_seq, kv->attn_ws, kv->attn_counters, kv->splits, c.sliding_window};
+        da.map_k = kv->k_map; da.map_v = kv->v_map; da.row_base = int(size_t(l) * kv->num_pages * FORGE_KV_PAGE); da.err = m->d_err;
         FORGE_TRY(attn_decode(da, st));
         FORGE_TRY(batched_row_sliced(m, L.o_t, m->d_attn, m->qk, PLAIN, n, st));
         FORGE_TRY(batched_product(m, L.gateup_t, m->d_hidden, m->h, NORM, L.ffn_norm, n, m->p_gu, nullptr, st));
@@ -469,6 +471,7 @@ int32_t decode_launches_gemm(ForgeModel* m, ForgeKV* kv, int batch, bool greedy,
                                 m->qk, m->kv, m->hd, st));
         AttnDecodeArgs da{m->d_attn, m->d_q, kp, vp, kv->d_page_table, kv->pages_per_seq, kv->d_seq_len, 0,
                           n, m->nq, m->nkv, m->hd, kv->max_seq, kv->attn_ws, kv->attn_counters, kv->splits, c.sliding_window};
+        da.map_k = kv->k_map; da.map_v = kv->v_map; da.row_base = int(size_t(l) * kv->num_pages * FORGE_KV_PAGE); da.err = m->d_err;
         FORGE_TRY(attn_decode(da, st));
         FORGE_TRY(f32_to_f16(m->p_attn16, alo, m->d_attn, size_t(n) * m->qk, st));
         FORGE_TRY(row_sliced_gemm_norm(m, L.o, m->p_attn16, alo, n, L.ffn_norm, nlo, st));
@@ -543,6 +546,7 @@ int32_t decode_launches(ForgeModel* m, ForgeKV* kv, int batch, bool greedy, bool
         }
         AttnDecodeArgs da{m->d_attn, m->d_q, kp, vp, page_table, kv->pages_per_seq, seq_len, 0,
                           batch, m->nq, m->nkv, m->hd, kv->max_seq, kv->attn_ws, kv->attn_counters, kv->splits, c.sliding_window};
+        da.map_k = kv->k_map; da.map_v = kv->v_map; da.row_base = int(size_t(l) * kv->num_pages * FORGE_KV_PAGE); da.err = m->d_err;
         FORGE_TRY(attn_decode(da, st));
         GemvArgs o;
         o.x = m->d_attn; o.out = hid[cur]; o.resid = hid[cur]; o.batch = batch;
@@ -908,6 +912,13 @@ int32_t forge_kv_create(ForgeModel* m, int32_t max_seq, int32_t batch, ForgeKV**
     if (cudaMalloc(&kv->k_pool, pool * sizeof(__half)) != cudaSuccess || cudaMalloc(&kv->v_pool, pool * sizeof(__half)) != cudaSuccess) {
         set_error("KV pool allocation of %zu bytes failed", 2 * pool * sizeof(__half)); cudaGetLastError(); return fail(FORGE_ERR_CUDA);
     }
+    static_assert(sizeof(kv->k_map) >= 128, "CUtensorMap is 128 bytes");
+    {
+        const size_t rows = size_t(kv->num_pages) * FORGE_KV_PAGE * m->cfg.num_layers;
+        int32_t rc = make_kv_map(kv->k_map, kv->k_pool, m->hd, m->nkv, rows);
+        if (rc == FORGE_OK) rc = make_kv_map(kv->v_map, kv->v_pool, m->hd, m->nkv, rows);
+        if (rc != FORGE_OK) return fail(rc);
+    }
     cudaMemsetAsync(kv->k_pool, 0, pool * sizeof(__half), m->stream);
     cudaMemsetAsync(kv->v_pool, 0, pool * sizeof(__half), m->stream);
     if (cudaMalloc(&kv->d_page_table, sizeof(int32_t) * kv->num_pages) != cudaSuccess || cudaMalloc(&kv->d_seq_len, sizeof(int32_t) * batch) != cudaSuccess)
@@ -918,11 +929,10 @@ int32_t forge_kv_create(ForgeModel* m, int32_t max_seq, int32_t batch, ForgeKV**
     kv->pages_used.assign(batch, 0);
     kv->len.assign(batch, 0);
     for (int i = kv->num_pages - 1; i >= 0; --i) kv->free_pages.push_back(i);
-    // split-KV: enough CTAs to cover the SMs about twice
+    // split-KV: enough CTAs to fill the SMs
     int sms = 148;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, m->device);
-    int want = (2 * sms + batch * m->nkv - 1) / (batch * m->nkv);
-    kv->splits = std::max(1, std::min({want, kv->pages_per_seq, 32}));
+    kv->splits = attn_decode_splits(kv->pages_per_seq, batch * m->nkv, sms);
     if (cudaMalloc(&kv->attn_ws, sizeof(float) * attn_decode_ws_floats(batch, m->nq, m->hd, kv->splits)) != cudaSuccess ||
         cudaMalloc(&kv->attn_counters, sizeof(int) * batch * m->nkv) != cudaSuccess) { set_error("attention workspace allocation failed"); return fail(FORGE_ERR_CUDA); }
     cudaMemsetAsync(kv->attn_counters, 0, sizeof(int) * batch * m->nkv, m->stream);

@@ -2,8 +2,8 @@
 library instead of per-call allocations, for hosts that cannot let the library allocate device memory.
 
 Collected last on purpose (file name): a run that stops at the first failure has then already run every
-other test.  The check is against the allocating entry point on the same inputs, twice in a row, so that a
-second call meets the scratch exactly as the first one left it."""
+other test.  The checks are against the allocating entry point on the same inputs and against the CPU restatement of
+attention_flash, several calls in a row, so that a later call meets the scratch exactly as an earlier one left it."""
 import numpy as np
 import pytest
 
@@ -19,7 +19,7 @@ def _case(rng, nq, nkv, hd, seq):
     return q, k, v
 
 
-def test_static_scratch_attention_matches_allocating_entry_point():
+def test_static_scratch_attention_matches_allocating_entry_point(oracle):
     import torch
     from forge_llm_b200._lib import check, lib
     rng = np.random.default_rng(77)
@@ -36,6 +36,9 @@ def test_static_scratch_attention_matches_allocating_entry_point():
         a, b = got.cpu().numpy(), ref.cpu().numpy()
         assert np.isfinite(a).all()
         assert rel_l2(a, b) < 3e-6  # the tolerance of the decode-attention parity test
+        # and against the CPU restatement (fp16 K/V stand-in), with the same bound as the allocating entry point's own test
+        want = oracle.attention_flash(q, oracle.KV_F16, k.astype(np.float32), v.astype(np.float32), None, None, seq, nq, nkv, hd)
+        assert rel_l2(a, want) < 3e-6
 
 
 def test_static_scratch_attention_rejects_oversized_shapes():
