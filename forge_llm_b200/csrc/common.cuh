@@ -68,6 +68,11 @@ struct TpComm;
 int32_t tp_unique_id(uint8_t* out);
 int32_t tp_init(TpComm** out, const uint8_t* id_bytes, int rank, int world);
 int32_t tp_allreduce_sum(TpComm* c, float* buf, size_t n, cudaStream_t st);  // in place, on st
+// hidden[0..count) += sum over ranks of part, through {value, tag} pairs in the ranks' exchange buffers (peer memory);
+// `region` and `cap` (pairs) place the [slot][rank][cap] area inside every rank's buffer
+int32_t tp_pair_sum(float* hidden, const float* part, uint2* const* peer_ll, const uint2* local_ll, size_t region, size_t cap, int count,
+                    int world, int rank, int slot, const uint32_t* step_counter, uint32_t step_mul, uint32_t step_add, uint32_t limit,
+                    int* err, cudaStream_t st);
 void tp_destroy(TpComm* c);
 
 // ------------------------------------------------------------------ programmatic dependent launch

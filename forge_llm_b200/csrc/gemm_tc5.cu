@@ -421,7 +421,7 @@ bool gemm_tc5_supported(const QWeight& w) { return w.K % BK == 0 && w.K >= BK; }
 // keep at least 16 K steps (1024 columns) per slice, at most 4.  A tensor-memory accumulator rounds toward zero at every
 // accumulation, a bias that grows with the chain (measured: 7e-6 of the result at K = 2048, 2.7e-5 at K = 8192) and,
 // being one-sided, adds up over the layers; shorter chains keep it at the K = 2048 level.
-int gemm_tc5_ksplit(const QWeight& w) { return std::max(1, std::min(4, w.K / 2048)); }
+int gemm_tc5_ksplit(const QWeight& w) { return std::max(1, std::min(4, w.K / 1024)); }
 
 int32_t gemm_tc5(float* out, const __half* A, const __half* Alo, const QWeight& w, int m, const float* resid, int* err, cudaStream_t st,
                  int ksplit, size_t part_stride) {

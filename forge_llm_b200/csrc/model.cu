@@ -305,6 +305,12 @@ int32_t row_sliced_gemv(ForgeModel* m, const QTiled& w, GemvArgs a, int batch, c
     return residual_add_f32(m->d_hidden, m->d_part, size_t(batch) * m->h, st);
 }
 
+// exchange buffer of {value, tag} pairs: ll[2 slots][world][h] for the single-sequence step, then
+// [2 slots][world][kTpxRows * h] for the rows of a batched step
+constexpr int kTpxRows = 32;
+inline size_t tpx_region_pairs(const ForgeModel* m) { return 2 * size_t(m->cfg.tp_world) * m->h; }
+inline size_t tpx_bytes(const ForgeModel* m) { return sizeof(uint2) * tpx_region_pairs(m) * (1 + kTpxRows); }
+
 int32_t decode_launches(ForgeModel* m, ForgeKV* kv, int batch, bool greedy, bool record, const struct PrefillToken* pt);
 int32_t prefill_per_token(ForgeModel* m, ForgeKV* kv, int seq, const uint32_t* tokens_host, int n);
 
@@ -368,8 +374,6 @@ int32_t prefill_seq(ForgeModel* m, ForgeKV* kv, int seq, const uint32_t* tokens_
     return FORGE_OK;
 }
 
-// exchange buffer: ll[2 slots][world][h] of {value, step} pairs
-inline size_t tpx_bytes(const ForgeModel* m) { return sizeof(uint2) * 2 * size_t(m->cfg.tp_world) * m->h; }
 
 // ------------------------------------------------------------------ one decode step (launch sequence)
 // forward(), emit.rs:4029-4500, for `batch` sequences.  Tokens are read from m->d_tok, positions
@@ -414,10 +418,17 @@ int32_t batched_product(ForgeModel* m, const QTiled& w, const float* x, size_t x
     return FORGE_OK;
 }
 
-// hidden += W f(x) for a projection whose K dimension is sliced over the tensor-parallel ranks
-int32_t batched_row_sliced(ForgeModel* m, const QTiled& w, const float* x, size_t x_stride, int mode, int n, cudaStream_t st) {
+// hidden += W f(x) for a projection whose K dimension is sliced over the tensor-parallel ranks; `sum_index` numbers
+// the step's sums (the pair exchange tags them with it)
+int32_t batched_row_sliced(ForgeModel* m, const QTiled& w, const float* x, size_t x_stride, int mode, int n, int* sum_index, cudaStream_t st) {
     if (m->cfg.tp_world == 1) return batched_product(m, w, x, x_stride, mode, nullptr, n, m->d_hidden, m->d_hidden, st);
     FORGE_TRY(batched_product(m, w, x, x_stride, mode, nullptr, n, m->d_part, nullptr, st));
+    if (m->tpx_ready && n <= kTpxRows) {
+        const int index = (*sum_index)++;
+        return tp_pair_sum(m->d_hidden, m->d_part, m->d_tpx_ll, static_cast<const uint2*>(m->tpx_local), tpx_region_pairs(m),
+                           size_t(kTpxRows) * m->h, n * m->h, m->cfg.tp_world, m->cfg.tp_rank, index & 1, m->d_tpx_step,
+                           uint32_t(2 * m->cfg.num_layers + 1), uint32_t(index + 1), m->wait_limit, m->d_err, st);
+    }
     FORGE_TRY(tp_allreduce_sum(m->tp, m->d_part, size_t(n) * m->h, st));
     return residual_add_f32(m->d_hidden, m->d_part, size_t(n) * m->h, st);
 }
@@ -427,6 +438,7 @@ int32_t decode_launches_batched(ForgeModel* m, ForgeKV* kv, int batch, bool gree
     cudaStream_t st = m->stream;
     const int n = batch;
     enum { PLAIN = 0, NORM = 1, SILU = 2 };
+    int sums = 0;  // tensor-parallel sums issued in this step
     FORGE_TRY(embedding_rows(m->d_hidden, m->embed, m->d_tok, n, m->h, record ? m->d_hist : nullptr, m->d_step, st));
     for (int l = 0; l < c.num_layers; ++l) {
         ForgeLayer& L = m->layers[l];
@@ -439,13 +451,13 @@ int32_t decode_launches_batched(ForgeModel* m, ForgeKV* kv, int batch, bool gree
                           n, m->nq, m->nkv, m->hd, kv->max_seq, kv->attn_ws, kv->attn_counters, kv->splits, c.sliding_window};
         da.map_k = kv->k_map; da.map_v = kv->v_map; da.row_base = int(size_t(l) * kv->num_pages * FORGE_KV_PAGE); da.err = m->d_err;
         FORGE_TRY(attn_decode(da, st));
-        FORGE_TRY(batched_row_sliced(m, L.o_t, m->d_attn, m->qk, PLAIN, n, st));
+        FORGE_TRY(batched_row_sliced(m, L.o_t, m->d_attn, m->qk, PLAIN, n, &sums, st));
         FORGE_TRY(batched_product(m, L.gateup_t, m->d_hidden, m->h, NORM, L.ffn_norm, n, m->p_gu, nullptr, st));
-        FORGE_TRY(batched_row_sliced(m, L.down_t, m->p_gu, size_t(2) * m->ff, SILU, n, st));
+        FORGE_TRY(batched_row_sliced(m, L.down_t, m->p_gu, size_t(2) * m->ff, SILU, n, &sums, st));
     }
     FORGE_TRY(batched_product(m, m->lm_head_t, m->d_hidden, m->h, NORM, m->final_norm, n, m->d_logits, nullptr, st));
     if (greedy) FORGE_TRY(argmax_slices(m->d_tok, m->d_logits, m->V, n, m->d_amax_val, m->d_amax_idx, m->d_amax_ticket, st));
-    return step_advance(kv->d_seq_len, n, m->d_step, st, nullptr);
+    return step_advance(kv->d_seq_len, n, m->d_step, st, sums ? m->d_tpx_step : nullptr);
 }
 
 // A decode step of more than 32 sequences: every projection is one tensor-core product over the batch rows (the rule

@@ -1,7 +1,8 @@
 """One rank of the tensor-parallel parity check (launched by test_tp_gpu.py under torch.distributed.run).
 
 Every rank builds the same synthetic model with tp_world = WORLD_SIZE on its own GPU; rank 0 compares the
-logits of a prefill and of teacher-forced decode steps, and the greedy ids, with the CPU restatement.
+logits of a prefill, of teacher-forced decode steps (single-sequence and batched), and the greedy ids, with the CPU
+restatement.
 """
 import os
 import sys
@@ -64,6 +65,33 @@ def main():
         worst = max(float(np.abs(a - b).max()) for a, b in zip(steps, ref))
         ok = same and worst < 2e-2 and np.array_equal(ids, ref_ids)
         print(f"TP{world} {key}: ranks identical={same} worst |dlogit|={worst:.3e} greedy ids equal={np.array_equal(ids, ref_ids)}", flush=True)
+    # a batched step (four sequences of different lengths): teacher-forced logits of every sequence, three steps
+    nb = 4
+    kvb = gm.new_cache(max_seq=n_prompt + 16, batch=nb)
+    prompts = [synth.prompt_tokens(c, n_prompt - 7 * b, seed=20 + b) for b in range(nb)]
+    last, oms = [], []
+    for b in range(nb):
+        gm.forward_prefill(prompts[b], kvb, seq=b, want_logits=False)
+        if rank == 0:
+            om_b = oracle.OracleModel(c, blob, kv_mode=oracle.KV_F16)
+            last.append(om_b.forward_prefill(prompts[b]))
+            oms.append(om_b)
+    worst_b, same_b = 0.0, True
+    for _ in range(3):
+        t = torch.tensor([int(oracle.argmax(l)) for l in last] if rank == 0 else [0] * nb, dtype=torch.int64)
+        dist.broadcast(t, 0)
+        lgb = gm.forward_batch(t.numpy().astype(np.uint32), kvb)
+        mine = torch.from_numpy(np.ascontiguousarray(lgb))
+        gathered = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(gathered, mine)
+        same_b = same_b and all(torch.equal(g, gathered[0]) for g in gathered)
+        if rank == 0:
+            last = [oms[b].forward(int(t[b].item())) for b in range(nb)]
+            worst_b = max(worst_b, max(float(np.abs(lgb[b] - last[b]).max()) for b in range(nb)))
+    kvb.close()
+    if rank == 0:
+        ok = ok and same_b and worst_b < 2e-2
+        print(f"TP{world} {key} batched step: ranks identical={same_b} worst |dlogit|={worst_b:.3e}", flush=True)
     flag = torch.tensor([1 if ok else 0])
     dist.broadcast(flag, 0)
     kv.close()
