@@ -13,7 +13,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(CSRC, "build")
 LIB = os.path.join(HERE, "libforge_b200.so")
-SOURCES = ["pack.cu", "gemv_tc.cu", "gemv_batch.cu", "elementwise.cu", "attn_decode.cu", "attn_prefill.cu", "gemm_mma.cu", "gemm_tc5.cu",
+SOURCES = ["pack.cu", "gemv_tc.cu", "gemv_batch.cu", "elementwise.cu", "attn_decode.cu", "attn_prefill_tc5.cu", "gemm_mma.cu", "gemm_tc5.cu",
            "tp_comm.cu", "gguf_reader.cu", "kquant_host.cu", "sampler.cu", "api_ops.cu", "model.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC,-fopenmp,-O3", "-Xptxas", "-v"]

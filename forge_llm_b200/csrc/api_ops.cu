@@ -260,13 +260,37 @@ int32_t forge_attention_flash(float* out, const float* q, const uint16_t* k_cach
     return attn_decode(a, st);
 }
 
+// the batched attention of the operator surface: f32 queries become fp16 hi + lo pairs (the tensor-core kernel's precise
+// form), the contiguous cache is addressed as pages of 64 positions, rows past the last position read as zero
+static int32_t attention_batch_f32(float* out, const float* q_batch, const uint16_t* k_cache, const uint16_t* v_cache, int32_t m, int32_t base_pos,
+                                   int32_t window, int32_t num_heads, int32_t num_kv_heads, int32_t head_dim, cudaStream_t st) {
+    if (m == 0) return FORGE_OK;
+    const size_t nq = size_t(m) * num_heads * head_dim;
+    AsyncBuf q16(st), q16lo(st), err(st);
+    FORGE_CUDA(q16.alloc(nq * sizeof(__half)));
+    FORGE_CUDA(q16lo.alloc(nq * sizeof(__half)));
+    FORGE_CUDA(err.alloc(sizeof(int)));
+    FORGE_CUDA(cudaMemsetAsync(err.p, 0, sizeof(int), st));
+    FORGE_TRY(f32_to_f16(static_cast<__half*>(q16.p), static_cast<__half*>(q16lo.p), q_batch, nq, st));
+    AttnPrefillArgs a{nullptr, nullptr, out, static_cast<const __half*>(q16.p), reinterpret_cast<const __half*>(k_cache), reinterpret_cast<const __half*>(v_cache),
+                      nullptr, m, base_pos, num_heads, num_kv_heads, head_dim, window};
+    a.q16_lo = static_cast<const __half*>(q16lo.p);
+    a.precise = 1;
+    a.pool_rows = size_t(base_pos) + size_t(m);
+    a.err = static_cast<int*>(err.p);
+    FORGE_TRY(attn_prefill(a, st));
+    int h_err = 0;
+    FORGE_CUDA(cudaMemcpyAsync(&h_err, err.p, sizeof(int), cudaMemcpyDeviceToHost, st));
+    FORGE_CUDA(cudaStreamSynchronize(st));
+    if (h_err) { set_error("attention: a bounded device-side wait gave up"); return FORGE_ERR_TIMEOUT; }
+    return FORGE_OK;
+}
+
 int32_t forge_attention_flash_batch(float* out, const float* q_batch, const uint16_t* k_cache, const uint16_t* v_cache, int32_t m,
                                     int32_t base_pos, int32_t num_heads, int32_t num_kv_heads, int32_t head_dim, void* stream) {
     FORGE_TRY(need_device());
     if (!out || !q_batch || !k_cache || !v_cache || m < 0 || base_pos < 0 || num_heads <= 0 || num_kv_heads <= 0) { set_error("bad argument to forge_attention_flash_batch"); return FORGE_ERR_INVALID_ARG; }
-    AttnPrefillArgs a{nullptr, nullptr, out, nullptr, reinterpret_cast<const __half*>(k_cache), reinterpret_cast<const __half*>(v_cache), nullptr,
-                      m, base_pos, num_heads, num_kv_heads, head_dim};
-    return attn_prefill_q32(a, q_batch, static_cast<cudaStream_t>(stream));
+    return attention_batch_f32(out, q_batch, k_cache, v_cache, m, base_pos, 0, num_heads, num_kv_heads, head_dim, static_cast<cudaStream_t>(stream));
 }
 
 int32_t forge_attention_sliding(float* out, const float* q, const uint16_t* k_cache, const uint16_t* v_cache, int32_t seq_len,
@@ -289,9 +313,7 @@ int32_t forge_attention_sliding_batch(float* out, const float* q_batch, const ui
                                       void* stream) {
     FORGE_TRY(need_device());
     if (!out || !q_batch || !k_cache || !v_cache || m < 0 || base_pos < 0 || window <= 0 || num_heads <= 0 || num_kv_heads <= 0) { set_error("bad argument to forge_attention_sliding_batch"); return FORGE_ERR_INVALID_ARG; }
-    AttnPrefillArgs a{nullptr, nullptr, out, nullptr, reinterpret_cast<const __half*>(k_cache), reinterpret_cast<const __half*>(v_cache), nullptr,
-                      m, base_pos, num_heads, num_kv_heads, head_dim, window};
-    return attn_prefill_q32(a, q_batch, static_cast<cudaStream_t>(stream));
+    return attention_batch_f32(out, q_batch, k_cache, v_cache, m, base_pos, window, num_heads, num_kv_heads, head_dim, static_cast<cudaStream_t>(stream));
 }
 
 int32_t forge_argmax(uint32_t* result, const float* logits, int32_t n, void* stream) {

@@ -21,7 +21,6 @@ namespace {
 constexpr int kThreads = 128;     // consumer threads (four warps); warp 4 is the producer
 constexpr int kBlock = kThreads + 32;
 constexpr int kStages = 4;        // most pages (K and V) in flight per CTA (a CTA with one or two pages takes a ring of two)
-constexpr int kGC = 4;  // most query heads processed per pass over the keys (the kernel is built for 1, 2 and 4)
 constexpr int kMaxGroup = 16;  // query heads per KV head
 constexpr int kMaxSplits = 32;    // context splits per KV head (the merge keeps one partial per split in registers)
 constexpr uint32_t kSpin = 1u << 22;

@@ -249,11 +249,12 @@ struct AttnPrefillArgs {
     int window = 0;                          // > 0: query position p sees keys [max(0, p - window + 1), p]
     // precise: queries and probabilities enter the tensor cores as fp16 hi + lo pairs (two MMAs each), which takes the
     // output from ~1e-4 to ~1e-6 of the f32 result; used where the output feeds an 8-bit rounding (K-quant models)
-    const __half* q16_lo = nullptr;          // [m][nq*hd] low parts of q16 (precise mode; null = zeros)
+    const __half* q16_lo = nullptr;          // [m][nq*hd] low parts of q16 (precise mode)
     int precise = 0;
+    size_t pool_rows = 0;                    // rows of k_pool / v_pool (positions); rows beyond them read as zero
+    int* err = nullptr;                      // set when a bounded wait gave up
 };
 int32_t attn_prefill(const AttnPrefillArgs& a, cudaStream_t st);
-int32_t attn_prefill_q32(const AttnPrefillArgs& a, const float* q32, cudaStream_t st);  // f32 queries, converted on load
 
 // ------------------------------------------------------------------ GEMM (prefill)
 // out f32 [m][N] = A f16 [m][K] x W^T; optional resid: out = resid + A W^T (may alias out)

@@ -355,6 +355,7 @@ int32_t prefill_seq(ForgeModel* m, ForgeKV* kv, int seq, const uint32_t* tokens_
         FORGE_TRY(qkv_post(qkv_src, n, base, L.qkv_bias, m->rope, m->p_q16, precise ? m->p_q16_lo : nullptr, kp, vp, page_row, m->qk, m->kv, m->hd, st, qks, qstride));
         AttnPrefillArgs pa{m->p_attn16, alo, nullptr, m->p_q16, kp, vp, page_row, n, base, m->nq, m->nkv, m->hd, c.sliding_window};
         if (precise) { pa.q16_lo = m->p_q16_lo; pa.precise = 1; }
+        pa.pool_rows = size_t(kv->num_pages) * FORGE_KV_PAGE; pa.err = m->d_err;
         FORGE_TRY(attn_prefill(pa, st));
         if (L.o.quant == FORGE_KQ_SOA) FORGE_TRY(q8_round_f16(m->p_attn16, alo, size_t(n) * m->qk, st));
         FORGE_TRY(row_sliced_gemm_norm(m, L.o, m->p_attn16, alo, n, L.ffn_norm, nlo, st));
