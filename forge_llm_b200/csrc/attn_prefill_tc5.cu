@@ -14,9 +14,11 @@
 // the cache's fp16 values either way, so the result is the f32 attention over those values to ~1e-5.
 // Warp roles (192 threads): warp 0 = TMA producer (3-D tiled copies: {64 dims, 1 head, rows}), warp 1 = TMEM
 // allocation and MMA issue (one lane), warps 2..5 = softmax, rescale and the final store.
-// Tensor memory (256 columns, so two CTAs share an SM when their shared memory allows): S [0,64), P_hi [64,96),
-// P_lo [96,128), O [128,128+HD).  Every wait is bounded; one that gives up sets the error word and the CTA still
-// frees its tensor memory.
+// The scores have two buffers: S of tile j + 1 is formed while the softmax warps work on tile j, and P V of tile j is
+// issued as soon as its probabilities are in place.  Tensor memory: S0 [0,64), S1 [64,128), P_hi [128,160), P_lo
+// [160,192), O from 192 (64-wide heads: 256 columns, two CTAs per SM) or from 256 (wider heads: 512 columns, one CTA
+// per SM, which is also what their shared memory allows).  Every wait is bounded; one that gives up sets the error
+// word and the CTA still frees its tensor memory.
 #include <cuda.h>
 
 #include <algorithm>
@@ -30,9 +32,11 @@ namespace {
 constexpr int BM = 128;   // query rows per CTA
 constexpr int BN = 64;    // keys per tile = one KV page
 constexpr int kThreads = 192;
-constexpr int KVS = 2;    // K/V stages
+constexpr int KVS = 3;    // K/V stages
 constexpr uint32_t kSpinLimit = 1u << 22;
-constexpr uint32_t kTmemCols = 256, kColS = 0, kColP = 64, kColO = 128;
+// tensor memory: two score buffers, the probabilities (hi | lo), the output
+constexpr uint32_t kColS = 0, kColP = 128;
+template <int HD> struct Tmem { static constexpr uint32_t cols = HD == 64 ? 256 : 512, o = HD == 64 ? 192 : 256; };
 
 struct Tc5AttnParams {
     AttnPrefillArgs a;
@@ -139,7 +143,8 @@ __global__ void __launch_bounds__(kThreads) attn_prefill_tc5_kernel(const __grid
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* sQ = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     unsigned char* sKV = sQ + Q_BYTES;
-    __shared__ uint64_t q_full, kv_full[KVS], kv_empty[KVS], s_full, p_full, pv_done;
+    __shared__ uint64_t q_full, kv_full[KVS], kv_empty[KVS], s_full[2], p_full, pv_done;
+    constexpr uint32_t kTmemCols = Tmem<HD>::cols, kColO = Tmem<HD>::o;
     __shared__ uint32_t s_tmem;
     __shared__ int s_err;
 
@@ -156,7 +161,8 @@ __global__ void __launch_bounds__(kThreads) attn_prefill_tc5_kernel(const __grid
     if (tid == 0) {
         mbar_init(&q_full, 1);
         for (int s = 0; s < KVS; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
-        mbar_init(&s_full, 1);
+        mbar_init(&s_full[0], 1);
+        mbar_init(&s_full[1], 1);
         mbar_init(&p_full, 4);
         mbar_init(&pv_done, 1);
         s_err = 0;
@@ -193,54 +199,48 @@ __global__ void __launch_bounds__(kThreads) attn_prefill_tc5_kernel(const __grid
             }
         }
     } else if (warp == 1) {
-        // ---------------- MMA issuer
+        // ---------------- MMA issuer: S of the next tile first, then P V of this one once its probabilities are in place
         if (lane == 0) {
             bool ok = mbar_wait(&q_full, 0, &s_err);
             const uint32_t q_base = smem_u32(sQ);
-            for (int j = 0; j < nblk && ok; ++j) {
-                const int s = j % KVS;
-                const uint32_t k_base = smem_u32(sKV + size_t(s) * STAGE);
-                // S = Q K^T may overwrite S once the softmax warps have read the previous tile's scores (they have when
-                // its probabilities are published)
-                if (!mbar_wait(&kv_full[s], (j / KVS) & 1, &s_err) || (j > 0 && !mbar_wait(&p_full, (j - 1) & 1, &s_err))) { ok = false; break; }
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                if (j > 0) {
-                    // O += P V of the previous tile (its probabilities are in place), then release that stage
-                    const int sp = (j - 1) % KVS;
-                    const uint32_t vp_base = smem_u32(sKV + size_t(sp) * STAGE) + NCH * KV_CHUNK;
-#pragma unroll
-                    for (int pass = 0; pass < NP; ++pass)
-#pragma unroll
-                        for (int k16 = 0; k16 < BN / 16; ++k16)
-                            umma_ts(tmem + kColO, tmem + kColP + uint32_t(pass * 32 + k16 * 8), desc_mnmajor(vp_base + k16 * 2048, KV_CHUNK),
-                                    Idesc<HD, true>::value, (j > 1 || pass > 0 || k16 > 0) ? 1u : 0u);
-                    umma_commit(&pv_done);
-                    umma_commit(&kv_empty[sp]);
-                }
+            auto issue_s = [&](int j) {   // S[j & 1] = Q K_j^T
+                const uint32_t k_base = smem_u32(sKV + size_t(j % KVS) * STAGE);
 #pragma unroll
                 for (int pass = 0; pass < NP; ++pass)
 #pragma unroll
                     for (int k16 = 0; k16 < HD / 16; ++k16) {
-                        const uint32_t off = uint32_t((k16 / 4)) , in = uint32_t((k16 % 4) * 32);
-                        umma_ss(tmem + kColS, desc_kmajor(q_base + (pass * NCH + off) * Q_CHUNK + in), desc_kmajor(k_base + off * KV_CHUNK + in),
-                                Idesc<BN, false>::value, (pass > 0 || k16 > 0) ? 1u : 0u);
+                        const uint32_t off = uint32_t(k16 / 4), in = uint32_t((k16 % 4) * 32);
+                        umma_ss(tmem + kColS + uint32_t((j & 1) * BN), desc_kmajor(q_base + (pass * NCH + off) * Q_CHUNK + in),
+                                desc_kmajor(k_base + off * KV_CHUNK + in), Idesc<BN, false>::value, (pass > 0 || k16 > 0) ? 1u : 0u);
                     }
-                umma_commit(&s_full);
-            }
-            if (ok && mbar_wait(&p_full, (nblk - 1) & 1, &s_err)) {
+                umma_commit(&s_full[j & 1]);
+            };
+            if (ok && mbar_wait(&kv_full[0], 0, &s_err)) {
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const int sp = (nblk - 1) % KVS;
-                const uint32_t vp_base = smem_u32(sKV + size_t(sp) * STAGE) + NCH * KV_CHUNK;
+                issue_s(0);
+            } else {
+                ok = false;
+            }
+            for (int j = 0; j < nblk && ok; ++j) {
+                if (j + 1 < nblk) {
+                    // its score buffer was last read for tile j - 1, whose probabilities were awaited one iteration ago
+                    if (!mbar_wait(&kv_full[(j + 1) % KVS], ((j + 1) / KVS) & 1, &s_err)) { ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    issue_s(j + 1);
+                }
+                if (!mbar_wait(&p_full, j & 1, &s_err)) { ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t v_base = smem_u32(sKV + size_t(j % KVS) * STAGE) + NCH * KV_CHUNK;
 #pragma unroll
                 for (int pass = 0; pass < NP; ++pass)
 #pragma unroll
                     for (int k16 = 0; k16 < BN / 16; ++k16)
-                        umma_ts(tmem + kColO, tmem + kColP + uint32_t(pass * 32 + k16 * 8), desc_mnmajor(vp_base + k16 * 2048, KV_CHUNK),
-                                Idesc<HD, true>::value, (nblk > 1 || pass > 0 || k16 > 0) ? 1u : 0u);
+                        umma_ts(tmem + kColO, tmem + kColP + uint32_t(pass * 32 + k16 * 8), desc_mnmajor(v_base + k16 * 2048, KV_CHUNK),
+                                Idesc<HD, true>::value, (j > 0 || pass > 0 || k16 > 0) ? 1u : 0u);
                 umma_commit(&pv_done);
-            } else {
-                atomicExch(&s_err, 1);
+                umma_commit(&kv_empty[j % KVS]);
             }
+            if (!ok) atomicExch(&s_err, 1);
         }
     } else {
         // ---------------- softmax (warps 2..5): TMEM lane = query row; a warp may only touch its lane quadrant
@@ -252,29 +252,38 @@ __global__ void __launch_bounds__(kThreads) attn_prefill_tc5_kernel(const __grid
         bool ok = true;
         for (int j = 0; j < nblk; ++j) {
             const int t0 = (lp_first + j) * BN;
-            if (ok && !mbar_wait(&s_full, j & 1, &s_err)) { atomicExch(&s_err, 1); ok = false; }
+            if (ok && !mbar_wait(&s_full[j & 1], (j >> 1) & 1, &s_err)) { atomicExch(&s_err, 1); ok = false; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             uint32_t sv[2][32];
-            tmem_ld32(lane_addr + kColS, sv[0]);
-            tmem_ld32(lane_addr + kColS + 32, sv[1]);
+            tmem_ld32(lane_addr + kColS + uint32_t((j & 1) * BN), sv[0]);
+            tmem_ld32(lane_addr + kColS + uint32_t((j & 1) * BN) + 32, sv[1]);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            // scores stay raw; the maximum and the exponent's argument take the scale (s * c - m * c is one fused
+            // multiply-add).  Only a tile that reaches past some row's position (or starts before its window) is masked.
+            const bool masked = t0 + BN - 1 > a.base_pos + q0 || (SW && t0 <= a.base_pos + q0 + BM - 1 - a.window);
             float mx = -INFINITY;
+            if (masked) {
 #pragma unroll
-            for (int c = 0; c < 64; ++c) {
-                const int t = t0 + c;
-                const bool seen = t <= pq && (!SW || t > pq - a.window);
-                const float s = seen ? __uint_as_float(sv[c >> 5][c & 31]) * p.scale_log2 : -INFINITY;
-                sv[c >> 5][c & 31] = __float_as_uint(s);
-                mx = fmaxf(mx, s);
+                for (int c = 0; c < 64; ++c) {
+                    const int t = t0 + c;
+                    const bool seen = t <= pq && (!SW || t > pq - a.window);
+                    const float s = seen ? __uint_as_float(sv[c >> 5][c & 31]) : -INFINITY;
+                    sv[c >> 5][c & 31] = __float_as_uint(s);
+                    mx = fmaxf(mx, s);
+                }
+            } else {
+#pragma unroll
+                for (int c = 0; c < 64; ++c) mx = fmaxf(mx, __uint_as_float(sv[c >> 5][c & 31]));
             }
-            const float m_new = fmaxf(m_run, mx);
+            const float m_new = fmaxf(m_run, mx * p.scale_log2);       // scale > 0: max(s) * c = max(s * c)
             const float m_use = m_new == -INFINITY ? 0.f : m_new;   // a row that has seen nothing yet: every p is 0
             const float alpha = m_run == -INFINITY ? (m_new == -INFINITY ? 1.f : 0.f) : ex2(m_run - m_new);
             float sum = 0.f;
             uint32_t ph[32], pl[32];
 #pragma unroll
             for (int c = 0; c < 64; c += 2) {
-                const float p0 = ex2(__uint_as_float(sv[c >> 5][c & 31]) - m_use), p1 = ex2(__uint_as_float(sv[c >> 5][(c & 31) + 1]) - m_use);
+                const float p0 = ex2(fmaf(__uint_as_float(sv[c >> 5][c & 31]), p.scale_log2, -m_use));
+                const float p1 = ex2(fmaf(__uint_as_float(sv[c >> 5][(c & 31) + 1]), p.scale_log2, -m_use));
                 sum += p0 + p1;
                 ph[c >> 1] = pack_h2(p0, p1);
                 if (PRECISE) pl[c >> 1] = pack_h2_lo(p0, p1, ph[c >> 1]);
