@@ -14,11 +14,13 @@
 // the cache's fp16 values either way, so the result is the f32 attention over those values to ~1e-5.
 // Warp roles (192 threads): warp 0 = TMA producer (3-D tiled copies: {64 dims, 1 head, rows}), warp 1 = TMEM
 // allocation and MMA issue (one lane), warps 2..5 = softmax, rescale and the final store.
-// The scores have two buffers: S of tile j + 1 is formed while the softmax warps work on tile j, and P V of tile j is
-// issued as soon as its probabilities are in place.  Tensor memory: S0 [0,64), S1 [64,128), P_hi [128,160), P_lo
-// [160,192), O from 192 (64-wide heads: 256 columns, two CTAs per SM) or from 256 (wider heads: 512 columns, one CTA
-// per SM, which is also what their shared memory allows).  Every wait is bounded; one that gives up sets the error
-// word and the CTA still frees its tensor memory.
+// The three stages overlap: S of tile j + 1 is issued as soon as the softmax warps have read S of tile j into registers;
+// the probabilities alternate between two buffers, so the softmax of tile j + 1 does not wait for P V of tile j; and the
+// running maximum is lazy - a row keeps its reference maximum (probabilities may then exceed 1, up to 2^8) until the
+// true maximum has moved by more than 8 in the base-2 domain, so O is rescaled (which does wait for the P V in flight)
+// only a few times per row.  Tensor memory: S [0,64), P0 [64,128), P1 [128,192) (hi | lo halves), O from 192: 256 columns
+// for 64-wide heads (two CTAs per SM), 512 for wider ones (one CTA per SM, which is also what their shared memory
+// allows).  Every wait is bounded; one that gives up sets the error word and the CTA still frees its tensor memory.
 #include <cuda.h>
 
 #include <algorithm>
@@ -34,9 +36,10 @@ constexpr int BN = 64;    // keys per tile = one KV page
 constexpr int kThreads = 192;
 constexpr int KVS = 3;    // K/V stages
 constexpr uint32_t kSpinLimit = 1u << 22;
-// tensor memory: two score buffers, the probabilities (hi | lo), the output
-constexpr uint32_t kColS = 0, kColP = 128;
-template <int HD> struct Tmem { static constexpr uint32_t cols = HD == 64 ? 256 : 512, o = HD == 64 ? 192 : 256; };
+// tensor memory: the scores, two probability buffers (hi | lo each), the output
+constexpr uint32_t kColS = 0, kColP = 64, kColO = 192;
+template <int HD> struct Tmem { static constexpr uint32_t cols = HD == 64 ? 256 : 512; };
+constexpr float kLazy = 8.f;   // a row's reference maximum moves only when the true one exceeds it by 2^8
 
 struct Tc5AttnParams {
     AttnPrefillArgs a;
@@ -143,8 +146,8 @@ __global__ void __launch_bounds__(kThreads) attn_prefill_tc5_kernel(const __grid
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* sQ = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     unsigned char* sKV = sQ + Q_BYTES;
-    __shared__ uint64_t q_full, kv_full[KVS], kv_empty[KVS], s_full[2], p_full, pv_done;
-    constexpr uint32_t kTmemCols = Tmem<HD>::cols, kColO = Tmem<HD>::o;
+    __shared__ uint64_t q_full, kv_full[KVS], kv_empty[KVS], s_full, s_free, p_full[2], pv_done[2];
+    constexpr uint32_t kTmemCols = Tmem<HD>::cols;
     __shared__ uint32_t s_tmem;
     __shared__ int s_err;
 
@@ -161,10 +164,9 @@ __global__ void __launch_bounds__(kThreads) attn_prefill_tc5_kernel(const __grid
     if (tid == 0) {
         mbar_init(&q_full, 1);
         for (int s = 0; s < KVS; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
-        mbar_init(&s_full[0], 1);
-        mbar_init(&s_full[1], 1);
-        mbar_init(&p_full, 4);
-        mbar_init(&pv_done, 1);
+        mbar_init(&s_full, 1);
+        mbar_init(&s_free, 4);
+        for (int s = 0; s < 2; ++s) { mbar_init(&p_full[s], 4); mbar_init(&pv_done[s], 1); }
         s_err = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -199,21 +201,21 @@ __global__ void __launch_bounds__(kThreads) attn_prefill_tc5_kernel(const __grid
             }
         }
     } else if (warp == 1) {
-        // ---------------- MMA issuer: S of the next tile first, then P V of this one once its probabilities are in place
+        // ---------------- MMA issuer: S of the next tile as soon as the score buffer has been read, then P V of this one
         if (lane == 0) {
             bool ok = mbar_wait(&q_full, 0, &s_err);
             const uint32_t q_base = smem_u32(sQ);
-            auto issue_s = [&](int j) {   // S[j & 1] = Q K_j^T
+            auto issue_s = [&](int j) {   // S = Q K_j^T
                 const uint32_t k_base = smem_u32(sKV + size_t(j % KVS) * STAGE);
 #pragma unroll
                 for (int pass = 0; pass < NP; ++pass)
 #pragma unroll
                     for (int k16 = 0; k16 < HD / 16; ++k16) {
                         const uint32_t off = uint32_t(k16 / 4), in = uint32_t((k16 % 4) * 32);
-                        umma_ss(tmem + kColS + uint32_t((j & 1) * BN), desc_kmajor(q_base + (pass * NCH + off) * Q_CHUNK + in),
-                                desc_kmajor(k_base + off * KV_CHUNK + in), Idesc<BN, false>::value, (pass > 0 || k16 > 0) ? 1u : 0u);
+                        umma_ss(tmem + kColS, desc_kmajor(q_base + (pass * NCH + off) * Q_CHUNK + in), desc_kmajor(k_base + off * KV_CHUNK + in),
+                                Idesc<BN, false>::value, (pass > 0 || k16 > 0) ? 1u : 0u);
                     }
-                umma_commit(&s_full[j & 1]);
+                umma_commit(&s_full);
             };
             if (ok && mbar_wait(&kv_full[0], 0, &s_err)) {
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -223,21 +225,21 @@ __global__ void __launch_bounds__(kThreads) attn_prefill_tc5_kernel(const __grid
             }
             for (int j = 0; j < nblk && ok; ++j) {
                 if (j + 1 < nblk) {
-                    // its score buffer was last read for tile j - 1, whose probabilities were awaited one iteration ago
-                    if (!mbar_wait(&kv_full[(j + 1) % KVS], ((j + 1) / KVS) & 1, &s_err)) { ok = false; break; }
+                    if (!mbar_wait(&kv_full[(j + 1) % KVS], ((j + 1) / KVS) & 1, &s_err) || !mbar_wait(&s_free, j & 1, &s_err)) { ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     issue_s(j + 1);
                 }
-                if (!mbar_wait(&p_full, j & 1, &s_err)) { ok = false; break; }
+                if (!mbar_wait(&p_full[j & 1], (j >> 1) & 1, &s_err)) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t v_base = smem_u32(sKV + size_t(j % KVS) * STAGE) + NCH * KV_CHUNK;
+                const uint32_t p_base = tmem + kColP + uint32_t((j & 1) * 64);
 #pragma unroll
                 for (int pass = 0; pass < NP; ++pass)
 #pragma unroll
                     for (int k16 = 0; k16 < BN / 16; ++k16)
-                        umma_ts(tmem + kColO, tmem + kColP + uint32_t(pass * 32 + k16 * 8), desc_mnmajor(v_base + k16 * 2048, KV_CHUNK),
+                        umma_ts(tmem + kColO, p_base + uint32_t(pass * 32 + k16 * 8), desc_mnmajor(v_base + k16 * 2048, KV_CHUNK),
                                 Idesc<HD, true>::value, (j > 0 || pass > 0 || k16 > 0) ? 1u : 0u);
-                umma_commit(&pv_done);
+                umma_commit(&pv_done[j & 1]);
                 umma_commit(&kv_empty[j % KVS]);
             }
             if (!ok) atomicExch(&s_err, 1);
@@ -248,73 +250,78 @@ __global__ void __launch_bounds__(kThreads) attn_prefill_tc5_kernel(const __grid
         const int r = quad * 32 + lane;
         const int pq = a.base_pos + q0 + r;           // position of this thread's query
         const uint32_t lane_addr = tmem + (uint32_t(quad * 32) << 16);
-        float m_run = -INFINITY, l_run = 0.f;
+        float m_ref = -INFINITY, l_run = 0.f;         // reference maximum (base-2 domain, scaled) and the sum relative to it
         bool ok = true;
         for (int j = 0; j < nblk; ++j) {
             const int t0 = (lp_first + j) * BN;
-            if (ok && !mbar_wait(&s_full[j & 1], (j >> 1) & 1, &s_err)) { atomicExch(&s_err, 1); ok = false; }
+            if (ok && !mbar_wait(&s_full, j & 1, &s_err)) { atomicExch(&s_err, 1); ok = false; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             uint32_t sv[2][32];
-            tmem_ld32(lane_addr + kColS + uint32_t((j & 1) * BN), sv[0]);
-            tmem_ld32(lane_addr + kColS + uint32_t((j & 1) * BN) + 32, sv[1]);
+            tmem_ld32(lane_addr + kColS, sv[0]);
+            tmem_ld32(lane_addr + kColS + 32, sv[1]);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&s_free);   // the scores are in registers: the next tile's S may be formed
             // scores stay raw; the maximum and the exponent's argument take the scale (s * c - m * c is one fused
             // multiply-add).  Only a tile that reaches past some row's position (or starts before its window) is masked.
             const bool masked = t0 + BN - 1 > a.base_pos + q0 || (SW && t0 <= a.base_pos + q0 + BM - 1 - a.window);
-            float mx = -INFINITY;
             if (masked) {
 #pragma unroll
                 for (int c = 0; c < 64; ++c) {
                     const int t = t0 + c;
                     const bool seen = t <= pq && (!SW || t > pq - a.window);
-                    const float s = seen ? __uint_as_float(sv[c >> 5][c & 31]) : -INFINITY;
-                    sv[c >> 5][c & 31] = __float_as_uint(s);
-                    mx = fmaxf(mx, s);
+                    if (!seen) sv[c >> 5][c & 31] = 0xff800000u;  // -inf
                 }
-            } else {
-#pragma unroll
-                for (int c = 0; c < 64; ++c) mx = fmaxf(mx, __uint_as_float(sv[c >> 5][c & 31]));
             }
-            const float m_new = fmaxf(m_run, mx * p.scale_log2);       // scale > 0: max(s) * c = max(s * c)
-            const float m_use = m_new == -INFINITY ? 0.f : m_new;   // a row that has seen nothing yet: every p is 0
-            const float alpha = m_run == -INFINITY ? (m_new == -INFINITY ? 1.f : 0.f) : ex2(m_run - m_new);
-            float sum = 0.f;
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four independent chains
+#pragma unroll
+            for (int c = 0; c < 64; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sv[c >> 5][c & 31]));
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;   // scale > 0: max(s) * c = max(s * c)
+            // a row that had seen nothing takes the tile's maximum (its O is still exactly zero); otherwise the reference
+            // moves, and O and l are rescaled, only when the maximum has grown past the slack
+            float alpha = 1.f;
+            if (m_ref == -INFINITY) m_ref = mx;
+            else if (mx > m_ref + kLazy) { alpha = ex2(m_ref - mx); m_ref = mx; }
+            const float m_use = m_ref == -INFINITY ? 0.f : m_ref;   // nothing seen yet: every p is 0
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
             uint32_t ph[32], pl[32];
 #pragma unroll
             for (int c = 0; c < 64; c += 2) {
                 const float p0 = ex2(fmaf(__uint_as_float(sv[c >> 5][c & 31]), p.scale_log2, -m_use));
                 const float p1 = ex2(fmaf(__uint_as_float(sv[c >> 5][(c & 31) + 1]), p.scale_log2, -m_use));
-                sum += p0 + p1;
+                sum4[(c >> 1) & 3] += p0 + p1;
                 ph[c >> 1] = pack_h2(p0, p1);
                 if (PRECISE) pl[c >> 1] = pack_h2_lo(p0, p1, ph[c >> 1]);
             }
-            l_run = l_run * alpha + sum;
-            m_run = m_new;
-            // the previous tile's P V must be complete before P is overwritten and O rescaled
-            if (j > 0) {
-                if (ok && !mbar_wait(&pv_done, (j - 1) & 1, &s_err)) { atomicExch(&s_err, 1); ok = false; }
+            l_run = l_run * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+            // this tile's probability buffer was last read by P V of tile j - 2
+            if (j >= 2 && ok && !mbar_wait(&pv_done[j & 1], ((j >> 1) - 1) & 1, &s_err)) { atomicExch(&s_err, 1); ok = false; }
+            if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+                // O changes scale: every P V issued so far must be complete (the next one waits for this tile's probabilities)
+                if (ok && !mbar_wait(&pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1, &s_err)) { atomicExch(&s_err, 1); ok = false; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                if (__any_sync(0xffffffffu, alpha != 1.f)) {
 #pragma unroll
-                    for (int c0 = 0; c0 < HD; c0 += 32) {
-                        uint32_t o[32];
-                        tmem_ld32(lane_addr + kColO + c0, o);
-                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                for (int c0 = 0; c0 < HD; c0 += 32) {
+                    uint32_t o[32];
+                    tmem_ld32(lane_addr + kColO + c0, o);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                        tmem_st32(lane_addr + kColO + c0, o);
-                    }
+                    for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                    tmem_st32(lane_addr + kColO + c0, o);
                 }
             }
-            tmem_st32(lane_addr + kColP, ph);
-            if (PRECISE) tmem_st32(lane_addr + kColP + 32, pl);
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t p_addr = lane_addr + kColP + uint32_t((j & 1) * 64);
+            tmem_st32(p_addr, ph);
+            if (PRECISE) tmem_st32(p_addr + 32, pl);
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
-            if (lane == 0) mbar_arrive(&p_full);
+            if (lane == 0) mbar_arrive(&p_full[j & 1]);
         }
         // ---------------- the tile's output: O / l
-        if (ok && !mbar_wait(&pv_done, (nblk - 1) & 1, &s_err)) { atomicExch(&s_err, 1); ok = false; }
+        if (ok && !mbar_wait(&pv_done[(nblk - 1) & 1], ((nblk - 1) >> 1) & 1, &s_err)) { atomicExch(&s_err, 1); ok = false; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
         const int qr = q0 + r;
