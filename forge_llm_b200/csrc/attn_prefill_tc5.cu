@@ -153,8 +153,10 @@ __global__ void __launch_bounds__(kThreads) attn_prefill_tc5_kernel(const __grid
 
     const AttnPrefillArgs& a = p.a;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int tile = int(gridDim.x) - 1 - int(blockIdx.x);  // the tiles with the most keys first
-    const int h = blockIdx.y, kvh = h / (a.nq / a.nkv);
+    // CTAs in the order of their work: all heads of the last query tile (the most key tiles) first, the first tile last
+    const int linear = int(blockIdx.x + gridDim.x * blockIdx.y);
+    const int h_ = linear % a.nq, tile = int(gridDim.x) - 1 - linear / a.nq;
+    const int h = h_, kvh = h / (a.nq / a.nkv);
     const int q0 = tile * BM;
     const int q_last = min(q0 + BM, a.m) - 1;
     const int lp_last = (a.base_pos + q_last) / BN;

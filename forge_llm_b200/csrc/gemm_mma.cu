@@ -213,12 +213,11 @@ int32_t gemm_f16a_mma(float* out, const __half* A, const __half* Alo, const QWei
 }
 
 int32_t gemm_f16a(float* out, const __half* A, const __half* Alo, const QWeight& w, int m, const float* resid, int* err, cudaStream_t st) {
-    static const bool force_mma = [] { const char* e = getenv("FORGE_B200_GEMM"); return e && !strcmp(e, "mma"); }();
     if (w.quant == FORGE_KQ_SOA) {  // K-quant rows exist in the tcgen05 kernel only (K is a multiple of 256 there)
         if (!gemm_tc5_supported(w)) { set_error("gemm: K-quant rows need K to be a multiple of 64"); return FORGE_ERR_SHAPE; }
         return gemm_tc5(out, A, Alo, w, m, resid, err, st);
     }
-    if (!force_mma && gemm_tc5_supported(w)) return gemm_tc5(out, A, Alo, w, m, resid, err, st);
+    if (gemm_tc5_supported(w)) return gemm_tc5(out, A, Alo, w, m, resid, err, st);
     return gemm_f16a_mma(out, A, Alo, w, m, resid, st);
 }
 

@@ -445,8 +445,6 @@ int32_t gemm_tc5(float* out, const __half* A, const __half* Alo, const QWeight& 
         const double cost = double((ctas + sms - 1) / sms) * (0.55 + 0.45 * cand / 256.0);
         if (cost < best_cost - 1e-9) { best_cost = cost; best = cand; }
     }
-    static const int force_nt = [] { const char* e = getenv("FORGE_B200_NT"); return e ? atoi(e) : 0; }();  // experiments
-    if (force_nt == 128 || force_nt == 192 || force_nt == 256) best = force_nt;
 #define FORGE_TS(Q)                                                                  \
     do {                                                                             \
         if (split) {                                                                 \

@@ -262,8 +262,6 @@ int gemv_slices(const QTiled& w, const GemvSplit& sp, int sms, int batch) {
 // CTA-level reduction per unit) streams fastest but comes in coarse units; it is used when whole rounds of 128-row
 // bands keep at least 80 % of the SMs busy.  Otherwise one tile per band (16-row units, all warps share the tile).
 int gemv_band_tiles(int N, int sms) {
-    static const int force = [] { const char* e = getenv("FORGE_B200_BAND_TILES"); return e ? atoi(e) : 0; }();
-    if (force == 1 || force == core::kBandTiles) return force;
     const int wide = (N + 127) / 128;
     const int rounds = (wide + sms - 1) / sms;
     return (5 * wide >= 4 * rounds * sms) ? core::kBandTiles : 1;

@@ -259,7 +259,7 @@ def test_attention_flash_batch(L, oracle, hd, nq, nkv, m, base):
     _sync()
     got = out.cpu().numpy()
     assert np.isfinite(got).all()  # NaN padding behind the causal limit must never leak
-    assert rel_l2(got, ref) < 5e-4  # q and p are fp16 operands of the tensor-core products
+    assert rel_l2(got, ref) < 2e-5  # q and p enter the tensor-core products as fp16 hi + lo pairs
 
 
 def test_kv_append_rounds_to_fp16(L):

@@ -96,7 +96,7 @@ def test_cuda_attention_sliding_batch(oracle, hd, nq, nkv, m, base, window):
     torch.cuda.synchronize()
     got = out.cpu().numpy()
     assert np.isfinite(got).all()
-    assert rel_l2(got, ref) < 5e-4  # q and p are fp16 operands of the tensor-core products
+    assert rel_l2(got, ref) < 2e-5  # q and p enter the tensor-core products as fp16 hi + lo pairs
 
 
 @pytest.mark.gpu
