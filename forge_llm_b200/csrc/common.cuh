@@ -264,8 +264,10 @@ int32_t gemm_f16a(float* out, const __half* A, const __half* Alo, const QWeight&
 int32_t gemm_f16a_mma(float* out, const __half* A, const __half* Alo, const QWeight& w, int m, const float* resid, cudaStream_t st);
 bool gemm_tc5_supported(const QWeight& w);
 // ksplit > 1: K slice z leaves its partial product (no residual) at out + z * part_stride; the caller adds the slices
+// act_hi != null (gate/up product, rows 2j = gate_j, 2j + 1 = up_j, one K slice): the epilogue stores SiLU(gate) * up as
+// fp16 hi (+ lo) rows [m][N / 2] and `out` is not written
 int32_t gemm_tc5(float* out, const __half* A, const __half* Alo, const QWeight& w, int m, const float* resid, int* err, cudaStream_t st,
-                 int ksplit = 1, size_t part_stride = 0);
+                 int ksplit = 1, size_t part_stride = 0, __half* act_hi = nullptr, __half* act_lo = nullptr);
 int gemm_tc5_ksplit(const QWeight& w);
 
 }  // namespace forge

@@ -84,6 +84,9 @@ struct Tc5Params {
     int* err;
     int ksplit;            // K slices (grid.z); slice z leaves its partial product at out + z * part_stride
     size_t part_stride;
+    // gate/up product (weight rows 2j = gate_j, 2j + 1 = up_j): when act_hi is set the epilogue stores
+    // SiLU(gate_j) * up_j as fp16 hi (+ lo) into act[token][N / 2] instead of the f32 rows
+    __half* act_hi; __half* act_lo;
 };
 
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
@@ -327,7 +330,25 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_ts_kernel(const __grid_const
                   "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
                 : "r"(taddr) : "memory");
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-            if (col_n < p.N) {
+            if (p.act_hi) {
+                // neighbouring lanes hold gate_j and up_j of the same tokens: the even lane takes the first sixteen
+                // tokens of the chunk, the odd lane the other sixteen, each getting the partner's half by shuffle
+                const bool even = !(lane & 1);
+                const size_t half_n = size_t(p.N) / 2;
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const uint32_t got = __shfl_xor_sync(0xffffffffu, even ? v[16 + j] : v[j], 1);
+                    const float g = __uint_as_float(even ? v[j] : got), u = __uint_as_float(even ? got : v[16 + j]);
+                    const int row = m0 + c0 + (even ? j : 16 + j);
+                    if (col_n < p.N && row < p.m) {
+                        const float x = (g / (1.0f + expf(-g))) * u;
+                        const __half hx = __float2half_rn(x);
+                        const size_t off = size_t(row) * half_n + size_t(col_n >> 1);
+                        p.act_hi[off] = hx;
+                        if (p.act_lo) p.act_lo[off] = __float2half_rn(x - __half2float(hx));
+                    }
+                }
+            } else if (col_n < p.N) {
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
                     const int row = m0 + c0 + j;
@@ -424,11 +445,12 @@ bool gemm_tc5_supported(const QWeight& w) { return w.K % BK == 0 && w.K >= BK; }
 int gemm_tc5_ksplit(const QWeight& w) { return std::max(1, std::min(4, w.K / 1024)); }
 
 int32_t gemm_tc5(float* out, const __half* A, const __half* Alo, const QWeight& w, int m, const float* resid, int* err, cudaStream_t st,
-                 int ksplit, size_t part_stride) {
+                 int ksplit, size_t part_stride, __half* act_hi, __half* act_lo) {
     if (m <= 0) return FORGE_OK;
     if (!gemm_tc5_supported(w)) { set_error("tcgen05 gemm: K=%d must be a multiple of %d", w.K, BK); return FORGE_ERR_SHAPE; }
-    if (ksplit < 1 || ksplit > w.K / BK || (ksplit > 1 && resid)) { set_error("tcgen05 gemm: bad K split"); return FORGE_ERR_INVALID_ARG; }
-    Tc5Params p{out, resid, w.qs, w.d, w.sf, m, w.N, w.K, err, ksplit, part_stride};
+    if (ksplit < 1 || ksplit > w.K / BK || (ksplit > 1 && (resid || act_hi))) { set_error("tcgen05 gemm: bad K split"); return FORGE_ERR_INVALID_ARG; }
+    if (act_hi && ((w.N & 1) || resid)) { set_error("tcgen05 gemm: the SiLU epilogue needs gate/up row pairs and no residual"); return FORGE_ERR_INVALID_ARG; }
+    Tc5Params p{out, resid, w.qs, w.d, w.sf, m, w.N, w.K, err, ksplit, part_stride, act_hi, act_lo};
     const bool split = Alo != nullptr;
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);

@@ -297,6 +297,13 @@ int32_t row_sliced_gemm_norm(ForgeModel* m, const QWeight& w, const __half* a, c
     if (next_norm) FORGE_TRY(rms_norm_f16(m->p_normed, nlo, m->p_hidden, next_norm, n, m->h, m->cfg.rms_norm_eps, st));
     return FORGE_OK;
 }
+// act = SiLU(gate) * up of the normed rows, as fp16 hi (+ lo): the GEMM's own epilogue where the tcgen05 kernel runs
+// (fusion pattern gate/up + SiLU, forgellm-optimizer/src/fusion.rs:12-27), else the product followed by the element-wise pass
+int32_t gateup_silu(ForgeModel* m, const QWeight& w, const __half* nlo, __half* flo, int n, cudaStream_t st) {
+    if (gemm_tc5_supported(w)) return gemm_tc5(nullptr, m->p_normed, nlo, w, n, nullptr, m->d_err, st, 1, 0, m->p_act16, flo);
+    FORGE_TRY(gemm_f16a(m->p_gu, m->p_normed, nlo, w, n, nullptr, m->d_err, st));
+    return silu_mul_f16(m->p_act16, flo, m->p_gu, n, m->ff, st);
+}
 int32_t row_sliced_gemv(ForgeModel* m, const QTiled& w, GemvArgs a, int batch, cudaStream_t st) {
     if (m->cfg.tp_world == 1) return gemv_tc(w, EPI_RESID, a, m->split, m->d_err, st);
     a.out = m->d_part; a.resid = nullptr;
@@ -360,8 +367,7 @@ int32_t prefill_seq(ForgeModel* m, ForgeKV* kv, int seq, const uint32_t* tokens_
         if (L.o.quant == FORGE_KQ_SOA) FORGE_TRY(q8_round_f16(m->p_attn16, alo, size_t(n) * m->qk, st));
         FORGE_TRY(row_sliced_gemm_norm(m, L.o, m->p_attn16, alo, n, L.ffn_norm, nlo, st));
         if (L.gateup.quant == FORGE_KQ_SOA) FORGE_TRY(q8_round_f16(m->p_normed, nlo, size_t(n) * m->h, st));
-        FORGE_TRY(gemm_f16a(m->p_gu, m->p_normed, nlo, L.gateup, n, nullptr, m->d_err, st));
-        FORGE_TRY(silu_mul_f16(m->p_act16, flo, m->p_gu, n, m->ff, st));
+        FORGE_TRY(gateup_silu(m, L.gateup, nlo, flo, n, st));
         if (L.down.quant == FORGE_KQ_SOA) FORGE_TRY(q8_round_f16(m->p_act16, flo, size_t(n) * m->ff, st));
         FORGE_TRY(row_sliced_gemm_norm(m, L.down, m->p_act16, flo, n, l + 1 < c.num_layers ? m->layers[l + 1].attn_norm : nullptr, nlo, st));
         if (m->trace_on)
@@ -488,8 +494,7 @@ int32_t decode_launches_gemm(ForgeModel* m, ForgeKV* kv, int batch, bool greedy,
         FORGE_TRY(attn_decode(da, st));
         FORGE_TRY(f32_to_f16(m->p_attn16, alo, m->d_attn, size_t(n) * m->qk, st));
         FORGE_TRY(row_sliced_gemm_norm(m, L.o, m->p_attn16, alo, n, L.ffn_norm, nlo, st));
-        FORGE_TRY(gemm_f16a(m->p_gu, m->p_normed, nlo, L.gateup, n, nullptr, m->d_err, st));
-        FORGE_TRY(silu_mul_f16(m->p_act16, flo, m->p_gu, n, m->ff, st));
+        FORGE_TRY(gateup_silu(m, L.gateup, nlo, flo, n, st));
         FORGE_TRY(row_sliced_gemm_norm(m, L.down, m->p_act16, flo, n, l + 1 < c.num_layers ? m->layers[l + 1].attn_norm : m->final_norm, nlo, st));
     }
     FORGE_TRY(gemm_f16a(m->d_logits, m->p_normed, nlo, m->lm_head, n, nullptr, m->d_err, st));
