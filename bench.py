@@ -485,11 +485,9 @@ def run_tp(args, rank, world, local_rank, dist, barrier, reduce_max, peaks):
         dist.broadcast(uid, 0)
         m = runtime.Model(c, blob, device=local_rank, tp_rank=rank, tp_world=world)
         m.tp_init(uid.cpu().numpy())
-        if peer_sums:   # batch-1 decode sums over peer memory (NVLink stores from the GEMV epilogue)
-            mine_h = torch.from_numpy(m.tp_exchange_handle()).cuda()
-            all_h = [torch.empty_like(mine_h) for _ in range(world)]
-            dist.all_gather(all_h, mine_h)
-            m.tp_exchange_attach(torch.cat(all_h).cpu().numpy())
+        if peer_sums:   # decode sums over peer memory (NVLink stores); the handles travel over a host channel with a time limit
+            from forge_llm_b200 import parallel
+            m.tp_exchange_attach(parallel.gather_exchange_handles(m.tp_exchange_handle(), world))
             dist.barrier()
         return m
 

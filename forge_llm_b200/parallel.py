@@ -48,3 +48,31 @@ def tp_plan(cfg: dict, rank: int, world: int) -> TpPlan:
     return TpPlan(range(rank * qk, (rank + 1) * qk), range(rank * kv, (rank + 1) * kv), range(rank * f, (rank + 1) * f),
                   range(rank * qk // 32, (rank + 1) * qk // 32), range(rank * f // 32, (rank + 1) * f // 32),
                   nh // world, nkv // world)
+
+
+class PeerTimeout(RuntimeError):
+    """A rank did not contribute to a host-side exchange within the limit."""
+
+
+def gather_exchange_handles(mine, world: int, timeout_s: float = 60.0):
+    """All ranks' exchange-buffer handles, in rank order (what ``forge_model_tp_exchange_attach`` takes).
+
+    The handles travel over a gloo group created for this one exchange with ``timeout_s`` as its limit: if a
+    rank never posts its handle (it died, or never reached this point) the others get ``PeerTimeout`` instead of
+    waiting for ever, and nothing has touched a GPU yet.  Needs an initialised ``torch.distributed``.
+    """
+    import datetime
+
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    group = dist.new_group(backend="gloo", timeout=datetime.timedelta(seconds=timeout_s))
+    local = torch.from_numpy(np.ascontiguousarray(mine, dtype=np.uint8).copy())
+    parts = [torch.empty_like(local) for _ in range(world)]
+    try:
+        dist.all_gather(parts, local, group=group)
+    except RuntimeError as e:  # gloo reports a missing peer as a timed-out / failed collective
+        raise PeerTimeout(f"a rank did not post its exchange handle within {timeout_s} s: {e}") from e
+    return torch.cat(parts).numpy()
+

@@ -100,3 +100,54 @@ def _rank_main(rank: int, world: int, port: int, quant: int):
 def test_tensor_parallel_cut_on_two_cpu_ranks(quant, oracle):
     import torch.multiprocessing as mp
     mp.spawn(_rank_main, args=(2, _free_port(), quant), nprocs=2, join=True)
+
+
+def _handle_rank(rank: int, world: int, port: int, posts: bool, out):
+    import datetime
+    import time
+
+    import torch.distributed as dist
+    sys.path.insert(0, ROOT)
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world,
+                            timeout=datetime.timedelta(seconds=30))
+    mine = np.full(64, rank + 1, np.uint8)
+    try:
+        if rank == 1 and not posts:
+            # this rank joins the group (group creation is collective) but never contributes its handle
+            import torch
+            dist.new_group(backend="gloo", timeout=datetime.timedelta(seconds=1.5))
+            time.sleep(4.0)
+            out.put((rank, "silent"))
+            return
+        try:
+            got = parallel.gather_exchange_handles(mine, world, timeout_s=1.5)
+            out.put((rank, got.tolist()))
+        except parallel.PeerTimeout:
+            out.put((rank, "timeout"))
+    finally:
+        try:
+            dist.destroy_process_group()
+        except Exception:
+            pass
+
+
+@pytest.mark.parametrize("posts", [True, False])
+def test_exchange_handles_gather_and_silent_rank(posts):
+    """Every rank gets all handles in rank order; a rank that never posts makes the others fail with PeerTimeout
+    within the limit instead of waiting (the failure is made on the host: no GPU is involved)."""
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_handle_rank, args=(r, 2, port, posts, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = dict(out.get(timeout=60) for _ in range(2))
+    for p in procs:
+        p.join(timeout=60)
+    if posts:
+        want = [1] * 64 + [2] * 64
+        assert got[0] == want and got[1] == want
+    else:
+        assert got[0] == "timeout" and got[1] == "silent"
+

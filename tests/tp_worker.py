@@ -30,10 +30,8 @@ def main():
     gm = runtime.Model(c, blob, device=local, tp_rank=rank, tp_world=world)
     gm.tp_init(uid.numpy())
     if len(sys.argv) > 6 and sys.argv[6] == "peer":  # decode sums over peer memory instead of the library all-reduce
-        mine_h = torch.from_numpy(gm.tp_exchange_handle())
-        all_h = [torch.empty_like(mine_h) for _ in range(world)]
-        dist.all_gather(all_h, mine_h)
-        gm.tp_exchange_attach(torch.cat(all_h).numpy())
+        from forge_llm_b200 import parallel
+        gm.tp_exchange_attach(parallel.gather_exchange_handles(gm.tp_exchange_handle(), world))
         dist.barrier()
     kv = gm.new_cache(max_seq=n_prompt + n_new + 8)
     lg = gm.forward_prefill(toks, kv)
