@@ -349,13 +349,18 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_ts_kernel(const __grid_const
                     }
                 }
             } else if (col_n < p.N) {
+                // the residual may be the output buffer itself: all of its loads are issued before the first store,
+                // otherwise every load would have to wait for the store in front of it (one memory round trip each)
+                float rv[32];
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
                     const int row = m0 + c0 + j;
-                    if (row < p.m) {
-                        const size_t off = size_t(row) * p.N + col_n;
-                        outp[off] = (p.resid ? p.resid[off] : 0.f) + __uint_as_float(v[j]);
-                    }
+                    rv[j] = (p.resid && row < p.m) ? p.resid[size_t(row) * p.N + col_n] : 0.f;
+                }
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const int row = m0 + c0 + j;
+                    if (row < p.m) outp[size_t(row) * p.N + col_n] = rv[j] + __uint_as_float(v[j]);
                 }
             }
         }
