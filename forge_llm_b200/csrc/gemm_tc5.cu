@@ -121,6 +121,17 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16
                    "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]) : "memory");
 }
 
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr) : "memory");
+}
+
 // 32 consecutive weights of one row (one quantisation block) -> 16 + 16 packed fp16 pairs (hi, lo)
 template <int QUANT, bool SPLIT>
 __device__ __forceinline__ void dequant_block(const uint32_t* cur, __half2 d2, uint32_t (&hi)[16], uint32_t (&lo)[16]) {
@@ -374,6 +385,302 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_ts_kernel(const __grid_const
     if (tid == 0 && s_err && p.err) atomicExch(p.err, 1);
 }
 
+// ------------------------------------------------------------------------------------------------
+// The same product for a few rows (m <= 32: batched decode steps, short prompts), bound by the weight stream instead of
+// the tensor pipe.  Differences from the kernel above:
+//   * the A operand in tensor memory holds the INTEGER weights (exact in fp16), one copy, no block scale;
+//   * the rows' hi and lo fp16 parts are the two halves of ONE B operand (MMA N = 2 * NT columns), so a K step is one
+//     pass of two K = 16 products per 32-column block;
+//   * every block's 128 x 2 NT sums are read out of tensor memory by four scale warps (tcgen05.ld, one weight row per
+//     thread) and added into register accumulators with the row's f16 block scale in f32;
+//   * every hand-off covers a GROUP of G K steps (rows by TMA, weights from the dequantising warps, block sums to the
+//     scale warps and back): a query of an mbarrier costs ~150 clocks even when its phase is complete (measured; a
+//     tcgen05.mma or commit issues in ~45), so the single issuing thread must meet few barriers per K step.
+// The products are exact in the weights and carry the rows to 22 bits; a tensor-memory chain is two products long.
+//   * the quantised bytes reach the dequantising threads through shared memory: 128 rows x 128 bytes per bulk tensor copy
+//     (SWIZZLE_128B, so a thread reads its row's 16-byte pieces without bank conflicts), four K steps per stage - a
+//     thread-per-row read from global memory fetches one sector per request and cannot keep HBM busy.
+// Warps (480 threads): 0 TMA for the rows, 1 MMA issue, 2..9 dequantise (one block of one row per thread and K step),
+// 10..13 scale + epilogue, 14 TMA for the weights.
+constexpr int kSmallThreads = 480;
+constexpr int kSuper = 4;   // K steps per weight stage
+
+// several barriers at once: the queries are issued together, so their latencies overlap
+__device__ __forceinline__ bool mbar_wait3(uint64_t* a, uint32_t pa, uint64_t* b, uint32_t pb, uint64_t* c, uint32_t pc, const volatile int* cta_err) {
+    const uint32_t aa = smem_u32(a), ab = smem_u32(b), ac = c ? smem_u32(c) : 0;
+    uint32_t da = 0, db = 0, dc = c ? 0u : 1u;
+    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+        if ((i & 1023u) == 1023u && *cta_err) return false;
+        uint32_t ta = 1, tb = 1, tc = 1;
+        if (!da) asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}" : "=r"(ta) : "r"(aa), "r"(pa) : "memory");
+        if (!db) asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}" : "=r"(tb) : "r"(ab), "r"(pb) : "memory");
+        if (!dc) asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}" : "=r"(tc) : "r"(ac), "r"(pc) : "memory");
+        da |= ta; db |= tb; dc |= tc;
+        if (da && db && dc) return true;
+    }
+    return false;
+}
+
+template <int QUANT>
+__device__ __forceinline__ void raw_block(const uint32_t* cur, uint32_t (&out)[16]) {
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t sel = (i & 1) ? 0x4342u : 0x4140u;
+            if (QUANT == FORGE_Q8_0) {
+                const uint32_t word = cur[2 * c + (i >> 1)];
+                out[4 * c + i] = as_u32(__hsub2(as_h2(prmt(word ^ 0x80808080u, 0x64646464u, sel)), __float2half2_rn(1152.f)));
+            } else {
+                const uint32_t word = cur[2 * (c & 1) + (i >> 1)];
+                const uint32_t two = prmt(word, 0u, sel) >> ((c >> 1) * 4);
+                out[4 * c + i] = as_u32(__hsub2(as_h2((two & 0x000F000Fu) | 0x64006400u), __float2half2_rn(1032.f)));
+            }
+        }
+    }
+}
+
+// NT rows (16 or 32); G = K steps per hand-off group
+template <int QUANT, int NT>
+__global__ void __launch_bounds__(kSmallThreads, 1) gemm_small_kernel(const __grid_constant__ CUtensorMap map_hi,
+                                                                      const __grid_constant__ CUtensorMap map_lo,
+                                                                      const __grid_constant__ CUtensorMap map_w, Tc5Params p) {
+    constexpr int NC = 2 * NT;                   // MMA N: hi columns, then lo columns
+    constexpr int G = NT == 16 ? 2 : 1;          // K steps per group
+    constexpr int BG = 2 * G;                    // 32-column blocks per group
+    constexpr int X_TILE = NT * BK * 2;          // bytes of one part (hi or lo) of one K step
+    constexpr int X_STAGE = G * 2 * X_TILE;
+    constexpr int XS = 4;                        // row stages (groups)
+    constexpr int W_COLS = BK / 2;               // 32-bit columns of one K step of weights
+    constexpr int WG = 256 / (G * W_COLS);       // weight stages (groups) in tensor memory
+    constexpr uint32_t kTmemCols = 512, kWBase = 256;   // two sets of BG block-sum buffers in [0, 256), weights from 256
+    static_assert(2 * BG * NC <= 256 && NC % 16 == 0 && WG >= 2, "tensor memory budget");
+    constexpr int Q_BOXES = QUANT == FORGE_Q4_0 ? 1 : 2;   // 128-byte boxes per row and weight stage (256 columns)
+    constexpr int Q_STAGE = Q_BOXES * 128 * 128;
+    constexpr int QS = QUANT == FORGE_Q4_0 ? 6 : 4;        // weight stages in shared memory
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char* sX = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    unsigned char* sQ = sX + XS * X_STAGE;
+    __shared__ uint64_t full_x[XS], empty_x[XS], full_w[WG], empty_w[WG], d_full[2], d_free[2], full_q[QS], empty_q[QS];
+    __shared__ uint32_t s_tmem;
+    __shared__ int s_err;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n0 = blockIdx.x * 128;
+    const int nk_all = p.K / BK;
+    const int kt_begin = (nk_all * int(blockIdx.z)) / p.ksplit;
+    const int nk = (nk_all * (int(blockIdx.z) + 1)) / p.ksplit - kt_begin;
+    const int ng = (nk + G - 1) / G;             // groups; the K steps of the last one beyond nk carry zero scales
+
+    if (tid == 0) {
+        for (int s = 0; s < XS; ++s) { mbar_init(&full_x[s], 1); mbar_init(&empty_x[s], 1); }
+        for (int s = 0; s < WG; ++s) { mbar_init(&full_w[s], 8); mbar_init(&empty_w[s], 1); }
+        for (int s = 0; s < 2; ++s) { mbar_init(&d_full[s], 1); mbar_init(&d_free[s], 4); }
+        for (int s = 0; s < QS; ++s) { mbar_init(&full_q[s], 1); mbar_init(&empty_q[s], 8); }
+        s_err = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem)), "n"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = s_tmem;
+    const int nss = (ng * G + kSuper - 1) / kSuper;   // weight stages of this CTA
+
+    if (warp == 14) {
+        // ---------------- TMA producer for the weights: 128 rows x 256 columns of quantised bytes per stage
+        if (lane == 0) {
+            const int bytes_per_col_num = QUANT == FORGE_Q4_0 ? 1 : 2;   // bytes per column, in halves
+            for (int ss = 0; ss < nss; ++ss) {
+                const int s = ss % QS, use = ss / QS;
+                if (use > 0 && !mbar_wait(&empty_q[s], (use - 1) & 1, &s_err)) { atomicExch(&s_err, 1); break; }
+                mbar_expect_tx(&full_q[s], uint32_t(Q_STAGE));
+                const int x0 = ((kt_begin + ss * kSuper) * BK * bytes_per_col_num) / 2;   // byte offset in the row
+#pragma unroll
+                for (int b = 0; b < Q_BOXES; ++b) tma_load_2d(sQ + size_t(s) * Q_STAGE + b * 16384, &map_w, x0 + b * 128, n0, &full_q[s]);
+            }
+        }
+    } else if (warp == 0) {
+        // ---------------- TMA producer: per group, the rows' hi and lo tiles of its K steps (columns past K read as zero)
+        if (lane == 0) {
+            for (int gi = 0; gi < ng; ++gi) {
+                const int s = gi % XS, use = gi / XS;
+                if (use > 0 && !mbar_wait(&empty_x[s], (use - 1) & 1, &s_err)) { atomicExch(&s_err, 1); break; }
+                mbar_expect_tx(&full_x[s], uint32_t(X_STAGE));
+                unsigned char* dst = sX + size_t(s) * X_STAGE;
+#pragma unroll
+                for (int g = 0; g < G; ++g) {
+                    tma_load_2d(dst + g * 2 * X_TILE, &map_hi, (kt_begin + gi * G + g) * BK, 0, &full_x[s]);
+                    tma_load_2d(dst + g * 2 * X_TILE + X_TILE, &map_lo, (kt_begin + gi * G + g) * BK, 0, &full_x[s]);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer: per group one meeting with its three partners, then 4 G products and three commits
+        if (lane == 0) {
+            for (int gi = 0; gi < ng; ++gi) {
+                const int sx = gi % XS, sw = gi % WG, ds = gi & 1;
+                if (!mbar_wait3(&full_x[sx], (gi / XS) & 1, &full_w[sw], (gi / WG) & 1, gi >= 2 ? &d_free[ds] : nullptr, ((gi >> 1) - 1) & 1, &s_err)) {
+                    atomicExch(&s_err, 1);
+                    break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint64_t xd = umma_desc(smem_u32(sX + size_t(sx) * X_STAGE));
+                const uint32_t w_base = tmem + kWBase + uint32_t(sw * G * W_COLS);
+                const uint32_t d_base = tmem + uint32_t(ds * BG * NC);
+#pragma unroll
+                for (int g = 0; g < G; ++g)
+#pragma unroll
+                    for (int k16 = 0; k16 < 4; ++k16)   // block k16 / 2 of this K step
+                        umma_ts_f16<NC>(d_base + uint32_t((2 * g + (k16 >> 1)) * NC), w_base + uint32_t(g * W_COLS + k16 * 8),
+                                        xd + uint64_t((g * 2 * X_TILE + k16 * 32) >> 4), (k16 & 1) ? 1u : 0u);
+                umma_commit(&d_full[ds]);
+                umma_commit(&empty_x[sx]);
+                umma_commit(&empty_w[sw]);
+            }
+        }
+    } else if (warp < 10) {
+        // ---------------- dequantise (warps 2..9): integer weights as fp16 into tensor memory, lane = weight row
+        const int quad = warp & 3, blk = (warp - 2) >> 2;
+        const int r = quad * 32 + lane;
+        const int n = n0 + r;
+        const bool n_ok = n < p.N;
+        constexpr int QV = QUANT == FORGE_Q4_0 ? 1 : 2;   // 16-byte pieces per block
+        constexpr int kUnroll = 8;
+        static_assert(kUnroll % G == 0 && (WG * G) % kUnroll == 0 && kUnroll % kSuper == 0, "one unrolled round covers whole groups and stages");
+        (void)n; (void)n_ok;
+        bool ok = true;
+        const uint32_t lane_base = tmem + (uint32_t(quad * 32) << 16) + kWBase + uint32_t(blk * 16);
+        const uint32_t sw7 = uint32_t(r & 7);
+        for (int kt0 = 0; kt0 < ng * G; kt0 += kUnroll) {
+#pragma unroll
+            for (int j = 0; j < kUnroll; ++j) {
+                const int kt = kt0 + j;
+                if (kt >= ng * G) break;
+                const int gi = kt / G, g = kt % G, sw = gi % WG;
+                const int ss = kt / kSuper, qi = kt % kSuper, sq = ss % QS;
+                if (qi == 0 && ok && !mbar_wait(&full_q[sq], (ss / QS) & 1, &s_err)) { atomicExch(&s_err, 1); ok = false; }
+                // this thread's block: 16-byte pieces of its row, un-swizzled (piece index ^ (row & 7))
+                uint32_t cur[4 * QV];
+                const unsigned char* stage = sQ + size_t(sq) * Q_STAGE;
+#pragma unroll
+                for (int i = 0; i < QV; ++i) {
+                    const int piece = QUANT == FORGE_Q4_0 ? qi * 2 + blk : ((qi & 1) * 2 + blk) * 2 + i;   // within the row's 128 bytes
+                    const int box = QUANT == FORGE_Q4_0 ? 0 : qi >> 1;
+                    const uint4 v = *reinterpret_cast<const uint4*>(stage + box * 16384 + r * 128 + ((uint32_t(piece) ^ sw7) << 4));
+                    cur[4 * i] = v.x; cur[4 * i + 1] = v.y; cur[4 * i + 2] = v.z; cur[4 * i + 3] = v.w;
+                }
+                if (qi == kSuper - 1 || kt == ng * G - 1) {   // the stage's bytes are in registers
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&empty_q[sq]);
+                }
+                uint32_t w16[16];
+                raw_block<QUANT>(cur, w16);
+                if (g == 0) {   // first K step of a group: its stage must have been read by the products that used it last
+                    const int use = gi / WG;
+                    if (ok && use > 0 && !mbar_wait(&empty_w[sw], (use - 1) & 1, &s_err)) { atomicExch(&s_err, 1); ok = false; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                }
+                tmem_st16(lane_base + uint32_t((sw * G + g) * W_COLS), w16);
+                if (g == G - 1) {   // the group is complete
+                    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&full_w[sw]);
+                }
+            }
+        }
+    } else {
+        // ---------------- scale warps (10..13): block sums out of tensor memory, times the row's block scale, in f32
+        const int quad = warp & 3;
+        const int r = quad * 32 + lane;
+        const int n = n0 + r;
+        const bool n_ok = n < p.N;
+        const __half2* dsrc = reinterpret_cast<const __half2*>(p.d + size_t(n_ok ? n : 0) * (p.K / 32) + 2 * kt_begin);   // two scales per K step
+        const uint32_t lane_addr = tmem + (uint32_t(quad * 32) << 16);
+        float acc[NC];
+#pragma unroll
+        for (int c = 0; c < NC; ++c) acc[c] = 0.f;
+        constexpr int kAhead = 4;                // groups of scales in flight
+        __half2 dq[kAhead][G];
+        auto dload = [&](int gi, int slot) {
+#pragma unroll
+            for (int g = 0; g < G; ++g) dq[slot][g] = (n_ok && gi * G + g < nk) ? dsrc[gi * G + g] : __float2half2_rn(0.f);
+        };
+#pragma unroll
+        for (int j = 0; j < kAhead; ++j) dload(j, j);
+        bool ok = true;
+        for (int g0 = 0; g0 < ng; g0 += kAhead) {
+#pragma unroll
+            for (int j = 0; j < kAhead; ++j) {
+                const int gi = g0 + j;
+                if (gi >= ng) break;
+                const int ds = gi & 1;
+                float dsc[BG];
+#pragma unroll
+                for (int g = 0; g < G; ++g) { const float2 d2 = __half22float2(dq[j][g]); dsc[2 * g] = d2.x; dsc[2 * g + 1] = d2.y; }
+                dload(gi + kAhead, j);
+                if (ok && !mbar_wait(&d_full[ds], (gi >> 1) & 1, &s_err)) { atomicExch(&s_err, 1); ok = false; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+                for (int b = 0; b < BG; ++b) {
+#pragma unroll
+                    for (int c0 = 0; c0 < NC; c0 += 32) {
+                        uint32_t v[32];
+                        tmem_ld32(lane_addr + uint32_t((ds * BG + b) * NC + c0), v);
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                        if (b == BG - 1 && c0 + 32 >= NC) {   // the group's sums are in registers: its buffers may be overwritten
+                            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(&d_free[ds]);
+                        }
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) acc[c0 + i] = fmaf(dsc[b], __uint_as_float(v[i]), acc[c0 + i]);
+                    }
+                }
+            }
+        }
+        // ---------------- epilogue: row n, tokens 0..m-1; hi and lo columns added
+        float* const outp = p.out + size_t(blockIdx.z) * p.part_stride;
+        if (p.act_hi) {
+            // neighbouring lanes hold gate_j and up_j: the even lane takes the first half of the tokens, the odd lane the rest
+            const bool even = !(lane & 1);
+            const size_t half_n = size_t(p.N) / 2;
+#pragma unroll
+            for (int j = 0; j < NT / 2; ++j) {
+                const float first = acc[j] + acc[NT + j], second = acc[NT / 2 + j] + acc[NT + NT / 2 + j];   // tokens j and NT/2 + j
+                const float got = __shfl_xor_sync(0xffffffffu, even ? second : first, 1);
+                const float g = even ? first : got, u = even ? got : second;
+                const int row = even ? j : NT / 2 + j;
+                if (n_ok && row < p.m) {
+                    const float x = (g / (1.0f + expf(-g))) * u;
+                    const __half hx = __float2half_rn(x);
+                    const size_t off = size_t(row) * half_n + size_t(n >> 1);
+                    p.act_hi[off] = hx;
+                    if (p.act_lo) p.act_lo[off] = __float2half_rn(x - __half2float(hx));
+                }
+            }
+        } else if (n_ok) {
+            float rv[NT];
+#pragma unroll
+            for (int j = 0; j < NT; ++j) rv[j] = (p.resid && j < p.m) ? p.resid[size_t(j) * p.N + n] : 0.f;
+#pragma unroll
+            for (int j = 0; j < NT; ++j)
+                if (j < p.m) outp[size_t(j) * p.N + n] = rv[j] + (acc[j] + acc[NT + j]);
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    }
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "n"(kTmemCols) : "memory");
+    }
+    if (tid == 0 && s_err && p.err) atomicExch(p.err, 1);
+}
+
 // ---- host: tensor maps through the driver entry point (no link-time dependency on libcuda)
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -439,6 +746,35 @@ int32_t launch_ts(const __half* A, const __half* Alo, const Tc5Params& p, cudaSt
     return FORGE_OK;
 }
 
+template <int QUANT, int NT>
+int32_t launch_small(const __half* A, const __half* Alo, const Tc5Params& p, cudaStream_t st) {
+    CUtensorMap mh, ml;
+    FORGE_TRY(make_map(&mh, A, p.m, p.K, NT));
+    FORGE_TRY(make_map(&ml, Alo, p.m, p.K, NT));
+    // the quantised bytes as a 2-D byte tensor {row bytes, N}, box {128 bytes, 128 rows}
+    CUtensorMap mw;
+    {
+        EncodeTiledFn fn = encode_fn();
+        if (!fn) { set_error("cuTensorMapEncodeTiled is not available from this driver"); return FORGE_ERR_UNSUPPORTED; }
+        const cuuint64_t row_bytes = QUANT == FORGE_Q4_0 ? cuuint64_t(p.K) / 2 : cuuint64_t(p.K);
+        const cuuint64_t dims[2] = {row_bytes, cuuint64_t(p.N)};
+        const cuuint64_t strides[1] = {row_bytes};
+        const cuuint32_t box[2] = {128, 128};
+        const cuuint32_t estr[2] = {1, 1};
+        CUresult r = fn(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(p.qs), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled failed for the weight bytes (%d)", int(r)); return FORGE_ERR_CUDA; }
+    }
+    constexpr int kQStage = (QUANT == FORGE_Q4_0 ? 1 : 2) * 128 * 128, kQStages = QUANT == FORGE_Q4_0 ? 6 : 4;
+    const size_t smem = size_t(4) * (NT == 16 ? 2 : 1) * 2 * NT * BK * 2 + size_t(kQStages) * kQStage + 1024;
+    auto kern = gemm_small_kernel<QUANT, NT>;
+    FORGE_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+    dim3 grid((p.N + 127) / 128, 1, p.ksplit);
+    kern<<<grid, kSmallThreads, smem, st>>>(mh, ml, mw, p);
+    FORGE_LAUNCH_CHECK();
+    return FORGE_OK;
+}
+
 }  // namespace
 
 bool gemm_tc5_supported(const QWeight& w) { return w.K % BK == 0 && w.K >= BK; }
@@ -457,6 +793,11 @@ int32_t gemm_tc5(float* out, const __half* A, const __half* Alo, const QWeight& 
     if (act_hi && ((w.N & 1) || resid)) { set_error("tcgen05 gemm: the SiLU epilogue needs gate/up row pairs and no residual"); return FORGE_ERR_INVALID_ARG; }
     Tc5Params p{out, resid, w.qs, w.d, w.sf, m, w.N, w.K, err, ksplit, part_stride, act_hi, act_lo};
     const bool split = Alo != nullptr;
+    // a few rows: the weight-streaming form (exact integer weights, block scales applied to the block sums in f32)
+    if (split && m <= 32 && w.quant != FORGE_KQ_SOA) {
+        if (w.quant == FORGE_Q8_0) return m <= 16 ? launch_small<FORGE_Q8_0, 16>(A, Alo, p, st) : launch_small<FORGE_Q8_0, 32>(A, Alo, p, st);
+        return m <= 16 ? launch_small<FORGE_Q4_0, 16>(A, Alo, p, st) : launch_small<FORGE_Q4_0, 32>(A, Alo, p, st);
+    }
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);

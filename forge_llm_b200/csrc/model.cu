@@ -535,8 +535,9 @@ int32_t decode_launches(ForgeModel* m, ForgeKV* kv, int batch, bool greedy, bool
         return gemv_tc(w, EPI_TP_PUSH, a, m->split, m->d_err, st);
     };
     if (batch >= 2 && !pt && m->uniform_basic && !m->trace_on) {
-        // up to 32 sequences: the streaming product, sixteen rows per pass over the weights; beyond: the tensor-core GEMM
-        if (batch > 2 * kBatchGroup && m->lm_head.qs) return decode_launches_gemm(m, kv, batch, greedy, record);
+        // up to 8 sequences: the mma.sync streaming product; beyond: the tcgen05 products (their weight-streaming form up to
+        // 32 rows, measured faster from about 16 rows on; the tile form for more)
+        if (batch > kBatchGroup / 2 && m->lm_head.qs) return decode_launches_gemm(m, kv, batch, greedy, record);
         return decode_launches_batched(m, kv, batch, greedy, record);
     }
     FORGE_TRY(embedding_rows(m->d_hidden, m->embed, pt ? pt->tok : m->d_tok, batch, m->h, record ? m->d_hist : nullptr, m->d_step, st));
