@@ -250,7 +250,7 @@ int32_t forge_attention_flash(float* out, const float* q, const uint16_t* k_cach
     FORGE_TRY(need_device());
     if (!out || !q || !k_cache || !v_cache || seq_len <= 0 || num_heads <= 0 || num_kv_heads <= 0) { set_error("bad argument to forge_attention_flash"); return FORGE_ERR_INVALID_ARG; }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    int splits = attn_decode_splits((seq_len + FORGE_KV_PAGE - 1) / FORGE_KV_PAGE, num_kv_heads, 148);
+    int splits = attn_decode_splits((seq_len + FORGE_KV_PAGE - 1) / FORGE_KV_PAGE, num_kv_heads, 148, head_dim, num_heads / num_kv_heads);
     AsyncBuf ws(st), cnt(st);
     FORGE_CUDA(ws.alloc(sizeof(float) * attn_decode_ws_floats(1, num_heads, head_dim, splits)));
     FORGE_CUDA(cnt.alloc(sizeof(int) * num_kv_heads));
@@ -298,7 +298,7 @@ int32_t forge_attention_sliding(float* out, const float* q, const uint16_t* k_ca
     FORGE_TRY(need_device());
     if (!out || !q || !k_cache || !v_cache || seq_len <= 0 || window <= 0 || num_heads <= 0 || num_kv_heads <= 0) { set_error("bad argument to forge_attention_sliding"); return FORGE_ERR_INVALID_ARG; }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    int splits = attn_decode_splits((seq_len + FORGE_KV_PAGE - 1) / FORGE_KV_PAGE, num_kv_heads, 148);
+    int splits = attn_decode_splits((seq_len + FORGE_KV_PAGE - 1) / FORGE_KV_PAGE, num_kv_heads, 148, head_dim, num_heads / num_kv_heads);
     AsyncBuf ws(st), cnt(st);
     FORGE_CUDA(ws.alloc(sizeof(float) * attn_decode_ws_floats(1, num_heads, head_dim, splits)));
     FORGE_CUDA(cnt.alloc(sizeof(int) * num_kv_heads));

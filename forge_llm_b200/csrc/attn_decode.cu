@@ -324,10 +324,21 @@ __global__ void __launch_bounds__(kBlock, (HD == 128 || GC == 4) ? 2 : 3) attn_d
 
 }  // namespace
 
-int attn_decode_splits(int pages, int groups, int sms) {
-    // about three CTAs per SM (what the kernel's registers and page ring allow to be resident), never more splits than pages
-    const int want = (3 * sms + groups - 1) / std::max(1, groups);
-    return std::max(1, std::min({want, pages, kMaxSplits}));
+int attn_decode_splits(int pages, int groups, int sms, int hd, int heads_per_group) {
+    // CTAs run in rounds over the resident slots (three CTAs per SM; two with 128-wide heads or four query heads per pass):
+    // pick the split count whose rounds waste the least, a CTA's work being 1 / splits of a sequence plus a few per cent
+    // per extra split for the merge.  Never more splits than pages.
+    const int per_sm = (hd == 128 || heads_per_group >= 3) ? 2 : 3;
+    const long slots = long(sms) * per_sm;
+    const int smax = std::max(1, std::min(pages, kMaxSplits));
+    int best = 1;
+    double best_cost = 1e30;
+    for (int s = 1; s <= smax; ++s) {
+        const long rounds = (long(groups) * s + slots - 1) / slots;
+        const double cost = double(rounds) / s * (1.0 + 0.03 * (s - 1));
+        if (cost < best_cost - 1e-12) { best_cost = cost; best = s; }
+    }
+    return best;
 }
 
 size_t attn_decode_ws_floats(int batch, int nq, int hd, int splits) { return size_t(batch) * nq * splits * (hd + 2); }
@@ -451,7 +462,7 @@ extern "C" int32_t forge_attention_flash_static(float* out, const float* q, cons
     StaticScratch* sc = nullptr;
     FORGE_TRY(static_scratch(&sc));
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    const int splits = std::min(kStaticMaxSplits, attn_decode_splits((seq_len + FORGE_KV_PAGE - 1) / FORGE_KV_PAGE, num_kv_heads, 148));
+    const int splits = std::min(kStaticMaxSplits, attn_decode_splits((seq_len + FORGE_KV_PAGE - 1) / FORGE_KV_PAGE, num_kv_heads, 148, head_dim, num_heads / num_kv_heads));
     // the tickets must start at zero; the partials are fully rewritten by every call that reads them
     FORGE_CUDA(cudaMemsetAsync(sc->counters, 0, sizeof(int) * num_kv_heads, st));
     AttnDecodeArgs a{out, q, reinterpret_cast<const __half*>(k_cache), reinterpret_cast<const __half*>(v_cache), nullptr, 0, nullptr,

@@ -233,7 +233,7 @@ struct AttnDecodeArgs {
     int* err = nullptr;                      // set when a bounded wait gave up
 };
 // context splits for `groups` = batch * kv_heads independent (sequence, KV head) pairs over `pages` pages
-int attn_decode_splits(int pages, int groups, int sms);
+int attn_decode_splits(int pages, int groups, int sms, int hd, int heads_per_group);
 size_t attn_decode_ws_floats(int batch, int nq, int hd, int splits);
 // Tiled tensor map over an fp16 K or V pool of `rows` rows of kv_heads * head_dim values: dimensions {head_dim, kv_heads,
 // rows}, box {head_dim, 1, 64} = one page of one KV head (`out`: a CUtensorMap in host memory)

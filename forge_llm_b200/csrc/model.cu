@@ -951,7 +951,7 @@ int32_t forge_kv_create(ForgeModel* m, int32_t max_seq, int32_t batch, ForgeKV**
     // split-KV: enough CTAs to fill the SMs
     int sms = 148;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, m->device);
-    kv->splits = attn_decode_splits(kv->pages_per_seq, batch * m->nkv, sms);
+    kv->splits = attn_decode_splits(kv->pages_per_seq, batch * m->nkv, sms, m->hd, m->nq / m->nkv);
     if (cudaMalloc(&kv->attn_ws, sizeof(float) * attn_decode_ws_floats(batch, m->nq, m->hd, kv->splits)) != cudaSuccess ||
         cudaMalloc(&kv->attn_counters, sizeof(int) * batch * m->nkv) != cudaSuccess) { set_error("attention workspace allocation failed"); return fail(FORGE_ERR_CUDA); }
     cudaMemsetAsync(kv->attn_counters, 0, sizeof(int) * batch * m->nkv, m->stream);
