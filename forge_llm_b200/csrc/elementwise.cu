@@ -91,11 +91,14 @@ __global__ void __launch_bounds__(256) add_parts_norm_kernel(float* __restrict__
         const int e = (threadIdx.x + i * 256) * 4;
         v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
         if (e < n) {
+            // all loads first (one memory round trip), then the sum in slice order
             v[i] = *reinterpret_cast<const float4*>(x + e);
-            for (int s = 0; s < nparts; ++s) {
-                const float4 a = *reinterpret_cast<const float4*>(pr + size_t(s) * pstride + e);
-                v[i].x += a.x; v[i].y += a.y; v[i].z += a.z; v[i].w += a.w;
-            }
+            float4 a[4];
+#pragma unroll
+            for (int s = 0; s < 4; ++s)
+                a[s] = s < nparts ? *reinterpret_cast<const float4*>(pr + size_t(s) * pstride + e) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int s = 0; s < 4; ++s) { v[i].x += a[s].x; v[i].y += a[s].y; v[i].z += a[s].z; v[i].w += a[s].w; }
             *reinterpret_cast<float4*>(x + e) = v[i];
         }
         ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
@@ -216,7 +219,8 @@ __global__ void qkv_post_rows_kernel(const float* __restrict__ qkv, const float*
     const int pos = seq_len[b];
     const float2* src = reinterpret_cast<const float2*>(qkv + size_t(b) * (qk + 2 * kv));
     const size_t prow = (size_t(page_table[size_t(b) * pages_per_seq + pos / FORGE_KV_PAGE]) * FORGE_KV_PAGE + pos % FORGE_KV_PAGE) * kv;
-    for (int i = threadIdx.x; i < npairs; i += blockDim.x) {
+    // one pair per thread: blockIdx.y walks the row in pieces of blockDim.x pairs (a few rows must not mean a few CTAs)
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < npairs; i += gridDim.y * blockDim.x) {
         float2 v = src[i];
         int col = 2 * i;
         if (bias) { v.x += bias[col]; v.y += bias[col + 1]; }
@@ -383,7 +387,7 @@ int32_t rms_norm_f16(__half* out, __half* lo, const float* in, const float* w, i
 int32_t add_parts_rms_norm_f16(float* hidden, const float* parts, int nparts, size_t pstride, __half* out, __half* lo, const float* w,
                                int rows, int n, float eps, cudaStream_t st) {
     if (rows <= 0) return FORGE_OK;
-    if (n % 4 || n > 8192) { set_error("add_parts_rms_norm: row length %d unsupported", n); return FORGE_ERR_SHAPE; }
+    if (n % 4 || n > 8192 || nparts < 1 || nparts > 4) { set_error("add_parts_rms_norm: row length %d / %d slices unsupported", n, nparts); return FORGE_ERR_SHAPE; }
     if (n <= 2048) add_parts_norm_kernel<2><<<rows, 256, 0, st>>>(hidden, parts, nparts, pstride, out, lo, w, n, eps);
     else if (n <= 4096) add_parts_norm_kernel<4><<<rows, 256, 0, st>>>(hidden, parts, nparts, pstride, out, lo, w, n, eps);
     else add_parts_norm_kernel<8><<<rows, 256, 0, st>>>(hidden, parts, nparts, pstride, out, lo, w, n, eps);
@@ -439,7 +443,8 @@ int32_t qkv_post(const float* qkv, int m, int base_pos, const float* bias, const
 int32_t qkv_post_rows(const float* qkv, int batch, const float* bias, const float* rope, float* q_out, __half* k_pool, __half* v_pool,
                       const int32_t* page_table, const int32_t* seq_len, int pages_per_seq, int qk, int kv, int hd, cudaStream_t st) {
     if (batch <= 0) return FORGE_OK;
-    qkv_post_rows_kernel<<<batch, 256, 0, st>>>(qkv, bias, reinterpret_cast<const float2*>(rope), q_out, k_pool, v_pool, page_table, seq_len,
+    const int npairs = (qk + 2 * kv) / 2;
+    qkv_post_rows_kernel<<<dim3(batch, (npairs + 255) / 256), 256, 0, st>>>(qkv, bias, reinterpret_cast<const float2*>(rope), q_out, k_pool, v_pool, page_table, seq_len,
                                                 pages_per_seq, qk, kv, hd);
     FORGE_LAUNCH_CHECK();
     return FORGE_OK;
