@@ -202,7 +202,8 @@ int32_t qkv_post(const float* qkv, int m, int base_pos, const float* bias, const
                  __half* k_pool, __half* v_pool, const int32_t* page_row, int qk, int kv, int hd, cudaStream_t st, int nparts = 1, size_t pstride = 0);
 // batched decode QKV epilogue: row b is sequence b at position seq_len[b]; q stays f32, k/v go to the sequence's page
 int32_t qkv_post_rows(const float* qkv, int batch, const float* bias, const float* rope, float* q_out, __half* k_pool, __half* v_pool,
-                      const int32_t* page_table, const int32_t* seq_len, int pages_per_seq, int qk, int kv, int hd, cudaStream_t st);
+                      const int32_t* page_table, const int32_t* seq_len, int pages_per_seq, int qk, int kv, int hd, cudaStream_t st, int nparts = 1,
+                      size_t pstride = 0);  // nparts > 1: the product arrives as K-slice partials, pstride floats apart
 int32_t argmax_last(uint32_t* result, const float* logits, int n, int batch, cudaStream_t st);
 // many-CTA form; sval/sidx: [batch][kArgmaxSlices] scratch, ticket: [batch] zero-initialised counters
 constexpr int kArgmaxSlices = 148;

@@ -210,7 +210,7 @@ __global__ void qkv_post_kernel(const float* __restrict__ qkv, int nparts, size_
 
 // batched decode glue: row b of the fused [q;k;v] product belongs to sequence b at position seq_len[b]:
 // (+bias) -> RoPE on q,k -> q f32 [b][qk], k/v into that sequence's cache page
-__global__ void qkv_post_rows_kernel(const float* __restrict__ qkv, const float* __restrict__ bias, const float2* __restrict__ rope,
+__global__ void qkv_post_rows_kernel(const float* __restrict__ qkv, int nparts, size_t pstride, const float* __restrict__ bias, const float2* __restrict__ rope,
                                      float* __restrict__ q_out, __half* __restrict__ k_pool, __half* __restrict__ v_pool,
                                      const int32_t* __restrict__ page_table, const int32_t* __restrict__ seq_len, int pages_per_seq,
                                      int qk, int kv, int hd) {
@@ -222,6 +222,13 @@ __global__ void qkv_post_rows_kernel(const float* __restrict__ qkv, const float*
     // one pair per thread: blockIdx.y walks the row in pieces of blockDim.x pairs (a few rows must not mean a few CTAs)
     for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < npairs; i += gridDim.y * blockDim.x) {
         float2 v = src[i];
+        {   // further K-slice partials of the product (pstride floats apart), added in slice order; loads first
+            float2 a[3];
+#pragma unroll
+            for (int s = 0; s < 3; ++s) a[s] = s + 1 < nparts ? *reinterpret_cast<const float2*>(qkv + size_t(s + 1) * pstride + size_t(b) * (qk + 2 * kv) + 2 * i) : make_float2(0.f, 0.f);
+#pragma unroll
+            for (int s = 0; s < 3; ++s) { v.x += a[s].x; v.y += a[s].y; }
+        }
         int col = 2 * i;
         if (bias) { v.x += bias[col]; v.y += bias[col + 1]; }
         int region = 0;
@@ -441,10 +448,12 @@ int32_t qkv_post(const float* qkv, int m, int base_pos, const float* bias, const
     return FORGE_OK;
 }
 int32_t qkv_post_rows(const float* qkv, int batch, const float* bias, const float* rope, float* q_out, __half* k_pool, __half* v_pool,
-                      const int32_t* page_table, const int32_t* seq_len, int pages_per_seq, int qk, int kv, int hd, cudaStream_t st) {
+                      const int32_t* page_table, const int32_t* seq_len, int pages_per_seq, int qk, int kv, int hd, cudaStream_t st, int nparts,
+                      size_t pstride) {
     if (batch <= 0) return FORGE_OK;
     const int npairs = (qk + 2 * kv) / 2;
-    qkv_post_rows_kernel<<<dim3(batch, (npairs + 255) / 256), 256, 0, st>>>(qkv, bias, reinterpret_cast<const float2*>(rope), q_out, k_pool, v_pool, page_table, seq_len,
+    if (nparts < 1 || nparts > 4) { set_error("qkv_post_rows: %d slices unsupported", nparts); return FORGE_ERR_INVALID_ARG; }
+    qkv_post_rows_kernel<<<dim3(batch, (npairs + 255) / 256), 256, 0, st>>>(qkv, nparts, pstride, bias, reinterpret_cast<const float2*>(rope), q_out, k_pool, v_pool, page_table, seq_len,
                                                 pages_per_seq, qk, kv, hd);
     FORGE_LAUNCH_CHECK();
     return FORGE_OK;

@@ -485,9 +485,13 @@ int32_t decode_launches_gemm(ForgeModel* m, ForgeKV* kv, int batch, bool greedy,
         ForgeLayer& L = m->layers[l];
         __half* kp = kv->k_pool + size_t(l) * kv->layer_stride;
         __half* vp = kv->v_pool + size_t(l) * kv->layer_stride;
-        FORGE_TRY(gemm_f16a(m->p_qkv, m->p_normed, nlo, L.qkv, n, nullptr, m->d_err, st));
-        FORGE_TRY(qkv_post_rows(m->p_qkv, n, L.qkv_bias, m->rope, m->d_q, kp, vp, kv->d_page_table, kv->d_seq_len, kv->pages_per_seq,
-                                m->qk, m->kv, m->hd, st));
+        // q/k/v as K slices like the prompt's (more CTAs for a product of few row tiles; the epilogue adds the slices)
+        const int qks = (c.tp_world == 1 && split && gemm_tc5_supported(L.qkv) && m->p_qkv_parts) ? std::max(1, std::min(4, L.qkv.K / 1024)) : 1;
+        const size_t qstride = size_t(n) * (m->qk + 2 * m->kv);
+        if (qks > 1) FORGE_TRY(gemm_tc5(m->p_qkv_parts, m->p_normed, nlo, L.qkv, n, nullptr, m->d_err, st, qks, qstride));
+        else FORGE_TRY(gemm_f16a(m->p_qkv, m->p_normed, nlo, L.qkv, n, nullptr, m->d_err, st));
+        FORGE_TRY(qkv_post_rows(qks > 1 ? m->p_qkv_parts : m->p_qkv, n, L.qkv_bias, m->rope, m->d_q, kp, vp, kv->d_page_table, kv->d_seq_len,
+                                kv->pages_per_seq, m->qk, m->kv, m->hd, st, qks, qstride));
         AttnDecodeArgs da{m->d_attn, m->d_q, kp, vp, kv->d_page_table, kv->pages_per_seq, kv->d_seq_len, 0,
                           n, m->nq, m->nkv, m->hd, kv->max_seq, kv->attn_ws, kv->attn_counters, kv->splits, c.sliding_window};
         da.map_k = kv->k_map; da.map_v = kv->v_map; da.row_base = int(size_t(l) * kv->num_pages * FORGE_KV_PAGE); da.err = m->d_err;
