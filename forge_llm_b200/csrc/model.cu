@@ -467,10 +467,11 @@ int32_t decode_launches_batched(ForgeModel* m, ForgeKV* kv, int batch, bool gree
     return step_advance(kv->d_seq_len, n, m->d_step, st, sums ? m->d_tpx_step : nullptr);
 }
 
-// A decode step of more than 32 sequences: every projection is one tensor-core product over the batch rows (the rule
-// the generated module applies to prompts, PREFILL_BATCH_THRESHOLD, emit.rs:203-206 and :4576-4587), the weights
-// dequantised once per step.  Operator order of forward() (emit.rs:4029-4500) with the batched products of
-// forward_prefill_batched (emit.rs:5118-5486); the rows live in the prompt scratch (fp16 hi/lo operands).
+// A decode step of more than 8 sequences: every projection is one tcgen05 product over the batch rows (the rule the
+// generated module applies to prompts, PREFILL_BATCH_THRESHOLD, emit.rs:203-206 and :4576-4587): up to 32 rows its
+// weight-streaming form, beyond that the tile form; the weights are read once per step either way.  Operator order of
+// forward() (emit.rs:4029-4500) with the batched products of forward_prefill_batched (emit.rs:5118-5486); the rows live
+// in the prompt scratch (fp16 hi/lo operands).
 int32_t decode_launches_gemm(ForgeModel* m, ForgeKV* kv, int batch, bool greedy, bool record) {
     const ForgeModelConfig& c = m->cfg;
     cudaStream_t st = m->stream;
