@@ -67,6 +67,28 @@ __device__ __forceinline__ void tma_page(void* dst, const CUtensorMap* map, int 
     asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
                  ::"r"(smem_u32(dst)), "l"(map), "r"(0), "r"(kvh), "r"(row), "r"(smem_u32(bar)) : "memory");
 }
+// the result in the form the caller asked for: f32, or fp16 hi (+ lo)
+__device__ __forceinline__ void store_out(const AttnDecodeArgs& a, size_t i, float x) {
+    if (a.out16) {
+        const __half h = __float2half_rn(x);
+        a.out16[i] = h;
+        if (a.out16_lo) a.out16_lo[i] = __float2half_rn(x - __half2float(h));
+    } else {
+        a.out[i] = x;
+    }
+}
+__device__ __forceinline__ void store_out2(const AttnDecodeArgs& a, size_t i, float2 x) {
+    if (a.out16) {
+        const __half2 h = __floats2half2_rn(x.x, x.y);
+        *reinterpret_cast<__half2*>(a.out16 + i) = h;
+        if (a.out16_lo) {
+            const float2 hf = __half22float2(h);
+            *reinterpret_cast<__half2*>(a.out16_lo + i) = __floats2half2_rn(x.x - hf.x, x.y - hf.y);
+        }
+    } else {
+        *reinterpret_cast<float2*>(a.out + i) = x;
+    }
+}
 __device__ __forceinline__ void csync() { asm volatile("bar.sync 1, %0;" ::"n"(kThreads) : "memory"); }
 
 // SW: sliding-window instantiation (the full-attention one carries no window tests)
@@ -261,7 +283,7 @@ __global__ void __launch_bounds__(kBlock, (HD == 128 || GC == 4) ? 2 : 3) attn_d
                 for (int pp = 0; pp < PARTS; ++pp) { M = fmaxf(M, s_m[pp][g]); L += s_l[pp][g] * s_w[pp][g]; }
             }
             if (a.splits == 1) {
-                a.out[(size_t(b) * a.nq + head) * HD + dd] = A * (1.0f / L);
+                store_out(a, (size_t(b) * a.nq + head) * HD + dd, A * (1.0f / L));
             } else {
                 float* w = a.ws + ((size_t(b) * a.nq + head) * a.splits + split) * (HD + 2);
                 w[2 + dd] = A;
@@ -318,7 +340,7 @@ __global__ void __launch_bounds__(kBlock, (HD == 128 || GC == 4) ? 2 : 3) attn_d
             A.x += pa[s].x * wt;
             A.y += pa[s].y * wt;
         }
-        if (on) *reinterpret_cast<float2*>(a.out + (size_t(b) * a.nq + kvh * G + g) * HD + 2 * d2) = A;
+        if (on) store_out2(a, (size_t(b) * a.nq + kvh * G + g) * HD + 2 * d2, A);
     }
 }
 

@@ -232,6 +232,9 @@ struct AttnDecodeArgs {
     const void* map_k = nullptr; const void* map_v = nullptr;
     int row_base = 0;
     int* err = nullptr;                      // set when a bounded wait gave up
+    // out16 != null: the result is stored as fp16 hi (+ lo) rows [batch][nq*hd] (the operand of a tensor-core product)
+    // instead of f32 `out`
+    __half* out16 = nullptr; __half* out16_lo = nullptr;
 };
 // context splits for `groups` = batch * kv_heads independent (sequence, KV head) pairs over `pages` pages
 int attn_decode_splits(int pages, int groups, int sms, int hd, int heads_per_group);

@@ -496,8 +496,8 @@ int32_t decode_launches_gemm(ForgeModel* m, ForgeKV* kv, int batch, bool greedy,
         AttnDecodeArgs da{m->d_attn, m->d_q, kp, vp, kv->d_page_table, kv->pages_per_seq, kv->d_seq_len, 0,
                           n, m->nq, m->nkv, m->hd, kv->max_seq, kv->attn_ws, kv->attn_counters, kv->splits, c.sliding_window};
         da.map_k = kv->k_map; da.map_v = kv->v_map; da.row_base = int(size_t(l) * kv->num_pages * FORGE_KV_PAGE); da.err = m->d_err;
+        da.out16 = m->p_attn16; da.out16_lo = alo;   // straight into the o-projection's operand form
         FORGE_TRY(attn_decode(da, st));
-        FORGE_TRY(f32_to_f16(m->p_attn16, alo, m->d_attn, size_t(n) * m->qk, st));
         FORGE_TRY(row_sliced_gemm_norm(m, L.o, m->p_attn16, alo, n, L.ffn_norm, nlo, st));
         FORGE_TRY(gateup_silu(m, L.gateup, nlo, flo, n, st));
         FORGE_TRY(row_sliced_gemm_norm(m, L.down, m->p_act16, flo, n, l + 1 < c.num_layers ? m->layers[l + 1].attn_norm : m->final_norm, nlo, st));
