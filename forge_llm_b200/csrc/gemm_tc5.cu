@@ -546,12 +546,9 @@ __global__ void __launch_bounds__(kSmallThreads, 1) gemm_small_kernel(const __gr
         // ---------------- dequantise (warps 2..9): integer weights as fp16 into tensor memory, lane = weight row
         const int quad = warp & 3, blk = (warp - 2) >> 2;
         const int r = quad * 32 + lane;
-        const int n = n0 + r;
-        const bool n_ok = n < p.N;
         constexpr int QV = QUANT == FORGE_Q4_0 ? 1 : 2;   // 16-byte pieces per block
         constexpr int kUnroll = 8;
         static_assert(kUnroll % G == 0 && (WG * G) % kUnroll == 0 && kUnroll % kSuper == 0, "one unrolled round covers whole groups and stages");
-        (void)n; (void)n_ok;
         bool ok = true;
         const uint32_t lane_base = tmem + (uint32_t(quad * 32) << 16) + kWBase + uint32_t(blk * 16);
         const uint32_t sw7 = uint32_t(r & 7);

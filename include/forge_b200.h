@@ -169,7 +169,10 @@ int32_t forge_attention_flash_static(float* out, const float* q, const uint16_t*
                                      const uint16_t* v_cache, int32_t seq_len, int32_t num_heads,
                                      int32_t num_kv_heads, int32_t head_dim, void* stream);
 /* attention_flash_batch(output, q_batch, k_cache, v_cache, .., m, base_pos, ...)  E:755-883.
- * Query row r sits at position base_pos + r and sees cache positions <= its own. */
+ * Query row r sits at position base_pos + r and sees cache positions <= its own.  The caches hold base_pos + m rows
+ * (rows past that are never read).  The call converts the queries to fp16 hi + lo pairs in a temporary buffer of the
+ * stream-ordered allocator, runs the tensor-core kernel and synchronises the stream to read the kernel's status
+ * (FORGE_ERR_TIMEOUT if a bounded device-side wait gave up); the sliding-window twin below does the same. */
 int32_t forge_attention_flash_batch(float* out, const float* q_batch, const uint16_t* k_cache,
                                     const uint16_t* v_cache, int32_t m, int32_t base_pos,
                                     int32_t num_heads, int32_t num_kv_heads, int32_t head_dim,
