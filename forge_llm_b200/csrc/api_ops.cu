@@ -189,7 +189,7 @@ int32_t forge_matmul_decode_batch(float* out, int32_t nb, const float* in, Forge
             w->bsplit.max_slices = kGemvMaxSlices;
         }
     }
-    FORGE_TRY(gemv_batch_pack(w->bact, in, size_t(w->tiled.K), nb, w->tiled.K, w->tiled.quant, 0, nullptr, 0.f, st));
+    FORGE_TRY(gemv_batch_pack(w->bact, const_cast<float*>(in), size_t(w->tiled.K), nb, w->tiled.K, w->tiled.quant, 0, nullptr, 0.f, st));
     return gemv_batch(w->tiled, w->bact, nb, out, nullptr, w->bsplit, w->err, st);
 }
 

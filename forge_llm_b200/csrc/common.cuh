@@ -178,8 +178,26 @@ size_t gemv_batch_act_words(int K, int nb);          // uint2 entries the packed
 size_t gemv_batch_scratch_floats(int N, int K, int quant, int sms);   // split-K scratch a matrix needs (0: not split)
 size_t gemv_batch_tickets(int N);
 int gemv_batch_slices(int groups, int chunks, int sms);
-int32_t gemv_batch_pack(uint2* dst, const float* x, size_t x_stride, int nb, int K, int quant, int mode, const float* norm_w, float eps, cudaStream_t st);
-int32_t gemv_batch(const QTiled& w, const uint2* act, int nb, float* out, const float* resid, const GemvSplit& sp, int* err, cudaStream_t st);
+// Tensor-parallel sum of a batched product over peer memory, fused into its two neighbours: the product's epilogue stores
+// every finished value as a {value, tag} pair into every rank's exchange buffer (push), and the packing kernel of the
+// next product forms hidden + sum over ranks while it reads its rows (consume), polling - bounded - for pairs whose tag is
+// not the expected one yet.  Element (row b, column j) of rank r's part lies at base + r * cap + b * N + j.
+struct BatchTp {
+    uint2* const* peer_ll = nullptr;         // device array [world]: every rank's exchange buffer (push)
+    const uint2* local_ll = nullptr;         // this rank's exchange buffer (consume)
+    size_t base = 0, cap = 0;                // pairs
+    int world = 0, rank = 0;
+    const uint32_t* step_counter = nullptr;  // device, advanced once per decode step
+    uint32_t step_mul = 0, step_add = 0;     // tag = *step_counter * step_mul + step_add
+    uint32_t wait_limit = 1u << 20;
+    int* err = nullptr;
+};
+// consume != null (mode 1 only): the rows are x + the ranks' pairs, and that sum is written back to x first
+int32_t gemv_batch_pack(uint2* dst, float* x, size_t x_stride, int nb, int K, int quant, int mode, const float* norm_w, float eps, cudaStream_t st,
+                        const BatchTp* consume = nullptr);
+// push != null: the product goes to the ranks' exchange buffers instead of `out`
+int32_t gemv_batch(const QTiled& w, const uint2* act, int nb, float* out, const float* resid, const GemvSplit& sp, int* err, cudaStream_t st,
+                   const BatchTp* push = nullptr);
 
 // ------------------------------------------------------------------ elementwise
 int32_t rms_norm_f32(float* out, const float* in, const float* w, int rows, int n, float eps, cudaStream_t st);

@@ -52,6 +52,7 @@ struct BatchParams {
     int K, N, kb, bt, groups, slices, units, nb;
     int bands16;             // 16-row bands the packed matrix really has (the last 128-row group may be short of them)
     int* err;
+    BatchTp tp;              // tp.peer_ll != null: the product is pushed to the ranks' exchange buffers
 };
 
 struct BShared {
@@ -239,6 +240,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_batch_kernel(BatchParams p) 
             }
         }
         if (finish) {
+            const uint32_t tag = p.tp.peer_ll ? __ldcg(p.tp.step_counter) * p.tp.step_mul + p.tp.step_add : 0u;
 #pragma unroll
             for (int cg = 0; cg < NCG; ++cg) {
                 const int b = 4 * cg + t;
@@ -248,7 +250,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_batch_kernel(BatchParams p) 
                     const int row = row0 + 8 * hh;
                     if (row < p.N) {
                         const size_t off = size_t(b) * p.N + row;
-                        p.out[off] = (p.resid ? p.resid[off] : 0.f) + v[cg][hh];
+                        if (p.tp.peer_ll) {
+                            // one 8-byte store per rank: value and tag travel together (own buffer included)
+                            const uint2 pair = make_uint2(__float_as_uint(v[cg][hh]), tag);
+                            for (int r = 0; r < p.tp.world; ++r) p.tp.peer_ll[r][p.tp.base + size_t(p.tp.rank) * p.tp.cap + off] = pair;
+                        } else {
+                            p.out[off] = (p.resid ? p.resid[off] : 0.f) + v[cg][hh];
+                        }
                     }
                 }
             }
@@ -264,16 +272,35 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_batch_kernel(BatchParams p) 
 enum PackMode { PACK_PLAIN = 0, PACK_NORM = 1, PACK_SILU = 2 };
 
 template <int QUANT>
-__global__ void __launch_bounds__(256) act_pack_kernel(const float* __restrict__ x, size_t x_stride, const float* __restrict__ norm_w, float eps,
-                                                       int mode, int K, int ncg, uint2* __restrict__ dst) {
+__global__ void __launch_bounds__(256) act_pack_kernel(float* x, size_t x_stride, const float* __restrict__ norm_w, float eps,
+                                                       int mode, int K, int ncg, uint2* __restrict__ dst, BatchTp tp) {
     __shared__ float s_red[8];
     const int b = blockIdx.x;
-    const float* row = x + size_t(b) * x_stride;
+    float* row = x + size_t(b) * x_stride;
     float inv = 1.0f;
     if (mode == PACK_NORM) {
+        const uint32_t tag = tp.local_ll ? __ldcg(tp.step_counter) * tp.step_mul + tp.step_add : 0u;
         float ss = 0.f;
         for (int i = threadIdx.x * 4; i < K; i += blockDim.x * 4) {
-            const float4 v = *reinterpret_cast<const float4*>(row + i);
+            float4 v = *reinterpret_cast<const float4*>(row + i);
+            if (tp.local_ll) {
+                // the row-sliced product in front of this one: add the ranks' parts in rank order (four pairs = two 16-byte
+                // loads per rank, polled until all four carry this sum's tag) and put the residual stream back
+                for (int r = 0; r < tp.world; ++r) {
+                    const uint2* src = tp.local_ll + tp.base + size_t(r) * tp.cap + size_t(b) * K + i;
+                    uint4 p0 = make_uint4(0, 0, 0, 0), p1 = p0;
+                    bool ok = false;
+                    for (uint32_t it = 0; it < tp.wait_limit && !ok; ++it) {
+                        asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(p0.x), "=r"(p0.y), "=r"(p0.z), "=r"(p0.w) : "l"(src) : "memory");
+                        asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(p1.x), "=r"(p1.y), "=r"(p1.z), "=r"(p1.w) : "l"(src + 2) : "memory");
+                        ok = p0.y == tag && p0.w == tag && p1.y == tag && p1.w == tag;
+                        if (!ok && (it & 1023u) == 1023u && *reinterpret_cast<volatile int*>(tp.err)) break;   // somebody already gave up
+                    }
+                    if (!ok) { atomicExch(tp.err, 1); p0.x = p0.z = p1.x = p1.z = 0; }
+                    v.x += __uint_as_float(p0.x); v.y += __uint_as_float(p0.z); v.z += __uint_as_float(p1.x); v.w += __uint_as_float(p1.z);
+                }
+                *reinterpret_cast<float4*>(row + i) = v;
+            }
             ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
         }
 #pragma unroll
@@ -347,17 +374,21 @@ size_t gemv_batch_scratch_floats(int N, int K, int quant, int sms) {
 }
 size_t gemv_batch_tickets(int N) { return size_t((N + kGroupRows - 1) / kGroupRows) * kBandTiles; }
 
-int32_t gemv_batch_pack(uint2* dst, const float* x, size_t x_stride, int nb, int K, int quant, int mode, const float* norm_w, float eps, cudaStream_t st) {
+int32_t gemv_batch_pack(uint2* dst, float* x, size_t x_stride, int nb, int K, int quant, int mode, const float* norm_w, float eps, cudaStream_t st,
+                        const BatchTp* consume) {
     if (nb <= 0) return FORGE_OK;
     if (nb > kBatchRows || K % 32 || (quant != FORGE_Q8_0 && quant != FORGE_Q4_0)) { set_error("batched product: %d rows / K=%d / format %d unsupported", nb, K, quant); return FORGE_ERR_SHAPE; }
     const int ncg = gemv_batch_ncg(nb);
-    if (quant == FORGE_Q8_0) act_pack_kernel<FORGE_Q8_0><<<nb, 256, 0, st>>>(x, x_stride, norm_w, eps, mode, K, ncg, dst);
-    else act_pack_kernel<FORGE_Q4_0><<<nb, 256, 0, st>>>(x, x_stride, norm_w, eps, mode, K, ncg, dst);
+    if (consume && (mode != PACK_NORM || !consume->local_ll || size_t(nb) * K > consume->cap)) { set_error("batched product: bad tensor-parallel consume"); return FORGE_ERR_INVALID_ARG; }
+    const BatchTp tp = consume ? *consume : BatchTp();
+    if (quant == FORGE_Q8_0) act_pack_kernel<FORGE_Q8_0><<<nb, 256, 0, st>>>(x, x_stride, norm_w, eps, mode, K, ncg, dst, tp);
+    else act_pack_kernel<FORGE_Q4_0><<<nb, 256, 0, st>>>(x, x_stride, norm_w, eps, mode, K, ncg, dst, tp);
     FORGE_LAUNCH_CHECK();
     return FORGE_OK;
 }
 
-int32_t gemv_batch(const QTiled& w, const uint2* act, int nb, float* out, const float* resid, const GemvSplit& sp, int* err, cudaStream_t st) {
+int32_t gemv_batch(const QTiled& w, const uint2* act, int nb, float* out, const float* resid, const GemvSplit& sp, int* err, cudaStream_t st,
+                   const BatchTp* push) {
     if (nb <= 0) return FORGE_OK;
     if (nb > kBatchRows || w.K % 32 || (w.quant != FORGE_Q8_0 && w.quant != FORGE_Q4_0) || (w.bt != 1 && w.bt != core::kBandTiles)) {
         set_error("batched product: %d rows / K=%d / format %d unsupported", nb, w.K, w.quant);
@@ -368,6 +399,10 @@ int32_t gemv_batch(const QTiled& w, const uint2* act, int nb, float* out, const 
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     BatchParams p{};
     p.w = w.data; p.act = act; p.out = out; p.resid = resid; p.K = w.K; p.N = w.N; p.kb = w.K / 32; p.bt = w.bt; p.nb = nb; p.err = err;
+    if (push) {
+        if (!push->peer_ll || size_t(nb) * w.N > push->cap) { set_error("batched product: bad tensor-parallel push"); return FORGE_ERR_INVALID_ARG; }
+        p.tp = *push;
+    }
     // 128-row groups; in the 16-row layout the matrix is padded to whole 16-row bands only, so the last group may be
     // short of bands (the kernel copies the ones that exist; rows beyond N are never stored)
     const int bands16 = w.bt == 1 ? w.bands : w.bands * core::kBandTiles;

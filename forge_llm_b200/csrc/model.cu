@@ -414,21 +414,44 @@ int32_t ensure_batch_buffers(ForgeModel* m) {
     return FORGE_OK;
 }
 
-// out[n][N] (+ resid) = f(x)[n][K] . W^T in groups of sixteen rows
-int32_t batched_product(ForgeModel* m, const QTiled& w, const float* x, size_t x_stride, int mode, const float* norm_w, int n,
-                        float* out, const float* resid, cudaStream_t st) {
+// The pair exchange of sum `index` of a step (see BatchTp): slot = parity of the index, tag = step * (2 L + 1) + index + 1
+BatchTp batch_tp(const ForgeModel* m, int index) {
+    BatchTp t;
+    t.peer_ll = m->d_tpx_ll; t.local_ll = static_cast<const uint2*>(m->tpx_local);
+    t.cap = size_t(kTpxRows) * m->h;
+    t.base = tpx_region_pairs(m) + size_t(index & 1) * m->cfg.tp_world * t.cap;
+    t.world = m->cfg.tp_world; t.rank = m->cfg.tp_rank;
+    t.step_counter = m->d_tpx_step; t.step_mul = uint32_t(2 * m->cfg.num_layers + 1); t.step_add = uint32_t(index + 1);
+    t.wait_limit = m->wait_limit; t.err = m->d_err;
+    return t;
+}
+
+// out[n][N] (+ resid) = f(x)[n][K] . W^T in groups of sixteen rows.  consume / push: the tensor-parallel sum in front of
+// this product is taken in while its rows are packed / this product's values go to the ranks' exchange buffers (both
+// for a single group of rows only).
+int32_t batched_product(ForgeModel* m, const QTiled& w, float* x, size_t x_stride, int mode, const float* norm_w, int n,
+                        float* out, const float* resid, cudaStream_t st, const BatchTp* consume = nullptr, const BatchTp* push = nullptr) {
+    if ((consume || push) && n > kBatchGroup) { set_error("batched product: fused tensor-parallel sums take one group of rows"); return FORGE_ERR_INVALID_ARG; }
     for (int g0 = 0; g0 < n; g0 += kBatchGroup) {
         const int nb = std::min(kBatchGroup, n - g0);
-        FORGE_TRY(gemv_batch_pack(m->d_bact, x + size_t(g0) * x_stride, x_stride, nb, w.K, w.quant, mode, norm_w, m->cfg.rms_norm_eps, st));
-        FORGE_TRY(gemv_batch(w, m->d_bact, nb, out + size_t(g0) * w.N, resid ? resid + size_t(g0) * w.N : nullptr, m->bsplit, m->d_err, st));
+        FORGE_TRY(gemv_batch_pack(m->d_bact, x + size_t(g0) * x_stride, x_stride, nb, w.K, w.quant, mode, norm_w, m->cfg.rms_norm_eps, st, consume));
+        FORGE_TRY(gemv_batch(w, m->d_bact, nb, out ? out + size_t(g0) * w.N : nullptr, resid ? resid + size_t(g0) * w.N : nullptr, m->bsplit, m->d_err, st, push));
     }
     return FORGE_OK;
 }
 
 // hidden += W f(x) for a projection whose K dimension is sliced over the tensor-parallel ranks; `sum_index` numbers
 // the step's sums (the pair exchange tags them with it)
-int32_t batched_row_sliced(ForgeModel* m, const QTiled& w, const float* x, size_t x_stride, int mode, int n, int* sum_index, cudaStream_t st) {
+// (`pending`: set when the sum was only pushed - the next normalising product has to consume it)
+int32_t batched_row_sliced(ForgeModel* m, const QTiled& w, float* x, size_t x_stride, int mode, int n, int* sum_index, int* pending, cudaStream_t st) {
     if (m->cfg.tp_world == 1) return batched_product(m, w, x, x_stride, mode, nullptr, n, m->d_hidden, m->d_hidden, st);
+    if (m->tpx_ready && n <= kBatchGroup) {
+        // the product's epilogue pushes the pairs; the next product's packing adds them to the residual stream
+        const int index = (*sum_index)++;
+        const BatchTp push = batch_tp(m, index);
+        *pending = index;
+        return batched_product(m, w, x, x_stride, mode, nullptr, n, nullptr, nullptr, st, nullptr, &push);
+    }
     FORGE_TRY(batched_product(m, w, x, x_stride, mode, nullptr, n, m->d_part, nullptr, st));
     if (m->tpx_ready && n <= kTpxRows) {
         const int index = (*sum_index)++;
@@ -445,24 +468,31 @@ int32_t decode_launches_batched(ForgeModel* m, ForgeKV* kv, int batch, bool gree
     cudaStream_t st = m->stream;
     const int n = batch;
     enum { PLAIN = 0, NORM = 1, SILU = 2 };
-    int sums = 0;  // tensor-parallel sums issued in this step
+    int sums = 0;      // tensor-parallel sums issued in this step
+    int pending = -1;  // index of a sum that was pushed and not consumed yet
+    auto normed_product = [&](const QTiled& w, const float* norm_w, float* out) -> int32_t {   // out = W RMSNorm(hidden), taking a pending sum in
+        if (pending < 0) return batched_product(m, w, m->d_hidden, m->h, NORM, norm_w, n, out, nullptr, st);
+        const BatchTp consume = batch_tp(m, pending);
+        pending = -1;
+        return batched_product(m, w, m->d_hidden, m->h, NORM, norm_w, n, out, nullptr, st, &consume);
+    };
     FORGE_TRY(embedding_rows(m->d_hidden, m->embed, m->d_tok, n, m->h, record ? m->d_hist : nullptr, m->d_step, st));
     for (int l = 0; l < c.num_layers; ++l) {
         ForgeLayer& L = m->layers[l];
         __half* kp = kv->k_pool + size_t(l) * kv->layer_stride;
         __half* vp = kv->v_pool + size_t(l) * kv->layer_stride;
-        FORGE_TRY(batched_product(m, L.qkv_t, m->d_hidden, m->h, NORM, L.attn_norm, n, m->p_qkv, nullptr, st));
+        FORGE_TRY(normed_product(L.qkv_t, L.attn_norm, m->p_qkv));
         FORGE_TRY(qkv_post_rows(m->p_qkv, n, L.qkv_bias, m->rope, m->d_q, kp, vp, kv->d_page_table, kv->d_seq_len, kv->pages_per_seq,
                                 m->qk, m->kv, m->hd, st));
         AttnDecodeArgs da{m->d_attn, m->d_q, kp, vp, kv->d_page_table, kv->pages_per_seq, kv->d_seq_len, 0,
                           n, m->nq, m->nkv, m->hd, kv->max_seq, kv->attn_ws, kv->attn_counters, kv->splits, c.sliding_window};
         da.map_k = kv->k_map; da.map_v = kv->v_map; da.row_base = int(size_t(l) * kv->num_pages * FORGE_KV_PAGE); da.err = m->d_err;
         FORGE_TRY(attn_decode(da, st));
-        FORGE_TRY(batched_row_sliced(m, L.o_t, m->d_attn, m->qk, PLAIN, n, &sums, st));
-        FORGE_TRY(batched_product(m, L.gateup_t, m->d_hidden, m->h, NORM, L.ffn_norm, n, m->p_gu, nullptr, st));
-        FORGE_TRY(batched_row_sliced(m, L.down_t, m->p_gu, size_t(2) * m->ff, SILU, n, &sums, st));
+        FORGE_TRY(batched_row_sliced(m, L.o_t, m->d_attn, m->qk, PLAIN, n, &sums, &pending, st));
+        FORGE_TRY(normed_product(L.gateup_t, L.ffn_norm, m->p_gu));
+        FORGE_TRY(batched_row_sliced(m, L.down_t, m->p_gu, size_t(2) * m->ff, SILU, n, &sums, &pending, st));
     }
-    FORGE_TRY(batched_product(m, m->lm_head_t, m->d_hidden, m->h, NORM, m->final_norm, n, m->d_logits, nullptr, st));
+    FORGE_TRY(normed_product(m->lm_head_t, m->final_norm, m->d_logits));
     if (greedy) FORGE_TRY(argmax_slices(m->d_tok, m->d_logits, m->V, n, m->d_amax_val, m->d_amax_idx, m->d_amax_ticket, st));
     return step_advance(kv->d_seq_len, n, m->d_step, st, sums ? m->d_tpx_step : nullptr);
 }
