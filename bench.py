@@ -499,8 +499,8 @@ def run_tp(args, rank, world, local_rank, dist, barrier, reduce_max, peaks):
 
     out = {"model": configs.CONFIGS["c5"]["name"], "parallelism": f"tensor-parallel over {world} GPUs: q/k/v and gate/up by rows, o and down by input columns",
            "sum": "prompt: NCCL all-reduce after o and down on the model's stream; batch-1 decode: {value, tag} pairs stored into every peer's exchange "
-                  "buffer from the projection's epilogue, summed by the next kernel while it stages its input (no collective kernel); batched decode: one "
-                  "kernel per sum that stores the rows as pairs into the peers' buffers and adds the peers' pairs from its own",
+                  "buffer from the projection's epilogue, summed by the next kernel while it stages its input (no collective kernel); batched decode: the "
+                  "same, pairs stored from the batched product's epilogue and added by the next product's packing kernel",
            "scaling": "strong"}
     # parity of the cut: two layers, 8192-token vocabulary, against the CPU restatement (rank 0 checks)
     cp, blobp, _, _ = model_inputs("c5", layers=2, vocab=8192) if rank == 0 else (None, None, None, None)

@@ -235,9 +235,8 @@ int32_t forge_model_tp_init(ForgeModel* model, const uint8_t* id);
  * all `tp_world` handles (rank order, FORGE_TP_HANDLE_BYTES each, gathered over any host channel) it attaches them.
  * From then on the batch-1 decode step pushes each row-sliced projection's partial rows straight into the peers'
  * buffers from the GEMV epilogue (NVLink stores) and the next kernel adds the ranks' parts while it stages its input;
- * a batched decode step of up to 32 sequences sums its rows with one kernel that stores {value, tag} pairs into the
- * peers' buffers and adds what the peers stored into its own; prompts and larger batches keep the library
- * all-reduce.  Needs peer access between the GPUs (one process per GPU, all GPUs visible to every process). */
+ * a batched decode step of up to 8 sequences does the same through the batched product's epilogue and the next
+ * packing kernel; prompts and larger batches keep the library all-reduce.  Needs peer access between the GPUs (one process per GPU, all GPUs visible to every process). */
 #define FORGE_TP_HANDLE_BYTES 64
 int32_t forge_model_tp_exchange_export(ForgeModel* model, uint8_t* handle_out);
 int32_t forge_model_tp_exchange_attach(ForgeModel* model, const uint8_t* handles);
